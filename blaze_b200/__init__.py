@@ -1,0 +1,2 @@
+"""blaze_b200 — a Blackwell-native LLM inference runtime (PyTorch + hand-written sm_100a CUDA + NCCL/NVLink)."""
+__version__ = "0.1.0"

@@ -1,0 +1,113 @@
+"""One engine step's metadata: which rows belong to which sequence, where their KV goes.
+
+Plays the role of the reference's ``StepMeta`` (``crates/blaze/src/engine.rs:43``) and ``plan``
+(``engine.rs:1168``): built on the host, packed into ONE pinned int32 staging buffer and sent to
+the device with a single copy (``engine.rs:220-326``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+PAGE = 16
+
+
+@dataclass
+class SeqChunk:
+    """Rows of one sequence in this step."""
+    slot: int                 # row of the block table / recurrent-state table
+    tokens: Sequence[int]     # new token ids (1 for decode, k+1 for verify, a chunk for prefill)
+    start_pos: int            # position of tokens[0]  (== KV length before this step)
+    want_logits: int = 1      # how many trailing rows need logits (0 = headless prefill chunk)
+
+
+@dataclass
+class StepBatch:
+    tokens: torch.Tensor          # [T] int32
+    positions: torch.Tensor       # [T] int32
+    slot_mapping: torch.Tensor    # [T] int32  flat KV slot (page*16 + offset) of each new token
+    seq_of_row: torch.Tensor      # [T] int32  index into the per-sequence arrays
+    slots: torch.Tensor           # [B] int32
+    q_start: torch.Tensor         # [B+1] int32
+    ctx_len: torch.Tensor         # [B] int32 KV length including this step's rows
+    logit_rows: torch.Tensor      # [R] int32 rows whose logits are wanted
+    # host mirrors (python ints) for the oracle path and for planning
+    h_slots: List[int] = field(default_factory=list)
+    h_q_start: List[int] = field(default_factory=list)
+    h_ctx_len: List[int] = field(default_factory=list)
+    h_logit_rows: List[int] = field(default_factory=list)
+    num_rows: int = 0
+    max_q_len: int = 1
+    max_ctx: int = 0
+    h2d_bytes: int = 0
+
+    @property
+    def num_seqs(self) -> int:
+        return len(self.h_slots)
+
+    @property
+    def is_decode_only(self) -> bool:
+        return self.max_q_len == 1
+
+
+def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device, pinned: Optional[torch.Tensor] = None,
+                pad_rows_to: int = 0) -> StepBatch:
+    """Pack the step metadata into one int32 buffer and copy it to ``device`` once.
+
+    ``pad_rows_to`` pads T (with rows of a dummy sequence that writes to slot -1 … never; rows are
+    clamped to the last real row's data but flagged by ``seq_of_row = -1``) so that CUDA-graph
+    buckets see fixed shapes.
+    """
+    B = len(chunks)
+    T = sum(len(c.tokens) for c in chunks)
+    Tp = max(T, pad_rows_to)
+    tokens = np.zeros(Tp, np.int32)
+    positions = np.zeros(Tp, np.int32)
+    slot_map = np.full(Tp, -1, np.int32)
+    seq_of_row = np.full(Tp, -1, np.int32)
+    slots = np.zeros(B, np.int32)
+    q_start = np.zeros(B + 1, np.int32)
+    ctx_len = np.zeros(B, np.int32)
+    logit_rows: List[int] = []
+    r = 0
+    max_q = 1
+    max_ctx = 0
+    for b, c in enumerate(chunks):
+        n = len(c.tokens)
+        tokens[r:r + n] = np.asarray(c.tokens, dtype=np.int64).astype(np.int32)
+        pos = np.arange(c.start_pos, c.start_pos + n, dtype=np.int32)
+        positions[r:r + n] = pos
+        pages = block_table_host[c.slot, pos // PAGE]
+        slot_map[r:r + n] = pages * PAGE + pos % PAGE
+        seq_of_row[r:r + n] = b
+        slots[b] = c.slot
+        q_start[b + 1] = r + n
+        ctx_len[b] = c.start_pos + n
+        for j in range(n - c.want_logits, n):
+            logit_rows.append(r + j)
+        r += n
+        max_q = max(max_q, n)
+        max_ctx = max(max_ctx, c.start_pos + n)
+    lr = np.asarray(logit_rows, np.int32)
+    parts = [tokens, positions, slot_map, seq_of_row, slots, q_start, ctx_len, lr]
+    total = sum(p.size for p in parts)
+    if pinned is not None and pinned.numel() >= total:
+        stage = pinned[:total]
+    else:
+        stage = torch.empty(total, dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
+    sn = stage.numpy()
+    off = 0
+    offs = []
+    for p in parts:
+        sn[off:off + p.size] = p
+        offs.append((off, p.size))
+        off += p.size
+    dev = stage.to(device, non_blocking=True)
+    v = [dev[o:o + n] for o, n in offs]
+    return StepBatch(tokens=v[0], positions=v[1], slot_mapping=v[2], seq_of_row=v[3], slots=v[4], q_start=v[5],
+                     ctx_len=v[6], logit_rows=v[7], h_slots=[int(s) for s in slots],
+                     h_q_start=[int(x) for x in q_start], h_ctx_len=[int(x) for x in ctx_len],
+                     h_logit_rows=logit_rows, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)

@@ -1,0 +1,350 @@
+"""Engine: owns the model, the paged KV pools and the page allocator; runs one step at a time.
+
+Role of the reference's ``crates/blaze/src/engine.rs``: page API ``open_from / close / snapshot /
+release`` with ref-counted shared pages (:1083-1164), ``plan`` (:1168), ``step`` / ``step_sampled`` /
+``prefill_only`` (:1260-1301), CUDA-graph replay keyed by step shape (``run_graph`` :326, first sight
+eager, later sights captured and replayed), and a watchdog (:582-656).  Ranks here are processes
+(one per GPU) that execute the same step plan; rank 0 plans and the others receive the plan over the
+control group.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .batch import PAGE, SeqChunk, StepBatch, build_batch
+from .config import ModelConfig
+from .kv import KVCache, kv_bytes_per_token
+from .models.qwen3 import Model
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PageAllocator:
+    """Ref-counted 16-token pages.  Page 0 is reserved as the scratch target of padded rows."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self.free: List[int] = list(range(num_pages - 1, 0, -1))
+        self.refs = np.zeros(num_pages, dtype=np.int32)
+
+    @property
+    def free_count(self) -> int:
+        return len(self.free)
+
+    def alloc(self, n: int) -> List[int]:
+        if n > len(self.free):
+            raise OutOfPages(f"need {n} pages, {len(self.free)} free")
+        out = [self.free.pop() for _ in range(n)]
+        self.refs[out] = 1
+        return out
+
+    def retain(self, pages: Sequence[int]) -> None:
+        for p in pages:
+            self.refs[p] += 1
+
+    def release(self, pages: Sequence[int]) -> None:
+        for p in pages:
+            self.refs[p] -= 1
+            if self.refs[p] == 0:
+                self.free.append(p)
+            elif self.refs[p] < 0:
+                raise RuntimeError(f"page {p} released twice")
+
+
+@dataclass
+class Seq:
+    """A live sequence row: its block-table row, pages and KV length (``engine.rs:24``)."""
+    row: int
+    pages: List[int] = field(default_factory=list)
+    length: int = 0            # tokens whose KV is in the cache
+    shared: int = 0            # leading pages shared with a snapshot (never written)
+
+
+@dataclass
+class Snapshot:
+    """A prefix-cache snapshot: shared page refs plus a recurrent-state row (``engine.rs:1119-1164``)."""
+    pages: List[int]
+    length: int
+    state_row: int = -1
+
+
+@dataclass
+class EngineConfig:
+    kv_tokens: int = 0                 # 0 = size from free memory
+    max_seqs: int = 256
+    max_model_len: int = 4096
+    kv_dtype: str = "bf16"             # fp32 | bf16 | fp8
+    chunk: int = 2048
+    use_graphs: bool = True
+    vram_reserve: int = 2 << 30
+    snapshot_rows: int = 8
+    hang_secs: float = 30.0
+    graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+
+
+class Engine:
+    def __init__(self, model: Model, ecfg: EngineConfig):
+        self.model, self.ecfg = model, ecfg
+        cfg = model.cfg
+        self.device = model.device
+        tpw = model.tp.world
+        per_tok = max(kv_bytes_per_token(cfg, ecfg.kv_dtype, tpw), 1)
+        kv_tokens = ecfg.kv_tokens
+        if kv_tokens <= 0:
+            if self.device.type == "cuda":
+                free, _ = torch.cuda.mem_get_info(self.device)
+                kv_tokens = max(int((free - ecfg.vram_reserve) // per_tok), 16 * PAGE)
+                kv_tokens = min(kv_tokens, ecfg.max_seqs * ecfg.max_model_len)
+            else:
+                kv_tokens = min(ecfg.max_seqs * ecfg.max_model_len, 1 << 16)
+        self.num_pages = kv_tokens // PAGE + 1
+        self.max_pages_per_seq = (ecfg.max_model_len + PAGE - 1) // PAGE
+        layout = "umma" if (self.device.type == "cuda" and ecfg.kv_dtype == "fp8" and model.ops.is_cuda) else "logical"
+        self.kv = KVCache(cfg, self.num_pages, ecfg.max_seqs, self.max_pages_per_seq, ecfg.kv_dtype, self.device,
+                          layout, tpw, state_rows=ecfg.max_seqs + ecfg.snapshot_rows)
+        self.pages = PageAllocator(self.num_pages)
+        self.free_rows: List[int] = list(range(ecfg.max_seqs - 1, -1, -1))
+        self.free_state_rows: List[int] = list(range(ecfg.max_seqs + ecfg.snapshot_rows - 1, ecfg.max_seqs - 1, -1))
+        self.seqs: Dict[int, Seq] = {}
+        self._graphs: Dict[Tuple, "_Graph"] = {}
+        self._seen: Dict[Tuple, int] = {}
+        self._pinned = None
+        if self.device.type == "cuda":
+            self._pinned = torch.empty(1 << 20, dtype=torch.int32, pin_memory=True)
+        self.steps = 0
+        self.last_step_started = 0.0
+        self.last_step_what = ""
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.kernel_launches = 0
+
+    # ================================================================== page API
+    @property
+    def free_tokens(self) -> int:
+        return self.pages.free_count * PAGE
+
+    def open_from(self, snap: Optional[Snapshot] = None) -> Seq:
+        """Claim a sequence row, optionally starting from a snapshot's shared pages and state."""
+        if not self.free_rows:
+            raise OutOfPages("no free sequence row")
+        row = self.free_rows.pop()
+        s = Seq(row=row)
+        if snap is not None:
+            self.pages.retain(snap.pages)
+            s.pages = list(snap.pages)
+            s.length = snap.length
+            s.shared = len(snap.pages)
+            self.kv.set_pages(row, s.pages, 0)
+            if snap.state_row >= 0 and self.kv.gdn_layers:
+                self.kv.copy_state(snap.state_row, row)
+        elif self.kv.gdn_layers:
+            self.kv.zero_state(row)
+        self.seqs[row] = s
+        return s
+
+    def reserve(self, s: Seq, new_len: int) -> None:
+        """Make sure pages exist for positions < new_len (copy-on-write is never needed: shared
+        prefixes are page-aligned and only whole pages are shared)."""
+        need = (new_len + PAGE - 1) // PAGE - len(s.pages)
+        if need > 0:
+            if len(s.pages) + need > self.max_pages_per_seq:
+                raise OutOfPages("sequence exceeds max_model_len")
+            new = self.pages.alloc(need)
+            self.kv.set_pages(s.row, new, len(s.pages))
+            s.pages.extend(new)
+
+    def snapshot(self, s: Seq, length: Optional[int] = None, with_state: bool = True) -> Snapshot:
+        """Share the pages covering ``length`` tokens (page-aligned down) for later reuse."""
+        n = s.length if length is None else min(length, s.length)
+        n -= n % PAGE
+        pg = s.pages[:n // PAGE]
+        self.pages.retain(pg)
+        row = -1
+        if with_state and self.kv.gdn_layers:
+            if n != s.length:
+                # recurrent state is only valid at the sequence's current length
+                self.pages.release(pg)
+                raise ValueError("recurrent models can only snapshot at the current, page-aligned length")
+            if not self.free_state_rows:
+                self.pages.release(pg)
+                raise OutOfPages("no free snapshot row")
+            row = self.free_state_rows.pop()
+            self.kv.copy_state(s.row, row)
+        return Snapshot(pages=list(pg), length=n, state_row=row)
+
+    def release(self, snap: Snapshot) -> None:
+        self.pages.release(snap.pages)
+        if snap.state_row >= 0:
+            self.free_state_rows.append(snap.state_row)
+        snap.pages = []
+
+    def close(self, s: Seq) -> None:
+        self.pages.release(s.pages)
+        s.pages = []
+        self.seqs.pop(s.row, None)
+        self.free_rows.append(s.row)
+
+    def truncate(self, s: Seq, length: int) -> None:
+        """Drop KV beyond ``length`` (rejected speculative rows); frees whole pages no longer needed."""
+        keep = (length + PAGE - 1) // PAGE
+        if keep < len(s.pages):
+            self.pages.release(s.pages[keep:])
+            del s.pages[keep:]
+        s.length = length
+
+    # ================================================================== stepping
+    def plan(self, items: Sequence[Tuple[Seq, Sequence[int], int]]) -> List[SeqChunk]:
+        """items: (seq, new tokens, rows wanting logits).  Reserves pages and advances lengths."""
+        chunks = []
+        for s, toks, want in items:
+            self.reserve(s, s.length + len(toks))
+            chunks.append(SeqChunk(slot=s.row, tokens=list(toks), start_pos=s.length, want_logits=want))
+            s.length += len(toks)
+        return chunks
+
+    def _bucket(self, rows: int) -> int:
+        for b in self.ecfg.graph_buckets:
+            if rows <= b:
+                return b
+        return rows
+
+    def forward(self, chunks: Sequence[SeqChunk], mode: str = "greedy", hidden_in: Optional[torch.Tensor] = None):
+        """Run one step.  ``mode``: ``greedy`` → token ids ``[R]``; ``logits`` → fp32 ``[R, vocab]``;
+        ``hidden`` → final-normed hidden rows; ``none`` → headless (prefill chunk without a head)."""
+        self.last_step_started = time.monotonic()
+        self.last_step_what = f"{mode} rows={sum(len(c.tokens) for c in chunks)} seqs={len(chunks)}"
+        decode_only = all(len(c.tokens) == 1 for c in chunks)
+        graphable = (self.ecfg.use_graphs and self.device.type == "cuda" and decode_only and mode == "greedy"
+                     and self.model.is_first_stage and self.model.is_last_stage and self.model.ops.is_cuda)
+        try:
+            if graphable:
+                out = self._forward_graph(chunks)
+            else:
+                batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned)
+                self.h2d_bytes += batch.h2d_bytes
+                out = self._run(batch, mode, hidden_in)
+        finally:
+            self.steps += 1
+            self.last_step_started = 0.0
+        return out
+
+    def _run(self, batch: StepBatch, mode: str, hidden_in=None):
+        m = self.model
+        x = m.forward(batch, self.kv, hidden_in)
+        if not m.is_last_stage:
+            return x
+        if mode == "none":
+            return None
+        rows = batch.logit_rows
+        if mode == "greedy":
+            return m.greedy(x, rows)
+        if mode == "logits":
+            return m.head(x, rows)
+        if mode == "hidden":
+            return m.final_hidden(x, rows)
+        if mode == "both":
+            return m.head(x, rows), x
+        raise ValueError(mode)
+
+    # ------------------------------------------------------------------ CUDA graphs for decode steps
+    def _forward_graph(self, chunks: Sequence[SeqChunk]):
+        B = len(chunks)
+        bucket = self._bucket(B)
+        key = ("decode", bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            seen = self._seen.get(key, 0)
+            self._seen[key] = seen + 1
+            if seen == 0:   # first sight: run eagerly (also warms allocator and lazy inits)
+                batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned)
+                self.h2d_bytes += batch.h2d_bytes
+                return self._run(batch, "greedy")
+            g = _Graph(self, bucket)
+            self._graphs[key] = g
+        return g.replay(chunks)
+
+    # ================================================================== watchdog
+    def start_watchdog(self, on_hang=None) -> threading.Thread:
+        """Report (never kill) a step that runs longer than ``hang_secs`` (``engine.rs:582-656``)."""
+        def loop():
+            while True:
+                time.sleep(min(self.ecfg.hang_secs / 4, 1.0))
+                t0 = self.last_step_started
+                if t0 and time.monotonic() - t0 > self.ecfg.hang_secs:
+                    msg = f"engine hang: step {self.steps} ({self.last_step_what}) running {time.monotonic() - t0:.1f}s"
+                    if on_hang:
+                        on_hang(msg)
+                    else:
+                        from . import log
+                        log.event("error", "engine.hang", what=msg)
+                    self.last_step_started = 0.0
+        th = threading.Thread(target=loop, name="blaze-watchdog", daemon=True)
+        th.start()
+        return th
+
+
+class _Graph:
+    """A captured decode step for a fixed row bucket; inputs live in static buffers."""
+
+    def __init__(self, eng: Engine, bucket: int):
+        self.eng, self.bucket = eng, bucket
+        dev = eng.device
+        n = bucket
+        self.total = 4 * n + n + (n + 1) + n + n
+        self.static = torch.zeros(self.total, dtype=torch.int32, device=dev)
+        self.stage = torch.zeros(self.total, dtype=torch.int32, pin_memory=True)
+        o = 0
+        v = []
+        for size in (n, n, n, n, n, n + 1, n, n):
+            v.append(self.static[o:o + size])
+            o += size
+        self.batch = StepBatch(tokens=v[0], positions=v[1], slot_mapping=v[2], seq_of_row=v[3], slots=v[4],
+                               q_start=v[5], ctx_len=v[6], logit_rows=v[7], num_rows=n, max_q_len=1)
+        self.batch.h_slots = [0] * n
+        self.batch.h_q_start = list(range(n + 1))
+        self.batch.h_ctx_len = [1] * n
+        self.batch.h_logit_rows = list(range(n))
+        self.batch.max_ctx = eng.ecfg.max_model_len
+        self.graph = None
+        self.out = None
+
+    def _fill(self, chunks: Sequence[SeqChunk]) -> int:
+        n, B = self.bucket, len(chunks)
+        s = self.stage.numpy()
+        bt = self.eng.kv.block_table_host
+        tok = np.fromiter((c.tokens[0] for c in chunks), np.int32, B)
+        pos = np.fromiter((c.start_pos for c in chunks), np.int32, B)
+        slot = np.fromiter((c.slot for c in chunks), np.int32, B)
+        s[:] = 0
+        s[0:B] = tok
+        s[n:n + B] = pos
+        s[2 * n:3 * n] = -1
+        s[2 * n:2 * n + B] = bt[slot, pos // PAGE] * PAGE + pos % PAGE
+        s[3 * n:4 * n] = -1
+        s[3 * n:3 * n + B] = np.arange(B, dtype=np.int32)
+        s[4 * n:4 * n + B] = slot
+        qs = np.minimum(np.arange(n + 1, dtype=np.int32), B)
+        s[5 * n:6 * n + 1] = qs
+        s[6 * n + 1:6 * n + 1 + B] = pos + 1
+        s[7 * n + 1:8 * n + 1] = np.minimum(np.arange(n, dtype=np.int32), max(B - 1, 0))
+        self.static.copy_(self.stage, non_blocking=True)
+        self.eng.h2d_bytes += self.total * 4
+        return B
+
+    def replay(self, chunks: Sequence[SeqChunk]):
+        B = self._fill(chunks)
+        if self.graph is None:
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.out = self.eng._run(self.batch, "greedy")
+        self.graph.replay()
+        return self.out[:B]

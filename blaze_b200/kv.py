@@ -1,0 +1,125 @@
+"""Paged KV pools, block tables and recurrent (Gated DeltaNet) state rows.
+
+Pages hold 16 tokens.  Two pool layouts exist:
+
+* ``logical`` — ``k[layer]``, ``v[layer]`` of shape ``[pages, kv_heads, 16, head_dim]`` in fp32 / bf16 /
+  e4m3; used by the PyTorch oracle and on CPU.
+* ``umma`` — one uint8 tensor ``[pages, kv_heads, 2, 16*head_dim]`` per layer holding e4m3 K in the
+  shared-memory layout the tcgen05 attention kernel consumes directly (8-row × 16-byte core matrices:
+  byte of token t, dim j at ``(t//8)*8*D + (j//16)*128 + (t%8)*16 + j%16``) followed by V transposed
+  (``[head_dim][16 tokens]``), so that one 1-D bulk copy per (page, head) feeds both MMAs.
+
+The reference keeps one-token pages and several KV dtypes (``crates/blaze/src/model.rs:499-583``,
+``alloc_kv`` :517); its page bookkeeping is in ``engine.rs:1083-1164``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .config import ModelConfig
+
+PAGE = 16
+
+
+def kv_bytes_per_token(cfg: ModelConfig, kv_dtype: str, tp_world: int = 1) -> int:
+    esz = {"fp32": 4, "bf16": 2, "fp8": 1}[kv_dtype]
+    n_attn = sum(1 for i in range(cfg.num_layers) if cfg.layer_type(i) == "full_attention")
+    kvh = max(cfg.num_kv_heads // tp_world, 1)
+    return n_attn * 2 * kvh * cfg.head_dim * esz
+
+
+class KVCache:
+    def __init__(self, cfg: ModelConfig, num_pages: int, max_seqs: int, max_pages_per_seq: int,
+                 kv_dtype: str = "bf16", device="cpu", layout: str = "logical", tp_world: int = 1,
+                 state_rows: Optional[int] = None):
+        self.cfg, self.num_pages, self.max_seqs = cfg, num_pages, max_seqs
+        self.max_pages_per_seq = max_pages_per_seq
+        self.kv_dtype, self.layout, self.device = kv_dtype, layout, torch.device(device)
+        self.kv_heads = max(cfg.num_kv_heads // tp_world, 1)
+        D = cfg.head_dim
+        tdt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[kv_dtype]
+        self.attn_layers = [i for i in range(cfg.num_layers) if cfg.layer_type(i) == "full_attention"]
+        self.gdn_layers = [i for i in range(cfg.num_layers) if cfg.layer_type(i) == "linear_attention"]
+        self.k: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        self.kv: Dict[int, torch.Tensor] = {}
+        for i in self.attn_layers:
+            if layout == "umma":
+                assert kv_dtype == "fp8"
+                self.kv[i] = torch.zeros(num_pages, self.kv_heads, 2, PAGE * D, dtype=torch.uint8, device=device)
+            else:
+                self.k[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
+                self.v[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
+        self.block_table = torch.zeros(max_seqs, max_pages_per_seq, dtype=torch.int32, device=device)
+        self.block_table_host = np.zeros((max_seqs, max_pages_per_seq), dtype=np.int32)
+        # recurrent state rows: one per sequence row plus snapshot rows for the prefix cache / speculation
+        self.state_rows = state_rows if state_rows is not None else max_seqs
+        self.conv_state: Dict[int, torch.Tensor] = {}
+        self.rec_state: Dict[int, torch.Tensor] = {}
+        if self.gdn_layers:
+            hk = max(cfg.linear_num_key_heads // tp_world, 1)
+            hv = max(cfg.linear_num_value_heads // tp_world, 1)
+            conv_dim = 2 * hk * cfg.linear_key_head_dim + hv * cfg.linear_value_head_dim
+            act = torch.float32 if kv_dtype == "fp32" else torch.bfloat16
+            for i in self.gdn_layers:
+                self.conv_state[i] = torch.zeros(self.state_rows, conv_dim, cfg.linear_conv_kernel_dim - 1,
+                                                 dtype=act, device=device)
+                self.rec_state[i] = torch.zeros(self.state_rows, hv, cfg.linear_key_head_dim,
+                                                cfg.linear_value_head_dim, dtype=torch.float32, device=device)
+
+    # ------------------------------------------------------------------ block table
+    def set_pages(self, row: int, pages: List[int], start: int = 0) -> None:
+        """Record pages ``start..`` of sequence row ``row`` (host mirror + device)."""
+        if not pages:
+            return
+        n = len(pages)
+        self.block_table_host[row, start:start + n] = pages
+        self.block_table[row, start:start + n] = torch.as_tensor(pages, dtype=torch.int32).to(
+            self.block_table.device, non_blocking=True)
+
+    def nbytes(self) -> int:
+        n = 0
+        for d in (self.k, self.v, self.kv, self.conv_state, self.rec_state):
+            n += sum(t.numel() * t.element_size() for t in d.values())
+        return n
+
+    # ------------------------------------------------------------------ recurrent state rows
+    def copy_state(self, src: int, dst: int) -> None:
+        """Copy the GDN conv + recurrent state of row ``src`` to row ``dst`` (``model.rs:2718``)."""
+        for i in self.gdn_layers:
+            self.conv_state[i][dst].copy_(self.conv_state[i][src])
+            self.rec_state[i][dst].copy_(self.rec_state[i][src])
+
+    def zero_state(self, row: int) -> None:
+        for i in self.gdn_layers:
+            self.conv_state[i][row].zero_()
+            self.rec_state[i][row].zero_()
+
+    # ------------------------------------------------------------------ layout helpers (tests, host tier)
+    @staticmethod
+    def pack_umma_page(k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """k, v ``[16, D]`` e4m3 (viewed as uint8) → ``[2, 16*D]`` bytes in the kernel layout."""
+        D = k.shape[1]
+        kb = k.view(torch.uint8).view(2, 8, D // 16, 16).permute(0, 2, 1, 3).contiguous().view(-1)
+        vb = v.view(torch.uint8).t().contiguous().view(-1)
+        return torch.stack([kb, vb])
+
+    @staticmethod
+    def unpack_umma_page(buf: torch.Tensor, D: int):
+        kb = buf[0].view(2, D // 16, 8, 16).permute(0, 2, 1, 3).contiguous().view(16, D)
+        vb = buf[1].view(D, 16).t().contiguous()
+        return kb.view(torch.float8_e4m3fn), vb.view(torch.float8_e4m3fn)
+
+    def logical_kv(self, layer: int):
+        """Return (k, v) ``[pages, kv_heads, 16, D]`` e4m3 whatever the layout (copy for ``umma``)."""
+        if self.layout != "umma":
+            return self.k[layer], self.v[layer]
+        D = self.cfg.head_dim
+        buf = self.kv[layer]
+        P, H = buf.shape[0], buf.shape[1]
+        kb = buf[:, :, 0].view(P, H, 2, D // 16, 8, 16).permute(0, 1, 2, 4, 3, 5).contiguous().view(P, H, 16, D)
+        vb = buf[:, :, 1].view(P, H, D, 16).transpose(2, 3).contiguous()
+        return kb.view(torch.float8_e4m3fn), vb.view(torch.float8_e4m3fn)

@@ -1,0 +1,587 @@
+"""Decoder model: Qwen3 dense, Qwen3-MoE and the Qwen3-Next style hybrid (Gated DeltaNet + gated
+attention + shared expert), loaded from safetensors or random-initialised, with tensor-parallel cuts.
+
+Mirrors the structure of the reference's ``crates/blaze/src/model.rs`` (``load`` :1031-1661 for the
+tensor names and TP cuts :1110-1282, ``forward`` :2330-2551, ``attention`` :2897, ``gdn`` :3513,
+``mlp`` :3594) while adding what it refuses: plain Qwen3 attention (no gate), MoE without a shared
+expert, and MoE under tensor / expert parallelism (``model.rs:1077-1080``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ..batch import StepBatch
+from ..config import ModelConfig, inv_freq
+from ..kv import KVCache
+from ..linear import Cut, Linear, part
+from ..quant import Format
+
+
+class Attn:
+    def __init__(self):
+        self.qkv: Linear = None
+        self.o: Linear = None
+        self.q_norm: Optional[torch.Tensor] = None
+        self.k_norm: Optional[torch.Tensor] = None
+        self.heads = 0
+        self.kv_heads = 0
+
+
+class Gdn:
+    def __init__(self):
+        self.in_proj: Linear = None      # rows [q | k | v | z | b | a]
+        self.out_proj: Linear = None
+        self.conv_w: torch.Tensor = None  # [conv_dim, k]
+        self.A_log: torch.Tensor = None
+        self.dt_bias: torch.Tensor = None
+        self.norm_w: torch.Tensor = None
+        self.k_heads = 0
+        self.v_heads = 0
+
+
+class DenseMlp:
+    def __init__(self):
+        self.gate_up: Linear = None
+        self.down: Linear = None
+
+
+class Experts:
+    """Routed experts of one layer (this rank's share under expert parallelism)."""
+
+    def __init__(self):
+        self.gate_up: List[Linear] = []
+        self.down: List[Linear] = []
+        self.num_experts = 0             # global expert count
+        self.first = 0                   # first global expert id held locally
+        self.count = 0                   # number held locally
+        self.cuda_pack = None
+
+    def forward_one(self, e: int, x: torch.Tensor) -> torch.Tensor:
+        from ..ops import ref
+        le = e - self.first
+        return self.down[le].ref(ref.silu_mul(self.gate_up[le].ref(x)))
+
+
+class MoeMlp:
+    def __init__(self):
+        self.router: Linear = None
+        self.experts: Experts = None
+        self.shared: Optional[DenseMlp] = None
+        self.shared_gate: Optional[Linear] = None
+        self.top_k = 0
+        self.renorm = True
+
+
+class Layer:
+    def __init__(self):
+        self.kind = "full_attention"
+        self.input_norm: torch.Tensor = None
+        self.post_norm: torch.Tensor = None
+        self.attn: Optional[Attn] = None
+        self.gdn: Optional[Gdn] = None
+        self.mlp = None
+
+
+class TPInfo:
+    """Rank layout.  ``group`` does the collectives (None on one rank)."""
+
+    def __init__(self, rank: int = 0, world: int = 1, group=None, ep: bool = False):
+        self.rank, self.world, self.group, self.ep = rank, world, group, ep
+
+
+class Model:
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, tp: Optional[TPInfo] = None, ops=None,
+                 first_layer: int = 0, last_layer: Optional[int] = None):
+        from ..ops import get_ops
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.tp = tp or TPInfo()
+        self.ops = ops or get_ops(device)
+        self.layers: List[Layer] = []
+        self.embed: torch.Tensor = None
+        self.final_norm: torch.Tensor = None
+        self.lm_head: Linear = None
+        self.first_layer = first_layer                        # pipeline stage range [first, last)
+        self.last_layer = cfg.num_layers if last_layer is None else last_layer
+        self.inv_freq = torch.tensor(inv_freq(cfg), dtype=torch.float32, device=device)
+        self.rope_scale = cfg.rope.rope_scale()
+        self.attn_scale = cfg.head_dim ** -0.5
+        self.gdn_chunked = False
+        self.capture_layers: List[int] = []                   # hidden states kept for drafters
+        self.captured: Dict[int, torch.Tensor] = {}
+        self.weight_format = Format.DENSE
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.first_layer == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.last_layer == self.cfg.num_layers
+
+    # ================================================================== construction
+    @classmethod
+    def random_init(cls, cfg: ModelConfig, fmt: Format = Format.DENSE, seed: int = 0, device="cpu",
+                    dtype=torch.bfloat16, tp: Optional[TPInfo] = None, std: float = 0.02, ops=None,
+                    first_layer: int = 0, last_layer: Optional[int] = None, lm_head_fmt: Format = Format.DENSE,
+                    router_std: Optional[float] = None) -> "Model":
+        """N(0, std) weights from ``seed`` (norm weights 1, or 0 when zero-centred), quantised to ``fmt``.
+
+        Full tensors are generated and quantised first and cut afterwards, so a TP=n model is an
+        exact cut of the TP=1 model with the same seed.
+        """
+        m = cls(cfg, device, dtype, tp, ops, first_layer, last_layer)
+        m.weight_format = fmt
+        tpw, tpr = m.tp.world, m.tp.rank
+        gen = torch.Generator(device=device)
+        D, H = cfg.head_dim, cfg.hidden_size
+
+        def rnd(n, k, tag, s=std):
+            gen.manual_seed((seed * 1000003 + tag) & 0x7FFFFFFF)
+            return torch.randn(n, k, generator=gen, device=device, dtype=torch.float32) * s
+
+        def ones(n):
+            return (torch.zeros if cfg.zero_centered_norm else torch.ones)(n, dtype=dtype, device=device)
+
+        def lin(w, cut, f=fmt, segments=None, unit=1):
+            if cut == Cut.COLS and tpw > 1:
+                a, b = part(w.shape[1], tpr, tpw)
+                w = w[:, a:b]
+                return _tag(Linear.from_dense(w, f, dtype=dtype, segments=segments), Cut.COLS)
+            if cut == Cut.ROWS and tpw > 1 and segments:
+                pieces, r = [], 0
+                for n in segments:
+                    a, b = part(n // unit, tpr, tpw)
+                    pieces.append(w[r + a * unit:r + b * unit])
+                    r += n
+                segs = [p.shape[0] for p in pieces]
+                return _tag(Linear.from_dense(torch.cat(pieces), f, dtype=dtype, segments=segs), Cut.ROWS)
+            if cut == Cut.ROWS and tpw > 1:
+                a, b = part(w.shape[0] // unit, tpr, tpw)
+                w = w[a * unit:b * unit]
+            return _tag(Linear.from_dense(w, f, dtype=dtype, segments=segments), cut)
+
+        def _tag(l, cut):
+            l.cut = cut
+            return l
+
+        if m.is_first_stage or cfg.tie_word_embeddings:
+            m.embed = rnd(cfg.vocab_size, H, 1).to(dtype)
+        for i in range(m.first_layer, m.last_layer):
+            L = Layer()
+            L.kind = cfg.layer_type(i)
+            base = 100 + i * 50
+            L.input_norm, L.post_norm = ones(H), ones(H)
+            if L.kind == "full_attention":
+                A = Attn()
+                A.heads, A.kv_heads = cfg.num_heads // tpw, max(cfg.num_kv_heads // tpw, 1)
+                qrows = cfg.num_heads * D * (2 if cfg.attn_output_gate else 1)
+                qunit = D * (2 if cfg.attn_output_gate else 1)
+                wq, wk, wv = rnd(qrows, H, base + 1), rnd(cfg.num_kv_heads * D, H, base + 2), rnd(cfg.num_kv_heads * D, H, base + 3)
+                if tpw > 1:
+                    qa, qb = part(cfg.num_heads, tpr, tpw)
+                    wq = wq[qa * qunit:qb * qunit]
+                    if cfg.num_kv_heads >= tpw:
+                        ka, kb = part(cfg.num_kv_heads, tpr, tpw)
+                    else:   # replicate KV heads: rank r uses head r * kv_heads // world
+                        ka = tpr * cfg.num_kv_heads // tpw
+                        kb = ka + 1
+                    wk, wv = wk[ka * D:kb * D], wv[ka * D:kb * D]
+                A.qkv = _tag(Linear.from_dense(torch.cat([wq, wk, wv]), fmt, dtype=dtype,
+                                               segments=[wq.shape[0], wk.shape[0], wv.shape[0]]), Cut.ROWS)
+                A.o = lin(rnd(H, cfg.num_heads * D, base + 4), Cut.COLS)
+                if cfg.qk_norm:
+                    A.q_norm, A.k_norm = ones(D), ones(D)
+                L.attn = A
+            else:
+                G = Gdn()
+                hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+                dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+                G.k_heads, G.v_heads = hk // tpw, hv // tpw
+                segs_full = [hk * dk, hk * dk, hv * dv, hv * dv, hv, hv]
+                units = [dk, dk, dv, dv, 1, 1]
+                ws = [rnd(n, H, base + 10 + j) for j, n in enumerate(segs_full)]
+                if tpw > 1:
+                    ws = [w[part(w.shape[0] // u, tpr, tpw)[0] * u:part(w.shape[0] // u, tpr, tpw)[1] * u]
+                          for w, u in zip(ws, units)]
+                # the small b / a projections stay dense: their outputs feed gates
+                G.in_proj = _tag(Linear.from_dense(torch.cat(ws), fmt, dtype=dtype, segments=[w.shape[0] for w in ws]), Cut.ROWS)
+                G.out_proj = lin(rnd(H, hv * dv, base + 17), Cut.COLS)
+                conv_dim = 2 * hk * dk + hv * dv
+                cw = rnd(conv_dim, cfg.linear_conv_kernel_dim, base + 18, 0.2)
+                if tpw > 1:
+                    qa, qb = part(hk, tpr, tpw)
+                    va, vb = part(hv, tpr, tpw)
+                    cw = torch.cat([cw[qa * dk:qb * dk], cw[hk * dk + qa * dk:hk * dk + qb * dk],
+                                    cw[2 * hk * dk + va * dv:2 * hk * dk + vb * dv]])
+                G.conv_w = cw.to(dtype)
+                al = torch.log(torch.linspace(1.0, 8.0, hv, device=device))
+                G.A_log = al[part(hv, tpr, tpw)[0]:part(hv, tpr, tpw)[1]].float().contiguous()
+                G.dt_bias = torch.zeros(G.v_heads, dtype=torch.float32, device=device)
+                G.norm_w = torch.ones(dv, dtype=dtype, device=device)
+                L.gdn = G
+            if cfg.is_moe:
+                M = MoeMlp()
+                M.top_k, M.renorm = cfg.num_experts_per_tok, cfg.norm_topk_prob
+                M.router = _tag(Linear.from_dense(rnd(cfg.num_experts, H, base + 20, router_std or std), Format.DENSE, dtype=dtype), Cut.ALL)
+                E = Experts()
+                E.num_experts = cfg.num_experts
+                I = cfg.moe_intermediate_size
+                if m.tp.ep:      # expert parallel: whole experts per rank
+                    E.first, end = part(cfg.num_experts, tpr, tpw)
+                    E.count = end - E.first
+                else:
+                    E.first, E.count = 0, cfg.num_experts
+                gen.manual_seed((seed * 1000003 + base + 21) & 0x7FFFFFFF)
+                for e in range(E.first, E.first + E.count):
+                    gen.manual_seed((seed * 1000003 + (base + 21) * 4099 + e) & 0x7FFFFFFF)
+                    wg = torch.randn(2 * I, H, generator=gen, device=device) * std
+                    wd = torch.randn(H, I, generator=gen, device=device) * std
+                    if not m.tp.ep and tpw > 1:   # tensor-parallel experts: cut the intermediate dim
+                        a, b = part(I, tpr, tpw)
+                        wg = torch.cat([wg[a:b], wg[I + a:I + b]])
+                        wd = wd[:, a:b]
+                    E.gate_up.append(Linear.from_dense(wg, fmt, dtype=dtype, segments=[wg.shape[0] // 2] * 2))
+                    E.down.append(Linear.from_dense(wd, fmt, dtype=dtype))
+                M.experts = E
+                if cfg.shared_expert_intermediate_size:
+                    S = DenseMlp()
+                    Is = cfg.shared_expert_intermediate_size
+                    S.gate_up = lin(rnd(2 * Is, H, base + 30), Cut.ROWS, segments=[Is, Is])
+                    S.down = lin(rnd(H, Is, base + 31), Cut.COLS)
+                    M.shared = S
+                    M.shared_gate = _tag(Linear.from_dense(rnd(1, H, base + 32), Format.DENSE, dtype=dtype), Cut.ALL)
+                L.mlp = M
+            else:
+                P = DenseMlp()
+                I = cfg.intermediate_size
+                P.gate_up = lin(rnd(2 * I, H, base + 40), Cut.ROWS, segments=[I, I])
+                P.down = lin(rnd(H, I, base + 41), Cut.COLS)
+                L.mlp = P
+            m.layers.append(L)
+        if m.is_last_stage:
+            m.final_norm = ones(H)
+            if cfg.tie_word_embeddings:
+                wl = m.embed.float()
+            else:
+                wl = rnd(cfg.vocab_size, H, 2)
+            if tpw > 1:
+                a, b = part(cfg.vocab_size, tpr, tpw)
+                wl = wl[a:b]
+            m.lm_head = _tag(Linear.from_dense(wl, lm_head_fmt, dtype=dtype), Cut.ROWS if tpw > 1 else Cut.ALL)
+        return m
+
+    @classmethod
+    def load(cls, model_dir: str, device="cpu", dtype=torch.bfloat16, tp: Optional[TPInfo] = None, ops=None,
+             first_layer: int = 0, last_layer: Optional[int] = None, cfg: Optional[ModelConfig] = None) -> "Model":
+        """Load a local safetensors checkpoint (tensor names of ``model.rs:1110-1282``)."""
+        from ..weights import Checkpoint
+        cfg = cfg or ModelConfig.load(model_dir)
+        ck = Checkpoint.open(model_dir)
+        m = cls(cfg, device, dtype, tp, ops, first_layer, last_layer)
+        p = ck.text_prefix()
+        tpw, tpr = m.tp.world, m.tp.rank
+        D = cfg.head_dim
+
+        def vec(name, cut_heads=None):
+            t = ck.get(name)
+            return t.to(dtype).to(device)
+
+        def rows(t, n_units, unit):
+            if tpw == 1:
+                return t
+            a, b = part(n_units, tpr, tpw)
+            return t[a * unit:b * unit]
+
+        def load_lin(mods, cut, units=None):
+            return Linear.load(ck, mods, cut, tpr, tpw, dtype, device)
+
+        if m.is_first_stage or cfg.tie_word_embeddings:
+            m.embed = ck.get(f"{p}embed_tokens.weight").to(dtype).to(device)
+        for i in range(m.first_layer, m.last_layer):
+            L = Layer()
+            L.kind = cfg.layer_type(i)
+            lp = f"{p}layers.{i}."
+            L.input_norm = vec(lp + "input_layernorm.weight")
+            L.post_norm = vec(lp + "post_attention_layernorm.weight")
+            if L.kind == "full_attention":
+                A = Attn()
+                A.heads, A.kv_heads = cfg.num_heads // tpw, max(cfg.num_kv_heads // tpw, 1)
+                sp = lp + "self_attn."
+                A.qkv = _load_stacked_heads(ck, [sp + "q_proj", sp + "k_proj", sp + "v_proj"],
+                                            [D * (2 if cfg.attn_output_gate else 1), D, D],
+                                            [cfg.num_heads, cfg.num_kv_heads, cfg.num_kv_heads], tpr, tpw, dtype, device)
+                A.o = load_lin([sp + "o_proj"], Cut.COLS)
+                if cfg.qk_norm and (sp + "q_norm.weight") in ck:
+                    A.q_norm, A.k_norm = vec(sp + "q_norm.weight"), vec(sp + "k_norm.weight")
+                L.attn = A
+            else:
+                G = Gdn()
+                hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+                dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+                G.k_heads, G.v_heads = hk // tpw, hv // tpw
+                gp = lp + "linear_attn."
+                if (gp + "in_proj_qkv.weight") in ck or (gp + "in_proj_qkv.weight_packed") in ck:
+                    # rows [q|k|v] in one module: cut each third on head boundaries
+                    G.in_proj = _load_gdn_in_proj(ck, gp, hk, hv, dk, dv, tpr, tpw, dtype, device)
+                else:
+                    G.in_proj = _load_gdn_fused(ck, gp, hk, hv, dk, dv, tpr, tpw, dtype, device)
+                G.out_proj = load_lin([gp + "out_proj"], Cut.COLS)
+                cw = ck.get(gp + "conv1d.weight").float()
+                cw = cw.view(cw.shape[0], -1)
+                if tpw > 1:
+                    qa, qb = part(hk, tpr, tpw)
+                    va, vb = part(hv, tpr, tpw)
+                    cw = torch.cat([cw[qa * dk:qb * dk], cw[hk * dk + qa * dk:hk * dk + qb * dk],
+                                    cw[2 * hk * dk + va * dv:2 * hk * dk + vb * dv]])
+                G.conv_w = cw.to(dtype).to(device)
+                G.A_log = rows(ck.get(gp + "A_log").float(), hv, 1).contiguous().to(device)
+                G.dt_bias = rows(ck.get(gp + "dt_bias").float(), hv, 1).contiguous().to(device)
+                G.norm_w = vec(gp + "norm.weight")
+                L.gdn = G
+            mp = lp + "mlp."
+            if cfg.is_moe and (mp + "gate.weight") in ck:
+                M = MoeMlp()
+                M.top_k, M.renorm = cfg.num_experts_per_tok, cfg.norm_topk_prob
+                M.router = Linear.load(ck, [mp + "gate"], Cut.ALL, 0, 1, dtype, device)
+                E = Experts()
+                E.num_experts = cfg.num_experts
+                if m.tp.ep:
+                    E.first, end = part(cfg.num_experts, tpr, tpw)
+                    E.count = end - E.first
+                else:
+                    E.first, E.count = 0, cfg.num_experts
+                for e in range(E.first, E.first + E.count):
+                    ep = f"{mp}experts.{e}."
+                    if m.tp.ep or tpw == 1:
+                        E.gate_up.append(Linear.load(ck, [ep + "gate_proj", ep + "up_proj"], Cut.ALL, 0, 1, dtype, device))
+                        E.down.append(Linear.load(ck, [ep + "down_proj"], Cut.ALL, 0, 1, dtype, device))
+                    else:
+                        E.gate_up.append(Linear.load(ck, [ep + "gate_proj", ep + "up_proj"], Cut.ROWS, tpr, tpw, dtype, device))
+                        E.down.append(Linear.load(ck, [ep + "down_proj"], Cut.COLS, tpr, tpw, dtype, device))
+                M.experts = E
+                if (mp + "shared_expert.gate_proj.weight") in ck or (mp + "shared_expert.gate_proj.weight_packed") in ck:
+                    S = DenseMlp()
+                    S.gate_up = load_lin([mp + "shared_expert.gate_proj", mp + "shared_expert.up_proj"], Cut.ROWS)
+                    S.down = load_lin([mp + "shared_expert.down_proj"], Cut.COLS)
+                    M.shared = S
+                    if (mp + "shared_expert_gate.weight") in ck:
+                        M.shared_gate = Linear.load(ck, [mp + "shared_expert_gate"], Cut.ALL, 0, 1, dtype, device)
+                L.mlp = M
+            else:
+                P = DenseMlp()
+                P.gate_up = load_lin([mp + "gate_proj", mp + "up_proj"], Cut.ROWS)
+                P.down = load_lin([mp + "down_proj"], Cut.COLS)
+                L.mlp = P
+            m.layers.append(L)
+        if m.is_last_stage:
+            m.final_norm = vec(f"{p}norm.weight")
+            if cfg.tie_word_embeddings or "lm_head.weight" not in ck:
+                wl = m.embed.float()
+                if tpw > 1:
+                    a, b = part(cfg.vocab_size, tpr, tpw)
+                    wl = wl[a:b]
+                m.lm_head = Linear.from_dense(wl, Format.DENSE, dtype=dtype)
+                m.lm_head.cut = Cut.ROWS if tpw > 1 else Cut.ALL
+            else:
+                m.lm_head = Linear.load(ck, ["lm_head"], Cut.ROWS if tpw > 1 else Cut.ALL, tpr, tpw, dtype, device)
+        fmts = [L.mlp.gate_up.fmt for L in m.layers if isinstance(L.mlp, DenseMlp)]
+        m.weight_format = fmts[0] if fmts else Format.DENSE
+        return m
+
+    # ================================================================== forward
+    def forward(self, batch: StepBatch, kv: KVCache, hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run this stage's layers.  Returns the residual stream ``[T, hidden]`` *before* the final norm
+        on the last stage (use :meth:`head` for logits), or the rows to hand to the next stage."""
+        ops, cfg = self.ops, self.cfg
+        if self.is_first_stage:
+            x = ops.embed(self.embed, batch.tokens)
+        else:
+            x = hidden_in
+        residual = None
+        rope = ops.rope_tables(self, batch)
+        for li, L in enumerate(self.layers):
+            gi = self.first_layer + li
+            if gi in self.capture_layers:
+                self.captured[gi] = x if residual is None else ops.add(x, residual)
+            first = L.attn.qkv if L.attn is not None else L.gdn.in_proj
+            h, residual = ops.norm(x, residual, L.input_norm, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=first)
+            if L.kind == "full_attention":
+                x = self._attention(L.attn, h, batch, kv, gi, rope)
+            else:
+                x = self._gdn(L.gdn, h, batch, kv, gi)
+            nxt = L.mlp.gate_up if isinstance(L.mlp, DenseMlp) else None
+            h, residual = ops.norm(x, residual, L.post_norm, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=nxt)
+            x = self._mlp(L.mlp, h)
+        # fold the last residual so the caller sees the full stream
+        if residual is not None:
+            x = ops.add(x, residual)
+        return x
+
+    def _attention(self, A: Attn, h, batch, kv, gi, rope):
+        ops = self.ops
+        qkv = ops.linear(A.qkv, h)
+        q, gate = ops.attn_prep_store(qkv, A, self, batch, kv, gi, rope)
+        o = ops.attention(q, self, batch, kv, gi, self.attn_scale)
+        if gate is not None:
+            o = ops.mul_sigmoid(o, gate.reshape(o.shape))
+        y = ops.linear(A.o, o)
+        return ops.all_reduce(y, self.tp.group)
+
+    def _gdn(self, G: Gdn, h, batch, kv, gi):
+        ops, cfg = self.ops, self.cfg
+        dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        proj = ops.linear(G.in_proj, h)
+        nq = 2 * G.k_heads * dk + G.v_heads * dv
+        nz = G.v_heads * dv
+        mixed, z = proj[:, :nq], proj[:, nq:nq + nz]
+        b, a = proj[:, nq + nz:nq + nz + G.v_heads], proj[:, nq + nz + G.v_heads:]
+        o = ops.gdn(mixed, z, b, a, G, self, batch, kv, gi)
+        y = ops.linear(G.out_proj, o)
+        return ops.all_reduce(y, self.tp.group)
+
+    def _mlp(self, M, h):
+        ops = self.ops
+        if isinstance(M, DenseMlp):
+            a = ops.silu_mul(ops.linear(M.gate_up, h), quant_for=M.down)
+            return ops.all_reduce(ops.linear(M.down, a), self.tp.group)
+        logits = ops.linear(M.router, h, out_dtype=torch.float32)
+        w, ids = ops.router_topk(logits, M.top_k, M.renorm)
+        if self.tp.ep and self.tp.world > 1:
+            y = self.tp.group.moe_ep(ops, h, w, ids, M.experts)
+        else:
+            y = ops.moe(h, w, ids, M.experts)
+        if M.shared is not None:
+            s = ops.linear(M.shared.down, ops.silu_mul(ops.linear(M.shared.gate_up, h), quant_for=M.shared.down))
+            if M.shared_gate is not None:
+                gl = ops.linear(M.shared_gate, h)
+                if self.tp.ep:
+                    s_full = ops.all_reduce(s, self.tp.group)
+                    return ops.add_sigmoid_scaled(y, s_full, gl)
+                # fold the shared expert into the same reduction as the routed sum
+                y = ops.add_sigmoid_scaled(y, s, gl)
+            else:
+                y = ops.add(y, s)
+        if self.tp.ep:
+            return y                      # moe_ep already returned complete rows
+        return ops.all_reduce(y, self.tp.group)
+
+    # ------------------------------------------------------------------ head
+    def final_hidden(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is not None:
+            x = x[rows.long()]
+        h, _ = self.ops.norm(x, None, self.final_norm, self.cfg.rms_norm_eps, self.cfg.zero_centered_norm)
+        return h
+
+    def head(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp32 logits ``[R, vocab]`` (this rank's vocab shard gathered over TP)."""
+        h = self.final_hidden(x, rows)
+        logits = self.ops.linear(self.lm_head, h, out_dtype=torch.float32)
+        if self.tp.world > 1 and self.tp.group is not None:
+            logits = self.tp.group.all_gather_cols(logits)
+        return logits
+
+    def greedy(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Greedy token per row; under TP each rank reduces its shard and (value, index) pairs are merged
+        (``model.rs:2669`` ``greedy_sharded``)."""
+        h = self.final_hidden(x, rows)
+        logits = self.ops.linear(self.lm_head, h, out_dtype=torch.float32)
+        if self.tp.world > 1 and self.tp.group is not None:
+            return self.tp.group.argmax_sharded(self.ops, logits, self.lm_head.N)
+        return self.ops.argmax(logits)
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for L in self.layers:
+            for obj in (L.attn, L.gdn, L.mlp):
+                if obj is None:
+                    continue
+                for v in vars(obj).values():
+                    if isinstance(v, Linear):
+                        n += v.nbytes()
+                    elif isinstance(v, DenseMlp):
+                        n += v.gate_up.nbytes() + v.down.nbytes()
+                    elif isinstance(v, Experts):
+                        n += sum(l.nbytes() for l in v.gate_up) + sum(l.nbytes() for l in v.down)
+        if self.lm_head is not None:
+            n += self.lm_head.nbytes()
+        if self.embed is not None:
+            n += self.embed.numel() * self.embed.element_size()
+        return n
+
+
+# ---------------------------------------------------------------------------------- loader helpers
+def _load_stacked_heads(ck, mods, units, counts, rank, world, dtype, device) -> Linear:
+    """Stack q/k/v cutting each on head boundaries; KV heads replicate when world > kv_heads."""
+    parts = []
+    for mod, unit, n in zip(mods, units, counts):
+        full = Linear.load(ck, [mod], Cut.ALL, 0, 1, dtype, "cpu")
+        if world > 1:
+            if n >= world:
+                a, b = part(n, rank, world)
+            else:
+                a = rank * n // world
+                b = a + 1
+            full = _slice_rows(full, a * unit, b * unit)
+        parts.append(full)
+    lin = Linear._stack(parts) if len(parts) > 1 else parts[0]
+    lin.cut = Cut.ROWS
+    return lin.to(device)
+
+
+def _slice_rows(lin: Linear, a: int, b: int) -> Linear:
+    out = Linear(lin.fmt, b - a, lin.K)
+    out.block, out.act_quant = lin.block, lin.act_quant
+    out.w = lin.w[a:b].contiguous()
+    if lin.sf is not None:
+        if lin.fmt == Format.FP8_BLOCK:
+            bn = lin.block[0]
+            assert a % bn == 0
+            out.sf = lin.sf[a // bn:-(-b // bn)].contiguous()
+        else:
+            out.sf = lin.sf[a:b].contiguous()
+    if lin.alpha is not None:
+        out.alpha = lin.alpha[a:b].contiguous()
+    if lin.bias is not None:
+        out.bias = lin.bias[a:b].contiguous()
+    return out
+
+
+def _load_gdn_in_proj(ck, gp, hk, hv, dk, dv, rank, world, dtype, device) -> Linear:
+    qkv = Linear.load(ck, [gp + "in_proj_qkv"], Cut.ALL, 0, 1, dtype, "cpu")
+    z = Linear.load(ck, [gp + "in_proj_z"], Cut.ALL, 0, 1, dtype, "cpu")
+    b = Linear.load(ck, [gp + "in_proj_b"], Cut.ALL, 0, 1, dtype, "cpu")
+    a = Linear.load(ck, [gp + "in_proj_a"], Cut.ALL, 0, 1, dtype, "cpu")
+    ka, kb = part(hk, rank, world)
+    va, vb = part(hv, rank, world)
+    pieces = [_slice_rows(qkv, ka * dk, kb * dk), _slice_rows(qkv, hk * dk + ka * dk, hk * dk + kb * dk),
+              _slice_rows(qkv, 2 * hk * dk + va * dv, 2 * hk * dk + vb * dv), _slice_rows(z, va * dv, vb * dv),
+              _slice_rows(b, va, vb), _slice_rows(a, va, vb)]
+    if len({p.fmt for p in pieces}) != 1:
+        raise ValueError("GDN in_proj modules mix formats")
+    lin = Linear._stack(pieces)
+    lin.cut = Cut.ROWS
+    return lin.to(device)
+
+
+def _load_gdn_fused(ck, gp, hk, hv, dk, dv, rank, world, dtype, device) -> Linear:
+    """Upstream Qwen3-Next layout: ``in_proj_qkvz`` (per key head: q, k, v-group, z-group) and ``in_proj_ba``."""
+    qkvz = Linear.load(ck, [gp + "in_proj_qkvz"], Cut.ALL, 0, 1, dtype, "cpu")
+    ba = Linear.load(ck, [gp + "in_proj_ba"], Cut.ALL, 0, 1, dtype, "cpu")
+    if qkvz.fmt != Format.DENSE or ba.fmt != Format.DENSE:
+        raise ValueError("fused GDN projections are supported for dense checkpoints only")
+    rep = hv // hk
+    per = 2 * dk + 2 * rep * dv
+    w = qkvz.w.view(hk, per, -1)
+    q, k = w[:, :dk], w[:, dk:2 * dk]
+    v, z = w[:, 2 * dk:2 * dk + rep * dv], w[:, 2 * dk + rep * dv:]
+    wb = ba.w.view(hk, 2 * rep, -1)
+    bb, aa = wb[:, :rep], wb[:, rep:]
+    ka, kb = part(hk, rank, world)
+    rows = [q[ka:kb].reshape(-1, w.shape[-1]), k[ka:kb].reshape(-1, w.shape[-1]), v[ka:kb].reshape(-1, w.shape[-1]),
+            z[ka:kb].reshape(-1, w.shape[-1]), bb[ka:kb].reshape(-1, w.shape[-1]), aa[ka:kb].reshape(-1, w.shape[-1])]
+    lin = Linear.from_dense(torch.cat(rows).float(), Format.DENSE, dtype=dtype)
+    lin.cut = Cut.ROWS
+    return lin.to(device)
