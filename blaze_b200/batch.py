@@ -34,6 +34,8 @@ class StepBatch:
     q_start: torch.Tensor         # [B+1] int32
     ctx_len: torch.Tensor         # [B] int32 KV length including this step's rows
     logit_rows: torch.Tensor      # [R] int32 rows whose logits are wanted
+    item_seq: Optional[torch.Tensor] = None   # [items] attention row-block items (None = one per sequence)
+    item_q0: Optional[torch.Tensor] = None
     # host mirrors (python ints) for the oracle path and for planning
     h_slots: List[int] = field(default_factory=list)
     h_q_start: List[int] = field(default_factory=list)
@@ -54,7 +56,7 @@ class StepBatch:
 
 
 def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device, pinned: Optional[torch.Tensor] = None,
-                pad_rows_to: int = 0) -> StepBatch:
+                pad_rows_to: int = 0, attn_tokens_per_block: int = 0) -> StepBatch:
     """Pack the step metadata into one int32 buffer and copy it to ``device`` once.
 
     ``pad_rows_to`` pads T (with rows of a dummy sequence that writes to slot -1 … never; rows are
@@ -92,7 +94,15 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
         max_q = max(max_q, n)
         max_ctx = max(max_ctx, c.start_pos + n)
     lr = np.asarray(logit_rows, np.int32)
-    parts = [tokens, positions, slot_map, seq_of_row, slots, q_start, ctx_len, lr]
+    items_s: List[int] = []
+    items_q: List[int] = []
+    if attn_tokens_per_block > 0 and max_q > 1:
+        for b, c in enumerate(chunks):
+            for q0 in range(0, len(c.tokens), attn_tokens_per_block):
+                items_s.append(b)
+                items_q.append(q0)
+    parts = [tokens, positions, slot_map, seq_of_row, slots, q_start, ctx_len, lr,
+             np.asarray(items_s, np.int32), np.asarray(items_q, np.int32)]
     total = sum(p.size for p in parts)
     if pinned is not None and pinned.numel() >= total:
         stage = pinned[:total]
@@ -108,6 +118,7 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     dev = stage.to(device, non_blocking=True)
     v = [dev[o:o + n] for o, n in offs]
     return StepBatch(tokens=v[0], positions=v[1], slot_mapping=v[2], seq_of_row=v[3], slots=v[4], q_start=v[5],
-                     ctx_len=v[6], logit_rows=v[7], h_slots=[int(s) for s in slots],
+                     ctx_len=v[6], logit_rows=v[7], item_seq=v[8] if items_s else None,
+                     item_q0=v[9] if items_s else None, h_slots=[int(s) for s in slots],
                      h_q_start=[int(x) for x in q_start], h_ctx_len=[int(x) for x in ctx_len],
                      h_logit_rows=logit_rows, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)

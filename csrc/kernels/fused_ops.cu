@@ -1,0 +1,481 @@
+// Bandwidth-bound fused ops around the GEMMs:
+//   embedding gather; residual-add + RMSNorm (+ NVFP4 / MXFP8 row quantisation for the next GEMM);
+//   SwiGLU (+ quantisation); per-head q/k RMSNorm + NeoX rotary + gate split + FP8 paged-KV write in the
+//   tcgen05 attention layout; sigmoid gate; argmax with lowest-index ties; row gather.
+//
+// Same math as the reference's kernels/src/cuda/ops_basic.cu (rmsnorm_kernel :42, attn_prep_kernel :102,
+// mul_sigmoid :161, silu_mul :166, argmax_kernel :249, gather_rows :346), kernels/src/cuda/nvfp4_gemm.cu
+// quant_rows_kernel :33, kernels/src/cuda/nvfp4_kv.cu kv_store_dense_kernel :188 and embed.cu:6 — fused so
+// that each activation makes one trip through HBM between GEMMs.
+#include "blaze/host.h"
+#include "blaze/sm100.cuh"
+
+namespace blz {
+
+// ---------------------------------------------------------------------------------------------- helpers
+__device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = is_max ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float r = is_max ? -INFINITY : 0.f;
+  for (int i = 0; i < nw; ++i) r = is_max ? fmaxf(r, sh[i]) : r + sh[i];
+  return r;
+}
+
+__device__ __forceinline__ uint8_t f2e4m3(float x) {
+  return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ float e4m32f(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+// round to E2M1 code (sign bit 3); nearest, ties to the even code, saturating at 6
+__device__ __forceinline__ uint32_t f2e2m1(float x) {
+  const float a = fminf(fabsf(x), 6.0f);
+  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
+  return c | ((__float_as_uint(x) >> 31) << 3);
+}
+// byte offset of scale (row, col) in the 128x4-tiled scale array with `col_tiles` tiles per row tile
+__device__ __forceinline__ size_t sf_offset(int row, int col, int col_tiles) {
+  return ((size_t)(row >> 7) * col_tiles + (col >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (col & 3);
+}
+
+// ---------------------------------------------------------------------------------------------- embedding
+__global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
+                             __nv_bfloat16* __restrict__ out, int H, int vocab) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)tok * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------------------------- RMSNorm (+quant)
+// QUANT: 0 none (bf16 out), 1 NVFP4 (packed + tiled e4m3 scales + per-row fp32 scale), 2 MXFP8 (e4m3 + tiled e8m0)
+template <int QUANT>
+__global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+                               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                               uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out, float* __restrict__ row_scale,
+                               int H, float eps, int zero_centered, int sf_col_tiles) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(dyn);     // the (x + residual) row, then the normed row
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* xr = x + (size_t)t * H;
+  __nv_bfloat16* rr = residual ? residual + (size_t)t * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 u = *reinterpret_cast<const uint4*>(xr + i);
+    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u);
+    if (rr) {
+      uint4 ur = *reinterpret_cast<const uint4*>(rr + i);
+      const __nv_bfloat16* er = reinterpret_cast<const __nv_bfloat16*>(&ur);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(bf2f(e[j]) + bf2f(er[j]));
+      *reinterpret_cast<uint4*>(rr + i) = u;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { float f = bf2f(e[j]); ss += f * f; }
+    *reinterpret_cast<uint4*>(row + i) = u;
+  }
+  ss = block_reduce(ss, red, false);
+  const float rstd = rsqrtf(ss / H + eps);
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 u = *reinterpret_cast<uint4*>(row + i);
+    uint4 uw = *reinterpret_cast<const uint4*>(w + i);
+    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u);
+    const __nv_bfloat16* ew = reinterpret_cast<const __nv_bfloat16*>(&uw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float wf = bf2f(ew[j]) + (zero_centered ? 1.f : 0.f);
+      e[j] = __float2bfloat16(bf2f(e[j]) * rstd * wf);
+      amax = fmaxf(amax, fabsf(bf2f(e[j])));
+    }
+    if (QUANT == 0) *reinterpret_cast<uint4*>(out + (size_t)t * H + i) = u;
+    else *reinterpret_cast<uint4*>(row + i) = u;
+  }
+  if (QUANT == 0) return;
+  if (QUANT == 1) {
+    amax = block_reduce(amax, red, true);
+    const float g = fmaxf(amax / (6.f * 448.f), 1e-30f);
+    if (threadIdx.x == 0) row_scale[t] = g;
+    __syncthreads();
+    for (int b = threadIdx.x; b < H / 16; b += blockDim.x) {
+      float v[16];
+      float bm = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { v[j] = bf2f(row[b * 16 + j]); bm = fmaxf(bm, fabsf(v[j])); }
+      const uint8_t sf = f2e4m3(bm / 6.f / g);
+      const float denom = e4m32f(sf) * g;
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lo |= f2e2m1(denom > 0.f ? v[j] / denom : 0.f) << (4 * j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hi |= f2e2m1(denom > 0.f ? v[8 + j] / denom : 0.f) << (4 * j);
+      (void)inv;
+      *reinterpret_cast<uint2*>(q_out + (size_t)t * (H / 2) + b * 8) = make_uint2(lo, hi);
+      sf_out[sf_offset(t, b, sf_col_tiles)] = sf;
+    }
+  } else {
+    __syncthreads();
+    for (int b = threadIdx.x; b < H / 32; b += blockDim.x) {
+      float v[32];
+      float bm = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { v[j] = bf2f(row[b * 32 + j]); bm = fmaxf(bm, fabsf(v[j])); }
+      bm = fmaxf(bm, 1.17549435e-38f);
+      int ex = (int)ceilf(log2f(bm / 448.f));
+      ex = max(-127, min(127, ex));
+      const float inv = exp2f((float)-ex);
+      uint32_t pk[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        pk[j] = f2e4m3(v[4 * j] * inv) | (f2e4m3(v[4 * j + 1] * inv) << 8) | (f2e4m3(v[4 * j + 2] * inv) << 16) |
+                (f2e4m3(v[4 * j + 3] * inv) << 24);
+      uint4* dst = reinterpret_cast<uint4*>(q_out + (size_t)t * H + b * 32);
+      dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      sf_out[sf_offset(t, b, sf_col_tiles)] = (uint8_t)(ex + 127);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- SwiGLU (+quant)
+// gu [T, 2I] = [gate | up];  MODE 0: out bf16 [T, I];  MODE 1: NVFP4;  MODE 2: MXFP8.  Optional plain-row input
+// (gate_up == nullptr is invalid).  `src_is_act`: quantise `gu` itself ([T, I], no SwiGLU) — used for attention output.
+template <int MODE>
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                              uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out, float* __restrict__ row_scale,
+                              int I, int src_is_act, int sf_col_tiles) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(dyn);
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* g = gu + (size_t)t * (src_is_act ? I : 2 * I);
+  const __nv_bfloat16* u = g + I;
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < I; i += blockDim.x * 8) {
+    uint4 ug = *reinterpret_cast<const uint4*>(g + i);
+    __nv_bfloat16* eg = reinterpret_cast<__nv_bfloat16*>(&ug);
+    if (!src_is_act) {
+      uint4 uu = *reinterpret_cast<const uint4*>(u + i);
+      const __nv_bfloat16* eu = reinterpret_cast<const __nv_bfloat16*>(&uu);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a = bf2f(eg[j]);
+        eg[j] = __float2bfloat16(a / (1.f + __expf(-a)) * bf2f(eu[j]));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(bf2f(eg[j])));
+    if (MODE == 0) *reinterpret_cast<uint4*>(out + (size_t)t * I + i) = ug;
+    else *reinterpret_cast<uint4*>(row + i) = ug;
+  }
+  if (MODE == 0) return;
+  if (MODE == 1) {
+    amax = block_reduce(amax, red, true);
+    const float gs = fmaxf(amax / (6.f * 448.f), 1e-30f);
+    if (threadIdx.x == 0) row_scale[t] = gs;
+    __syncthreads();
+    for (int b = threadIdx.x; b < I / 16; b += blockDim.x) {
+      float v[16];
+      float bm = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { v[j] = bf2f(row[b * 16 + j]); bm = fmaxf(bm, fabsf(v[j])); }
+      const uint8_t sf = f2e4m3(bm / 6.f / gs);
+      const float denom = e4m32f(sf) * gs;
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lo |= f2e2m1(denom > 0.f ? v[j] / denom : 0.f) << (4 * j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hi |= f2e2m1(denom > 0.f ? v[8 + j] / denom : 0.f) << (4 * j);
+      *reinterpret_cast<uint2*>(q_out + (size_t)t * (I / 2) + b * 8) = make_uint2(lo, hi);
+      sf_out[sf_offset(t, b, sf_col_tiles)] = sf;
+    }
+  } else {
+    __syncthreads();
+    for (int b = threadIdx.x; b < I / 32; b += blockDim.x) {
+      float v[32];
+      float bm = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { v[j] = bf2f(row[b * 32 + j]); bm = fmaxf(bm, fabsf(v[j])); }
+      bm = fmaxf(bm, 1.17549435e-38f);
+      int ex = (int)ceilf(log2f(bm / 448.f));
+      ex = max(-127, min(127, ex));
+      const float inv = exp2f((float)-ex);
+      uint32_t pk[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        pk[j] = f2e4m3(v[4 * j] * inv) | (f2e4m3(v[4 * j + 1] * inv) << 8) | (f2e4m3(v[4 * j + 2] * inv) << 16) |
+                (f2e4m3(v[4 * j + 3] * inv) << 24);
+      uint4* dst = reinterpret_cast<uint4*>(q_out + (size_t)t * I + b * 32);
+      dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      sf_out[sf_offset(t, b, sf_col_tiles)] = (uint8_t)(ex + 127);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- attention prep
+// One warp per (token, head).  Heads 0..Hq-1 are query heads, then Hkv key heads, then Hkv value heads.
+// qkv row layout: [q heads (x2 when gated: q | gate per head)] [k heads] [v heads].
+template <int D>
+__global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                 __nv_bfloat16* __restrict__ gate_out, uint8_t* __restrict__ kv_pool,
+                                 const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+                                 const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
+                                 const __nv_bfloat16* __restrict__ k_norm_w, int T, int Hq, int Hkv, int rot_dim,
+                                 float eps, float rope_scale, int gated, int zero_centered, float k_scale_inv,
+                                 float v_scale_inv) {
+  constexpr int VPL = D / 32;
+  const int lane = threadIdx.x & 31;
+  const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int heads = Hq + 2 * Hkv;
+  if (wid >= T * heads) return;
+  const int t = wid / heads, h = wid % heads;
+  const int qw = Hq * D * (gated ? 2 : 1);
+  const size_t row_w = (size_t)qw + 2 * (size_t)Hkv * D;
+  const __nv_bfloat16* src;
+  int kind;  // 0 q, 1 k, 2 v
+  if (h < Hq) { kind = 0; src = qkv + t * row_w + (size_t)h * D * (gated ? 2 : 1); }
+  else if (h < Hq + Hkv) { kind = 1; src = qkv + t * row_w + qw + (size_t)(h - Hq) * D; }
+  else { kind = 2; src = qkv + t * row_w + qw + (size_t)Hkv * D + (size_t)(h - Hq - Hkv) * D; }
+  float v[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) v[j] = bf2f(src[lane * VPL + j]);
+  if (kind == 0 && gated) {
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) gate_out[((size_t)t * Hq + h) * D + lane * VPL + j] = src[D + lane * VPL + j];
+  }
+  if (kind < 2) {
+    const __nv_bfloat16* nw = kind == 0 ? q_norm_w : k_norm_w;
+    if (nw) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) ss += v[j] * v[j];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+      for (int j = 0; j < VPL; ++j)
+        v[j] = bf2f(__float2bfloat16(v[j] * rstd * (bf2f(nw[lane * VPL + j]) + (zero_centered ? 1.f : 0.f))));
+    }
+    // NeoX rotary over the first rot_dim dims: pairs (i, i + half)
+    const int half = rot_dim / 2;
+    const int lanes_half = half / VPL;          // partner lane distance (power of two)
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int i = lane * VPL + j;
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], lanes_half);
+      if (i < rot_dim) {
+        const int fi = i < half ? i : i - half;
+        float s, c;
+        sincosf(pos * inv_freq[fi], &s, &c);
+        s *= rope_scale; c *= rope_scale;
+        v[j] = i < half ? v[j] * c - other * s : v[j] * c + other * s;
+      }
+    }
+  }
+  if (kind == 0) {
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) q_out[((size_t)t * Hq + h) * D + lane * VPL + j] = __float2bfloat16(v[j]);
+    return;
+  }
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int page = slot >> 4, tp = slot & 15;
+  const int kh = kind == 1 ? h - Hq : h - Hq - Hkv;
+  uint8_t* blk = kv_pool + ((size_t)page * Hkv + kh) * (size_t)(2 * 16 * D);
+  if (kind == 1) {
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int i = lane * VPL + j;
+      const float r = bf2f(__float2bfloat16(v[j]));
+      blk[(tp >> 3) * 8 * D + (i >> 4) * 128 + (tp & 7) * 16 + (i & 15)] = f2e4m3(r * k_scale_inv);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int i = lane * VPL + j;
+      blk[16 * D + i * 16 + tp] = f2e4m3(v[j] * v_scale_inv);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- small elementwise
+__global__ void mul_sigmoid_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = __float2bfloat16(bf2f(x[i]) / (1.f + __expf(-bf2f(gate[i]))));
+}
+__global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16(bf2f(a[i]) + bf2f(b[i]));
+}
+// out[t, :] = a[t, :] + b[t, :] * bf16(sigmoid(gate_logit[t]))
+__global__ void add_sigmoid_scaled_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, const __nv_bfloat16* gl,
+                                          __nv_bfloat16* out, int H) {
+  const int t = blockIdx.x;
+  const float s = bf2f(__float2bfloat16(1.f / (1.f + __expf(-bf2f(gl[t])))));
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[(size_t)t * H + i] = __float2bfloat16(bf2f(a[(size_t)t * H + i]) + bf2f(b[(size_t)t * H + i]) * s);
+}
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rows,
+                                   __nv_bfloat16* __restrict__ out, int H) {
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)rows[blockIdx.x] * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// argmax over fp32 rows, lowest index wins ties; writes int64 ids (and optionally the max value)
+__global__ void argmax_kernel(const float* __restrict__ logits, long long* __restrict__ out, float* __restrict__ out_val,
+                              int V, long long ld, int index_offset) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const float* row = logits + (size_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float x = row[i];
+    if (x > best || (x == best && i < bi)) { best = x; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      out[blockIdx.x] = (long long)(bi == 0x7fffffff ? 0 : bi) + index_offset;
+      if (out_val) out_val[blockIdx.x] = best;
+    }
+  }
+}
+
+}  // namespace blz
+
+using namespace blz;
+typedef __nv_bfloat16 bf16;
+
+static void configure_once() {
+  static bool attr = false;
+  if (attr) return;
+  cudaFuncSetAttribute(swiglu_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  cudaFuncSetAttribute(swiglu_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  cudaFuncSetAttribute(rmsnorm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  cudaFuncSetAttribute(rmsnorm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  cudaFuncSetAttribute(rmsnorm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  attr = true;
+}
+
+static inline int norm_threads(int H) {
+  int t = H / 8;
+  t = (t + 31) / 32 * 32;
+  return t < 32 ? 32 : (t > 1024 ? 1024 : t);
+}
+
+BLZ_API int blz_embed(const void* table, const int* tokens, void* out, int T, int H, int vocab, cudaStream_t s) {
+  if (H % 8) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  embed_kernel<<<T, 256, 0, s>>>((const bf16*)table, tokens, (bf16*)out, H, vocab);
+  return (int)cudaGetLastError();
+}
+
+// quant: 0 → bf16 `out`; 1 → NVFP4 (q_out [T, H/2], sf_out tiled, row_scale [T]); 2 → MXFP8 (q_out [T, H], sf_out tiled)
+BLZ_API int blz_rmsnorm(const void* x, void* residual, const void* w, void* out, void* q_out, void* sf_out,
+                        float* row_scale, int T, int H, float eps, int zero_centered, int quant, cudaStream_t s) {
+  if (H % 32 || T < 0) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  configure_once();
+  const int thr = norm_threads(H);
+  const size_t sm = (size_t)H * 2;
+  const int ct = quant == 1 ? (H + 63) / 64 : (H + 127) / 128;
+  if (quant == 0)
+    rmsnorm_kernel<0><<<T, thr, sm, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, nullptr, nullptr, nullptr, H, eps, zero_centered, 0);
+  else if (quant == 1)
+    rmsnorm_kernel<1><<<T, thr, sm, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct);
+  else
+    rmsnorm_kernel<2><<<T, thr, sm, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct);
+  return (int)cudaGetLastError();
+}
+
+// mode as `quant` above; src_is_act = 1 quantises the [T, I] input as is (no SwiGLU)
+BLZ_API int blz_swiglu(const void* gu, void* out, void* q_out, void* sf_out, float* row_scale, int T, int I,
+                       int mode, int src_is_act, cudaStream_t s) {
+  if (I % 32 || T < 0) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  const int thr = norm_threads(I);
+  const size_t sm = (size_t)I * 2;
+  const int ct = mode == 1 ? (I + 63) / 64 : (I + 127) / 128;
+  configure_once();
+  if (mode == 0) swiglu_kernel<0><<<T, thr, 0, s>>>((const bf16*)gu, (bf16*)out, nullptr, nullptr, nullptr, I, src_is_act, 0);
+  else if (mode == 1) swiglu_kernel<1><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct);
+  else swiglu_kernel<2><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct);
+  return (int)cudaGetLastError();
+}
+
+BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv_pool, const int* positions,
+                          const int* slot_mapping, const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
+                          int T, int Hq, int Hkv, int D, int rot_dim, float eps, float rope_scale, int gated,
+                          int zero_centered, float k_scale, float v_scale, cudaStream_t s) {
+  if (T == 0) return 0;
+  const int half = rot_dim / 2, vpl = D / 32;
+  if ((D != 64 && D != 128 && D != 256) || rot_dim > D || half % vpl || ((half / vpl) & (half / vpl - 1)) || half / vpl > 16)
+    return (int)cudaErrorInvalidValue;
+  const int warps = T * (Hq + 2 * Hkv);
+  const int wpb = 8;
+  const int grid = (warps + wpb - 1) / wpb;
+#define BLZ_PREP(DD)                                                                                                 \
+  attn_prep_kernel<DD><<<grid, wpb * 32, 0, s>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)gate_out, (uint8_t*)kv_pool, \
+                                                 positions, slot_mapping, inv_freq, (const bf16*)q_norm_w,            \
+                                                 (const bf16*)k_norm_w, T, Hq, Hkv, rot_dim, eps, rope_scale, gated,  \
+                                                 zero_centered, 1.f / k_scale, 1.f / v_scale)
+  if (D == 64) BLZ_PREP(64); else if (D == 128) BLZ_PREP(128); else BLZ_PREP(256);
+#undef BLZ_PREP
+  return (int)cudaGetLastError();
+}
+
+BLZ_API int blz_mul_sigmoid(void* x, const void* gate, long long n, cudaStream_t s) {
+  if (n == 0) return 0;
+  mul_sigmoid_kernel<<<(int)((n + 1023) / 1024 > 4096 ? 4096 : (n + 1023) / 1024), 256, 0, s>>>((bf16*)x, (const bf16*)gate, (size_t)n);
+  return (int)cudaGetLastError();
+}
+BLZ_API int blz_add(const void* a, const void* b, void* out, long long n, cudaStream_t s) {
+  if (n == 0) return 0;
+  add_kernel<<<(int)((n + 1023) / 1024 > 4096 ? 4096 : (n + 1023) / 1024), 256, 0, s>>>((const bf16*)a, (const bf16*)b, (bf16*)out, (size_t)n);
+  return (int)cudaGetLastError();
+}
+BLZ_API int blz_add_sigmoid_scaled(const void* a, const void* b, const void* gl, void* out, int T, int H, cudaStream_t s) {
+  if (T == 0) return 0;
+  add_sigmoid_scaled_kernel<<<T, 256, 0, s>>>((const bf16*)a, (const bf16*)b, (const bf16*)gl, (bf16*)out, H);
+  return (int)cudaGetLastError();
+}
+BLZ_API int blz_gather_rows(const void* x, const int* rows, void* out, int R, int H, cudaStream_t s) {
+  if (R == 0) return 0;
+  if (H % 8) return (int)cudaErrorInvalidValue;
+  gather_rows_kernel<<<R, 256, 0, s>>>((const bf16*)x, rows, (bf16*)out, H);
+  return (int)cudaGetLastError();
+}
+BLZ_API int blz_argmax(const float* logits, long long* out, float* out_val, int R, int V, long long ld, int index_offset,
+                       cudaStream_t s) {
+  if (R == 0) return 0;
+  argmax_kernel<<<R, 1024, 0, s>>>(logits, out, out_val, V, ld, index_offset);
+  return (int)cudaGetLastError();
+}

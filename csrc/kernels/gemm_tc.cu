@@ -1,0 +1,311 @@
+// tcgen05 GEMM family:  C[M,N] = (A[M,K] · B[N,K]^T) * row_scale[m] * alpha[n] (+ bias[n])
+//
+//   kind 0  bf16 x bf16                      (kind::f16,  64 elements per 128-byte stage row)
+//   kind 1  NVFP4 x NVFP4, e4m3 scale / 16   (kind::mxf4nvf4.block_scale.scale_vec::4X, 256 elements per row)
+//   kind 2  MXFP8 x MXFP8, e8m0 scale / 32   (kind::mxf8f6f4.block_scale, 128 elements per row)
+//   kind 3  e4m3 x e4m3, no block scales     (kind::f8f6f4; per-row / per-channel scales in the epilogue)
+//
+// One persistent CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane,
+// owns the TMEM allocation), warps 2-5 = epilogue (one TMEM lane quadrant each).  Operands are staged in
+// 128B-swizzled shared memory by TMA tensor loads (never multicast); scale factors arrive by 1-D bulk
+// copies in the 128x4 tiled layout and are moved to tensor memory with tcgen05.cp; accumulators live in
+// TMEM, double-buffered so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Covers what the reference spreads over kernels/src/cuda/nvfp4_gemm.cu (w4a4_kernel :114, sm_120a-only
+// mma.sync), nvfp4_linear.cu (gemv / small-m mma kernels :49-:320), fp8_linear.cu (:40, :159, :270) and the
+// cuBLAS call in gemm.cu:55.
+#include "blaze/host.h"
+#include "blaze/sm100.cuh"
+
+namespace blz {
+
+struct GemmParams {
+  int M, N, K;               // K in elements
+  void* C;                   // bf16 or fp32 [M, ldc]
+  long long ldc;
+  const float* row_scale;    // [M] or null
+  const float* alpha;        // [N] or null
+  const __nv_bfloat16* bias; // [N] or null
+  const uint8_t* sfa;        // scale factors of A, 128x4-tiled (kinds 1, 2)
+  const uint8_t* sfb;
+  int sfa_col_tiles;         // number of 4-column tiles per 128-row tile in sfa / sfb
+  int* status;
+};
+
+template <int KIND>
+struct KindTraits;
+template <> struct KindTraits<0> { static constexpr int KMMA = 16, ELEMS_PER_BYTE_X2 = 1, SF_ATOMS = 0; };
+template <> struct KindTraits<1> { static constexpr int KMMA = 64, SF_ATOMS = 4; };
+template <> struct KindTraits<2> { static constexpr int KMMA = 32, SF_ATOMS = 1; };
+template <> struct KindTraits<3> { static constexpr int KMMA = 32, SF_ATOMS = 0; };
+
+template <int KIND, int BN>
+struct GemmCfg {
+  static constexpr int BM = 128;
+  static constexpr int KMMA = KindTraits<KIND>::KMMA;
+  static constexpr int BK = KMMA * 4;                    // elements per stage; always 128 bytes per row
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SF_ATOMS = KindTraits<KIND>::SF_ATOMS;   // 512-byte atoms per 128 rows per stage
+  static constexpr int SFA_BYTES = SF_ATOMS * 512;
+  static constexpr int SFB_BYTES = SF_ATOMS * 512 * (BN / 128);
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (SF_ATOMS ? 5 : 6);
+  static constexpr int ACC_BUFS = (BN == 256 && SF_ATOMS) ? 1 : 2;
+  static constexpr int SF_COLS_PER_STAGE = SF_ATOMS * 4 * (1 + BN / 128);
+  static constexpr int SF_COL0 = ACC_BUFS * BN;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(SF_COL0 + STAGES * SF_COLS_PER_STAGE <= 512, "TMEM budget");
+};
+
+template <int KIND, int BN, bool OUT_F32>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  using Cfg = GemmCfg<KIND, BN>;
+  constexpr int BM = Cfg::BM, BK = Cfg::BK, STAGES = Cfg::STAGES, ACC = Cfg::ACC_BUFS;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + STAGES * Cfg::A_BYTES;
+  uint8_t* sSFA = sB + STAGES * Cfg::B_BYTES;
+  uint8_t* sSFB = sSFA + STAGES * Cfg::SFA_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSFB + STAGES * Cfg::SFB_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint64_t* acc_empty = acc_full + ACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_tiles = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < ACC; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (elect_one()) {
+      int s = 0; uint32_t ph = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        const int mt = t % tiles_m, nt = t / tiles_m;
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status)) goto producer_done;
+          uint32_t bytes = Cfg::A_BYTES + Cfg::B_BYTES;
+          int atoms = 0;
+          if constexpr (Cfg::SF_ATOMS > 0) {
+            atoms = min(Cfg::SF_ATOMS, p.sfa_col_tiles - kt * Cfg::SF_ATOMS);
+            bytes += atoms * 512 * (1 + BN / 128);
+          }
+          mbar_expect_tx(&full[s], bytes);
+          const int kc = (KIND == 0) ? kt * BK : kt * 128;   // coordinate in map elements (bf16 or bytes)
+          tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, kc, mt * BM, &full[s]);
+          tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, nt * BN, &full[s]);
+          if constexpr (Cfg::SF_ATOMS > 0) {
+            const size_t a_off = ((size_t)mt * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
+            bulk_load(sSFA + s * Cfg::SFA_BYTES, p.sfa + a_off, atoms * 512, &full[s]);
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h) {
+              const size_t b_off = ((size_t)(nt * (BN / 128) + h) * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
+              bulk_load(sSFB + s * Cfg::SFB_BYTES + h * Cfg::SFA_BYTES, p.sfb + b_off, atoms * 512, &full[s]);
+            }
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    producer_done:;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      int s = 0; uint32_t ph = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+        const int ab = it % ACC;
+        const uint32_t aph = (it / ACC) & 1;
+        if (!mbar_wait(&acc_empty[ab], aph ^ 1, abort_flag, p.status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + ab * BN;
+        bool ok = true;
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES), b_addr = smem_u32(sB + s * Cfg::B_BYTES);
+          const int nblk = min(4, (p.K - kt * BK + Cfg::KMMA - 1) / Cfg::KMMA);
+          const uint32_t sf_t = tmem + Cfg::SF_COL0 + s * Cfg::SF_COLS_PER_STAGE;
+          if constexpr (Cfg::SF_ATOMS > 0) {
+            const int atoms = min(Cfg::SF_ATOMS, p.sfa_col_tiles - kt * Cfg::SF_ATOMS);
+            for (int a = 0; a < atoms; ++a) {
+              tmem_cp_sf(sf_t + a * 4, make_smem_desc(smem_u32(sSFA + s * Cfg::SFA_BYTES + a * 512), 0, 128, kSwzNone));
+#pragma unroll
+              for (int h = 0; h < BN / 128; ++h)
+                tmem_cp_sf(sf_t + Cfg::SF_ATOMS * 4 + (a * (BN / 128) + h) * 4,
+                           make_smem_desc(smem_u32(sSFB + s * Cfg::SFB_BYTES + h * Cfg::SFA_BYTES + a * 512), 0, 128, kSwzNone));
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (j < nblk) {
+              const uint64_t da = desc_sw128(a_addr + j * 32), db = desc_sw128(b_addr + j * 32);
+              const uint32_t acc = (kt > 0 || j > 0) ? 1u : 0u;
+              if constexpr (KIND == 0) {
+                mma_f16(d_tmem, da, db, make_idesc(1, 1, BM, BN), acc);
+              } else if constexpr (KIND == 3) {
+                mma_f8(d_tmem, da, db, make_idesc(0, 0, BM, BN), acc);
+              } else if constexpr (KIND == 1) {
+                mma_nvfp4(d_tmem, da, db, make_idesc_bs(1, 1, 0, BM, BN), sf_t + j * 4,
+                          sf_t + Cfg::SF_ATOMS * 4 + j * 4 * (BN / 128), acc);
+              } else {
+                // one atom holds the scales of all four K blocks; the block is selected by the sf id
+                mma_mxf8(d_tmem, da, db, make_idesc_bs(0, 0, 1, BM, BN, j, j), sf_t, sf_t + Cfg::SF_ATOMS * 4, acc);
+              }
+            }
+          }
+          mma_commit(&empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&acc_full[ab]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      const int mt = t % tiles_m, nt = t / tiles_m;
+      const int ab = it % ACC;
+      const uint32_t aph = (it / ACC) & 1;
+      if (!mbar_wait(&acc_full[ab], aph, abort_flag, p.status)) break;
+      tc_fence_after();
+      const int row = mt * BM + q * 32 + lane;
+      const float rs = (p.row_scale && row < p.M) ? p.row_scale[row] : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ab * BN + c * 32 + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        const int col0 = nt * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(r[i]) * rs;
+            const int col = col0 + i;
+            if (col < p.N) {
+              if (p.alpha) x *= __ldg(p.alpha + col);
+              if (p.bias) x += bf2f(p.bias[col]);
+            }
+            v[i] = x;
+          }
+          if constexpr (OUT_F32) {
+            float* dst = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = v[i];
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 u = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
+                                     pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+                *reinterpret_cast<uint4*>(dst + i) = u;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = __float2bfloat16(v[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[ab]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int KIND, int BN, bool OUT_F32>
+static cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
+                          cudaStream_t stream) {
+  using Cfg = GemmCfg<KIND, BN>;
+  auto kern = gemm_tc_kernel<KIND, BN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  kern<<<grid, 192, Cfg::SMEM, stream>>>(tmA, tmB, p);
+  return cudaGetLastError();
+}
+
+}  // namespace blz
+
+// kind: 0 bf16, 1 nvfp4, 2 mxfp8, 3 fp8.  A [M, K] and B [N, K] row-major (packed bytes for 4/8-bit kinds);
+// lda / ldb in BYTES.  out_f32: C is fp32, else bf16; ldc in elements.  bn: 128 or 256 (0 = choose).
+BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
+                        int M, int N, int K, const float* row_scale, const float* alpha, const void* bias,
+                        const void* sfa, const void* sfb, int out_f32, int bn, int max_ctas, cudaStream_t stream) {
+  using namespace blz;
+  if (M <= 0 || N <= 0 || K <= 0 || kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
+  const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
+  if (K % kmma) return (int)cudaErrorInvalidValue;
+  if ((kind == 1 || kind == 2) && (!sfa || !sfb)) return (int)cudaErrorInvalidValue;
+  if (bn == 0) {
+    const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
+    bn = (tiles128 >= 2L * sm_count() && N % 256 == 0) ? 256 : 128;
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.row_scale = row_scale; p.alpha = alpha;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.sfa = reinterpret_cast<const uint8_t*>(sfa); p.sfb = reinterpret_cast<const uint8_t*>(sfb);
+  p.sfa_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
+  p.status = status_word();
+  CUtensorMap tmA, tmB;
+  cudaError_t e;
+  if (kind == 0) {
+    e = encode_tmap(&tmA, A, 2, K, M, lda, 64, 128, 3);
+    if (e != cudaSuccess) return (int)e;
+    e = encode_tmap(&tmB, B, 2, K, N, ldb, 64, bn, 3);
+  } else {
+    const uint64_t kbytes = kind == 1 ? K / 2 : K;
+    e = encode_tmap(&tmA, A, 1, kbytes, M, lda, 128, 128, 3);
+    if (e != cudaSuccess) return (int)e;
+    e = encode_tmap(&tmB, B, 1, kbytes, N, ldb, 128, bn, 3);
+  }
+  if (e != cudaSuccess) return (int)e;
+#define BLZ_GEMM_CASE(KD, BNV)                                                                        \
+  if (kind == KD && bn == BNV)                                                                        \
+    return (int)(out_f32 ? launch<KD, BNV, true>(tmA, tmB, p, max_ctas, stream)                       \
+                         : launch<KD, BNV, false>(tmA, tmB, p, max_ctas, stream));
+  BLZ_GEMM_CASE(0, 128) BLZ_GEMM_CASE(0, 256) BLZ_GEMM_CASE(1, 128) BLZ_GEMM_CASE(1, 256)
+  BLZ_GEMM_CASE(2, 128) BLZ_GEMM_CASE(2, 256) BLZ_GEMM_CASE(3, 128) BLZ_GEMM_CASE(3, 256)
+#undef BLZ_GEMM_CASE
+  return (int)cudaErrorInvalidValue;
+}
