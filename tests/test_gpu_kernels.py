@@ -112,10 +112,12 @@ def test_rmsnorm_and_quant(ops):
     xd = quant.nvfp4_dequantize(qa.data, sfx, qa.row_scale)
     p, sf, gs = quant.nvfp4_quantize(want, per_row=True)
     xr = quant.nvfp4_dequantize(p, sf, gs)
-    mism = (xd != xr).float().mean().item()
-    print(f"[rmsnorm_quant] element mismatch fraction vs reference quantiser: {mism:.5f}")
-    assert mism < 0.01
-    assert (xd - want.float()).abs().mean().item() < 0.1
+    # the kernel's normed row can differ from the oracle's by one bf16 ulp, which moves the row scale; what must
+    # hold is that the kernel's quantisation error is no worse than the reference quantiser's
+    err_k = (xd - want.float()).abs().mean().item()
+    err_r = (xr - want.float()).abs().mean().item()
+    print(f"[rmsnorm_quant] mean abs quantisation error: kernel {err_k:.5f} reference {err_r:.5f}")
+    assert err_k < 1.05 * err_r + 1e-4
 
 
 def test_swiglu(ops):
