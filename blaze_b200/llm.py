@@ -1,0 +1,121 @@
+"""Public offline API: ``LLM(...).generate(prompt_token_ids, params)``.
+
+Builds the model (a local safetensors directory, or a named random-init shape), the engine and the
+scheduler, and drives requests to completion.  The HTTP server uses the same three objects with the
+scheduler running on its own thread.  Corresponds to the reference's ``Engine::load_with`` + ``Scheduler::start``
+wiring in ``crates/blaze/src/main.rs:889-1078`` and its ``generate`` subcommand (:364-551).
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from . import log
+from .config import ModelConfig, named_config
+from .engine import Engine, EngineConfig
+from .models.qwen3 import Model, TPInfo
+from .quant import Format
+from .sampler import SamplingParams
+from .sched import Finish, GenEvent, GenRequest, SchedConfig, Scheduler
+
+
+class RequestOutput:
+    def __init__(self, request_id: str):
+        self.request_id = request_id
+        self.token_ids: List[int] = []
+        self.logprobs: List[dict] = []
+        self.finish_reason: Optional[str] = None
+        self.error: Optional[str] = None
+        self.prompt_tokens = 0
+        self.cached_tokens = 0
+        self.t_first = 0.0
+        self.t_done = 0.0
+        self.hidden = None
+
+
+class LLM:
+    def __init__(self, model: Union[str, ModelConfig, Model], *, weight_format: str = "dense", device: Optional[str] = None,
+                 dtype=torch.bfloat16, tp=None, kv_cache_dtype: str = "auto", kv_tokens: int = 0, max_seqs: int = 256,
+                 max_model_len: int = 4096, chunk: int = 2048, enable_prefix_caching: bool = True, cache_slots: int = 4,
+                 use_graphs: bool = True, spec_method: str = "none", max_draft: int = 4, seed: int = 0,
+                 eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192):
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        tpi = tp if isinstance(tp, TPInfo) else TPInfo()
+        fmt = {"dense": Format.DENSE, "bf16": Format.DENSE, "nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8,
+               "fp8_block": Format.FP8_BLOCK, "fp8": Format.FP8_CHANNEL}[weight_format]
+        with log.Stage("model"):
+            if isinstance(model, Model):
+                self.model = model
+            elif isinstance(model, ModelConfig):
+                self.model = Model.random_init(model, fmt, seed, self.device, dtype, tpi)
+            elif os.path.isdir(model):
+                self.model = Model.load(model, self.device, dtype, tpi)
+            else:
+                self.model = Model.random_init(named_config(model), fmt, seed, self.device, dtype, tpi)
+        cfg = self.model.cfg
+        if kv_cache_dtype == "auto":
+            kv_cache_dtype = "fp8" if (self.device.type == "cuda" and self.model.ops.is_cuda) else \
+                ("fp32" if dtype == torch.float32 else "bf16")
+        with log.Stage("kv"):
+            self.engine = Engine(self.model, EngineConfig(kv_tokens=kv_tokens, max_seqs=max_seqs, max_model_len=max_model_len,
+                                                          kv_dtype=kv_cache_dtype, chunk=chunk, use_graphs=use_graphs))
+        eos = tuple(eos_ids) or tuple(cfg.eos_token_ids)
+        self.sched = Scheduler(self.engine, SchedConfig(chunk=chunk, max_seqs=max_seqs, prefix_cache=enable_prefix_caching,
+                                                        cache_slots=cache_slots, spec_method=spec_method, max_draft=max_draft,
+                                                        eos_ids=eos, max_model_len=max_model_len,
+                                                        max_step_tokens=max_step_tokens), drafter=drafter)
+        self._n = 0
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 on_event=None) -> List[RequestOutput]:
+        """Run ``prompts`` (lists of token ids) to completion; returns outputs in input order."""
+        outs: Dict[str, RequestOutput] = {}
+        order: List[str] = []
+
+        def sink(ev: GenEvent):
+            o = outs[ev.request_id]
+            if ev.tokens:
+                if not o.token_ids:
+                    o.t_first = time.monotonic()
+                o.token_ids.extend(ev.tokens)
+            if ev.logprobs:
+                o.logprobs.extend(ev.logprobs)
+            if ev.hidden is not None:
+                o.hidden = ev.hidden
+            if ev.finish is not None:
+                o.finish_reason, o.error, o.t_done = ev.finish.value, ev.error, time.monotonic()
+            o.prompt_tokens, o.cached_tokens = ev.prompt_tokens, ev.cached_tokens
+            if on_event:
+                on_event(ev)
+
+        for i, p in enumerate(prompts):
+            sp = params[i] if isinstance(params, (list, tuple)) else (params or SamplingParams())
+            rid = f"gen-{self._n}"
+            self._n += 1
+            outs[rid] = RequestOutput(rid)
+            order.append(rid)
+            self.sched.submit(GenRequest(rid, list(p), sp, sink=sink))
+        self.sched.run_until_idle()
+        return [outs[r] for r in order]
+
+    def embed(self, prompts: Sequence[Sequence[int]]) -> List[torch.Tensor]:
+        outs: Dict[str, RequestOutput] = {}
+        order = []
+
+        def sink(ev):
+            if ev.hidden is not None:
+                outs[ev.request_id].hidden = ev.hidden
+
+        for p in prompts:
+            rid = f"emb-{self._n}"
+            self._n += 1
+            outs[rid] = RequestOutput(rid)
+            order.append(rid)
+            self.sched.submit(GenRequest(rid, list(p), SamplingParams(max_tokens=1), embed_only=True, sink=sink))
+        self.sched.run_until_idle()
+        return [outs[r].hidden for r in order]

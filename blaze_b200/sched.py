@@ -1,0 +1,756 @@
+"""Continuous-batching scheduler: admission, chunked prefill, decode-first steps, preemption, prefix
+cache with GreedyDual-Size eviction, speculative decoding with exact-match acceptance.
+
+Policy follows the reference's ``crates/blaze/src/sched.rs``: one iteration = every decoding request
+plus prefill work up to the chunk budget, cut at prefix-cache points (``step`` :2156); FIFO admission that
+reserves KV for the prompt and for the active requests' next rows (``admit`` :1211); recompute preemption
+of the newest decoding request under KV pressure, resumed before new admissions (``preempt`` :2036,
+``resume_preempted`` :2062); prefix-cache entries worth ``inflation + tokens * usefulness(kind)`` evicted
+GreedyDual-Size style (``CacheEntry`` :81, ``lookup`` :1131, ``remember`` :1150); speculative rows are sampled
+with the request's own parameters and RNG stream and accepted while they equal the draft (:1625-1667);
+draft length chosen by an online cost model (``SpecCost`` :262, ``Acceptance`` :235).
+"""
+from __future__ import annotations
+
+import collections
+import enum
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import log
+from .batch import PAGE
+from .engine import Engine, OutOfPages, Seq, Snapshot
+from .sampler import Rng, SamplingParams, penalty_edits
+from .telemetry import Histogram
+
+
+class Finish(enum.Enum):
+    STOP = "stop"          # eos / stop token / stop string
+    LENGTH = "length"      # max_tokens or context limit
+    ABORT = "abort"
+    ERROR = "error"
+
+
+@dataclass
+class GenEvent:
+    request_id: str
+    tokens: List[int] = field(default_factory=list)
+    logprobs: Optional[List[dict]] = None
+    finish: Optional[Finish] = None
+    error: Optional[str] = None
+    prompt_tokens: int = 0
+    cached_tokens: int = 0
+    hidden: Optional[torch.Tensor] = None     # embeddings requests
+
+
+@dataclass
+class ThinkBudget:
+    """After ``budget`` tokens inside a thinking block, force ``closing`` token ids (``server.rs:616-634``)."""
+    budget: int
+    open_id: int
+    close_id: int
+    closing: List[int]
+
+
+@dataclass
+class GenRequest:
+    request_id: str
+    prompt: List[int]
+    params: SamplingParams = field(default_factory=SamplingParams)
+    cache_point: Optional[int] = None          # explicit prefix-cache boundary (token count)
+    constraint: Optional[object] = None        # structured-output constraint (mask / advance)
+    think: Optional[ThinkBudget] = None
+    embed_only: bool = False                   # return the final-normed hidden state of the last token
+    mm: Optional[object] = None                # multimodal inputs
+    sink: Optional[Callable[[GenEvent], None]] = None
+    t_submit: float = field(default_factory=time.monotonic)
+
+
+class SnapKind(enum.Enum):
+    POINT = 0     # explicit boundary (e.g. the last <|im_start|>)
+    PROMPT = 1    # end of a prompt
+    FINISH = 2    # end of a generation
+
+
+@dataclass
+class CacheEntry:
+    tokens: Tuple[int, ...]
+    snap: Snapshot
+    kind: SnapKind
+    worth: float
+    last_used: float = 0.0
+
+
+class Usefulness:
+    """(used + 1) / (made + 2) per snapshot kind with 0.98 decay (``sched.rs:139-180``)."""
+
+    def __init__(self):
+        self.used = {k: 0.0 for k in SnapKind}
+        self.made = {k: 0.0 for k in SnapKind}
+
+    def made_one(self, k: SnapKind):
+        self.made[k] = self.made[k] * 0.98 + 1.0
+        self.used[k] *= 0.98
+
+    def used_one(self, k: SnapKind):
+        self.used[k] += 1.0
+
+    def of(self, k: SnapKind) -> float:
+        return (self.used[k] + 1.0) / (self.made[k] + 2.0)
+
+
+class PrefixCache:
+    """Snapshots keyed by their token list; longest strict prefix wins; GreedyDual-Size eviction."""
+
+    def __init__(self, engine: Engine, slots: int = 4, enabled: bool = True):
+        self.engine, self.slots, self.enabled = engine, slots, enabled
+        self.entries: List[CacheEntry] = []
+        self.inflation = 0.0
+        self.use = Usefulness()
+        self.hits = self.lookups = self.hit_tokens = 0
+
+    def lookup(self, prompt: Sequence[int]) -> Optional[CacheEntry]:
+        if not self.enabled:
+            return None
+        self.lookups += 1
+        best = None
+        n = len(prompt)
+        for e in self.entries:
+            L = len(e.tokens)
+            if L < n and (best is None or L > len(best.tokens)) and tuple(prompt[:L]) == e.tokens:
+                best = e
+        if best is not None:
+            self.hits += 1
+            self.hit_tokens += len(best.tokens)
+            best.last_used = time.monotonic()
+            self.use.used_one(best.kind)
+            best.worth = self.inflation + len(best.tokens) * self.use.of(best.kind)
+        return best
+
+    def remember(self, tokens: Sequence[int], seq: Seq, kind: SnapKind) -> bool:
+        """Snapshot ``seq`` at ``len(tokens)`` (must be page aligned and equal to its length for recurrent models)."""
+        if not self.enabled or self.slots <= 0:
+            return False
+        n = len(tokens) - len(tokens) % PAGE
+        if n < PAGE:
+            return False
+        key = tuple(tokens[:n])
+        for e in self.entries:
+            if e.tokens == key:
+                e.last_used = time.monotonic()
+                return False
+        self.use.made_one(kind)
+        worth = self.inflation + n * self.use.of(kind)
+        while len(self.entries) >= self.slots:
+            victim = self._victim(protect=None, incoming=(kind, worth))
+            if victim is None:
+                return False
+            self.evict(victim)
+        try:
+            snap = self.engine.snapshot(seq, n, with_state=True)
+        except (ValueError, OutOfPages):
+            return False
+        self.entries.append(CacheEntry(key, snap, kind, worth, time.monotonic()))
+        return True
+
+    def _victim(self, protect: Optional[CacheEntry], incoming=None) -> Optional[CacheEntry]:
+        """Lowest worth; POINT anchors used recently are protected unless the newcomer is a POINT too."""
+        now = time.monotonic()
+        cands = [e for e in self.entries if e is not protect]
+        if not cands:
+            return None
+
+        def key(e):
+            guard = 1 if (e.kind == SnapKind.POINT and now - e.last_used < 60.0) else 0
+            return (guard, e.worth)
+        v = min(cands, key=key)
+        if incoming is not None and incoming[0] != SnapKind.POINT and v.kind == SnapKind.POINT and v.worth > incoming[1]:
+            return None
+        return v
+
+    def evict(self, e: CacheEntry) -> None:
+        self.inflation = max(self.inflation, e.worth)
+        self.engine.release(e.snap)
+        self.entries.remove(e)
+
+    def evict_for_room(self, protect: Optional[CacheEntry]) -> bool:
+        v = self._victim(protect)
+        if v is None:
+            return False
+        self.evict(v)
+        return True
+
+    def clear(self) -> None:
+        for e in list(self.entries):
+            self.engine.release(e.snap)
+        self.entries = []
+
+
+class Acceptance:
+    """Per-depth acceptance ratio, 0.9-decayed, shrunk towards the previous depth (``sched.rs:235-255``)."""
+
+    def __init__(self, depth: int = 16):
+        self.hit = [0.0] * depth
+        self.tried = [0.0] * depth
+
+    def record(self, drafted: int, accepted: int) -> None:
+        for d in range(min(drafted, len(self.hit))):
+            self.tried[d] = self.tried[d] * 0.9 + 1.0
+            self.hit[d] = self.hit[d] * 0.9 + (1.0 if d < accepted else 0.0)
+
+    def rate(self, d: int) -> float:
+        prev = 0.7 if d == 0 else self.rate(d - 1)
+        if d >= len(self.hit):
+            return prev
+        return (self.hit[d] + 2.0 * prev) / (self.tried[d] + 2.0)
+
+
+class SpecCost:
+    """Choose draft lengths: greedy marginal allocation by expected gain, keep the prefix of the allocation
+    order that maximises tokens/s under measured verify times by row count (``sched.rs:262-321``)."""
+
+    def __init__(self):
+        self.step_ms: Dict[int, float] = {}     # rows (bucketed) → EMA of step time
+
+    @staticmethod
+    def _bucket(rows: int) -> int:
+        b = 1
+        while b < rows:
+            b *= 2
+        return b
+
+    def observe(self, rows: int, ms: float) -> None:
+        b = self._bucket(rows)
+        self.step_ms[b] = ms if b not in self.step_ms else 0.8 * self.step_ms[b] + 0.2 * ms
+
+    def time_for(self, rows: int) -> float:
+        b = self._bucket(rows)
+        if b in self.step_ms:
+            return self.step_ms[b]
+        known = sorted(self.step_ms)
+        if not known:
+            return 1.0 + 0.001 * rows
+        lo = max([k for k in known if k <= b], default=known[0])
+        return self.step_ms[lo] * (1.0 + 0.15 * max(0, (b // max(lo, 1)) - 1))
+
+    def choose(self, acc: Sequence[Acceptance], max_draft: Sequence[int]) -> List[int]:
+        n = len(acc)
+        k = [0] * n
+        prob = [1.0] * n
+        order: List[int] = []
+        while True:
+            best, gain = -1, 0.0
+            for i in range(n):
+                if k[i] < max_draft[i]:
+                    gi = prob[i] * acc[i].rate(k[i])
+                    if gi > gain:
+                        best, gain = i, gi
+            if best < 0 or gain < 0.05:
+                break
+            prob[best] *= acc[best].rate(k[best])
+            k[best] += 1
+            order.append(best)
+        # pick the prefix of `order` with the best expected tokens per millisecond
+        best_rate, best_len = n / self.time_for(n), 0
+        exp_tokens = float(n)
+        kk = [0] * n
+        pp = [1.0] * n
+        for j, i in enumerate(order):
+            pp[i] *= acc[i].rate(kk[i])
+            kk[i] += 1
+            exp_tokens += pp[i]
+            r = exp_tokens / self.time_for(n + j + 1)
+            if r > best_rate:
+                best_rate, best_len = r, j + 1
+        out = [0] * n
+        for i in order[:best_len]:
+            out[i] += 1
+        return out
+
+
+def ngram_propose(history: Sequence[int], k: int, min_n: int = 2, max_n: int = 4, window: int = 65536) -> List[int]:
+    """Prompt-lookup drafting: longest suffix n-gram seen earlier (most recent occurrence) → following tokens
+    (``sched.rs:2450-2474``)."""
+    h = history[-window:]
+    L = len(h)
+    for n in range(min(max_n, L - 1), min_n - 1, -1):
+        suf = h[L - n:]
+        for start in range(L - n - 1, -1, -1):
+            if h[start:start + n] == suf:
+                nxt = h[start + n:start + n + k]
+                if nxt:
+                    return list(nxt)
+    return []
+
+
+@dataclass
+class SchedConfig:
+    chunk: int = 2048                  # prefill tokens per iteration
+    max_step_tokens: int = 8192
+    max_seqs: int = 256
+    prefix_cache: bool = True
+    cache_slots: int = 4
+    spec_method: str = "none"          # none | ngram | suffix | mtp | eagle
+    max_draft: int = 4
+    max_verify: int = 8
+    eos_ids: Tuple[int, ...] = ()
+    max_model_len: int = 4096
+
+
+@dataclass
+class SchedStats:
+    steps: int = 0
+    prompt_tokens: int = 0
+    cached_tokens: int = 0
+    output_tokens: int = 0
+    preemptions: int = 0
+    draft_tokens: int = 0
+    accepted_tokens: int = 0
+    finished: int = 0
+    failed: int = 0
+
+
+class Active:
+    def __init__(self, req: GenRequest, seq: Seq, cached: int):
+        self.req, self.seq = req, seq
+        self.tokens: List[int] = list(req.prompt)     # prompt + generated
+        self.n_prompt = len(req.prompt)
+        self.computed = cached                         # tokens whose KV is in the cache
+        self.cached = cached
+        self.rng = Rng(req.params.seed if req.params.seed is not None else (hash(req.request_id) & 0xFFFFFFFF))
+        self.acc = Acceptance()
+        self.t_first = 0.0
+        self.t_last = 0.0
+        self.think_used = -1
+        self.forced: Deque[int] = collections.deque()
+        self.admitted_at = time.monotonic()
+        self.snap_points: List[int] = []
+
+    @property
+    def generated(self) -> List[int]:
+        return self.tokens[self.n_prompt:]
+
+    @property
+    def decoding(self) -> bool:
+        return self.computed >= len(self.tokens) - 1 and len(self.tokens) > self.n_prompt - 1 and self.computed >= self.n_prompt - 1 and self._started
+
+    _started = False
+
+
+class Scheduler:
+    def __init__(self, engine: Engine, cfg: SchedConfig, drafter=None, sample_fn=None):
+        self.engine, self.cfg, self.drafter = engine, cfg, drafter
+        self.waiting: Deque[GenRequest] = collections.deque()
+        self.preempted: Deque[Active] = collections.deque()
+        self.active: List[Active] = []
+        self.cache = PrefixCache(engine, cfg.cache_slots, cfg.prefix_cache)
+        self.stats = SchedStats()
+        self.cost = SpecCost()
+        self.inbox: "queue.Queue[GenRequest]" = queue.Queue()
+        self.aborts: "queue.Queue[str]" = queue.Queue()
+        self._thread: Optional[threading.Thread] = None
+        self._stop = threading.Event()
+        self.ttft = Histogram.latency()
+        self.tpot = Histogram.latency()
+        self.step_ms = Histogram.latency()
+        self.sample_fn = sample_fn
+        self.on_step: Optional[Callable[[float, int], None]] = None
+        from .suffix import SuffixIndex
+        self.suffix = SuffixIndex() if cfg.spec_method == "suffix" else None
+
+    # ================================================================== public
+    def submit(self, req: GenRequest) -> None:
+        self.inbox.put(req)
+
+    def abort(self, request_id: str) -> None:
+        self.aborts.put(request_id)
+
+    def start(self) -> None:
+        self._thread = threading.Thread(target=self._loop, name="blaze-sched", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=10)
+
+    @property
+    def idle(self) -> bool:
+        return not (self.active or self.waiting or self.preempted) and self.inbox.empty()
+
+    def run_until_idle(self, max_steps: int = 1 << 30) -> None:
+        n = 0
+        while not self.idle and n < max_steps:
+            self.step()
+            n += 1
+
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            if self.idle:
+                try:
+                    self.waiting.append(self.inbox.get(timeout=0.05))
+                except queue.Empty:
+                    continue
+            try:
+                self.step()
+            except Exception as e:  # a failed step fails the active requests but keeps the loop alive
+                log.error("sched.step_failed", error=repr(e))
+                for a in list(self.active):
+                    self._retire(a, Finish.ERROR, error=repr(e))
+                self.stats.failed += 1
+
+    # ================================================================== admission
+    def _reserved(self) -> int:
+        r = 0
+        for a in self.active:
+            r += max(self.cfg.max_verify if self.cfg.spec_method != "none" else 1, len(a.tokens) - a.computed) + PAGE
+        return r
+
+    def _emit(self, a_or_req, ev: GenEvent) -> None:
+        req = a_or_req.req if isinstance(a_or_req, Active) else a_or_req
+        if req.sink:
+            req.sink(ev)
+
+    def _admit(self) -> None:
+        while True:
+            try:
+                self.waiting.append(self.inbox.get_nowait())
+            except queue.Empty:
+                break
+        while True:
+            try:
+                rid = self.aborts.get_nowait()
+            except queue.Empty:
+                break
+            for a in list(self.active):
+                if a.req.request_id == rid:
+                    self._retire(a, Finish.ABORT)
+            self.waiting = collections.deque(r for r in self.waiting if r.request_id != rid)
+        # preempted requests come back before new admissions
+        while self.preempted and self._try_admit(self.preempted[0].req, resume=self.preempted[0]):
+            self.preempted.popleft()
+        while self.waiting and not self.preempted:
+            req = self.waiting[0]
+            ok = self._try_admit(req)
+            if ok is None:
+                self.waiting.popleft()     # rejected with an error event
+                continue
+            if not ok:
+                break
+            self.waiting.popleft()
+
+    def _try_admit(self, req: GenRequest, resume: Optional[Active] = None):
+        eng = self.engine
+        tokens = resume.tokens if resume else req.prompt
+        if len(self.active) >= self.cfg.max_seqs or not eng.free_rows:
+            return False
+        if not tokens:
+            self._emit(req, GenEvent(req.request_id, finish=Finish.ERROR, error="empty prompt"))
+            return None
+        limit = min(self.cfg.max_model_len, eng.max_pages_per_seq * PAGE)
+        if len(tokens) + 1 > limit:
+            self._emit(req, GenEvent(req.request_id, finish=Finish.ERROR,
+                                     error=f"prompt of {len(tokens)} tokens exceeds the context limit {limit}"))
+            self.stats.failed += 1
+            return None
+        entry = self.cache.lookup(tokens)
+        cached = len(entry.tokens) if entry else 0
+        need = len(tokens) - cached + 16 + self._reserved()
+        while eng.free_tokens < need:
+            if not self.cache.evict_for_room(protect=entry):
+                break
+        if eng.free_tokens < need:
+            if not self.active and not self.cache.entries:
+                self._emit(req, GenEvent(req.request_id, finish=Finish.ERROR, error="prompt can never fit the KV pool"))
+                self.stats.failed += 1
+                return None
+            return False
+        seq = eng.open_from(entry.snap if entry else None)
+        if resume:
+            a = resume
+            a.seq, a.computed, a.cached = seq, cached, cached
+        else:
+            a = Active(req, seq, cached)
+            self.stats.prompt_tokens += len(tokens)
+        self.stats.cached_tokens += cached
+        # prefill cut points: explicit cache point and the page-aligned end of the prompt
+        pts = []
+        if req.cache_point and cached < req.cache_point < len(tokens):
+            pts.append(req.cache_point - req.cache_point % PAGE)
+        end = (a.n_prompt - 1) - (a.n_prompt - 1) % PAGE
+        if end > cached:
+            pts.append(end)
+        a.snap_points = sorted(set(p for p in pts if p > cached))
+        self.active.append(a)
+        return True
+
+    # ================================================================== preemption
+    def _preempt_newest(self, keep: Optional[Active] = None) -> bool:
+        cands = [a for a in self.active if a is not keep]
+        if not cands:
+            return False
+        a = max(cands, key=lambda x: x.admitted_at)
+        self.engine.close(a.seq)
+        self.active.remove(a)
+        a.seq = None
+        a.computed = 0
+        a._started = False
+        self.preempted.append(a)
+        self.stats.preemptions += 1
+        log.debug("sched.preempt", request_id=a.req.request_id, tokens=len(a.tokens))
+        return True
+
+    # ================================================================== one iteration
+    def step(self) -> None:
+        self._admit()
+        if not self.active:
+            return
+        eng, cfg = self.engine, self.cfg
+        t0 = time.monotonic()
+        # ---- plan rows: decoding requests first, then prefill work within the chunk budget
+        plan: List[Tuple[Active, List[int], int, List[int]]] = []   # (active, tokens, want_logits, draft)
+        budget = cfg.max_step_tokens
+        decoders = [a for a in self.active if a.computed == len(a.tokens) - 1 and a.computed >= a.n_prompt - 1]
+        spec = cfg.spec_method != "none" and decoders
+        drafts: Dict[int, List[int]] = {}
+        if spec:
+            drafts = self._draft(decoders)
+        for a in decoders:
+            d = drafts.get(id(a), [])
+            plan.append((a, [a.tokens[-1]] + d, 1 + len(d), d))
+            budget -= 1 + len(d)
+        chunk_left = min(cfg.chunk, max(budget, 0))
+        for a in self.active:
+            if a in decoders or chunk_left <= 0:
+                continue
+            remaining = len(a.tokens) - a.computed
+            n = min(remaining, chunk_left)
+            for pt in a.snap_points:
+                if a.computed < pt < a.computed + n:
+                    n = pt - a.computed
+                    break
+            last = a.computed + n == len(a.tokens)
+            plan.append((a, a.tokens[a.computed:a.computed + n], 1 if last else 0, []))
+            chunk_left -= n
+        if not plan:
+            return
+        # ---- KV room (recompute-preempt the newest request when pages run out)
+        while True:
+            try:
+                items = []
+                for a, toks, want, _ in plan:
+                    eng.reserve(a.seq, a.computed + len(toks))
+                    items.append((a.seq, toks, want))
+                break
+            except OutOfPages:
+                if self.cache.evict_for_room(None):
+                    continue
+                victim_ok = self._preempt_newest(keep=plan[0][0] if len(plan) == 1 else None)
+                if not victim_ok:
+                    a = plan[0][0]
+                    self._retire(a, Finish.LENGTH)
+                    return
+                plan = [p for p in plan if p[0] in self.active]
+                if not plan:
+                    return
+        for a, toks, _, _ in plan:
+            a.seq.length = a.computed            # plan() advances from here
+        chunks = eng.plan(items)
+        want_any = any(w for _, _, w, _ in plan)
+        need_logits = any(w and (a.req.params.needs_candidates() or a.req.constraint is not None or a.req.embed_only)
+                          for a, _, w, _ in plan)
+        mode = "none" if not want_any else ("both" if any(a.req.embed_only for a, _, w, _ in plan if w) else
+                                            ("logits" if need_logits else "greedy"))
+        out = eng.forward(chunks, mode)
+        # ---- consume results
+        row = 0
+        rows_total = sum(len(t) for _, t, _, _ in plan)
+        host_tokens = None
+        logits = hidden = None
+        if mode == "greedy":
+            host_tokens = out.tolist()
+            eng.d2h_bytes += out.numel() * out.element_size()
+        elif mode == "logits":
+            logits = out
+        elif mode == "both":
+            logits, hidden = out
+        for a, toks, want, draft in plan:
+            a.computed += len(toks)
+            a._started = True
+            if a.computed in a.snap_points and a.computed <= a.n_prompt:
+                kind = SnapKind.POINT if a.req.cache_point and a.computed <= a.req.cache_point else SnapKind.PROMPT
+                self.cache.remember(a.tokens[:a.computed], a.seq, kind)
+            if not want:
+                continue
+            if a.req.embed_only:
+                from .batch import StepBatch  # noqa: F401
+                h = eng.model.final_hidden(hidden, torch.tensor([eng_row_index(plan, a)], device=hidden.device))
+                self._emit(a, GenEvent(a.req.request_id, hidden=h[0].float().cpu(), prompt_tokens=a.n_prompt,
+                                       cached_tokens=a.cached))
+                self._retire(a, Finish.STOP, silent=True)
+                row += want
+                continue
+            new: List[int] = []
+            lps: List[dict] = []
+            accepted = 0
+            for j in range(want):
+                if a.forced:
+                    tok, lp = a.forced.popleft(), None
+                elif host_tokens is not None:
+                    tok, lp = host_tokens[row + j], None
+                else:
+                    tok, lp = self._sample(a, logits[row + j], new)
+                new.append(tok)
+                if lp is not None:
+                    lps.append(lp)
+                if j < len(draft) and tok == draft[j]:
+                    accepted += 1
+                    continue
+                break
+            row += want
+            if draft:
+                a.acc.record(len(draft), accepted)
+                self.stats.draft_tokens += len(draft)
+                self.stats.accepted_tokens += accepted
+                # KV of rejected draft rows is dropped; the last emitted token's KV is computed next step
+                a.computed = a.computed - len(toks) + 1 + accepted
+                eng.truncate(a.seq, a.computed)
+            self._append(a, new, lps)
+        dt = (time.monotonic() - t0) * 1e3
+        self.cost.observe(rows_total, dt)
+        self.step_ms.observe(dt / 1e3)
+        self.stats.steps += 1
+        if self.on_step:
+            self.on_step(dt, rows_total)
+
+    # ------------------------------------------------------------------ helpers
+    def _draft(self, decoders: List[Active]) -> Dict[int, List[int]]:
+        cfg = self.cfg
+        maxd = []
+        for a in decoders:
+            room = a.req.params.max_tokens - len(a.generated) - 1
+            ok = a.req.constraint is None and not a.forced
+            maxd.append(max(0, min(cfg.max_draft, room)) if ok else 0)
+        want = self.cost.choose([a.acc for a in decoders], maxd)
+        out: Dict[int, List[int]] = {}
+        if cfg.spec_method == "ngram":
+            for a, k in zip(decoders, want):
+                if k > 0:
+                    d = ngram_propose(a.tokens, k)
+                    if d:
+                        out[id(a)] = d
+        elif cfg.spec_method == "suffix" and self.suffix is not None:
+            for a, k in zip(decoders, want):
+                if k > 0:
+                    d = self.suffix.draft(a.tokens, k)
+                    if d:
+                        out[id(a)] = d
+        elif self.drafter is not None:
+            reqs = [(a, k) for a, k in zip(decoders, want) if k > 0]
+            if reqs:
+                ds = self.drafter.propose([a for a, _ in reqs], [k for _, k in reqs])
+                for (a, _), d in zip(reqs, ds):
+                    if d:
+                        out[id(a)] = list(d)
+        return out
+
+    def _sample(self, a: Active, logits_row: torch.Tensor, pending: List[int]):
+        p = a.req.params
+        edits = penalty_edits(p, a.tokens[:a.n_prompt], a.generated, self.cfg.eos_ids, draft_prefix=pending) \
+            if (p.has_penalties() or p.logit_bias) else {}
+        allowed = a.req.constraint.mask(pending) if a.req.constraint is not None else None
+        draw = a.rng.uniform()
+        fn = self.sample_fn
+        if fn is None:
+            from .sampler_torch import sample_row
+            fn = sample_row
+        res = fn(logits_row, p, draw, edits, allowed, self.engine.model.cfg.vocab_size)
+        if res.status != 0:
+            raise RuntimeError(f"sampler status {res.status} for request {a.req.request_id}")
+        lp = None
+        if p.logprobs is not None:
+            lp = {"token": res.token, "logprob": res.logprob, "top": res.top[:p.logprobs]}
+        if a.req.constraint is not None:
+            a.req.constraint.advance(res.token)
+        return res.token, lp
+
+    def _append(self, a: Active, new: List[int], lps: List[dict]) -> None:
+        now = time.monotonic()
+        p = a.req.params
+        first = not a.generated
+        out: List[int] = []
+        finish = None
+        for tok in new:
+            a.tokens.append(tok)
+            out.append(tok)
+            if self.suffix is not None:
+                self.suffix.push(tok)
+            n_gen = len(a.tokens) - a.n_prompt
+            if a.req.think is not None:
+                self._think(a, tok)
+            if not p.ignore_eos and n_gen >= p.min_tokens and (tok in self.cfg.eos_ids or tok in p.stop_token_ids):
+                finish = Finish.STOP
+                break
+            if n_gen >= p.max_tokens or len(a.tokens) + 1 >= min(self.cfg.max_model_len, self.engine.max_pages_per_seq * PAGE):
+                finish = Finish.LENGTH
+                break
+        if len(out) < len(new):
+            # tokens after the stop were sampled speculatively: drop their KV
+            drop = len(new) - len(out)
+            a.computed = min(a.computed, len(a.tokens) - 1)
+        self.stats.output_tokens += len(out)
+        if first and out:
+            a.t_first = now
+            self.ttft.observe(now - a.req.t_submit)
+        elif out and a.t_last:
+            self.tpot.observe((now - a.t_last) / len(out))
+        a.t_last = now
+        self._emit(a, GenEvent(a.req.request_id, tokens=out, logprobs=lps or None, prompt_tokens=a.n_prompt,
+                               cached_tokens=a.cached))
+        if finish is not None:
+            self._retire(a, finish)
+
+    def _think(self, a: Active, tok: int) -> None:
+        th = a.req.think
+        if tok == th.open_id:
+            a.think_used = 0
+        elif tok == th.close_id:
+            a.think_used = -1
+        elif a.think_used >= 0:
+            a.think_used += 1
+            if a.think_used >= th.budget and not a.forced:
+                a.forced.extend(th.closing)
+                a.think_used = -1
+
+    def _retire(self, a: Active, why: Finish, error: Optional[str] = None, silent: bool = False) -> None:
+        if a in self.active:
+            self.active.remove(a)
+        if a.seq is not None:
+            if why in (Finish.STOP, Finish.LENGTH) and not a.req.embed_only:
+                # keep the finished conversation for follow-up turns
+                n = a.seq.length - a.seq.length % PAGE
+                if n >= PAGE and not self.engine.kv.gdn_layers:
+                    self.cache.remember(a.tokens[:n], a.seq, SnapKind.FINISH)
+            self.engine.close(a.seq)
+            a.seq = None
+        self.stats.finished += 1
+        if not silent or why != Finish.STOP:
+            self._emit(a, GenEvent(a.req.request_id, finish=why, error=error, prompt_tokens=a.n_prompt,
+                                   cached_tokens=a.cached))
+        else:
+            self._emit(a, GenEvent(a.req.request_id, finish=why, prompt_tokens=a.n_prompt, cached_tokens=a.cached))
+
+
+def eng_row_index(plan, target) -> int:
+    """Row index (in the step's row order) of the last row of ``target``."""
+    r = 0
+    for a, toks, _, _ in plan:
+        r += len(toks)
+        if a is target:
+            return r - 1
+    raise KeyError("request not in plan")

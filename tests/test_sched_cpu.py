@@ -1,0 +1,111 @@
+"""Scheduler / LLM API on CPU: batching, chunked prefill, prefix cache, preemption, n-gram speculation exactness."""
+import torch
+
+from blaze_b200.config import named_config
+from blaze_b200.llm import LLM
+from blaze_b200.sampler import SamplingParams
+from blaze_b200.sched import PrefixCache, SpecCost, Acceptance, ngram_propose
+
+
+def _llm(**kw):
+    base = dict(device="cpu", dtype=torch.float32, max_seqs=8, max_model_len=256, use_graphs=False, seed=0)
+    base.update(kw)
+    return LLM(named_config("tiny"), **base)
+
+
+def _prompts(n, L, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 1024, (n, L), generator=g).tolist()
+
+
+GREEDY = SamplingParams(temperature=0.0, max_tokens=12)
+
+
+def test_generate_matches_single_request_runs():
+    llm = _llm()
+    ps = _prompts(5, 20)
+    batch = llm.generate(ps, GREEDY)
+    for p, o in zip(ps, batch):
+        solo = _llm().generate([p], GREEDY)[0]
+        assert o.token_ids == solo.token_ids
+        assert o.finish_reason == "length" and len(o.token_ids) == 12
+
+
+def test_chunked_prefill_equals_unchunked():
+    ps = _prompts(3, 70, seed=1)
+    a = _llm(chunk=2048).generate(ps, GREEDY)
+    b = _llm(chunk=16).generate(ps, GREEDY)
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+
+
+def test_prefix_cache_hit_gives_same_tokens():
+    llm = _llm()
+    base = _prompts(1, 64, seed=2)[0]
+    first = llm.generate([base + [5, 6, 7]], GREEDY)[0]
+    assert llm.sched.cache.entries, "the finished request should have left a snapshot"
+    second = llm.generate([base + [5, 6, 7] + first.token_ids[:4] + [9]], GREEDY)[0]
+    assert second.cached_tokens >= 64
+    cold = _llm(enable_prefix_caching=False).generate([base + [5, 6, 7] + first.token_ids[:4] + [9]], GREEDY)[0]
+    assert second.token_ids == cold.token_ids
+
+
+def test_preemption_under_kv_pressure_keeps_outputs():
+    ps = _prompts(6, 40, seed=3)
+    want = [o.token_ids for o in _llm().generate(ps, SamplingParams(temperature=0.0, max_tokens=30))]
+    small = _llm(kv_tokens=16 * 16, enable_prefix_caching=False)   # 16 pages: cannot hold six 70-token sequences
+    got = small.generate(ps, SamplingParams(temperature=0.0, max_tokens=30))
+    assert [o.token_ids for o in got] == want
+    assert small.sched.stats.preemptions > 0
+    assert small.engine.pages.free_count == small.engine.num_pages - 1
+
+
+def test_ngram_speculation_is_exact():
+    rep = [3, 4, 5, 6, 7, 8] * 6
+    ps = [rep, _prompts(1, 30, seed=4)[0]]
+    want = [o.token_ids for o in _llm().generate(ps, SamplingParams(temperature=0.0, max_tokens=24))]
+    spec = _llm(spec_method="ngram")
+    got = spec.generate(ps, SamplingParams(temperature=0.0, max_tokens=24))
+    assert [o.token_ids for o in got] == want
+    assert spec.sched.stats.draft_tokens > 0
+
+
+def test_sampled_generation_is_seeded():
+    ps = _prompts(2, 16, seed=5)
+    sp = SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=7, max_tokens=8)
+    a = [o.token_ids for o in _llm().generate(ps, sp)]
+    b = [o.token_ids for o in _llm().generate(ps, sp)]
+    assert a == b
+    c = [o.token_ids for o in _llm().generate(ps, SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=8, max_tokens=8))]
+    assert a != c
+
+
+def test_stop_token_and_logprobs():
+    llm = _llm()
+    p = _prompts(1, 10, seed=6)[0]
+    free = llm.generate([p], SamplingParams(temperature=0.0, max_tokens=10, logprobs=3))[0]
+    assert len(free.logprobs) == 10 and all(len(l["top"]) == 3 for l in free.logprobs)
+    assert all(l["logprob"] <= 0 for l in free.logprobs)
+    stop_at = free.token_ids[4]
+    cut = llm.generate([p], SamplingParams(temperature=0.0, max_tokens=10, stop_token_ids=(stop_at,)))[0]
+    assert cut.finish_reason == "stop" and cut.token_ids[-1] == stop_at and len(cut.token_ids) <= 5
+
+
+def test_spec_cost_and_ngram_helpers():
+    assert ngram_propose([1, 2, 3, 9, 1, 2, 3], 2) == [9, 1]
+    assert ngram_propose([1, 2, 3], 2) == []
+    acc = Acceptance()
+    for _ in range(20):
+        acc.record(4, 4)
+    bad = Acceptance()
+    for _ in range(20):
+        bad.record(4, 0)
+    cost = SpecCost()
+    for rows in (1, 2, 4, 8, 16):
+        cost.observe(rows, 10.0 * rows)
+    k = cost.choose([acc, bad], [4, 4])
+    assert k[0] >= k[1] and k[1] <= 1
+    for rows in (1, 2, 4, 8, 16):
+        for _ in range(30):
+            cost.observe(rows, 10.0)
+    k = cost.choose([acc, bad], [4, 4])
+    assert k[0] >= 3
