@@ -279,6 +279,10 @@ class Engine:
             self._graphs[key] = g
         return g.replay(chunks)
 
+    def graph_kernel_count(self) -> int:
+        """Kernels of this library inside one captured decode step (the largest captured bucket)."""
+        return max((g.kernels for g in self._graphs.values()), default=0)
+
     # ================================================================== watchdog
     def start_watchdog(self, on_hang=None) -> threading.Thread:
         """Report (never kill) a step that runs longer than ``hang_secs`` (``engine.rs:582-656``)."""
@@ -323,6 +327,7 @@ class _Graph:
         self.batch.max_ctx = eng.ecfg.max_model_len
         self.graph = None
         self.out = None
+        self.kernels = 0
 
     def _fill(self, chunks: Sequence[SeqChunk]) -> int:
         n, B = self.bucket, len(chunks)
@@ -352,7 +357,9 @@ class _Graph:
         if self.graph is None:
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
+            l0 = self.eng.model.ops.launches
             with torch.cuda.graph(self.graph):
                 self.out = self.eng._run(self.batch, "greedy")
+            self.kernels = self.eng.model.ops.launches - l0
         self.graph.replay()
         return self.out[:B]
