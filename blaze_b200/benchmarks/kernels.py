@@ -1,0 +1,151 @@
+"""Kernel micro-benchmarks (device-timed with CUDA events, L2 flushed between iterations).
+
+    python -m blaze_b200.benchmarks.kernels attention --batch 256 --ctx 1024 --hq 32 --hkv 8
+    python -m blaze_b200.benchmarks.kernels gemm --kind nvfp4 --m 256 --n 24576 --k 4096
+    python -m blaze_b200.benchmarks.kernels norm --rows 256 --hidden 4096
+
+Each prints one JSON line with the achieved bandwidth / FLOP rate and its fraction of the measured peaks in
+``MEASURED_PEAKS.json`` when that file is present.  Plays the role of the reference's manual kernel benches
+(``kernels/tests/bench_attn_prefill.cu``, ``bench_mma_peak.cu``, ``kernels/tools/membw.cpp``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+def timeit(fn, iters: int, warmup: int = 3, flush: bool = True):
+    scratch = torch.empty(192 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush:
+            scratch.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def bench_attention(a):
+    from ..batch import SeqChunk, build_batch
+    from ..config import ModelConfig, RopeConfig
+    from ..kv import KVCache
+    from ..ops import get_ops
+    ops = get_ops("cuda")
+    D = 128
+    cfg = ModelConfig(hidden_size=a.hq * D, num_heads=a.hq, num_kv_heads=a.hkv, head_dim=D, num_layers=1, rope=RopeConfig(theta=1e6))
+    cfg.layer_types = ["full_attention"]
+    B = a.batch
+    pages_per = (a.ctx + 15) // 16 + 1
+    kv = KVCache(cfg, 1 + B * pages_per, B, pages_per, "fp8", "cuda", "umma")
+    perm = torch.randperm(B * pages_per).tolist()
+    for b in range(B):
+        kv.set_pages(b, [1 + p for p in perm[b * pages_per:(b + 1) * pages_per]])
+    kv.kv[0].copy_(torch.randint(0, 120, kv.kv[0].shape, dtype=torch.uint8, device="cuda"))   # finite e4m3 codes
+    tpb = 128 // (a.hq // a.hkv)
+    chunks = [SeqChunk(b, [0] * a.qlen, a.ctx - a.qlen) for b in range(B)]
+    batch = build_batch(chunks, kv.block_table_host, "cuda", attn_tokens_per_block=tpb)
+    q = torch.randn(B * a.qlen, a.hq, D, device="cuda").bfloat16()
+
+    class M:
+        pass
+    fn = lambda: ops.attention(q, M, batch, kv, 0, D ** -0.5, splits=a.splits)  # noqa: E731
+    med, best = timeit(fn, a.iters)
+    causal = 1.0 if a.qlen == 1 else (a.ctx - a.qlen / 2) / a.ctx
+    kv_bytes = B * a.ctx * a.hkv * 2 * D * (1.0 if a.qlen <= tpb else 1.0)
+    flops = 4.0 * B * a.qlen * a.hq * a.ctx * causal * D
+    pk = peaks()
+    print(json.dumps({"kernel": "attn_tc", "batch": B, "ctx": a.ctx, "qlen": a.qlen, "hq": a.hq, "hkv": a.hkv,
+                      "ms_median": med, "ms_best": best, "kv_gbs": kv_bytes / med / 1e6,
+                      "frac_hbm_" + pk["src"]: kv_bytes / med / 1e6 / pk["hbm_gbs"], "tflops": flops / med / 1e9,
+                      "status": ops.take_status()}))
+
+
+def bench_gemm(a):
+    from ..linear import Linear
+    from ..ops import get_ops
+    from ..quant import Format
+    ops = get_ops("cuda")
+    fmt = {"bf16": Format.DENSE, "nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "fp8": Format.FP8_CHANNEL}[a.kind]
+    w = torch.randn(a.n, a.k, device="cuda") * 0.02
+    lin = Linear.from_dense(w, fmt)
+    del w
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    xin = ops.quantize_rows(x, lin) if ops._qmode(lin) else x
+    out = torch.empty(a.m, a.n, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: ops.linear(lin, xin, out=out, bn=a.bn)  # noqa: E731
+    med, best = timeit(fn, a.iters)
+    flops = 2.0 * a.m * a.n * a.k
+    wbytes = lin.nbytes()
+    pk = peaks()
+    print(json.dumps({"kernel": f"gemm_tc {a.kind}", "m": a.m, "n": a.n, "k": a.k, "bn": a.bn, "ms_median": med, "ms_best": best,
+                      "tflops": flops / med / 1e9, "x_bf16_cublas_" + pk["src"]: flops / med / 1e9 / pk["bf16_tflops"],
+                      "weight_gbs": wbytes / med / 1e6, "status": ops.take_status()}))
+
+
+def bench_norm(a):
+    from ..linear import Linear
+    from ..ops import get_ops
+    from ..quant import Format
+    ops = get_ops("cuda")
+    x = torch.randn(a.rows, a.hidden, device="cuda").bfloat16()
+    r = torch.randn(a.rows, a.hidden, device="cuda").bfloat16()
+    w = torch.ones(a.hidden, device="cuda").bfloat16()
+    lin = Linear.from_dense(torch.randn(128, a.hidden, device="cuda") * 0.02, Format.NVFP4)
+    fn = lambda: ops.norm(x, r, w, 1e-6, quant_for=lin)  # noqa: E731
+    med, best = timeit(fn, a.iters)
+    nbytes = a.rows * a.hidden * (2 + 2 + 2 + 0.5625)
+    pk = peaks()
+    print(json.dumps({"kernel": "rmsnorm+nvfp4", "rows": a.rows, "hidden": a.hidden, "ms_median": med,
+                      "gbs": nbytes / med / 1e6, "frac_hbm_" + pk["src"]: nbytes / med / 1e6 / pk["hbm_gbs"]}))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="blaze_b200.benchmarks.kernels")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("attention")
+    p.add_argument("--batch", type=int, default=256)
+    p.add_argument("--ctx", type=int, default=1024)
+    p.add_argument("--qlen", type=int, default=1)
+    p.add_argument("--hq", type=int, default=32)
+    p.add_argument("--hkv", type=int, default=8)
+    p.add_argument("--splits", type=int, default=0)
+    p.add_argument("--iters", type=int, default=10)
+    p = sub.add_parser("gemm")
+    p.add_argument("--kind", default="nvfp4")
+    p.add_argument("--m", type=int, default=256)
+    p.add_argument("--n", type=int, default=6144)
+    p.add_argument("--k", type=int, default=4096)
+    p.add_argument("--bn", type=int, default=0)
+    p.add_argument("--iters", type=int, default=10)
+    p = sub.add_parser("norm")
+    p.add_argument("--rows", type=int, default=256)
+    p.add_argument("--hidden", type=int, default=4096)
+    p.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args(argv)
+    {"attention": bench_attention, "gemm": bench_gemm, "norm": bench_norm}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
