@@ -13,6 +13,7 @@ import numpy as np
 import torch
 
 PAGE = 16
+SMALL_ROWS = 64     # sequences with q_len * group <= this use the decode attention kernel
 
 
 @dataclass
@@ -36,6 +37,8 @@ class StepBatch:
     logit_rows: torch.Tensor      # [R] int32 rows whose logits are wanted
     item_seq: Optional[torch.Tensor] = None   # [items] attention row-block items (None = one per sequence)
     item_q0: Optional[torch.Tensor] = None
+    small_rows_max: int = 0       # largest q_len * group among sequences handled by the decode attention kernel
+    num_large: int = 0            # sequences handled by the row-block (prefill) attention kernel
     # host mirrors (python ints) for the oracle path and for planning
     h_slots: List[int] = field(default_factory=list)
     h_q_start: List[int] = field(default_factory=list)
@@ -56,7 +59,7 @@ class StepBatch:
 
 
 def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device, pinned: Optional[torch.Tensor] = None,
-                pad_rows_to: int = 0, attn_tokens_per_block: int = 0) -> StepBatch:
+                pad_rows_to: int = 0, attn_group: int = 0) -> StepBatch:
     """Pack the step metadata into one int32 buffer and copy it to ``device`` once.
 
     ``pad_rows_to`` pads T (with rows of a dummy sequence that writes to slot -1 … never; rows are
@@ -96,9 +99,16 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     lr = np.asarray(logit_rows, np.int32)
     items_s: List[int] = []
     items_q: List[int] = []
-    if attn_tokens_per_block > 0 and max_q > 1:
+    small_rows_max = num_large = 0
+    if attn_group > 0:
+        tpb = max(128 // attn_group, 1)
         for b, c in enumerate(chunks):
-            for q0 in range(0, len(c.tokens), attn_tokens_per_block):
+            rows = len(c.tokens) * attn_group
+            if rows <= SMALL_ROWS:
+                small_rows_max = max(small_rows_max, rows)
+                continue
+            num_large += 1
+            for q0 in range(0, len(c.tokens), tpb):
                 items_s.append(b)
                 items_q.append(q0)
     parts = [tokens, positions, slot_map, seq_of_row, slots, q_start, ctx_len, lr,
@@ -121,4 +131,4 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
                      ctx_len=v[6], logit_rows=v[7], item_seq=v[8] if items_s else None,
                      item_q0=v[9] if items_s else None, h_slots=[int(s) for s in slots],
                      h_q_start=[int(x) for x in q_start], h_ctx_len=[int(x) for x in ctx_len],
-                     h_logit_rows=logit_rows, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)
+                     h_logit_rows=logit_rows, small_rows_max=small_rows_max, num_large=num_large, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)

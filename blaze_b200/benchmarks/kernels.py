@@ -65,7 +65,7 @@ def bench_attention(a):
     kv.kv[0].copy_(torch.randint(0, 120, kv.kv[0].shape, dtype=torch.uint8, device="cuda"))   # finite e4m3 codes
     tpb = 128 // (a.hq // a.hkv)
     chunks = [SeqChunk(b, [0] * a.qlen, a.ctx - a.qlen) for b in range(B)]
-    batch = build_batch(chunks, kv.block_table_host, "cuda", attn_tokens_per_block=tpb)
+    batch = build_batch(chunks, kv.block_table_host, "cuda", attn_group=a.hq // a.hkv)
     q = torch.randn(B * a.qlen, a.hq, D, device="cuda").bfloat16()
 
     class M:

@@ -119,6 +119,9 @@ class Engine:
         self._pinned = None
         if self.device.type == "cuda":
             self._pinned = torch.empty(1 << 20, dtype=torch.int32, pin_memory=True)
+        self.attn_group = 0
+        if model.ops.is_cuda:
+            self.attn_group = max(max(cfg.num_heads // tpw, 1) // max(cfg.num_kv_heads // tpw, 1), 1)
         self.steps = 0
         self.last_step_started = 0.0
         self.last_step_what = ""
@@ -237,12 +240,7 @@ class Engine:
 
     def _build(self, chunks: Sequence[SeqChunk]) -> StepBatch:
         cfg = self.model.cfg
-        tpb = 0
-        if self.model.ops.is_cuda:
-            tpw = self.model.tp.world
-            group = max(cfg.num_heads // tpw, 1) // max(cfg.num_kv_heads // tpw, 1)
-            tpb = max(128 // max(group, 1), 1)
-        batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned, attn_tokens_per_block=tpb)
+        batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned, attn_group=self.attn_group)
         self.h2d_bytes += batch.h2d_bytes
         return batch
 
@@ -325,6 +323,7 @@ class _Graph:
         self.batch.h_ctx_len = [1] * n
         self.batch.h_logit_rows = list(range(n))
         self.batch.max_ctx = eng.ecfg.max_model_len
+        self.batch.small_rows_max = max(eng.attn_group, 1)
         self.graph = None
         self.out = None
         self.kernels = 0

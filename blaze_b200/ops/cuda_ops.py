@@ -50,6 +50,9 @@ class CudaOps:
                                       _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_float, _c.c_float, VP]
         lib.blz_attn_tc.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                     _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
+        lib.blz_attn_decode.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                        _c.c_float, _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                        VP, VP, _c.c_int, VP]
         lib.blz_mul_sigmoid.argtypes = [VP, VP, _c.c_longlong, VP]
         lib.blz_add.argtypes = [VP, VP, VP, _c.c_longlong, VP]
         lib.blz_add_sigmoid_scaled.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
@@ -251,28 +254,45 @@ class CudaOps:
         return q, gate
 
     def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0):
+        """Sequences with few query rows (decode, verify) go to the decode kernel, the rest to the row-block kernel."""
         T, Hq, D = q.shape
         Hkv = kv.kv_heads
+        group = Hq // Hkv
         out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=self.device)
+        B = batch.slots.numel()
+        tiles = max((batch.max_ctx + 127) // 128, 1)
+        small = batch.small_rows_max if (batch.small_rows_max or batch.num_large) else group * batch.max_q_len
+        if small > 0:
+            nmax = 16 if small <= 16 else 32
+            rb = (small + nmax - 1) // nmax
+            work = B * Hkv * rb
+            sp = splits if splits > 0 else (1 if work >= 2 * self._sm else max(1, min(8, tiles, (2 * self._sm) // max(work, 1))))
+            po = pm = None
+            if sp > 1:
+                n = work * sp * nmax
+                po = self._buf("attn_part_o", n * D * 4).view(torch.float32)
+                pm = self._buf("attn_part_ml", n * 2 * 4).view(torch.float32)
+            self._check(self.lib.blz_attn_decode(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
+                                                 _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), B, Hq, Hkv, D,
+                                                 kv.block_table.stride(0), scale, 1.0, 1.0, nmax, rb, 1, small, sp,
+                                                 _ptr(po), _ptr(pm), max_ctas, self._stream()), "attn_decode")
+            if sp > 1:
+                self.launches += 1
         if batch.item_seq is not None:
-            n_items, iseq, iq0 = batch.item_seq.numel(), batch.item_seq, batch.item_q0
-        else:
-            n_items, iseq, iq0 = batch.slots.numel(), None, None
-        if splits <= 0:
+            n_items = batch.item_seq.numel()
             work = n_items * Hkv
-            tiles = max((batch.max_ctx + 127) // 128, 1)
-            splits = 1 if work >= self._sm else max(1, min(8, tiles, self._sm // max(work, 1)))
-        po = pm = None
-        if splits > 1:
-            n = n_items * Hkv * splits * 128
-            po = self._buf("attn_part_o", n * D * 4)
-            pm = self._buf("attn_part_ml", n * 2 * 4)
-        self._check(self.lib.blz_attn_tc(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table), _ptr(batch.slots),
-                                         _ptr(batch.q_start), _ptr(batch.ctx_len), _ptr(iseq), _ptr(iq0), n_items, Hq, Hkv, D,
-                                         kv.block_table.stride(0), scale, 1.0, 1.0, splits, _ptr(po), _ptr(pm), max_ctas,
-                                         self._stream()), "attention")
-        if splits > 1:
-            self.launches += 1
+            sp = splits if splits > 0 else (1 if work >= self._sm else max(1, min(8, tiles, self._sm // max(work, 1))))
+            po = pm = None
+            if sp > 1:
+                n = work * sp * 128
+                po = self._buf("attn_part_o2", n * D * 4).view(torch.float32)
+                pm = self._buf("attn_part_ml2", n * 2 * 4).view(torch.float32)
+            self._check(self.lib.blz_attn_tc(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
+                                             _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), _ptr(batch.item_seq),
+                                             _ptr(batch.item_q0), n_items, Hq, Hkv, D, kv.block_table.stride(0), scale, 1.0,
+                                             1.0, sp, _ptr(po), _ptr(pm), max_ctas, self._stream()), "attn_prefill")
+            if sp > 1:
+                self.launches += 1
         return out.view(T, Hq * D)
 
     # ------------------------------------------------------------------ head

@@ -1,0 +1,415 @@
+// Paged GQA decode / speculative-verify attention over FP8 KV on tcgen05, tokens on the TMEM lanes.
+//
+// With one (or a few) query tokens per sequence only `q_len * group` rows are live; putting them on the MMA's
+// M dimension would leave 124 of 128 softmax rows idle and makes the exponential unit the bottleneck.  Here the
+// problem is transposed:
+//     S^T = K Q^T   : A = K tile [128 tokens x D] (smem, straight from the page pool), B = Q [NMAX rows x D]
+//     O^T_t = V^T P^T : A = V^T tile [D x 128 tokens] (smem, from the pool), B = P [NMAX rows x 128 tokens]
+// so every softmax thread owns one key position and touches only NMAX (16 or 32) columns of tensor memory, and
+// every accumulate thread owns one output dimension with NMAX running sums in registers.  Row maxima are
+// exchanged across the four softmax warps once per tile; row sums are reduced once per work item.
+//
+// Work item = (sequence, kv head, block of NMAX rows, kv split); persistent CTAs; 192 threads (page loader warp,
+// MMA warp, four softmax warps); 2 CTAs per SM for NMAX = 16.  Every wait is a bounded mbarrier wait.
+//
+// Reference counterparts: kernels/src/cuda/mha_nvfp4.cu mha_decode_kernel :259 and mha_combine_kernel :572,
+// kernels/src/cuda/mha_verify.cu verify_kernel :50.
+#include "blaze/attn.cuh"
+#include "blaze/host.h"
+
+namespace blz {
+
+template <int NMAX>
+struct DecCfg {
+  static constexpr int D = 128;
+  static constexpr int PAGE_BYTES = 16 * D;
+  static constexpr int TILE_BYTES = 8 * PAGE_BYTES;
+  static constexpr int STAGES = 3;
+  static constexpr int Q_BYTES = NMAX * D;
+  static constexpr int P_BYTES = NMAX * 128;
+  static constexpr int TMEM_COLS = NMAX <= 16 ? 64 : 128;
+  static constexpr int SMEM = Q_BYTES + STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 1024 + 512;
+};
+
+template <int N>
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[N]) {
+  if constexpr (N == 16) tmem_ld16(taddr, r); else tmem_ld32(taddr, r);
+}
+
+template <int NMAX>
+__global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(AttnParams p) {
+  using Cfg = DecCfg<NMAX>;
+  constexpr int ST = Cfg::STAGES, D = Cfg::D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + ST * Cfg::TILE_BYTES;
+  uint8_t* sQ = sV + ST * Cfg::TILE_BYTES;
+  uint8_t* sP = sQ + Cfg::Q_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::P_BYTES);
+  uint64_t* k_full = bars;                 // [ST]
+  uint64_t* v_full = k_full + ST;          // [ST]
+  uint64_t* kv_empty = v_full + ST;        // [ST]
+  uint64_t* s_full = kv_empty + ST;        // [2]
+  uint64_t* s_empty = s_full + 2;          // [2]
+  uint64_t* p_full = s_empty + 2;          // [2]
+  uint64_t* o_full = p_full + 2;           // [2]
+  uint64_t* o_empty = o_full + 2;          // [2]
+  uint64_t* wm_bar = o_empty + 2;          // [2] row-max exchange among the softmax warps
+  uint64_t* q_full = wm_bar + 2;           // [1]
+  uint64_t* q_empty = q_full + 1;          // [1]
+  uint64_t* fin_bar = q_empty + 1;         // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fin_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float s_c[NMAX];
+  __shared__ int s_pos[NMAX];
+  __shared__ float s_wmax[2][4][NMAX];
+  __shared__ float s_l[4][NMAX];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&p_full[i], 4);
+      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4); mbar_init(&wm_bar[i], 4);
+    }
+    mbar_init(q_full, 4); mbar_init(q_empty, 1); mbar_init(fin_bar, 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  const int group = p.Hq / p.Hkv;
+  const int total = p.num_items * p.Hkv * p.row_blocks * p.splits;
+  int g = 0, item_it = 0;
+
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    const int split = w % p.splits;
+    const int rb = (w / p.splits) % p.row_blocks;
+    const int kh = (w / (p.splits * p.row_blocks)) % p.Hkv;
+    const int b = w / (p.splits * p.row_blocks * p.Hkv);
+    const int r0 = p.q_start[b], qlen = p.q_start[b + 1] - r0;
+    const int rows_total = qlen * group;
+    if (rows_total < p.min_rows || rows_total > p.max_rows) continue;
+    const int row0 = rb * NMAX;
+    const int nrows = min(NMAX, rows_total - row0);
+    if (nrows <= 0) continue;
+    const int ctx = p.ctx_len[b];
+    const int kv_end = ctx - qlen + (row0 + nrows - 1) / group + 1;       // keys visible to the block's last row
+    const int tiles_all = (kv_end + 127) >> 7;
+    const int per = (tiles_all + p.splits - 1) / p.splits;
+    const int t0 = split * per;
+    const int n = max(min(tiles_all, t0 + per) - t0, 0);
+    const int slot = p.slots[b];
+
+    if (warp == 0) {
+      // -------------------------------------------------------------- page loader
+      const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+      const int npages = (kv_end + 15) >> 4;
+      for (int i = 0; i < n; ++i) {
+        const int gi = g + i, s = gi % ST;
+        if (!mbar_wait(&kv_empty[s], ((gi / ST) & 1) ^ 1, abort_flag, p.status)) break;
+        if (lane == 0) {
+          mbar_expect_tx(&k_full[s], Cfg::TILE_BYTES);
+          mbar_expect_tx(&v_full[s], Cfg::TILE_BYTES);
+        }
+        __syncwarp();
+        if (lane < 16) {
+          const int pg = lane & 7;
+          const int pidx = (t0 + i) * 8 + pg;
+          const int page = pidx < npages ? bt[pidx] : 0;          // page 0 is the all-zero scratch page
+          const uint8_t* src = p.pool + ((size_t)page * p.Hkv + kh) * (size_t)(2 * Cfg::PAGE_BYTES);
+          if (lane < 8) bulk_load(sK + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &k_full[s]);
+          else bulk_load(sV + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src + Cfg::PAGE_BYTES, Cfg::PAGE_BYTES, &v_full[s]);
+        }
+        __syncwarp();
+      }
+    } else if (warp == 1) {
+      // -------------------------------------------------------------- MMA issuer
+      if (lane == 0 && n > 0) {
+        bool ok = mbar_wait(q_full, item_it & 1, abort_flag, p.status);
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ);
+        auto issue_pv = [&](int gj) -> bool {
+          const int s = gj % ST, pb = gj & 1;
+          if (!mbar_wait(&v_full[s], (gj / ST) & 1, abort_flag, p.status)) return false;
+          if (!mbar_wait(&p_full[pb], (gj >> 1) & 1, abort_flag, p.status)) return false;
+          if (!mbar_wait(&o_empty[pb], ((gj >> 1) & 1) ^ 1, abort_flag, p.status)) return false;
+          tc_fence_after();
+          const uint32_t pa = smem_u32(sP + pb * Cfg::P_BYTES), va = smem_u32(sV + s * Cfg::TILE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_f8(tmem + 2 * NMAX + pb * NMAX,
+                   make_smem_desc(va + ks * 2 * Cfg::PAGE_BYTES, Cfg::PAGE_BYTES, 128, kSwzNone),
+                   make_smem_desc(pa + ks * 256, 128, 1024, kSwzNone), make_idesc(0, 0, 128, NMAX), ks > 0);
+          mma_commit(&o_full[pb]);
+          mma_commit(&kv_empty[s]);
+          return true;
+        };
+        for (int i = 0; i < n && ok; ++i) {
+          const int gi = g + i, s = gi % ST, sb = gi & 1;
+          if (!mbar_wait(&k_full[s], (gi / ST) & 1, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(&s_empty[sb], ((gi >> 1) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t ka = smem_u32(sK + s * Cfg::TILE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < D / 32; ++ks)
+            mma_f8(tmem + sb * NMAX, make_smem_desc(ka + ks * 256, 128, 8 * D, kSwzNone),
+                   make_smem_desc(q_addr + ks * 256, 128, 8 * D, kSwzNone), make_idesc(0, 0, 128, NMAX), ks > 0);
+          mma_commit(&s_full[sb]);
+          if (i > 0) ok = issue_pv(gi - 1);
+        }
+        if (ok) ok = issue_pv(g + n - 1);
+        if (ok) mma_commit(q_empty);
+      }
+    } else {
+      // -------------------------------------------------------------- softmax (thread = key position) and
+      //                                                                accumulate (thread = output dimension)
+      const int qd = warp & 3;
+      const int t = qd * 32 + lane;
+      const uint32_t lane_bits = (uint32_t)(qd * 32) << 16;
+      float m_run[NMAX], l_part[NMAX], acc[NMAX];
+#pragma unroll
+      for (int i = 0; i < NMAX; ++i) { m_run[i] = -INFINITY; l_part[i] = 0.f; acc[i] = 0.f; }
+      bool ok = true;
+      if (n > 0) {
+        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag, p.status)) break;
+        if (t < NMAX) {
+          const int R = row0 + t;
+          const bool live = t < nrows;
+          const int tq = R / group, hq = kh * group + R % group;
+          const __nv_bfloat16* qrow = p.q + ((size_t)(r0 + tq) * p.Hq + hq) * D;
+          float amax = 0.f;
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < D; j += 8) {
+              uint4 u = *reinterpret_cast<const uint4*>(qrow + j);
+              const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(bf2f(e[k])));
+            }
+          }
+          const float qscale = fmaxf(amax, 1e-12f) / 448.f;
+          const float qinv = 1.f / qscale;
+          uint8_t* qdst = sQ + (t >> 3) * (8 * D) + (t & 7) * 16;
+#pragma unroll
+          for (int j = 0; j < D; j += 16) {
+            uint4 o = make_uint4(0, 0, 0, 0);
+            if (live) {
+              uint4 u0 = *reinterpret_cast<const uint4*>(qrow + j), u1 = *reinterpret_cast<const uint4*>(qrow + j + 8);
+              const __nv_bfloat16* e0 = reinterpret_cast<const __nv_bfloat16*>(&u0);
+              const __nv_bfloat16* e1 = reinterpret_cast<const __nv_bfloat16*>(&u1);
+              o.x = pack_e4m3x4(bf2f(e0[0]) * qinv, bf2f(e0[1]) * qinv, bf2f(e0[2]) * qinv, bf2f(e0[3]) * qinv);
+              o.y = pack_e4m3x4(bf2f(e0[4]) * qinv, bf2f(e0[5]) * qinv, bf2f(e0[6]) * qinv, bf2f(e0[7]) * qinv);
+              o.z = pack_e4m3x4(bf2f(e1[0]) * qinv, bf2f(e1[1]) * qinv, bf2f(e1[2]) * qinv, bf2f(e1[3]) * qinv);
+              o.w = pack_e4m3x4(bf2f(e1[4]) * qinv, bf2f(e1[5]) * qinv, bf2f(e1[6]) * qinv, bf2f(e1[7]) * qinv);
+            }
+            *reinterpret_cast<uint4*>(qdst + (j >> 4) * 128) = o;
+          }
+          s_c[t] = p.scale_log2 * qscale;
+          s_pos[t] = live ? ctx - qlen + tq : -1;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_full);
+        // the per-row constants are read by all four warps: wait until every warp has published its part
+        if (!mbar_wait(q_full, item_it & 1, abort_flag, p.status)) break;
+      }
+      for (int i = 0; i < n && ok; ++i) {
+        const int gi = g + i, sb = gi & 1;
+        if (!mbar_wait(&s_full[sb], (gi >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t v[NMAX];
+        tmem_ldn<NMAX>(tmem + sb * NMAX + lane_bits, v);
+        tmem_ld_wait();
+        const int key = (t0 + i) * 128 + t;
+        float x[NMAX];
+#pragma unroll
+        for (int r = 0; r < NMAX; ++r) {
+          if (r < nrows) {
+            x[r] = key <= s_pos[r] ? __uint_as_float(v[r]) * s_c[r] : -INFINITY;
+            const float wm = warp_max(x[r]);
+            if (lane == 0) s_wmax[sb][qd][r] = wm;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&wm_bar[sb]);
+        // fold the previous tile's output while the other warps catch up
+        if (i > 0) {
+          const int gj = gi - 1, ob = gj & 1;
+          if (!mbar_wait(&o_full[ob], (gj >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          uint32_t o[NMAX];
+          tmem_ldn<NMAX>(tmem + 2 * NMAX + ob * NMAX + lane_bits, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int r = 0; r < NMAX; ++r)
+            if (r < nrows) acc[r] += __uint_as_float(o[r]);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_empty[ob]);
+        }
+        if (!mbar_wait(&wm_bar[sb], (gi >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        uint8_t* pdst = sP + sb * Cfg::P_BYTES + (t >> 4) * 128 + (t & 15);
+#pragma unroll
+        for (int r = 0; r < NMAX; ++r) {
+          if (r < nrows) {
+            const float mt = fmaxf(fmaxf(s_wmax[sb][0][r], s_wmax[sb][1][r]), fmaxf(s_wmax[sb][2][r], s_wmax[sb][3][r]));
+            const float m_new = fmaxf(m_run[r], mt);
+            const float alpha = (m_run[r] == -INFINITY) ? 0.f : ex2(m_run[r] - m_new);
+            const float pr = (x[r] == -INFINITY) ? 0.f : ex2(x[r] - m_new + 8.f);     // P scaled by 2^8 for e4m3
+            l_part[r] = l_part[r] * alpha + pr;
+            acc[r] *= alpha;
+            m_run[r] = m_new;
+            pdst[(r >> 3) * 1024 + (r & 7) * 16] = (uint8_t)__nv_cvt_float_to_fp8(pr, __NV_SATFINITE, __NV_E4M3);
+          }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(&p_full[sb]); }
+      }
+      if (ok && n > 0) {
+        const int gj = g + n - 1, ob = gj & 1;
+        if (!mbar_wait(&o_full[ob], (gj >> 1) & 1, abort_flag, p.status)) ok = false;
+        if (ok) {
+          tc_fence_after();
+          uint32_t o[NMAX];
+          tmem_ldn<NMAX>(tmem + 2 * NMAX + ob * NMAX + lane_bits, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int r = 0; r < NMAX; ++r)
+            if (r < nrows) acc[r] += __uint_as_float(o[r]);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_empty[ob]);
+        }
+      }
+      if (!ok) break;
+      // ---- row sums over all key positions of this item
+      if (n > 0) {
+#pragma unroll
+        for (int r = 0; r < NMAX; ++r) {
+          if (r < nrows) {
+            const float ws = warp_sum(l_part[r]);
+            if (lane == 0) s_l[qd][r] = ws;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(fin_bar);
+        if (!mbar_wait(fin_bar, item_it & 1, abort_flag, p.status)) break;
+      }
+#pragma unroll
+      for (int r = 0; r < NMAX; ++r) {
+        if (r < nrows) {
+          const float l = n > 0 ? s_l[0][r] + s_l[1][r] + s_l[2][r] + s_l[3][r] : 0.f;
+          const int R = row0 + r;
+          const int tq = R / group, hq = kh * group + R % group;
+          if (p.splits == 1) {
+            const float inv = l > 0.f ? p.v_scale / l : 0.f;
+            p.out[((size_t)(r0 + tq) * p.Hq + hq) * D + t] = __float2bfloat16(acc[r] * inv);
+          } else {
+            p.part_o[((size_t)w * NMAX + r) * D + t] = acc[r];
+            if (t == 0) {
+              p.part_ml[((size_t)w * NMAX + r) * 2] = m_run[r];
+              p.part_ml[((size_t)w * NMAX + r) * 2 + 1] = l;
+            }
+          }
+        }
+      }
+    }
+    g += n;
+    if (n > 0) ++item_it;
+    if (*abort_flag) break;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+// Merge kv-split partials of the decode kernel.  One CTA per (sequence, kv head, row block); thread = dimension.
+template <int NMAX>
+__global__ void attn_decode_combine_kernel(AttnParams p) {
+  constexpr int D = 128;
+  const int rb = blockIdx.x % p.row_blocks;
+  const int kh = (blockIdx.x / p.row_blocks) % p.Hkv;
+  const int b = blockIdx.x / (p.row_blocks * p.Hkv);
+  const int group = p.Hq / p.Hkv;
+  const int r0 = p.q_start[b], qlen = p.q_start[b + 1] - r0;
+  const int rows_total = qlen * group;
+  if (rows_total < p.min_rows || rows_total > p.max_rows) return;
+  const int row0 = rb * NMAX;
+  const int nrows = min(NMAX, rows_total - row0);
+  const int t = threadIdx.x;
+  for (int r = 0; r < nrows; ++r) {
+    float m = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) {
+      const size_t w = (size_t)blockIdx.x * p.splits + s;
+      if (p.part_ml[(w * NMAX + r) * 2 + 1] > 0.f) m = fmaxf(m, p.part_ml[(w * NMAX + r) * 2]);
+    }
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const size_t w = (size_t)blockIdx.x * p.splits + s;
+      const float ls = p.part_ml[(w * NMAX + r) * 2 + 1];
+      if (!(ls > 0.f)) continue;
+      const float f = exp2f(p.part_ml[(w * NMAX + r) * 2] - m);
+      l += ls * f;
+      o += p.part_o[(w * NMAX + r) * D + t] * f;
+    }
+    const int R = row0 + r;
+    const int tq = R / group, hq = kh * group + R % group;
+    p.out[((size_t)(r0 + tq) * p.Hq + hq) * D + t] = __float2bfloat16(l > 0.f ? o * p.v_scale / l : 0.f);
+  }
+}
+
+template <int NMAX>
+static cudaError_t launch_decode(const AttnParams& p, int max_ctas, cudaStream_t stream) {
+  using Cfg = DecCfg<NMAX>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int total = p.num_items * p.Hkv * p.row_blocks * p.splits;
+  const int per_sm = NMAX <= 16 ? 2 : 1;
+  int grid = total < per_sm * sm_count() ? total : per_sm * sm_count();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  attn_decode_kernel<NMAX><<<grid, 192, Cfg::SMEM, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || p.splits == 1) return e;
+  attn_decode_combine_kernel<NMAX><<<p.num_items * p.Hkv * p.row_blocks, 128, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace blz
+
+// Decode / verify attention for every sequence with min_rows <= q_len * (Hq / Hkv) <= max_rows.
+// nmax: 16 or 32 rows per work item; row_blocks = ceil(max rows of any processed sequence / nmax).
+// Scratch for splits > 1: part_o = B*Hkv*row_blocks*splits*nmax*128 floats, part_ml = ...*nmax*2 floats.
+BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
+                            const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride,
+                            float scale, float k_scale, float v_scale, int nmax, int row_blocks, int min_rows,
+                            int max_rows, int splits, float* part_o, float* part_ml, int max_ctas, cudaStream_t stream) {
+  using namespace blz;
+  if (num_seqs <= 0) return 0;
+  if (D != 128 || Hq % Hkv || (nmax != 16 && nmax != 32) || row_blocks < 1 || splits < 1 ||
+      (splits > 1 && (!part_o || !part_ml)))
+    return (int)cudaErrorInvalidValue;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
+  p.block_table = block_table; p.slots = slots; p.q_start = q_start; p.ctx_len = ctx_len;
+  p.item_seq = nullptr; p.item_q0 = nullptr; p.part_o = part_o; p.part_ml = part_ml;
+  p.num_items = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.bt_stride = bt_stride; p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f * k_scale; p.v_scale = v_scale;
+  p.tokens_per_block = 0; p.min_rows = min_rows; p.max_rows = max_rows; p.row_blocks = row_blocks;
+  p.status = status_word();
+  return (int)(nmax == 16 ? launch_decode<16>(p, max_ctas, stream) : launch_decode<32>(p, max_ctas, stream));
+}

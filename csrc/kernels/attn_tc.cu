@@ -18,28 +18,9 @@
 // (mma.sync, register dequant), mha_verify.cu :50, mha_prefill.cu prefill_kernel :118 (FA2 style, D=256 only).
 #include "blaze/host.h"
 #include "blaze/sm100.cuh"
+#include "blaze/attn.cuh"
 
 namespace blz {
-
-struct AttnParams {
-  const __nv_bfloat16* q;      // [T, Hq, D]
-  __nv_bfloat16* out;          // [T, Hq, D]
-  const uint8_t* pool;         // [pages, Hkv, 2, 16*D]
-  const int* block_table;      // [max_seqs, bt_stride]
-  const int* slots;            // [B]
-  const int* q_start;          // [B+1]
-  const int* ctx_len;          // [B]
-  const int* item_seq;         // [items] or null (then item = seq * Hkv... decode mapping)
-  const int* item_q0;          // [items] first token (relative to the sequence's rows) of the row block
-  float* part_o;               // [items*splits, 128, D] partial outputs (splits > 1)
-  float* part_ml;              // [items*splits, 128, 2] partial (max, sum)
-  int num_items;               // row-block items (without heads / splits)
-  int Hq, Hkv, bt_stride, splits;
-  float scale_log2;            // softmax scale * log2(e) * k_scale
-  float v_scale;
-  int tokens_per_block;        // 128 / group (rows per item = tokens_per_block * group)
-  int* status;
-};
 
 template <int D>
 struct AttnCfg {
@@ -51,12 +32,6 @@ struct AttnCfg {
   static constexpr int P_BYTES = 128 * 128;
   static constexpr int SMEM = Q_BYTES + STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 1024 + 512;
 };
-
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
 
 template <int D>
 __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
@@ -261,17 +236,23 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
         const int lim = min(pos_q, kv_end - 1) - k0;        // columns <= lim are visible to this row
         const uint32_t s_addr = tmem + sb * 128 + ((uint32_t)(qd * 32) << 16);
         float m_tile = -INFINITY;
+        const bool full = lim >= 127;                       // no masking needed for this row in this tile
 #pragma unroll 1
         for (int cch = 0; cch < 4; ++cch) {
           uint32_t v[32];
           tmem_ld32(s_addr + cch * 32, v);
           tmem_ld_wait();
+          if (full) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (cch * 32 + j <= lim) m_tile = fmaxf(m_tile, __uint_as_float(v[j]));
+            for (int j = 0; j < 32; ++j) m_tile = fmaxf(m_tile, __uint_as_float(v[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cch * 32 + j <= lim) m_tile = fmaxf(m_tile, __uint_as_float(v[j]));
+          }
         }
         const float m_new = fmaxf(m_run, m_tile * c);
-        const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+        const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
         const float off = (m_new == -INFINITY) ? 0.f : m_new - 8.f;     // P is scaled by 2^8 to use the e4m3 range
         float rs = 0.f;
         uint8_t* pdst = sP + sb * Cfg::P_BYTES + (r >> 3) * 1024 + (r & 7) * 16;
@@ -281,11 +262,16 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
           tmem_ld32(s_addr + cch * 32, v);
           tmem_ld_wait();
           float e[32];
+          if (full) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float x = (cch * 32 + j <= lim) ? exp2f(__uint_as_float(v[j]) * c - off) : 0.f;
-            e[j] = x;
-            rs += x;
+            for (int j = 0; j < 32; ++j) { e[j] = ex2(fmaf(__uint_as_float(v[j]), c, -off)); rs += e[j]; }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float x = (cch * 32 + j <= lim) ? ex2(fmaf(__uint_as_float(v[j]), c, -off)) : 0.f;
+              e[j] = x;
+              rs += x;
+            }
           }
 #pragma unroll
           for (int h = 0; h < 2; ++h) {

@@ -183,7 +183,7 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8):
                 chunks.append(SeqChunk(b, [0] * qlens[b], pre))
         if not chunks:
             continue
-        batch = build_batch(chunks, kv.block_table_host, DEV, attn_tokens_per_block=tpb)
+        batch = build_batch(chunks, kv.block_table_host, DEV, attn_group=Hq // Hkv)
         T = batch.num_rows
         qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g, device=DEV).bfloat16()
         q, _ = ops.attn_prep_store(qkv, attn, model, batch, kv, 0, None)
