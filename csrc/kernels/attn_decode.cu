@@ -27,8 +27,9 @@ struct DecCfg {
   static constexpr int STAGES = 3;
   static constexpr int Q_BYTES = NMAX * D;
   static constexpr int P_BYTES = NMAX * 128;
-  static constexpr int TMEM_COLS = NMAX <= 16 ? 64 : 128;
-  static constexpr int SMEM = Q_BYTES + STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 1024 + 512;
+  static constexpr int NB = 3;                       // S^T / P / O^T buffers (softmax runs up to two tiles ahead of the fold)
+  static constexpr int TMEM_COLS = NMAX <= 16 ? 128 : 256;
+  static constexpr int SMEM = Q_BYTES + STAGES * 2 * TILE_BYTES + NB * P_BYTES + 1024 + 512;
 };
 
 template <int N>
@@ -39,37 +40,37 @@ __device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[N]) {
 template <int NMAX>
 __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(AttnParams p) {
   using Cfg = DecCfg<NMAX>;
-  constexpr int ST = Cfg::STAGES, D = Cfg::D;
+  constexpr int ST = Cfg::STAGES, D = Cfg::D, NB = Cfg::NB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + ST * Cfg::TILE_BYTES;
   uint8_t* sQ = sV + ST * Cfg::TILE_BYTES;
   uint8_t* sP = sQ + Cfg::Q_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + NB * Cfg::P_BYTES);
   uint64_t* k_full = bars;                 // [ST]
   uint64_t* v_full = k_full + ST;          // [ST]
   uint64_t* kv_empty = v_full + ST;        // [ST]
-  uint64_t* s_full = kv_empty + ST;        // [2]
-  uint64_t* s_empty = s_full + 2;          // [2]
-  uint64_t* p_full = s_empty + 2;          // [2]
-  uint64_t* o_full = p_full + 2;           // [2]
-  uint64_t* o_empty = o_full + 2;          // [2]
-  uint64_t* wm_bar = o_empty + 2;          // [2] row-max exchange among the softmax warps
-  uint64_t* q_full = wm_bar + 2;           // [1]
+  uint64_t* s_full = kv_empty + ST;        // [NB]
+  uint64_t* s_empty = s_full + NB;         // [NB]
+  uint64_t* p_full = s_empty + NB;         // [NB]
+  uint64_t* o_full = p_full + NB;          // [NB]
+  uint64_t* o_empty = o_full + NB;         // [NB]
+  uint64_t* wm_bar = o_empty + NB;         // [NB] row-max exchange among the softmax warps
+  uint64_t* q_full = wm_bar + NB;          // [1]
   uint64_t* q_empty = q_full + 1;          // [1]
   uint64_t* fin_bar = q_empty + 1;         // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fin_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ float s_c[NMAX];
   __shared__ int s_pos[NMAX];
-  __shared__ float s_wmax[2][4][NMAX];
+  __shared__ float s_wmax[Cfg::NB][4][NMAX];
   __shared__ float s_l[4][NMAX];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int i = 0; i < ST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NB; ++i) {
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&p_full[i], 4);
       mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4); mbar_init(&wm_bar[i], 4);
     }
@@ -135,15 +136,15 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
         tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ);
         auto issue_pv = [&](int gj) -> bool {
-          const int s = gj % ST, pb = gj & 1;
+          const int s = gj % ST, pb = gj % NB;
           if (!mbar_wait(&v_full[s], (gj / ST) & 1, abort_flag, p.status)) return false;
-          if (!mbar_wait(&p_full[pb], (gj >> 1) & 1, abort_flag, p.status)) return false;
-          if (!mbar_wait(&o_empty[pb], ((gj >> 1) & 1) ^ 1, abort_flag, p.status)) return false;
+          if (!mbar_wait(&p_full[pb], (gj / NB) & 1, abort_flag, p.status)) return false;
+          if (!mbar_wait(&o_empty[pb], ((gj / NB) & 1) ^ 1, abort_flag, p.status)) return false;
           tc_fence_after();
           const uint32_t pa = smem_u32(sP + pb * Cfg::P_BYTES), va = smem_u32(sV + s * Cfg::TILE_BYTES);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            mma_f8(tmem + 2 * NMAX + pb * NMAX,
+            mma_f8(tmem + NB * NMAX + pb * NMAX,
                    make_smem_desc(va + ks * 2 * Cfg::PAGE_BYTES, Cfg::PAGE_BYTES, 128, kSwzNone),
                    make_smem_desc(pa + ks * 256, 128, 1024, kSwzNone), make_idesc(0, 0, 128, NMAX), ks > 0);
           mma_commit(&o_full[pb]);
@@ -151,9 +152,9 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
           return true;
         };
         for (int i = 0; i < n && ok; ++i) {
-          const int gi = g + i, s = gi % ST, sb = gi & 1;
+          const int gi = g + i, s = gi % ST, sb = gi % NB;
           if (!mbar_wait(&k_full[s], (gi / ST) & 1, abort_flag, p.status)) { ok = false; break; }
-          if (!mbar_wait(&s_empty[sb], ((gi >> 1) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(&s_empty[sb], ((gi / NB) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t ka = smem_u32(sK + s * Cfg::TILE_BYTES);
 #pragma unroll
@@ -219,9 +220,28 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
         // the per-row constants are read by all four warps: wait until every warp has published its part
         if (!mbar_wait(q_full, item_it & 1, abort_flag, p.status)) break;
       }
+      float a1[NMAX];                                      // alpha of the previous tile (m_{i-2} -> m_{i-1})
+#pragma unroll
+      for (int r = 0; r < NMAX; ++r) a1[r] = 1.f;
+      // fold tile gj's O^T (held relative to the row maxima of tile gj) into the running sums
+      auto fold = [&](int gj, bool scaled) -> bool {
+        const int ob = gj % NB;
+        if (!mbar_wait(&o_full[ob], (gj / NB) & 1, abort_flag, p.status)) return false;
+        tc_fence_after();
+        uint32_t o[NMAX];
+        tmem_ldn<NMAX>(tmem + NB * NMAX + ob * NMAX + lane_bits, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int r = 0; r < NMAX; ++r)
+          if (r < nrows) acc[r] = scaled ? fmaf(__uint_as_float(o[r]), a1[r], acc[r]) : acc[r] + __uint_as_float(o[r]);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_empty[ob]);
+        return true;
+      };
       for (int i = 0; i < n && ok; ++i) {
-        const int gi = g + i, sb = gi & 1;
-        if (!mbar_wait(&s_full[sb], (gi >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        const int gi = g + i, sb = gi % NB;
+        if (!mbar_wait(&s_full[sb], (gi / NB) & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         uint32_t v[NMAX];
         tmem_ldn<NMAX>(tmem + sb * NMAX + lane_bits, v);
@@ -238,22 +258,9 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&wm_bar[sb]);
-        // fold the previous tile's output while the other warps catch up
-        if (i > 0) {
-          const int gj = gi - 1, ob = gj & 1;
-          if (!mbar_wait(&o_full[ob], (gj >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
-          tc_fence_after();
-          uint32_t o[NMAX];
-          tmem_ldn<NMAX>(tmem + 2 * NMAX + ob * NMAX + lane_bits, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int r = 0; r < NMAX; ++r)
-            if (r < nrows) acc[r] += __uint_as_float(o[r]);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&o_empty[ob]);
-        }
-        if (!mbar_wait(&wm_bar[sb], (gi >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        // fold the output of two tiles ago while the other warps catch up
+        if (i >= 2 && !fold(gi - 2, true)) { ok = false; break; }
+        if (!mbar_wait(&wm_bar[sb], (gi / NB) & 1, abort_flag, p.status)) { ok = false; break; }
         uint8_t* pdst = sP + sb * Cfg::P_BYTES + (t >> 4) * 128 + (t & 15);
 #pragma unroll
         for (int r = 0; r < NMAX; ++r) {
@@ -264,6 +271,7 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
             const float pr = (x[r] == -INFINITY) ? 0.f : ex2(x[r] - m_new + 8.f);     // P scaled by 2^8 for e4m3
             l_part[r] = l_part[r] * alpha + pr;
             acc[r] *= alpha;
+            a1[r] = alpha;
             m_run[r] = m_new;
             pdst[(r >> 3) * 1024 + (r & 7) * 16] = (uint8_t)__nv_cvt_float_to_fp8(pr, __NV_SATFINITE, __NV_E4M3);
           }
@@ -273,22 +281,8 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
         __syncwarp();
         if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(&p_full[sb]); }
       }
-      if (ok && n > 0) {
-        const int gj = g + n - 1, ob = gj & 1;
-        if (!mbar_wait(&o_full[ob], (gj >> 1) & 1, abort_flag, p.status)) ok = false;
-        if (ok) {
-          tc_fence_after();
-          uint32_t o[NMAX];
-          tmem_ldn<NMAX>(tmem + 2 * NMAX + ob * NMAX + lane_bits, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int r = 0; r < NMAX; ++r)
-            if (r < nrows) acc[r] += __uint_as_float(o[r]);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&o_empty[ob]);
-        }
-      }
+      if (ok && n >= 2) ok = fold(g + n - 2, true);
+      if (ok && n >= 1) ok = fold(g + n - 1, false);
       if (!ok) break;
       // ---- row sums over all key positions of this item
       if (n > 0) {

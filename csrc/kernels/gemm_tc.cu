@@ -54,7 +54,7 @@ struct GemmCfg {
   static constexpr int ACC_BUFS = (BN == 256 && SF_ATOMS) ? 1 : 2;
   static constexpr int SF_COLS_PER_STAGE = SF_ATOMS * 4 * (1 + BN / 128);
   static constexpr int SF_COL0 = ACC_BUFS * BN;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;   // + 8*BN*4 static
   static_assert(SF_COL0 + STAGES * SF_COLS_PER_STAGE <= 512, "TMEM budget");
 };
 
@@ -76,6 +76,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* acc_empty = acc_full + ACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ __align__(16) float s_alpha[4][BN];
+  __shared__ __align__(16) float s_bias[4][BN];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
@@ -193,6 +195,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
       const float rs = (p.row_scale && row < p.M) ? p.row_scale[row] : 1.0f;
+      // per-column multipliers and bias of this tile, staged once per warp
+      float* sal = s_alpha[warp - 2];
+      float* sbi = s_bias[warp - 2];
+      __syncwarp();
+#pragma unroll
+      for (int i = lane; i < BN; i += 32) {
+        const int col = nt * BN + i;
+        sal[i] = (p.alpha && col < p.N) ? __ldg(p.alpha + col) : 1.0f;
+        sbi[i] = (p.bias && col < p.N) ? bf2f(p.bias[col]) : 0.0f;
+      }
+      __syncwarp();
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -200,36 +213,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
         const int col0 = nt * BN + c * 32;
         if (row < p.M && col0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(r[i]) * rs;
-            const int col = col0 + i;
-            if (col < p.N) {
-              if (p.alpha) x *= __ldg(p.alpha + col);
-              if (p.bias) x += bf2f(p.bias[col]);
-            }
-            v[i] = x;
-          }
+          const bool whole = col0 + 32 <= p.N;
           if constexpr (OUT_F32) {
             float* dst = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
-            if (col0 + 32 <= p.N) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = v[i];
+            for (int i = 0; i < 32; i += 4) {
+              const float4 al = *reinterpret_cast<const float4*>(sal + c * 32 + i);
+              const float4 bi = *reinterpret_cast<const float4*>(sbi + c * 32 + i);
+              float4 o;
+              o.x = fmaf(__uint_as_float(r[i]) * rs, al.x, bi.x);
+              o.y = fmaf(__uint_as_float(r[i + 1]) * rs, al.y, bi.y);
+              o.z = fmaf(__uint_as_float(r[i + 2]) * rs, al.z, bi.z);
+              o.w = fmaf(__uint_as_float(r[i + 3]) * rs, al.w, bi.w);
+              if (whole) {
+                *reinterpret_cast<float4*>(dst + i) = o;
+              } else {
+                if (col0 + i < p.N) dst[i] = o.x;
+                if (col0 + i + 1 < p.N) dst[i + 1] = o.y;
+                if (col0 + i + 2 < p.N) dst[i + 2] = o.z;
+                if (col0 + i + 3 < p.N) dst[i + 3] = o.w;
+              }
             }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
-            if (col0 + 32 <= p.N) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 u = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
-                                     pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
-                *reinterpret_cast<uint4*>(dst + i) = u;
+            for (int i = 0; i < 32; i += 8) {
+              const float4 a0 = *reinterpret_cast<const float4*>(sal + c * 32 + i);
+              const float4 a1 = *reinterpret_cast<const float4*>(sal + c * 32 + i + 4);
+              const float4 b0 = *reinterpret_cast<const float4*>(sbi + c * 32 + i);
+              const float4 b1 = *reinterpret_cast<const float4*>(sbi + c * 32 + i + 4);
+              const float o0 = fmaf(__uint_as_float(r[i]) * rs, a0.x, b0.x), o1 = fmaf(__uint_as_float(r[i + 1]) * rs, a0.y, b0.y);
+              const float o2 = fmaf(__uint_as_float(r[i + 2]) * rs, a0.z, b0.z), o3 = fmaf(__uint_as_float(r[i + 3]) * rs, a0.w, b0.w);
+              const float o4 = fmaf(__uint_as_float(r[i + 4]) * rs, a1.x, b1.x), o5 = fmaf(__uint_as_float(r[i + 5]) * rs, a1.y, b1.y);
+              const float o6 = fmaf(__uint_as_float(r[i + 6]) * rs, a1.z, b1.z), o7 = fmaf(__uint_as_float(r[i + 7]) * rs, a1.w, b1.w);
+              if (whole) {
+                *reinterpret_cast<uint4*>(dst + i) =
+                    make_uint4(pack_bf16x2(o0, o1), pack_bf16x2(o2, o3), pack_bf16x2(o4, o5), pack_bf16x2(o6, o7));
+              } else {
+                if (col0 + i < p.N) dst[i] = __float2bfloat16(o0);
+                if (col0 + i + 1 < p.N) dst[i + 1] = __float2bfloat16(o1);
+                if (col0 + i + 2 < p.N) dst[i + 2] = __float2bfloat16(o2);
+                if (col0 + i + 3 < p.N) dst[i + 3] = __float2bfloat16(o3);
+                if (col0 + i + 4 < p.N) dst[i + 4] = __float2bfloat16(o4);
+                if (col0 + i + 5 < p.N) dst[i + 5] = __float2bfloat16(o5);
+                if (col0 + i + 6 < p.N) dst[i + 6] = __float2bfloat16(o6);
+                if (col0 + i + 7 < p.N) dst[i + 7] = __float2bfloat16(o7);
               }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = __float2bfloat16(v[i]);
             }
           }
         }
