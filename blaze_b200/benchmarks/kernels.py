@@ -72,6 +72,18 @@ def bench_attention(a):
         pass
     fn = lambda: ops.attention(q, M, batch, kv, 0, D ** -0.5, splits=a.splits)  # noqa: E731
     med, best = timeit(fn, a.iters)
+    if a.prof:
+        ops.attn_prof = torch.zeros(8 * 3 * 16, dtype=torch.int64, device="cuda")
+        fn()
+        torch.cuda.synchronize()
+        names = ["kv_empty", "k_full", "s_empty", "v_full", "p_full", "o_empty", "q_full", "s_full", "wm_bar", "o_full",
+                 "q_empty", "fin", "total"]
+        pr = ops.attn_prof.view(8, 3, 16).cpu()
+        for blk in range(2):
+            for w, role in enumerate(["loader", "mma", "softmax"]):
+                print(f"[prof] block {blk} {role}: " + " ".join(f"{n}={int(pr[blk, w, i])}" for i, n in enumerate(names) if int(pr[blk, w, i])),
+                      file=sys.stderr)
+        ops.attn_prof = None
     causal = 1.0 if a.qlen == 1 else (a.ctx - a.qlen / 2) / a.ctx
     kv_bytes = B * a.ctx * a.hkv * 2 * D * (1.0 if a.qlen <= tpb else 1.0)
     flops = 4.0 * B * a.qlen * a.hq * a.ctx * causal * D
@@ -131,6 +143,7 @@ def main(argv=None):
     p.add_argument("--hq", type=int, default=32)
     p.add_argument("--hkv", type=int, default=8)
     p.add_argument("--splits", type=int, default=0)
+    p.add_argument("--prof", action="store_true", help="print per-role wait cycles of the decode kernel")
     p.add_argument("--iters", type=int, default=10)
     p = sub.add_parser("gemm")
     p.add_argument("--kind", default="nvfp4")

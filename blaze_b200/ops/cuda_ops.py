@@ -37,6 +37,7 @@ class CudaOps:
         self.device = torch.device(device)
         self.lib = kernels()
         self.launches = 0
+        self.attn_prof = None      # optional int64 [8*3*16] wait-cycle counters of the decode attention kernel
         self._scratch: Dict[str, torch.Tensor] = {}
         self._sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         lib = self.lib
@@ -52,7 +53,7 @@ class CudaOps:
                                     _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
         lib.blz_attn_decode.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                         _c.c_float, _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
-                                        VP, VP, _c.c_int, VP]
+                                        VP, VP, _c.c_int, VP, VP]
         lib.blz_mul_sigmoid.argtypes = [VP, VP, _c.c_longlong, VP]
         lib.blz_add.argtypes = [VP, VP, VP, _c.c_longlong, VP]
         lib.blz_add_sigmoid_scaled.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
@@ -263,10 +264,10 @@ class CudaOps:
         tiles = max((batch.max_ctx + 127) // 128, 1)
         small = batch.small_rows_max if (batch.small_rows_max or batch.num_large) else group * batch.max_q_len
         if small > 0:
-            nmax = 16 if small <= 16 else 32
+            nmax = 16
             rb = (small + nmax - 1) // nmax
             work = B * Hkv * rb
-            sp = splits if splits > 0 else (1 if work >= 2 * self._sm else max(1, min(8, tiles, (2 * self._sm) // max(work, 1))))
+            sp = splits if splits > 0 else (1 if work >= 3 * self._sm else max(1, min(8, tiles, (3 * self._sm) // max(work, 1))))
             po = pm = None
             if sp > 1:
                 n = work * sp * nmax
@@ -275,7 +276,7 @@ class CudaOps:
             self._check(self.lib.blz_attn_decode(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
                                                  _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), B, Hq, Hkv, D,
                                                  kv.block_table.stride(0), scale, 1.0, 1.0, nmax, rb, 1, small, sp,
-                                                 _ptr(po), _ptr(pm), max_ctas, self._stream()), "attn_decode")
+                                                 _ptr(po), _ptr(pm), max_ctas, _ptr(self.attn_prof), self._stream()), "attn_decode")
             if sp > 1:
                 self.launches += 1
         if batch.item_seq is not None:

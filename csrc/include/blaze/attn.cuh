@@ -23,6 +23,7 @@ struct AttnParams {
   int tokens_per_block;        // 128 / group (rows per item = tokens_per_block * group)
   int min_rows, max_rows;      // a sequence is processed iff min_rows <= q_len * group <= max_rows
   int row_blocks;              // decode kernel: row blocks of NMAX rows per (sequence, kv head)
+  long long* prof;             // optional [blocks][16] wait-cycle counters (null = off)
   int* status;
 };
 

@@ -64,12 +64,25 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same, but the hardware may keep the thread suspended for up to `ns` nanoseconds while the phase is incomplete
+// (it still wakes as soon as the phase completes), so a waiting warp does not steal issue slots by polling.
+__device__ __forceinline__ bool mbar_try_sleep(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  `abort_flag` is a CTA-shared int that every role polls; once set, all waits return false.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
   if (mbar_try(bar, parity)) return true;
   long long t0 = clock64();
   while (true) {
-    if (mbar_try(bar, parity)) return true;
+    if (mbar_try_sleep(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kSpinLimit) {
       *abort_flag = 1;

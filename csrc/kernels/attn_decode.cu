@@ -9,8 +9,9 @@
 // every accumulate thread owns one output dimension with NMAX running sums in registers.  Row maxima are
 // exchanged across the four softmax warps once per tile; row sums are reduced once per work item.
 //
-// Work item = (sequence, kv head, block of NMAX rows, kv split); persistent CTAs; 192 threads (page loader warp,
-// MMA warp, four softmax warps); 2 CTAs per SM for NMAX = 16.  Every wait is a bounded mbarrier wait.
+// Work item = (sequence, kv head, block of NMAX rows, kv split); persistent CTAs; 320 threads (page loader warp,
+// MMA warp, two sets of four softmax warps that take alternate tiles and are merged per work item like kv splits);
+// 2 CTAs per SM when at most 8 rows are live.  Every wait is a bounded mbarrier wait.
 //
 // Reference counterparts: kernels/src/cuda/mha_nvfp4.cu mha_decode_kernel :259 and mha_combine_kernel :572,
 // kernels/src/cuda/mha_verify.cu verify_kernel :50.
@@ -19,62 +20,79 @@
 
 namespace blz {
 
-template <int NMAX>
+// NMAX = MMA N (rows per work item, 16 or 32); RMAX = rows kept in registers by the softmax threads (>= live rows).
+template <int NMAX, int RMAX>
 struct DecCfg {
   static constexpr int D = 128;
   static constexpr int PAGE_BYTES = 16 * D;
   static constexpr int TILE_BYTES = 8 * PAGE_BYTES;
-  static constexpr int STAGES = 3;
+  static constexpr int THREADS = 320;                // loader warp, MMA warp, two sets of four softmax warps
+  static constexpr int CTAS_PER_SM = RMAX <= 8 ? 2 : 1;
+  static constexpr int STAGES = CTAS_PER_SM == 2 ? 3 : 5;   // depth of the K ring and of the V ring (released separately)
   static constexpr int Q_BYTES = NMAX * D;
   static constexpr int P_BYTES = NMAX * 128;
   static constexpr int NB = 3;                       // S^T / P / O^T buffers (softmax runs up to two tiles ahead of the fold)
   static constexpr int TMEM_COLS = NMAX <= 16 ? 128 : 256;
-  static constexpr int SMEM = Q_BYTES + STAGES * 2 * TILE_BYTES + NB * P_BYTES + 1024 + 512;
+  static constexpr int SMEM = 2 * Q_BYTES + STAGES * 2 * TILE_BYTES + NB * P_BYTES + 128 + 640;
 };
+
+__device__ __forceinline__ bool timed_wait(long long& acc, bool on, uint64_t* bar, uint32_t par, volatile int* abort_flag,
+                                           int* status) {
+  if (!on) return mbar_wait(bar, par, abort_flag, status);
+  const long long t = clock64();
+  const bool r = mbar_wait(bar, par, abort_flag, status);
+  acc += clock64() - t;
+  return r;
+}
 
 template <int N>
 __device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[N]) {
   if constexpr (N == 16) tmem_ld16(taddr, r); else tmem_ld32(taddr, r);
 }
 
-template <int NMAX>
-__global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(AttnParams p) {
-  using Cfg = DecCfg<NMAX>;
+template <int NMAX, int RMAX>
+__global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_decode_kernel(AttnParams p) {
+  using Cfg = DecCfg<NMAX, RMAX>;
   constexpr int ST = Cfg::STAGES, D = Cfg::D, NB = Cfg::NB;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint8_t* sK = smem;
   uint8_t* sV = sK + ST * Cfg::TILE_BYTES;
   uint8_t* sQ = sV + ST * Cfg::TILE_BYTES;
-  uint8_t* sP = sQ + Cfg::Q_BYTES;
+  uint8_t* sP = sQ + 2 * Cfg::Q_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + NB * Cfg::P_BYTES);
   uint64_t* k_full = bars;                 // [ST]
   uint64_t* v_full = k_full + ST;          // [ST]
-  uint64_t* kv_empty = v_full + ST;        // [ST]
-  uint64_t* s_full = kv_empty + ST;        // [NB]
+  uint64_t* k_empty = v_full + ST;         // [ST] released when S^T = K Q^T of the tile has completed
+  uint64_t* v_empty = k_empty + ST;        // [ST] released when O^T = V^T P^T of the tile has completed
+  uint64_t* s_full = v_empty + ST;         // [NB]
   uint64_t* s_empty = s_full + NB;         // [NB]
   uint64_t* p_full = s_empty + NB;         // [NB]
   uint64_t* o_full = p_full + NB;          // [NB]
   uint64_t* o_empty = o_full + NB;         // [NB]
   uint64_t* wm_bar = o_empty + NB;         // [NB] row-max exchange among the softmax warps
-  uint64_t* q_full = wm_bar + NB;          // [1]
-  uint64_t* q_empty = q_full + 1;          // [1]
-  uint64_t* fin_bar = q_empty + 1;         // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fin_bar + 1);
+  uint64_t* q_full = wm_bar + NB;          // [2]
+  uint64_t* q_empty = q_full + 2;          // [2]
+  uint64_t* fin_bar = q_empty + 2;         // [1] both sets have published their partial results
+  uint64_t* acc_free = fin_bar + 1;        // [1] set 0 has consumed set 1's partial results
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __shared__ float s_c[NMAX];
-  __shared__ int s_pos[NMAX];
+  __shared__ float s_c[2][NMAX];
+  __shared__ int s_pos[2][NMAX];
   __shared__ float s_wmax[Cfg::NB][4][NMAX];
-  __shared__ float s_l[4][NMAX];
+  __shared__ float s_l[2][4][RMAX];                  // [set][warp][row] partial row sums
+  __shared__ float s_m[RMAX];                        // set 1's row maxima
+  __shared__ float s_acc[RMAX][128];                 // set 1's output sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < ST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < ST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1); }
     for (int i = 0; i < NB; ++i) {
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&p_full[i], 4);
       mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4); mbar_init(&wm_bar[i], 4);
     }
-    mbar_init(q_full, 4); mbar_init(q_empty, 1); mbar_init(fin_bar, 4);
+    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    mbar_init(fin_bar, 8); mbar_init(acc_free, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -87,6 +105,11 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
   const int group = p.Hq / p.Hkv;
   const int total = p.num_items * p.Hkv * p.row_blocks * p.splits;
   int g = 0, item_it = 0;
+  long long pc[13];
+#pragma unroll
+  for (int i = 0; i < 13; ++i) pc[i] = 0;
+  const long long t_start = clock64();
+#define TW(cat, bar, par) timed_wait(pc[cat], p.prof != nullptr, bar, par, abort_flag, p.status)
 
   for (int w = blockIdx.x; w < total; w += gridDim.x) {
     const int split = w % p.splits;
@@ -111,35 +134,97 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
       // -------------------------------------------------------------- page loader
       const int* bt = p.block_table + (size_t)slot * p.bt_stride;
       const int npages = (kv_end + 15) >> 4;
+      if (n > 0) {
+        // ---- this item's Q rows → e4m3 in the K-major core-matrix layout, plus the per-row constants
+        constexpr int LPR = 32 / NMAX == 0 ? 1 : 32 / NMAX;        // lanes per row (2 for NMAX 16, 1 for NMAX 32)
+        constexpr int DPL = D / LPR;                               // dims per lane
+        const int qb = item_it & 1;
+        const int rr = lane / LPR, part = lane % LPR;
+        const int R = row0 + rr;
+        const bool live = rr < nrows;
+        const int tq = R / group, hq = kh * group + R % group;
+        uint4 raw[DPL / 8];
+        float amax = 0.f;
+        if (live) {
+          const __nv_bfloat16* qrow = p.q + ((size_t)(r0 + tq) * p.Hq + hq) * D + part * DPL;
+#pragma unroll
+          for (int j = 0; j < DPL / 8; ++j) raw[j] = *reinterpret_cast<const uint4*>(qrow + j * 8);
+#pragma unroll
+          for (int j = 0; j < DPL / 8; ++j) {
+            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw[j]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(bf2f(e[k])));
+          }
+        }
+        if (LPR == 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        const float qscale = fmaxf(amax, 1e-12f) / 448.f;
+        const float qinv = 1.f / qscale;
+        if (!TW(10, &q_empty[qb], ((item_it >> 1) & 1) ^ 1)) break;
+        uint8_t* qdst = sQ + qb * Cfg::Q_BYTES + (rr >> 3) * (8 * D) + (rr & 7) * 16 + (part * DPL / 16) * 128;
+#pragma unroll
+        for (int j = 0; j < DPL / 16; ++j) {
+          uint4 o = make_uint4(0, 0, 0, 0);
+          if (live) {
+            const __nv_bfloat16* e0 = reinterpret_cast<const __nv_bfloat16*>(&raw[2 * j]);
+            const __nv_bfloat16* e1 = reinterpret_cast<const __nv_bfloat16*>(&raw[2 * j + 1]);
+            o.x = pack_e4m3x4(bf2f(e0[0]) * qinv, bf2f(e0[1]) * qinv, bf2f(e0[2]) * qinv, bf2f(e0[3]) * qinv);
+            o.y = pack_e4m3x4(bf2f(e0[4]) * qinv, bf2f(e0[5]) * qinv, bf2f(e0[6]) * qinv, bf2f(e0[7]) * qinv);
+            o.z = pack_e4m3x4(bf2f(e1[0]) * qinv, bf2f(e1[1]) * qinv, bf2f(e1[2]) * qinv, bf2f(e1[3]) * qinv);
+            o.w = pack_e4m3x4(bf2f(e1[4]) * qinv, bf2f(e1[5]) * qinv, bf2f(e1[6]) * qinv, bf2f(e1[7]) * qinv);
+          }
+          *reinterpret_cast<uint4*>(qdst + j * 128) = o;
+        }
+        if (part == 0) {
+          s_c[qb][rr] = p.scale_log2 * qscale;
+          s_pos[qb][rr] = live ? ctx - qlen + tq : -1;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&q_full[qb]);
+      }
       for (int i = 0; i < n; ++i) {
         const int gi = g + i, s = gi % ST;
-        if (!mbar_wait(&kv_empty[s], ((gi / ST) & 1) ^ 1, abort_flag, p.status)) break;
-        if (lane == 0) {
-          mbar_expect_tx(&k_full[s], Cfg::TILE_BYTES);
-          mbar_expect_tx(&v_full[s], Cfg::TILE_BYTES);
-        }
+        if (!TW(0, &k_empty[s], ((gi / ST) & 1) ^ 1)) break;
+        if (lane == 0) mbar_expect_tx(&k_full[s], Cfg::TILE_BYTES);
         __syncwarp();
-        if (lane < 16) {
-          const int pg = lane & 7;
-          const int pidx = (t0 + i) * 8 + pg;
+        if (lane < 8) {
+          const int pidx = (t0 + i) * 8 + lane;
           const int page = pidx < npages ? bt[pidx] : 0;          // page 0 is the all-zero scratch page
           const uint8_t* src = p.pool + ((size_t)page * p.Hkv + kh) * (size_t)(2 * Cfg::PAGE_BYTES);
-          if (lane < 8) bulk_load(sK + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &k_full[s]);
-          else bulk_load(sV + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src + Cfg::PAGE_BYTES, Cfg::PAGE_BYTES, &v_full[s]);
+          bulk_load(sK + s * Cfg::TILE_BYTES + lane * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &k_full[s]);
         }
         __syncwarp();
       }
     } else if (warp == 1) {
+      // -------------------------------------------------------------- V^T page loader (upper half of the warp)
+      if (lane >= 16) {
+        const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+        const int npages = (kv_end + 15) >> 4;
+        for (int i = 0; i < n; ++i) {
+          const int gi = g + i, s = gi % ST;
+          if (!mbar_wait(&v_empty[s], ((gi / ST) & 1) ^ 1, abort_flag, p.status)) break;
+          if (lane == 16) mbar_expect_tx(&v_full[s], Cfg::TILE_BYTES);
+          __syncwarp(0xFFFF0000u);
+          if (lane < 24) {
+            const int pg = lane - 16;
+            const int pidx = (t0 + i) * 8 + pg;
+            const int page = pidx < npages ? bt[pidx] : 0;
+            const uint8_t* src = p.pool + ((size_t)page * p.Hkv + kh) * (size_t)(2 * Cfg::PAGE_BYTES) + Cfg::PAGE_BYTES;
+            bulk_load(sV + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &v_full[s]);
+          }
+          __syncwarp(0xFFFF0000u);
+        }
+      }
       // -------------------------------------------------------------- MMA issuer
       if (lane == 0 && n > 0) {
-        bool ok = mbar_wait(q_full, item_it & 1, abort_flag, p.status);
+        bool ok = TW(6, &q_full[item_it & 1], (item_it >> 1) & 1);
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ);
+        const uint32_t q_addr = smem_u32(sQ + (item_it & 1) * Cfg::Q_BYTES);
         auto issue_pv = [&](int gj) -> bool {
           const int s = gj % ST, pb = gj % NB;
-          if (!mbar_wait(&v_full[s], (gj / ST) & 1, abort_flag, p.status)) return false;
-          if (!mbar_wait(&p_full[pb], (gj / NB) & 1, abort_flag, p.status)) return false;
-          if (!mbar_wait(&o_empty[pb], ((gj / NB) & 1) ^ 1, abort_flag, p.status)) return false;
+          if (!TW(3, &v_full[s], (gj / ST) & 1)) return false;
+          if (!TW(4, &p_full[pb], (gj / NB) & 1)) return false;
+          if (!TW(5, &o_empty[pb], ((gj / NB) & 1) ^ 1)) return false;
           tc_fence_after();
           const uint32_t pa = smem_u32(sP + pb * Cfg::P_BYTES), va = smem_u32(sV + s * Cfg::TILE_BYTES);
 #pragma unroll
@@ -148,13 +233,13 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
                    make_smem_desc(va + ks * 2 * Cfg::PAGE_BYTES, Cfg::PAGE_BYTES, 128, kSwzNone),
                    make_smem_desc(pa + ks * 256, 128, 1024, kSwzNone), make_idesc(0, 0, 128, NMAX), ks > 0);
           mma_commit(&o_full[pb]);
-          mma_commit(&kv_empty[s]);
+          mma_commit(&v_empty[s]);
           return true;
         };
         for (int i = 0; i < n && ok; ++i) {
           const int gi = g + i, s = gi % ST, sb = gi % NB;
-          if (!mbar_wait(&k_full[s], (gi / ST) & 1, abort_flag, p.status)) { ok = false; break; }
-          if (!mbar_wait(&s_empty[sb], ((gi / NB) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
+          if (!TW(1, &k_full[s], (gi / ST) & 1)) { ok = false; break; }
+          if (!TW(2, &s_empty[sb], ((gi / NB) & 1) ^ 1)) { ok = false; break; }
           tc_fence_after();
           const uint32_t ka = smem_u32(sK + s * Cfg::TILE_BYTES);
 #pragma unroll
@@ -162,156 +247,133 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
             mma_f8(tmem + sb * NMAX, make_smem_desc(ka + ks * 256, 128, 8 * D, kSwzNone),
                    make_smem_desc(q_addr + ks * 256, 128, 8 * D, kSwzNone), make_idesc(0, 0, 128, NMAX), ks > 0);
           mma_commit(&s_full[sb]);
-          if (i > 0) ok = issue_pv(gi - 1);
+          mma_commit(&k_empty[s]);
+          if (i > 1) ok = issue_pv(gi - 2);
         }
+        if (ok && n > 1) ok = issue_pv(g + n - 2);
         if (ok) ok = issue_pv(g + n - 1);
-        if (ok) mma_commit(q_empty);
+        if (ok) mma_commit(&q_empty[item_it & 1]);
       }
     } else {
       // -------------------------------------------------------------- softmax (thread = key position) and
       //                                                                accumulate (thread = output dimension)
       const int qd = warp & 3;
+      const int set = (warp - 2) >> 2;                     // two softmax warp sets take alternate tiles
       const int t = qd * 32 + lane;
       const uint32_t lane_bits = (uint32_t)(qd * 32) << 16;
-      float m_run[NMAX], l_part[NMAX], acc[NMAX];
+      float m_run[RMAX], l_part[RMAX], acc[RMAX];
 #pragma unroll
-      for (int i = 0; i < NMAX; ++i) { m_run[i] = -INFINITY; l_part[i] = 0.f; acc[i] = 0.f; }
+      for (int i = 0; i < RMAX; ++i) { m_run[i] = -INFINITY; l_part[i] = 0.f; acc[i] = 0.f; }
       bool ok = true;
-      if (n > 0) {
-        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag, p.status)) break;
-        if (t < NMAX) {
-          const int R = row0 + t;
-          const bool live = t < nrows;
-          const int tq = R / group, hq = kh * group + R % group;
-          const __nv_bfloat16* qrow = p.q + ((size_t)(r0 + tq) * p.Hq + hq) * D;
-          float amax = 0.f;
-          if (live) {
-#pragma unroll
-            for (int j = 0; j < D; j += 8) {
-              uint4 u = *reinterpret_cast<const uint4*>(qrow + j);
-              const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(bf2f(e[k])));
-            }
-          }
-          const float qscale = fmaxf(amax, 1e-12f) / 448.f;
-          const float qinv = 1.f / qscale;
-          uint8_t* qdst = sQ + (t >> 3) * (8 * D) + (t & 7) * 16;
-#pragma unroll
-          for (int j = 0; j < D; j += 16) {
-            uint4 o = make_uint4(0, 0, 0, 0);
-            if (live) {
-              uint4 u0 = *reinterpret_cast<const uint4*>(qrow + j), u1 = *reinterpret_cast<const uint4*>(qrow + j + 8);
-              const __nv_bfloat16* e0 = reinterpret_cast<const __nv_bfloat16*>(&u0);
-              const __nv_bfloat16* e1 = reinterpret_cast<const __nv_bfloat16*>(&u1);
-              o.x = pack_e4m3x4(bf2f(e0[0]) * qinv, bf2f(e0[1]) * qinv, bf2f(e0[2]) * qinv, bf2f(e0[3]) * qinv);
-              o.y = pack_e4m3x4(bf2f(e0[4]) * qinv, bf2f(e0[5]) * qinv, bf2f(e0[6]) * qinv, bf2f(e0[7]) * qinv);
-              o.z = pack_e4m3x4(bf2f(e1[0]) * qinv, bf2f(e1[1]) * qinv, bf2f(e1[2]) * qinv, bf2f(e1[3]) * qinv);
-              o.w = pack_e4m3x4(bf2f(e1[4]) * qinv, bf2f(e1[5]) * qinv, bf2f(e1[6]) * qinv, bf2f(e1[7]) * qinv);
-            }
-            *reinterpret_cast<uint4*>(qdst + (j >> 4) * 128) = o;
-          }
-          s_c[t] = p.scale_log2 * qscale;
-          s_pos[t] = live ? ctx - qlen + tq : -1;
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(q_full);
-        // the per-row constants are read by all four warps: wait until every warp has published its part
-        if (!mbar_wait(q_full, item_it & 1, abort_flag, p.status)) break;
-      }
-      float a1[NMAX];                                      // alpha of the previous tile (m_{i-2} -> m_{i-1})
-#pragma unroll
-      for (int r = 0; r < NMAX; ++r) a1[r] = 1.f;
-      // fold tile gj's O^T (held relative to the row maxima of tile gj) into the running sums
-      auto fold = [&](int gj, bool scaled) -> bool {
+      const int qb = item_it & 1;
+      if (n > 0 && !TW(6, &q_full[qb], (item_it >> 1) & 1)) break;     // per-row constants are published with Q
+      // add tile gj's O^T (relative to this set's row maxima at tile gj) to the running sums
+      auto fold = [&](int gj) -> bool {
         const int ob = gj % NB;
-        if (!mbar_wait(&o_full[ob], (gj / NB) & 1, abort_flag, p.status)) return false;
+        if (!TW(9, &o_full[ob], (gj / NB) & 1)) return false;
         tc_fence_after();
         uint32_t o[NMAX];
         tmem_ldn<NMAX>(tmem + NB * NMAX + ob * NMAX + lane_bits, o);
         tmem_ld_wait();
 #pragma unroll
-        for (int r = 0; r < NMAX; ++r)
-          if (r < nrows) acc[r] = scaled ? fmaf(__uint_as_float(o[r]), a1[r], acc[r]) : acc[r] + __uint_as_float(o[r]);
+        for (int r = 0; r < RMAX; ++r) {
+          if (r >= nrows) break;
+          acc[r] += __uint_as_float(o[r]);
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&o_empty[ob]);
         return true;
       };
-      for (int i = 0; i < n && ok; ++i) {
+      int last = -1;
+      for (int i = set; i < n && ok; i += 2) {
         const int gi = g + i, sb = gi % NB;
-        if (!mbar_wait(&s_full[sb], (gi / NB) & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!TW(7, &s_full[sb], (gi / NB) & 1)) { ok = false; break; }
         tc_fence_after();
         uint32_t v[NMAX];
         tmem_ldn<NMAX>(tmem + sb * NMAX + lane_bits, v);
         tmem_ld_wait();
         const int key = (t0 + i) * 128 + t;
-        float x[NMAX];
+        float x[RMAX];
 #pragma unroll
-        for (int r = 0; r < NMAX; ++r) {
-          if (r < nrows) {
-            x[r] = key <= s_pos[r] ? __uint_as_float(v[r]) * s_c[r] : -INFINITY;
-            const float wm = warp_max(x[r]);
-            if (lane == 0) s_wmax[sb][qd][r] = wm;
-          }
+        for (int r = 0; r < RMAX; ++r) {
+          if (r >= nrows) break;
+          x[r] = key <= s_pos[qb][r] ? __uint_as_float(v[r]) * s_c[qb][r] : -INFINITY;
+          const float wm = warp_max(x[r]);
+          if (lane == 0) s_wmax[sb][qd][r] = wm;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&wm_bar[sb]);
-        // fold the output of two tiles ago while the other warps catch up
-        if (i >= 2 && !fold(gi - 2, true)) { ok = false; break; }
-        if (!mbar_wait(&wm_bar[sb], (gi / NB) & 1, abort_flag, p.status)) { ok = false; break; }
+        // fold this set's previous tile while the other warps of the set catch up
+        if (last >= 0 && !fold(last)) { ok = false; break; }
+        if (!TW(8, &wm_bar[sb], (gi / NB) & 1)) { ok = false; break; }
         uint8_t* pdst = sP + sb * Cfg::P_BYTES + (t >> 4) * 128 + (t & 15);
 #pragma unroll
-        for (int r = 0; r < NMAX; ++r) {
-          if (r < nrows) {
-            const float mt = fmaxf(fmaxf(s_wmax[sb][0][r], s_wmax[sb][1][r]), fmaxf(s_wmax[sb][2][r], s_wmax[sb][3][r]));
-            const float m_new = fmaxf(m_run[r], mt);
-            const float alpha = (m_run[r] == -INFINITY) ? 0.f : ex2(m_run[r] - m_new);
-            const float pr = (x[r] == -INFINITY) ? 0.f : ex2(x[r] - m_new + 8.f);     // P scaled by 2^8 for e4m3
-            l_part[r] = l_part[r] * alpha + pr;
-            acc[r] *= alpha;
-            a1[r] = alpha;
-            m_run[r] = m_new;
-            pdst[(r >> 3) * 1024 + (r & 7) * 16] = (uint8_t)__nv_cvt_float_to_fp8(pr, __NV_SATFINITE, __NV_E4M3);
-          }
+        for (int r = 0; r < RMAX; ++r) {
+          if (r >= nrows) break;
+          const float mt = fmaxf(fmaxf(s_wmax[sb][0][r], s_wmax[sb][1][r]), fmaxf(s_wmax[sb][2][r], s_wmax[sb][3][r]));
+          const float m_new = fmaxf(m_run[r], mt);
+          const float alpha = ex2(m_run[r] - m_new);                   // ex2(-inf) = 0 on the first tile
+          const float pr = ex2(x[r] - m_new + 8.f);                    // masked keys: ex2(-inf) = 0; P scaled by 2^8
+          l_part[r] = l_part[r] * alpha + pr;
+          acc[r] *= alpha;
+          m_run[r] = m_new;
+          pdst[(r >> 3) * 1024 + (r & 7) * 16] = (uint8_t)__nv_cvt_float_to_fp8(pr, __NV_SATFINITE, __NV_E4M3);
         }
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(&p_full[sb]); }
+        last = gi;
       }
-      if (ok && n >= 2) ok = fold(g + n - 2, true);
-      if (ok && n >= 1) ok = fold(g + n - 1, false);
+      if (ok && last >= 0) ok = fold(last);
       if (!ok) break;
-      // ---- row sums over all key positions of this item
+      // ---- merge the two sets and the four warps of each: row sums, maxima, output sums
       if (n > 0) {
+        // the exchange buffers are single: set 1 writes them only after set 0 has read the previous item's
+        if (set == 1 && !TW(11, acc_free, (item_it & 1) ^ 1)) break;
 #pragma unroll
-        for (int r = 0; r < NMAX; ++r) {
-          if (r < nrows) {
-            const float ws = warp_sum(l_part[r]);
-            if (lane == 0) s_l[qd][r] = ws;
-          }
+        for (int r = 0; r < RMAX; ++r) {
+          if (r >= nrows) break;
+          const float ws = warp_sum(l_part[r]);
+          if (lane == 0) s_l[set][qd][r] = ws;
+          if (set == 1) s_acc[r][t] = acc[r];
+          if (set == 1 && t == 0) s_m[r] = m_run[r];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(fin_bar);
-        if (!mbar_wait(fin_bar, item_it & 1, abort_flag, p.status)) break;
-      }
+        if (!TW(11, fin_bar, item_it & 1)) break;
+        if (set == 0) {
 #pragma unroll
-      for (int r = 0; r < NMAX; ++r) {
-        if (r < nrows) {
-          const float l = n > 0 ? s_l[0][r] + s_l[1][r] + s_l[2][r] + s_l[3][r] : 0.f;
-          const int R = row0 + r;
-          const int tq = R / group, hq = kh * group + R % group;
-          if (p.splits == 1) {
-            const float inv = l > 0.f ? p.v_scale / l : 0.f;
-            p.out[((size_t)(r0 + tq) * p.Hq + hq) * D + t] = __float2bfloat16(acc[r] * inv);
-          } else {
-            p.part_o[((size_t)w * NMAX + r) * D + t] = acc[r];
-            if (t == 0) {
-              p.part_ml[((size_t)w * NMAX + r) * 2] = m_run[r];
-              p.part_ml[((size_t)w * NMAX + r) * 2 + 1] = l;
+          for (int r = 0; r < RMAX; ++r) {
+            if (r >= nrows) break;
+            const float mb = s_m[r];
+            const float m = fmaxf(m_run[r], mb);
+            const float fa = ex2(m_run[r] - m), fb = ex2(mb - m);      // set 0 always has at least one tile
+            const float l = (s_l[0][0][r] + s_l[0][1][r] + s_l[0][2][r] + s_l[0][3][r]) * fa +
+                            (s_l[1][0][r] + s_l[1][1][r] + s_l[1][2][r] + s_l[1][3][r]) * fb;
+            const float o = acc[r] * fa + s_acc[r][t] * fb;
+            const int R = row0 + r;
+            const int tq = R / group, hq = kh * group + R % group;
+            if (p.splits == 1) {
+              p.out[((size_t)(r0 + tq) * p.Hq + hq) * D + t] = __float2bfloat16(l > 0.f ? o * p.v_scale / l : 0.f);
+            } else {
+              p.part_o[((size_t)w * NMAX + r) * D + t] = o;
+              if (t == 0) {
+                p.part_ml[((size_t)w * NMAX + r) * 2] = m;
+                p.part_ml[((size_t)w * NMAX + r) * 2 + 1] = l;
+              }
             }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_free);
+        }
+      } else if (set == 0 && p.splits > 1) {
+        for (int r = 0; r < nrows; ++r) {
+          p.part_o[((size_t)w * NMAX + r) * D + t] = 0.f;
+          if (t == 0) {
+            p.part_ml[((size_t)w * NMAX + r) * 2] = -INFINITY;
+            p.part_ml[((size_t)w * NMAX + r) * 2 + 1] = 0.f;
           }
         }
       }
@@ -319,6 +381,11 @@ __global__ void __launch_bounds__(192, (NMAX <= 16 ? 2 : 1)) attn_decode_kernel(
     g += n;
     if (n > 0) ++item_it;
     if (*abort_flag) break;
+  }
+#undef TW
+  if (p.prof && blockIdx.x < 8 && lane == 0 && warp < 3) {
+    pc[12] = clock64() - t_start;
+    for (int i = 0; i < 13; ++i) p.prof[((size_t)blockIdx.x * 3 + warp) * 16 + i] = pc[i];
   }
   tc_fence_before();
   __syncthreads();
@@ -363,20 +430,20 @@ __global__ void attn_decode_combine_kernel(AttnParams p) {
   }
 }
 
-template <int NMAX>
+template <int NMAX, int RMAX>
 static cudaError_t launch_decode(const AttnParams& p, int max_ctas, cudaStream_t stream) {
-  using Cfg = DecCfg<NMAX>;
+  using Cfg = DecCfg<NMAX, RMAX>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NMAX, RMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int total = p.num_items * p.Hkv * p.row_blocks * p.splits;
-  const int per_sm = NMAX <= 16 ? 2 : 1;
-  int grid = total < per_sm * sm_count() ? total : per_sm * sm_count();
+  const int cap = Cfg::CTAS_PER_SM * sm_count();
+  int grid = total < cap ? total : cap;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  attn_decode_kernel<NMAX><<<grid, 192, Cfg::SMEM, stream>>>(p);
+  attn_decode_kernel<NMAX, RMAX><<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || p.splits == 1) return e;
   attn_decode_combine_kernel<NMAX><<<p.num_items * p.Hkv * p.row_blocks, 128, 0, stream>>>(p);
@@ -391,7 +458,8 @@ static cudaError_t launch_decode(const AttnParams& p, int max_ctas, cudaStream_t
 BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
                             const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride,
                             float scale, float k_scale, float v_scale, int nmax, int row_blocks, int min_rows,
-                            int max_rows, int splits, float* part_o, float* part_ml, int max_ctas, cudaStream_t stream) {
+                            int max_rows, int splits, float* part_o, float* part_ml, int max_ctas, long long* prof,
+                            cudaStream_t stream) {
   using namespace blz;
   if (num_seqs <= 0) return 0;
   if (D != 128 || Hq % Hkv || (nmax != 16 && nmax != 32) || row_blocks < 1 || splits < 1 ||
@@ -405,5 +473,10 @@ BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const in
   p.scale_log2 = scale * 1.4426950408889634f * k_scale; p.v_scale = v_scale;
   p.tokens_per_block = 0; p.min_rows = min_rows; p.max_rows = max_rows; p.row_blocks = row_blocks;
   p.status = status_word();
-  return (int)(nmax == 16 ? launch_decode<16>(p, max_ctas, stream) : launch_decode<32>(p, max_ctas, stream));
+  p.prof = prof;
+  if (nmax == 32) return (int)launch_decode<32, 32>(p, max_ctas, stream);
+  const int live = max_rows < 16 ? max_rows : 16;     // most live rows of any work item
+  if (live <= 4) return (int)launch_decode<16, 4>(p, max_ctas, stream);
+  if (live <= 8) return (int)launch_decode<16, 8>(p, max_ctas, stream);
+  return (int)launch_decode<16, 16>(p, max_ctas, stream);
 }

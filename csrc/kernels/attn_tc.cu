@@ -383,6 +383,7 @@ BLZ_API int blz_attn_tc(const void* q, void* out, const void* pool, const int* b
   p.scale_log2 = scale * 1.4426950408889634f * k_scale; p.v_scale = v_scale;
   p.tokens_per_block = 128 / (Hq / Hkv);
   p.status = status_word();
+  p.min_rows = 0; p.max_rows = 1 << 30; p.row_blocks = 1; p.prof = nullptr;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<128>::SMEM);
