@@ -394,43 +394,92 @@ class Model:
     # ================================================================== forward
     def forward(self, batch: StepBatch, kv: KVCache, hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run this stage's layers.  Returns the residual stream ``[T, hidden]`` *before* the final norm
-        on the last stage (use :meth:`head` for logits), or the rows to hand to the next stage."""
+        on the last stage (use :meth:`head` for logits), or the rows to hand to the next stage.
+
+        Every block returns its output as this rank's *partial* sums; the reduction over ranks happens together with
+        the residual add and the next RMSNorm — one fused peer-memory kernel when the group has one
+        (``reduce_norm`` in ``crates/blaze/src/model.rs:2555``), else all-reduce followed by the norm kernel."""
         ops, cfg = self.ops, self.cfg
         if self.is_first_stage:
             x = ops.embed(self.embed, batch.tokens)
         else:
             x = hidden_in
-        residual = None
+        fused = self._fused()
         rope = ops.rope_tables(self, batch)
+        residual = None          # full rows, or this rank's row shard on the fused path
+        partial = False          # is x a partial sum that still needs the reduction?
         for li, L in enumerate(self.layers):
             gi = self.first_layer + li
-            if gi in self.capture_layers:
-                self.captured[gi] = x if residual is None else ops.add(x, residual)
             first = L.attn.qkv if L.attn is not None else L.gdn.in_proj
-            h, residual = ops.norm(x, residual, L.input_norm, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=first)
+            if gi in self.capture_layers:
+                self.captured[gi] = self._materialise(x, residual, partial, fused)
+            h, residual = self._reduce_norm(x, residual, partial, L.input_norm, first, fused)
             if L.kind == "full_attention":
-                x = self._attention(L.attn, h, batch, kv, gi, rope)
+                x = self._attention(L.attn, h, batch, kv, gi, rope, fused)
             else:
-                x = self._gdn(L.gdn, h, batch, kv, gi)
+                x = self._gdn(L.gdn, h, batch, kv, gi, fused)
+            partial = self.tp.world > 1
             nxt = L.mlp.gate_up if isinstance(L.mlp, DenseMlp) else None
-            h, residual = ops.norm(x, residual, L.post_norm, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=nxt)
-            x = self._mlp(L.mlp, h)
-        # fold the last residual so the caller sees the full stream
+            h, residual = self._reduce_norm(x, residual, partial, L.post_norm, nxt, fused)
+            x, partial = self._mlp(L.mlp, h, fused)
+        return self._materialise(x, residual, partial, fused)
+
+    def _fused(self):
+        g = self.tp.group
+        return g.fused if (g is not None and g.world > 1 and getattr(g, "fused", None) is not None and self.ops.is_cuda) else None
+
+    def _reduce_norm(self, x, residual, partial, w, quant_for, fused):
+        ops, cfg = self.ops, self.cfg
+        if fused is not None:
+            if residual is None:                       # first norm of the stage: shard the residual stream by rows
+                residual = fused.shard_rows(x)
+                h, _ = ops.norm(x, None, w, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=quant_for)
+                return h, residual
+            if not partial:                            # complete rows (expert-parallel MoE output): add this rank's share
+                x = self._as_partial(x, fused)
+            h = fused.reduce_norm(x, residual, w, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for)
+            return h, residual
+        if partial:
+            x = ops.all_reduce(x, self.tp.group)
+        return ops.norm(x, residual, w, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=quant_for)
+
+    def _as_partial(self, x, fused):
+        """Present complete rows as partial sums: rank 0 contributes them, the others contribute zeros."""
+        buf = fused.next_input(x.shape[0], x.shape[1])
+        if self.tp.rank == 0:
+            buf.copy_(x)
+        else:
+            buf.zero_()
+        return buf
+
+    def _materialise(self, x, residual, partial, fused):
+        """The complete residual stream on every rank."""
+        ops = self.ops
+        if fused is not None and residual is not None:
+            if not partial:
+                x = self._as_partial(x, fused)
+            return fused.reduce_norm(x, residual, None, self.cfg.rms_norm_eps, False, None)
+        if partial:
+            x = ops.all_reduce(x, self.tp.group)
         if residual is not None:
             x = ops.add(x, residual)
         return x
 
-    def _attention(self, A: Attn, h, batch, kv, gi, rope):
+    def _out_buf(self, fused, rows, cols):
+        return fused.next_input(rows, cols) if fused is not None else None
+
+    def _attention(self, A: Attn, h, batch, kv, gi, rope, fused=None):
         ops = self.ops
         qkv = ops.linear(A.qkv, h)
         q, gate = ops.attn_prep_store(qkv, A, self, batch, kv, gi, rope)
         o = ops.attention(q, self, batch, kv, gi, self.attn_scale)
         if gate is not None:
             o = ops.mul_sigmoid(o, gate.reshape(o.shape))
-        y = ops.linear(A.o, o)
-        return ops.all_reduce(y, self.tp.group)
+        if fused is not None:
+            return ops.linear(A.o, o, out=fused.next_input(o.shape[0], A.o.N))
+        return ops.linear(A.o, o)
 
-    def _gdn(self, G: Gdn, h, batch, kv, gi):
+    def _gdn(self, G: Gdn, h, batch, kv, gi, fused=None):
         ops, cfg = self.ops, self.cfg
         dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         proj = ops.linear(G.in_proj, h)
@@ -439,34 +488,37 @@ class Model:
         mixed, z = proj[:, :nq], proj[:, nq:nq + nz]
         b, a = proj[:, nq + nz:nq + nz + G.v_heads], proj[:, nq + nz + G.v_heads:]
         o = ops.gdn(mixed, z, b, a, G, self, batch, kv, gi)
-        y = ops.linear(G.out_proj, o)
-        return ops.all_reduce(y, self.tp.group)
+        if fused is not None:
+            return ops.linear(G.out_proj, o, out=fused.next_input(o.shape[0], G.out_proj.N))
+        return ops.linear(G.out_proj, o)
 
-    def _mlp(self, M, h):
+    def _mlp(self, M, h, fused=None):
+        """Returns (output, is_partial_sum)."""
         ops = self.ops
+        tp = self.tp.world > 1
         if isinstance(M, DenseMlp):
             a = ops.silu_mul(ops.linear(M.gate_up, h), quant_for=M.down)
-            return ops.all_reduce(ops.linear(M.down, a), self.tp.group)
-        logits = ops.linear(M.router, h, out_dtype=torch.float32)
+            if fused is not None:
+                return ops.linear(M.down, a, out=fused.next_input(a.rows if hasattr(a, "rows") else a.shape[0], M.down.N)), True
+            return ops.linear(M.down, a), tp
+        hd = h.dense if hasattr(h, "dense") and h.dense is not None else h
+        logits = ops.linear(M.router, hd, out_dtype=torch.float32)
         w, ids = ops.router_topk(logits, M.top_k, M.renorm)
-        if self.tp.ep and self.tp.world > 1:
-            y = self.tp.group.moe_ep(ops, h, w, ids, M.experts)
+        if self.tp.ep and tp:
+            y = self.tp.group.moe_ep(ops, hd, w, ids, M.experts)          # complete rows on every rank
+            routed_partial = False
         else:
-            y = ops.moe(h, w, ids, M.experts)
+            y = ops.moe(hd, w, ids, M.experts)
+            routed_partial = tp
         if M.shared is not None:
-            s = ops.linear(M.shared.down, ops.silu_mul(ops.linear(M.shared.gate_up, h), quant_for=M.shared.down))
+            s = ops.linear(M.shared.down, ops.silu_mul(ops.linear(M.shared.gate_up, hd), quant_for=M.shared.down))
+            if tp and not routed_partial:
+                s = ops.all_reduce(s, self.tp.group)
             if M.shared_gate is not None:
-                gl = ops.linear(M.shared_gate, h)
-                if self.tp.ep:
-                    s_full = ops.all_reduce(s, self.tp.group)
-                    return ops.add_sigmoid_scaled(y, s_full, gl)
-                # fold the shared expert into the same reduction as the routed sum
-                y = ops.add_sigmoid_scaled(y, s, gl)
+                y = ops.add_sigmoid_scaled(y, s, ops.linear(M.shared_gate, hd))
             else:
                 y = ops.add(y, s)
-        if self.tp.ep:
-            return y                      # moe_ep already returned complete rows
-        return ops.all_reduce(y, self.tp.group)
+        return y, routed_partial
 
     # ------------------------------------------------------------------ head
     def final_hidden(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:

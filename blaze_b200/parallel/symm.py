@@ -1,0 +1,205 @@
+"""Symmetric memory over NVLink and the in-kernel collectives built on it.
+
+One allocation per rank is mapped into every peer (``torch.distributed._symmetric_memory``: cuMem handles exchanged
+over the process group; an NVSwitch multicast address when the fabric supports it).  The arena is carved into the
+buffers the fused kernels use: two alternating partial-sum buffers that the row-cut GEMMs write directly, the
+broadcast targets for normed / quantised activations, and the flag pads of the rank barrier.
+
+``SymmAllReduce`` is what ``TPGroup.fused`` holds.  It offers
+  * ``all_reduce``   — in place on a partial-sum buffer (multimem or peer loads/stores inside one kernel);
+  * ``reduce_norm``  — all-reduce + residual add + RMSNorm (+ NVFP4 / MXFP8 quantisation) in one kernel, leaving
+    the residual stream sharded by rows between the two collectives of a layer.
+
+The reference's transport for the same two operations is pinned host memory (``kernels/src/cuda/host_allreduce.cu``,
+``blz_host_ar_open`` :420 with POSIX shm, ``host_ar_rmsnorm_kernel`` :280).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Tuple
+
+import torch
+
+from .._native import kernels
+from ..linear import Linear, QuantAct
+from ..quant import Format
+
+VP = ctypes.c_void_p
+
+
+def _arr(ptrs: List[int]):
+    return (VP * len(ptrs))(*[VP(p) for p in ptrs])
+
+
+class SymmArena:
+    """A symmetric byte buffer: local tensor, peer base pointers, multicast base pointer (0 when absent)."""
+
+    def __init__(self, group, device, nbytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.nbytes = (nbytes + 4095) // 4096 * 4096
+        self.local = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=torch.device(device))
+        self.handle = symm_mem.rendezvous(self.local, group.pg)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        mc = 0
+        try:
+            mc = int(self.handle.multicast_ptr or 0)
+        except Exception:
+            mc = 0
+        self.mc = mc
+        self.rank, self.world = group.rank, group.world
+        self.off = 0
+
+    def carve(self, nbytes: int, align: int = 4096) -> int:
+        off = (self.off + align - 1) // align * align
+        if off + nbytes > self.nbytes:
+            raise MemoryError("symmetric arena exhausted")
+        self.off = off + nbytes
+        return off
+
+    def view(self, off: int, nbytes: int) -> torch.Tensor:
+        return self.local[off:off + nbytes]
+
+    def peers(self, off: int) -> List[int]:
+        return [p + off for p in self.ptrs]
+
+    def mcast(self, off: int) -> int:
+        return self.mc + off if self.mc else 0
+
+
+class SymmAllReduce:
+    def __init__(self, group, device, max_rows: int, hidden: int, use_multicast: bool = True):
+        self.group, self.device = group, torch.device(device)
+        self.lib = kernels()
+        lib = self.lib
+        lib.blz_comm_create.restype = VP
+        lib.blz_comm_create.argtypes = [ctypes.c_int, ctypes.c_int, VP, VP, ctypes.c_int]
+        lib.blz_comm_allreduce.argtypes = [VP, VP, VP, VP, VP, ctypes.c_longlong, ctypes.c_int, VP]
+        lib.blz_comm_allreduce_norm.argtypes = [VP] + [VP] * 8 + [VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                                  ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, VP]
+        self.max_rows, self.hidden = max_rows, hidden
+        row_tiles = (max_rows + 127) // 128
+        self.in_bytes = max_rows * hidden * 2
+        self.q_bytes = max_rows * hidden                      # e4m3 rows (NVFP4 uses half of it)
+        self.sf_bytes = row_tiles * ((hidden + 63) // 64) * 512
+        self.rs_bytes = max_rows * 4
+        pad_bytes = int(lib.blz_comm_pad_bytes())
+        total = 2 * self.in_bytes + self.in_bytes + self.q_bytes + self.sf_bytes + self.rs_bytes + pad_bytes + 16 * 4096
+        self.arena = SymmArena(group, device, total)
+        a = self.arena
+        self.off_in = [a.carve(self.in_bytes), a.carve(self.in_bytes)]
+        self.off_out = a.carve(self.in_bytes)
+        self.off_q = a.carve(self.q_bytes)
+        self.off_sf = a.carve(self.sf_bytes)
+        self.off_rs = a.carve(self.rs_bytes)
+        self.off_pad = a.carve(pad_bytes)
+        a.view(self.off_pad, pad_bytes).zero_()
+        self.epoch = torch.zeros(int(lib.blz_comm_epoch_bytes()) // 4, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        group.barrier()
+        self.comm = lib.blz_comm_create(group.rank, group.world, _arr(a.peers(self.off_pad)), VP(self.epoch.data_ptr()), 1)
+        if not self.comm:
+            raise RuntimeError("blz_comm_create failed")
+        self.use_mc = bool(use_multicast and a.mc)
+        self.cur = 0
+        self.launches = 0
+
+    @classmethod
+    def create(cls, group, device, max_rows: int = 8192, hidden: int = 4096, **kw) -> "SymmAllReduce":
+        return cls(group, device, max_rows, hidden, **kw)
+
+    # ------------------------------------------------------------------ buffers
+    def next_input(self, rows: int, cols: int) -> torch.Tensor:
+        """A bf16 ``[rows, cols]`` view of the next partial-sum buffer; the producing GEMM writes into it."""
+        n = rows * cols * 2
+        if n > self.in_bytes:
+            raise ValueError(f"partial-sum buffer too small for {rows}x{cols}")
+        self.cur ^= 1
+        return self.arena.view(self.off_in[self.cur], n).view(torch.bfloat16).view(rows, cols)
+
+    def _which(self, x: torch.Tensor) -> Optional[int]:
+        base = self.arena.local.data_ptr()
+        for i, off in enumerate(self.off_in):
+            if x.data_ptr() == base + off:
+                return i
+        return None
+
+    def _stream(self) -> VP:
+        return VP(torch.cuda.current_stream(self.device).cuda_stream)
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """Sum ``x`` over ranks.  ``x`` should be a buffer from :meth:`next_input` (otherwise it is copied in)."""
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            return None
+        nbytes = x.numel() * 2
+        if nbytes > self.in_bytes or nbytes % 16:
+            return None
+        i = self._which(x)
+        if i is None:
+            buf = self.next_input(x.shape[0], x.numel() // x.shape[0]).view(x.shape)
+            buf.copy_(x)
+            x, i = buf, self.cur
+        a = self.arena
+        off = self.off_in[i]
+        mc = a.mcast(off) if self.use_mc else 0
+        blocks = max(1, min(64, (nbytes // 16 + 511) // 512 // max(self.group.world, 1) + 1))
+        rc = self.lib.blz_comm_allreduce(self.comm, _arr(a.peers(off)), _arr(a.peers(off)), VP(mc), VP(mc), nbytes, blocks,
+                                         self._stream())
+        if rc != 0:
+            raise RuntimeError(f"blz_comm_allreduce failed: {rc}")
+        self.launches += 1
+        return x
+
+    def rows_per(self, T: int) -> int:
+        return (T + self.group.world - 1) // self.group.world
+
+    def shard_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """This rank's slice of a full ``[T, H]`` tensor as a fresh ``[rows_per, H]`` residual shard."""
+        T = x.shape[0]
+        per = self.rows_per(T)
+        lo = self.group.rank * per
+        out = torch.zeros(per, x.shape[1], dtype=x.dtype, device=x.device)
+        hi = min(T, lo + per)
+        if hi > lo:
+            out[:hi - lo] = x[lo:hi]
+        return out
+
+    def reduce_norm(self, partial: torch.Tensor, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor],
+                    eps: float, zero_centered: bool, quant_for: Optional[Linear] = None):
+        """``partial``: this rank's ``[T, H]`` partial sums in a buffer from :meth:`next_input`.
+        ``residual``: this rank's ``[rows_per, H]`` slice of the residual stream (updated in place).
+        Returns the normed rows on every rank: a bf16 ``[T, H]`` tensor or a :class:`QuantAct`.
+        With ``norm_w=None`` the summed (+ residual) rows are returned unnormalised."""
+        T, H = partial.shape
+        i = self._which(partial)
+        if i is None:
+            buf = self.next_input(T, H)
+            buf.copy_(partial)
+            partial, i = buf, self.cur
+        mode = 0
+        if quant_for is not None and quant_for.act_quant and norm_w is not None:
+            mode = 1 if quant_for.fmt == Format.NVFP4 else (2 if quant_for.fmt in (Format.MXFP8, Format.FP8_BLOCK) else 0)
+        a = self.arena
+        off_in = self.off_in[i]
+        off_out = self.off_out if mode == 0 else self.off_q
+        mc = self.use_mc
+        per = self.rows_per(T)
+        blocks = max(1, min(per, 512))
+        rc = self.lib.blz_comm_allreduce_norm(
+            self.comm, _arr(a.peers(off_in)), _arr(a.peers(off_out)), _arr(a.peers(self.off_sf)), _arr(a.peers(self.off_rs)),
+            VP(a.mcast(off_in) if mc else 0), VP(a.mcast(off_out) if mc else 0), VP(a.mcast(self.off_sf) if mc else 0),
+            VP(a.mcast(self.off_rs) if mc else 0), VP(residual.data_ptr() if residual is not None else 0),
+            VP(norm_w.data_ptr() if norm_w is not None else 0), T, H, per, eps, int(zero_centered), mode, blocks, self._stream())
+        if rc != 0:
+            raise RuntimeError(f"blz_comm_allreduce_norm failed: {rc}")
+        self.launches += 1
+        if mode == 0:
+            return a.view(off_out, T * H * 2).view(torch.bfloat16).view(T, H)
+        if mode == 1:
+            data = a.view(off_out, T * H // 2).view(T, H // 2)
+            sf = a.view(self.off_sf, ((T + 127) // 128) * ((H + 63) // 64) * 512)
+            rs = a.view(self.off_rs, T * 4).view(torch.float32)
+            return QuantAct(Format.NVFP4, data, sf, rs, T, H)
+        data = a.view(off_out, T * H).view(T, H)
+        sf = a.view(self.off_sf, ((T + 127) // 128) * ((H + 127) // 128) * 512)
+        return QuantAct(Format.MXFP8, data, sf, None, T, H)

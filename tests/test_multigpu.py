@@ -1,0 +1,34 @@
+"""Multi-GPU tests (2 GPUs): in-kernel all-reduce over peer memory / NVSwitch multimem, the fused
+all-reduce + residual + RMSNorm (+ quantise) kernel, and tensor-parallel decoding through the fused path."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(case, multicast="1", nproc=2):
+    env = dict(os.environ, BLAZE_TEST_MULTICAST=multicast, NCCL_DEBUG="WARN")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", "29611", os.path.join(HERE, "_tp_worker.py"), case]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    print(r.stdout[-3000:])
+    print(r.stderr[-3000:])
+    assert r.returncode == 0
+
+
+@pytest.mark.parametrize("multicast", ["1", "0"])
+def test_allreduce(multicast):
+    _run("allreduce", multicast)
+
+
+@pytest.mark.parametrize("multicast", ["1", "0"])
+def test_reduce_norm(multicast):
+    _run("reduce_norm", multicast)
+
+
+def test_tp2_model_fused_matches_tp1():
+    _run("model")
