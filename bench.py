@@ -74,6 +74,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the line invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collectives: in-kernel peer memory, or NCCL")
     ap.add_argument("--cuda-profiler", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -100,15 +101,19 @@ def main():
     dev = f"cuda:{local}"
     group = TPGroup.from_env(dev)
     tp = TPInfo(rank, world, group)
-    if group is not None:
-        try:
-            from blaze_b200.parallel.symm import SymmAllReduce
-            group.fused = SymmAllReduce.create(group, dev, max_bytes=args.batch * 8192 * 2 * 4)
-        except Exception as e:  # the NCCL path stays available
-            if rank == 0:
-                print(f"[bench] fused all-reduce unavailable ({e!r}); using NCCL", file=sys.stderr)
-
     cfg = named_config(args.model)
+    comm = "none"
+    if group is not None:
+        comm = "nccl"
+        if args.comm == "fused":
+            try:
+                from blaze_b200.parallel.symm import SymmAllReduce
+                group.fused = SymmAllReduce.create(group, dev, max_rows=args.batch + 4096 + 64, hidden=cfg.hidden_size)
+                comm = "fused peer-memory kernels (" + ("multimem" if group.fused.use_mc else "p2p") + ")"
+            except Exception as e:  # the NCCL path stays available
+                if rank == 0:
+                    print(f"[bench] fused collectives unavailable ({e!r}); using NCCL", file=sys.stderr)
+
     invalid = None
     if args.layers:
         cfg.num_layers = args.layers
@@ -219,7 +224,7 @@ def main():
             "n_gpus": args.gpus, "steps": K, "warmup": max(W, 3), "ms_per_step": ms / K, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": f"{args.weights} weights, fp8 KV, bf16 activations",
             "data": "synthetic token ids, random-init N(0,0.02) weights", "impl": "ours",
-            "config": {"model": args.model, "global_batch": B, "seq_len": P, "parallelism": f"tp{args.gpus}",
+            "config": {"model": args.model, "global_batch": B, "seq_len": P, "parallelism": f"tp{args.gpus}", "collectives": comm,
                        "kv": "fp8 e4m3, 16-token pages", "l2": "inputs larger than L2 (KV + weights read per step >> 126 MB)",
                        "layers": cfg.num_layers},
             "clocks": clocks_summary(clk_path),
