@@ -414,7 +414,10 @@ class Scheduler:
     def _emit(self, a_or_req, ev: GenEvent) -> None:
         req = a_or_req.req if isinstance(a_or_req, Active) else a_or_req
         if req.sink:
-            req.sink(ev)
+            try:
+                req.sink(ev)
+            except Exception as e:   # a consumer that went away must not take the step down with it
+                log.debug("sched.sink_failed", request_id=req.request_id, error=repr(e))
 
     def _admit(self) -> None:
         while True:

@@ -1,0 +1,932 @@
+"""OpenAI-compatible HTTP API (FastAPI): chat/completions, completions, embeddings, Responses, Anthropic Messages,
+tokenize / detokenize, models, health, metrics, server info.
+
+Route list and behaviour follow the reference's ``crates/blaze/src/server.rs:282-301`` and ``server/*.rs``:
+early 503 ``model_loading`` body with the current load stage while the model loads (:177-245), auth by Bearer or
+``x-api-key`` (``server/control.rs:44``), request id / CORS / semaphore admission / deadline middleware (:100), SSE
+streaming with ``[DONE]``, usage accounting, Prometheus text at ``/metrics`` (:360-406), an in-memory store of the
+last 256 Responses objects (``server/responses.rs``).
+"""
+from __future__ import annotations
+
+import asyncio
+import base64
+import hmac
+import json
+import struct
+import time
+import uuid
+from collections import OrderedDict
+from typing import Any, AsyncIterator, Dict, List, Optional
+
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from .. import __version__, log
+from ..chat import ChatFormatter, ChatResponseProcessor, get_tool_parser
+from ..sampler import SamplingParams
+from ..sched import Finish, GenEvent, GenRequest, ThinkBudget
+from ..service import (MAX_COMPLETIONS_PER_REQUEST, RequestError, ServiceArgs, sampling_of, stop_strings_of,
+                       thinking_budget_of)
+from ..structured import ConstraintError, Grammars, grammar_of
+from ..telemetry import Histogram
+
+RESPONSES_KEPT = 256
+THINK_CLOSING = "\n\nConsidering the limited time, I have to give the solution based on the thinking directly now.\n</think>\n\n"
+
+
+def _err(status: int, message: str, typ: str = "invalid_request_error", param=None, code=None) -> JSONResponse:
+    return JSONResponse({"error": {"message": message, "type": typ, "param": param, "code": code}}, status_code=status)
+
+
+class Totals:
+    def __init__(self):
+        self.requests = self.errors = self.prompt_tokens = self.cached_tokens = self.output_tokens = 0
+        self.e2e = Histogram.latency()
+        self.inflight = 0
+
+
+class ServerState:
+    """Everything the handlers need.  ``llm`` is None while the model is loading."""
+
+    def __init__(self, svc: ServiceArgs, model_name: str = "blaze"):
+        self.svc, self.model_name = svc, svc.served_model_name or model_name
+        self.llm = None
+        self.tokenizer = None
+        self.formatter: Optional[ChatFormatter] = None
+        self.grammars: Optional[Grammars] = None
+        self.vision = None
+        self.totals = Totals()
+        self.started = time.time()
+        self.responses: "OrderedDict[str, Dict[str, Any]]" = OrderedDict()
+        self.sem = asyncio.Semaphore(svc.max_concurrency)
+        self.waiting = 0
+        self.shutting_down = False
+
+    def attach(self, llm, tokenizer, vision=None) -> None:
+        self.tokenizer = tokenizer
+        self.formatter = ChatFormatter(getattr(tokenizer, "chat_template", None))
+        cfg = llm.model.cfg
+        eos = tuple(llm.sched.cfg.eos_ids) or tuple(getattr(tokenizer, "eos_ids", ()))
+        llm.sched.cfg.eos_ids = eos
+        self.grammars = Grammars.load(tokenizer, cfg.vocab_size, eos)
+        self.vision = vision
+        self.llm = llm
+        if llm.sched._thread is None:
+            llm.sched.start()
+
+    @property
+    def ready(self) -> bool:
+        return self.llm is not None
+
+    @property
+    def vocab(self) -> int:
+        return self.llm.model.cfg.vocab_size
+
+    @property
+    def max_len(self) -> int:
+        return self.llm.sched.cfg.max_model_len
+
+
+class Gen:
+    """One generation in flight: submits to the scheduler and yields events on the asyncio side (``server.rs:794``)."""
+
+    def __init__(self, st: ServerState, prompt: List[int], params: SamplingParams, **kw):
+        self.st = st
+        self.q: "asyncio.Queue[GenEvent]" = asyncio.Queue()
+        self.loop = asyncio.get_running_loop()
+        self.rid = "req-" + uuid.uuid4().hex[:16]
+        self.req = GenRequest(self.rid, prompt, params, sink=self._sink, **kw)
+        self.prompt_tokens = len(prompt)
+        self.cached = 0
+        self.finish: Optional[Finish] = None
+        self.error: Optional[str] = None
+        self.n_out = 0
+        st.llm.sched.submit(self.req)
+
+    def _sink(self, ev: GenEvent) -> None:
+        try:
+            self.loop.call_soon_threadsafe(self.q.put_nowait, ev)
+        except RuntimeError:       # the client's event loop is gone
+            pass
+
+    async def events(self) -> AsyncIterator[GenEvent]:
+        deadline = time.monotonic() + self.st.svc.request_timeout_s
+        while True:
+            try:
+                ev = await asyncio.wait_for(self.q.get(), timeout=max(deadline - time.monotonic(), 0.01))
+            except asyncio.TimeoutError:
+                self.st.llm.sched.abort(self.rid)
+                self.finish, self.error = Finish.ABORT, "request deadline exceeded"
+                return
+            self.cached = ev.cached_tokens
+            self.n_out += len(ev.tokens)
+            if ev.tokens or ev.hidden is not None:
+                yield ev
+            if ev.finish is not None:
+                self.finish, self.error = ev.finish, ev.error
+                return
+
+    def abort(self) -> None:
+        self.st.llm.sched.abort(self.rid)
+
+
+def finish_reason(f: Optional[Finish], tool_calls: bool = False, stopped_by_string: bool = False) -> str:
+    if tool_calls:
+        return "tool_calls"
+    if stopped_by_string or f == Finish.STOP:
+        return "stop"
+    if f == Finish.LENGTH:
+        return "length"
+    return "stop" if f is None else f.value
+
+
+def _usage(prompt: int, out: int, cached: int = 0) -> Dict[str, Any]:
+    return {"prompt_tokens": prompt, "completion_tokens": out, "total_tokens": prompt + out,
+            "prompt_tokens_details": {"cached_tokens": cached}}
+
+
+def _lp_entry(tok, lp: dict) -> Dict[str, Any]:
+    def one(tid, v):
+        b = tok.token_bytes(tid)
+        return {"token": b.decode("utf-8", errors="replace"), "logprob": max(v, -9999.0), "bytes": list(b)}
+    e = one(lp["token"], lp["logprob"])
+    e["top_logprobs"] = [one(t, v) for t, v in lp.get("top", [])]
+    return e
+
+
+def create_app(st: ServerState) -> FastAPI:
+    app = FastAPI(title="blaze_b200", version=__version__)
+
+    # ------------------------------------------------------------------ middleware: request id, CORS, auth, loading, admission
+    @app.middleware("http")
+    async def control(request: Request, call_next):
+        rid = request.headers.get("x-request-id") or uuid.uuid4().hex
+        path = request.url.path
+        cors = {"access-control-allow-origin": ",".join(st.svc.cors_origins), "access-control-allow-headers": "*",
+                "access-control-allow-methods": "GET,POST,DELETE,OPTIONS", "x-request-id": rid}
+        if request.method == "OPTIONS":
+            return PlainTextResponse("", headers=cors)
+        open_paths = ("/health", "/ping", "/version", "/metrics")
+        if st.svc.api_keys and path not in open_paths:
+            key = request.headers.get("x-api-key")
+            auth = request.headers.get("authorization", "")
+            if auth.lower().startswith("bearer "):
+                key = auth[7:].strip()
+            if not key or not any(hmac.compare_digest(key, k) for k in st.svc.api_keys):
+                r = _err(401, "invalid or missing API key", "authentication_error", code="invalid_api_key")
+                r.headers.update(cors)
+                return r
+        if not st.ready and path not in ("/ping", "/version", "/metrics"):
+            body = {"error": {"message": "model is loading", "type": "service_unavailable", "code": "model_loading"},
+                    "status": "loading", **log.Stage.status()}
+            return JSONResponse(body, status_code=503, headers={**cors, "retry-after": "5"})
+        heavy = request.method == "POST" and path.startswith("/v1/") and path not in ("/v1/messages/count_tokens",)
+        if heavy:
+            if st.shutting_down:
+                return _err(503, "server is shutting down", "service_unavailable")
+            if st.waiting >= st.svc.max_queue:
+                st.totals.errors += 1
+                return _err(429, "too many requests queued", "rate_limit_error", code="queue_full")
+            st.waiting += 1
+            try:
+                await st.sem.acquire()
+            finally:
+                st.waiting -= 1
+            st.totals.inflight += 1
+        t0 = time.monotonic()
+        released = False
+
+        def release():
+            nonlocal released
+            if heavy and not released:
+                released = True
+                st.sem.release()
+                st.totals.inflight -= 1
+                st.totals.e2e.observe(time.monotonic() - t0)
+        try:
+            resp = await call_next(request)
+        except Exception:
+            release()
+            raise
+        resp.headers.update(cors)
+        if isinstance(resp, StreamingResponse) or hasattr(resp, "body_iterator"):
+            inner = resp.body_iterator
+
+            async def wrapped():
+                try:
+                    async for chunk in inner:
+                        yield chunk
+                finally:
+                    release()
+            resp.body_iterator = wrapped()
+        else:
+            release()
+        return resp
+
+    async def _body(request: Request) -> Dict[str, Any]:
+        try:
+            b = await request.json()
+        except Exception:
+            raise RequestError("request body must be JSON")
+        if not isinstance(b, dict):
+            raise RequestError("request body must be a JSON object")
+        return b
+
+    @app.exception_handler(RequestError)
+    async def on_request_error(request: Request, e: RequestError):
+        st.totals.errors += 1
+        return _err(e.status, e.message, e.code if e.code != "invalid_request_error" else "invalid_request_error", e.param)
+
+    @app.exception_handler(ConstraintError)
+    async def on_constraint_error(request: Request, e: ConstraintError):
+        st.totals.errors += 1
+        return _err(400, str(e), param="response_format")
+
+    # ------------------------------------------------------------------ control plane
+    @app.get("/health")
+    async def health():
+        return {"status": "ok"}
+
+    @app.get("/ping")
+    async def ping():
+        return PlainTextResponse("pong")
+
+    @app.get("/version")
+    async def version():
+        return {"version": __version__}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [_model_card()]}
+
+    @app.get("/v1/models/{model_id:path}")
+    async def model(model_id: str):
+        if model_id != st.model_name:
+            return _err(404, f"model {model_id!r} not found", code="model_not_found")
+        return _model_card()
+
+    def _model_card():
+        return {"id": st.model_name, "object": "model", "created": int(st.started), "owned_by": "blaze_b200",
+                "max_model_len": st.max_len}
+
+    @app.get("/server_info")
+    @app.get("/get_server_info")
+    async def server_info():
+        llm = st.llm
+        s = llm.sched.stats
+        return {"version": __version__, "model": st.model_name, "uptime_s": round(time.time() - st.started, 1),
+                "max_model_len": st.max_len, "tp": llm.model.tp.world, "kv_dtype": llm.engine.ecfg.kv_dtype,
+                "kv_pages": llm.engine.num_pages, "kv_pages_free": llm.engine.pages.free_count,
+                "active": len(llm.sched.active), "waiting": len(llm.sched.waiting), "preempted": len(llm.sched.preempted),
+                "stats": vars(s), "prefix_cache": {"entries": len(llm.sched.cache.entries), "hits": llm.sched.cache.hits,
+                                                   "lookups": llm.sched.cache.lookups},
+                "weights": llm.model.weight_format.value, "kernels": llm.model.ops.name}
+
+    @app.get("/metrics")
+    async def metrics():
+        t = st.totals
+        lines = []
+
+        def counter(name, v, help_):
+            lines.append(f"# HELP {name} {help_}\n# TYPE {name} counter\n{name} {v}\n")
+
+        def gauge(name, v, help_):
+            lines.append(f"# HELP {name} {help_}\n# TYPE {name} gauge\n{name} {v}\n")
+        counter("blaze_requests_total", t.requests, "Requests accepted")
+        counter("blaze_request_errors_total", t.errors, "Requests rejected or failed")
+        counter("blaze_prompt_tokens_total", t.prompt_tokens, "Prompt tokens processed")
+        counter("blaze_cached_prompt_tokens_total", t.cached_tokens, "Prompt tokens served from the prefix cache")
+        counter("blaze_generation_tokens_total", t.output_tokens, "Tokens generated")
+        gauge("blaze_requests_in_flight", t.inflight, "Requests being served")
+        gauge("blaze_requests_waiting", st.waiting, "Requests waiting for admission")
+        if st.ready:
+            sc = st.llm.sched
+            gauge("blaze_sequences_active", len(sc.active), "Sequences in the running batch")
+            gauge("blaze_kv_pages_free", st.llm.engine.pages.free_count, "Free KV pages")
+            counter("blaze_preemptions_total", sc.stats.preemptions, "Recompute preemptions")
+            counter("blaze_draft_tokens_total", sc.stats.draft_tokens, "Speculative tokens proposed")
+            counter("blaze_accepted_draft_tokens_total", sc.stats.accepted_tokens, "Speculative tokens accepted")
+            lines.append(sc.ttft.render("blaze_time_to_first_token_seconds", "Time to first token"))
+            lines.append(sc.tpot.render("blaze_time_per_output_token_seconds", "Time per output token"))
+            lines.append(sc.step_ms.render("blaze_step_seconds", "Engine step time"))
+        lines.append(t.e2e.render("blaze_request_seconds", "End-to-end request time"))
+        return PlainTextResponse("".join(lines), media_type="text/plain; version=0.0.4")
+
+    # ------------------------------------------------------------------ tokenisation
+    @app.post("/tokenize")
+    async def tokenize(request: Request):
+        b = await _body(request)
+        if "messages" in b:
+            text = st.formatter.render(b["messages"], b.get("tools"), b.get("add_generation_prompt", True))
+        else:
+            text = b.get("prompt", b.get("text"))
+        if not isinstance(text, str):
+            raise RequestError("prompt must be a string", "prompt")
+        ids = st.tokenizer.encode(text, add_special_tokens=bool(b.get("add_special_tokens", False)))
+        return {"tokens": ids, "count": len(ids), "max_model_len": st.max_len}
+
+    @app.post("/detokenize")
+    async def detokenize(request: Request):
+        b = await _body(request)
+        ids = b.get("tokens")
+        if not isinstance(ids, list) or any(not isinstance(t, int) or t < 0 for t in ids):
+            raise RequestError("tokens must be a list of token ids", "tokens")
+        return {"prompt": st.tokenizer.decode(ids, skip_special_tokens=bool(b.get("skip_special_tokens", False)))}
+
+    # ------------------------------------------------------------------ helpers shared by the generation routes
+    def _check_model(b):
+        m = b.get("model")
+        if m is not None and m != st.model_name and m != "default":
+            raise RequestError(f"model {m!r} is not served here (serving {st.model_name!r})", "model", "model_not_found", 404)
+
+    def _check_len(n_prompt: int, params: SamplingParams):
+        if n_prompt == 0:
+            raise RequestError("prompt is empty", "prompt")
+        if n_prompt + 1 > st.max_len:
+            raise RequestError(f"prompt has {n_prompt} tokens; the context limit is {st.max_len}", "prompt",
+                               "context_length_exceeded")
+        params.max_tokens = max(1, min(params.max_tokens, st.max_len - n_prompt - 1))
+
+    def _think(b, enable_thinking) -> Optional[ThinkBudget]:
+        budget = thinking_budget_of(b)
+        if budget is None:
+            return None
+        o, c = st.tokenizer.token_id("<think>"), st.tokenizer.token_id("</think>")
+        if o is None or c is None:
+            return None
+        return ThinkBudget(budget, o, c, st.tokenizer.encode(THINK_CLOSING))
+
+    def _cache_point(prompt_ids: List[int]) -> Optional[int]:
+        """Prefix-cache boundary: the last ``<|im_start|>`` (``server.rs:926-933``)."""
+        ims = st.tokenizer.token_id("<|im_start|>")
+        if ims is None:
+            return None
+        for i in range(len(prompt_ids) - 1, 0, -1):
+            if prompt_ids[i] == ims:
+                return i
+        return None
+
+    def _account(g: Gen):
+        t = st.totals
+        t.requests += 1
+        t.prompt_tokens += g.prompt_tokens
+        t.cached_tokens += g.cached
+        t.output_tokens += g.n_out
+        if g.finish == Finish.ERROR:
+            t.errors += 1
+
+    def _sse(obj) -> bytes:
+        return ("data: " + json.dumps(obj, ensure_ascii=False, separators=(",", ":")) + "\n\n").encode()
+
+    # ------------------------------------------------------------------ /v1/chat/completions
+    async def _prepare_chat(b: Dict[str, Any]):
+        _check_model(b)
+        msgs = b.get("messages")
+        if not isinstance(msgs, list) or not msgs:
+            raise RequestError("messages must be a non-empty list", "messages")
+        tools = b.get("tools")
+        tool_choice = b.get("tool_choice", "auto" if tools else "none")
+        if tool_choice == "none":
+            tools_for_prompt = None
+        else:
+            tools_for_prompt = tools
+        ctk = b.get("chat_template_kwargs") or {}
+        enable_thinking = ctk.get("enable_thinking", b.get("enable_thinking"))
+        text = st.formatter.render(msgs, tools_for_prompt, True, enable_thinking)
+        ids = st.tokenizer.encode(text)
+        mm = None
+        if st.vision is not None:
+            from .media import collect_images
+            mm = await collect_images(msgs, st.vision)
+        params = sampling_of(b, st.svc, st.vocab)
+        _check_len(len(ids), params)
+        spec = grammar_of(b)
+        return ids, params, tools_for_prompt, enable_thinking, spec, mm
+
+    @app.post("/v1/chat/completions")
+    async def chat(request: Request):
+        b = await _body(request)
+        ids, params, tools, enable_thinking, spec, mm = await _prepare_chat(b)
+        stops = stop_strings_of(b)
+        include_stop = bool(b.get("include_stop_str_in_output", b.get("no_stop_trim", False)))
+        skip_special = bool(b.get("skip_special_tokens", True))
+        n = params.n
+        stream = bool(b.get("stream", False))
+        reasoning = st.svc.reasoning_parser is not None and enable_thinking is not False
+        created, cid = int(time.time()), "chatcmpl-" + uuid.uuid4().hex[:24]
+        want_lp = params.logprobs is not None
+
+        def make(i):
+            p = SamplingParams(**{**vars(params), "seed": None if params.seed is None else params.seed + i, "n": 1})
+            cons = st.grammars.constraint(spec) if spec else None
+            g = Gen(st, ids, p, cache_point=_cache_point(ids), constraint=cons, think=_think(b, enable_thinking), mm=mm)
+            proc = ChatResponseProcessor(st.tokenizer, stops, include_stop, skip_special, reasoning=reasoning,
+                                         tool_parser=get_tool_parser(st.svc.tool_call_parser, tools) if tools else None)
+            return g, proc
+        gens = [make(i) for i in range(n)]
+
+        if not stream:
+            choices = []
+            for i, (g, proc) in enumerate(gens):
+                lps = []
+                async for ev in g.events():
+                    d = proc.push(ev.tokens)
+                    if ev.logprobs:
+                        lps.extend(ev.logprobs)
+                    if d.stopped:
+                        g.abort()
+                        break
+                proc.finish()
+                _account(g)
+                if g.finish == Finish.ERROR:
+                    return _err(500, g.error or "generation failed", "server_error")
+                msg: Dict[str, Any] = {"role": "assistant", "content": proc.text or (None if proc.tool_calls else "")}
+                if proc.reasoning_text:
+                    msg["reasoning_content"] = proc.reasoning_text
+                if proc.tool_calls:
+                    msg["tool_calls"] = [{k: v for k, v in c.to_openai(j).items() if k != "index"} for j, c in enumerate(proc.tool_calls)]
+                ch = {"index": i, "message": msg, "finish_reason": finish_reason(g.finish, bool(proc.tool_calls), proc.stopped)}
+                if want_lp:
+                    ch["logprobs"] = {"content": [_lp_entry(st.tokenizer, l) for l in lps]}
+                choices.append(ch)
+            usage = _usage(len(ids), sum(g.n_out for g, _ in gens), gens[0][0].cached)
+            return {"id": cid, "object": "chat.completion", "created": created, "model": st.model_name, "choices": choices,
+                    "usage": usage}
+
+        include_usage = bool((b.get("stream_options") or {}).get("include_usage", False))
+
+        async def gen_stream():
+            base = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": st.model_name}
+            try:
+                for i, (g, proc) in enumerate(gens):
+                    yield _sse({**base, "choices": [{"index": i, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]})
+                    n_tools = 0
+
+                    def chunks_of(d, lps=None):
+                        nonlocal n_tools
+                        out = []
+                        delta: Dict[str, Any] = {}
+                        if d.reasoning:
+                            delta["reasoning_content"] = d.reasoning
+                        if d.content:
+                            delta["content"] = d.content
+                        if d.tool_calls:
+                            delta["tool_calls"] = [c.to_openai(n_tools + j) for j, c in enumerate(d.tool_calls)]
+                            n_tools += len(d.tool_calls)
+                        if delta:
+                            ch = {"index": i, "delta": delta, "finish_reason": None}
+                            if lps:
+                                ch["logprobs"] = {"content": [_lp_entry(st.tokenizer, l) for l in lps]}
+                            out.append(_sse({**base, "choices": [ch]}))
+                        return out
+                    async for ev in g.events():
+                        d = proc.push(ev.tokens)
+                        for c in chunks_of(d, ev.logprobs if want_lp else None):
+                            yield c
+                        if d.stopped:
+                            g.abort()
+                            break
+                    for c in chunks_of(proc.finish()):
+                        yield c
+                    _account(g)
+                    if g.finish == Finish.ERROR:
+                        yield _sse({"error": {"message": g.error or "generation failed", "type": "server_error"}})
+                    yield _sse({**base, "choices": [{"index": i, "delta": {}, "finish_reason":
+                                                     finish_reason(g.finish, bool(proc.tool_calls), proc.stopped)}]})
+                if include_usage:
+                    yield _sse({**base, "choices": [], "usage": _usage(len(ids), sum(g.n_out for g, _ in gens), gens[0][0].cached)})
+                yield b"data: [DONE]\n\n"
+            finally:
+                for g, _ in gens:
+                    if g.finish is None:
+                        g.abort()
+        return StreamingResponse(gen_stream(), media_type="text/event-stream")
+
+    # ------------------------------------------------------------------ /v1/completions
+    def _prompts_of(b) -> List[List[int]]:
+        p = b.get("prompt")
+        if isinstance(p, str):
+            return [st.tokenizer.encode(p)]
+        if isinstance(p, list) and p and all(isinstance(x, int) for x in p):
+            return [list(p)]
+        if isinstance(p, list) and p and all(isinstance(x, str) for x in p):
+            return [st.tokenizer.encode(x) for x in p]
+        if isinstance(p, list) and p and all(isinstance(x, list) and all(isinstance(t, int) for t in x) for x in p):
+            return [list(x) for x in p]
+        raise RequestError("prompt must be a string, a list of strings, a list of token ids or a list of those", "prompt")
+
+    @app.post("/v1/completions")
+    async def completions(request: Request):
+        b = await _body(request)
+        _check_model(b)
+        prompts = _prompts_of(b)
+        params = sampling_of(b, st.svc, st.vocab)
+        if len(prompts) * params.n > MAX_COMPLETIONS_PER_REQUEST:
+            raise RequestError(f"at most {MAX_COMPLETIONS_PER_REQUEST} generations per request", "n")
+        for p in prompts:
+            if any(t < 0 or t >= st.vocab for t in p):
+                raise RequestError("prompt token id outside the vocabulary", "prompt")
+            _check_len(len(p), params)
+        stops = stop_strings_of(b)
+        include_stop = bool(b.get("include_stop_str_in_output", False))
+        echo = bool(b.get("echo", False))
+        stream = bool(b.get("stream", False))
+        spec = grammar_of(b)
+        created, cid = int(time.time()), "cmpl-" + uuid.uuid4().hex[:24]
+        gens = []
+        for pi, p in enumerate(prompts):
+            for j in range(params.n):
+                sp = SamplingParams(**{**vars(params), "seed": None if params.seed is None else params.seed + j, "n": 1})
+                cons = st.grammars.constraint(spec) if spec else None
+                gens.append((Gen(st, p, sp, constraint=cons), ChatResponseProcessor(
+                    st.tokenizer, stops, include_stop, bool(b.get("skip_special_tokens", True))), p))
+
+        def lp_obj(lps):
+            toks = [st.tokenizer.token_bytes(l["token"]).decode("utf-8", errors="replace") for l in lps]
+            return {"tokens": toks, "token_logprobs": [max(l["logprob"], -9999.0) for l in lps],
+                    "top_logprobs": [{st.tokenizer.token_bytes(t).decode("utf-8", errors="replace"): max(v, -9999.0)
+                                      for t, v in l.get("top", [])} for l in lps]}
+
+        if not stream:
+            choices = []
+            for i, (g, proc, p) in enumerate(gens):
+                lps = []
+                async for ev in g.events():
+                    d = proc.push(ev.tokens)
+                    if ev.logprobs:
+                        lps.extend(ev.logprobs)
+                    if d.stopped:
+                        g.abort()
+                        break
+                proc.finish()
+                _account(g)
+                if g.finish == Finish.ERROR:
+                    return _err(500, g.error or "generation failed", "server_error")
+                text = (st.tokenizer.decode(p) if echo else "") + proc.text
+                ch = {"index": i, "text": text, "finish_reason": finish_reason(g.finish, False, proc.stopped), "logprobs": None}
+                if params.logprobs is not None:
+                    ch["logprobs"] = lp_obj(lps)
+                choices.append(ch)
+            return {"id": cid, "object": "text_completion", "created": created, "model": st.model_name, "choices": choices,
+                    "usage": _usage(sum(len(p) for _, _, p in gens), sum(g.n_out for g, _, _ in gens), 0)}
+
+        include_usage = bool((b.get("stream_options") or {}).get("include_usage", False))
+
+        async def gen_stream():
+            base = {"id": cid, "object": "text_completion", "created": created, "model": st.model_name}
+            try:
+                for i, (g, proc, p) in enumerate(gens):
+                    if echo:
+                        yield _sse({**base, "choices": [{"index": i, "text": st.tokenizer.decode(p), "finish_reason": None}]})
+                    async for ev in g.events():
+                        d = proc.push(ev.tokens)
+                        if d.content:
+                            yield _sse({**base, "choices": [{"index": i, "text": d.content, "finish_reason": None}]})
+                        if d.stopped:
+                            g.abort()
+                            break
+                    d = proc.finish()
+                    _account(g)
+                    yield _sse({**base, "choices": [{"index": i, "text": d.content,
+                                                     "finish_reason": finish_reason(g.finish, False, proc.stopped)}]})
+                if include_usage:
+                    yield _sse({**base, "choices": [], "usage": _usage(sum(len(p) for _, _, p in gens), sum(g.n_out for g, _, _ in gens))})
+                yield b"data: [DONE]\n\n"
+            finally:
+                for g, _, _ in gens:
+                    if g.finish is None:
+                        g.abort()
+        return StreamingResponse(gen_stream(), media_type="text/event-stream")
+
+    # ------------------------------------------------------------------ /v1/embeddings
+    @app.post("/v1/embeddings")
+    async def embeddings(request: Request):
+        b = await _body(request)
+        _check_model(b)
+        inp = b.get("input")
+        if isinstance(inp, str):
+            items = [st.tokenizer.encode(inp)]
+        elif isinstance(inp, list) and inp and all(isinstance(x, str) for x in inp):
+            items = [st.tokenizer.encode(x) for x in inp]
+        elif isinstance(inp, list) and inp and all(isinstance(x, int) for x in inp):
+            items = [inp]
+        elif isinstance(inp, list) and inp and all(isinstance(x, list) for x in inp):
+            items = inp
+        else:
+            raise RequestError("input must be a string, a list of strings or token ids", "input")
+        dims = b.get("dimensions")
+        if dims is not None and (not isinstance(dims, int) or dims < 1 or dims > st.llm.model.cfg.hidden_size):
+            raise RequestError("dimensions must be between 1 and the hidden size", "dimensions")
+        fmt = b.get("encoding_format", "float")
+        if fmt not in ("float", "base64"):
+            raise RequestError("encoding_format must be float or base64", "encoding_format")
+        data, total = [], 0
+        for i, ids in enumerate(items):
+            if not ids or len(ids) + 1 > st.max_len:
+                raise RequestError("input is empty or longer than the context limit", "input")
+            g = Gen(st, list(ids), SamplingParams(max_tokens=1), embed_only=True)
+            vec = None
+            async for ev in g.events():
+                if ev.hidden is not None:
+                    vec = ev.hidden
+            _account(g)
+            if vec is None:
+                return _err(500, g.error or "embedding failed", "server_error")
+            if dims:
+                vec = vec[:dims]
+            vec = vec / vec.norm().clamp_min(1e-12)
+            vals = vec.tolist()
+            emb = base64.b64encode(struct.pack(f"<{len(vals)}f", *vals)).decode() if fmt == "base64" else vals
+            data.append({"object": "embedding", "index": i, "embedding": emb})
+            total += len(ids)
+        return {"object": "list", "data": data, "model": st.model_name, "usage": {"prompt_tokens": total, "total_tokens": total}}
+
+    # ------------------------------------------------------------------ /v1/responses (OpenAI Responses API adapter)
+    def _responses_to_messages(b) -> List[Dict[str, Any]]:
+        msgs: List[Dict[str, Any]] = []
+        prev = b.get("previous_response_id")
+        if prev:
+            old = st.responses.get(prev)
+            if old is None:
+                raise RequestError(f"previous response {prev!r} not found", "previous_response_id", "not_found", 404)
+            msgs.extend(old["_messages"])
+        if b.get("instructions"):
+            msgs.insert(0, {"role": "system", "content": b["instructions"]})
+        inp = b.get("input")
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        elif isinstance(inp, list):
+            for it in inp:
+                t = it.get("type", "message")
+                if t == "message":
+                    msgs.append({"role": it.get("role", "user"), "content": it.get("content")})
+                elif t == "function_call":
+                    msgs.append({"role": "assistant", "content": None, "tool_calls": [
+                        {"id": it.get("call_id"), "type": "function", "function": {"name": it.get("name"), "arguments": it.get("arguments", "{}")}}]})
+                elif t == "function_call_output":
+                    msgs.append({"role": "tool", "tool_call_id": it.get("call_id"), "content": it.get("output", "")})
+        else:
+            raise RequestError("input must be a string or a list of items", "input")
+        return msgs
+
+    @app.post("/v1/responses")
+    async def responses(request: Request):
+        b = await _body(request)
+        _check_model(b)
+        msgs = _responses_to_messages(b)
+        tools = [{"type": "function", "function": {k: v for k, v in t.items() if k != "type"}} for t in (b.get("tools") or [])
+                 if t.get("type") == "function"] or None
+        cb = {**b, "messages": msgs, "tools": tools, "max_tokens": b.get("max_output_tokens")}
+        tf = (b.get("text") or {}).get("format")
+        if isinstance(tf, dict) and tf.get("type") in ("json_schema", "json_object"):
+            cb["response_format"] = {"type": tf["type"], "json_schema": {"schema": tf.get("schema", {})}}
+        ids, params, tools_p, enable_thinking, spec, mm = await _prepare_chat(cb)
+        rid, created = "resp_" + uuid.uuid4().hex[:24], int(time.time())
+        cons = st.grammars.constraint(spec) if spec else None
+        g = Gen(st, ids, params, cache_point=_cache_point(ids), constraint=cons, mm=mm)
+        proc = ChatResponseProcessor(st.tokenizer, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
+                                     tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None)
+        stream = bool(b.get("stream", False))
+
+        def build(status: str) -> Dict[str, Any]:
+            output = []
+            if proc.reasoning_text:
+                output.append({"type": "reasoning", "id": "rs_" + rid[5:], "summary": [{"type": "summary_text", "text": proc.reasoning_text}]})
+            if proc.text or not proc.tool_calls:
+                output.append({"type": "message", "id": "msg_" + rid[5:], "role": "assistant", "status": "completed",
+                               "content": [{"type": "output_text", "text": proc.text, "annotations": []}]})
+            for c in proc.tool_calls:
+                output.append({"type": "function_call", "id": "fc_" + c.id[5:], "call_id": c.id, "name": c.name,
+                               "arguments": c.arguments, "status": "completed"})
+            return {"id": rid, "object": "response", "created_at": created, "status": status, "model": st.model_name,
+                    "output": output, "output_text": proc.text,
+                    "incomplete_details": {"reason": "max_output_tokens"} if g.finish == Finish.LENGTH else None,
+                    "usage": {"input_tokens": len(ids), "output_tokens": g.n_out, "total_tokens": len(ids) + g.n_out,
+                              "input_tokens_details": {"cached_tokens": g.cached}},
+                    "previous_response_id": b.get("previous_response_id")}
+
+        def remember(obj):
+            if b.get("store", True):
+                kept = dict(obj)
+                am: Dict[str, Any] = {"role": "assistant", "content": proc.text}
+                if proc.tool_calls:
+                    am["tool_calls"] = [{k: v for k, v in c.to_openai().items() if k != "index"} for c in proc.tool_calls]
+                kept["_messages"] = [m for m in msgs if m.get("role") != "system"] + [am]
+                st.responses[rid] = kept
+                while len(st.responses) > RESPONSES_KEPT:
+                    st.responses.popitem(last=False)
+
+        if not stream:
+            async for ev in g.events():
+                proc.push(ev.tokens)
+            proc.finish()
+            _account(g)
+            if g.finish == Finish.ERROR:
+                return _err(500, g.error or "generation failed", "server_error")
+            obj = build("incomplete" if g.finish == Finish.LENGTH else "completed")
+            remember(obj)
+            return obj
+
+        async def gen_stream():
+            seq = 0
+
+            def evt(typ, **kw):
+                nonlocal seq
+                seq += 1
+                return (f"event: {typ}\n" + "data: " + json.dumps({"type": typ, "sequence_number": seq, **kw}, ensure_ascii=False) + "\n\n").encode()
+            yield evt("response.created", response={"id": rid, "object": "response", "status": "in_progress", "model": st.model_name})
+            try:
+                async for ev in g.events():
+                    d = proc.push(ev.tokens)
+                    if d.reasoning:
+                        yield evt("response.reasoning_summary_text.delta", delta=d.reasoning, item_id="rs_" + rid[5:])
+                    if d.content:
+                        yield evt("response.output_text.delta", delta=d.content, item_id="msg_" + rid[5:], output_index=0, content_index=0)
+                d = proc.finish()
+                if d.content:
+                    yield evt("response.output_text.delta", delta=d.content, item_id="msg_" + rid[5:], output_index=0, content_index=0)
+                _account(g)
+                obj = build("incomplete" if g.finish == Finish.LENGTH else "completed")
+                remember(obj)
+                yield evt("response.output_text.done", text=proc.text, item_id="msg_" + rid[5:])
+                yield evt("response.completed", response=obj)
+            finally:
+                if g.finish is None:
+                    g.abort()
+        return StreamingResponse(gen_stream(), media_type="text/event-stream")
+
+    @app.get("/v1/responses/{rid}")
+    async def get_response(rid: str):
+        obj = st.responses.get(rid)
+        if obj is None:
+            return _err(404, f"response {rid!r} not found", code="not_found")
+        return {k: v for k, v in obj.items() if not k.startswith("_")}
+
+    @app.delete("/v1/responses/{rid}")
+    async def delete_response(rid: str):
+        if st.responses.pop(rid, None) is None:
+            return _err(404, f"response {rid!r} not found", code="not_found")
+        return {"id": rid, "object": "response.deleted", "deleted": True}
+
+    # ------------------------------------------------------------------ /v1/messages (Anthropic Messages adapter)
+    def _anthropic_to_chat(b) -> Dict[str, Any]:
+        msgs: List[Dict[str, Any]] = []
+        sysm = b.get("system")
+        if isinstance(sysm, list):
+            sysm = "".join(p.get("text", "") for p in sysm if p.get("type") == "text")
+        if sysm:
+            msgs.append({"role": "system", "content": sysm})
+        for m in b.get("messages") or []:
+            role, content = m.get("role"), m.get("content")
+            if isinstance(content, str):
+                msgs.append({"role": role, "content": content})
+                continue
+            text, calls = [], []
+            for p in content or []:
+                t = p.get("type")
+                if t == "text":
+                    text.append(p.get("text", ""))
+                elif t == "tool_use":
+                    calls.append({"id": p.get("id"), "type": "function", "function": {"name": p.get("name"), "arguments": json.dumps(p.get("input", {}))}})
+                elif t == "tool_result":
+                    c = p.get("content")
+                    if isinstance(c, list):
+                        c = "".join(x.get("text", "") for x in c if x.get("type") == "text")
+                    msgs.append({"role": "tool", "tool_call_id": p.get("tool_use_id"), "content": c or ""})
+                elif t == "image":
+                    src = p.get("source", {})
+                    if src.get("type") == "base64":
+                        text.append("")
+                        msgs.append({"role": role, "content": [{"type": "image_url", "image_url": {"url": f"data:{src.get('media_type')};base64,{src.get('data')}"}}]})
+            if text or calls:
+                mm: Dict[str, Any] = {"role": role, "content": "".join(text)}
+                if calls:
+                    mm["tool_calls"] = calls
+                msgs.append(mm)
+        tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
+                                                   "parameters": t.get("input_schema", {})}} for t in (b.get("tools") or [])] or None
+        out = {**{k: v for k, v in b.items() if k in ("temperature", "top_p", "top_k", "stop_sequences", "stream", "model")},
+               "messages": msgs, "tools": tools, "max_tokens": b.get("max_tokens")}
+        if b.get("stop_sequences"):
+            out["stop"] = b["stop_sequences"]
+        th = b.get("thinking") or {}
+        if th.get("type") == "enabled":
+            out["enable_thinking"] = True
+            if th.get("budget_tokens"):
+                out["thinking_token_budget"] = th["budget_tokens"]
+        elif th.get("type") == "disabled":
+            out["enable_thinking"] = False
+        return out
+
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens(request: Request):
+        b = await _body(request)
+        cb = _anthropic_to_chat(b)
+        text = st.formatter.render(cb["messages"], cb.get("tools"), True)
+        return {"input_tokens": len(st.tokenizer.encode(text))}
+
+    @app.post("/v1/messages")
+    async def messages(request: Request):
+        b = await _body(request)
+        if not isinstance(b.get("max_tokens"), int):
+            raise RequestError("max_tokens is required", "max_tokens")
+        cb = _anthropic_to_chat(b)
+        ids, params, tools_p, enable_thinking, spec, mm = await _prepare_chat(cb)
+        stops = stop_strings_of(cb)
+        mid = "msg_" + uuid.uuid4().hex[:24]
+        g = Gen(st, ids, params, cache_point=_cache_point(ids), mm=mm)
+        proc = ChatResponseProcessor(st.tokenizer, stops, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
+                                     tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None)
+
+        def stop_reason():
+            if proc.tool_calls:
+                return "tool_use"
+            if proc.stopped:
+                return "stop_sequence"
+            return "max_tokens" if g.finish == Finish.LENGTH else "end_turn"
+
+        def blocks():
+            out = []
+            if proc.reasoning_text:
+                out.append({"type": "thinking", "thinking": proc.reasoning_text, "signature": ""})
+            if proc.text or not proc.tool_calls:
+                out.append({"type": "text", "text": proc.text})
+            for c in proc.tool_calls:
+                try:
+                    inp = json.loads(c.arguments)
+                except ValueError:
+                    inp = {"_raw": c.arguments}
+                out.append({"type": "tool_use", "id": c.id.replace("call_", "toolu_"), "name": c.name, "input": inp})
+            return out
+
+        if not b.get("stream"):
+            async for ev in g.events():
+                d = proc.push(ev.tokens)
+                if d.stopped:
+                    g.abort()
+                    break
+            proc.finish()
+            _account(g)
+            if g.finish == Finish.ERROR:
+                return JSONResponse({"type": "error", "error": {"type": "api_error", "message": g.error or "generation failed"}}, status_code=500)
+            return {"id": mid, "type": "message", "role": "assistant", "model": st.model_name, "content": blocks(),
+                    "stop_reason": stop_reason(), "stop_sequence": None,
+                    "usage": {"input_tokens": len(ids), "output_tokens": g.n_out, "cache_read_input_tokens": g.cached}}
+
+        async def gen_stream():
+            def evt(typ, **kw):
+                return (f"event: {typ}\n" + "data: " + json.dumps({"type": typ, **kw}, ensure_ascii=False) + "\n\n").encode()
+            yield evt("message_start", message={"id": mid, "type": "message", "role": "assistant", "model": st.model_name, "content": [],
+                                                "stop_reason": None, "usage": {"input_tokens": len(ids), "output_tokens": 0}})
+            idx, open_kind = -1, None
+
+            def open_block(kind):
+                nonlocal idx, open_kind
+                out = []
+                if open_kind is not None and open_kind != kind:
+                    out.append(evt("content_block_stop", index=idx))
+                    open_kind = None
+                if open_kind is None:
+                    idx += 1
+                    open_kind = kind
+                    cb_ = {"type": "thinking", "thinking": ""} if kind == "thinking" else {"type": "text", "text": ""}
+                    out.append(evt("content_block_start", index=idx, content_block=cb_))
+                return out
+            try:
+                async def emit(d):
+                    out = []
+                    if d.reasoning:
+                        out += open_block("thinking")
+                        out.append(evt("content_block_delta", index=idx, delta={"type": "thinking_delta", "thinking": d.reasoning}))
+                    if d.content:
+                        out += open_block("text")
+                        out.append(evt("content_block_delta", index=idx, delta={"type": "text_delta", "text": d.content}))
+                    return out
+                async for ev in g.events():
+                    d = proc.push(ev.tokens)
+                    for c in await emit(d):
+                        yield c
+                    if d.stopped:
+                        g.abort()
+                        break
+                for c in await emit(proc.finish()):
+                    yield c
+                nonlocal_idx = idx
+                if open_kind is not None:
+                    yield evt("content_block_stop", index=nonlocal_idx)
+                for c in proc.tool_calls:
+                    nonlocal_idx += 1
+                    yield evt("content_block_start", index=nonlocal_idx, content_block={"type": "tool_use", "id": c.id.replace("call_", "toolu_"),
+                                                                                      "name": c.name, "input": {}})
+                    yield evt("content_block_delta", index=nonlocal_idx, delta={"type": "input_json_delta", "partial_json": c.arguments})
+                    yield evt("content_block_stop", index=nonlocal_idx)
+                _account(g)
+                yield evt("message_delta", delta={"stop_reason": stop_reason(), "stop_sequence": None}, usage={"output_tokens": g.n_out})
+                yield evt("message_stop")
+            finally:
+                if g.finish is None:
+                    g.abort()
+        return StreamingResponse(gen_stream(), media_type="text/event-stream")
+
+    return app

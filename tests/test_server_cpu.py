@@ -1,0 +1,115 @@
+"""HTTP API on CPU with the tiny model and the byte tokenizer (in-process ASGI client)."""
+import json
+
+import pytest
+import torch
+from starlette.testclient import TestClient
+
+from blaze_b200.config import named_config
+from blaze_b200.llm import LLM
+from blaze_b200.server.app import ServerState, create_app
+from blaze_b200.service import ServiceArgs
+from blaze_b200.text import ByteTokenizer
+
+
+@pytest.fixture(scope="module")
+def client():
+    st = ServerState(ServiceArgs(api_keys=("secret",), default_max_tokens=8), "tiny")
+    app = create_app(st)
+    c = TestClient(app)
+    # while loading: 503 with the load stage
+    r = c.get("/v1/models", headers={"authorization": "Bearer secret"})
+    assert r.status_code == 503 and r.json()["error"]["code"] == "model_loading"
+    llm = LLM(named_config("tiny"), device="cpu", dtype=torch.float32, max_seqs=8, max_model_len=512, use_graphs=False)
+    st.attach(llm, ByteTokenizer(1024))
+    yield c
+    llm.sched.stop()
+
+
+H = {"authorization": "Bearer secret"}
+
+
+def test_control_plane(client):
+    assert client.get("/health").json() == {"status": "ok"}
+    assert client.get("/ping").text == "pong"
+    assert client.get("/v1/models").status_code == 401
+    assert client.get("/v1/models", headers={"x-api-key": "secret"}).json()["data"][0]["id"] == "tiny"
+    assert client.get("/v1/models/nope", headers=H).status_code == 404
+    info = client.get("/server_info", headers=H).json()
+    assert info["model"] == "tiny" and "stats" in info
+    m = client.get("/metrics").text
+    assert "blaze_requests_total" in m and "blaze_time_to_first_token_seconds_bucket" in m
+
+
+def test_tokenize_roundtrip(client):
+    r = client.post("/tokenize", json={"prompt": "héllo"}, headers=H).json()
+    assert r["count"] == len("héllo".encode())
+    assert client.post("/detokenize", json={"tokens": r["tokens"]}, headers=H).json()["prompt"] == "héllo"
+    r = client.post("/tokenize", json={"messages": [{"role": "user", "content": "hi"}]}, headers=H).json()
+    assert r["count"] > 4
+
+
+def test_completions_and_validation(client):
+    r = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 5, "temperature": 0}, headers=H)
+    assert r.status_code == 200
+    j = r.json()
+    assert j["usage"]["completion_tokens"] == 5 and j["choices"][0]["finish_reason"] == "length"
+    again = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 5, "temperature": 0}, headers=H).json()
+    assert again["choices"][0]["text"] == j["choices"][0]["text"]
+    ids = client.post("/v1/completions", json={"prompt": [97, 98, 99], "max_tokens": 5, "temperature": 0, "logprobs": 2}, headers=H).json()
+    assert ids["choices"][0]["text"] == j["choices"][0]["text"]
+    assert len(ids["choices"][0]["logprobs"]["token_logprobs"]) == 5
+    for bad in ({"prompt": "a", "temperature": -1}, {"prompt": "a", "top_p": 0}, {"prompt": "a", "n": 100},
+                {"prompt": "a", "logit_bias": {"5": 500}}, {"prompt": "a", "presence_penalty": 3}, {"prompt": 5},
+                {"prompt": "a", "samplers": "top_k,top_k"}, {"prompt": "a", "top_h": 0.5}, {"prompt": "a", "model": "other"},
+                {"prompt": "a", "min_tokens": 9, "max_tokens": 3}, {"prompt": "x" * 600}):
+        rr = client.post("/v1/completions", json=bad, headers=H)
+        assert rr.status_code in (400, 404), (bad, rr.text)
+        assert "error" in rr.json()
+    two = client.post("/v1/completions", json={"prompt": ["ab", "cd"], "n": 2, "max_tokens": 3, "seed": 1}, headers=H).json()
+    assert len(two["choices"]) == 4
+
+
+def test_chat_and_stream(client):
+    body = {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0}
+    r = client.post("/v1/chat/completions", json=body, headers=H).json()
+    assert r["object"] == "chat.completion" and r["choices"][0]["message"]["role"] == "assistant"
+    assert r["usage"]["completion_tokens"] <= 6
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True, "stream_options": {"include_usage": True}}, headers=H) as s:
+        lines = [l for l in s.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[6:]) for l in lines[:-1]]
+    text = "".join(c["choices"][0]["delta"].get("content") or "" for c in chunks if c["choices"])
+    assert text == (r["choices"][0]["message"]["content"] or "")
+    assert chunks[-1]["usage"]["completion_tokens"] == r["usage"]["completion_tokens"]
+    assert any(c["choices"] and c["choices"][0]["finish_reason"] for c in chunks)
+
+
+def test_stop_string_and_choice_constraint(client):
+    free = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 8, "temperature": 0}, headers=H).json()["choices"][0]["text"]
+    if len(free) >= 3:
+        stop = free[2]
+        cut = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 8, "temperature": 0, "stop": stop}, headers=H).json()
+        assert cut["choices"][0]["finish_reason"] == "stop" and stop not in cut["choices"][0]["text"]
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "pick"}], "max_tokens": 8,
+                                                  "guided_choice": ["yes", "no"]}, headers=H).json()
+    assert r["choices"][0]["message"]["content"] in ("yes", "no")
+
+
+def test_embeddings_responses_messages(client):
+    e = client.post("/v1/embeddings", json={"input": ["hello", "world"], "dimensions": 16}, headers=H).json()
+    assert len(e["data"]) == 2 and len(e["data"][0]["embedding"]) == 16
+    assert abs(sum(x * x for x in e["data"][0]["embedding"]) - 1.0) < 1e-3
+    r = client.post("/v1/responses", json={"input": "hi", "max_output_tokens": 4, "temperature": 0}, headers=H).json()
+    assert r["object"] == "response" and r["status"] in ("completed", "incomplete")
+    assert client.get(f"/v1/responses/{r['id']}", headers=H).json()["id"] == r["id"]
+    r2 = client.post("/v1/responses", json={"input": "more", "previous_response_id": r["id"], "max_output_tokens": 4}, headers=H)
+    assert r2.status_code == 200 and r2.json()["usage"]["input_tokens"] > r["usage"]["input_tokens"]
+    assert client.post("/v1/responses", json={"input": "x", "previous_response_id": "resp_missing"}, headers=H).status_code == 404
+    m = client.post("/v1/messages", json={"max_tokens": 5, "messages": [{"role": "user", "content": "hi"}], "system": "be brief"}, headers=H).json()
+    assert m["type"] == "message" and m["stop_reason"] in ("max_tokens", "end_turn") and m["content"][0]["type"] == "text"
+    ct = client.post("/v1/messages/count_tokens", json={"messages": [{"role": "user", "content": "hi"}]}, headers=H).json()
+    assert ct["input_tokens"] > 0
+    with client.stream("POST", "/v1/messages", json={"max_tokens": 4, "stream": True, "messages": [{"role": "user", "content": "hi"}]}, headers=H) as s:
+        ev = [l for l in s.iter_lines() if l.startswith("event: ")]
+    assert ev[0] == "event: message_start" and ev[-1] == "event: message_stop"
