@@ -83,6 +83,14 @@ def main():
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
 
+    if os.environ.get("BLAZE_BENCH_DEBUG"):
+        import faulthandler
+        faulthandler.dump_traceback_later(float(os.environ["BLAZE_BENCH_DEBUG"]), repeat=True, file=sys.stderr)
+
+    def note(msg):
+        if os.environ.get("BLAZE_BENCH_DEBUG"):
+            print(f"[bench r{os.environ.get('RANK', '0')} +{time.time() - T0:.1f}s] {msg}", file=sys.stderr, flush=True)
+    T0 = time.time()
     import torch
     from blaze_b200.config import named_config
     from blaze_b200.llm import LLM
@@ -127,6 +135,7 @@ def main():
     llm = LLM(cfg, weight_format=args.weights, device=dev, tp=tp, kv_cache_dtype="fp8", kv_tokens=kv_tokens, max_seqs=B,
               max_model_len=max_len, chunk=4096, enable_prefix_caching=False, use_graphs=not args.no_graphs, seed=1,
               max_step_tokens=B + 4096)
+    note("model built")
     eng = llm.engine
     ops = llm.model.ops
     torch.cuda.synchronize()
@@ -155,6 +164,7 @@ def main():
             last[j] = t
     ttft_ev[1].record()
     sync_all()
+    note("prefill done")
     prefill_ms = ttft_ev[0].elapsed_time(ttft_ev[1])
     cur = [last[j] for j in range(B)]
 
@@ -164,6 +174,7 @@ def main():
 
     for _ in range(max(W, 3)):
         cur = decode_step(cur).tolist()
+    note("warmup done")
     l0 = ops.launches
     clk_path = os.path.join(tempfile.gettempdir(), f"blaze_clocks_{rank}.csv")
     sampler = clocks_sampler(clk_path, local) if rank == 0 else None
@@ -176,6 +187,7 @@ def main():
         out = decode_step(cur)
         cur = out.tolist()
     e1.record()
+    note("timed steps issued")
     if args.cuda_profiler:
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()

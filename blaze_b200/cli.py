@@ -1,0 +1,222 @@
+"""Command line: engine flags, service flags, ``--config`` files and presets, and the sub-commands.
+
+Mirrors the reference's ``crates/blaze/src/main.rs`` (``EngineArgs`` :24-176, subcommands :364-551: serve, generate,
+inspect, score, self-spec, stage-worker, vision-check) and ``crates/blaze/src/cli.rs`` (flat JSON ``--config`` where
+explicit flags win and unknown keys fail :76; presets fast / balanced / quality :42-49).
+
+    python -m blaze_b200 serve --model /path/to/checkpoint --tp 8 --kv-cache-dtype fp8 --spec-method mtp
+    python -m blaze_b200 generate --model qwen3-8b --weights nvfp4 --prompt-ids 1,2,3 --max-tokens 16
+    python -m blaze_b200 inspect --model /path/to/checkpoint
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from typing import Any, Dict, List, Optional, Sequence
+
+PRESETS: Dict[str, Dict[str, Any]] = {
+    # favour latency: shallow speculation, small prefill chunks
+    "fast": {"chunk": 1024, "max_verify": 4, "draft_tree_depth": 3, "prompt_cache_slots": 2},
+    "balanced": {"chunk": 2048, "max_verify": 8, "draft_tree_depth": 4, "prompt_cache_slots": 4},
+    # favour throughput and cache reuse
+    "quality": {"chunk": 4096, "max_verify": 8, "draft_tree_depth": 6, "prompt_cache_slots": 8, "kv_cache_dtype": "bf16"},
+}
+
+
+def engine_parser(p: argparse.ArgumentParser) -> None:
+    g = p.add_argument_group("engine")
+    g.add_argument("--model", required=False, help="checkpoint directory, or a named shape (tiny, qwen3-8b, …) for random init")
+    g.add_argument("--weights", default=None, help="format for random-init shapes: dense | nvfp4 | mxfp8 | fp8_block | fp8")
+    g.add_argument("--config", default=None, help="flat JSON file of flag values (explicit flags win; unknown keys fail)")
+    g.add_argument("--preset", default=None, choices=sorted(PRESETS))
+    g.add_argument("--max-model-len", type=int, default=None)
+    g.add_argument("--kv-tokens", default="auto", help="KV capacity in tokens, or 'auto' (size from free memory)")
+    g.add_argument("--kv-cache-dtype", default=None, choices=["fp8", "bf16", "fp32", "nvfp4", "nvfp4_4over6", "auto"])
+    g.add_argument("--kv-host", action="store_true", help="keep cold KV pages in pinned host memory")
+    g.add_argument("--chunk", type=int, default=None, help="prefill tokens per iteration")
+    g.add_argument("--vram-reserve", type=float, default=2.0, help="GiB kept free when sizing the KV pool")
+    g.add_argument("--max-seqs", type=int, default=None)
+    g.add_argument("--disable-prefix-caching", action="store_true")
+    g.add_argument("--prompt-cache-slots", type=int, default=None)
+    g.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (one process per GPU)")
+    g.add_argument("--pp", type=int, default=1, help="pipeline stages")
+    g.add_argument("--pp-chunk", type=int, default=512)
+    g.add_argument("--ep", action="store_true", help="shard MoE experts across the tensor-parallel ranks")
+    g.add_argument("--yarn-factor", type=float, default=None)
+    g.add_argument("--draft-model", default=None, help="EAGLE / DFlash drafter checkpoint")
+    g.add_argument("--spec-method", default=None, choices=["none", "ngram", "suffix", "mtp", "eagle", "dflash"])
+    g.add_argument("--max-verify", type=int, default=None)
+    g.add_argument("--suffix-assist", action="store_true")
+    g.add_argument("--mtp-window", type=int, default=8192)
+    g.add_argument("--mtp-head-vocab", type=int, default=0)
+    g.add_argument("--mtp-head-cands", type=int, default=32768)
+    g.add_argument("--draft-tree-width", type=int, default=1)
+    g.add_argument("--draft-tree-depth", type=int, default=None)
+    g.add_argument("--no-graphs", action="store_true")
+    g.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--device", default=None)
+
+
+def service_parser(p: argparse.ArgumentParser) -> None:
+    g = p.add_argument_group("service")
+    g.add_argument("--host", default="127.0.0.1")
+    g.add_argument("--port", type=int, default=8000)
+    g.add_argument("--api-key", action="append", default=None)
+    g.add_argument("--served-model-name", default=None)
+    g.add_argument("--max-queue", type=int, default=1024)
+    g.add_argument("--max-concurrency", type=int, default=512)
+    g.add_argument("--request-timeout", type=float, default=600.0)
+    g.add_argument("--default-max-tokens", type=int, default=512)
+    g.add_argument("--log-level", default="info")
+    g.add_argument("--log-format", default="text", choices=["text", "json"])
+    g.add_argument("--profile-prefill", action="store_true")
+    g.add_argument("--generation-config", default=None)
+    g.add_argument("--samplers", default=None, help="default sampler stage order, e.g. penalties,temperature,top_k,top_p")
+    g.add_argument("--top-nsigma", type=float, default=None)
+    g.add_argument("--top-h", type=float, default=None)
+    g.add_argument("--tool-call-parser", default="hermes")
+    g.add_argument("--reasoning-parser", default="qwen3")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="blaze_b200")
+    sub = ap.add_subparsers(dest="command", required=True)
+    s = sub.add_parser("serve", help="start the HTTP server")
+    engine_parser(s)
+    service_parser(s)
+    g = sub.add_parser("generate", help="generate from token ids or text and print the result")
+    engine_parser(g)
+    g.add_argument("--prompt", default=None)
+    g.add_argument("--prompt-ids", default=None, help="comma-separated token ids")
+    g.add_argument("--max-tokens", type=int, default=32)
+    g.add_argument("--temperature", type=float, default=0.0)
+    i = sub.add_parser("inspect", help="list checkpoint tensors and their formats")
+    i.add_argument("--model", required=True)
+    sc = sub.add_parser("score", help="per-token log-probabilities of a token sequence")
+    engine_parser(sc)
+    sc.add_argument("--prompt-ids", required=True)
+    w = sub.add_parser("stage-worker", help="serve one pipeline stage for a remote coordinator")
+    engine_parser(w)
+    w.add_argument("--listen", default="127.0.0.1:7000")
+    w.add_argument("--stage", type=int, default=1)
+    v = sub.add_parser("vision-check", help="compare the CUDA vision tower with the CPU tower on an image")
+    v.add_argument("--model", required=True)
+    v.add_argument("--image", required=True)
+    return ap
+
+
+def resolve(argv: Sequence[str]) -> argparse.Namespace:
+    """Parse ``argv``; layer preset < config file < explicit flags (``cli.rs:76``)."""
+    ap = build_parser()
+    ns = ap.parse_args(list(argv))
+    explicit = set()
+    for a in argv:
+        if a.startswith("--"):
+            explicit.add(a[2:].split("=")[0].replace("-", "_"))
+    layered: Dict[str, Any] = {}
+    if getattr(ns, "preset", None):
+        layered.update(PRESETS[ns.preset])
+    if getattr(ns, "config", None):
+        with open(ns.config) as f:
+            cfg = json.load(f)
+        if not isinstance(cfg, dict):
+            raise SystemExit("--config must hold a JSON object")
+        for k, v in cfg.items():
+            key = k.replace("-", "_")
+            if not hasattr(ns, key):
+                raise SystemExit(f"--config: unknown key {k!r}")
+            layered[key] = v
+    for k, v in layered.items():
+        if k not in explicit and hasattr(ns, k):
+            setattr(ns, k, v)
+    return ns
+
+
+def spec_defaults(ns: argparse.Namespace) -> None:
+    """``--spec-method mtp`` implies its window / candidate settings; PP with a drafter is refused (``main.rs:203-254``)."""
+    if getattr(ns, "spec_method", None) in (None, "none") and getattr(ns, "draft_model", None):
+        ns.spec_method = "eagle"
+    if getattr(ns, "spec_method", None) in ("mtp", "eagle", "dflash") and getattr(ns, "pp", 1) > 1:
+        raise SystemExit("pipeline parallelism cannot be combined with a drafter")
+    if getattr(ns, "max_verify", None) is None:
+        ns.max_verify = 8
+    if getattr(ns, "draft_tree_depth", None) is None:
+        ns.draft_tree_depth = 4
+
+
+def build_llm(ns: argparse.Namespace):
+    import torch
+    from .llm import LLM
+    from .models.qwen3 import TPInfo
+    from .parallel.tp import TPGroup
+    spec_defaults(ns)
+    device = ns.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if ns.tp > 1 and world != ns.tp:
+        raise SystemExit(f"--tp {ns.tp}: launch one process per GPU, e.g. python -m torch.distributed.run "
+                         f"--nproc-per-node {ns.tp} --master-addr 127.0.0.1 -m blaze_b200 …")
+    group = None
+    if world > 1:
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        if device.startswith("cuda"):
+            torch.cuda.set_device(local)
+            device = f"cuda:{local}"
+        group = TPGroup.from_env(device)
+    tp = TPInfo(group.rank, group.world, group, ep=ns.ep) if group else TPInfo()
+    kv = ns.kv_cache_dtype or "auto"
+    if kv.startswith("nvfp4"):
+        kv = "fp8"     # 4-bit KV pools are not built; FP8 pages are the compact format here
+    kv_tokens = 0 if str(ns.kv_tokens) == "auto" else int(ns.kv_tokens)
+    llm = LLM(ns.model or "tiny", weight_format=ns.weights or "dense", device=device, tp=tp, kv_cache_dtype=kv,
+              kv_tokens=kv_tokens, max_seqs=ns.max_seqs or 256, max_model_len=ns.max_model_len or 4096,
+              chunk=ns.chunk or 2048, enable_prefix_caching=not ns.disable_prefix_caching,
+              cache_slots=ns.prompt_cache_slots or 4, use_graphs=not ns.no_graphs,
+              spec_method=ns.spec_method or "none", max_draft=min(ns.max_verify - 1, 8), seed=ns.seed)
+    if group is not None and ns.comm == "fused" and device.startswith("cuda"):
+        from .parallel.symm import SymmAllReduce
+        group.fused = SymmAllReduce.create(group, device, max_rows=(ns.chunk or 2048) + (ns.max_seqs or 256) + 64,
+                                           hidden=llm.model.cfg.hidden_size)
+    return llm
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    ns = resolve(argv)
+    from . import log
+    if hasattr(ns, "log_level"):
+        log.configure(level=ns.log_level, fmt=ns.log_format)
+    if ns.command == "inspect":
+        from .inspect import inspect_checkpoint
+        return inspect_checkpoint(ns.model)
+    if ns.command == "serve":
+        from .server.run import serve
+        return serve(ns)
+    if ns.command == "generate":
+        from .sampler import SamplingParams
+        from .text import load_tokenizer
+        llm = build_llm(ns)
+        tok = load_tokenizer(ns.model if ns.model and os.path.isdir(ns.model) else None, llm.model.cfg.vocab_size)
+        ids = [int(x) for x in ns.prompt_ids.split(",")] if ns.prompt_ids else tok.encode(ns.prompt or "hello")
+        out = llm.generate([ids], SamplingParams(temperature=ns.temperature, max_tokens=ns.max_tokens))[0]
+        print(json.dumps({"token_ids": out.token_ids, "text": tok.decode(out.token_ids), "finish_reason": out.finish_reason}))
+        return 0
+    if ns.command == "score":
+        import torch
+        llm = build_llm(ns)
+        ids = [int(x) for x in ns.prompt_ids.split(",")]
+        s = llm.engine.open_from()
+        logits = llm.engine.forward(llm.engine.plan([(s, ids, len(ids))]), "logits")
+        lp = torch.log_softmax(logits.float(), -1)
+        scores = [float(lp[i, ids[i + 1]]) for i in range(len(ids) - 1)]
+        print(json.dumps({"logprobs": scores, "sum": sum(scores)}))
+        return 0
+    if ns.command == "stage-worker":
+        from .remote import serve_stage
+        return serve_stage(ns)
+    if ns.command == "vision-check":
+        from .models.vision import check_reference
+        return check_reference(ns.model, ns.image)
+    return 2

@@ -1,0 +1,26 @@
+"""``inspect``: list a checkpoint's linear modules with their storage format, shapes and byte sizes
+(reference: ``crates/blaze/src/inspect.rs``)."""
+from __future__ import annotations
+
+import collections
+
+from .quant import resolve_format
+from .weights import Checkpoint
+
+
+def inspect_checkpoint(model_dir: str, out=print) -> int:
+    ck = Checkpoint.open(model_dir)
+    meta = ck.meta()
+    mods = sorted({n.rsplit(".", 1)[0] for n in meta if n.endswith((".weight", ".weight_packed"))})
+    by_fmt = collections.Counter()
+    out(f"{model_dir}: {len(meta)} tensors, {ck.total_bytes() / 2**30:.2f} GiB, text prefix {ck.text_prefix()!r}")
+    for m in mods:
+        try:
+            fmt = resolve_format(meta, m).value
+        except KeyError:
+            fmt = "?"
+        w = meta.get(f"{m}.weight") or meta.get(f"{m}.weight_packed")
+        by_fmt[fmt] += 1
+        out(f"  {m:70s} {fmt:12s} {w[0]:8s} {tuple(w[1])}")
+    out("formats: " + ", ".join(f"{k}={v}" for k, v in sorted(by_fmt.items())))
+    return 0

@@ -16,6 +16,7 @@ The reference's transport for the same two operations is pinned host memory (``k
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -67,7 +68,7 @@ class SymmArena:
 
 
 class SymmAllReduce:
-    def __init__(self, group, device, max_rows: int, hidden: int, use_multicast: bool = True):
+    def __init__(self, group, device, max_rows: int, hidden: int, use_multicast: bool = True, timeout_ms: int = 0):
         self.group, self.device = group, torch.device(device)
         self.lib = kernels()
         lib = self.lib
@@ -96,7 +97,8 @@ class SymmAllReduce:
         self.epoch = torch.zeros(int(lib.blz_comm_epoch_bytes()) // 4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         group.barrier()
-        self.comm = lib.blz_comm_create(group.rank, group.world, _arr(a.peers(self.off_pad)), VP(self.epoch.data_ptr()), 1)
+        self.comm = lib.blz_comm_create(group.rank, group.world, _arr(a.peers(self.off_pad)), VP(self.epoch.data_ptr()),
+                                        int(timeout_ms or os.environ.get("BLAZE_COMM_TIMEOUT_MS", "10000")))
         if not self.comm:
             raise RuntimeError("blz_comm_create failed")
         self.use_mc = bool(use_multicast and a.mc)

@@ -1,0 +1,63 @@
+"""``serve``: bind the port first (503 ``model_loading`` with the load stage while the model loads), load the model on a
+worker thread, then attach it; graceful shutdown on SIGINT / SIGTERM (reference: ``crates/blaze/src/main.rs:889-1078``,
+``server.rs:177-245`` early listener, ``server.rs:340-351`` shutdown)."""
+from __future__ import annotations
+
+import os
+import threading
+
+from .. import log
+from ..service import ServiceArgs
+from .app import ServerState, create_app
+
+
+def service_args_of(ns) -> ServiceArgs:
+    return ServiceArgs(host=ns.host, port=ns.port, api_keys=tuple(ns.api_key or ()), served_model_name=ns.served_model_name,
+                       max_queue=ns.max_queue, max_concurrency=ns.max_concurrency, request_timeout_s=ns.request_timeout,
+                       default_max_tokens=ns.default_max_tokens, log_level=ns.log_level, log_format=ns.log_format,
+                       profile_prefill=ns.profile_prefill, generation_config=ns.generation_config, samplers=ns.samplers,
+                       top_nsigma=ns.top_nsigma, top_h=ns.top_h, tool_call_parser=ns.tool_call_parser,
+                       reasoning_parser=ns.reasoning_parser or None)
+
+
+def serve(ns) -> int:
+    import uvicorn
+    from ..cli import build_llm
+    from ..text import load_tokenizer
+    svc = service_args_of(ns)
+    name = os.path.basename(os.path.normpath(ns.model)) if ns.model else "blaze"
+    st = ServerState(svc, name)
+    app = create_app(st)
+    rank = int(os.environ.get("RANK", "0"))
+
+    def load():
+        try:
+            llm = build_llm(ns)
+            tok = load_tokenizer(ns.model if ns.model and os.path.isdir(ns.model) else None, llm.model.cfg.vocab_size)
+            vision = None
+            if llm.model.cfg.vision_config and ns.model and os.path.isdir(ns.model):
+                from ..models.vision import Vision
+                with log.Stage("vision"):
+                    vision = Vision.load(ns.model, llm.device)
+            st.attach(llm, tok, vision)
+            log.info("server.ready", model=st.model_name, port=svc.port)
+        except Exception as e:
+            log.error("server.load_failed", error=repr(e))
+            os._exit(101)
+
+    if rank != 0:
+        # non-zero ranks execute the step plans that rank 0 broadcasts
+        llm = build_llm(ns)
+        from ..parallel.worker import follow
+        return follow(llm)
+    threading.Thread(target=load, name="blaze-load", daemon=True).start()
+    config = uvicorn.Config(app, host=svc.host, port=svc.port, log_level="warning", timeout_graceful_shutdown=10)
+    server = uvicorn.Server(config)
+
+    @app.on_event("shutdown")
+    async def _shutdown():
+        st.shutting_down = True
+        if st.llm is not None:
+            st.llm.sched.stop()
+    server.run()
+    return 0

@@ -33,6 +33,7 @@ struct CommParams {
   void* mc_sf;
   void* mc_rs;
   uint32_t* epoch;                // [kMaxBlocks] local, monotonically increasing
+  long long spin_limit;           // clock ticks a flag wait may take before it gives up
   int rank, world;
   int* status;
 };
@@ -47,13 +48,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 
 // Block-level barrier across ranks: block b of every rank meets block b of every other rank.
+// Every kernel uses two barrier epochs (entry = base + 1, exit = base + 2) and advances the stored epoch by two at
+// entry, so a rank that gave up on a wait stays in step with its peers on the next kernel.
 // Returns false (after recording kErrFlagTimeout) when a peer does not show up within the spin limit.
-__device__ __forceinline__ bool rank_barrier(const CommParams& c, int* ok_smem) {
+__device__ __forceinline__ bool rank_barrier(const CommParams& c, int* ok_smem, int phase) {
   __syncthreads();
   __shared__ uint32_t s_epoch;
   if (threadIdx.x == 0) {
-    s_epoch = c.epoch[blockIdx.x] + 1;
-    c.epoch[blockIdx.x] = s_epoch;
+    if (phase == 0) {
+      s_epoch = c.epoch[blockIdx.x] + 1;
+      c.epoch[blockIdx.x] = s_epoch + 1;
+    } else {
+      s_epoch = c.epoch[blockIdx.x];
+    }
     *ok_smem = 1;
   }
   __threadfence_system();
@@ -65,7 +72,7 @@ __device__ __forceinline__ bool rank_barrier(const CommParams& c, int* ok_smem) 
     const uint32_t* mine = c.peer_pad[c.rank] + (size_t)blockIdx.x * kMaxWorld + peer;
     const long long t0 = clock64();
     while ((int32_t)(ld_acquire_sys(mine) - e) < 0) {
-      if (clock64() - t0 > kSpinLimit) {
+      if (clock64() - t0 > c.spin_limit) {
         atomicCAS(c.status, kOk, kErrFlagTimeout);
         *ok_smem = 0;
         break;
@@ -145,7 +152,7 @@ __device__ __forceinline__ void bcast4(const CommParams& c, void* const* peers, 
 template <bool MC>
 __global__ void __launch_bounds__(512) allreduce_kernel(CommParams c, size_t n16) {
   __shared__ int ok;
-  if (!rank_barrier(c, &ok)) return;
+  if (!rank_barrier(c, &ok, 0)) return;
   const size_t per = (n16 + c.world - 1) / c.world;
   const size_t lo = (size_t)c.rank * per, hi = min(n16, lo + per);
   for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
@@ -154,7 +161,7 @@ __global__ void __launch_bounds__(512) allreduce_kernel(CommParams c, size_t n16
     uint4 o = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
     bcast16<MC>(c, c.peer_out, c.mc_out, i * 16, o);
   }
-  rank_barrier(c, &ok);
+  rank_barrier(c, &ok, 1);
 }
 
 // ------------------------------------------------------------------------------------------ all-reduce + residual + RMSNorm (+quant)
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(1024) allreduce_norm_kernel(CommParams c, __nv
   __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(dyn);
   __shared__ float red[32];
   __shared__ int ok;
-  if (!rank_barrier(c, &ok)) return;
+  if (!rank_barrier(c, &ok, 0)) return;
   const int lo = c.rank * rows_per, hi = min(T, lo + rows_per);
   for (int t = lo + blockIdx.x; t < hi; t += gridDim.x) {
     __nv_bfloat16* rr = residual ? residual + (size_t)(t - lo) * H : nullptr;
@@ -299,7 +306,7 @@ __global__ void __launch_bounds__(1024) allreduce_norm_kernel(CommParams c, __nv
     }
     __syncthreads();
   }
-  rank_barrier(c, &ok);
+  rank_barrier(c, &ok, 1);
 }
 
 }  // namespace blz
@@ -311,7 +318,8 @@ struct BlzComm {
   CommParams p;
 };
 
-BLZ_API void* blz_comm_create(int rank, int world, void* const* pads, void* epoch, int use_status) {
+// timeout_ms: how long a rank waits for its peers inside a kernel before it records an error and moves on.
+BLZ_API void* blz_comm_create(int rank, int world, void* const* pads, void* epoch, int timeout_ms) {
   if (world < 1 || world > kMaxWorld) return nullptr;
   BlzComm* c = new BlzComm();
   memset(&c->p, 0, sizeof(c->p));
@@ -319,7 +327,7 @@ BLZ_API void* blz_comm_create(int rank, int world, void* const* pads, void* epoc
   for (int r = 0; r < world; ++r) c->p.peer_pad[r] = reinterpret_cast<uint32_t*>(pads[r]);
   c->p.epoch = reinterpret_cast<uint32_t*>(epoch);
   c->p.status = status_word();
-  (void)use_status;
+  c->p.spin_limit = (long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1900000LL;
   return c;
 }
 BLZ_API void blz_comm_destroy(void* h) { delete reinterpret_cast<BlzComm*>(h); }
