@@ -503,13 +503,14 @@ class Model:
             return ops.linear(M.down, a), tp
         hd = h.dense if hasattr(h, "dense") and h.dense is not None else h
         logits = ops.linear(M.router, hd, out_dtype=torch.float32)
-        w, ids = ops.router_topk(logits, M.top_k, M.renorm)
-        if self.tp.ep and tp:
-            y = self.tp.group.moe_ep(ops, hd, w, ids, M.experts)          # complete rows on every rank
-            routed_partial = False
+        if ops.is_cuda:
+            w, ids = ops.router_topk(logits, M.top_k, M.renorm, M.experts.first, M.experts.count)
         else:
-            y = ops.moe(hd, w, ids, M.experts)
-            routed_partial = tp
+            w, ids = ops.router_topk(logits, M.top_k, M.renorm)
+        # Tokens are replicated across the ranks, so expert parallelism needs no dispatch: every rank runs the routed
+        # pairs whose expert it holds and the partial outputs are summed by the reduce + norm that follows.
+        y = ops.moe(hd, w, ids, M.experts)
+        routed_partial = tp
         if M.shared is not None:
             s = ops.linear(M.shared.down, ops.silu_mul(ops.linear(M.shared.gate_up, hd), quant_for=M.shared.down))
             if tp and not routed_partial:

@@ -43,7 +43,7 @@ class CudaOps:
         lib = self.lib
         lib.blz_gemm_tc.restype = _c.c_int
         lib.blz_gemm_tc.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
-                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
+                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, VP]
         lib.blz_embed.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_rmsnorm.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int, VP]
         lib.blz_swiglu.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
@@ -59,6 +59,16 @@ class CudaOps:
         lib.blz_add_sigmoid_scaled.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
         lib.blz_gather_rows.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, VP]
         lib.blz_argmax.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, _c.c_longlong, _c.c_int, VP]
+        lib.blz_moe_route.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_moe_plan.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_moe_scatter.argtypes = [_c.c_int, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                        _c.c_int, VP]
+        lib.blz_moe_combine.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
+        self._route_counts = None
+        lib.blz_gdn_conv.argtypes = [VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_gdn_recurrent.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
+                                          _c.c_int, _c.c_int, VP]
+        lib.blz_gated_rmsnorm.argtypes = [VP, VP, _c.c_longlong, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_float, _c.c_int, VP]
         lib.blz_status_take.restype = _c.c_int
 
     # ------------------------------------------------------------------ plumbing
@@ -192,7 +202,7 @@ class CudaOps:
         ldb = w.shape[1] * w.element_size()
         self._check(self.lib.blz_gemm_tc(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), out.stride(0), M, lin.N, lin.K,
                                          _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
-                                         int(f32), bn, max_ctas, self._stream()), f"gemm kind {kind}")
+                                         int(f32), bn, max_ctas, VP(0), 0, self._stream()), f"gemm kind {kind}")
         return out
 
     def silu_mul(self, gu, quant_for: Optional[Linear] = None):
@@ -305,13 +315,132 @@ class CudaOps:
                                         self._stream()), "argmax")
         return (out, vals) if want_values else out
 
-    # ------------------------------------------------------------------ not yet on the device: MoE routing, GDN
-    def router_topk(self, logits, k, renorm=True):
-        from . import ref
-        return ref.router_topk(logits, k, renorm)
+    # ------------------------------------------------------------------ mixture of experts
+    def router_topk(self, logits, k, renorm=True, first: int = 0, local_n: int = -1):
+        """Softmax → top-k → renormalise on the device; also counts the routed rows of each local expert."""
+        T, E = logits.shape
+        local_n = E if local_n < 0 else local_n
+        w = torch.empty(T, k, dtype=torch.float32, device=self.device)
+        ids = torch.empty(T, k, dtype=torch.int32, device=self.device)
+        counts = torch.empty(max(local_n, 1), dtype=torch.int32, device=self.device)
+        self._check(self.lib.blz_moe_route(_ptr(logits.contiguous()), _ptr(w), _ptr(ids), _ptr(counts), T, E, k, int(renorm),
+                                           first, local_n, self._stream()), "moe_route")
+        self._route_counts = (counts, first, local_n)
+        return w, ids
+
+    def pack_experts(self, ex):
+        """Stack the local experts' weights into two grouped-GEMM operands (gate_up and down)."""
+        if ex.cuda_pack is not None:
+            return ex.cuda_pack
+
+        def stack(lins):
+            pk0 = self.pack(lins[0])
+            kind = pk0["kind"]
+            w = torch.cat([self.pack(l)["w"] for l in lins])
+            alpha = torch.cat([self.pack(l)["alpha"] for l in lins]) if pk0["alpha"] is not None else None
+            sf = None
+            if kind in (1, 2):
+                l0 = lins[0]
+                if l0.N % 128:
+                    raise CudaError("grouped GEMM needs expert output dims that are multiples of 128")
+                per = l0.K // (16 if kind == 1 else 32)
+                if kind == 1:
+                    raw = torch.cat([l.sf.to(self.device).view(torch.uint8) for l in lins])
+                else:
+                    raw = torch.cat([quant.unswizzle_sf_128x4(self.pack(l)["sf"], (l.N + 255) // 256 * 256, per)[:l.N] for l in lins])
+                rows = (raw.shape[0] + 255) // 256 * 256
+                buf = torch.zeros(rows, per, dtype=torch.uint8, device=self.device)
+                buf[:raw.shape[0]] = raw
+                sf = quant.swizzle_sf_128x4(buf)
+            for l in lins:
+                l.cuda_pack = None          # the stacked copy replaces the per-expert ones
+            return {"kind": kind, "w": w.contiguous(), "sf": sf, "alpha": alpha, "N": lins[0].N, "K": lins[0].K,
+                    "fmt": lins[0].fmt, "act_quant": lins[0].act_quant}
+        ex.cuda_pack = {"gate_up": stack(ex.gate_up), "down": stack(ex.down)}
+        return ex.cuda_pack
+
+    def _grouped_gemm(self, pk, a, M_pad, tile_expert, n_exp, out):
+        kind = pk["kind"]
+        if kind in (1, 2):
+            data, sfa, rs = a.data, a.sf, a.row_scale
+            lda = data.shape[1]
+        else:
+            data, sfa, rs = a, None, None
+            lda = a.shape[1] * 2
+        w = pk["w"]
+        self._check(self.lib.blz_gemm_tc(kind, _ptr(data), lda, _ptr(w), w.shape[1] * w.element_size(), _ptr(out), out.stride(0),
+                                         M_pad, pk["N"], pk["K"], _ptr(rs), _ptr(pk["alpha"]), VP(0), _ptr(sfa), _ptr(pk["sf"]),
+                                         0, 128, 0, _ptr(tile_expert), n_exp, self._stream()), "grouped gemm")
+        return out
 
     def moe(self, x, topk_w, topk_id, experts):
-        raise CudaError("MoE expert path: use parallel.ep / ops.moe_cuda once built")
+        """Routed experts held by this rank: scatter rows by expert → grouped gate_up GEMM → SwiGLU → grouped down GEMM →
+        weighted combine.  ``x`` is bf16 ``[T, H]``.  Under expert parallelism the result is a partial sum."""
+        pk = self.pack_experts(experts)
+        gu, dn = pk["gate_up"], pk["down"]
+        T, H = x.shape
+        k = topk_id.shape[1]
+        n_exp, first = experts.count, experts.first
+        counts, cf, cn = getattr(self, "_route_counts", (None, -1, -1))
+        if counts is None or cf != first or cn != n_exp:
+            # routing was computed elsewhere: rebuild the histogram of local experts
+            le = (topk_id.long() - first).flatten()
+            ok = (le >= 0) & (le < n_exp)
+            counts = torch.bincount(le[ok], minlength=n_exp).to(torch.int32)
+        max_tiles = (T * k + 127) // 128 + n_exp
+        M_pad = max_tiles * 128
+        dev = self.device
+        offsets = torch.empty(n_exp, dtype=torch.int32, device=dev)
+        fill = torch.empty(n_exp, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+        row_map = torch.empty(T, k, dtype=torch.int32, device=dev)
+        self._check(self.lib.blz_moe_plan(_ptr(counts), _ptr(offsets), _ptr(fill), _ptr(tile_expert), n_exp, max_tiles,
+                                          self._stream()), "moe_plan")
+        mode = 1 if (gu["fmt"] == Format.NVFP4 and gu["act_quant"]) else (2 if gu["kind"] == 2 else 0)
+        if mode:
+            proxy = Linear(gu["fmt"], gu["N"], gu["K"])
+            proxy.act_quant = True
+            xq = self.quantize_rows(x.contiguous(), proxy)
+            a = self._alloc_qact(Format.NVFP4 if mode == 1 else Format.MXFP8, M_pad, H)
+            self._check(self.lib.blz_moe_scatter(mode, _ptr(xq.data), _ptr(xq.sf), _ptr(xq.row_scale), _ptr(a.data), _ptr(a.sf),
+                                                 _ptr(a.row_scale), _ptr(topk_id), _ptr(offsets), _ptr(fill), _ptr(row_map), T, H, k,
+                                                 first, n_exp, self._stream()), "moe_scatter")
+        else:
+            a = torch.empty(M_pad, H, dtype=torch.bfloat16, device=dev)
+            self._check(self.lib.blz_moe_scatter(0, _ptr(x.contiguous()), VP(0), VP(0), _ptr(a), VP(0), VP(0), _ptr(topk_id),
+                                                 _ptr(offsets), _ptr(fill), _ptr(row_map), T, H, k, first, n_exp, self._stream()),
+                        "moe_scatter")
+        g = torch.empty(M_pad, gu["N"], dtype=torch.bfloat16, device=dev)
+        self._grouped_gemm(gu, a, M_pad, tile_expert, n_exp, g)
+        proxy_d = Linear(dn["fmt"], dn["N"], dn["K"])
+        proxy_d.act_quant = dn["act_quant"]
+        act = self.silu_mul(g, quant_for=proxy_d if dn["kind"] in (1, 2) else None)
+        y = torch.empty(M_pad, dn["N"], dtype=torch.bfloat16, device=dev)
+        self._grouped_gemm(dn, act, M_pad, tile_expert, n_exp, y)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        self._check(self.lib.blz_moe_combine(_ptr(y), _ptr(topk_w.contiguous()), _ptr(row_map), _ptr(out), T, H, k, self._stream()),
+                    "moe_combine")
+        self._route_counts = None
+        return out
 
-    def gdn(self, *a, **k):
-        raise CudaError("GDN kernel not built")
+    # ------------------------------------------------------------------ Gated DeltaNet
+    def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx):
+        """Causal conv + SiLU → gated delta rule (gates computed in the kernel) → gated RMSNorm."""
+        cfg = model.cfg
+        dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        hk, hv = gdn.k_heads, gdn.v_heads
+        T = mixed_qkv.shape[0]
+        C = 2 * hk * dk + hv * dv
+        B = batch.slots.numel()
+        conv = torch.empty(T, C, dtype=torch.bfloat16, device=self.device)
+        self._check(self.lib.blz_gdn_conv(_ptr(mixed_qkv), mixed_qkv.stride(0), _ptr(conv), _ptr(kv.conv_state[layer_idx]),
+                                          _ptr(gdn.conv_w), _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), B, C,
+                                          gdn.conv_w.shape[1], self._stream()), "gdn_conv")
+        o = torch.empty(T, hv, dv, dtype=torch.bfloat16, device=self.device)
+        self._check(self.lib.blz_gdn_recurrent(_ptr(conv), _ptr(a), _ptr(b), a.stride(0), _ptr(gdn.A_log), _ptr(gdn.dt_bias),
+                                               _ptr(kv.rec_state[layer_idx]), _ptr(o), _ptr(batch.slots), _ptr(batch.q_start),
+                                               _ptr(batch.ctx_len), B, hk, hv, dk, dv, self._stream()), "gdn_recurrent")
+        y = torch.empty(T, hv * dv, dtype=torch.bfloat16, device=self.device)
+        self._check(self.lib.blz_gated_rmsnorm(_ptr(o), _ptr(z), z.stride(0), _ptr(gdn.norm_w), _ptr(y), T, hv, dv,
+                                               cfg.rms_norm_eps, 0, self._stream()), "gated_rmsnorm")
+        return y

@@ -165,7 +165,9 @@ def router_topk(logits: torch.Tensor, k: int, renorm: bool = True):
 def moe_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_id: torch.Tensor, expert_fn, num_experts: int):
     """Reference mixture: ``out[t] = sum_j w[t,j] * expert_fn(e_j, x[t])`` evaluated per expert."""
     out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
-    for e in range(num_experts):
+    first = getattr(getattr(expert_fn, "__self__", None), "first", 0)
+    count = getattr(getattr(expert_fn, "__self__", None), "count", num_experts)
+    for e in range(first, first + count):
         tok, slot = (topk_id == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue

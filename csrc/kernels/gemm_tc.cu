@@ -29,6 +29,7 @@ struct GemmParams {
   const uint8_t* sfa;        // scale factors of A, 128x4-tiled (kinds 1, 2)
   const uint8_t* sfb;
   int sfa_col_tiles;         // number of 4-column tiles per 128-row tile in sfa / sfb
+  const int* tile_expert;    // grouped GEMM: expert of every 128-row M tile (-1 = skip); B / alpha / sfb rows are offset by expert * N
   int* status;
 };
 
@@ -104,6 +105,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0; uint32_t ph = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         const int mt = t % tiles_m, nt = t / tiles_m;
+        const int ex = p.tile_expert ? p.tile_expert[mt] : 0;
+        if (ex < 0) continue;
+        const int brow = ex * p.N + nt * BN;                  // first B row of this tile
         for (int kt = 0; kt < k_tiles; ++kt) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status)) goto producer_done;
           uint32_t bytes = Cfg::A_BYTES + Cfg::B_BYTES;
@@ -115,13 +119,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(&full[s], bytes);
           const int kc = (KIND == 0) ? kt * BK : kt * 128;   // coordinate in map elements (bf16 or bytes)
           tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, kc, mt * BM, &full[s]);
-          tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, nt * BN, &full[s]);
+          tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, brow, &full[s]);
           if constexpr (Cfg::SF_ATOMS > 0) {
             const size_t a_off = ((size_t)mt * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
             bulk_load(sSFA + s * Cfg::SFA_BYTES, p.sfa + a_off, atoms * 512, &full[s]);
 #pragma unroll
             for (int h = 0; h < BN / 128; ++h) {
-              const size_t b_off = ((size_t)(nt * (BN / 128) + h) * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
+              const size_t b_off = ((size_t)(brow / 128 + h) * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
               bulk_load(sSFB + s * Cfg::SFB_BYTES + h * Cfg::SFA_BYTES, p.sfb + b_off, atoms * 512, &full[s]);
             }
           }
@@ -135,9 +139,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (elect_one()) {
       int s = 0; uint32_t ph = 0;
       int it = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        if (p.tile_expert && p.tile_expert[t % tiles_m] < 0) continue;
         const int ab = it % ACC;
         const uint32_t aph = (it / ACC) & 1;
+        ++it;
         if (!mbar_wait(&acc_empty[ab], aph ^ 1, abort_flag, p.status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + ab * BN;
@@ -187,10 +193,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                       // TMEM lane quadrant this warp may read
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       const int mt = t % tiles_m, nt = t / tiles_m;
+      const int ex = p.tile_expert ? p.tile_expert[mt] : 0;
+      if (ex < 0) continue;
       const int ab = it % ACC;
       const uint32_t aph = (it / ACC) & 1;
+      ++it;
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, p.status)) break;
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
@@ -202,8 +211,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
       for (int i = lane; i < BN; i += 32) {
         const int col = nt * BN + i;
-        sal[i] = (p.alpha && col < p.N) ? __ldg(p.alpha + col) : 1.0f;
-        sbi[i] = (p.bias && col < p.N) ? bf2f(p.bias[col]) : 0.0f;
+        sal[i] = (p.alpha && col < p.N) ? __ldg(p.alpha + (size_t)ex * p.N + col) : 1.0f;
+        sbi[i] = (p.bias && col < p.N) ? bf2f(p.bias[(size_t)ex * p.N + col]) : 0.0f;
       }
       __syncwarp();
 #pragma unroll 1
@@ -300,15 +309,17 @@ static cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
 // lda / ldb in BYTES.  out_f32: C is fp32, else bf16; ldc in elements.  bn: 128 or 256 (0 = choose).
 BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
                         int M, int N, int K, const float* row_scale, const float* alpha, const void* bias,
-                        const void* sfa, const void* sfb, int out_f32, int bn, int max_ctas, cudaStream_t stream) {
+                        const void* sfa, const void* sfb, int out_f32, int bn, int max_ctas, const int* tile_expert,
+                        int num_experts, cudaStream_t stream) {
   using namespace blz;
   if (M <= 0 || N <= 0 || K <= 0 || kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
   const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
   if (K % kmma) return (int)cudaErrorInvalidValue;
   if ((kind == 1 || kind == 2) && (!sfa || !sfb)) return (int)cudaErrorInvalidValue;
   if (bn == 0) {
+    // block-scaled kinds keep two accumulator buffers only at BN = 128; the dense kinds have room for BN = 256
     const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
-    bn = (tiles128 >= 2L * sm_count() && N % 256 == 0) ? 256 : 128;
+    bn = ((kind == 0 || kind == 3) && tiles128 >= 2L * sm_count() && N % 256 == 0) ? 256 : 128;
   }
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.row_scale = row_scale; p.alpha = alpha;
@@ -316,17 +327,20 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   p.sfa = reinterpret_cast<const uint8_t*>(sfa); p.sfb = reinterpret_cast<const uint8_t*>(sfb);
   p.sfa_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
   p.status = status_word();
+  p.tile_expert = tile_expert;
+  const uint64_t b_rows = (uint64_t)N * (tile_expert ? (num_experts > 0 ? num_experts : 1) : 1);
+  if (tile_expert && N % bn) return (int)cudaErrorInvalidValue;
   CUtensorMap tmA, tmB;
   cudaError_t e;
   if (kind == 0) {
     e = encode_tmap(&tmA, A, 2, K, M, lda, 64, 128, 3);
     if (e != cudaSuccess) return (int)e;
-    e = encode_tmap(&tmB, B, 2, K, N, ldb, 64, bn, 3);
+    e = encode_tmap(&tmB, B, 2, K, b_rows, ldb, 64, bn, 3);
   } else {
     const uint64_t kbytes = kind == 1 ? K / 2 : K;
     e = encode_tmap(&tmA, A, 1, kbytes, M, lda, 128, 128, 3);
     if (e != cudaSuccess) return (int)e;
-    e = encode_tmap(&tmB, B, 1, kbytes, N, ldb, 128, bn, 3);
+    e = encode_tmap(&tmB, B, 1, kbytes, b_rows, ldb, 128, bn, 3);
   }
   if (e != cudaSuccess) return (int)e;
 #define BLZ_GEMM_CASE(KD, BNV)                                                                        \

@@ -226,3 +226,102 @@ def test_attention_split_kv(ops):
     o, want = _attention_case(ops, 8, 2, [2000, 1500], [1, 1])
     mx, rel = _report("attention split-kv", o, want)
     assert rel < 0.06
+
+
+def _experts(n, H, I, fmt, seed):
+    from blaze_b200.models.qwen3 import Experts
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    ex = Experts()
+    ex.num_experts, ex.first, ex.count = n, 0, n
+    for _ in range(n):
+        ex.gate_up.append(Linear.from_dense(torch.randn(2 * I, H, generator=g, device=DEV) * 0.05, fmt, segments=[I, I]))
+        ex.down.append(Linear.from_dense(torch.randn(H, I, generator=g, device=DEV) * 0.05, fmt))
+    return ex
+
+
+@pytest.mark.parametrize("fmt,T,E,k", [(Format.DENSE, 37, 8, 2), (Format.NVFP4, 200, 16, 4), (Format.MXFP8, 64, 8, 8)])
+def test_moe_routed_experts(ops, fmt, T, E, k):
+    H, I = 512, 256
+    ex = _experts(E, H, I, fmt, 21)
+    g = torch.Generator(device=DEV).manual_seed(22)
+    x = torch.randn(T, H, generator=g, device=DEV).bfloat16()
+    logits = torch.randn(T, E, generator=g, device=DEV)
+    w, ids = ops.router_topk(logits, k, True, 0, E)
+    wr, idr = ref.router_topk(logits, k, True)
+    assert torch.equal(ids.cpu(), idr.cpu())
+    assert torch.allclose(w, wr, atol=1e-5)
+    y = ops.moe(x, w, ids, ex)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    want = ref.moe_forward(x, wr, idr, ex.forward_one, E)
+    mx, rel = _report(f"moe {fmt.value} T{T} E{E} k{k}", y, want)
+    assert rel < (0.02 if fmt == Format.DENSE else 0.08)
+
+
+def test_moe_expert_parallel_partials_sum_to_full(ops):
+    H, I, E, k, T = 512, 256, 8, 2, 50
+    full = _experts(E, H, I, Format.DENSE, 31)
+    g = torch.Generator(device=DEV).manual_seed(32)
+    x = torch.randn(T, H, generator=g, device=DEV).bfloat16()
+    logits = torch.randn(T, E, generator=g, device=DEV)
+    from blaze_b200.models.qwen3 import Experts
+    total = torch.zeros(T, H, device=DEV)
+    for r in range(2):
+        part = Experts()
+        part.num_experts, part.first, part.count = E, r * 4, 4
+        part.gate_up, part.down = full.gate_up[r * 4:r * 4 + 4], full.down[r * 4:r * 4 + 4]
+        w, ids = ops.router_topk(logits, k, True, part.first, part.count)
+        total += ops.moe(x, w, ids, part).float()
+    wr, idr = ref.router_topk(logits, k, True)
+    want = ref.moe_forward(x, wr, idr, full.forward_one, E)
+    mx, rel = _report("moe expert-parallel partial sums", total, want)
+    assert rel < 0.03
+
+
+def test_gdn_layer(ops):
+    from blaze_b200.batch import SeqChunk, build_batch
+    from blaze_b200.config import named_config
+    from blaze_b200.ops.ref_ops import RefOps
+    cfg = named_config("qwen3-next-80b-a3b")
+    cfg.linear_num_key_heads, cfg.linear_num_value_heads = 2, 4
+    cfg.num_layers, cfg.layer_types = 1, ["linear_attention"]
+    hk, hv, dk, dv = 2, 4, 128, 128
+    g = torch.Generator(device=DEV).manual_seed(41)
+
+    class G:
+        pass
+    gd = G()
+    gd.k_heads, gd.v_heads = hk, hv
+    C = 2 * hk * dk + hv * dv
+    gd.conv_w = (torch.randn(C, 4, generator=g, device=DEV) * 0.3).bfloat16()
+    gd.A_log = torch.log(torch.linspace(1, 4, hv, device=DEV))
+    gd.dt_bias = torch.randn(hv, generator=g, device=DEV) * 0.1
+    gd.norm_w = (1 + 0.1 * torch.randn(dv, generator=g, device=DEV)).bfloat16()
+
+    class M:
+        pass
+    m = M()
+    m.cfg, m.gdn_chunked = cfg, False
+    outs = {}
+    for name, o in (("cuda", ops), ("ref", RefOps())):
+        kv = KVCache(cfg, 4, 4, 8, "bf16", DEV, "logical")
+        gi = torch.Generator(device=DEV).manual_seed(42)
+        res = []
+        for step, lens in enumerate(([40, 7], [1, 1], [3, 1])):       # prefill, decode, verify-like rows
+            chunks = []
+            for b, n in enumerate(lens):
+                done = sum(l[b] for l in ([40, 7], [1, 1], [3, 1])[:step])
+                chunks.append(SeqChunk(b, [0] * n, done))
+            batch = build_batch(chunks, kv.block_table_host, DEV)
+            T = batch.num_rows
+            mixed = torch.randn(T, C, generator=gi, device=DEV).bfloat16()
+            z = torch.randn(T, hv * dv, generator=gi, device=DEV).bfloat16()
+            bb = torch.randn(T, hv, generator=gi, device=DEV).bfloat16()
+            aa = torch.randn(T, hv, generator=gi, device=DEV).bfloat16()
+            res.append(o.gdn(mixed, z, bb, aa, gd, m, batch, kv, 0).float())
+        outs[name] = (torch.cat(res), kv.rec_state[0].clone(), kv.conv_state[0].float().clone())
+    torch.cuda.synchronize()
+    mx, rel = _report("gdn layer output", outs["cuda"][0], outs["ref"][0])
+    assert rel < 0.03
+    assert (outs["cuda"][1] - outs["ref"][1]).abs().max().item() < 0.05
+    assert (outs["cuda"][2] - outs["ref"][2]).abs().max().item() < 0.02
