@@ -260,6 +260,8 @@ class Engine:
             return m.final_hidden(x, rows)
         if mode == "both":
             return m.head(x, rows), x
+        if mode == "greedy_hidden":
+            return m.greedy(x, rows), x
         raise ValueError(mode)
 
     # ------------------------------------------------------------------ CUDA graphs for decode steps

@@ -400,10 +400,10 @@ class Model:
         the residual add and the next RMSNorm — one fused peer-memory kernel when the group has one
         (``reduce_norm`` in ``crates/blaze/src/model.rs:2555``), else all-reduce followed by the norm kernel."""
         ops, cfg = self.ops, self.cfg
-        if self.is_first_stage:
-            x = ops.embed(self.embed, batch.tokens)
-        else:
+        if hidden_in is not None:
             x = hidden_in
+        else:
+            x = ops.embed(self.embed, batch.tokens)
         fused = self._fused()
         rope = ops.rope_tables(self, batch)
         residual = None          # full rows, or this rank's row shard on the fused path

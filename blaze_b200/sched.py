@@ -490,6 +490,17 @@ class Scheduler:
             pts.append(end)
         a.snap_points = sorted(set(p for p in pts if p > cached))
         self.active.append(a)
+        if self.drafter is not None and hasattr(self.drafter, "open"):
+            self.drafter.close(req.request_id)
+            self.drafter.open(req.request_id)
+            if cached:
+                # the drafter has no state for a cached prefix: it starts drafting from what it sees from here on
+                self.drafter.states[req.request_id].fed = cached
+                try:
+                    self.drafter.engine.reserve(self.drafter.states[req.request_id].seq, cached)
+                    self.drafter.states[req.request_id].seq.length = cached
+                except Exception:
+                    pass
         return True
 
     # ================================================================== preemption
@@ -504,6 +515,8 @@ class Scheduler:
         a.computed = 0
         a._started = False
         self.preempted.append(a)
+        if self.drafter is not None and hasattr(self.drafter, "close"):
+            self.drafter.close(a.req.request_id)
         self.stats.preemptions += 1
         log.debug("sched.preempt", request_id=a.req.request_id, tokens=len(a.tokens))
         return True
@@ -569,12 +582,17 @@ class Scheduler:
                           for a, _, w, _ in plan)
         mode = "none" if not want_any else ("both" if any(a.req.embed_only for a, _, w, _ in plan if w) else
                                             ("logits" if need_logits else "greedy"))
+        if self.drafter is not None and mode in ("greedy", "logits"):
+            mode = "greedy_hidden" if mode == "greedy" else "both"      # the drafter reads the target's hidden rows
         out = eng.forward(chunks, mode)
         # ---- consume results
         row = 0
         rows_total = sum(len(t) for _, t, _, _ in plan)
         host_tokens = None
         logits = hidden = None
+        if mode == "greedy_hidden":
+            out, hidden = out
+            mode = "greedy"
         if mode == "greedy":
             host_tokens = out.tolist()
             eng.d2h_bytes += out.numel() * out.element_size()
@@ -582,7 +600,11 @@ class Scheduler:
             logits = out
         elif mode == "both":
             logits, hidden = out
+        row0 = 0
+        seen: List[Tuple[Active, int, int, int]] = []      # (request, first row, first position, rows) for the drafter
         for a, toks, want, draft in plan:
+            seen.append((a, row0, a.computed, len(toks)))
+            row0 += len(toks)
             a.computed += len(toks)
             a._started = True
             if a.computed in a.snap_points and a.computed <= a.n_prompt:
@@ -624,6 +646,13 @@ class Scheduler:
                 a.computed = a.computed - len(toks) + 1 + accepted
                 eng.truncate(a.seq, a.computed)
             self._append(a, new, lps)
+        if self.drafter is not None and hidden is not None:
+            for a, r0, p0, n in seen:
+                if a.seq is None or a.req.embed_only:
+                    continue
+                keep = min(n, a.computed - p0, len(a.tokens) - 1 - p0)     # rows whose KV survived and whose next token is known
+                if keep > 0:
+                    self.drafter.observe(a.req.request_id, hidden[r0:r0 + keep], a.tokens[p0 + 1:p0 + 1 + keep], p0)
         dt = (time.monotonic() - t0) * 1e3
         self.cost.observe(rows_total, dt)
         self.step_ms.observe(dt / 1e3)
@@ -733,6 +762,8 @@ class Scheduler:
     def _retire(self, a: Active, why: Finish, error: Optional[str] = None, silent: bool = False) -> None:
         if a in self.active:
             self.active.remove(a)
+        if self.drafter is not None and hasattr(self.drafter, "close"):
+            self.drafter.close(a.req.request_id)
         if a.seq is not None:
             if why in (Finish.STOP, Finish.LENGTH) and not a.req.embed_only:
                 # keep the finished conversation for follow-up turns

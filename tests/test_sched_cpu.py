@@ -109,3 +109,16 @@ def test_spec_cost_and_ngram_helpers():
             cost.observe(rows, 10.0)
     k = cost.choose([acc, bad], [4, 4])
     assert k[0] >= 3
+
+
+def test_mtp_drafter_keeps_outputs_exact():
+    from blaze_b200.models.drafter import ChainDrafter
+    ps = _prompts(3, 24, seed=9)
+    want = [o.token_ids for o in _llm().generate(ps, SamplingParams(temperature=0.0, max_tokens=14))]
+    llm = _llm(spec_method="mtp")
+    d = ChainDrafter.random_init(llm.model, seed=3, max_seqs=8, max_model_len=256, kv_dtype="fp32")
+    llm.sched.drafter = d
+    got = llm.generate(ps, SamplingParams(temperature=0.0, max_tokens=14))
+    assert [o.token_ids for o in got] == want
+    assert llm.sched.stats.draft_tokens > 0 and d.proposed > 0
+    assert not d.states and d.engine.pages.free_count == d.engine.num_pages - 1
