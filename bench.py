@@ -248,7 +248,12 @@ def main():
             line["invalid"] = invalid
         print(json.dumps(line))
     if group is not None:
-        torch.distributed.destroy_process_group()
+        # captured graphs hold NCCL work; tearing the process group down under them can block, so leave together instead
+        sys.stdout.flush()
+        sys.stderr.flush()
+        eng._graphs.clear()
+        sync_all()
+        os._exit(0)
     return 0
 
 
