@@ -1,0 +1,104 @@
+"""Kernel autotuner: times candidate configurations per row-count bucket and keeps the winners in a JSON cache.
+
+Reference: ``crates/blaze/src/tune.rs`` (row ``BUCKETS`` :13, candidates split x tiles :129, cache file
+``~/.cache/blaze/tune-sm*.json`` :182, ``tune`` :243) and ``attn_tune.rs`` (attention split cache per GPU / rank).
+Here the tunables are the GEMM N-tile (128 / 256) and CTA cap per (kind, N, K, row bucket), and the kv-split count of
+the decode attention kernel per (batch bucket, context bucket).
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Callable, Dict, Iterable, Optional, Tuple
+
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192)
+
+
+def bucket(rows: int) -> int:
+    for b in BUCKETS:
+        if rows <= b:
+            return b
+    return BUCKETS[-1]
+
+
+def cache_path(sm: int = 100, sms: int = 148, rank: int = 0) -> str:
+    root = os.environ.get("BLAZE_CACHE_DIR", os.path.join(os.path.expanduser("~"), ".cache", "blaze_b200"))
+    return os.path.join(root, f"tune-sm{sm}-{sms}sm-r{rank}.json")
+
+
+class Tuning:
+    def __init__(self, path: Optional[str] = None):
+        self.path = path or cache_path()
+        self.table: Dict[str, Dict] = {}
+        self.dirty = False
+        try:
+            with open(self.path) as f:
+                self.table = json.load(f)
+        except (OSError, ValueError):
+            self.table = {}
+
+    @staticmethod
+    def key(kind: str, *shape) -> str:
+        return kind + ":" + "x".join(str(s) for s in shape)
+
+    def get(self, kind: str, *shape) -> Optional[Dict]:
+        return self.table.get(self.key(kind, *shape))
+
+    def put(self, kind: str, shape: Tuple, cfg: Dict, ms: float) -> None:
+        self.table[self.key(kind, *shape)] = {**cfg, "ms": round(ms, 5)}
+        self.dirty = True
+
+    def save(self) -> None:
+        if not self.dirty:
+            return
+        os.makedirs(os.path.dirname(self.path), exist_ok=True)
+        tmp = self.path + ".tmp"
+        with open(tmp, "w") as f:
+            json.dump(self.table, f, indent=1, sort_keys=True)
+        os.replace(tmp, self.path)
+        self.dirty = False
+
+    def tune(self, kind: str, shape: Tuple, candidates: Iterable[Dict], run: Callable[[Dict], float]) -> Dict:
+        """Time every candidate with ``run(cfg) -> ms`` (the caller does warm-up and event timing) and keep the best."""
+        hit = self.get(kind, *shape)
+        if hit is not None:
+            return hit
+        best, best_ms = None, float("inf")
+        for c in candidates:
+            try:
+                ms = run(c)
+            except Exception:
+                continue
+            if ms < best_ms:
+                best, best_ms = c, ms
+        if best is None:
+            raise RuntimeError(f"no candidate ran for {kind} {shape}")
+        self.put(kind, shape, best, best_ms)
+        return self.table[self.key(kind, *shape)]
+
+
+def gemm_candidates(kind: int, N: int):
+    out = [{"bn": 128, "max_ctas": 0}]
+    if N % 256 == 0:
+        out.append({"bn": 256, "max_ctas": 0})
+    return out
+
+
+def tune_linear(ops, lin, rows: int, tuning: Tuning, iters: int = 5) -> Dict:
+    """Pick the N-tile for ``lin`` at ``rows`` rows on the current device."""
+    import torch
+    pk = ops.pack(lin)
+    x = torch.randn(rows, lin.K, device=ops.device).bfloat16()
+    xin = ops.quantize_rows(x, lin) if ops._qmode(lin) else x
+
+    def run(cfg):
+        for _ in range(2):
+            ops.linear(lin, xin, bn=cfg["bn"], max_ctas=cfg["max_ctas"])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            ops.linear(lin, xin, bn=cfg["bn"], max_ctas=cfg["max_ctas"])
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+    return tuning.tune(f"gemm{pk['kind']}", (lin.N, lin.K, bucket(rows)), gemm_candidates(pk["kind"], lin.N), run)
