@@ -406,42 +406,43 @@ class Model:
             x = ops.embed(self.embed, batch.tokens)
         fused = self._fused()
         rope = ops.rope_tables(self, batch)
-        residual = None          # full rows, or this rank's row shard on the fused path
-        partial = False          # is x a partial sum that still needs the reduction?
+        residual = None          # full rows, or this rank's row shard on the reduce+norm path
+        kind = "full"            # x is: "full" rows | "partial" sums to reduce | "acc" (summed in a symmetric buffer to re-zero)
         for li, L in enumerate(self.layers):
             gi = self.first_layer + li
             first = L.attn.qkv if L.attn is not None else L.gdn.in_proj
             if gi in self.capture_layers:
-                self.captured[gi] = self._materialise(x, residual, partial, fused)
-            h, residual = self._reduce_norm(x, residual, partial, L.input_norm, first, fused)
+                self.captured[gi] = self._materialise(x, residual, kind, fused, keep=True)
+            h, residual = self._reduce_norm(x, residual, kind, L.input_norm, first, fused)
             if L.kind == "full_attention":
-                x = self._attention(L.attn, h, batch, kv, gi, rope, fused)
+                x, kind = self._attention(L.attn, h, batch, kv, gi, rope, fused)
             else:
-                x = self._gdn(L.gdn, h, batch, kv, gi, fused)
-            partial = self.tp.world > 1
+                x, kind = self._gdn(L.gdn, h, batch, kv, gi, fused)
             nxt = L.mlp.gate_up if isinstance(L.mlp, DenseMlp) else None
-            h, residual = self._reduce_norm(x, residual, partial, L.post_norm, nxt, fused)
-            x, partial = self._mlp(L.mlp, h, fused)
-        return self._materialise(x, residual, partial, fused)
+            h, residual = self._reduce_norm(x, residual, kind, L.post_norm, nxt, fused)
+            x, kind = self._mlp(L.mlp, h, fused)
+        return self._materialise(x, residual, kind, fused)
 
     def _fused(self):
         g = self.tp.group
         return g.fused if (g is not None and g.world > 1 and getattr(g, "fused", None) is not None and self.ops.is_cuda) else None
 
-    def _reduce_norm(self, x, residual, partial, w, quant_for, fused):
+    def _reduce_norm(self, x, residual, kind, w, quant_for, fused):
         ops, cfg = self.ops, self.cfg
-        if fused is not None:
+        eps, zc = cfg.rms_norm_eps, cfg.zero_centered_norm
+        if fused is not None and fused.mode == "reduce_norm":
             if residual is None:                       # first norm of the stage: shard the residual stream by rows
                 residual = fused.shard_rows(x)
-                h, _ = ops.norm(x, None, w, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=quant_for)
+                h, _ = ops.norm(x, None, w, eps, zc, quant_for=quant_for)
                 return h, residual
-            if not partial:                            # complete rows (expert-parallel MoE output): add this rank's share
+            if kind != "partial":                      # complete rows: rank 0 contributes them, the others zeros
                 x = self._as_partial(x, fused)
-            h = fused.reduce_norm(x, residual, w, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for)
-            return h, residual
-        if partial:
+            return fused.reduce_norm(x, residual, w, eps, zc, quant_for), residual
+        if kind == "acc":                              # already summed by the GEMM epilogue; re-zero the buffer while reading
+            return ops.norm(x, residual, w, eps, zc, quant_for=quant_for, zero_src=True)
+        if kind == "partial":
             x = ops.all_reduce(x, self.tp.group)
-        return ops.norm(x, residual, w, cfg.rms_norm_eps, cfg.zero_centered_norm, quant_for=quant_for)
+        return ops.norm(x, residual, w, eps, zc, quant_for=quant_for)
 
     def _as_partial(self, x, fused):
         """Present complete rows as partial sums: rank 0 contributes them, the others contribute zeros."""
@@ -452,18 +453,31 @@ class Model:
             buf.zero_()
         return buf
 
-    def _materialise(self, x, residual, partial, fused):
+    def _materialise(self, x, residual, kind, fused, keep: bool = False):
         """The complete residual stream on every rank."""
         ops = self.ops
-        if fused is not None and residual is not None:
-            if not partial:
+        if fused is not None and fused.mode == "reduce_norm" and residual is not None:
+            if kind != "partial":
                 x = self._as_partial(x, fused)
-            return fused.reduce_norm(x, residual, None, self.cfg.rms_norm_eps, False, None)
-        if partial:
+            res = residual.clone() if keep else residual
+            return fused.reduce_norm(x, res, None, self.cfg.rms_norm_eps, False, None)
+        if kind == "partial":
             x = ops.all_reduce(x, self.tp.group)
-        if residual is not None:
-            x = ops.add(x, residual)
-        return x
+        out = ops.add(x, residual) if residual is not None else x
+        if kind == "acc" and not keep:
+            if residual is None:
+                out = x.clone()
+            x.zero_()
+        return out
+
+    def _row_cut(self, lin, a, rows, fused):
+        """Row-parallel projection: returns (output, kind)."""
+        ops = self.ops
+        if fused is None:
+            return ops.linear(lin, a), ("partial" if self.tp.world > 1 else "full")
+        if fused.mode == "gemm_red":
+            return fused.gemm_allreduce(ops, lin, a, rows), "acc"
+        return ops.linear(lin, a, out=fused.next_input(rows, lin.N)), "partial"
 
     def _out_buf(self, fused, rows, cols):
         return fused.next_input(rows, cols) if fused is not None else None
@@ -475,9 +489,7 @@ class Model:
         o = ops.attention(q, self, batch, kv, gi, self.attn_scale)
         if gate is not None:
             o = ops.mul_sigmoid(o, gate.reshape(o.shape))
-        if fused is not None:
-            return ops.linear(A.o, o, out=fused.next_input(o.shape[0], A.o.N))
-        return ops.linear(A.o, o)
+        return self._row_cut(A.o, o, o.shape[0], fused)
 
     def _gdn(self, G: Gdn, h, batch, kv, gi, fused=None):
         ops, cfg = self.ops, self.cfg
@@ -488,19 +500,15 @@ class Model:
         mixed, z = proj[:, :nq], proj[:, nq:nq + nz]
         b, a = proj[:, nq + nz:nq + nz + G.v_heads], proj[:, nq + nz + G.v_heads:]
         o = ops.gdn(mixed, z, b, a, G, self, batch, kv, gi)
-        if fused is not None:
-            return ops.linear(G.out_proj, o, out=fused.next_input(o.shape[0], G.out_proj.N))
-        return ops.linear(G.out_proj, o)
+        return self._row_cut(G.out_proj, o, o.shape[0], fused)
 
     def _mlp(self, M, h, fused=None):
-        """Returns (output, is_partial_sum)."""
+        """Returns (output, kind) with kind as in :meth:`forward`."""
         ops = self.ops
         tp = self.tp.world > 1
         if isinstance(M, DenseMlp):
             a = ops.silu_mul(ops.linear(M.gate_up, h), quant_for=M.down)
-            if fused is not None:
-                return ops.linear(M.down, a, out=fused.next_input(a.rows if hasattr(a, "rows") else a.shape[0], M.down.N)), True
-            return ops.linear(M.down, a), tp
+            return self._row_cut(M.down, a, a.rows if hasattr(a, "rows") else a.shape[0], fused)
         hd = h.dense if hasattr(h, "dense") and h.dense is not None else h
         logits = ops.linear(M.router, hd, out_dtype=torch.float32)
         if ops.is_cuda:
@@ -519,7 +527,7 @@ class Model:
                 y = ops.add_sigmoid_scaled(y, s, ops.linear(M.shared_gate, hd))
             else:
                 y = ops.add(y, s)
-        return y, routed_partial
+        return y, ("partial" if routed_partial else "full")
 
     # ------------------------------------------------------------------ head
     def final_hidden(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:

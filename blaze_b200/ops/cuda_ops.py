@@ -45,7 +45,7 @@ class CudaOps:
         lib.blz_gemm_tc.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
                                     _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, VP]
         lib.blz_embed.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
-        lib.blz_rmsnorm.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int, VP]
+        lib.blz_rmsnorm.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_swiglu.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_attn_prep.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                       _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_float, _c.c_float, VP]
@@ -162,18 +162,18 @@ class CudaOps:
         self._check(self.lib.blz_embed(_ptr(table), _ptr(tokens), _ptr(out), T, H, table.shape[0], self._stream()), "embed")
         return out
 
-    def norm(self, x, residual, w, eps, zero_centered=False, quant_for: Optional[Linear] = None):
+    def norm(self, x, residual, w, eps, zero_centered=False, quant_for: Optional[Linear] = None, zero_src: bool = False):
         T, H = x.shape
         mode = self._qmode(quant_for)
         new_res = residual if residual is not None else x
         if mode == 0:
             out = torch.empty_like(x)
             self._check(self.lib.blz_rmsnorm(_ptr(x), _ptr(residual), _ptr(w), _ptr(out), VP(0), VP(0), VP(0), T, H, eps,
-                                             int(zero_centered), 0, self._stream()), "rmsnorm")
+                                             int(zero_centered), 0, int(zero_src), self._stream()), "rmsnorm")
             return out, new_res
         qa = self._alloc_qact(Format.NVFP4 if mode == 1 else Format.MXFP8, T, H)
         self._check(self.lib.blz_rmsnorm(_ptr(x), _ptr(residual), _ptr(w), VP(0), _ptr(qa.data), _ptr(qa.sf),
-                                         _ptr(qa.row_scale), T, H, eps, int(zero_centered), mode, self._stream()), "rmsnorm_q")
+                                         _ptr(qa.row_scale), T, H, eps, int(zero_centered), mode, int(zero_src), self._stream()), "rmsnorm_q")
         return qa, new_res
 
     def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0):

@@ -74,6 +74,7 @@ class SymmAllReduce:
         lib = self.lib
         lib.blz_comm_create.restype = VP
         lib.blz_comm_create.argtypes = [ctypes.c_int, ctypes.c_int, VP, VP, ctypes.c_int]
+        lib.blz_gemm_fuse_allreduce.argtypes = [VP, VP, VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int]
         lib.blz_comm_allreduce.argtypes = [VP, VP, VP, VP, VP, ctypes.c_longlong, ctypes.c_int, VP]
         lib.blz_comm_allreduce_norm.argtypes = [VP] + [VP] * 8 + [VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                                   ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, VP]
@@ -84,7 +85,7 @@ class SymmAllReduce:
         self.sf_bytes = row_tiles * ((hidden + 63) // 64) * 512
         self.rs_bytes = max_rows * 4
         pad_bytes = int(lib.blz_comm_pad_bytes())
-        total = 2 * self.in_bytes + self.in_bytes + self.q_bytes + self.sf_bytes + self.rs_bytes + pad_bytes + 16 * 4096
+        total = 4 * self.in_bytes + self.in_bytes + self.q_bytes + self.sf_bytes + self.rs_bytes + pad_bytes + 32 * 4096
         self.arena = SymmArena(group, device, total)
         a = self.arena
         self.off_in = [a.carve(self.in_bytes), a.carve(self.in_bytes)]
@@ -94,6 +95,15 @@ class SymmAllReduce:
         self.off_rs = a.carve(self.rs_bytes)
         self.off_pad = a.carve(pad_bytes)
         a.view(self.off_pad, pad_bytes).zero_()
+        # fused GEMM + all-reduce: two zeroed accumulation buffers that every rank's epilogue reduces into, a flag row
+        self.off_acc = [a.carve(self.in_bytes), a.carve(self.in_bytes)]
+        for o in self.off_acc:
+            a.view(o, self.in_bytes).zero_()
+        self.off_pad2 = a.carve(4096)
+        a.view(self.off_pad2, 4096).zero_()
+        self.gemm_state = torch.zeros(4, dtype=torch.int32, device=self.device)     # [done counter, epoch]
+        self.acc_cur = 0
+        self.timeout_ms = int(timeout_ms or os.environ.get("BLAZE_COMM_TIMEOUT_MS", "10000"))
         self.epoch = torch.zeros(int(lib.blz_comm_epoch_bytes()) // 4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         group.barrier()
@@ -102,6 +112,12 @@ class SymmAllReduce:
         if not self.comm:
             raise RuntimeError("blz_comm_create failed")
         self.use_mc = bool(use_multicast and a.mc)
+        # "gemm_red": the row-cut GEMM's epilogue reduces through the switch (one kernel per reduction, replicated norm);
+        # "reduce_norm": GEMM writes partial sums, one kernel reduces + norms + quantises a row slice per rank.
+        default = "gemm_red" if (self.use_mc and group.world <= 2) else "reduce_norm"
+        self.mode = os.environ.get("BLAZE_TP_FUSION", default)
+        if self.mode == "gemm_red" and not self.use_mc:
+            self.mode = "reduce_norm"
         self.cur = 0
         self.launches = 0
 
@@ -151,6 +167,26 @@ class SymmAllReduce:
             raise RuntimeError(f"blz_comm_allreduce failed: {rc}")
         self.launches += 1
         return x
+
+    def gemm_allreduce(self, ops, lin: Linear, x, rows: int) -> torch.Tensor:
+        """``sum over ranks of (x @ W_shard^T)`` in ONE kernel: the tcgen05 GEMM's epilogue adds each bf16 tile into every
+        rank's accumulation buffer with ``multimem.red`` and the kernel ends with a cross-rank barrier.  Returns the
+        complete ``[rows, N]`` sum in local memory; the consumer must hand the buffer back zeroed (``zero_src``)."""
+        n = rows * lin.N * 2
+        if n > self.in_bytes:
+            raise ValueError("accumulation buffer too small")
+        self.acc_cur ^= 1
+        off = self.off_acc[self.acc_cur]
+        a = self.arena
+        rc = self.lib.blz_gemm_fuse_allreduce(VP(a.mcast(off)), VP(self.gemm_state.data_ptr()), _arr(a.peers(self.off_pad2)),
+                                              VP(self.gemm_state.data_ptr() + 4), self.group.rank, self.group.world,
+                                              self.timeout_ms)
+        if rc != 0:
+            raise RuntimeError(f"blz_gemm_fuse_allreduce failed: {rc}")
+        out = a.view(off, n).view(torch.bfloat16).view(rows, lin.N)
+        ops.linear(lin, x, out=out)
+        self.launches += 1
+        return out
 
     def rows_per(self, T: int) -> int:
         return (T + self.group.world - 1) // self.group.world

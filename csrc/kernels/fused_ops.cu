@@ -56,19 +56,20 @@ __global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const int*
 // ---------------------------------------------------------------------------------------------- RMSNorm (+quant)
 // QUANT: 0 none (bf16 out), 1 NVFP4 (packed + tiled e4m3 scales + per-row fp32 scale), 2 MXFP8 (e4m3 + tiled e8m0)
 template <int QUANT>
-__global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+__global__ void rmsnorm_kernel(__nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
                                uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out, float* __restrict__ row_scale,
-                               int H, float eps, int zero_centered, int sf_col_tiles) {
+                               int H, float eps, int zero_centered, int sf_col_tiles, int zero_src) {
   extern __shared__ __align__(16) uint8_t dyn[];
   __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(dyn);     // the (x + residual) row, then the normed row
   __shared__ float red[32];
   const int t = blockIdx.x;
-  const __nv_bfloat16* xr = x + (size_t)t * H;
+  __nv_bfloat16* xr = x + (size_t)t * H;
   __nv_bfloat16* rr = residual ? residual + (size_t)t * H : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     uint4 u = *reinterpret_cast<const uint4*>(xr + i);
+    if (zero_src) *reinterpret_cast<uint4*>(xr + i) = make_uint4(0, 0, 0, 0);   // hand the accumulation buffer back zeroed
     __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u);
     if (rr) {
       uint4 ur = *reinterpret_cast<const uint4*>(rr + i);
@@ -399,8 +400,8 @@ BLZ_API int blz_embed(const void* table, const int* tokens, void* out, int T, in
 }
 
 // quant: 0 → bf16 `out`; 1 → NVFP4 (q_out [T, H/2], sf_out tiled, row_scale [T]); 2 → MXFP8 (q_out [T, H], sf_out tiled)
-BLZ_API int blz_rmsnorm(const void* x, void* residual, const void* w, void* out, void* q_out, void* sf_out,
-                        float* row_scale, int T, int H, float eps, int zero_centered, int quant, cudaStream_t s) {
+BLZ_API int blz_rmsnorm(void* x, void* residual, const void* w, void* out, void* q_out, void* sf_out,
+                        float* row_scale, int T, int H, float eps, int zero_centered, int quant, int zero_src, cudaStream_t s) {
   if (H % 32 || T < 0) return (int)cudaErrorInvalidValue;
   if (T == 0) return 0;
   configure_once();
@@ -408,11 +409,11 @@ BLZ_API int blz_rmsnorm(const void* x, void* residual, const void* w, void* out,
   const size_t sm = (size_t)H * 2;
   const int ct = quant == 1 ? (H + 63) / 64 : (H + 127) / 128;
   if (quant == 0)
-    rmsnorm_kernel<0><<<T, thr, sm, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, nullptr, nullptr, nullptr, H, eps, zero_centered, 0);
+    rmsnorm_kernel<0><<<T, thr, sm, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, nullptr, nullptr, nullptr, H, eps, zero_centered, 0, zero_src);
   else if (quant == 1)
-    rmsnorm_kernel<1><<<T, thr, sm, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct);
+    rmsnorm_kernel<1><<<T, thr, sm, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src);
   else
-    rmsnorm_kernel<2><<<T, thr, sm, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct);
+    rmsnorm_kernel<2><<<T, thr, sm, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src);
   return (int)cudaGetLastError();
 }
 

@@ -29,6 +29,15 @@ struct GemmParams {
   const uint8_t* sfa;        // scale factors of A, 128x4-tiled (kinds 1, 2)
   const uint8_t* sfb;
   int sfa_col_tiles;         // number of 4-column tiles per 128-row tile in sfa / sfb
+  // fused all-reduce (OUT mode 2): the epilogue adds this rank's partial tile into every rank's output through the
+  // NVSwitch (multimem.red); the last CTA then meets the other ranks at a flag barrier, so kernel completion means
+  // the summed output is complete in local memory.
+  void* mc_out;              // multicast address of C (bf16 [M, ldc])
+  unsigned* done_ctr;        // local counter of finished CTAs (returns to zero at the end of the kernel)
+  uint32_t* peer_pad[8];     // one flag row per rank: pad[r][src_rank]
+  uint32_t* epoch;           // local barrier epoch
+  long long spin_limit;
+  int rank, world;
   const int* tile_expert;    // grouped GEMM: expert of every 128-row M tile (-1 = skip); B / alpha / sfb rows are offset by expert * N
   int* status;
 };
@@ -255,7 +264,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const float o2 = fmaf(__uint_as_float(r[i + 2]) * rs, a0.z, b0.z), o3 = fmaf(__uint_as_float(r[i + 3]) * rs, a0.w, b0.w);
               const float o4 = fmaf(__uint_as_float(r[i + 4]) * rs, a1.x, b1.x), o5 = fmaf(__uint_as_float(r[i + 5]) * rs, a1.y, b1.y);
               const float o6 = fmaf(__uint_as_float(r[i + 6]) * rs, a1.z, b1.z), o7 = fmaf(__uint_as_float(r[i + 7]) * rs, a1.w, b1.w);
-              if (whole) {
+              if (p.mc_out != nullptr) {
+                if (whole) {
+                  const size_t off = ((size_t)row * p.ldc + col0 + i) * 2;
+                  asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1,%2,%3,%4};"
+                               ::"l"(reinterpret_cast<uint8_t*>(p.mc_out) + off), "r"(pack_bf16x2(o0, o1)), "r"(pack_bf16x2(o2, o3)),
+                                 "r"(pack_bf16x2(o4, o5)), "r"(pack_bf16x2(o6, o7))
+                               : "memory");
+                }
+              } else if (whole) {
                 *reinterpret_cast<uint4*>(dst + i) =
                     make_uint4(pack_bf16x2(o0, o1), pack_bf16x2(o2, o3), pack_bf16x2(o4, o5), pack_bf16x2(o6, o7));
               } else {
@@ -283,6 +300,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+  if (p.mc_out != nullptr && threadIdx.x == 0) {
+    // every CTA's reductions are ordered before its count; the last CTA of this rank tells the peers and waits for them
+    __threadfence_system();
+    const unsigned prev = atomicAdd(p.done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.done_ctr = 0;
+      const uint32_t e = *p.epoch + 1;
+      *p.epoch = e;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_pad[r] + p.rank), "r"(e) : "memory");
+      for (int r = 0; r < p.world; ++r) {
+        const long long t0 = clock64();
+        while (true) {
+          uint32_t v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.peer_pad[p.rank] + r) : "memory");
+          if ((int32_t)(v - e) >= 0) break;
+          if (clock64() - t0 > p.spin_limit) { atomicCAS(p.status, kOk, kErrFlagTimeout); break; }
+        }
+      }
+    }
+  }
 }
 
 template <int KIND, int BN, bool OUT_F32>
@@ -304,6 +343,33 @@ static cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
 }
 
 }  // namespace blz
+
+namespace {
+struct FuseArgs {
+  void* mc_out = nullptr;
+  unsigned* done_ctr = nullptr;
+  uint32_t* peer_pad[8] = {nullptr};
+  uint32_t* epoch = nullptr;
+  long long spin_limit = 0;
+  int rank = 0, world = 1;
+};
+thread_local FuseArgs g_fuse;
+}  // namespace
+
+// Arms the NEXT blz_gemm_tc call on this thread as a fused GEMM + all-reduce: its epilogue reduces the bf16 partial
+// tiles into `mc_out` (the multicast view of a zeroed output buffer that every rank maps) and the kernel ends with a
+// cross-rank barrier.  pads[r] points at rank r's flag row (world uint32), epoch / done_ctr are local device words.
+BLZ_API int blz_gemm_fuse_allreduce(void* mc_out, void* done_ctr, void* const* pads, void* epoch, int rank, int world,
+                                    int timeout_ms) {
+  if (!mc_out || world < 1 || world > 8) return (int)cudaErrorInvalidValue;
+  g_fuse.mc_out = mc_out;
+  g_fuse.done_ctr = reinterpret_cast<unsigned*>(done_ctr);
+  g_fuse.epoch = reinterpret_cast<uint32_t*>(epoch);
+  g_fuse.rank = rank; g_fuse.world = world;
+  g_fuse.spin_limit = (long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1900000LL;
+  for (int r = 0; r < world; ++r) g_fuse.peer_pad[r] = reinterpret_cast<uint32_t*>(pads[r]);
+  return 0;
+}
 
 // kind: 0 bf16, 1 nvfp4, 2 mxfp8, 3 fp8.  A [M, K] and B [N, K] row-major (packed bytes for 4/8-bit kinds);
 // lda / ldb in BYTES.  out_f32: C is fp32, else bf16; ldc in elements.  bn: 128 or 256 (0 = choose).
@@ -328,6 +394,14 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   p.sfa_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
   p.status = status_word();
   p.tile_expert = tile_expert;
+  p.mc_out = nullptr; p.done_ctr = nullptr; p.epoch = nullptr; p.spin_limit = 0; p.rank = 0; p.world = 1;
+  if (g_fuse.mc_out) {
+    if (out_f32 || (N % 32)) return (int)cudaErrorInvalidValue;
+    p.mc_out = g_fuse.mc_out; p.done_ctr = g_fuse.done_ctr; p.epoch = g_fuse.epoch; p.spin_limit = g_fuse.spin_limit;
+    p.rank = g_fuse.rank; p.world = g_fuse.world;
+    for (int r = 0; r < g_fuse.world; ++r) p.peer_pad[r] = g_fuse.peer_pad[r];
+    g_fuse.mc_out = nullptr;      // one-shot: applies to this launch only
+  }
   const uint64_t b_rows = (uint64_t)N * (tile_expert ? (num_experts > 0 ? num_experts : 1) : 1);
   if (tile_expert && N % bn) return (int)cudaErrorInvalidValue;
   CUtensorMap tmA, tmB;

@@ -48,6 +48,28 @@ def main():
             lst = [torch.zeros_like(chk) for _ in range(world)]
             dist.all_gather(lst, chk)
             assert all(float(v) == float(lst[0]) for v in lst), "ranks disagree"
+    elif case == "gemm_allreduce":
+        from blaze_b200.ops import get_ops
+        ops = get_ops(dev)
+        if not fused.use_mc:
+            print("[worker] no multicast mapping: fused GEMM + all-reduce skipped", flush=True)
+        else:
+            for fmt, M, N, K in ((Format.DENSE, 200, 2048, 1024), (Format.NVFP4, 256, 2048, 2048), (Format.DENSE, 64, 2048, 512)):
+                w = torch.randn(N, K, generator=g, device=dev) * 0.05
+                lin = Linear.from_dense(w, fmt)
+                x = torch.randn(M, K, generator=g, device=dev).bfloat16()
+                local = ops.linear(lin, x).float()
+                want = local.clone()
+                dist.all_reduce(want)
+                for rep in range(2):
+                    y = fused.gemm_allreduce(ops, lin, x, M)
+                    torch.cuda.synchronize()
+                    err = (y.float() - want).abs().max().item()
+                    ref_mag = want.abs().mean().item()
+                    assert err < 0.05 * max(ref_mag, 1.0) + 0.05, f"fused GEMM+all-reduce mismatch {err} (mean |ref| {ref_mag})"
+                    y.zero_()            # hand the accumulation buffer back zeroed, as the norm kernel does
+                    torch.cuda.synchronize()
+                    dist.barrier()
     elif case == "reduce_norm":
         w = (1 + 0.1 * torch.randn(H, generator=torch.Generator(device=dev).manual_seed(7), device=dev)).bfloat16()
         gfull = torch.Generator(device=dev).manual_seed(11)
@@ -103,6 +125,8 @@ def main():
         solo = run(TPInfo(), False)
         nccl = run(TPInfo(rank, world, group), False)
         fus = run(TPInfo(rank, world, group), True)
+        if rank == 0:
+            print("[worker] fusion mode", group.fused.mode, flush=True)
         if rank == 0:
             print("[worker] tp1  ", solo[:3], "\n[worker] nccl ", nccl[:3], "\n[worker] fused", fus[:3], flush=True)
         agree = sum(a == b for a, b in zip(sum(solo, []), sum(fus, [])))

@@ -10,8 +10,10 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(case, multicast="1", nproc=2):
+def _run(case, multicast="1", nproc=2, fusion=None):
     env = dict(os.environ, BLAZE_TEST_MULTICAST=multicast, NCCL_DEBUG="WARN")
+    if fusion:
+        env["BLAZE_TP_FUSION"] = fusion
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", "29611", os.path.join(HERE, "_tp_worker.py"), case]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -30,5 +32,10 @@ def test_reduce_norm(multicast):
     _run("reduce_norm", multicast)
 
 
-def test_tp2_model_fused_matches_tp1():
-    _run("model")
+def test_gemm_allreduce_one_kernel():
+    _run("gemm_allreduce")
+
+
+@pytest.mark.parametrize("fusion", ["gemm_red", "reduce_norm"])
+def test_tp2_model_fused_matches_tp1(fusion):
+    _run("model", fusion=fusion)
