@@ -70,7 +70,7 @@ def main():
     ap.add_argument("--weights", default="nvfp4")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--prompt-len", type=int, default=1024)
-    ap.add_argument("--e2e-out", type=int, default=0, help="output tokens per request in the end-to-end run (0 = steps + warmup)")
+    ap.add_argument("--e2e-out", type=int, default=0, help="output tokens per request in the end-to-end run (0 = the workload's 256)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the line invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
@@ -128,13 +128,13 @@ def main():
         cfg.layer_types = cfg.layer_types[:args.layers]
         invalid = f"truncated to {args.layers} layers"
     B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
-    out_tokens = args.e2e_out or (K + W)
+    out_tokens = args.e2e_out or 256
     max_len = P + max(out_tokens, K + W) + 32
     kv_tokens = B * (max_len + 16)
     t_load = time.time()
     llm = LLM(cfg, weight_format=args.weights, device=dev, tp=tp, kv_cache_dtype="fp8", kv_tokens=kv_tokens, max_seqs=B,
               max_model_len=max_len, chunk=4096, enable_prefix_caching=False, use_graphs=not args.no_graphs, seed=1,
-              max_step_tokens=B + 4096)
+              max_step_tokens=B + 4096, warm_graphs=not args.no_graphs)
     note("model built")
     eng = llm.engine
     ops = llm.model.ops

@@ -279,6 +279,33 @@ class Engine:
             self._graphs[key] = g
         return g.replay(chunks)
 
+    def capture_decode_graphs(self, max_batch: Optional[int] = None) -> int:
+        """Capture the decode-step graph of every batch bucket up front (server start-up), so that no request pays for a
+        capture.  Uses scratch sequences that are closed again; returns the number of graphs captured."""
+        if not (self.ecfg.use_graphs and self.device.type == "cuda" and self.model.ops.is_cuda
+                and self.model.is_first_stage and self.model.is_last_stage):
+            return 0
+        cap = min(max_batch or self.ecfg.max_seqs, len(self.free_rows), max(self.pages.free_count, 0))
+        n = 0
+        for b in self.ecfg.graph_buckets:
+            if b > cap:
+                break
+            if ("decode", b) in self._graphs:
+                continue
+            seqs = [self.open_from() for _ in range(b)]
+            try:
+                for _ in range(2):      # first sight runs eagerly, second sight captures
+                    for s in seqs:
+                        s.length = 0
+                    self.forward(self.plan([(s, [0], 1) for s in seqs]), "greedy")
+                n += 1
+            finally:
+                for s in seqs:
+                    self.close(s)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        return n
+
     def graph_kernel_count(self) -> int:
         """Kernels of this library inside one captured decode step (the largest captured bucket)."""
         return max((g.kernels for g in self._graphs.values()), default=0)

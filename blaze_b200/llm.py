@@ -41,7 +41,7 @@ class LLM:
                  dtype=torch.bfloat16, tp=None, kv_cache_dtype: str = "auto", kv_tokens: int = 0, max_seqs: int = 256,
                  max_model_len: int = 4096, chunk: int = 2048, enable_prefix_caching: bool = True, cache_slots: int = 4,
                  use_graphs: bool = True, spec_method: str = "none", max_draft: int = 4, seed: int = 0,
-                 eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192):
+                 eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192, warm_graphs: bool = False):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -69,6 +69,9 @@ class LLM:
                                                         cache_slots=cache_slots, spec_method=spec_method, max_draft=max_draft,
                                                         eos_ids=eos, max_model_len=max_model_len,
                                                         max_step_tokens=max_step_tokens), drafter=drafter)
+        if warm_graphs:
+            with log.Stage("graphs"):
+                self.engine.capture_decode_graphs()
         self._n = 0
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
