@@ -75,8 +75,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collectives: in-kernel peer memory, or NCCL")
-    ap.add_argument("--cuda-profiler", action="store_true",
-                    help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--cuda-profiler", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
+                    help="bracket the timed decode steps (or the second prefill chunk) with cudaProfilerStart/Stop "
+                         "(for ncu --profile-from-start off)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -159,7 +160,14 @@ def main():
     last = {}
     for i in range(0, B, per):          # prefill in chunks of ~4096 tokens
         part = list(range(i, min(B, i + per)))
+        prof_this = args.cuda_profiler == "prefill" and i == per
+        if prof_this:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
         out = eng.forward(eng.plan([(seqs[j], prompts[j], 1) for j in part]), "greedy")
+        if prof_this:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
         for j, t in zip(part, out.tolist()):
             last[j] = t
     ttft_ev[1].record()
@@ -180,7 +188,7 @@ def main():
     sampler = clocks_sampler(clk_path, local) if rank == 0 else None
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if args.cuda_profiler:
+    if args.cuda_profiler == "decode":
         torch.cuda.profiler.start()
     e0.record()
     for _ in range(K):
@@ -188,7 +196,7 @@ def main():
         cur = out.tolist()
     e1.record()
     note("timed steps issued")
-    if args.cuda_profiler:
+    if args.cuda_profiler == "decode":
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
     sync_all()
