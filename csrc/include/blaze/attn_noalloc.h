@@ -1,0 +1,45 @@
+// Decode attention for callers that cannot allocate device memory.
+//
+// This entry point has no counterpart in the reference: there the host always owns and passes every buffer
+// (kernels/include/blaze/*.h take raw pointers for scratch as well).
+//
+// Who needs it: code that runs where cudaMalloc is forbidden or would deadlock — inside a CUDA-graph capture that was
+// started by someone else, inside a stream callback / host function, in a process whose memory pool is owned by another
+// runtime and must not grow, or in a latency-critical path that may not take the allocator lock.  The split-KV variant of
+// the paged decode attention needs scratch for its per-split partial outputs; `blz_attn_decode` takes that scratch from
+// the caller, this variant keeps it inside the library instead.
+//
+// How: the partial outputs and (max, sum) pairs live in ONE file-scope `static __device__ __align__(256)` array of
+// BLZ_ATTN_NOALLOC_SCRATCH_BYTES (16.5 MiB); every GPU that loads the library holds it until the process exits.
+// The first call on a device looks the array's device address up (cudaGetSymbolAddress) and configures the kernel's
+// shared-memory limit; make that first call outside of any stream capture.  Later calls on that device only launch.
+// The function never calls cudaMalloc / cudaFree or any allocating library routine.
+//
+// Limits: seqs * kv_heads * row_blocks * splits * 16 rows of 130 floats must fit the array, otherwise the call returns
+// cudaErrorInvalidValue and `blz_attn_decode_noalloc_error()` explains what was too large.  All calls share the array:
+// it keeps the last call's contents (nothing in it has to start at zero — every slot that is read is written first by
+// the same call), and two calls that overlap on the GPU (different streams, or concurrent graphs) race on it.
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BLZ_ATTN_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u + 512u * 1024u)
+
+// Same arguments and result as blz_attn_decode with nmax = 16, minus the scratch pointers.
+int blz_attn_decode_noalloc(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
+                            const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride,
+                            float scale, float k_scale, float v_scale, int row_blocks, int min_rows, int max_rows, int splits,
+                            int max_ctas, cudaStream_t stream);
+
+// Text of the last size / set-up error of this thread ("" when the last call succeeded).
+const char* blz_attn_decode_noalloc_error(void);
+
+// Bytes of scratch the given problem needs (to check against BLZ_ATTN_NOALLOC_SCRATCH_BYTES beforehand).
+long long blz_attn_decode_noalloc_bytes(int num_seqs, int Hkv, int row_blocks, int splits);
+
+#ifdef __cplusplus
+}
+#endif

@@ -480,3 +480,93 @@ BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const in
   if (live <= 8) return (int)launch_decode<16, 8>(p, max_ctas, stream);
   return (int)launch_decode<16, 16>(p, max_ctas, stream);
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Allocation-free variant (see blaze/attn_noalloc.h): the split-KV partials live in a library-owned device array.
+#include <cstdio>
+
+#include "blaze/attn_noalloc.h"
+
+namespace {
+// partial outputs [work][16][128] floats followed by (max, sum) pairs [work][16][2] floats
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BLZ_ATTN_NOALLOC_SCRATCH_BYTES];
+static __device__ int g_noalloc_status;
+
+struct NoAllocDev {
+  bool ready = false;
+  float* scratch = nullptr;     // device address of g_noalloc_scratch on that device
+  int* status = nullptr;
+};
+NoAllocDev g_noalloc_dev[64];
+thread_local char g_noalloc_err[256] = "";
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) const char* blz_attn_decode_noalloc_error(void) { return g_noalloc_err; }
+
+extern "C" __attribute__((visibility("default"))) long long blz_attn_decode_noalloc_bytes(int num_seqs, int Hkv, int row_blocks,
+                                                                                          int splits) {
+  const long long work = (long long)num_seqs * Hkv * row_blocks * splits;
+  return work * 16 * (128 + 2) * (long long)sizeof(float);
+}
+
+extern "C" __attribute__((visibility("default"))) int blz_attn_decode_noalloc(
+    const void* q, void* out, const void* pool, const int* block_table, const int* slots, const int* q_start, const int* ctx_len,
+    int num_seqs, int Hq, int Hkv, int D, int bt_stride, float scale, float k_scale, float v_scale, int row_blocks, int min_rows,
+    int max_rows, int splits, int max_ctas, cudaStream_t stream) {
+  using namespace blz;
+  g_noalloc_err[0] = 0;
+  if (num_seqs <= 0) return 0;
+  if (D != 128 || Hkv <= 0 || Hq % Hkv || row_blocks < 1 || splits < 1) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "unsupported shape: head_dim %d, heads %d/%d, row_blocks %d, splits %d", D, Hq,
+             Hkv, row_blocks, splits);
+    return (int)cudaErrorInvalidValue;
+  }
+  const long long need = blz_attn_decode_noalloc_bytes(num_seqs, Hkv, row_blocks, splits);
+  if (splits > 1 && need > (long long)BLZ_ATTN_NOALLOC_SCRATCH_BYTES) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err),
+             "split-KV scratch of %lld bytes (%d seqs x %d kv heads x %d row blocks x %d splits) exceeds the built-in %u bytes; "
+             "use fewer splits or blz_attn_decode with caller-owned scratch",
+             need, num_seqs, Hkv, row_blocks, splits, (unsigned)BLZ_ATTN_NOALLOC_SCRATCH_BYTES);
+    return (int)cudaErrorInvalidValue;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "cudaGetDevice failed (%d)", (int)e);
+    return (int)(e != cudaSuccess ? e : cudaErrorInvalidDevice);
+  }
+  NoAllocDev& d = g_noalloc_dev[dev];
+  if (!d.ready) {
+    // first call on this device, with this device current: resolve the device addresses of the library-owned arrays.
+    // In host code the array names are host-side stand-ins, never device pointers.
+    void* p_scratch = nullptr;
+    void* p_status = nullptr;
+    e = cudaGetSymbolAddress(&p_scratch, g_noalloc_scratch);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&p_status, g_noalloc_status);
+    if (e != cudaSuccess) {
+      snprintf(g_noalloc_err, sizeof(g_noalloc_err), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    d.scratch = reinterpret_cast<float*>(p_scratch);
+    d.status = reinterpret_cast<int*>(p_status);
+    d.ready = true;
+  }
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
+  p.block_table = block_table; p.slots = slots; p.q_start = q_start; p.ctx_len = ctx_len;
+  p.item_seq = nullptr; p.item_q0 = nullptr;
+  const long long work = (long long)num_seqs * Hkv * row_blocks * splits;
+  p.part_o = d.scratch;
+  p.part_ml = d.scratch + work * 16 * 128;
+  p.num_items = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.bt_stride = bt_stride; p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f * k_scale; p.v_scale = v_scale;
+  p.tokens_per_block = 0; p.min_rows = min_rows; p.max_rows = max_rows; p.row_blocks = row_blocks;
+  p.status = d.status;
+  p.prof = nullptr;
+  const int live = max_rows < 16 ? max_rows : 16;
+  if (live <= 4) e = launch_decode<16, 4>(p, max_ctas, stream);
+  else if (live <= 8) e = launch_decode<16, 8>(p, max_ctas, stream);
+  else e = launch_decode<16, 16>(p, max_ctas, stream);
+  if (e != cudaSuccess) snprintf(g_noalloc_err, sizeof(g_noalloc_err), "launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
