@@ -13,6 +13,7 @@ import numpy as np
 import torch
 
 PAGE = 16
+TINY_ROWS = 8       # ... of which those with at most this many rows run in the two-CTAs-per-SM configuration
 SMALL_ROWS = 64     # sequences with q_len * group <= this use the decode attention kernel
 
 
@@ -37,7 +38,10 @@ class StepBatch:
     logit_rows: torch.Tensor      # [R] int32 rows whose logits are wanted
     item_seq: Optional[torch.Tensor] = None   # [items] attention row-block items (None = one per sequence)
     item_q0: Optional[torch.Tensor] = None
-    small_rows_max: int = 0       # largest q_len * group among sequences handled by the decode attention kernel
+    tiny_rows_max: int = 0        # largest q_len * group among sequences with at most TINY_ROWS rows (plain decode)
+    num_tiny: int = 0
+    small_rows_max: int = 0       # largest q_len * group among the other sequences handled by the decode attention kernel
+    num_small: int = 0
     num_large: int = 0            # sequences handled by the row-block (prefill) attention kernel
     # host mirrors (python ints) for the oracle path and for planning
     h_slots: List[int] = field(default_factory=list)
@@ -99,13 +103,18 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     lr = np.asarray(logit_rows, np.int32)
     items_s: List[int] = []
     items_q: List[int] = []
-    small_rows_max = num_large = 0
+    small_rows_max = num_large = tiny_rows_max = num_tiny = num_small = 0
     if attn_group > 0:
         tpb = max(128 // attn_group, 1)
         for b, c in enumerate(chunks):
             rows = len(c.tokens) * attn_group
+            if rows <= TINY_ROWS:
+                tiny_rows_max = max(tiny_rows_max, rows)
+                num_tiny += 1
+                continue
             if rows <= SMALL_ROWS:
                 small_rows_max = max(small_rows_max, rows)
+                num_small += 1
                 continue
             num_large += 1
             for q0 in range(0, len(c.tokens), tpb):
@@ -131,4 +140,5 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
                      ctx_len=v[6], logit_rows=v[7], item_seq=v[8] if items_s else None,
                      item_q0=v[9] if items_s else None, h_slots=[int(s) for s in slots],
                      h_q_start=[int(x) for x in q_start], h_ctx_len=[int(x) for x in ctx_len],
-                     h_logit_rows=logit_rows, small_rows_max=small_rows_max, num_large=num_large, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)
+                     h_logit_rows=logit_rows, tiny_rows_max=tiny_rows_max, num_tiny=num_tiny, small_rows_max=small_rows_max,
+                     num_small=num_small, num_large=num_large, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)

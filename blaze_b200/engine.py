@@ -88,6 +88,7 @@ class EngineConfig:
     snapshot_rows: int = 8
     hang_secs: float = 30.0
     graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+    feedback_eager: bool = False       # allow token feedback on uncaptured decode steps too (CPU tests of the run-ahead loop)
 
 
 class Engine:
@@ -118,7 +119,10 @@ class Engine:
         self._seen: Dict[Tuple, int] = {}
         self._pinned = None
         if self.device.type == "cuda":
-            self._pinned = torch.empty(1 << 20, dtype=torch.int32, pin_memory=True)
+            self._pinned = [torch.empty(1 << 19, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._pinned_ev = [None, None]
+        self._pin_turn = 0
+        self._last_greedy = None            # output of the last greedy decode step (source of token feedback)
         self.attn_group = 0
         if model.ops.is_cuda:
             self.attn_group = max(max(cfg.num_heads // tpw, 1) // max(cfg.num_kv_heads // tpw, 1), 1)
@@ -219,9 +223,13 @@ class Engine:
                 return b
         return rows
 
-    def forward(self, chunks: Sequence[SeqChunk], mode: str = "greedy", hidden_in: Optional[torch.Tensor] = None):
+    def forward(self, chunks: Sequence[SeqChunk], mode: str = "greedy", hidden_in: Optional[torch.Tensor] = None,
+                feedback: bool = False):
         """Run one step.  ``mode``: ``greedy`` → token ids ``[R]``; ``logits`` → fp32 ``[R, vocab]``;
-        ``hidden`` → final-normed hidden rows; ``none`` → headless (prefill chunk without a head)."""
+        ``hidden`` → final-normed hidden rows; ``none`` → headless (prefill chunk without a head).
+        ``feedback`` (captured decode steps only): the input token of row i is the token the previous captured step of
+        the same bucket produced for row i, taken on the device — the caller need not have read it yet."""
+        self.kv.flush()
         self.last_step_started = time.monotonic()
         self.last_step_what = f"{mode} rows={sum(len(c.tokens) for c in chunks)} seqs={len(chunks)}"
         decode_only = all(len(c.tokens) == 1 for c in chunks)
@@ -229,18 +237,37 @@ class Engine:
                      and self.model.is_first_stage and self.model.is_last_stage and self.model.ops.is_cuda)
         try:
             if graphable:
-                out = self._forward_graph(chunks)
+                out = self._forward_graph(chunks, feedback)
             else:
                 batch = self._build(chunks)
+                if feedback:
+                    if not (self.ecfg.feedback_eager and decode_only and self._last_greedy is not None):
+                        raise RuntimeError("token feedback needs a captured decode step")
+                    batch.tokens[:len(chunks)] = self._last_greedy[:len(chunks)].to(batch.tokens.dtype)
                 out = self._run(batch, mode, hidden_in)
+            if mode == "greedy" and decode_only:
+                self._last_greedy = out
         finally:
             self.steps += 1
             self.last_step_started = 0.0
         return out
 
     def _build(self, chunks: Sequence[SeqChunk]) -> StepBatch:
-        cfg = self.model.cfg
-        batch = build_batch(chunks, self.kv.block_table_host, self.device, self._pinned, attn_group=self.attn_group)
+        self.kv.flush()
+        pinned = None
+        if self._pinned is not None:
+            # two staging buffers in turn: a headless prefill step is not read back by the host, so its copy may still be
+            # queued when the next step is planned
+            self._pin_turn ^= 1
+            ev = self._pinned_ev[self._pin_turn]
+            if ev is not None:
+                ev.synchronize()
+            pinned = self._pinned[self._pin_turn]
+        batch = build_batch(chunks, self.kv.block_table_host, self.device, pinned, attn_group=self.attn_group)
+        if pinned is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._pinned_ev[self._pin_turn] = ev
         self.h2d_bytes += batch.h2d_bytes
         return batch
 
@@ -265,7 +292,14 @@ class Engine:
         raise ValueError(mode)
 
     # ------------------------------------------------------------------ CUDA graphs for decode steps
-    def _forward_graph(self, chunks: Sequence[SeqChunk]):
+    def can_feed_back(self, n_rows: int) -> bool:
+        """True when a decode step of ``n_rows`` rows would replay a captured graph (so ``feedback`` is available)."""
+        if self.ecfg.feedback_eager:
+            return self.model.is_first_stage and self.model.is_last_stage
+        return (self.ecfg.use_graphs and self.device.type == "cuda" and self.model.ops.is_cuda and self.model.is_first_stage
+                and self.model.is_last_stage and ("decode", self._bucket(n_rows)) in self._graphs)
+
+    def _forward_graph(self, chunks: Sequence[SeqChunk], feedback: bool = False):
         B = len(chunks)
         bucket = self._bucket(B)
         key = ("decode", bucket)
@@ -273,11 +307,13 @@ class Engine:
         if g is None:
             seen = self._seen.get(key, 0)
             self._seen[key] = seen + 1
+            if feedback:
+                raise RuntimeError("token feedback needs a captured decode step")
             if seen == 0:   # first sight: run eagerly (also warms allocator and lazy inits)
                 return self._run(self._build(chunks), "greedy")
             g = _Graph(self, bucket)
             self._graphs[key] = g
-        return g.replay(chunks)
+        return g.replay(chunks, feedback)
 
     def capture_decode_graphs(self, max_batch: Optional[int] = None) -> int:
         """Capture the decode-step graph of every batch bucket up front (server start-up), so that no request pays for a
@@ -339,7 +375,9 @@ class _Graph:
         n = bucket
         self.total = 4 * n + n + (n + 1) + n + n
         self.static = torch.zeros(self.total, dtype=torch.int32, device=dev)
-        self.stage = torch.zeros(self.total, dtype=torch.int32, pin_memory=True)
+        # two staging buffers: with token feedback the host may fill step k+1 while the copy of step k is still queued
+        self.stages = [torch.zeros(self.total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.turn = 0
         o = 0
         v = []
         for size in (n, n, n, n, n, n + 1, n, n):
@@ -352,14 +390,21 @@ class _Graph:
         self.batch.h_ctx_len = [1] * n
         self.batch.h_logit_rows = list(range(n))
         self.batch.max_ctx = eng.ecfg.max_model_len
-        self.batch.small_rows_max = max(eng.attn_group, 1)
+        from .batch import TINY_ROWS
+        g = max(eng.attn_group, 1)
+        if g <= TINY_ROWS:
+            self.batch.tiny_rows_max, self.batch.num_tiny = g, n
+        else:
+            self.batch.small_rows_max, self.batch.num_small = g, n
         self.graph = None
         self.out = None
         self.kernels = 0
 
-    def _fill(self, chunks: Sequence[SeqChunk]) -> int:
+    def _fill(self, chunks: Sequence[SeqChunk], feedback: bool = False) -> int:
         n, B = self.bucket, len(chunks)
-        s = self.stage.numpy()
+        self.turn ^= 1
+        stage = self.stages[self.turn]
+        s = stage.numpy()
         bt = self.eng.kv.block_table_host
         tok = np.fromiter((c.tokens[0] for c in chunks), np.int32, B)
         pos = np.fromiter((c.start_pos for c in chunks), np.int32, B)
@@ -376,12 +421,20 @@ class _Graph:
         s[5 * n:6 * n + 1] = qs
         s[6 * n + 1:6 * n + 1 + B] = pos + 1
         s[7 * n + 1:8 * n + 1] = np.minimum(np.arange(n, dtype=np.int32), max(B - 1, 0))
-        self.static.copy_(self.stage, non_blocking=True)
-        self.eng.h2d_bytes += self.total * 4
+        if feedback:
+            # everything but the tokens comes from the host; the tokens are the previous step's output, still on the device
+            self.static[n:].copy_(stage[n:], non_blocking=True)
+            self.static[:n].copy_(self.out)
+            self.eng.h2d_bytes += (self.total - n) * 4
+        else:
+            self.static.copy_(stage, non_blocking=True)
+            self.eng.h2d_bytes += self.total * 4
         return B
 
-    def replay(self, chunks: Sequence[SeqChunk]):
-        B = self._fill(chunks)
+    def replay(self, chunks: Sequence[SeqChunk], feedback: bool = False):
+        if feedback and self.graph is None:
+            raise RuntimeError("token feedback needs a captured decode step")
+        B = self._fill(chunks, feedback)
         if self.graph is None:
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()

@@ -272,20 +272,28 @@ class CudaOps:
         out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=self.device)
         B = batch.slots.numel()
         tiles = max((batch.max_ctx + 127) // 128, 1)
-        small = batch.small_rows_max if (batch.small_rows_max or batch.num_large) else group * batch.max_q_len
-        if small > 0:
+        # the decode kernel runs once per row tier: plain decode rows (<= 8 rows per kv head) take its two-CTAs-per-SM
+        # configuration, short multi-token sequences (verify rows, prompt tails) the wider one
+        tiers = []
+        if batch.tiny_rows_max:
+            tiers.append((1, batch.tiny_rows_max, batch.num_tiny))
+        if batch.small_rows_max:
+            tiers.append((batch.tiny_rows_max + 1 if batch.tiny_rows_max else 1, batch.small_rows_max, batch.num_small))
+        if not tiers and not batch.num_large:
+            tiers.append((1, group * batch.max_q_len, B))
+        for lo, hi, count in tiers:
             nmax = 16
-            rb = (small + nmax - 1) // nmax
-            work = B * Hkv * rb
+            rb = (hi + nmax - 1) // nmax
+            work = max(count, 1) * Hkv * rb
             sp = splits if splits > 0 else (1 if work >= 3 * self._sm else max(1, min(8, tiles, (3 * self._sm) // max(work, 1))))
             po = pm = None
             if sp > 1:
-                n = work * sp * nmax
+                n = B * Hkv * rb * sp * nmax
                 po = self._buf("attn_part_o", n * D * 4).view(torch.float32)
                 pm = self._buf("attn_part_ml", n * 2 * 4).view(torch.float32)
             self._check(self.lib.blz_attn_decode(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
                                                  _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), B, Hq, Hkv, D,
-                                                 kv.block_table.stride(0), scale, 1.0, 1.0, nmax, rb, 1, small, sp,
+                                                 kv.block_table.stride(0), scale, 1.0, 1.0, nmax, rb, lo, hi, sp,
                                                  _ptr(po), _ptr(pm), max_ctas, _ptr(self.attn_prof), self._stream()), "attn_decode")
             if sp > 1:
                 self.launches += 1

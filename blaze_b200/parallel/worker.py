@@ -18,13 +18,23 @@ class Leader:
     def __init__(self, engine, group):
         self.engine, self.group = engine, group
         self._forward = engine.forward
+        self._sent = {}          # row -> page list as the followers know it
         engine.forward = self.forward
 
-    def forward(self, chunks, mode="greedy", hidden_in=None):
-        plan = ("step", mode, [(c.slot, list(c.tokens), c.start_pos, c.want_logits) for c in chunks],
-                {r: list(s.pages) for r, s in self.engine.seqs.items()})
+    def forward(self, chunks, mode="greedy", hidden_in=None, feedback=False):
+        # only the rows whose page list changed since the last step travel (a decode step changes one row in sixteen)
+        changed, live = {}, self.engine.seqs
+        for r, s in live.items():
+            old = self._sent.get(r)
+            if old is None or len(old) != len(s.pages) or old != s.pages:
+                changed[r] = list(s.pages)
+                self._sent[r] = changed[r]
+        gone = [r for r in self._sent if r not in live]
+        for r in gone:
+            del self._sent[r]
+        plan = ("step", mode, [(c.slot, list(c.tokens), c.start_pos, c.want_logits) for c in chunks], changed, gone, feedback)
         self.group.broadcast_object(plan, 0)
-        return self._forward(chunks, mode, hidden_in)
+        return self._forward(chunks, mode, hidden_in, feedback)
 
     def quit(self):
         self.group.broadcast_object(("quit",), 0)
@@ -38,17 +48,20 @@ def follow(llm) -> int:
         msg = group.broadcast_object(None, 0)
         if msg[0] == "quit":
             return 0
-        _, mode, raw, pages = msg
+        _, mode, raw, changed, gone, feedback = msg
         # mirror the page tables (same allocator decisions are implied by copying rank 0's)
-        for row, pg in pages.items():
+        for row, pg in changed.items():
             s = eng.seqs.get(row)
             if s is None:
                 s = Seq(row=row)
                 eng.seqs[row] = s
             if pg != s.pages:
-                eng.kv.set_pages(row, pg, 0)
+                keep = 0
+                while keep < min(len(pg), len(s.pages)) and pg[keep] == s.pages[keep]:
+                    keep += 1
+                eng.kv.set_pages(row, pg[keep:], keep)
                 s.pages = list(pg)
-        for row in [r for r in eng.seqs if r not in pages]:
-            eng.seqs.pop(row)
+        for row in gone:
+            eng.seqs.pop(row, None)
         chunks = [SeqChunk(slot, toks, start, want) for slot, toks, start, want in raw]
-        eng.forward(chunks, mode)
+        eng.forward(chunks, mode, feedback=feedback)

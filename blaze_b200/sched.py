@@ -23,7 +23,7 @@ from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
 import torch
 
 from . import log
-from .batch import PAGE
+from .batch import PAGE, SeqChunk
 from .engine import Engine, OutOfPages, Seq, Snapshot
 from .sampler import Rng, SamplingParams, penalty_edits
 from .telemetry import Histogram
@@ -300,6 +300,7 @@ class SchedConfig:
     max_verify: int = 8
     eos_ids: Tuple[int, ...] = ()
     max_model_len: int = 4096
+    run_ahead: bool = True             # launch greedy decode step k+1 before reading step k (tokens fed back on the device)
 
 
 @dataclass
@@ -342,6 +343,14 @@ class Active:
     _started = False
 
 
+class _Ahead:
+    """A greedy decode step that was launched but whose tokens the host has not read yet."""
+    __slots__ = ("actives", "tokens", "event", "t0")
+
+    def __init__(self, actives, tokens, event, t0):
+        self.actives, self.tokens, self.event, self.t0 = actives, tokens, event, t0
+
+
 class Scheduler:
     def __init__(self, engine: Engine, cfg: SchedConfig, drafter=None, sample_fn=None):
         self.engine, self.cfg, self.drafter = engine, cfg, drafter
@@ -360,6 +369,7 @@ class Scheduler:
         self.step_ms = Histogram.latency()
         self.sample_fn = sample_fn
         self.on_step: Optional[Callable[[float, int], None]] = None
+        self._ahead: Optional[_Ahead] = None
         from .suffix import SuffixIndex
         self.suffix = SuffixIndex() if cfg.spec_method == "suffix" else None
 
@@ -381,7 +391,7 @@ class Scheduler:
 
     @property
     def idle(self) -> bool:
-        return not (self.active or self.waiting or self.preempted) and self.inbox.empty()
+        return not (self.active or self.waiting or self.preempted or self._ahead) and self.inbox.empty()
 
     def run_until_idle(self, max_steps: int = 1 << 30) -> None:
         n = 0
@@ -522,7 +532,81 @@ class Scheduler:
         return True
 
     # ================================================================== one iteration
+    # ================================================================== run-ahead decode
+    # While every active request is a plain greedy decoder, the next step's input tokens are this step's output, and they
+    # are already on the device.  So step k+1 is launched (tokens fed back on the device) before the host reads step k:
+    # the host's bookkeeping for step k then overlaps the GPU's work on step k+1.  A request that stops on a token the
+    # host had not seen yet (EOS) has taken part in one step too many; its row is ignored and its pages are released
+    # — later owners of those pages write them after that step in stream order.
+    def _plain_greedy(self, a: Active) -> bool:
+        p, r = a.req.params, a.req
+        return not (p.needs_candidates() or r.constraint is not None or r.embed_only or r.think is not None or a.forced
+                    or p.logprobs is not None)
+
+    def _continues(self, a: Active, in_flight: int) -> bool:
+        """True when ``a`` certainly wants another token after the ``in_flight`` tokens that are not appended yet."""
+        n = len(a.tokens) + in_flight
+        limit = min(self.cfg.max_model_len, self.engine.max_pages_per_seq * PAGE)
+        return n - a.n_prompt < a.req.params.max_tokens and n + 1 < limit
+
+    def _hand_off(self, actives: List[Active], out: torch.Tensor, t0: float) -> _Ahead:
+        if out.device.type == "cuda":
+            host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+            host.copy_(out, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        else:
+            host, ev = out.clone(), None
+        self.engine.d2h_bytes += out.numel() * out.element_size()
+        return _Ahead(actives, host, ev, t0)
+
+    def _launch_ahead(self, actives: List[Active]) -> Optional[_Ahead]:
+        eng = self.engine
+        t0 = time.monotonic()
+        try:
+            for a in actives:
+                eng.reserve(a.seq, a.computed + 2)
+        except OutOfPages:
+            return None
+        chunks = []
+        for a in actives:
+            chunks.append(SeqChunk(slot=a.seq.row, tokens=[0], start_pos=a.computed + 1, want_logits=1))
+            a.seq.length = a.computed + 2
+        out = eng.forward(chunks, "greedy", feedback=True)
+        return self._hand_off(actives, out, t0)
+
+    def _consume_ahead(self, ah: _Ahead) -> None:
+        if ah.event is not None:
+            ah.event.synchronize()
+        toks = ah.tokens.tolist()
+        n = 0
+        for a, tok in zip(ah.actives, toks):
+            if a.seq is None:           # stopped, aborted or preempted while the step was in flight
+                continue
+            a.computed += 1
+            a._started = True
+            n += 1
+            self._append(a, [tok], [])
+        dt = (time.monotonic() - ah.t0) * 1e3
+        self.step_ms.observe(dt / 1e3)
+        self.stats.steps += 1
+        if self.on_step:
+            self.on_step(dt, n)
+
+    def _step_ahead(self) -> None:
+        ah = self._ahead
+        self._admit()
+        nxt = None
+        same = len(self.active) == len(ah.actives) and all(x is y for x, y in zip(self.active, ah.actives))
+        if same and all(self._continues(a, 1) for a in ah.actives):
+            nxt = self._launch_ahead(ah.actives)
+        self._ahead = None
+        self._consume_ahead(ah)
+        self._ahead = nxt
+
     def step(self) -> None:
+        if self._ahead is not None:
+            return self._step_ahead()
         self._admit()
         if not self.active:
             return
@@ -585,6 +669,10 @@ class Scheduler:
         if self.drafter is not None and mode in ("greedy", "logits"):
             mode = "greedy_hidden" if mode == "greedy" else "both"      # the drafter reads the target's hidden rows
         out = eng.forward(chunks, mode)
+        if (mode == "greedy" and cfg.run_ahead and len(plan) == len(self.active) and all(len(t) == 1 for _, t, _, _ in plan)
+                and eng.can_feed_back(len(plan)) and all(self._plain_greedy(a) and self._continues(a, 1) for a, _, _, _ in plan)):
+            self._ahead = self._hand_off([a for a, _, _, _ in plan], out, t0)
+            return
         # ---- consume results
         row = 0
         rows_total = sum(len(t) for _, t, _, _ in plan)

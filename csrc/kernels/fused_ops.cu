@@ -222,11 +222,188 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
   }
 }
 
+// ---------------------------------------------------------------------------------------------- register-resident rows
+// Fast path of the two row kernels above for widths up to 6 chunks of 8 elements per thread: the row never touches
+// shared memory, every load of a thread is issued before the first use, and the quantiser works on the registers
+// (a 16-element NVFP4 block is two neighbouring threads, a 32-element MXFP8 block four).
+__device__ __forceinline__ uint32_t pack_e2m1x8(const float (&v)[8], float inv) {
+  uint32_t r;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(r)
+      : "f"(v[0] * inv), "f"(v[1] * inv), "f"(v[2] * inv), "f"(v[3] * inv), "f"(v[4] * inv), "f"(v[5] * inv), "f"(v[6] * inv),
+        "f"(v[7] * inv));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_e4m3x4_f(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// Quantise this thread's 8 elements [e0, e0+8) of row t.  Every lane of the warp must call it (shuffles); `valid` gates the stores.
+template <int QUANT>
+__device__ __forceinline__ void quant_store8(const uint4& packed, bool valid, int t, int e0, int W, float g, uint8_t* q_out,
+                                             uint8_t* sf_out, int ct) {
+  const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&packed);
+  float v[8];
+  float bm = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { v[j] = valid ? bf2f(e[j]) : 0.f; bm = fmaxf(bm, fabsf(v[j])); }
+  bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+  if (QUANT == 1) {
+    const uint8_t sf = f2e4m3(bm / 6.f / g);
+    const float denom = e4m32f(sf) * g;
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    const uint32_t codes = pack_e2m1x8(v, inv);
+    if (valid) {
+      *reinterpret_cast<uint32_t*>(q_out + (size_t)t * (W / 2) + e0 / 2) = codes;
+      if ((e0 & 15) == 0) sf_out[sf_offset(t, e0 >> 4, ct)] = sf;
+    }
+  } else {
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+    bm = fmaxf(bm, 1.17549435e-38f);
+    int ex = (int)ceilf(log2f(bm / 448.f));
+    ex = max(-127, min(127, ex));
+    const float inv = exp2f((float)-ex);
+    if (valid) {
+      *reinterpret_cast<uint2*>(q_out + (size_t)t * W + e0) =
+          make_uint2(pack_e4m3x4_f(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                     pack_e4m3x4_f(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+      if ((e0 & 31) == 0) sf_out[sf_offset(t, e0 >> 5, ct)] = (uint8_t)(ex + 127);
+    }
+  }
+}
+
+template <int QUANT, int CH>
+__global__ void __launch_bounds__(512) rmsnorm_reg_kernel(__nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+                                                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                                            uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out,
+                                                            float* __restrict__ row_scale, int H, float eps, int zero_centered,
+                                                            int sf_col_tiles, int zero_src) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  __nv_bfloat16* xr = x + (size_t)t * H;
+  __nv_bfloat16* rr = residual ? residual + (size_t)t * H : nullptr;
+  uint4 u[CH], ur[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    u[c] = ur[c] = make_uint4(0, 0, 0, 0);
+    if (i < H) {
+      u[c] = *reinterpret_cast<const uint4*>(xr + i);
+      if (rr) ur[c] = *reinterpret_cast<const uint4*>(rr + i);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u[c]);
+    if (i < H) {
+      if (zero_src) *reinterpret_cast<uint4*>(xr + i) = make_uint4(0, 0, 0, 0);
+      if (rr) {
+        const __nv_bfloat16* er = reinterpret_cast<const __nv_bfloat16*>(&ur[c]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(bf2f(e[j]) + bf2f(er[j]));
+        *reinterpret_cast<uint4*>(rr + i) = u[c];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float f = bf2f(e[j]); ss += f * f; }
+  }
+  ss = block_reduce(ss, red, false);
+  const float rstd = rsqrtf(ss / H + eps);
+  float amax = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u[c]);
+    const uint4 uw = i < H ? *reinterpret_cast<const uint4*>(w + i) : make_uint4(0, 0, 0, 0);   // the weight row stays in L1/L2
+    const __nv_bfloat16* ew = reinterpret_cast<const __nv_bfloat16*>(&uw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float wf = bf2f(ew[j]) + (zero_centered ? 1.f : 0.f);
+      e[j] = __float2bfloat16(bf2f(e[j]) * rstd * wf);
+      amax = fmaxf(amax, fabsf(bf2f(e[j])));
+    }
+    if (QUANT == 0 && i < H) *reinterpret_cast<uint4*>(out + (size_t)t * H + i) = u[c];
+  }
+  if (QUANT == 0) return;
+  float g = 1.f;
+  if (QUANT == 1) {
+    amax = block_reduce(amax, red, true);
+    g = fmaxf(amax / (6.f * 448.f), 1e-30f);
+    if (threadIdx.x == 0) row_scale[t] = g;
+  }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    quant_store8<QUANT>(u[c], i < H, t, i, H, g, q_out, sf_out, sf_col_tiles);
+  }
+}
+
+template <int MODE, int CH>
+__global__ void __launch_bounds__(512) swiglu_reg_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                                           uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out,
+                                                           float* __restrict__ row_scale, int I, int src_is_act, int sf_col_tiles) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* g = gu + (size_t)t * (src_is_act ? I : 2 * I);
+  const __nv_bfloat16* up = g + I;
+  uint4 a[CH], b[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    a[c] = b[c] = make_uint4(0, 0, 0, 0);
+    if (i < I) {
+      a[c] = *reinterpret_cast<const uint4*>(g + i);
+      if (!src_is_act) b[c] = *reinterpret_cast<const uint4*>(up + i);
+    }
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    __nv_bfloat16* eg = reinterpret_cast<__nv_bfloat16*>(&a[c]);
+    const __nv_bfloat16* eu = reinterpret_cast<const __nv_bfloat16*>(&b[c]);
+    if (!src_is_act) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float x = bf2f(eg[j]);
+        eg[j] = __float2bfloat16(x / (1.f + __expf(-x)) * bf2f(eu[j]));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(bf2f(eg[j])));
+    if (MODE == 0 && i < I) *reinterpret_cast<uint4*>(out + (size_t)t * I + i) = a[c];
+  }
+  if (MODE == 0) return;
+  float gs = 1.f;
+  if (MODE == 1) {
+    amax = block_reduce(amax, red, true);
+    gs = fmaxf(amax / (6.f * 448.f), 1e-30f);
+    if (threadIdx.x == 0) row_scale[t] = gs;
+  }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    quant_store8<MODE>(a[c], i < I, t, i, I, gs, q_out, sf_out, sf_col_tiles);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- attention prep
-// One warp per (token, head).  Heads 0..Hq-1 are query heads, then Hkv key heads, then Hkv value heads.
-// qkv row layout: [q heads (x2 when gated: q | gate per head)] [k heads] [v heads].
+// One CTA per token; its warps walk the token's heads.  Heads 0..Hq-1 are query heads, then Hkv key heads, then Hkv
+// value heads.  qkv row layout: [q heads (x2 when gated: q | gate per head)] [k heads] [v heads].  The rotary
+// sine/cosine pairs of the token are computed once into shared memory and reused by every q and k head.
 template <int D>
-__global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+__global__ void __launch_bounds__(256) attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                                  __nv_bfloat16* __restrict__ gate_out, uint8_t* __restrict__ kv_pool,
                                  const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                                  const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
@@ -234,81 +411,105 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfl
                                  float eps, float rope_scale, int gated, int zero_centered, float k_scale_inv,
                                  float v_scale_inv) {
   constexpr int VPL = D / 32;
-  const int lane = threadIdx.x & 31;
-  const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  __shared__ float2 cs[D / 2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int t = blockIdx.x;
   const int heads = Hq + 2 * Hkv;
-  if (wid >= T * heads) return;
-  const int t = wid / heads, h = wid % heads;
+  const int half = rot_dim / 2;
+  {
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float s, c;
+      sincosf(pos * inv_freq[i], &s, &c);
+      cs[i] = make_float2(c * rope_scale, s * rope_scale);
+    }
+  }
+  __syncthreads();
   const int qw = Hq * D * (gated ? 2 : 1);
   const size_t row_w = (size_t)qw + 2 * (size_t)Hkv * D;
-  const __nv_bfloat16* src;
-  int kind;  // 0 q, 1 k, 2 v
-  if (h < Hq) { kind = 0; src = qkv + t * row_w + (size_t)h * D * (gated ? 2 : 1); }
-  else if (h < Hq + Hkv) { kind = 1; src = qkv + t * row_w + qw + (size_t)(h - Hq) * D; }
-  else { kind = 2; src = qkv + t * row_w + qw + (size_t)Hkv * D + (size_t)(h - Hq - Hkv) * D; }
-  float v[VPL];
+  const __nv_bfloat16* row = qkv + t * row_w;
+  const int lanes_half = half / VPL;          // partner lane distance (power of two)
+  const int slot = slot_mapping[t];
+  float nwq[VPL], nwk[VPL];
 #pragma unroll
-  for (int j = 0; j < VPL; ++j) v[j] = bf2f(src[lane * VPL + j]);
-  if (kind == 0 && gated) {
-#pragma unroll
-    for (int j = 0; j < VPL; ++j) gate_out[((size_t)t * Hq + h) * D + lane * VPL + j] = src[D + lane * VPL + j];
+  for (int j = 0; j < VPL; ++j) {
+    nwq[j] = q_norm_w ? bf2f(q_norm_w[lane * VPL + j]) + (zero_centered ? 1.f : 0.f) : 0.f;
+    nwk[j] = k_norm_w ? bf2f(k_norm_w[lane * VPL + j]) + (zero_centered ? 1.f : 0.f) : 0.f;
   }
-  if (kind < 2) {
-    const __nv_bfloat16* nw = kind == 0 ? q_norm_w : k_norm_w;
-    if (nw) {
-      float ss = 0.f;
+  for (int h = warp; h < heads; h += nwarps) {
+    const __nv_bfloat16* src;
+    int kind;  // 0 q, 1 k, 2 v
+    if (h < Hq) { kind = 0; src = row + (size_t)h * D * (gated ? 2 : 1); }
+    else if (h < Hq + Hkv) { kind = 1; src = row + qw + (size_t)(h - Hq) * D; }
+    else { kind = 2; src = row + qw + (size_t)Hkv * D + (size_t)(h - Hq - Hkv) * D; }
+    if (kind != 0 && slot < 0) continue;
+    __align__(16) __nv_bfloat16 raw[VPL];
+    if constexpr (VPL == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src + lane * 4);
+    else if constexpr (VPL == 8) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src + lane * 8);
+    else *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src + lane * 2);
+    float v[VPL];
 #pragma unroll
-      for (int j = 0; j < VPL; ++j) ss += v[j] * v[j];
-      ss = warp_sum(ss);
-      const float rstd = rsqrtf(ss / D + eps);
-#pragma unroll
-      for (int j = 0; j < VPL; ++j)
-        v[j] = bf2f(__float2bfloat16(v[j] * rstd * (bf2f(nw[lane * VPL + j]) + (zero_centered ? 1.f : 0.f))));
+    for (int j = 0; j < VPL; ++j) v[j] = bf2f(raw[j]);
+    if (kind == 0 && gated) {
+      __nv_bfloat16* gdst = gate_out + ((size_t)t * Hq + h) * D + lane * VPL;
+      if constexpr (VPL == 4) *reinterpret_cast<uint2*>(gdst) = *reinterpret_cast<const uint2*>(src + D + lane * 4);
+      else if constexpr (VPL == 8) *reinterpret_cast<uint4*>(gdst) = *reinterpret_cast<const uint4*>(src + D + lane * 8);
+      else *reinterpret_cast<uint32_t*>(gdst) = *reinterpret_cast<const uint32_t*>(src + D + lane * 2);
     }
-    // NeoX rotary over the first rot_dim dims: pairs (i, i + half)
-    const int half = rot_dim / 2;
-    const int lanes_half = half / VPL;          // partner lane distance (power of two)
-    const float pos = (float)positions[t];
+    if (kind < 2) {
+      if (kind == 0 ? q_norm_w != nullptr : k_norm_w != nullptr) {
+        float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) {
-      const int i = lane * VPL + j;
-      const float other = __shfl_xor_sync(0xffffffffu, v[j], lanes_half);
-      if (i < rot_dim) {
-        const int fi = i < half ? i : i - half;
-        float s, c;
-        sincosf(pos * inv_freq[fi], &s, &c);
-        s *= rope_scale; c *= rope_scale;
-        v[j] = i < half ? v[j] * c - other * s : v[j] * c + other * s;
+        for (int j = 0; j < VPL; ++j) ss += v[j] * v[j];
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) v[j] = bf2f(__float2bfloat16(v[j] * rstd * (kind == 0 ? nwq[j] : nwk[j])));
+      }
+      // NeoX rotary over the first rot_dim dims: pairs (i, i + half)
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int i = lane * VPL + j;
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], lanes_half);
+        if (i < rot_dim) {
+          const float2 c = cs[i < half ? i : i - half];
+          v[j] = i < half ? v[j] * c.x - other * c.y : v[j] * c.x + other * c.y;
+        }
       }
     }
-  }
-  if (kind == 0) {
+    if (kind == 0) {
+      __align__(16) __nv_bfloat16 o[VPL];
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) q_out[((size_t)t * Hq + h) * D + lane * VPL + j] = __float2bfloat16(v[j]);
-    return;
-  }
-  const int slot = slot_mapping[t];
-  if (slot < 0) return;
-  const int page = slot >> 4, tp = slot & 15;
-  const int kh = kind == 1 ? h - Hq : h - Hq - Hkv;
-  uint8_t* blk = kv_pool + ((size_t)page * Hkv + kh) * (size_t)(2 * 16 * D);
-  if (kind == 1) {
-#pragma unroll
-    for (int j = 0; j < VPL; ++j) {
-      const int i = lane * VPL + j;
-      const float r = bf2f(__float2bfloat16(v[j]));
-      blk[(tp >> 3) * 8 * D + (i >> 4) * 128 + (tp & 7) * 16 + (i & 15)] = f2e4m3(r * k_scale_inv);
+      for (int j = 0; j < VPL; ++j) o[j] = __float2bfloat16(v[j]);
+      __nv_bfloat16* dst = q_out + ((size_t)t * Hq + h) * D + lane * VPL;
+      if constexpr (VPL == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+      else if constexpr (VPL == 8) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+      else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(o);
+      continue;
     }
-  } else {
+    const int page = slot >> 4, tp = slot & 15;
+    const int kh = kind == 1 ? h - Hq : h - Hq - Hkv;
+    uint8_t* blk = kv_pool + ((size_t)page * Hkv + kh) * (size_t)(2 * 16 * D);
+    if (kind == 1) {
+      // the lane's VPL dims are consecutive bytes of one 16-byte core-matrix row
+      __align__(8) uint8_t b[VPL];
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) {
-      const int i = lane * VPL + j;
-      blk[16 * D + i * 16 + tp] = f2e4m3(v[j] * v_scale_inv);
+      for (int j = 0; j < VPL; ++j) b[j] = f2e4m3(bf2f(__float2bfloat16(v[j])) * k_scale_inv);
+      const int i0 = lane * VPL;
+      uint8_t* dst = blk + (tp >> 3) * 8 * D + (i0 >> 4) * 128 + (tp & 7) * 16 + (i0 & 15);
+      if constexpr (VPL == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(b);
+      else if constexpr (VPL == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(b);
+      else *reinterpret_cast<uint16_t*>(dst) = *reinterpret_cast<const uint16_t*>(b);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int i = lane * VPL + j;
+        blk[16 * D + i * 16 + tp] = f2e4m3(v[j] * v_scale_inv);
+      }
     }
   }
 }
 
-// ---------------------------------------------------------------------------------------------- small elementwise
 __global__ void mul_sigmoid_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate, size_t n) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     x[i] = __float2bfloat16(bf2f(x[i]) / (1.f + __expf(-bf2f(gate[i]))));
@@ -386,6 +587,19 @@ static void configure_once() {
   attr = true;
 }
 
+// threads and chunks per thread of the register-resident row kernels; chunks == 0: width not covered
+static inline void reg_shape(int W, int* threads, int* chunks) {
+  *threads = W <= 12288 ? 256 : 512;
+  const int ch = (W + *threads * 8 - 1) / (*threads * 8);
+  *chunks = (W % 32 == 0 && ch <= 6) ? ch : 0;
+}
+
+#define BLZ_CH_SWITCH(ch, CALL)                                                                    \
+  switch (ch) {                                                                                     \
+    case 1: CALL(1); break; case 2: CALL(2); break; case 3: CALL(3); break; case 4: CALL(4); break; \
+    case 5: CALL(5); break; default: CALL(6); break;                                                \
+  }
+
 static inline int norm_threads(int H) {
   int t = H / 8;
   t = (t + 31) / 32 * 32;
@@ -408,6 +622,17 @@ BLZ_API int blz_rmsnorm(void* x, void* residual, const void* w, void* out, void*
   const int thr = norm_threads(H);
   const size_t sm = (size_t)H * 2;
   const int ct = quant == 1 ? (H + 63) / 64 : (H + 127) / 128;
+  int rt, ch;
+  reg_shape(H, &rt, &ch);
+  if (ch) {
+#define BLZ_RN(C)                                                                                                              \
+  if (quant == 0) rmsnorm_reg_kernel<0, C><<<T, rt, 0, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, nullptr, nullptr, nullptr, H, eps, zero_centered, 0, zero_src); \
+  else if (quant == 1) rmsnorm_reg_kernel<1, C><<<T, rt, 0, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src); \
+  else rmsnorm_reg_kernel<2, C><<<T, rt, 0, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src)
+    BLZ_CH_SWITCH(ch, BLZ_RN)
+#undef BLZ_RN
+    return (int)cudaGetLastError();
+  }
   if (quant == 0)
     rmsnorm_kernel<0><<<T, thr, sm, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, nullptr, nullptr, nullptr, H, eps, zero_centered, 0, zero_src);
   else if (quant == 1)
@@ -426,6 +651,17 @@ BLZ_API int blz_swiglu(const void* gu, void* out, void* q_out, void* sf_out, flo
   const size_t sm = (size_t)I * 2;
   const int ct = mode == 1 ? (I + 63) / 64 : (I + 127) / 128;
   configure_once();
+  int rt, ch;
+  reg_shape(I, &rt, &ch);
+  if (ch) {
+#define BLZ_SW(C)                                                                                                              \
+  if (mode == 0) swiglu_reg_kernel<0, C><<<T, rt, 0, s>>>((const bf16*)gu, (bf16*)out, nullptr, nullptr, nullptr, I, src_is_act, 0); \
+  else if (mode == 1) swiglu_reg_kernel<1, C><<<T, rt, 0, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct); \
+  else swiglu_reg_kernel<2, C><<<T, rt, 0, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct)
+    BLZ_CH_SWITCH(ch, BLZ_SW)
+#undef BLZ_SW
+    return (int)cudaGetLastError();
+  }
   if (mode == 0) swiglu_kernel<0><<<T, thr, 0, s>>>((const bf16*)gu, (bf16*)out, nullptr, nullptr, nullptr, I, src_is_act, 0);
   else if (mode == 1) swiglu_kernel<1><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct);
   else swiglu_kernel<2><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct);
@@ -440,9 +676,8 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
   const int half = rot_dim / 2, vpl = D / 32;
   if ((D != 64 && D != 128 && D != 256) || rot_dim > D || half % vpl || ((half / vpl) & (half / vpl - 1)) || half / vpl > 16)
     return (int)cudaErrorInvalidValue;
-  const int warps = T * (Hq + 2 * Hkv);
-  const int wpb = 8;
-  const int grid = (warps + wpb - 1) / wpb;
+  const int wpb = (Hq + 2 * Hkv) >= 8 ? 8 : (Hq + 2 * Hkv);
+  const int grid = T;
 #define BLZ_PREP(DD)                                                                                                 \
   attn_prep_kernel<DD><<<grid, wpb * 32, 0, s>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)gate_out, (uint8_t*)kv_pool, \
                                                  positions, slot_mapping, inv_freq, (const bf16*)q_norm_w,            \

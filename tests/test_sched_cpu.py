@@ -122,3 +122,56 @@ def test_mtp_drafter_keeps_outputs_exact():
     assert [o.token_ids for o in got] == want
     assert llm.sched.stats.draft_tokens > 0 and d.proposed > 0
     assert not d.states and d.engine.pages.free_count == d.engine.num_pages - 1
+
+
+def _ahead_llm(**kw):
+    llm = _llm(**kw)
+    llm.engine.ecfg.feedback_eager = True        # token feedback without captured graphs, so the loop runs on CPU
+    return llm
+
+
+def test_run_ahead_decode_is_exact_and_used():
+    ps = _prompts(5, 20, seed=11)
+    want = [o.token_ids for o in _llm().generate(ps, GREEDY)]
+    llm = _ahead_llm()
+    fed = []
+    fwd = llm.engine.forward
+    llm.engine.forward = lambda chunks, mode="greedy", hidden_in=None, feedback=False: (fed.append(feedback), fwd(chunks, mode, hidden_in, feedback))[1]
+    got = llm.generate(ps, GREEDY)
+    assert [o.token_ids for o in got] == want
+    assert sum(fed) >= 8, "decode steps should have been launched ahead of the host"
+    assert llm.engine.pages.free_count + sum(len(e.snap.pages) for e in llm.sched.cache.entries) >= 1
+
+
+def test_run_ahead_stops_on_eos_seen_late_and_admits_new_requests():
+    ps = _prompts(4, 24, seed=12)
+    ref = _llm().generate(ps, SamplingParams(temperature=0.0, max_tokens=20))
+    # make a token that request 0 produces mid-way its stop token: the host learns of it one step late
+    stop = ref[0].token_ids[7]
+    sp = [SamplingParams(temperature=0.0, max_tokens=20, stop_token_ids=[stop])] + [SamplingParams(temperature=0.0, max_tokens=20)] * 3
+    want = _llm().generate(ps, sp)
+    llm = _ahead_llm(max_seqs=4)
+    extra = _prompts(1, 10, seed=13)[0]
+    outs = {}
+
+    def late(ev):
+        outs.setdefault(ev.request_id, []).extend(ev.tokens or [])
+
+    from blaze_b200.sched import GenRequest
+    n = {"steps": 0}
+    orig = llm.sched.step
+
+    def step():
+        n["steps"] += 1
+        if n["steps"] == 6:      # arrives while steps are in flight
+            llm.sched.submit(GenRequest("late", extra, SamplingParams(temperature=0.0, max_tokens=6), sink=late))
+        orig()
+
+    llm.sched.step = step
+    got = llm.generate(ps, sp)
+    assert [o.token_ids for o in got] == [o.token_ids for o in want]
+    assert got[0].finish_reason == "stop" and len(got[0].token_ids) <= 8
+    solo = _llm().generate([extra], SamplingParams(temperature=0.0, max_tokens=6))[0]
+    assert outs["late"] == solo.token_ids
+    llm.sched.cache.clear()
+    assert llm.engine.pages.free_count == llm.engine.num_pages - 1
