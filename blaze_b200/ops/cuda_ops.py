@@ -7,6 +7,8 @@ one kernel, one attention kernel for prefill / decode / verify rows.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 from typing import Dict, Optional, Tuple
 
@@ -43,7 +45,17 @@ class CudaOps:
         lib = self.lib
         lib.blz_gemm_tc.restype = _c.c_int
         lib.blz_gemm_tc.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
-                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, VP]
+                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_gemm_wide.restype = _c.c_int
+        lib.blz_gemm_wide.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
+                                      _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_longlong, VP,
+                                      _c.c_int, _c.c_int, VP]
+        lib.blz_gemm_wide_ksplit.restype = _c.c_int
+        lib.blz_gemm_wide_ksplit.argtypes = [_c.c_int, _c.c_int, _c.c_int]
+        self._wide_ok = os.environ.get("BLAZE_GEMM_WIDE", "1") != "0"
+        # tile-major weight storage measured no faster than row-major on B200 and keeps a second copy of the weights: opt-in
+        self._tiled_ok = os.environ.get("BLAZE_TILED_WEIGHTS", "0") == "1"
+        self._wide_ws = self._wide_ctr = None
         lib.blz_embed.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_rmsnorm.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_swiglu.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
@@ -92,9 +104,36 @@ class CudaOps:
         return b
 
     # ------------------------------------------------------------------ weights → kernel layouts
-    def pack(self, lin: Linear):
+    @staticmethod
+    def tile_major(w: torch.Tensor) -> Tuple[torch.Tensor, int]:
+        """Row-major weight bytes [N, row bytes] -> [ceil(N/128), kt, 128, 128] (zero padded): every 128-row x 128-byte
+        operand tile becomes one contiguous 16 KB run, so a CTA streaming a weight tile reads DRAM pages end to end
+        instead of touching a new page for every 128 bytes."""
+        b = w.contiguous().view(torch.uint8).view(w.shape[0], -1)
+        N, KB = b.shape
+        NP, KP = (N + 127) // 128 * 128, (KB + 127) // 128 * 128
+        if (NP, KP) != (N, KB):
+            pad = torch.zeros(NP, KP, dtype=torch.uint8, device=b.device)
+            pad[:N, :KB] = b
+            b = pad
+        kt = KP // 128
+        return b.view(NP // 128, 128, kt, 128).permute(0, 2, 1, 3).contiguous(), kt
+
+    def pack(self, lin: Linear, tiled: Optional[bool] = None):
+        """``tiled`` (default: off unless BLAZE_TILED_WEIGHTS=1): store the weight tile-major (see ``tile_major``); the grouped
+        expert GEMM asks for row-major."""
         if lin.cuda_pack is not None:
             return lin.cuda_pack
+        pk = self._pack(lin)
+        if tiled is None:
+            tiled = self._tiled_ok
+        pk["kt"] = 0
+        if tiled:
+            pk["w"], pk["kt"] = self.tile_major(pk["w"])
+        lin.cuda_pack = pk
+        return pk
+
+    def _pack(self, lin: Linear):
         dev = self.device
         if lin.fmt == Format.DENSE:
             pk = {"kind": 0, "w": lin.w.to(dev, torch.bfloat16).contiguous(), "sf": None, "alpha": None}
@@ -120,7 +159,6 @@ class CudaOps:
             pk = {"kind": 3, "w": lin.w.to(dev).view(torch.uint8).contiguous(), "sf": None,
                   "alpha": lin.alpha.to(dev, torch.float32).contiguous()}
         pk["bias"] = None if lin.bias is None else lin.bias.to(dev, torch.bfloat16).contiguous()
-        lin.cuda_pack = pk
         return pk
 
     # ------------------------------------------------------------------ activation quantisation
@@ -176,7 +214,12 @@ class CudaOps:
                                          _ptr(qa.row_scale), T, H, eps, int(zero_centered), mode, int(zero_src), self._stream()), "rmsnorm_q")
         return qa, new_res
 
-    def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0):
+    WIDE_WS_BYTES = 40 << 20
+
+    def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0,
+               wide: Optional[bool] = None, ksplit: int = 0):
+        """``wide``: None = choose; False = the 128-column kernel (needed by the fused all-reduce epilogue); True = insist on
+        the wide-N kernel (raises when the shape is not covered)."""
         pk = self.pack(lin)
         kind = pk["kind"]
         f32 = out_dtype == torch.float32
@@ -199,10 +242,39 @@ class CudaOps:
         if M == 0:
             return out
         w = pk["w"]
-        ldb = w.shape[1] * w.element_size()
+        kt = pk.get("kt", 0)
+        ldb = 128 if kt else w.shape[1] * w.element_size()
+        if wide is None:
+            # Measured on B200 (Qwen3-8B shapes, captured-graph timing): 256-feature tiles win for block-scaled prefill GEMMs
+            # (NVFP4 2048x24576x4096: 156 -> 119 us); the swapped orientation wins for the very wide bf16 head
+            # (256x151936x4096: 346 -> 315 us) but not for the per-layer decode GEMMs, which stay on the 128-column kernel.
+            wide = self._wide_ok and bn == 0 and ((M <= 256 and kind == 0 and lin.N >= 32768)
+                                                  or (kind in (1, 2) and lin.N % 256 == 0 and M > 256))
+        if wide:
+            swap = M <= 256
+            ks, ws, ctr = 1, None, None
+            if swap:
+                tok = 64 if M <= 64 else (128 if M <= 128 else 256)
+                tiles = (lin.N + 127) // 128
+                k_tiles = (lin.K + (64 if kind == 0 else 256 if kind == 1 else 128) - 1) // (64 if kind == 0 else 256 if kind == 1 else 128)
+                ks = ksplit or 1          # the split along K is opt-in: its workspace round trip costs more than it saves so far
+                while ks > 1 and tiles * ks * 128 * tok * 4 > self.WIDE_WS_BYTES:
+                    ks -= 1
+                if ks > 1:
+                    if self._wide_ws is None:
+                        self._wide_ws = torch.empty(self.WIDE_WS_BYTES, dtype=torch.uint8, device=self.device)
+                        self._wide_ctr = torch.zeros(8192, dtype=torch.int32, device=self.device)
+                    if tiles > self._wide_ctr.numel():
+                        ks = 1
+                    ws, ctr = self._wide_ws, self._wide_ctr
+            self._check(self.lib.blz_gemm_wide(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), out.stride(0), M, lin.N, lin.K,
+                                               _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
+                                               int(f32), int(swap), ks, _ptr(ws), self.WIDE_WS_BYTES if ws is not None else 0,
+                                               _ptr(ctr), max_ctas, kt, self._stream()), f"gemm_wide kind {kind}")
+            return out
         self._check(self.lib.blz_gemm_tc(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), out.stride(0), M, lin.N, lin.K,
                                          _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
-                                         int(f32), bn, max_ctas, VP(0), 0, self._stream()), f"gemm kind {kind}")
+                                         int(f32), bn, max_ctas, VP(0), 0, kt, self._stream()), f"gemm kind {kind}")
         return out
 
     def silu_mul(self, gu, quant_for: Optional[Linear] = None):
@@ -342,10 +414,10 @@ class CudaOps:
             return ex.cuda_pack
 
         def stack(lins):
-            pk0 = self.pack(lins[0])
+            pk0 = self.pack(lins[0], tiled=False)
             kind = pk0["kind"]
-            w = torch.cat([self.pack(l)["w"] for l in lins])
-            alpha = torch.cat([self.pack(l)["alpha"] for l in lins]) if pk0["alpha"] is not None else None
+            w = torch.cat([self.pack(l, tiled=False)["w"] for l in lins])
+            alpha = torch.cat([self.pack(l, tiled=False)["alpha"] for l in lins]) if pk0["alpha"] is not None else None
             sf = None
             if kind in (1, 2):
                 l0 = lins[0]
@@ -355,7 +427,7 @@ class CudaOps:
                 if kind == 1:
                     raw = torch.cat([l.sf.to(self.device).view(torch.uint8) for l in lins])
                 else:
-                    raw = torch.cat([quant.unswizzle_sf_128x4(self.pack(l)["sf"], (l.N + 255) // 256 * 256, per)[:l.N] for l in lins])
+                    raw = torch.cat([quant.unswizzle_sf_128x4(self.pack(l, tiled=False)["sf"], (l.N + 255) // 256 * 256, per)[:l.N] for l in lins])
                 rows = (raw.shape[0] + 255) // 256 * 256
                 buf = torch.zeros(rows, per, dtype=torch.uint8, device=self.device)
                 buf[:raw.shape[0]] = raw
@@ -378,7 +450,7 @@ class CudaOps:
         w = pk["w"]
         self._check(self.lib.blz_gemm_tc(kind, _ptr(data), lda, _ptr(w), w.shape[1] * w.element_size(), _ptr(out), out.stride(0),
                                          M_pad, pk["N"], pk["K"], _ptr(rs), _ptr(pk["alpha"]), VP(0), _ptr(sfa), _ptr(pk["sf"]),
-                                         0, 128, 0, _ptr(tile_expert), n_exp, self._stream()), "grouped gemm")
+                                         0, 128, 0, _ptr(tile_expert), n_exp, 0, self._stream()), "grouped gemm")
         return out
 
     def moe(self, x, topk_w, topk_id, experts):

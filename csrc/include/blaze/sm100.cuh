@@ -240,6 +240,14 @@ __device__ __forceinline__ void bar_sync(int id, int threads) {
 }
 
 // ------------------------------------------------------------------------------------------ small math
+// named barrier over `threads` threads that also ANDs a predicate across them (every participant gets the result)
+__device__ __forceinline__ bool bar_red_and(int id, int threads, bool pred) {
+  uint32_t out;
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbar.red.and.pred q, %2, %3, p;\nselp.u32 %0, 1, 0, q;\n}"
+               : "=r"(out) : "r"((uint32_t)pred), "r"(id), "r"(threads) : "memory");
+  return out != 0;
+}
+
 __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);

@@ -39,6 +39,7 @@ struct GemmParams {
   long long spin_limit;
   int rank, world;
   const int* tile_expert;    // grouped GEMM: expert of every 128-row M tile (-1 = skip); B / alpha / sfb rows are offset by expert * N
+  int b_kt;                  // > 0: B is tile-major, [N/128][b_kt][128 rows][128 bytes] (dense weights repacked at load)
   int* status;
 };
 
@@ -128,7 +129,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(&full[s], bytes);
           const int kc = (KIND == 0) ? kt * BK : kt * 128;   // coordinate in map elements (bf16 or bytes)
           tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, kc, mt * BM, &full[s]);
-          tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, brow, &full[s]);
+          if (p.b_kt > 0) {
+            // tile-major weights: every 128-row x 128-byte tile is one contiguous 16 KB run of DRAM
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              tma_load_2d(sB + s * Cfg::B_BYTES + h * 16384, &tmB, 0, ((nt * (BN / 128) + h) * p.b_kt + kt) * 128, &full[s]);
+          } else {
+            tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, brow, &full[s]);
+          }
           if constexpr (Cfg::SF_ATOMS > 0) {
             const size_t a_off = ((size_t)mt * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
             bulk_load(sSFA + s * Cfg::SFA_BYTES, p.sfa + a_off, atoms * 512, &full[s]);
@@ -231,7 +239,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
         const int col0 = nt * BN + c * 32;
         if (row < p.M && col0 < p.N) {
-          const bool whole = col0 + 32 <= p.N;
+          // vector stores need the whole 32-column group inside N and rows that start on a 16-byte boundary
+          const bool whole = col0 + 32 <= p.N && (p.ldc & (OUT_F32 ? 3 : 7)) == 0;
           if constexpr (OUT_F32) {
             float* dst = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
 #pragma unroll
@@ -373,10 +382,11 @@ BLZ_API int blz_gemm_fuse_allreduce(void* mc_out, void* done_ctr, void* const* p
 
 // kind: 0 bf16, 1 nvfp4, 2 mxfp8, 3 fp8.  A [M, K] and B [N, K] row-major (packed bytes for 4/8-bit kinds);
 // lda / ldb in BYTES.  out_f32: C is fp32, else bf16; ldc in elements.  bn: 128 or 256 (0 = choose).
+// b_kt > 0: B is the tile-major repack [ceil(N/128)][b_kt][128][128 bytes] (zero padded), b_kt = ceil(row bytes / 128).
 BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
                         int M, int N, int K, const float* row_scale, const float* alpha, const void* bias,
                         const void* sfa, const void* sfb, int out_f32, int bn, int max_ctas, const int* tile_expert,
-                        int num_experts, cudaStream_t stream) {
+                        int num_experts, int b_kt, cudaStream_t stream) {
   using namespace blz;
   if (M <= 0 || N <= 0 || K <= 0 || kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
   const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
@@ -394,6 +404,8 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   p.sfa_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
   p.status = status_word();
   p.tile_expert = tile_expert;
+  p.b_kt = b_kt;
+  if (b_kt > 0 && tile_expert) return (int)cudaErrorInvalidValue;
   p.mc_out = nullptr; p.done_ctr = nullptr; p.epoch = nullptr; p.spin_limit = 0; p.rank = 0; p.world = 1;
   if (g_fuse.mc_out) {
     if (out_f32 || (N % 32)) return (int)cudaErrorInvalidValue;
@@ -409,12 +421,14 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   if (kind == 0) {
     e = encode_tmap(&tmA, A, 2, K, M, lda, 64, 128, 3);
     if (e != cudaSuccess) return (int)e;
-    e = encode_tmap(&tmB, B, 2, K, b_rows, ldb, 64, bn, 3);
+    if (b_kt > 0) e = encode_tmap(&tmB, B, 2, 64, (uint64_t)((N + 127) / 128) * b_kt * 128, 128, 64, 128, 3);
+    else e = encode_tmap(&tmB, B, 2, K, b_rows, ldb, 64, bn, 3);
   } else {
     const uint64_t kbytes = kind == 1 ? K / 2 : K;
     e = encode_tmap(&tmA, A, 1, kbytes, M, lda, 128, 128, 3);
     if (e != cudaSuccess) return (int)e;
-    e = encode_tmap(&tmB, B, 1, kbytes, b_rows, ldb, 128, bn, 3);
+    if (b_kt > 0) e = encode_tmap(&tmB, B, 1, 128, (uint64_t)((N + 127) / 128) * b_kt * 128, 128, 128, 128, 3);
+    else e = encode_tmap(&tmB, B, 1, kbytes, b_rows, ldb, 128, bn, 3);
   }
   if (e != cudaSuccess) return (int)e;
 #define BLZ_GEMM_CASE(KD, BNV)                                                                        \

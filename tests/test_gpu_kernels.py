@@ -81,6 +81,61 @@ def test_gemm_mxfp8(ops, M, N, K, bn):
     assert rel < 0.02
 
 
+@pytest.mark.parametrize("fmt,M,N,K,ksplit", [
+    ("nvfp4", 256, 4096, 4096, 4), ("nvfp4", 256, 6144, 4096, 3), ("nvfp4", 200, 1024, 12288, 8), ("nvfp4", 77, 512, 1024, 1),
+    ("nvfp4", 1, 384, 512, 2), ("nvfp4", 128, 256, 256, 0), ("nvfp4", 1024, 1024, 4096, 0), ("nvfp4", 333, 512, 1024, 0),
+    ("mxfp8", 256, 1024, 2048, 4), ("mxfp8", 40, 384, 1024, 1), ("mxfp8", 700, 512, 2048, 0),
+    ("bf16", 256, 1000, 1024, 2), ("bf16", 19, 131, 320, 1), ("fp8", 192, 384, 512, 2)])
+def test_gemm_wide(ops, fmt, M, N, K, ksplit):
+    """Wide-N kernel: swapped orientation (M <= 256, optional split along K) and 256-feature tiles (M > 256)."""
+    g = torch.Generator(device=DEV).manual_seed(21)
+    x = (torch.randn(M, K, generator=g, device=DEV)).bfloat16()
+    w = torch.randn(N, K, generator=g, device=DEV) * 0.02
+    f = {"nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "bf16": Format.DENSE, "fp8": Format.FP8_CHANNEL}[fmt]
+    lin = Linear.from_dense(w, f)
+    if fmt == "bf16":
+        lin.bias = (torch.randn(N, generator=g, device=DEV) * 0.1).bfloat16()
+        lin.cuda_pack = None
+    y = ops.linear(lin, x, wide=True, ksplit=ksplit)
+    y_tc = ops.linear(lin, x, wide=False)
+    y32 = ops.linear(lin, x, out_dtype=torch.float32, wide=True, ksplit=ksplit)
+    again = ops.linear(lin, x, wide=True, ksplit=ksplit)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert torch.equal(y, again), "the split-K sum must be deterministic"
+    mx, rel = _report(f"gemm_wide {fmt} {M}x{N}x{K} ks{ksplit} vs 128-column kernel", y, y_tc.float())
+    assert rel < 2e-3
+    mx, rel = _report(f"gemm_wide {fmt} fp32 out", y32, y_tc.float())
+    assert rel < 4e-3
+    want = lin.ref(x, torch.float32)
+    mx, rel = _report(f"gemm_wide {fmt} vs oracle", y, want)
+    assert rel < 0.05
+
+
+@pytest.mark.parametrize("fmt,M,N,K", [("nvfp4", 300, 512, 1024), ("nvfp4", 64, 384, 576 * 2), ("bf16", 100, 200, 320),
+                                       ("mxfp8", 130, 256, 640)])
+def test_gemm_tile_major_weights(ops, fmt, M, N, K):
+    """The tile-major weight repack gives the same result as row-major storage, through both GEMM kernels."""
+    g = torch.Generator(device=DEV).manual_seed(22)
+    x = (torch.randn(M, K, generator=g, device=DEV)).bfloat16()
+    w = torch.randn(N, K, generator=g, device=DEV) * 0.02
+    f = {"nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "bf16": Format.DENSE}[fmt]
+    lin = Linear.from_dense(w, f)
+    want = ops.linear(lin, x, wide=False)
+    lin.cuda_pack = None
+    pk = ops.pack(lin, tiled=True)
+    assert pk["kt"] > 0 and pk["w"].dim() == 4
+    got = ops.linear(lin, x, wide=False)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert torch.equal(got, want)
+    if M <= 256 or (N % 256 == 0 and fmt != "bf16"):
+        got_w = ops.linear(lin, x, wide=True)
+        torch.cuda.synchronize()
+        _, rel = _report(f"tile-major {fmt} wide", got_w, want.float())
+        assert rel < 2e-3
+
+
 def test_gemm_fp8_channel(ops):
     g = torch.Generator(device=DEV).manual_seed(4)
     x = (torch.randn(192, 512, generator=g, device=DEV)).bfloat16()
