@@ -34,11 +34,14 @@ def part(n: int, rank: int, world: int):
 
 class QuantAct:
     """A quantised activation matrix handed from a producer epilogue to the next GEMM."""
-    __slots__ = ("fmt", "data", "sf", "row_scale", "rows", "cols", "dense")
+    __slots__ = ("fmt", "data", "sf", "row_scale", "rows", "cols", "dense", "wait")
 
     def __init__(self, fmt, data, sf, row_scale, rows, cols, dense=None):
         self.fmt, self.data, self.sf, self.row_scale = fmt, data, sf, row_scale
         self.rows, self.cols, self.dense = rows, cols, dense
+        # (arrival counters ptr, expected-count ptr, world, timeout ms) while peers may still be writing this buffer: the first
+        # GEMM that consumes it waits for the flags inside its producer warp
+        self.wait = None
 
 
 class Linear:

@@ -413,13 +413,13 @@ class Model:
             first = L.attn.qkv if L.attn is not None else L.gdn.in_proj
             if gi in self.capture_layers:
                 self.captured[gi] = self._materialise(x, residual, kind, fused, keep=True)
-            h, residual = self._reduce_norm(x, residual, kind, L.input_norm, first, fused)
+            h, residual = self._reduce_norm(x, residual, kind, L.input_norm, first, fused, defer=True)
             if L.kind == "full_attention":
                 x, kind = self._attention(L.attn, h, batch, kv, gi, rope, fused)
             else:
                 x, kind = self._gdn(L.gdn, h, batch, kv, gi, fused)
             nxt = L.mlp.gate_up if isinstance(L.mlp, DenseMlp) else None
-            h, residual = self._reduce_norm(x, residual, kind, L.post_norm, nxt, fused)
+            h, residual = self._reduce_norm(x, residual, kind, L.post_norm, nxt, fused, defer=nxt is not None)
             x, kind = self._mlp(L.mlp, h, fused)
         return self._materialise(x, residual, kind, fused)
 
@@ -427,7 +427,9 @@ class Model:
         g = self.tp.group
         return g.fused if (g is not None and g.world > 1 and getattr(g, "fused", None) is not None and self.ops.is_cuda) else None
 
-    def _reduce_norm(self, x, residual, kind, w, quant_for, fused):
+    def _reduce_norm(self, x, residual, kind, w, quant_for, fused, defer: bool = False):
+        """``defer``: the result goes straight into ``ops.linear`` (attention / GDN input projection, dense MLP), which
+        may then take over the wait for the peers' rows."""
         ops, cfg = self.ops, self.cfg
         eps, zc = cfg.rms_norm_eps, cfg.zero_centered_norm
         if fused is not None and fused.mode == "reduce_norm":
@@ -437,7 +439,7 @@ class Model:
                 return h, residual
             if kind != "partial":                      # complete rows: rank 0 contributes them, the others zeros
                 x = self._as_partial(x, fused)
-            return fused.reduce_norm(x, residual, w, eps, zc, quant_for), residual
+            return fused.reduce_norm(x, residual, w, eps, zc, quant_for, defer=defer), residual
         if kind == "acc":                              # already summed by the GEMM epilogue; re-zero the buffer while reading
             return ops.norm(x, residual, w, eps, zc, quant_for=quant_for, zero_src=True)
         if kind == "partial":

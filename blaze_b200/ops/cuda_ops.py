@@ -46,6 +46,8 @@ class CudaOps:
         lib.blz_gemm_tc.restype = _c.c_int
         lib.blz_gemm_tc.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
                                     _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_gemm_wait_flags.restype = _c.c_int
+        lib.blz_gemm_wait_flags.argtypes = [VP, VP, _c.c_int, _c.c_int]
         lib.blz_gemm_wide.restype = _c.c_int
         lib.blz_gemm_wide.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
                                       _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_longlong, VP,
@@ -244,6 +246,17 @@ class CudaOps:
         w = pk["w"]
         kt = pk.get("kt", 0)
         ldb = 128 if kt else w.shape[1] * w.element_size()
+        pending = getattr(x, "wait", None) if isinstance(x, QuantAct) else None
+        if pending is not None:
+            # the peers may still be writing these rows: the 128-column kernel waits for their flags after it has sent
+            # its first weight tiles
+            if wide:
+                raise CudaError("an activation with a pending peer wait needs the 128-column GEMM")
+            wide = False
+            rc = self.lib.blz_gemm_wait_flags(VP(pending[0]), VP(pending[1]), pending[2], pending[3])
+            if rc != 0:
+                raise CudaError(f"blz_gemm_wait_flags failed: {rc}")
+            x.wait = None
         if wide is None:
             # Measured on B200 (Qwen3-8B shapes, captured-graph timing): 256-feature tiles win for block-scaled prefill GEMMs
             # (NVFP4 2048x24576x4096: 156 -> 119 us); the swapped orientation wins for the very wide bf16 head

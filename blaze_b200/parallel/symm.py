@@ -77,7 +77,8 @@ class SymmAllReduce:
         lib.blz_gemm_fuse_allreduce.argtypes = [VP, VP, VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int]
         lib.blz_comm_allreduce.argtypes = [VP, VP, VP, VP, VP, ctypes.c_longlong, ctypes.c_int, VP]
         lib.blz_comm_allreduce_norm.argtypes = [VP] + [VP] * 8 + [VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                                                  ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, VP]
+                                                                  ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                                  ctypes.c_int, VP]
         self.max_rows, self.hidden = max_rows, hidden
         row_tiles = (max_rows + 127) // 128
         self.in_bytes = max_rows * hidden * 2
@@ -85,7 +86,7 @@ class SymmAllReduce:
         self.sf_bytes = row_tiles * ((hidden + 63) // 64) * 512
         self.rs_bytes = max_rows * 4
         pad_bytes = int(lib.blz_comm_pad_bytes())
-        total = 4 * self.in_bytes + self.in_bytes + self.q_bytes + self.sf_bytes + self.rs_bytes + pad_bytes + 32 * 4096
+        total = 4 * self.in_bytes + self.in_bytes + self.q_bytes + self.sf_bytes + self.rs_bytes + pad_bytes + 40 * 4096
         self.arena = SymmArena(group, device, total)
         a = self.arena
         self.off_in = [a.carve(self.in_bytes), a.carve(self.in_bytes)]
@@ -101,6 +102,9 @@ class SymmAllReduce:
             a.view(o, self.in_bytes).zero_()
         self.off_pad2 = a.carve(4096)
         a.view(self.off_pad2, 4096).zero_()
+        self.off_sig = a.carve(4096)               # arrival counters of kernels that signal instead of waiting
+        a.view(self.off_sig, 4096).zero_()
+        self.sig_expect = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.gemm_state = torch.zeros(4, dtype=torch.int32, device=self.device)     # [done counter, epoch]
         self.acc_cur = 0
         self.timeout_ms = int(timeout_ms or os.environ.get("BLAZE_COMM_TIMEOUT_MS", "10000"))
@@ -111,13 +115,20 @@ class SymmAllReduce:
                                         int(timeout_ms or os.environ.get("BLAZE_COMM_TIMEOUT_MS", "10000")))
         if not self.comm:
             raise RuntimeError("blz_comm_create failed")
+        lib.blz_comm_set_signals.argtypes = [VP, VP, VP]
+        lib.blz_comm_set_signals(self.comm, _arr(a.peers(self.off_sig)), VP(self.sig_expect.data_ptr()))
         self.use_mc = bool(use_multicast and a.mc)
         # "gemm_red": the row-cut GEMM's epilogue reduces through the switch (one kernel per reduction, replicated norm);
         # "reduce_norm": GEMM writes partial sums, one kernel reduces + norms + quantises a row slice per rank.
-        default = "gemm_red" if (self.use_mc and group.world <= 2) else "reduce_norm"
+        # measured on 2 B200s (Qwen3-8B, 256 rows): reduce_norm 21 us per reduction against 55 us for gemm_red, whose
+        # epilogue also collapses on prefill-sized tiles; gemm_red stays available for experiments
+        default = "reduce_norm"
         self.mode = os.environ.get("BLAZE_TP_FUSION", default)
         if self.mode == "gemm_red" and not self.use_mc:
             self.mode = "reduce_norm"
+        # letting the consumer GEMM take over the closing wait measured slower on 2 B200s (37.6 us against 32.9 us for the
+        # reduction + GEMM pair), so it is opt-in
+        self.defer_ok = os.environ.get("BLAZE_TP_DEFER", "0") == "1"
         self.cur = 0
         self.launches = 0
 
@@ -203,11 +214,14 @@ class SymmAllReduce:
         return out
 
     def reduce_norm(self, partial: torch.Tensor, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor],
-                    eps: float, zero_centered: bool, quant_for: Optional[Linear] = None):
+                    eps: float, zero_centered: bool, quant_for: Optional[Linear] = None, defer: bool = False):
         """``partial``: this rank's ``[T, H]`` partial sums in a buffer from :meth:`next_input`.
         ``residual``: this rank's ``[rows_per, H]`` slice of the residual stream (updated in place).
         Returns the normed rows on every rank: a bf16 ``[T, H]`` tensor or a :class:`QuantAct`.
-        With ``norm_w=None`` the summed (+ residual) rows are returned unnormalised."""
+        With ``norm_w=None`` the summed (+ residual) rows are returned unnormalised.
+        ``defer``: the caller promises that the result's first consumer is ``ops.linear``; for quantised results of
+        decode-sized steps the kernel then only signals the peers on its way out and the GEMM waits for their flags
+        after it has started fetching its weights (``QuantAct.wait``)."""
         T, H = partial.shape
         i = self._which(partial)
         if i is None:
@@ -223,11 +237,13 @@ class SymmAllReduce:
         mc = self.use_mc
         per = self.rows_per(T)
         blocks = max(1, min(per, 512))
+        defer = bool(defer and self.defer_ok and mode != 0 and T <= 256)
         rc = self.lib.blz_comm_allreduce_norm(
             self.comm, _arr(a.peers(off_in)), _arr(a.peers(off_out)), _arr(a.peers(self.off_sf)), _arr(a.peers(self.off_rs)),
             VP(a.mcast(off_in) if mc else 0), VP(a.mcast(off_out) if mc else 0), VP(a.mcast(self.off_sf) if mc else 0),
             VP(a.mcast(self.off_rs) if mc else 0), VP(residual.data_ptr() if residual is not None else 0),
-            VP(norm_w.data_ptr() if norm_w is not None else 0), T, H, per, eps, int(zero_centered), mode, blocks, self._stream())
+            VP(norm_w.data_ptr() if norm_w is not None else 0), T, H, per, eps, int(zero_centered), mode, blocks, int(defer),
+            self._stream())
         if rc != 0:
             raise RuntimeError(f"blz_comm_allreduce_norm failed: {rc}")
         self.launches += 1
@@ -237,7 +253,11 @@ class SymmAllReduce:
             data = a.view(off_out, T * H // 2).view(T, H // 2)
             sf = a.view(self.off_sf, ((T + 127) // 128) * ((H + 63) // 64) * 512)
             rs = a.view(self.off_rs, T * 4).view(torch.float32)
-            return QuantAct(Format.NVFP4, data, sf, rs, T, H)
-        data = a.view(off_out, T * H).view(T, H)
-        sf = a.view(self.off_sf, ((T + 127) // 128) * ((H + 127) // 128) * 512)
-        return QuantAct(Format.MXFP8, data, sf, None, T, H)
+            qa = QuantAct(Format.NVFP4, data, sf, rs, T, H)
+        else:
+            data = a.view(off_out, T * H).view(T, H)
+            sf = a.view(self.off_sf, ((T + 127) // 128) * ((H + 127) // 128) * 512)
+            qa = QuantAct(Format.MXFP8, data, sf, None, T, H)
+        if defer:
+            qa.wait = (a.local.data_ptr() + self.off_sig, self.sig_expect.data_ptr(), self.group.world, self.timeout_ms)
+        return qa

@@ -36,7 +36,18 @@ struct CommParams {
   long long spin_limit;           // clock ticks a flag wait may take before it gives up
   int rank, world;
   int* status;
+  uint32_t* peer_sig[kMaxWorld];  // arrival counters of every rank, [kMaxWorld] uint32 each (slot = source rank)
+  uint32_t* sig_expect;           // local: the count a consumer of a signalling kernel's result must wait for
+  long long* prof;                // optional [8] nanosecond stamps of block 0 (entry, after each phase); null = off
 };
+
+__device__ __forceinline__ void stamp(const CommParams& c, int k) {
+  if (c.prof && blockIdx.x == 0 && threadIdx.x == 0) {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    c.prof[k] = t;
+  }
+}
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -47,12 +58,27 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // Block-level barrier across ranks: block b of every rank meets block b of every other rank.
 // Every kernel uses two barrier epochs (entry = base + 1, exit = base + 2) and advances the stored epoch by two at
 // entry, so a rank that gave up on a wait stays in step with its peers on the next kernel.
 // Returns false (after recording kErrFlagTimeout) when a peer does not show up within the spin limit.
+//
+// Cost matters here (a decode step runs dozens of these): only the `world` signalling threads touch the fabric.  The
+// CTA barrier orders every thread's earlier stores before the signalling threads; at the exit phase those threads
+// issue ONE system-scope fence (so the result stores are visible before the flag) and at the entry phase none (there
+// is nothing to publish).  Flags are written and polled relaxed; one fence after the wait orders the reads that follow.
+// phase 2 = exit without waiting: publish the results and the flag, return at once; whoever consumes the results waits
+// for the flags itself (the GEMM that follows does, after it has started fetching its weights).
 __device__ __forceinline__ bool rank_barrier(const CommParams& c, int* ok_smem, int phase) {
-  __syncthreads();
   __shared__ uint32_t s_epoch;
   if (threadIdx.x == 0) {
     if (phase == 0) {
@@ -63,21 +89,27 @@ __device__ __forceinline__ bool rank_barrier(const CommParams& c, int* ok_smem, 
     }
     *ok_smem = 1;
   }
-  __threadfence_system();
   __syncthreads();
   const uint32_t e = s_epoch;
   if (threadIdx.x < c.world) {
     const int peer = threadIdx.x;
-    st_release_sys(c.peer_pad[peer] + (size_t)blockIdx.x * kMaxWorld + c.rank, e);
+    if (phase >= 1) __threadfence_system();
+    if (phase == 2) {
+      // one arrival per block on every peer's counter; the consumer polls `world` words instead of one flag per block
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(c.peer_sig[peer] + c.rank), "r"(1u) : "memory");
+    } else {
+      st_relaxed_sys(c.peer_pad[peer] + (size_t)blockIdx.x * kMaxWorld + c.rank, e);
+    }
     const uint32_t* mine = c.peer_pad[c.rank] + (size_t)blockIdx.x * kMaxWorld + peer;
     const long long t0 = clock64();
-    while ((int32_t)(ld_acquire_sys(mine) - e) < 0) {
+    while (phase != 2 && (int32_t)(ld_relaxed_sys(mine) - e) < 0) {
       if (clock64() - t0 > c.spin_limit) {
         atomicCAS(c.status, kOk, kErrFlagTimeout);
         *ok_smem = 0;
         break;
       }
     }
+    if (phase == 0) __threadfence_system();
   }
   __syncthreads();
   return *ok_smem != 0;
@@ -152,7 +184,9 @@ __device__ __forceinline__ void bcast4(const CommParams& c, void* const* peers, 
 template <bool MC>
 __global__ void __launch_bounds__(512) allreduce_kernel(CommParams c, size_t n16) {
   __shared__ int ok;
+  stamp(c, 0);
   if (!rank_barrier(c, &ok, 0)) return;
+  stamp(c, 1);
   const size_t per = (n16 + c.world - 1) / c.world;
   const size_t lo = (size_t)c.rank * per, hi = min(n16, lo + per);
   for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
@@ -161,7 +195,9 @@ __global__ void __launch_bounds__(512) allreduce_kernel(CommParams c, size_t n16
     uint4 o = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
     bcast16<MC>(c, c.peer_out, c.mc_out, i * 16, o);
   }
+  stamp(c, 3);
   rank_barrier(c, &ok, 1);
+  stamp(c, 4);
 }
 
 // ------------------------------------------------------------------------------------------ all-reduce + residual + RMSNorm (+quant)
@@ -190,51 +226,84 @@ __device__ __forceinline__ float block_reduce_c(float v, float* sh, bool is_max)
 // partial rows of all ranks, adds its slice of the residual stream (`residual` is LOCAL, [rows_per, H], updated in
 // place), normalises, and broadcasts the result row: bf16 (QUANT 0), NVFP4 (1) or MXFP8 (2) into every rank's
 // output buffers.  With `norm_w == nullptr` the summed (+ residual) row itself is broadcast (final layer).
-template <bool MC, int QUANT>
+//
+// One row per CTA at a time; thread i owns CH chunks of 8 consecutive elements (chunk c covers elements
+// (c * blockDim + i) * 8 ...), which stay in registers from the reduction to the quantised stores.  A 16-element NVFP4
+// block is two neighbouring threads, a 32-element MXFP8 block four; neighbours pool their packed codes through
+// shuffles so that what goes through the switch are 16-byte (codes) and 4-byte (scale tile column) stores.
+__device__ __forceinline__ uint32_t pack_e2m1x8_c(const float (&v)[8], float inv) {
+  uint32_t r;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(r)
+      : "f"(v[0] * inv), "f"(v[1] * inv), "f"(v[2] * inv), "f"(v[3] * inv), "f"(v[4] * inv), "f"(v[5] * inv), "f"(v[6] * inv),
+        "f"(v[7] * inv));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_e4m3x4_c(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+template <bool MC, int QUANT, int CH>
 __global__ void __launch_bounds__(1024) allreduce_norm_kernel(CommParams c, __nv_bfloat16* residual,
                                                               const __nv_bfloat16* __restrict__ norm_w, int T, int H,
-                                                              int rows_per, float eps, int zero_centered, int sf_col_tiles) {
-  extern __shared__ __align__(16) uint8_t dyn[];
-  __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(dyn);
+                                                              int rows_per, float eps, int zero_centered, int sf_col_tiles,
+                                                              int defer_exit) {
   __shared__ float red[32];
   __shared__ int ok;
+  stamp(c, 0);
+  if (defer_exit && blockIdx.x == 0 && threadIdx.x == 0) *c.sig_expect += gridDim.x;
   if (!rank_barrier(c, &ok, 0)) return;
+  stamp(c, 1);
   const int lo = c.rank * rows_per, hi = min(T, lo + rows_per);
+  const int lane = threadIdx.x & 31;
   for (int t = lo + blockIdx.x; t < hi; t += gridDim.x) {
     __nv_bfloat16* rr = residual ? residual + (size_t)(t - lo) * H : nullptr;
+    uint4 u[CH];
     float ss = 0.f;
-    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-      float f[8];
-      reduce8<MC>(c, ((size_t)t * H + i) * 2, f);
-      uint4 u;
-      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u);
-      if (rr) {
-        uint4 ur = *reinterpret_cast<const uint4*>(rr + i);
-        const __nv_bfloat16* er = reinterpret_cast<const __nv_bfloat16*>(&ur);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(bf2f(__float2bfloat16(f[j])) + bf2f(er[j]));
-        *reinterpret_cast<uint4*>(rr + i) = u;
-      } else {
+    for (int ch = 0; ch < CH; ++ch) {
+      const int i = (ch * blockDim.x + threadIdx.x) * 8;
+      u[ch] = make_uint4(0, 0, 0, 0);
+      if (i < H) {
+        float f[8];
+        reduce8<MC>(c, ((size_t)t * H + i) * 2, f);
+        __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u[ch]);
+        if (rr) {
+          const uint4 ur = *reinterpret_cast<const uint4*>(rr + i);
+          const __nv_bfloat16* er = reinterpret_cast<const __nv_bfloat16*>(&ur);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(f[j]);
+          for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(bf2f(__float2bfloat16(f[j])) + bf2f(er[j]));
+          *reinterpret_cast<uint4*>(rr + i) = u[ch];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(f[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float x = bf2f(e[j]); ss += x * x; }
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { const float x = bf2f(e[j]); ss += x * x; }
-      *reinterpret_cast<uint4*>(row + i) = u;
     }
     float rstd = 1.f;
     if (norm_w) {
       ss = block_reduce_c(ss, red, false);
       rstd = rsqrtf(ss / H + eps);
-    } else {
-      __syncthreads();
     }
+    stamp(c, 2);
     float amax = 0.f;
-    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-      uint4 u = *reinterpret_cast<uint4*>(row + i);
-      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u);
-      if (norm_w) {
-        uint4 uw = *reinterpret_cast<const uint4*>(norm_w + i);
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) {
+      const int i = (ch * blockDim.x + threadIdx.x) * 8;
+      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u[ch]);
+      if (norm_w && i < H) {
+        const uint4 uw = *reinterpret_cast<const uint4*>(norm_w + i);
         const __nv_bfloat16* ew = reinterpret_cast<const __nv_bfloat16*>(&uw);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -242,71 +311,71 @@ __global__ void __launch_bounds__(1024) allreduce_norm_kernel(CommParams c, __nv
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(bf2f(e[j])));
-      if (QUANT == 0) bcast16<MC>(c, c.peer_out, c.mc_out, ((size_t)t * H + i) * 2, u);
-      else *reinterpret_cast<uint4*>(row + i) = u;
+      if (QUANT == 0 && i < H) bcast16<MC>(c, c.peer_out, c.mc_out, ((size_t)t * H + i) * 2, u[ch]);
     }
     if (QUANT == 1) {
       amax = block_reduce_c(amax, red, true);
       const float g = fmaxf(amax / (6.f * 448.f), 1e-30f);
       if (threadIdx.x == 0) bcast4<MC>(c, c.peer_rs, c.mc_rs, (size_t)t * 4, __float_as_uint(g));
-      // one thread per 64 elements: four 16-element blocks → 32 packed bytes and the 4 scale bytes of one tile column
-      for (int b4 = threadIdx.x; b4 < H / 64; b4 += blockDim.x) {
-        uint32_t sfw = 0;
-        uint32_t pk[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float v[16];
-          float bm = 0.f;
+      for (int ch = 0; ch < CH; ++ch) {
+        const int i = (ch * blockDim.x + threadIdx.x) * 8;
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u[ch]);
+        float v[8];
+        float bm = 0.f;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { v[j] = bf2f(row[b4 * 64 + q * 16 + j]); bm = fmaxf(bm, fabsf(v[j])); }
-          const uint8_t sf = f2e4m3_c(bm / 6.f / g);
-          const float denom = e4m32f_c(sf) * g;
-          uint32_t lo4 = 0, hi4 = 0;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) lo4 |= f2e2m1_c(denom > 0.f ? v[j] / denom : 0.f) << (4 * j);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) hi4 |= f2e2m1_c(denom > 0.f ? v[8 + j] / denom : 0.f) << (4 * j);
-          pk[q * 2] = lo4; pk[q * 2 + 1] = hi4;
-          sfw |= (uint32_t)sf << (8 * q);
+        for (int j = 0; j < 8; ++j) { v[j] = bf2f(e[j]); bm = fmaxf(bm, fabsf(v[j])); }
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        const uint32_t sf = f2e4m3_c(bm / 6.f / g);
+        const float denom = e4m32f_c((uint8_t)sf) * g;
+        const uint32_t codes = pack_e2m1x8_c(v, denom > 0.f ? 1.f / denom : 0.f);
+        // four threads -> 16 bytes of codes (32 elements); eight threads -> the 4 scale bytes of one 64-element tile column
+        const uint32_t c1 = __shfl_down_sync(0xffffffffu, codes, 1), c2 = __shfl_down_sync(0xffffffffu, codes, 2),
+                       c3 = __shfl_down_sync(0xffffffffu, codes, 3);
+        const uint32_t s2 = __shfl_down_sync(0xffffffffu, sf, 2), s4 = __shfl_down_sync(0xffffffffu, sf, 4),
+                       s6 = __shfl_down_sync(0xffffffffu, sf, 6);
+        if (i < H) {
+          if ((lane & 3) == 0) bcast16<MC>(c, c.peer_out, c.mc_out, (size_t)t * (H / 2) + i / 2, make_uint4(codes, c1, c2, c3));
+          if ((lane & 7) == 0) {
+            const size_t soff = ((size_t)(t >> 7) * sf_col_tiles + (i >> 6)) * 512 + (t & 31) * 16 + ((t >> 5) & 3) * 4;
+            bcast4<MC>(c, c.peer_sf, c.mc_sf, soff, sf | (s2 << 8) | (s4 << 16) | (s6 << 24));
+          }
         }
-        const size_t qoff = (size_t)t * (H / 2) + (size_t)b4 * 32;
-        bcast16<MC>(c, c.peer_out, c.mc_out, qoff, make_uint4(pk[0], pk[1], pk[2], pk[3]));
-        bcast16<MC>(c, c.peer_out, c.mc_out, qoff + 16, make_uint4(pk[4], pk[5], pk[6], pk[7]));
-        const size_t soff = ((size_t)(t >> 7) * sf_col_tiles + b4) * 512 + (t & 31) * 16 + ((t >> 5) & 3) * 4;
-        bcast4<MC>(c, c.peer_sf, c.mc_sf, soff, sfw);
       }
     } else if (QUANT == 2) {
-      __syncthreads();
-      // one thread per 128 elements: four 32-element blocks → 128 e4m3 bytes and 4 e8m0 scale bytes
-      for (int b4 = threadIdx.x; b4 < H / 128; b4 += blockDim.x) {
-        uint32_t sfw = 0;
-#pragma unroll 1
-        for (int q = 0; q < 4; ++q) {
-          float v[32];
-          float bm = 0.f;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) { v[j] = bf2f(row[b4 * 128 + q * 32 + j]); bm = fmaxf(bm, fabsf(v[j])); }
-          bm = fmaxf(bm, 1.17549435e-38f);
-          int ex = (int)ceilf(log2f(bm / 448.f));
-          ex = max(-127, min(127, ex));
-          const float inv = exp2f((float)-ex);
-          uint32_t w[8];
+      for (int ch = 0; ch < CH; ++ch) {
+        const int i = (ch * blockDim.x + threadIdx.x) * 8;
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u[ch]);
+        float v[8];
+        float bm = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            w[j] = f2e4m3_c(v[4 * j] * inv) | (f2e4m3_c(v[4 * j + 1] * inv) << 8) | (f2e4m3_c(v[4 * j + 2] * inv) << 16) |
-                   (f2e4m3_c(v[4 * j + 3] * inv) << 24);
-          const size_t qoff = (size_t)t * H + (size_t)b4 * 128 + q * 32;
-          bcast16<MC>(c, c.peer_out, c.mc_out, qoff, make_uint4(w[0], w[1], w[2], w[3]));
-          bcast16<MC>(c, c.peer_out, c.mc_out, qoff + 16, make_uint4(w[4], w[5], w[6], w[7]));
-          sfw |= (uint32_t)(ex + 127) << (8 * q);
+        for (int j = 0; j < 8; ++j) { v[j] = bf2f(e[j]); bm = fmaxf(bm, fabsf(v[j])); }
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        bm = fmaxf(bm, 1.17549435e-38f);
+        int ex = (int)ceilf(log2f(bm / 448.f));
+        ex = max(-127, min(127, ex));
+        const float inv = exp2f((float)-ex);
+        const uint32_t w0 = pack_e4m3x4_c(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+        const uint32_t w1 = pack_e4m3x4_c(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+        const uint32_t n0 = __shfl_down_sync(0xffffffffu, w0, 1), n1 = __shfl_down_sync(0xffffffffu, w1, 1);
+        const uint32_t sf = (uint32_t)(ex + 127);
+        const uint32_t s4 = __shfl_down_sync(0xffffffffu, sf, 4), s8 = __shfl_down_sync(0xffffffffu, sf, 8),
+                       s12 = __shfl_down_sync(0xffffffffu, sf, 12);
+        if (i < H) {
+          if ((lane & 1) == 0) bcast16<MC>(c, c.peer_out, c.mc_out, (size_t)t * H + i, make_uint4(w0, w1, n0, n1));
+          if ((lane & 15) == 0) {
+            const size_t soff = ((size_t)(t >> 7) * sf_col_tiles + (i >> 7)) * 512 + (t & 31) * 16 + ((t >> 5) & 3) * 4;
+            bcast4<MC>(c, c.peer_sf, c.mc_sf, soff, sf | (s4 << 8) | (s8 << 16) | (s12 << 24));
+          }
         }
-        const size_t soff = ((size_t)(t >> 7) * sf_col_tiles + b4) * 512 + (t & 31) * 16 + ((t >> 5) & 3) * 4;
-        bcast4<MC>(c, c.peer_sf, c.mc_sf, soff, sfw);
       }
     }
-    __syncthreads();
   }
-  rank_barrier(c, &ok, 1);
+  stamp(c, 3);
+  rank_barrier(c, &ok, defer_exit ? 2 : 1);
+  stamp(c, 4);
 }
 
 }  // namespace blz
@@ -329,6 +398,18 @@ BLZ_API void* blz_comm_create(int rank, int world, void* const* pads, void* epoc
   c->p.status = status_word();
   c->p.spin_limit = (long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1900000LL;
   return c;
+}
+// Arrival counters for kernels that signal instead of waiting: sigs[r] = rank r's counter row (kMaxWorld uint32, zeroed),
+// expect = a zeroed local device word.
+BLZ_API void blz_comm_set_signals(void* h, void* const* sigs, void* expect) {
+  BlzComm* c = reinterpret_cast<BlzComm*>(h);
+  if (!c) return;
+  for (int r = 0; r < c->p.world; ++r) c->p.peer_sig[r] = reinterpret_cast<uint32_t*>(sigs[r]);
+  c->p.sig_expect = reinterpret_cast<uint32_t*>(expect);
+}
+// Nanosecond stamps of block 0 of every later collective kernel go to `prof` (device memory, 8 x int64); null turns it off.
+BLZ_API void blz_comm_set_prof(void* h, void* prof) {
+  if (h) reinterpret_cast<BlzComm*>(h)->p.prof = reinterpret_cast<long long*>(prof);
 }
 BLZ_API void blz_comm_destroy(void* h) { delete reinterpret_cast<BlzComm*>(h); }
 BLZ_API int blz_comm_pad_bytes() { return kMaxBlocks * kMaxWorld * 4; }
@@ -359,28 +440,31 @@ BLZ_API int blz_comm_allreduce(void* h, void* const* in, void* const* out, void*
 }
 
 // Fused all-reduce + residual + RMSNorm (+ quantise).  quant: 0 bf16 rows, 1 NVFP4, 2 MXFP8.
+// defer_exit: the kernel signals the peers and returns without waiting for theirs; the consumer of the result must wait
+// for this rank's arrival counters to reach the expected count (blz_comm_set_signals, blz_gemm_wait_flags).
 BLZ_API int blz_comm_allreduce_norm(void* h, void* const* in, void* const* out, void* const* sf, void* const* rs, void* mc_in,
                                     void* mc_out, void* mc_sf, void* mc_rs, void* residual, const void* norm_w, int T, int H,
-                                    int rows_per, float eps, int zero_centered, int quant, int blocks, cudaStream_t s) {
+                                    int rows_per, float eps, int zero_centered, int quant, int blocks, int defer_exit,
+                                    cudaStream_t s) {
   BlzComm* c = reinterpret_cast<BlzComm*>(h);
   if (!c || H % 128 || blocks < 1 || blocks > kMaxBlocks || quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
   CommParams p = c->p;
   fill(p, p.world, in, out, sf, rs, mc_in, mc_out, mc_sf, mc_rs);
+  if (defer_exit && !p.sig_expect) return (int)cudaErrorInvalidValue;
   const bool mc = mc_in && mc_out && (quant == 0 || mc_sf) && (quant != 1 || mc_rs);
-  int thr = (H / 8 + 31) / 32 * 32;
-  thr = thr > 1024 ? 1024 : thr;
-  const size_t sm = (size_t)H * 2;
+  // threads: a multiple of 32 covering H/8 chunks in at most 4 rounds
+  int ch = (H / 8 + 1023) / 1024;
+  if (ch > 4) return (int)cudaErrorInvalidValue;
+  int thr = ((H / 8 + ch - 1) / ch + 31) / 32 * 32;
   const int ct = quant == 1 ? (H + 63) / 64 : (H + 127) / 128;
   __nv_bfloat16* res = reinterpret_cast<__nv_bfloat16*>(residual);
   const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(norm_w);
-#define BLZ_ARN(MCV, Q)                                                                                              \
-  {                                                                                                                  \
-    static bool done = false;                                                                                        \
-    if (!done) { cudaFuncSetAttribute(allreduce_norm_kernel<MCV, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); done = true; } \
-    allreduce_norm_kernel<MCV, Q><<<blocks, thr, sm, s>>>(p, res, w, T, H, rows_per, eps, zero_centered, ct);          \
-  }
-  if (mc) { if (quant == 0) BLZ_ARN(true, 0) else if (quant == 1) BLZ_ARN(true, 1) else BLZ_ARN(true, 2) }
-  else { if (quant == 0) BLZ_ARN(false, 0) else if (quant == 1) BLZ_ARN(false, 1) else BLZ_ARN(false, 2) }
-#undef BLZ_ARN
+#define BLZ_ARN3(MCV, Q, C) allreduce_norm_kernel<MCV, Q, C><<<blocks, thr, 0, s>>>(p, res, w, T, H, rows_per, eps, zero_centered, ct, defer_exit)
+#define BLZ_ARN2(MCV, Q)                                                                  \
+  { if (ch == 1) BLZ_ARN3(MCV, Q, 1); else if (ch == 2) BLZ_ARN3(MCV, Q, 2); else if (ch == 3) BLZ_ARN3(MCV, Q, 3); else BLZ_ARN3(MCV, Q, 4); }
+  if (mc) { if (quant == 0) BLZ_ARN2(true, 0) else if (quant == 1) BLZ_ARN2(true, 1) else BLZ_ARN2(true, 2) }
+  else { if (quant == 0) BLZ_ARN2(false, 0) else if (quant == 1) BLZ_ARN2(false, 1) else BLZ_ARN2(false, 2) }
+#undef BLZ_ARN2
+#undef BLZ_ARN3
   return (int)cudaGetLastError();
 }

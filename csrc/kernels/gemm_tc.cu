@@ -39,6 +39,12 @@ struct GemmParams {
   long long spin_limit;
   int rank, world;
   const int* tile_expert;    // grouped GEMM: expert of every 128-row M tile (-1 = skip); B / alpha / sfb rows are offset by expert * N
+  // activations still in flight from the peers (fused all-reduce + norm that signals instead of waiting): the producer
+  // sends the first weight tiles, then waits until counter[r] >= *wait_expect for every rank r, then loads A
+  const uint32_t* wait_pad;  // own arrival counters, one uint32 per source rank (peers add to them)
+  const uint32_t* wait_epoch;  // the count to wait for (device word, advanced by the signalling kernel)
+  int wait_world;
+  long long wait_limit;
   int b_kt;                  // > 0: B is tile-major, [N/128][b_kt][128 rows][128 bytes] (dense weights repacked at load)
   int* status;
 };
@@ -111,40 +117,78 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    if (elect_one()) {
+    // what: 1 = the B tile (+ its scales) and the stage's byte count, 2 = the A tile (+ its scales), 3 = both
+    auto issue = [&](int s, int mt, int nt, int ex, int kt, int what) {
+      int atoms = 0;
+      if constexpr (Cfg::SF_ATOMS > 0) atoms = min(Cfg::SF_ATOMS, p.sfa_col_tiles - kt * Cfg::SF_ATOMS);
+      const int kc = (KIND == 0) ? kt * BK : kt * 128;   // coordinate in map elements (bf16 or bytes)
+      if (what & 1) {
+        uint32_t bytes = Cfg::A_BYTES + Cfg::B_BYTES;
+        if constexpr (Cfg::SF_ATOMS > 0) bytes += atoms * 512 * (1 + BN / 128);
+        mbar_expect_tx(&full[s], bytes);
+        const int brow = ex * p.N + nt * BN;                  // first B row of this tile
+        if (p.b_kt > 0) {
+          // tile-major weights: every 128-row x 128-byte tile is one contiguous 16 KB run of DRAM
+#pragma unroll
+          for (int h = 0; h < BN / 128; ++h)
+            tma_load_2d(sB + s * Cfg::B_BYTES + h * 16384, &tmB, 0, ((nt * (BN / 128) + h) * p.b_kt + kt) * 128, &full[s]);
+        } else {
+          tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, brow, &full[s]);
+        }
+        if constexpr (Cfg::SF_ATOMS > 0) {
+#pragma unroll
+          for (int h = 0; h < BN / 128; ++h) {
+            const size_t b_off = ((size_t)(brow / 128 + h) * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
+            bulk_load(sSFB + s * Cfg::SFB_BYTES + h * Cfg::SFA_BYTES, p.sfb + b_off, atoms * 512, &full[s]);
+          }
+        }
+      }
+      if (what & 2) {
+        tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, kc, mt * BM, &full[s]);
+        if constexpr (Cfg::SF_ATOMS > 0) {
+          const size_t a_off = ((size_t)mt * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
+          bulk_load(sSFA + s * Cfg::SFA_BYTES, p.sfa + a_off, atoms * 512, &full[s]);
+        }
+      }
+    };
+    int pre = 0;                      // stages of the first tile whose weights went out before the wait
+    bool go = true;
+    if (p.wait_pad != nullptr) {
+      if (lane == 0 && (int)blockIdx.x < num_tiles && !p.tile_expert) {
+        pre = min(STAGES, k_tiles);
+        const int t = blockIdx.x;
+        for (int kt = 0; kt < pre; ++kt) issue(kt, t % tiles_m, t / tiles_m, 0, kt, 1);
+      }
+      pre = __shfl_sync(0xffffffffu, pre, 0);
+      if (lane < p.wait_world) {
+        const uint32_t want = *p.wait_epoch;
+        const uint32_t* f = p.wait_pad + lane;
+        const long long t0 = clock64();
+        while (true) {
+          uint32_t v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+          if ((int32_t)(v - want) >= 0) break;
+          if (clock64() - t0 > p.wait_limit) { atomicCAS(p.status, kOk, kErrFlagTimeout); go = false; break; }
+        }
+      }
+      __syncwarp();
+      // the A tiles are fetched by the async proxy: order those reads after the flag observation
+      if (lane == 0) asm volatile("fence.proxy.async;" ::: "memory");
+      go = __all_sync(0xffffffffu, go);
+      if (!go && lane == 0) *abort_flag = 1;
+    }
+    if (lane == 0 && go) {
       int s = 0; uint32_t ph = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         const int mt = t % tiles_m, nt = t / tiles_m;
         const int ex = p.tile_expert ? p.tile_expert[mt] : 0;
         if (ex < 0) continue;
-        const int brow = ex * p.N + nt * BN;                  // first B row of this tile
         for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status)) goto producer_done;
-          uint32_t bytes = Cfg::A_BYTES + Cfg::B_BYTES;
-          int atoms = 0;
-          if constexpr (Cfg::SF_ATOMS > 0) {
-            atoms = min(Cfg::SF_ATOMS, p.sfa_col_tiles - kt * Cfg::SF_ATOMS);
-            bytes += atoms * 512 * (1 + BN / 128);
-          }
-          mbar_expect_tx(&full[s], bytes);
-          const int kc = (KIND == 0) ? kt * BK : kt * 128;   // coordinate in map elements (bf16 or bytes)
-          tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, kc, mt * BM, &full[s]);
-          if (p.b_kt > 0) {
-            // tile-major weights: every 128-row x 128-byte tile is one contiguous 16 KB run of DRAM
-#pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              tma_load_2d(sB + s * Cfg::B_BYTES + h * 16384, &tmB, 0, ((nt * (BN / 128) + h) * p.b_kt + kt) * 128, &full[s]);
+          if (t == (int)blockIdx.x && kt < pre) {
+            issue(s, mt, nt, ex, kt, 2);             // its weights are already on their way
           } else {
-            tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, brow, &full[s]);
-          }
-          if constexpr (Cfg::SF_ATOMS > 0) {
-            const size_t a_off = ((size_t)mt * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
-            bulk_load(sSFA + s * Cfg::SFA_BYTES, p.sfa + a_off, atoms * 512, &full[s]);
-#pragma unroll
-            for (int h = 0; h < BN / 128; ++h) {
-              const size_t b_off = ((size_t)(brow / 128 + h) * p.sfa_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512;
-              bulk_load(sSFB + s * Cfg::SFB_BYTES + h * Cfg::SFA_BYTES, p.sfb + b_off, atoms * 512, &full[s]);
-            }
+            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status)) goto producer_done;
+            issue(s, mt, nt, ex, kt, 3);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -363,7 +407,27 @@ struct FuseArgs {
   int rank = 0, world = 1;
 };
 thread_local FuseArgs g_fuse;
+struct WaitArgs {
+  const uint32_t* pad = nullptr;
+  const uint32_t* epoch = nullptr;
+  int world = 0;
+  long long limit = 0;
+};
+thread_local WaitArgs g_wait;
 }  // namespace
+
+// Arms the NEXT blz_gemm_tc call on this thread to wait, inside its producer warp and after it has sent its first weight
+// tiles, for the A operand: arrival counter r of `counters` (uint32 per source rank, in this GPU's memory) must reach the
+// value in the device word `expect` for every rank r < world.  A signalling collective kernel advances `expect` by its
+// block count when it starts and every one of its blocks adds one to the peers' counters on its way out.
+BLZ_API int blz_gemm_wait_flags(const void* counters, const void* expect, int world, int timeout_ms) {
+  if (!counters || !expect || world < 1 || world > 8) return (int)cudaErrorInvalidValue;
+  g_wait.pad = reinterpret_cast<const uint32_t*>(counters);
+  g_wait.epoch = reinterpret_cast<const uint32_t*>(expect);
+  g_wait.world = world;
+  g_wait.limit = (long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1900000LL;
+  return 0;
+}
 
 // Arms the NEXT blz_gemm_tc call on this thread as a fused GEMM + all-reduce: its epilogue reduces the bf16 partial
 // tiles into `mc_out` (the multicast view of a zeroed output buffer that every rank maps) and the kernel ends with a
@@ -407,6 +471,9 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   p.b_kt = b_kt;
   if (b_kt > 0 && tile_expert) return (int)cudaErrorInvalidValue;
   p.mc_out = nullptr; p.done_ctr = nullptr; p.epoch = nullptr; p.spin_limit = 0; p.rank = 0; p.world = 1;
+  p.wait_pad = g_wait.pad; p.wait_epoch = g_wait.epoch; p.wait_world = g_wait.world;
+  p.wait_limit = g_wait.limit;
+  g_wait.pad = nullptr;           // one-shot
   if (g_fuse.mc_out) {
     if (out_f32 || (N % 32)) return (int)cudaErrorInvalidValue;
     p.mc_out = g_fuse.mc_out; p.done_ctr = g_fuse.done_ctr; p.epoch = g_fuse.epoch; p.spin_limit = g_fuse.spin_limit;
