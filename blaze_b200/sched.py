@@ -13,6 +13,7 @@ draft length chosen by an online cost model (``SpecCost`` :262, ``Acceptance`` :
 from __future__ import annotations
 
 import collections
+import os
 import enum
 import queue
 import threading
@@ -370,6 +371,11 @@ class Scheduler:
         self.sample_fn = sample_fn
         self.on_step: Optional[Callable[[float, int], None]] = None
         self._ahead: Optional[_Ahead] = None
+        self._cuda_sampler = None
+        ops = getattr(getattr(engine, "model", None), "ops", None)
+        if ops is not None and getattr(ops, "is_cuda", False) and sample_fn is None and os.environ.get("BLAZE_CUDA_SAMPLER", "1") != "0":
+            from .sampler_cuda import CudaSampler
+            self._cuda_sampler = CudaSampler(ops)
         from .suffix import SuffixIndex
         self.suffix = SuffixIndex() if cfg.spec_method == "suffix" else None
 
@@ -688,6 +694,29 @@ class Scheduler:
             logits = out
         elif mode == "both":
             logits, hidden = out
+        # rows whose chain the batched CUDA sampler covers are drawn with one launch and one copy for the whole step
+        pre: Dict[int, object] = {}
+        if logits is not None and self._cuda_sampler is not None:
+            from .sampler_cuda import eligible
+            picks, rows_in, r = [], [], 0
+            for a, toks, want, draft in plan:
+                if want == 1 and not a.req.embed_only and not a.forced and eligible(a.req.params):
+                    p = a.req.params
+                    edits = penalty_edits(p, a.tokens[:a.n_prompt], a.generated, self.cfg.eos_ids) \
+                        if (p.has_penalties() or p.logit_bias) else {}
+                    allowed = a.req.constraint.mask([]) if a.req.constraint is not None else None
+                    picks.append(a)
+                    rows_in.append((p, a.rng.uniform(), edits, allowed))
+                    r_idx = r
+                    rows_in[-1] = rows_in[-1] + (r_idx,)
+                r += want
+            if picks:
+                idx = torch.tensor([x[4] for x in rows_in], device=logits.device)
+                res = self._cuda_sampler.sample(logits.index_select(0, idx).contiguous(), [x[:4] for x in rows_in],
+                                                self.engine.model.cfg.vocab_size)
+                eng.d2h_bytes += len(picks) * (8 + 4 * 130)
+                for a, rr in zip(picks, res):
+                    pre[id(a)] = rr
         row0 = 0
         seen: List[Tuple[Active, int, int, int]] = []      # (request, first row, first position, rows) for the drafter
         for a, toks, want, draft in plan:
@@ -716,6 +745,8 @@ class Scheduler:
                     tok, lp = a.forced.popleft(), None
                 elif host_tokens is not None:
                     tok, lp = host_tokens[row + j], None
+                elif id(a) in pre:
+                    tok, lp = self._take_presampled(a, pre.pop(id(a)))
                 else:
                     tok, lp = self._sample(a, logits[row + j], new)
                 new.append(tok)
@@ -792,6 +823,17 @@ class Scheduler:
         res = fn(logits_row, p, draw, edits, allowed, self.engine.model.cfg.vocab_size)
         if res.status != 0:
             raise RuntimeError(f"sampler status {res.status} for request {a.req.request_id}")
+        lp = None
+        if p.logprobs is not None:
+            lp = {"token": res.token, "logprob": res.logprob, "top": res.top[:p.logprobs]}
+        if a.req.constraint is not None:
+            a.req.constraint.advance(res.token)
+        return res.token, lp
+
+    def _take_presampled(self, a: Active, res):
+        if res.status != 0:
+            raise RuntimeError(f"sampler status {res.status} for request {a.req.request_id}")
+        p = a.req.params
         lp = None
         if p.logprobs is not None:
             lp = {"token": res.token, "logprob": res.logprob, "top": res.top[:p.logprobs]}

@@ -17,7 +17,7 @@ struct SamplingRow {
   int top_k;            // <= 64 on this path (<= 0: 64)
   int stage_mask;       // 4 bits per position: stage ids in chain order (1 penalties, 2 bias, 3 temperature, 4 top_k, 5 top_p, 6 min_p)
   int edit_begin, edit_count;    // slice of the edits array
-  int want_lse;
+  int want_lse;         // 0 no log-probs, 1 log-prob of the chosen token, 2 also the top-64 alternatives
 };
 
 struct Edit { int id; float mul_pos, mul_neg, sub, bias, banned; };
@@ -30,7 +30,8 @@ __global__ void __launch_bounds__(1024) sample_bounded_kernel(const float* __res
                                                               const SamplingRow* __restrict__ rows, const Edit* __restrict__ edits,
                                                               const uint32_t* __restrict__ allowed, int allowed_words,
                                                               long long* __restrict__ out_token, float* __restrict__ out_logprob,
-                                                              float* __restrict__ top_vals, int* __restrict__ top_ids,
+                                                              float* __restrict__ out_lse, float* __restrict__ top_vals,
+                                                              int* __restrict__ top_ids,
                                                               int* __restrict__ status, float* __restrict__ work) {
   const int r = blockIdx.x;
   const SamplingRow row = rows[r];
@@ -79,8 +80,9 @@ __global__ void __launch_bounds__(1024) sample_bounded_kernel(const float* __res
   const bool greedy = do_temp && row.temperature == 0.f;
   const float inv_t = (do_temp && row.temperature > 0.f) ? 1.f / row.temperature : 1.f;
   // ---- top-64 by repeated arg-max; every thread keeps the best of its strided slice
-  int K = row.top_k > 0 && row.top_k < 64 ? row.top_k : 64;
-  if (greedy) K = 1;
+  // candidates to collect: the top_k of the chain, or all 64 when the caller also wants log-prob alternatives
+  const int k_sel = greedy ? 1 : (row.top_k > 0 && row.top_k < 64 ? row.top_k : 64);
+  const int K = row.want_lse >= 2 ? 64 : k_sel;
   float best = -INFINITY;
   int bi = 0x7fffffff;
   for (int i = tid; i < V; i += blockDim.x) better(best, bi, w[i], i);
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(1024) sample_bounded_kernel(const float* __res
   if (found == 0) { if (tid == 0) { status[r] = -1; out_token[r] = -1; } return; }
   // ---- filters on the sorted candidates + draw (one thread; <= 64 items)
   if (tid == 0) {
-    int n = found;
+    int n = found < k_sel ? found : k_sel;
     double p[64];
     const double m = (double)cand_v[0] * inv_t;
     auto renorm = [&](int cnt) {
@@ -194,20 +196,23 @@ __global__ void __launch_bounds__(1024) sample_bounded_kernel(const float* __res
       if (v > -INFINITY) tot += exp(v - (double)mx);
       if (ed.id == chosen) canon_chosen = v;
     }
-    out_logprob[r] = (float)(canon_chosen - ((double)mx + log(tot)));
+    const double lse = (double)mx + log(tot);
+    out_logprob[r] = (float)(canon_chosen - lse);
+    out_lse[r] = (float)lse;
   }
 }
 
 }  // namespace blz
 
 // rows: R records of 9 x 4 bytes (see SamplingRow); edits: records of 6 x 4 bytes; allowed: optional bit masks
-// [R, allowed_words]; work: R * V floats of scratch.  Outputs: token ids (int64), canonical log-probs, top-64 pairs, status.
+// [R, allowed_words]; work: R * V floats of scratch.  Outputs: token ids (int64), canonical log-prob of the token, the
+// canonical log-sum-exp (rows with want_lse), the top-64 (value, id) pairs of the edited logits, status.
 BLZ_API int blz_sample_bounded(const float* logits, long long ld, int R, int V, const void* rows, const void* edits,
-                               const void* allowed, int allowed_words, long long* out_token, float* out_logprob, float* top_vals,
-                               int* top_ids, int* status, float* work, cudaStream_t s) {
+                               const void* allowed, int allowed_words, long long* out_token, float* out_logprob, float* out_lse,
+                               float* top_vals, int* top_ids, int* status, float* work, cudaStream_t s) {
   if (R == 0) return 0;
   blz::sample_bounded_kernel<<<R, 1024, 0, s>>>(logits, ld, V, (const blz::SamplingRow*)rows, (const blz::Edit*)edits,
-                                                (const uint32_t*)allowed, allowed_words, out_token, out_logprob, top_vals, top_ids,
-                                                status, work);
+                                                (const uint32_t*)allowed, allowed_words, out_token, out_logprob, out_lse, top_vals,
+                                                top_ids, status, work);
   return (int)cudaGetLastError();
 }
