@@ -53,7 +53,7 @@ class KVCache:
             else:
                 self.k[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
                 self.v[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
-        self.block_table = torch.zeros(max_seqs, max_pages_per_seq, dtype=torch.int32, device=device)
+        self._block_table = torch.zeros(max_seqs, max_pages_per_seq, dtype=torch.int32, device=device)
         self.block_table_host = np.zeros((max_seqs, max_pages_per_seq), dtype=np.int32)
         self._dirty: List[tuple] = []          # (row, first page slot, count) not yet uploaded
         # recurrent state rows: one per sequence row plus snapshot rows for the prefix cache / speculation
@@ -80,25 +80,32 @@ class KVCache:
         self.block_table_host[row, start:start + n] = pages
         self._dirty.append((row, start, n))
 
+    @property
+    def block_table(self) -> torch.Tensor:
+        """The device block table, with every pending ``set_pages`` applied (so no reader can see a stale table)."""
+        if self._dirty:
+            self.flush()
+        return self._block_table
+
     def flush(self) -> None:
         """Upload the block-table entries changed since the last flush: one copy and one scatter, in stream order
         before the step that needs them (page boundaries are crossed by many sequences in the same step)."""
         if not self._dirty:
             return
         dirty, self._dirty = self._dirty, []
-        if len(dirty) == 1 or self.block_table.device.type != "cuda":
+        if len(dirty) == 1 or self._block_table.device.type != "cuda":
             for row, start, n in dirty:
-                self.block_table[row, start:start + n] = torch.from_numpy(
-                    self.block_table_host[row, start:start + n].copy()).to(self.block_table.device)
+                self._block_table[row, start:start + n] = torch.from_numpy(
+                    self.block_table_host[row, start:start + n].copy()).to(self._block_table.device)
             return
-        W = self.block_table.shape[1]
+        W = self._block_table.shape[1]
         flat = np.concatenate([np.arange(row * W + start, row * W + start + n, dtype=np.int64) for row, start, n in dirty])
         vals = self.block_table_host.reshape(-1)[flat]
         buf = torch.empty(2, flat.size, dtype=torch.int64).pin_memory()
         buf[0].numpy()[:] = flat
         buf[1].numpy()[:] = vals
-        d = buf.to(self.block_table.device, non_blocking=True)
-        self.block_table.view(-1).index_put_((d[0],), d[1].to(torch.int32))
+        d = buf.to(self._block_table.device, non_blocking=True)
+        self._block_table.view(-1).index_put_((d[0],), d[1].to(torch.int32))
 
     def nbytes(self) -> int:
         n = 0
