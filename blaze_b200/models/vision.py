@@ -356,6 +356,32 @@ class VisionTower:
         return out
 
 
+class Vision:
+    """What the server holds: the tower plus the ids it needs to splice image embeddings into a prompt
+    (``vision.rs:88`` ``Vision::load``)."""
+
+    def __init__(self, tower: VisionTower, image_pad_id: int):
+        self.tower, self.image_pad_id = tower, image_pad_id
+        self.cfg = tower.cfg
+
+    @classmethod
+    def load(cls, model_dir: str, device) -> Optional["Vision"]:
+        tower = VisionTower.load(model_dir, device)
+        if tower is None:
+            return None
+        with open(os.path.join(model_dir, "config.json")) as f:
+            raw = json.load(f)
+        pad = raw.get("image_token_id", raw.get("vision_config", {}).get("image_token_id", -1))
+        return cls(tower, int(pad))
+
+    def encode(self, image) -> Tuple[torch.Tensor, Tuple[int, int]]:
+        """One decoded RGB image (``[H, W, 3]`` uint8) -> (embeddings ``[tokens, out_hidden]``, merged (h, w) grid)."""
+        patches, grid = preprocess(torch.as_tensor(image), self.cfg)
+        emb = self.tower.encode(patches, [grid])
+        m = self.cfg.spatial_merge_size
+        return emb, (grid[1] // m, grid[2] // m)
+
+
 def check_reference(model_dir: Optional[str], image_path: Optional[str]) -> int:
     """CLI ``vision-check``: run one image through the device tower and the C++ CPU tower and print the difference."""
     dev = "cuda" if torch.cuda.is_available() else "cpu"
