@@ -41,7 +41,8 @@ class LLM:
                  dtype=torch.bfloat16, tp=None, kv_cache_dtype: str = "auto", kv_tokens: int = 0, max_seqs: int = 256,
                  max_model_len: int = 4096, chunk: int = 2048, enable_prefix_caching: bool = True, cache_slots: int = 4,
                  use_graphs: bool = True, spec_method: str = "none", max_draft: int = 4, seed: int = 0,
-                 eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192, warm_graphs: bool = False):
+                 eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192, warm_graphs: bool = False,
+                 kv_host_tokens: int = 0):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -68,7 +69,8 @@ class LLM:
         self.sched = Scheduler(self.engine, SchedConfig(chunk=chunk, max_seqs=max_seqs, prefix_cache=enable_prefix_caching,
                                                         cache_slots=cache_slots, spec_method=spec_method, max_draft=max_draft,
                                                         eos_ids=eos, max_model_len=max_model_len,
-                                                        max_step_tokens=max_step_tokens), drafter=drafter)
+                                                        max_step_tokens=max_step_tokens, kv_host_pages=kv_host_tokens // 16),
+                               drafter=drafter)
         if warm_graphs:
             with log.Stage("graphs"):
                 self.engine.capture_decode_graphs()

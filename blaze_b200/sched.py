@@ -85,6 +85,7 @@ class CacheEntry:
     kind: SnapKind
     worth: float
     last_used: float = 0.0
+    host_run: Optional[Tuple[int, int]] = None      # (start, count) in the host tier while the pages are not on the device
 
 
 class Usefulness:
@@ -108,9 +109,16 @@ class Usefulness:
 class PrefixCache:
     """Snapshots keyed by their token list; longest strict prefix wins; GreedyDual-Size eviction."""
 
-    def __init__(self, engine: Engine, slots: int = 4, enabled: bool = True):
+    def __init__(self, engine: Engine, slots: int = 4, enabled: bool = True, host_pages: int = 0):
         self.engine, self.slots, self.enabled = engine, slots, enabled
         self.entries: List[CacheEntry] = []
+        # second tier: snapshots evicted from the device wait in pinned host memory (oldest dropped first)
+        self.host = None
+        self.host_entries: List[CacheEntry] = []
+        self.host_hits = 0
+        if enabled and host_pages > 0:
+            from .kv_host import HostKVTier
+            self.host = HostKVTier(engine.kv, host_pages)
         self.inflation = 0.0
         self.use = Usefulness()
         self.hits = self.lookups = self.hit_tokens = 0
@@ -125,6 +133,12 @@ class PrefixCache:
             L = len(e.tokens)
             if L < n and (best is None or L > len(best.tokens)) and tuple(prompt[:L]) == e.tokens:
                 best = e
+        for e in self.host_entries:
+            L = len(e.tokens)
+            if L < n and (best is None or L > len(best.tokens)) and tuple(prompt[:L]) == e.tokens:
+                best = e
+        if best is not None and best.host_run is not None and not self._promote(best):
+            best = None                # no device pages for it right now: treat as a miss
         if best is not None:
             self.hits += 1
             self.hit_tokens += len(best.tokens)
@@ -176,8 +190,41 @@ class PrefixCache:
 
     def evict(self, e: CacheEntry) -> None:
         self.inflation = max(self.inflation, e.worth)
-        self.engine.release(e.snap)
         self.entries.remove(e)
+        if self.host is not None and e.snap.state_row < 0 and e.snap.pages:
+            n = len(e.snap.pages)
+            while self.host.free_pages < n and self.host_entries:
+                old = self.host_entries.pop(0)
+                self.host.drop(old.host_run)
+            run = self.host.spill(e.snap.pages)
+            if run is not None:
+                # the copies are queued on the model's stream, so the pages may go back to the allocator right away
+                e.host_run = run
+                self.engine.release(e.snap)
+                self.host_entries.append(e)
+                return
+        self.engine.release(e.snap)
+
+    def _promote(self, e: CacheEntry) -> bool:
+        """Bring a host-resident entry back: new device pages, one copy per layer, and a device slot for it."""
+        n = e.host_run[1]
+        try:
+            pages = self.engine.pages.alloc(n)
+        except OutOfPages:
+            return False
+        self.host.restore(e.host_run, pages)
+        self.host.drop(e.host_run)
+        self.host_entries.remove(e)
+        e.host_run = None
+        e.snap = Snapshot(pages=pages, length=e.snap.length, state_row=-1)
+        self.host_hits += 1
+        while len(self.entries) >= max(self.slots, 1):
+            v = self._victim(protect=e)
+            if v is None:
+                break
+            self.evict(v)
+        self.entries.append(e)
+        return True
 
     def evict_for_room(self, protect: Optional[CacheEntry]) -> bool:
         v = self._victim(protect)
@@ -190,6 +237,9 @@ class PrefixCache:
         for e in list(self.entries):
             self.engine.release(e.snap)
         self.entries = []
+        for e in self.host_entries:
+            self.host.drop(e.host_run)
+        self.host_entries = []
 
 
 class Acceptance:
@@ -301,6 +351,7 @@ class SchedConfig:
     max_verify: int = 8
     eos_ids: Tuple[int, ...] = ()
     max_model_len: int = 4096
+    kv_host_pages: int = 0             # pinned host pages behind the prefix cache (0 = no host tier)
     run_ahead: bool = True             # launch greedy decode step k+1 before reading step k (tokens fed back on the device)
 
 
@@ -358,7 +409,7 @@ class Scheduler:
         self.waiting: Deque[GenRequest] = collections.deque()
         self.preempted: Deque[Active] = collections.deque()
         self.active: List[Active] = []
-        self.cache = PrefixCache(engine, cfg.cache_slots, cfg.prefix_cache)
+        self.cache = PrefixCache(engine, cfg.cache_slots, cfg.prefix_cache, cfg.kv_host_pages)
         self.stats = SchedStats()
         self.cost = SpecCost()
         self.inbox: "queue.Queue[GenRequest]" = queue.Queue()

@@ -380,3 +380,29 @@ def test_gdn_layer(ops):
     assert rel < 0.03
     assert (outs["cuda"][1] - outs["ref"][1]).abs().max().item() < 0.05
     assert (outs["cuda"][2] - outs["ref"][2]).abs().max().item() < 0.02
+
+
+def test_host_kv_tier_roundtrip_on_device():
+    """Spill a set of FP8 pages to pinned host memory and restore them into other pages: bytes come back identical."""
+    from blaze_b200.config import ModelConfig, RopeConfig
+    from blaze_b200.kv import KVCache
+    from blaze_b200.kv_host import HostKVTier
+    cfg = ModelConfig(hidden_size=512, num_heads=4, num_kv_heads=2, head_dim=128, num_layers=2, rope=RopeConfig(theta=1e6))
+    cfg.layer_types = ["full_attention"] * 2
+    kv = KVCache(cfg, 64, 4, 16, "fp8", "cuda", "umma")
+    for i in kv.attn_layers:
+        kv.kv[i].copy_(torch.randint(0, 255, kv.kv[i].shape, dtype=torch.uint8, device=DEV))
+    tier = HostKVTier(kv, 32)
+    src = [3, 9, 17, 4, 40]
+    want = {i: kv.kv[i][src].clone() for i in kv.attn_layers}
+    run = tier.spill(src)
+    assert run is not None and tier.free_pages == 32 - 5
+    for i in kv.attn_layers:
+        kv.kv[i][src] = 0
+    dst = [50, 51, 7, 8, 60]
+    tier.restore(run, dst)
+    torch.cuda.synchronize()
+    for i in kv.attn_layers:
+        assert torch.equal(kv.kv[i][dst], want[i])
+    tier.drop(run)
+    assert tier.free_pages == 32 and tier.free == [(0, 32)]

@@ -175,3 +175,27 @@ def test_run_ahead_stops_on_eos_seen_late_and_admits_new_requests():
     assert outs["late"] == solo.token_ids
     llm.sched.cache.clear()
     assert llm.engine.pages.free_count == llm.engine.num_pages - 1
+
+
+def test_host_kv_tier_restores_evicted_snapshots():
+    """With one device cache slot, a second conversation pushes the first one's snapshot to the host tier; when the first
+    conversation comes back its prefix is restored from there and the tokens equal a cold run."""
+    a = _prompts(1, 64, seed=21)[0]
+    b = _prompts(1, 64, seed=22)[0]
+    follow = a + [5, 6, 7, 8, 9]
+    cold = _llm(enable_prefix_caching=False).generate([follow], GREEDY)[0]
+    llm = _llm(cache_slots=1, kv_host_tokens=64 * 16)
+    llm.generate([a], GREEDY)
+    llm.generate([b], GREEDY)                       # evicts a's snapshot(s) to the host
+    cache = llm.sched.cache
+    assert cache.host is not None and cache.host_entries and cache.host.spilled_pages > 0
+    free_before = llm.engine.pages.free_count
+    got = llm.generate([follow], GREEDY)[0]
+    assert cache.host_hits == 1 and cache.host.restored_pages > 0
+    assert got.cached_tokens >= 48
+    assert got.token_ids == cold.token_ids
+    # nothing leaks: dropping every snapshot returns every page and every host page
+    cache.clear()
+    assert llm.engine.pages.free_count == llm.engine.num_pages - 1
+    assert cache.host.free_pages == cache.host.capacity
+    assert free_before > 0
