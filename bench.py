@@ -74,6 +74,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the line invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--schedule", default="prefill_first", choices=["interleave", "prefill_first"],
+                    help="scheduler policy of the end-to-end run (LLM(schedule=...)): prompts first, or decode rows + one chunk per step")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collectives: in-kernel peer memory, or NCCL")
     ap.add_argument("--cuda-profiler", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="bracket the timed decode steps (or the second prefill chunk) with cudaProfilerStart/Stop "
@@ -135,7 +137,7 @@ def main():
     t_load = time.time()
     llm = LLM(cfg, weight_format=args.weights, device=dev, tp=tp, kv_cache_dtype="fp8", kv_tokens=kv_tokens, max_seqs=B,
               max_model_len=max_len, chunk=4096, enable_prefix_caching=False, use_graphs=not args.no_graphs, seed=1,
-              max_step_tokens=B + 4096, warm_graphs=not args.no_graphs)
+              max_step_tokens=B + 4096, warm_graphs=not args.no_graphs, schedule=args.schedule)
     note("model built")
     eng = llm.engine
     ops = llm.model.ops
@@ -259,7 +261,7 @@ def main():
             "data": "synthetic token ids, random-init N(0,0.02) weights", "impl": "ours",
             "config": {"model": args.model, "global_batch": B, "seq_len": P, "parallelism": f"tp{args.gpus}", "collectives": comm,
                        "kv": "fp8 e4m3, 16-token pages", "l2": "inputs larger than L2 (KV + weights read per step >> 126 MB)",
-                       "layers": cfg.num_layers, "decode_tokens": "fed back on the device, copied to the host every step" if feed else "read by the host every step"},
+                       "layers": cfg.num_layers, "schedule": args.schedule, "decode_tokens": "fed back on the device, copied to the host every step" if feed else "read by the host every step"},
             "clocks": clocks_summary(clk_path),
             "e2e": e2e, "gpu_launches": ops.launches - l0 if not eng._graphs else eng.graph_kernel_count() * K,
             "prefill_ms": prefill_ms, "prefill_tok_s": B * P / (prefill_ms / 1e3), "load_s": t_load,

@@ -33,6 +33,9 @@ def engine_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--preset", default=None, choices=sorted(PRESETS))
     g.add_argument("--max-model-len", type=int, default=None)
     g.add_argument("--kv-tokens", default="auto", help="KV capacity in tokens, or 'auto' (size from free memory)")
+    g.add_argument("--schedule", default="interleave", choices=["interleave", "prefill_first"],
+                   help="interleave: decode rows + one prefill chunk per step; prefill_first: prompts first, decode rows join "
+                        "at most every 0.25 s while prompts are waiting")
     g.add_argument("--kv-host-tokens", type=int, default=0,
                    help="pinned host memory behind the prefix cache, in tokens: evicted snapshots wait there (0 = off)")
     g.add_argument("--kv-cache-dtype", default=None, choices=["fp8", "bf16", "fp32", "nvfp4", "nvfp4_4over6", "auto"])
@@ -177,7 +180,7 @@ def build_llm(ns: argparse.Namespace):
               chunk=ns.chunk or 2048, enable_prefix_caching=not ns.disable_prefix_caching,
               cache_slots=ns.prompt_cache_slots or 4, use_graphs=not ns.no_graphs,
               spec_method=ns.spec_method or "none", max_draft=min(ns.max_verify - 1, 8), seed=ns.seed,
-              kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0)
+              kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"))
     if group is not None and ns.comm == "fused" and device.startswith("cuda"):
         from .parallel.symm import SymmAllReduce
         group.fused = SymmAllReduce.create(group, device, max_rows=(ns.chunk or 2048) + (ns.max_seqs or 256) + 64,

@@ -351,6 +351,11 @@ class SchedConfig:
     max_verify: int = 8
     eos_ids: Tuple[int, ...] = ()
     max_model_len: int = 4096
+    # "interleave": every step takes all decoding requests plus at most one prefill chunk (steady token flow for running
+    # requests); "prefill_first": while prompts are waiting to be read, steps carry prefill chunks only and decoding
+    # requests join at most every `max_decode_stall` seconds (higher throughput and earlier first tokens under bursts)
+    schedule: str = "interleave"
+    max_decode_stall: float = 0.25
     kv_host_pages: int = 0             # pinned host pages behind the prefix cache (0 = no host tier)
     run_ahead: bool = True             # launch greedy decode step k+1 before reading step k (tokens fed back on the device)
 
@@ -422,6 +427,7 @@ class Scheduler:
         self.sample_fn = sample_fn
         self.on_step: Optional[Callable[[float, int], None]] = None
         self._ahead: Optional[_Ahead] = None
+        self._last_decode = 0.0
         self._cuda_sampler = None
         ops = getattr(getattr(engine, "model", None), "ops", None)
         if ops is not None and getattr(ops, "is_cuda", False) and sample_fn is None and os.environ.get("BLAZE_CUDA_SAMPLER", "1") != "0":
@@ -673,6 +679,11 @@ class Scheduler:
         plan: List[Tuple[Active, List[int], int, List[int]]] = []   # (active, tokens, want_logits, draft)
         budget = cfg.max_step_tokens
         decoders = [a for a in self.active if a.computed == len(a.tokens) - 1 and a.computed >= a.n_prompt - 1]
+        if cfg.schedule == "prefill_first" and decoders and len(decoders) < len(self.active):
+            if t0 - self._last_decode < cfg.max_decode_stall:
+                decoders = []            # prompts first; the running requests wait a bounded time
+        if decoders:
+            self._last_decode = t0
         spec = cfg.spec_method != "none" and decoders
         drafts: Dict[int, List[int]] = {}
         if spec:
@@ -682,10 +693,13 @@ class Scheduler:
             plan.append((a, [a.tokens[-1]] + d, 1 + len(d), d))
             budget -= 1 + len(d)
         chunk_left = min(cfg.chunk, max(budget, 0))
+        dec_ids = {id(a) for a in decoders}
         for a in self.active:
-            if a in decoders or chunk_left <= 0:
+            if id(a) in dec_ids or chunk_left <= 0:
                 continue
             remaining = len(a.tokens) - a.computed
+            if remaining <= 1 and a.computed >= a.n_prompt - 1:
+                continue                 # a decoding request that sits this step out
             n = min(remaining, chunk_left)
             for pt in a.snap_points:
                 if a.computed < pt < a.computed + n:

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define BLZ_API extern "C" __attribute__((visibility("default")))
 
@@ -18,6 +19,33 @@ int* status_word();
 cudaError_t encode_tmap(CUtensorMap* out, const void* base, int dtype_bytes, uint64_t dim0, uint64_t dim1,
                         uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle, uint64_t dim2 = 0,
                         uint64_t stride2_bytes = 0, uint32_t box2 = 1);
+
+// BLAZE_PDL=0 turns programmatic dependent launch off (every kernel then starts after its predecessor has finished).
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("BLAZE_PDL");
+    on = (e && e[0] == '1') ? 1 : 0;
+  }
+  return on != 0;
+}
+
+// Launch a kernel that follows the pdl_trigger / pdl_wait protocol (sm100.cuh) so that its prologue — and, for the
+// GEMMs, the first weight tiles — overlap the tail of the kernel before it on the stream.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 inline int sm_count() {
   static int n = 0;

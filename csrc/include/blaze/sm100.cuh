@@ -234,6 +234,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may become resident while its
+// predecessor still runs.  pdl_trigger() lets the successor of THIS kernel do so; pdl_wait() returns when the predecessor
+// has completed and its memory is visible — nothing it wrote may be read, and no global memory written, before that.
+// Both are no-ops for kernels launched the plain way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // named barrier among a subset of warps
 __device__ __forceinline__ void bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

@@ -52,6 +52,7 @@ __device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[N]) {
 
 template <int NMAX, int RMAX>
 __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_decode_kernel(AttnParams p) {
+  pdl_trigger();
   using Cfg = DecCfg<NMAX, RMAX>;
   constexpr int ST = Cfg::STAGES, D = Cfg::D, NB = Cfg::NB;
   extern __shared__ uint8_t smem_raw[];
@@ -101,6 +102,7 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();          // the queries and this step's K/V rows come from the kernel before this one
 
   const int group = p.Hq / p.Hkv;
   const int total = p.num_items * p.Hkv * p.row_blocks * p.splits;
@@ -398,6 +400,8 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
 // Merge kv-split partials of the decode kernel.  One CTA per (sequence, kv head, row block); thread = dimension.
 template <int NMAX>
 __global__ void attn_decode_combine_kernel(AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int D = 128;
   const int rb = blockIdx.x % p.row_blocks;
   const int kh = (blockIdx.x / p.row_blocks) % p.Hkv;
@@ -443,11 +447,9 @@ static cudaError_t launch_decode(const AttnParams& p, int max_ctas, cudaStream_t
   const int cap = Cfg::CTAS_PER_SM * sm_count();
   int grid = total < cap ? total : cap;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  attn_decode_kernel<NMAX, RMAX><<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(attn_decode_kernel<NMAX, RMAX>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM, stream, p);
   if (e != cudaSuccess || p.splits == 1) return e;
-  attn_decode_combine_kernel<NMAX><<<p.num_items * p.Hkv * p.row_blocks, 128, 0, stream>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(attn_decode_combine_kernel<NMAX>, dim3(p.num_items * p.Hkv * p.row_blocks), dim3(128), 0, stream, p);
 }
 
 }  // namespace blz

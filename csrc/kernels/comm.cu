@@ -184,6 +184,8 @@ __device__ __forceinline__ void bcast4(const CommParams& c, void* const* peers, 
 template <bool MC>
 __global__ void __launch_bounds__(512) allreduce_kernel(CommParams c, size_t n16) {
   __shared__ int ok;
+  pdl_trigger();
+  pdl_wait();
   stamp(c, 0);
   if (!rank_barrier(c, &ok, 0)) return;
   stamp(c, 1);
@@ -259,6 +261,8 @@ __global__ void __launch_bounds__(1024) allreduce_norm_kernel(CommParams c, __nv
                                                               int defer_exit) {
   __shared__ float red[32];
   __shared__ int ok;
+  pdl_trigger();
+  pdl_wait();
   stamp(c, 0);
   if (defer_exit && blockIdx.x == 0 && threadIdx.x == 0) *c.sig_expect += gridDim.x;
   if (!rank_barrier(c, &ok, 0)) return;
@@ -434,8 +438,8 @@ BLZ_API int blz_comm_allreduce(void* h, void* const* in, void* const* out, void*
   if (!c || nbytes % 16 || blocks < 1 || blocks > kMaxBlocks) return (int)cudaErrorInvalidValue;
   CommParams p = c->p;
   fill(p, p.world, in, out, nullptr, nullptr, mc_in, mc_out, nullptr, nullptr);
-  if (mc_in && mc_out) allreduce_kernel<true><<<blocks, 512, 0, s>>>(p, (size_t)nbytes / 16);
-  else allreduce_kernel<false><<<blocks, 512, 0, s>>>(p, (size_t)nbytes / 16);
+  if (mc_in && mc_out) launch_pdl(allreduce_kernel<true>, dim3(blocks), dim3(512), 0, s, p, (size_t)nbytes / 16);
+  else launch_pdl(allreduce_kernel<false>, dim3(blocks), dim3(512), 0, s, p, (size_t)nbytes / 16);
   return (int)cudaGetLastError();
 }
 
@@ -459,7 +463,7 @@ BLZ_API int blz_comm_allreduce_norm(void* h, void* const* in, void* const* out, 
   const int ct = quant == 1 ? (H + 63) / 64 : (H + 127) / 128;
   __nv_bfloat16* res = reinterpret_cast<__nv_bfloat16*>(residual);
   const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(norm_w);
-#define BLZ_ARN3(MCV, Q, C) allreduce_norm_kernel<MCV, Q, C><<<blocks, thr, 0, s>>>(p, res, w, T, H, rows_per, eps, zero_centered, ct, defer_exit)
+#define BLZ_ARN3(MCV, Q, C) launch_pdl(allreduce_norm_kernel<MCV, Q, C>, dim3(blocks), dim3(thr), 0, s, p, res, w, T, H, rows_per, eps, zero_centered, ct, defer_exit)
 #define BLZ_ARN2(MCV, Q)                                                                  \
   { if (ch == 1) BLZ_ARN3(MCV, Q, 1); else if (ch == 2) BLZ_ARN3(MCV, Q, 2); else if (ch == 3) BLZ_ARN3(MCV, Q, 3); else BLZ_ARN3(MCV, Q, 4); }
   if (mc) { if (quant == 0) BLZ_ARN2(true, 0) else if (quant == 1) BLZ_ARN2(true, 1) else BLZ_ARN2(true, 2) }

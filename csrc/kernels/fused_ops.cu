@@ -45,6 +45,8 @@ __device__ __forceinline__ size_t sf_offset(int row, int col, int col_tiles) {
 // ---------------------------------------------------------------------------------------------- embedding
 __global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
                              __nv_bfloat16* __restrict__ out, int H, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
@@ -287,6 +289,8 @@ __global__ void __launch_bounds__(512) rmsnorm_reg_kernel(__nv_bfloat16* __restr
                                                             uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out,
                                                             float* __restrict__ row_scale, int H, float eps, int zero_centered,
                                                             int sf_col_tiles, int zero_src) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int t = blockIdx.x;
   __nv_bfloat16* xr = x + (size_t)t * H;
@@ -353,6 +357,8 @@ template <int MODE, int CH>
 __global__ void __launch_bounds__(512) swiglu_reg_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                                            uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out,
                                                            float* __restrict__ row_scale, int I, int src_is_act, int sf_col_tiles) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int t = blockIdx.x;
   const __nv_bfloat16* g = gu + (size_t)t * (src_is_act ? I : 2 * I);
@@ -410,6 +416,8 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const __nv_bfloat16* __r
                                  const __nv_bfloat16* __restrict__ k_norm_w, int T, int Hq, int Hkv, int rot_dim,
                                  float eps, float rope_scale, int gated, int zero_centered, float k_scale_inv,
                                  float v_scale_inv) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int VPL = D / 32;
   __shared__ float2 cs[D / 2];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -536,6 +544,8 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
 // argmax over fp32 rows, lowest index wins ties; writes int64 ids (and optionally the max value)
 __global__ void argmax_kernel(const float* __restrict__ logits, long long* __restrict__ out, float* __restrict__ out_val,
                               int V, long long ld, int index_offset) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* row = logits + (size_t)blockIdx.x * ld;
@@ -609,7 +619,7 @@ static inline int norm_threads(int H) {
 BLZ_API int blz_embed(const void* table, const int* tokens, void* out, int T, int H, int vocab, cudaStream_t s) {
   if (H % 8) return (int)cudaErrorInvalidValue;
   if (T == 0) return 0;
-  embed_kernel<<<T, 256, 0, s>>>((const bf16*)table, tokens, (bf16*)out, H, vocab);
+  launch_pdl(embed_kernel, dim3(T), dim3(256), 0, s, (const bf16*)table, tokens, (bf16*)out, H, vocab);
   return (int)cudaGetLastError();
 }
 
@@ -626,9 +636,9 @@ BLZ_API int blz_rmsnorm(void* x, void* residual, const void* w, void* out, void*
   reg_shape(H, &rt, &ch);
   if (ch) {
 #define BLZ_RN(C)                                                                                                              \
-  if (quant == 0) rmsnorm_reg_kernel<0, C><<<T, rt, 0, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, nullptr, nullptr, nullptr, H, eps, zero_centered, 0, zero_src); \
-  else if (quant == 1) rmsnorm_reg_kernel<1, C><<<T, rt, 0, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src); \
-  else rmsnorm_reg_kernel<2, C><<<T, rt, 0, s>>>((bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src)
+  if (quant == 0) launch_pdl(rmsnorm_reg_kernel<0, C>, dim3(T), dim3(rt), 0, s, (bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, (uint8_t*)nullptr, (uint8_t*)nullptr, (float*)nullptr, H, eps, zero_centered, 0, zero_src); \
+  else if (quant == 1) launch_pdl(rmsnorm_reg_kernel<1, C>, dim3(T), dim3(rt), 0, s, (bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src); \
+  else launch_pdl(rmsnorm_reg_kernel<2, C>, dim3(T), dim3(rt), 0, s, (bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, H, eps, zero_centered, ct, zero_src)
     BLZ_CH_SWITCH(ch, BLZ_RN)
 #undef BLZ_RN
     return (int)cudaGetLastError();
@@ -655,9 +665,9 @@ BLZ_API int blz_swiglu(const void* gu, void* out, void* q_out, void* sf_out, flo
   reg_shape(I, &rt, &ch);
   if (ch) {
 #define BLZ_SW(C)                                                                                                              \
-  if (mode == 0) swiglu_reg_kernel<0, C><<<T, rt, 0, s>>>((const bf16*)gu, (bf16*)out, nullptr, nullptr, nullptr, I, src_is_act, 0); \
-  else if (mode == 1) swiglu_reg_kernel<1, C><<<T, rt, 0, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct); \
-  else swiglu_reg_kernel<2, C><<<T, rt, 0, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct)
+  if (mode == 0) launch_pdl(swiglu_reg_kernel<0, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)out, (uint8_t*)nullptr, (uint8_t*)nullptr, (float*)nullptr, I, src_is_act, 0); \
+  else if (mode == 1) launch_pdl(swiglu_reg_kernel<1, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct); \
+  else launch_pdl(swiglu_reg_kernel<2, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct)
     BLZ_CH_SWITCH(ch, BLZ_SW)
 #undef BLZ_SW
     return (int)cudaGetLastError();
@@ -679,10 +689,9 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
   const int wpb = (Hq + 2 * Hkv) >= 8 ? 8 : (Hq + 2 * Hkv);
   const int grid = T;
 #define BLZ_PREP(DD)                                                                                                 \
-  attn_prep_kernel<DD><<<grid, wpb * 32, 0, s>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)gate_out, (uint8_t*)kv_pool, \
-                                                 positions, slot_mapping, inv_freq, (const bf16*)q_norm_w,            \
-                                                 (const bf16*)k_norm_w, T, Hq, Hkv, rot_dim, eps, rope_scale, gated,  \
-                                                 zero_centered, 1.f / k_scale, 1.f / v_scale)
+  launch_pdl(attn_prep_kernel<DD>, dim3(grid), dim3(wpb * 32), 0, s, (const bf16*)qkv, (bf16*)q_out, (bf16*)gate_out,  \
+             (uint8_t*)kv_pool, positions, slot_mapping, inv_freq, (const bf16*)q_norm_w, (const bf16*)k_norm_w, T, Hq, \
+             Hkv, rot_dim, eps, rope_scale, gated, zero_centered, 1.f / k_scale, 1.f / v_scale)
   if (D == 64) BLZ_PREP(64); else if (D == 128) BLZ_PREP(128); else BLZ_PREP(256);
 #undef BLZ_PREP
   return (int)cudaGetLastError();
@@ -712,6 +721,6 @@ BLZ_API int blz_gather_rows(const void* x, const int* rows, void* out, int R, in
 BLZ_API int blz_argmax(const float* logits, long long* out, float* out_val, int R, int V, long long ld, int index_offset,
                        cudaStream_t s) {
   if (R == 0) return 0;
-  argmax_kernel<<<R, 1024, 0, s>>>(logits, out, out_val, V, ld, index_offset);
+  launch_pdl(argmax_kernel, dim3(R), dim3(1024), 0, s, logits, out, out_val, V, ld, index_offset);
   return (int)cudaGetLastError();
 }

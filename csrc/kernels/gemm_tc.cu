@@ -78,6 +78,7 @@ struct GemmCfg {
 template <int KIND, int BN, bool OUT_F32>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  pdl_trigger();
   using Cfg = GemmCfg<KIND, BN>;
   constexpr int BM = Cfg::BM, BK = Cfg::BK, STAGES = Cfg::STAGES, ACC = Cfg::ACC_BUFS;
   extern __shared__ uint8_t smem_raw[];
@@ -151,15 +152,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
     };
-    int pre = 0;                      // stages of the first tile whose weights went out before the wait
+    // The weights do not depend on the kernel before this one: the first tile's B stages go out first, then the producer
+    // waits for that kernel (and, when armed, for the peers' arrival counters), then it loads the activations.
+    int pre = 0;
     bool go = true;
+    if (lane == 0 && (int)blockIdx.x < num_tiles && !p.tile_expert) {
+      pre = min(STAGES, k_tiles);
+      const int t = blockIdx.x;
+      for (int kt = 0; kt < pre; ++kt) issue(kt, t % tiles_m, t / tiles_m, 0, kt, 1);
+    }
+    pre = __shfl_sync(0xffffffffu, pre, 0);
+    pdl_wait();
     if (p.wait_pad != nullptr) {
-      if (lane == 0 && (int)blockIdx.x < num_tiles && !p.tile_expert) {
-        pre = min(STAGES, k_tiles);
-        const int t = blockIdx.x;
-        for (int kt = 0; kt < pre; ++kt) issue(kt, t % tiles_m, t / tiles_m, 0, kt, 1);
-      }
-      pre = __shfl_sync(0xffffffffu, pre, 0);
       if (lane < p.wait_world) {
         const uint32_t want = *p.wait_epoch;
         const uint32_t* f = p.wait_pad + lane;
@@ -197,6 +201,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    pdl_wait();
     if (elect_one()) {
       int s = 0; uint32_t ph = 0;
       int it = 0;
@@ -252,6 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
+    pdl_wait();
     const int q = warp & 3;                       // TMEM lane quadrant this warp may read
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -391,8 +397,7 @@ static cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kern<<<grid, 192, Cfg::SMEM, stream>>>(tmA, tmB, p);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(grid), dim3(192), Cfg::SMEM, stream, tmA, tmB, p);
 }
 
 }  // namespace blz

@@ -77,6 +77,7 @@ struct WideCfg {
 template <int KIND, int BN, bool SWAP>
 __global__ void __launch_bounds__(320, 1) gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA,
                                                             const __grid_constant__ CUtensorMap tmB, const WideParams p) {
+  pdl_trigger();
   using Cfg = WideCfg<KIND, BN>;
   constexpr int STAGES = Cfg::STAGES, BK = Cfg::BK, CPT = Cfg::CPT;
   extern __shared__ uint8_t smem_raw[];
@@ -118,6 +119,7 @@ __global__ void __launch_bounds__(320, 1) gemm_wide_kernel(const __grid_constant
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t SF_COL0 = BN;
+  pdl_wait();
 
   // unit u -> (lane tile, column tile, k slice); lane tiles of one column tile are neighbours so that CTAs running
   // together share the column operand in L2
@@ -396,8 +398,7 @@ static cudaError_t launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, c
   }
   int grid = units < sm_count() ? units : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tmA, tmB, p);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM, stream, tmA, tmB, p);
 }
 
 }  // namespace blz

@@ -199,3 +199,22 @@ def test_host_kv_tier_restores_evicted_snapshots():
     assert llm.engine.pages.free_count == llm.engine.num_pages - 1
     assert cache.host.free_pages == cache.host.capacity
     assert free_before > 0
+
+
+def test_prefill_first_schedule_keeps_tokens_and_defers_decode_rows():
+    ps = _prompts(6, 40, seed=31)
+    sp = SamplingParams(temperature=0.0, max_tokens=10)
+    want = [o.token_ids for o in _llm(chunk=48).generate(ps, sp)]
+    llm = _llm(chunk=48, schedule="prefill_first")
+    llm.sched.cfg.max_decode_stall = 3600.0           # never force decode rows into a prefill step in this test
+    mixed = []
+    fwd = llm.engine.forward
+
+    def spy(chunks, mode="greedy", hidden_in=None, feedback=False):
+        lens = [len(c.tokens) for c in chunks]
+        mixed.append(any(n == 1 for n in lens) and any(n > 1 for n in lens))
+        return fwd(chunks, mode, hidden_in, feedback)
+    llm.engine.forward = spy
+    got = [o.token_ids for o in llm.generate(ps, sp)]
+    assert got == want
+    assert sum(mixed) <= 1, "decode rows should sit out while prompts are being read"
