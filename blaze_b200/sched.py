@@ -408,6 +408,17 @@ class _Ahead:
         self.actives, self.tokens, self.event, self.t0 = actives, tokens, event, t0
 
 
+class _Pending:
+    """A launched step whose results the host has not consumed yet."""
+    __slots__ = ("plan", "mode", "out", "t0", "seen", "host", "event")
+
+    def __init__(self, plan, mode, out, t0):
+        self.plan, self.mode, self.out, self.t0 = plan, mode, out, t0
+        self.seen: List[tuple] = []      # (request, first row, first position, rows)
+        self.host = None                 # pinned copy of the greedy tokens when the step is left in flight
+        self.event = None
+
+
 class Scheduler:
     def __init__(self, engine: Engine, cfg: SchedConfig, drafter=None, sample_fn=None):
         self.engine, self.cfg, self.drafter = engine, cfg, drafter
@@ -427,6 +438,7 @@ class Scheduler:
         self.sample_fn = sample_fn
         self.on_step: Optional[Callable[[float, int], None]] = None
         self._ahead: Optional[_Ahead] = None
+        self._pending: Optional[_Pending] = None
         self._last_decode = 0.0
         self._cuda_sampler = None
         ops = getattr(getattr(engine, "model", None), "ops", None)
@@ -454,7 +466,7 @@ class Scheduler:
 
     @property
     def idle(self) -> bool:
-        return not (self.active or self.waiting or self.preempted or self._ahead) and self.inbox.empty()
+        return not (self.active or self.waiting or self.preempted or self._ahead or self._pending) and self.inbox.empty()
 
     def run_until_idle(self, max_steps: int = 1 << 30) -> None:
         n = 0
@@ -473,6 +485,7 @@ class Scheduler:
                 self.step()
             except Exception as e:  # a failed step fails the active requests but keeps the loop alive
                 log.error("sched.step_failed", error=repr(e))
+                self._ahead = self._pending = None
                 for a in list(self.active):
                     self._retire(a, Finish.ERROR, error=repr(e))
                 self.stats.failed += 1
@@ -698,8 +711,8 @@ class Scheduler:
             if id(a) in dec_ids or chunk_left <= 0:
                 continue
             remaining = len(a.tokens) - a.computed
-            if remaining <= 1 and a.computed >= a.n_prompt - 1:
-                continue                 # a decoding request that sits this step out
+            if remaining <= 0 or (remaining <= 1 and a.computed >= a.n_prompt - 1):
+                continue                 # its last step is still in flight, or a decoding request that sits this step out
             n = min(remaining, chunk_left)
             for pt in a.snap_points:
                 if a.computed < pt < a.computed + n:
@@ -709,6 +722,9 @@ class Scheduler:
             plan.append((a, a.tokens[a.computed:a.computed + n], 1 if last else 0, []))
             chunk_left -= n
         if not plan:
+            if self._pending is not None:
+                prev, self._pending = self._pending, None
+                self._consume(prev)
             return
         # ---- KV room (recompute-preempt the newest request when pages run out)
         while True:
@@ -744,6 +760,54 @@ class Scheduler:
                 and eng.can_feed_back(len(plan)) and all(self._plain_greedy(a) and self._continues(a, 1) for a, _, _, _ in plan)):
             self._ahead = self._hand_off([a for a, _, _, _ in plan], out, t0)
             return
+        pend = _Pending(plan, mode, out, t0)
+        self._advance(pend)
+        # The step before this one may still be unread: its results are taken now, while the GPU works on the new step.
+        prev, self._pending = self._pending, None
+        if prev is not None:
+            self._consume(prev)
+        if self._may_stay_in_flight(pend):
+            if mode == "greedy":
+                if out.device.type == "cuda":
+                    pend.host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+                    pend.host.copy_(out, non_blocking=True)
+                    pend.event = torch.cuda.Event()
+                    pend.event.record()
+                else:
+                    pend.host = out.clone()
+            self._pending = pend
+        else:
+            self._consume(pend)
+
+    def _may_stay_in_flight(self, pend: "_Pending") -> bool:
+        """Plain greedy / headless steps without drafts: nothing the host decides next depends on their tokens, except
+        for the requests in the step themselves, and those sit out until the tokens are read."""
+        if not self.cfg.run_ahead or self.drafter is not None or pend.mode not in ("greedy", "none"):
+            return False
+        if pend.out is not None and pend.out.device.type != "cuda":
+            return self.engine.ecfg.feedback_eager          # CPU tests of the overlap logic
+        if pend.out is None and self.engine.device.type != "cuda":
+            return self.engine.ecfg.feedback_eager
+        # decode rows would have to sit out the next step (their token is not read yet): only prompt chunks stay in flight
+        if any(p0 >= a.n_prompt - 1 for a, _, p0, _ in pend.seen):
+            return False
+        return all(not d and (w == 0 or self._plain_greedy(a)) for a, _, w, d in pend.plan)
+
+    def _advance(self, pend: "_Pending") -> None:
+        """Book the step's rows as computed (and take the prefix-cache snapshots that fall on its end) at launch time."""
+        row0 = 0
+        for a, toks, want, draft in pend.plan:
+            pend.seen.append((a, row0, a.computed, len(toks)))
+            row0 += len(toks)
+            a.computed += len(toks)
+            a._started = True
+            if a.computed in a.snap_points and a.computed <= a.n_prompt:
+                kind = SnapKind.POINT if a.req.cache_point and a.computed <= a.req.cache_point else SnapKind.PROMPT
+                self.cache.remember(a.tokens[:a.computed], a.seq, kind)
+
+    def _consume(self, pend: "_Pending") -> None:
+        eng = self.engine
+        plan, mode, out, t0 = pend.plan, pend.mode, pend.out, pend.t0
         # ---- consume results
         row = 0
         rows_total = sum(len(t) for _, t, _, _ in plan)
@@ -753,7 +817,12 @@ class Scheduler:
             out, hidden = out
             mode = "greedy"
         if mode == "greedy":
-            host_tokens = out.tolist()
+            if pend.host is not None:
+                if pend.event is not None:
+                    pend.event.synchronize()
+                host_tokens = pend.host.tolist()
+            else:
+                host_tokens = out.tolist()
             eng.d2h_bytes += out.numel() * out.element_size()
         elif mode == "logits":
             logits = out
@@ -782,17 +851,12 @@ class Scheduler:
                 eng.d2h_bytes += len(picks) * (8 + 4 * 130)
                 for a, rr in zip(picks, res):
                     pre[id(a)] = rr
-        row0 = 0
-        seen: List[Tuple[Active, int, int, int]] = []      # (request, first row, first position, rows) for the drafter
+        seen = pend.seen
         for a, toks, want, draft in plan:
-            seen.append((a, row0, a.computed, len(toks)))
-            row0 += len(toks)
-            a.computed += len(toks)
-            a._started = True
-            if a.computed in a.snap_points and a.computed <= a.n_prompt:
-                kind = SnapKind.POINT if a.req.cache_point and a.computed <= a.req.cache_point else SnapKind.PROMPT
-                self.cache.remember(a.tokens[:a.computed], a.seq, kind)
             if not want:
+                continue
+            if a.seq is None:            # aborted or preempted while the step was in flight
+                row += want
                 continue
             if a.req.embed_only:
                 from .batch import StepBatch  # noqa: F401

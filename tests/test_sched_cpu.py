@@ -218,3 +218,36 @@ def test_prefill_first_schedule_keeps_tokens_and_defers_decode_rows():
     got = [o.token_ids for o in llm.generate(ps, sp)]
     assert got == want
     assert sum(mixed) <= 1, "decode rows should sit out while prompts are being read"
+
+
+def test_steps_left_in_flight_give_the_same_results():
+    """Chunked prefill, KV pressure with preemption and prefix-cache reuse with launched-but-unread steps (the overlap the
+    GPU path uses) must give the tokens of the step-by-step scheduler."""
+    ps = _prompts(6, 70, seed=41)
+    sp = SamplingParams(temperature=0.0, max_tokens=14)
+    want = [o.token_ids for o in _llm(chunk=32).generate(ps, sp)]
+    for schedule in ("interleave", "prefill_first"):
+        llm = _ahead_llm(chunk=32, schedule=schedule)
+        seen_pending = []
+        orig = llm.sched.step
+
+        def step(orig=orig, llm=llm, seen_pending=seen_pending):
+            orig()
+            seen_pending.append(llm.sched._pending is not None)
+        llm.sched.step = step
+        got = [o.token_ids for o in llm.generate(ps, sp)]
+        assert got == want, schedule
+        assert any(seen_pending), "some steps should have been left in flight"
+    # KV pressure: preemption may hit a request whose step is still unread
+    want2 = [o.token_ids for o in _llm().generate(_prompts(6, 40, seed=3), SamplingParams(temperature=0.0, max_tokens=30))]
+    small = _ahead_llm(kv_tokens=16 * 16, enable_prefix_caching=False)
+    got2 = [o.token_ids for o in small.generate(_prompts(6, 40, seed=3), SamplingParams(temperature=0.0, max_tokens=30))]
+    assert got2 == want2 and small.sched.stats.preemptions > 0
+    assert small.engine.pages.free_count == small.engine.num_pages - 1
+    # prefix cache across requests
+    llm = _ahead_llm()
+    base = _prompts(1, 64, seed=2)[0]
+    first = llm.generate([base + [5, 6, 7]], GREEDY)[0]
+    second = llm.generate([base + [5, 6, 7] + first.token_ids[:4] + [9]], GREEDY)[0]
+    cold = _llm(enable_prefix_caching=False).generate([base + [5, 6, 7] + first.token_ids[:4] + [9]], GREEDY)[0]
+    assert second.cached_tokens >= 64 and second.token_ids == cold.token_ids
