@@ -38,7 +38,12 @@ class TPGroup:
             if backend == "nccl":
                 kw["device_id"] = torch.device(device)
             dist.init_process_group(backend, rank=rank, world_size=world, **kw)
-        return cls(rank, world, dist.group.WORLD, device)
+        g = cls(rank, world, dist.group.WORLD, device)
+        if dist.get_backend() == "nccl":
+            # Control messages (step plans, quit) travel over a host-side group: an object broadcast over NCCL is ordered
+            # behind the kernels already queued on the stream and would make every rank wait for the GPU each step.
+            g.ctrl = dist.new_group(backend="gloo")
+        return g
 
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -78,7 +83,7 @@ class TPGroup:
 
     def broadcast_object(self, obj, src: int = 0):
         box = [obj]
-        dist.broadcast_object_list(box, src=src, group=self.pg)
+        dist.broadcast_object_list(box, src=src, group=getattr(self, "ctrl", None) or self.pg)
         return box[0]
 
     def barrier(self):
