@@ -509,7 +509,7 @@ class Model:
         ops = self.ops
         tp = self.tp.world > 1
         if isinstance(M, DenseMlp):
-            a = ops.silu_mul(ops.linear(M.gate_up, h), quant_for=M.down)
+            a = ops.linear_swiglu(M.gate_up, h, quant_for=M.down)
             return self._row_cut(M.down, a, a.rows if hasattr(a, "rows") else a.shape[0], fused)
         hd = h.dense if hasattr(h, "dense") and h.dense is not None else h
         logits = ops.linear(M.router, hd, out_dtype=torch.float32)
@@ -522,7 +522,7 @@ class Model:
         y = ops.moe(hd, w, ids, M.experts)
         routed_partial = tp
         if M.shared is not None:
-            s = ops.linear(M.shared.down, ops.silu_mul(ops.linear(M.shared.gate_up, hd), quant_for=M.shared.down))
+            s = ops.linear(M.shared.down, ops.linear_swiglu(M.shared.gate_up, hd, quant_for=M.shared.down))
             if tp and not routed_partial:
                 s = ops.all_reduce(s, self.tp.group)
             if M.shared_gate is not None:

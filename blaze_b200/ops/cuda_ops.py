@@ -45,13 +45,13 @@ class CudaOps:
         lib = self.lib
         lib.blz_gemm_tc.restype = _c.c_int
         lib.blz_gemm_tc.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
-                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, _c.c_int, VP]
+                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_gemm_wait_flags.restype = _c.c_int
         lib.blz_gemm_wait_flags.argtypes = [VP, VP, _c.c_int, _c.c_int]
         lib.blz_gemm_wide.restype = _c.c_int
         lib.blz_gemm_wide.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
                                       _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_longlong, VP,
-                                      _c.c_int, _c.c_int, VP]
+                                      _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_gemm_wide_ksplit.restype = _c.c_int
         lib.blz_gemm_wide_ksplit.argtypes = [_c.c_int, _c.c_int, _c.c_int]
         self._wide_ok = os.environ.get("BLAZE_GEMM_WIDE", "1") != "0"
@@ -121,12 +121,24 @@ class CudaOps:
         kt = KP // 128
         return b.view(NP // 128, 128, kt, 128).permute(0, 2, 1, 3).contiguous(), kt
 
-    def pack(self, lin: Linear, tiled: Optional[bool] = None):
+    @staticmethod
+    def swiglu_order(n_rows: int) -> torch.Tensor:
+        """Row order that turns stacked ``[gate (I rows); up (I rows)]`` into groups of 16 gate rows followed by the 16 up
+        rows of the same features, so that one 32-column group of the GEMM output holds both halves of 16 activations."""
+        I = n_rows // 2
+        g = torch.arange(I).view(I // 16, 16)
+        return torch.cat([g, g + I], dim=1).reshape(-1)
+
+    def pack(self, lin: Linear, tiled: Optional[bool] = None, swiglu: bool = False):
         """``tiled`` (default: off unless BLAZE_TILED_WEIGHTS=1): store the weight tile-major (see ``tile_major``); the grouped
-        expert GEMM asks for row-major."""
+        expert GEMM asks for row-major.  ``swiglu``: interleave the gate and up rows for the GEMM's SwiGLU epilogue (the
+        packed weight is then only valid for ``linear_swiglu``)."""
         if lin.cuda_pack is not None:
+            if bool(lin.cuda_pack.get("swiglu")) != bool(swiglu):
+                raise CudaError("this weight was packed for the other epilogue (plain / SwiGLU)")
             return lin.cuda_pack
-        pk = self._pack(lin)
+        pk = self._pack(lin, self.swiglu_order(lin.N).to(self.device) if swiglu else None)
+        pk["swiglu"] = bool(swiglu)
         if tiled is None:
             tiled = self._tiled_ok
         pk["kt"] = 0
@@ -135,16 +147,21 @@ class CudaOps:
         lin.cuda_pack = pk
         return pk
 
-    def _pack(self, lin: Linear):
+    def _pack(self, lin: Linear, order: Optional[torch.Tensor] = None):
+        """``order``: optional permutation of the output rows applied to the weight, its scales, alpha and bias."""
         dev = self.device
+
+        def perm(t):
+            return t if (order is None or t is None) else t.to(dev)[order]
+
         if lin.fmt == Format.DENSE:
-            pk = {"kind": 0, "w": lin.w.to(dev, torch.bfloat16).contiguous(), "sf": None, "alpha": None}
+            pk = {"kind": 0, "w": perm(lin.w.to(dev, torch.bfloat16)).contiguous(), "sf": None, "alpha": None}
         elif lin.fmt == Format.NVFP4:
             rows = (lin.N + 255) // 256 * 256
             sf = torch.zeros(rows, lin.K // 16, dtype=torch.uint8, device=dev)
-            sf[:lin.N] = lin.sf.to(dev).view(torch.uint8)
-            pk = {"kind": 1, "w": lin.w.to(dev).contiguous(), "sf": quant.swizzle_sf_128x4(sf),
-                  "alpha": lin.alpha.to(dev, torch.float32).contiguous()}
+            sf[:lin.N] = perm(lin.sf.to(dev).view(torch.uint8))
+            pk = {"kind": 1, "w": perm(lin.w.to(dev)).contiguous(), "sf": quant.swizzle_sf_128x4(sf),
+                  "alpha": perm(lin.alpha.to(dev, torch.float32)).contiguous()}
         elif lin.fmt in (Format.MXFP8, Format.FP8_BLOCK):
             if lin.fmt == Format.FP8_BLOCK:
                 # 128x128 fp32 block scales have no native MMA mode: re-express the weight as e4m3 with one e8m0
@@ -154,13 +171,13 @@ class CudaOps:
                 q, e8 = lin.w.to(dev), lin.sf.to(dev)
             rows = (lin.N + 255) // 256 * 256
             sf = torch.full((rows, lin.K // 32), 127, dtype=torch.uint8, device=dev)
-            sf[:lin.N] = e8.view(torch.uint8)
-            alpha = None if lin.fmt == Format.FP8_BLOCK else lin.alpha.to(dev, torch.float32).contiguous()
-            pk = {"kind": 2, "w": q.view(torch.uint8).contiguous(), "sf": quant.swizzle_sf_128x4(sf), "alpha": alpha}
+            sf[:lin.N] = perm(e8.view(torch.uint8))
+            alpha = None if lin.fmt == Format.FP8_BLOCK else perm(lin.alpha.to(dev, torch.float32)).contiguous()
+            pk = {"kind": 2, "w": perm(q.view(torch.uint8)).contiguous(), "sf": quant.swizzle_sf_128x4(sf), "alpha": alpha}
         else:  # per-channel / per-tensor FP8
-            pk = {"kind": 3, "w": lin.w.to(dev).view(torch.uint8).contiguous(), "sf": None,
-                  "alpha": lin.alpha.to(dev, torch.float32).contiguous()}
-        pk["bias"] = None if lin.bias is None else lin.bias.to(dev, torch.bfloat16).contiguous()
+            pk = {"kind": 3, "w": perm(lin.w.to(dev).view(torch.uint8)).contiguous(), "sf": None,
+                  "alpha": perm(lin.alpha.to(dev, torch.float32)).contiguous()}
+        pk["bias"] = None if lin.bias is None else perm(lin.bias.to(dev, torch.bfloat16)).contiguous()
         return pk
 
     # ------------------------------------------------------------------ activation quantisation
@@ -218,13 +235,22 @@ class CudaOps:
 
     WIDE_WS_BYTES = 40 << 20
 
+    def linear_swiglu(self, lin: Linear, x, quant_for: Optional[Linear] = None):
+        """``silu(x @ Wg^T) * (x @ Wu^T)`` for a stacked ``[gate; up]`` weight with the activation computed in the GEMM's
+        epilogue (the ``[T, 2I]`` intermediate never reaches memory); quantised for ``quant_for`` when that GEMM wants it."""
+        if lin.N % 32 or (lin.N // 2) % 8:
+            return self.silu_mul(self.linear(lin, x), quant_for=quant_for)
+        act = self.linear(lin, x, swiglu=True)
+        return self.quantize_rows(act, quant_for) if self._qmode(quant_for) else act
+
     def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0,
-               wide: Optional[bool] = None, ksplit: int = 0):
+               wide: Optional[bool] = None, ksplit: int = 0, swiglu: bool = False):
         """``wide``: None = choose; False = the 128-column kernel (needed by the fused all-reduce epilogue); True = insist on
         the wide-N kernel (raises when the shape is not covered)."""
-        pk = self.pack(lin)
+        pk = self.pack(lin, swiglu=swiglu)
         kind = pk["kind"]
         f32 = out_dtype == torch.float32
+        n_out = lin.N // 2 if swiglu else lin.N
         sfa = rs = None
         if kind in (1, 2):
             if not isinstance(x, QuantAct):
@@ -240,7 +266,7 @@ class CudaOps:
             a = x.contiguous()
             M, lda = a.shape[0], a.shape[1] * 2
         if out is None:
-            out = torch.empty(M, lin.N, dtype=torch.float32 if f32 else torch.bfloat16, device=self.device)
+            out = torch.empty(M, n_out, dtype=torch.float32 if f32 else torch.bfloat16, device=self.device)
         if M == 0:
             return out
         w = pk["w"]
@@ -261,7 +287,7 @@ class CudaOps:
             # Measured on B200 (Qwen3-8B shapes, captured-graph timing): 256-feature tiles win for block-scaled prefill GEMMs
             # (NVFP4 2048x24576x4096: 156 -> 119 us); the swapped orientation wins for the very wide bf16 head
             # (256x151936x4096: 346 -> 315 us) but not for the per-layer decode GEMMs, which stay on the 128-column kernel.
-            wide = self._wide_ok and bn == 0 and ((M <= 256 and kind == 0 and lin.N >= 32768)
+            wide = self._wide_ok and bn == 0 and ((M <= 256 and kind == 0 and lin.N >= 32768 and not swiglu)
                                                   or (kind in (1, 2) and lin.N % 256 == 0 and M > 256))
         if wide:
             swap = M <= 256
@@ -283,11 +309,11 @@ class CudaOps:
             self._check(self.lib.blz_gemm_wide(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), out.stride(0), M, lin.N, lin.K,
                                                _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
                                                int(f32), int(swap), ks, _ptr(ws), self.WIDE_WS_BYTES if ws is not None else 0,
-                                               _ptr(ctr), max_ctas, kt, self._stream()), f"gemm_wide kind {kind}")
+                                               _ptr(ctr), max_ctas, kt, int(swiglu), self._stream()), f"gemm_wide kind {kind}")
             return out
         self._check(self.lib.blz_gemm_tc(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), out.stride(0), M, lin.N, lin.K,
                                          _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
-                                         int(f32), bn, max_ctas, VP(0), 0, kt, self._stream()), f"gemm kind {kind}")
+                                         int(f32), bn, max_ctas, VP(0), 0, kt, int(swiglu), self._stream()), f"gemm kind {kind}")
         return out
 
     def silu_mul(self, gu, quant_for: Optional[Linear] = None):
@@ -463,7 +489,7 @@ class CudaOps:
         w = pk["w"]
         self._check(self.lib.blz_gemm_tc(kind, _ptr(data), lda, _ptr(w), w.shape[1] * w.element_size(), _ptr(out), out.stride(0),
                                          M_pad, pk["N"], pk["K"], _ptr(rs), _ptr(pk["alpha"]), VP(0), _ptr(sfa), _ptr(pk["sf"]),
-                                         0, 128, 0, _ptr(tile_expert), n_exp, 0, self._stream()), "grouped gemm")
+                                         0, 128, 0, _ptr(tile_expert), n_exp, 0, 0, self._stream()), "grouped gemm")
         return out
 
     def moe(self, x, topk_w, topk_id, experts):

@@ -26,6 +26,9 @@ class RefOps:
     def silu_mul(self, gu, quant_for: Optional[Linear] = None):
         return ref.silu_mul(gu)
 
+    def linear_swiglu(self, lin: Linear, x, quant_for: Optional[Linear] = None):
+        return ref.silu_mul(self.linear(lin, x))
+
     def mul_sigmoid(self, x, gate):
         return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)
 

@@ -45,6 +45,7 @@ struct GemmParams {
   const uint32_t* wait_epoch;  // the count to wait for (device word, advanced by the signalling kernel)
   int wait_world;
   long long wait_limit;
+  int act;                   // 1: B rows are [16 gate | 16 up] groups; the epilogue writes silu(gate) * up, bf16 [M, N/2]
   int b_kt;                  // > 0: B is tile-major, [N/128][b_kt][128 rows][128 bytes] (dense weights repacked at load)
   int* status;
 };
@@ -311,6 +312,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (col0 + i + 3 < p.N) dst[i + 3] = o.w;
               }
             }
+          } else if (p.act) {
+            // SwiGLU in the epilogue: columns [0,16) of the group are gate, [16,32) the matching up features
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0 / 2;
+            uint32_t pk[8];
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              float a[2];
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const float g = bf2f(__float2bfloat16(fmaf(__uint_as_float(r[i + j]) * rs, sal[c * 32 + i + j], sbi[c * 32 + i + j])));
+                const float u = bf2f(__float2bfloat16(fmaf(__uint_as_float(r[16 + i + j]) * rs, sal[c * 32 + 16 + i + j], sbi[c * 32 + 16 + i + j])));
+                a[j] = g / (1.f + __expf(-g)) * u;
+              }
+              pk[i / 2] = pack_bf16x2(a[0], a[1]);
+            }
+            if (whole) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
 #pragma unroll
@@ -451,11 +471,12 @@ BLZ_API int blz_gemm_fuse_allreduce(void* mc_out, void* done_ctr, void* const* p
 
 // kind: 0 bf16, 1 nvfp4, 2 mxfp8, 3 fp8.  A [M, K] and B [N, K] row-major (packed bytes for 4/8-bit kinds);
 // lda / ldb in BYTES.  out_f32: C is fp32, else bf16; ldc in elements.  bn: 128 or 256 (0 = choose).
+// act = 1: B's rows come in groups of [16 gate | 16 up] features and C is bf16 [M, N/2] = silu(gate) * up (ldc % 8 == 0).
 // b_kt > 0: B is the tile-major repack [ceil(N/128)][b_kt][128][128 bytes] (zero padded), b_kt = ceil(row bytes / 128).
 BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
                         int M, int N, int K, const float* row_scale, const float* alpha, const void* bias,
                         const void* sfa, const void* sfb, int out_f32, int bn, int max_ctas, const int* tile_expert,
-                        int num_experts, int b_kt, cudaStream_t stream) {
+                        int num_experts, int b_kt, int act, cudaStream_t stream) {
   using namespace blz;
   if (M <= 0 || N <= 0 || K <= 0 || kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
   const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
@@ -474,6 +495,8 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   p.status = status_word();
   p.tile_expert = tile_expert;
   p.b_kt = b_kt;
+  p.act = act;
+  if (act && (out_f32 || N % 32 || (ldc & 7) || tile_expert)) return (int)cudaErrorInvalidValue;
   if (b_kt > 0 && tile_expert) return (int)cudaErrorInvalidValue;
   p.mc_out = nullptr; p.done_ctr = nullptr; p.epoch = nullptr; p.spin_limit = 0; p.rank = 0; p.world = 1;
   p.wait_pad = g_wait.pad; p.wait_epoch = g_wait.epoch; p.wait_world = g_wait.world;

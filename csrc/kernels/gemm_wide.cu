@@ -40,6 +40,7 @@ struct WideParams {
   int ksplit;                 // CTAs sharing one output tile along K
   float* ws;                  // [tiles * ksplit][128][BN] fp32 partial tiles (ksplit > 1)
   unsigned* ctr;              // [tiles] arrival counters, zero between launches
+  int act;                    // 1 (plain orientation): columns are [16 gate | 16 up] groups; C = silu(gate) * up, bf16 [tokens, N/2]
   int w_kt;                   // > 0: the weight operand is tile-major, [rows/128][w_kt][128][128 bytes]
   int* status;
 };
@@ -355,6 +356,28 @@ __global__ void __launch_bounds__(320, 1) gemm_wide_kernel(const __grid_constant
                     dst[i + j] = fmaf(__uint_as_float(r[i + j]) * ls, s_cs[half * CPT + i + j], s_cb[half * CPT + i + j]);
               }
             }
+          } else if (p.act) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)tok * p.ldc + c0 / 2;
+#pragma unroll
+            for (int gq = 0; gq < CPT; gq += 32) {
+              uint32_t pk[8];
+#pragma unroll
+              for (int i = 0; i < 16; i += 2) {
+                float a[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  const int cg = half * CPT + gq + i + j, cu = cg + 16;
+                  const float g = bf2f(__float2bfloat16(fmaf(__uint_as_float(r[gq + i + j]) * ls, s_cs[cg], s_cb[cg])));
+                  const float u = bf2f(__float2bfloat16(fmaf(__uint_as_float(r[gq + 16 + i + j]) * ls, s_cs[cu], s_cb[cu])));
+                  a[j] = g / (1.f + __expf(-g)) * u;
+                }
+                pk[i / 2] = pack_bf16x2(a[0], a[1]);
+              }
+              if (c0 + gq + 32 <= p.cols_total) {
+                *reinterpret_cast<uint4*>(dst + gq / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(dst + gq / 2 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+              }
+            }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)tok * p.ldc + c0;
 #pragma unroll
@@ -425,7 +448,7 @@ BLZ_API int blz_gemm_wide_ksplit(int tiles, int k_tiles, int sms) {
 BLZ_API int blz_gemm_wide(int kind, const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int M,
                           int N, int K, const float* row_scale, const float* alpha, const void* bias, const void* sfx,
                           const void* sfw, int out_f32, int swap, int ksplit, void* ws, long long ws_bytes, void* ctr,
-                          int max_ctas, int w_kt, cudaStream_t stream) {
+                          int max_ctas, int w_kt, int act, cudaStream_t stream) {
   using namespace blz;
   if (M <= 0 || N <= 0 || K <= 0 || kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
   const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
@@ -447,6 +470,8 @@ BLZ_API int blz_gemm_wide(int kind, const void* X, long long ldx, const void* W,
   p.sf_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
   p.status = status_word();
   p.w_kt = w_kt;
+  p.act = act;
+  if (act && (swap || out_f32 || (ldc & 7))) return (int)cudaErrorInvalidValue;
   const void *A, *B;
   long long lda, ldb;
   if (swap) {

@@ -136,6 +136,37 @@ def test_gemm_tile_major_weights(ops, fmt, M, N, K):
         assert rel < 2e-3
 
 
+@pytest.mark.parametrize("fmt,M,I,K", [("nvfp4", 300, 512, 1024), ("nvfp4", 77, 384, 512), ("nvfp4", 256, 1024, 1024),
+                                       ("mxfp8", 600, 256, 1024), ("bf16", 90, 160, 320)])
+def test_gemm_swiglu_epilogue(ops, fmt, M, I, K):
+    """SwiGLU computed in the GEMM epilogue (interleaved gate / up rows) equals GEMM followed by the SwiGLU kernel."""
+    g = torch.Generator(device=DEV).manual_seed(23)
+    x = (torch.randn(M, K, generator=g, device=DEV)).bfloat16()
+    w = torch.randn(2 * I, K, generator=g, device=DEV) * 0.05
+    f = {"nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "bf16": Format.DENSE}[fmt]
+    lin = Linear.from_dense(w, f, segments=[I, I])
+    down = Linear.from_dense(torch.randn(64, I, generator=g, device=DEV) * 0.05, f)
+    want = ops.silu_mul(ops.linear(lin, x))
+    lin.cuda_pack = None
+    got = ops.linear_swiglu(lin, x)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert got.shape == (M, I)
+    d = (got.float() - want.float()).abs()
+    print(f"[swiglu epilogue {fmt} {M}x{I}x{K}] max diff {d.max().item():.3g} mean |ref| {want.float().abs().mean().item():.3g}")
+    assert d.max().item() <= 0.02 * max(1.0, want.float().abs().max().item())
+    assert (d > 0).float().mean().item() < 0.02
+    if fmt != "bf16":
+        qa = ops.linear_swiglu(lin, x, quant_for=down)
+        qb = ops.quantize_rows(got, down)
+        per = 16 if fmt == "nvfp4" else 32
+        sa = quant.unswizzle_sf_128x4(qa.sf, M, I // per)
+        sb = quant.unswizzle_sf_128x4(qb.sf, M, I // per)
+        assert torch.equal(qa.data, qb.data) and torch.equal(sa, sb)
+    with pytest.raises(Exception):
+        ops.linear(lin, x)          # packed for the SwiGLU epilogue: the plain GEMM must refuse it
+
+
 def test_gemm_fp8_channel(ops):
     g = torch.Generator(device=DEV).manual_seed(4)
     x = (torch.randn(192, 512, generator=g, device=DEV)).bfloat16()
