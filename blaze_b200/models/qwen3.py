@@ -8,6 +8,8 @@ expert, and MoE under tensor / expert parallelism (``model.rs:1077-1080``).
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Dict, List, Optional
 
@@ -83,6 +85,37 @@ class Layer:
         self.attn: Optional[Attn] = None
         self.gdn: Optional[Gdn] = None
         self.mlp = None
+
+
+_PROFILE_PHASES = os.environ.get("BLAZE_PROFILE_PHASES", "0") == "1"
+
+
+class _PhaseTimer:
+    """CUDA-event timers around the phases of a forward pass (collective + norm, attention / GDN mixer, MLP), summed over
+    the layers and logged as one ``model.phases`` event per step — the counterpart of the reference's ``--profile-prefill``
+    (``model.rs:2233-2252``).  Enabled by ``BLAZE_PROFILE_PHASES=1``; never active inside a graph capture."""
+
+    def __init__(self, device):
+        self.on = torch.device(device).type == "cuda"
+        self.marks = []
+
+    def mark(self, name: str) -> None:
+        if self.on:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
+
+    def finish(self, **fields) -> None:
+        if not self.on or not self.marks:
+            return
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
+        end.synchronize()
+        tot = {}
+        for (name, ev), nxt in zip(self.marks, [e for _, e in self.marks[1:]] + [end]):
+            tot[name] = tot.get(name, 0.0) + ev.elapsed_time(nxt)
+        from .. import log
+        log.event("info", "model.phases", **{k.replace("+", "_"): round(v, 3) for k, v in tot.items()}, **fields)
 
 
 class TPInfo:
@@ -408,19 +441,26 @@ class Model:
         rope = ops.rope_tables(self, batch)
         residual = None          # full rows, or this rank's row shard on the reduce+norm path
         kind = "full"            # x is: "full" rows | "partial" sums to reduce | "acc" (summed in a symmetric buffer to re-zero)
+        prof = _PhaseTimer(self.device) if _PROFILE_PHASES and not torch.cuda.is_current_stream_capturing() else None
         for li, L in enumerate(self.layers):
             gi = self.first_layer + li
             first = L.attn.qkv if L.attn is not None else L.gdn.in_proj
             if gi in self.capture_layers:
                 self.captured[gi] = self._materialise(x, residual, kind, fused, keep=True)
+            if prof: prof.mark("reduce+norm")
             h, residual = self._reduce_norm(x, residual, kind, L.input_norm, first, fused, defer=True)
+            if prof: prof.mark("mixer")
             if L.kind == "full_attention":
                 x, kind = self._attention(L.attn, h, batch, kv, gi, rope, fused)
             else:
                 x, kind = self._gdn(L.gdn, h, batch, kv, gi, fused)
             nxt = L.mlp.gate_up if isinstance(L.mlp, DenseMlp) else None
+            if prof: prof.mark("reduce+norm")
             h, residual = self._reduce_norm(x, residual, kind, L.post_norm, nxt, fused, defer=nxt is not None)
+            if prof: prof.mark("mlp")
             x, kind = self._mlp(L.mlp, h, fused)
+        if prof:
+            prof.finish(rows=int(batch.num_rows), layers=len(self.layers))
         return self._materialise(x, residual, kind, fused)
 
     def _fused(self):
