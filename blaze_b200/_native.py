@@ -117,7 +117,8 @@ def kernels() -> ctypes.CDLL:
             build()
         if not os.path.exists(KERNELS_SO):
             raise RuntimeError(f"{KERNELS_SO} is missing: run `python -c 'import __graft_entry__ as g; g.build()'`")
-        _kernels = ctypes.CDLL(KERNELS_SO)
+        # BLAZE_KERNELS_SO: load another build of the kernel library (A/B timing of kernel variants in one process set-up)
+        _kernels = ctypes.CDLL(os.environ.get("BLAZE_KERNELS_SO") or KERNELS_SO)
     return _kernels
 
 

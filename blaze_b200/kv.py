@@ -14,6 +14,8 @@ The reference keeps one-token pages and several KV dtypes (``crates/blaze/src/mo
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, List, Optional
 
 import numpy as np
@@ -29,6 +31,9 @@ def kv_bytes_per_token(cfg: ModelConfig, kv_dtype: str, tp_world: int = 1) -> in
     n_attn = sum(1 for i in range(cfg.num_layers) if cfg.layer_type(i) == "full_attention")
     kvh = max(cfg.num_kv_heads // tp_world, 1)
     return n_attn * 2 * kvh * cfg.head_dim * esz
+
+
+HEAD_MAJOR = os.environ.get("BLAZE_KV_HEAD_MAJOR", "0") == "1"
 
 
 class KVCache:
@@ -49,7 +54,13 @@ class KVCache:
         for i in self.attn_layers:
             if layout == "umma":
                 assert kv_dtype == "fp8"
-                self.kv[i] = torch.zeros(num_pages, self.kv_heads, 2, PAGE * D, dtype=torch.uint8, device=device)
+                if HEAD_MAJOR:
+                    # storage [kv_heads, pages, 2, 16*D]: the pages of one head are neighbours in memory, so a CTA that
+                    # walks a sequence's (mostly consecutive) pages for one head streams DRAM instead of hopping by
+                    # kv_heads * 4 KB; the tensor is exposed page-first like the page-major form (strides tell the kernels)
+                    self.kv[i] = torch.zeros(self.kv_heads, num_pages, 2, PAGE * D, dtype=torch.uint8, device=device).permute(1, 0, 2, 3)
+                else:
+                    self.kv[i] = torch.zeros(num_pages, self.kv_heads, 2, PAGE * D, dtype=torch.uint8, device=device)
             else:
                 self.k[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
                 self.v[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
@@ -147,6 +158,6 @@ class KVCache:
         D = self.cfg.head_dim
         buf = self.kv[layer]
         P, H = buf.shape[0], buf.shape[1]
-        kb = buf[:, :, 0].view(P, H, 2, D // 16, 8, 16).permute(0, 1, 2, 4, 3, 5).contiguous().view(P, H, 16, D)
-        vb = buf[:, :, 1].view(P, H, D, 16).transpose(2, 3).contiguous()
+        kb = buf[:, :, 0].reshape(P, H, 2, D // 16, 8, 16).permute(0, 1, 2, 4, 3, 5).contiguous().view(P, H, 16, D)
+        vb = buf[:, :, 1].reshape(P, H, D, 16).transpose(2, 3).contiguous()
         return kb.view(torch.float8_e4m3fn), vb.view(torch.float8_e4m3fn)

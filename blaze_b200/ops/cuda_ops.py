@@ -62,11 +62,12 @@ class CudaOps:
         lib.blz_rmsnorm.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_swiglu.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_attn_prep.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
-                                      _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_float, _c.c_float, VP]
+                                      _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_float, _c.c_float, _c.c_longlong,
+                                      _c.c_longlong, VP]
         lib.blz_attn_tc.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
-                                    _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
+                                    _c.c_longlong, _c.c_longlong, _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
         lib.blz_attn_decode.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
-                                        _c.c_float, _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                        _c.c_longlong, _c.c_longlong, _c.c_float, _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                         VP, VP, _c.c_int, VP, VP]
         lib.blz_mul_sigmoid.argtypes = [VP, VP, _c.c_longlong, VP]
         lib.blz_add.argtypes = [VP, VP, VP, _c.c_longlong, VP]
@@ -372,7 +373,7 @@ class CudaOps:
                                            _ptr(batch.slot_mapping), _ptr(model.inv_freq), _ptr(attn.q_norm), _ptr(attn.k_norm),
                                            T, attn.heads, attn.kv_heads, D, cfg.rotary_dim, cfg.rms_norm_eps,
                                            model.rope_scale, int(cfg.attn_output_gate), int(cfg.zero_centered_norm),
-                                           1.0, 1.0, self._stream()), "attn_prep")
+                                           1.0, 1.0, kv.kv[layer_idx].stride(0), kv.kv[layer_idx].stride(1), self._stream()), "attn_prep")
         return q, gate
 
     def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0):
@@ -404,7 +405,8 @@ class CudaOps:
                 pm = self._buf("attn_part_ml", n * 2 * 4).view(torch.float32)
             self._check(self.lib.blz_attn_decode(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
                                                  _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), B, Hq, Hkv, D,
-                                                 kv.block_table.stride(0), scale, 1.0, 1.0, nmax, rb, lo, hi, sp,
+                                                 kv.block_table.stride(0), kv.kv[layer_idx].stride(0), kv.kv[layer_idx].stride(1),
+                                                 scale, 1.0, 1.0, nmax, rb, lo, hi, sp,
                                                  _ptr(po), _ptr(pm), max_ctas, _ptr(self.attn_prof), self._stream()), "attn_decode")
             if sp > 1:
                 self.launches += 1
@@ -419,7 +421,8 @@ class CudaOps:
                 pm = self._buf("attn_part_ml2", n * 2 * 4).view(torch.float32)
             self._check(self.lib.blz_attn_tc(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
                                              _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), _ptr(batch.item_seq),
-                                             _ptr(batch.item_q0), n_items, Hq, Hkv, D, kv.block_table.stride(0), scale, 1.0,
+                                             _ptr(batch.item_q0), n_items, Hq, Hkv, D, kv.block_table.stride(0), kv.kv[layer_idx].stride(0),
+                                             kv.kv[layer_idx].stride(1), scale, 1.0,
                                              1.0, sp, _ptr(po), _ptr(pm), max_ctas, self._stream()), "attn_prefill")
             if sp > 1:
                 self.launches += 1

@@ -7,7 +7,8 @@ namespace blz {
 struct AttnParams {
   const __nv_bfloat16* q;      // [T, Hq, D]
   __nv_bfloat16* out;          // [T, Hq, D]
-  const uint8_t* pool;         // [pages, Hkv, 2, 16*D]
+  const uint8_t* pool;         // blocks of [2, 16*D] bytes (K, V^T) addressed by page * page_stride + head * head_stride
+  long long page_stride, head_stride;   // bytes; the storage may be page-major or head-major
   const int* block_table;      // [max_seqs, bt_stride]
   const int* slots;            // [B]
   const int* q_start;          // [B+1]

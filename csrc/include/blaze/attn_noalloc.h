@@ -28,10 +28,11 @@ extern "C" {
 
 #define BLZ_ATTN_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u + 512u * 1024u)
 
-// Same arguments and result as blz_attn_decode with nmax = 16, minus the scratch pointers.
+// Same arguments and result as blz_attn_decode with nmax = 16, minus the scratch pointers.  page_stride / head_stride:
+// bytes between the [2, 16*D] blocks of consecutive pages / kv heads in the pool (0 = page-major [pages, Hkv, 2, 16*D]).
 int blz_attn_decode_noalloc(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
                             const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride,
-                            float scale, float k_scale, float v_scale, int row_blocks, int min_rows, int max_rows, int splits,
+                            long long page_stride, long long head_stride, float scale, float k_scale, float v_scale, int row_blocks, int min_rows, int max_rows, int splits,
                             int max_ctas, cudaStream_t stream);
 
 // Text of the last size / set-up error of this thread ("" when the last call succeeded).

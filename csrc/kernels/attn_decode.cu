@@ -184,39 +184,47 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
         __syncwarp();
         if (lane == 0) mbar_arrive(&q_full[qb]);
       }
-      for (int i = 0; i < n; ++i) {
-        const int gi = g + i, s = gi % ST;
-        if (!TW(0, &k_empty[s], ((gi / ST) & 1) ^ 1)) break;
-        if (lane == 0) mbar_expect_tx(&k_full[s], Cfg::TILE_BYTES);
-        __syncwarp();
-        if (lane < 8) {
-          const int pidx = (t0 + i) * 8 + lane;
-          const int page = pidx < npages ? bt[pidx] : 0;          // page 0 is the all-zero scratch page
-          const uint8_t* src = p.pool + ((size_t)page * p.Hkv + kh) * (size_t)(2 * Cfg::PAGE_BYTES);
-          bulk_load(sK + s * Cfg::TILE_BYTES + lane * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &k_full[s]);
-        }
-        __syncwarp();
-      }
-    } else if (warp == 1) {
-      // -------------------------------------------------------------- V^T page loader (upper half of the warp)
-      if (lane >= 16) {
-        const int* bt = p.block_table + (size_t)slot * p.bt_stride;
-        const int npages = (kv_end + 15) >> 4;
+      // The lower half of the warp streams K tiles, the upper half V^T tiles: the two rings are released at different
+      // times (K after S^T = K Q^T, V two tiles later after O^T = V^T P^T), so each half waits only for its own ring.
+      // (the page number of the next tile is fetched before the wait for its ring slot, off the critical path)
+      if (lane < 16) {
+        int page = 0;
+        if (lane < 8 && n > 0) { const int pidx = t0 * 8 + lane; page = pidx < npages ? bt[pidx] : 0; }
         for (int i = 0; i < n; ++i) {
           const int gi = g + i, s = gi % ST;
+          int next = 0;
+          if (lane < 8 && i + 1 < n) { const int pidx = (t0 + i + 1) * 8 + lane; next = pidx < npages ? bt[pidx] : 0; }
+          if (!TW(0, &k_empty[s], ((gi / ST) & 1) ^ 1)) break;
+          if (lane == 0) mbar_expect_tx(&k_full[s], Cfg::TILE_BYTES);
+          __syncwarp(0x0000FFFFu);
+          if (lane < 8) {
+            const uint8_t* src = p.pool + (size_t)page * p.page_stride + (size_t)kh * p.head_stride;   // page 0 = zero scratch page
+            bulk_load(sK + s * Cfg::TILE_BYTES + lane * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &k_full[s]);
+          }
+          __syncwarp(0x0000FFFFu);
+          page = next;
+        }
+      } else {
+        int page = 0;
+        if (lane < 24 && n > 0) { const int pidx = t0 * 8 + lane - 16; page = pidx < npages ? bt[pidx] : 0; }
+        for (int i = 0; i < n; ++i) {
+          const int gi = g + i, s = gi % ST;
+          int next = 0;
+          if (lane < 24 && i + 1 < n) { const int pidx = (t0 + i + 1) * 8 + lane - 16; next = pidx < npages ? bt[pidx] : 0; }
           if (!mbar_wait(&v_empty[s], ((gi / ST) & 1) ^ 1, abort_flag, p.status)) break;
           if (lane == 16) mbar_expect_tx(&v_full[s], Cfg::TILE_BYTES);
           __syncwarp(0xFFFF0000u);
           if (lane < 24) {
             const int pg = lane - 16;
-            const int pidx = (t0 + i) * 8 + pg;
-            const int page = pidx < npages ? bt[pidx] : 0;
-            const uint8_t* src = p.pool + ((size_t)page * p.Hkv + kh) * (size_t)(2 * Cfg::PAGE_BYTES) + Cfg::PAGE_BYTES;
+            const uint8_t* src = p.pool + (size_t)page * p.page_stride + (size_t)kh * p.head_stride + Cfg::PAGE_BYTES;
             bulk_load(sV + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &v_full[s]);
           }
           __syncwarp(0xFFFF0000u);
+          page = next;
         }
       }
+      __syncwarp();
+    } else if (warp == 1) {
       // -------------------------------------------------------------- MMA issuer
       if (lane == 0 && n > 0) {
         bool ok = TW(6, &q_full[item_it & 1], (item_it >> 1) & 1);
@@ -458,7 +466,7 @@ static cudaError_t launch_decode(const AttnParams& p, int max_ctas, cudaStream_t
 // nmax: 16 or 32 rows per work item; row_blocks = ceil(max rows of any processed sequence / nmax).
 // Scratch for splits > 1: part_o = B*Hkv*row_blocks*splits*nmax*128 floats, part_ml = ...*nmax*2 floats.
 BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
-                            const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride,
+                            const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride, long long page_stride, long long head_stride,
                             float scale, float k_scale, float v_scale, int nmax, int row_blocks, int min_rows,
                             int max_rows, int splits, float* part_o, float* part_ml, int max_ctas, long long* prof,
                             cudaStream_t stream) {
@@ -469,6 +477,8 @@ BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const in
     return (int)cudaErrorInvalidValue;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
+  p.page_stride = page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D;
+  p.head_stride = head_stride > 0 ? head_stride : (long long)2 * 16 * D;
   p.block_table = block_table; p.slots = slots; p.q_start = q_start; p.ctx_len = ctx_len;
   p.item_seq = nullptr; p.item_q0 = nullptr; p.part_o = part_o; p.part_ml = part_ml;
   p.num_items = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.bt_stride = bt_stride; p.splits = splits;
@@ -513,7 +523,7 @@ extern "C" __attribute__((visibility("default"))) long long blz_attn_decode_noal
 
 extern "C" __attribute__((visibility("default"))) int blz_attn_decode_noalloc(
     const void* q, void* out, const void* pool, const int* block_table, const int* slots, const int* q_start, const int* ctx_len,
-    int num_seqs, int Hq, int Hkv, int D, int bt_stride, float scale, float k_scale, float v_scale, int row_blocks, int min_rows,
+    int num_seqs, int Hq, int Hkv, int D, int bt_stride, long long page_stride, long long head_stride, float scale, float k_scale, float v_scale, int row_blocks, int min_rows,
     int max_rows, int splits, int max_ctas, cudaStream_t stream) {
   using namespace blz;
   g_noalloc_err[0] = 0;
@@ -555,6 +565,8 @@ extern "C" __attribute__((visibility("default"))) int blz_attn_decode_noalloc(
   }
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
+  p.page_stride = page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D;
+  p.head_stride = head_stride > 0 ? head_stride : (long long)2 * 16 * D;
   p.block_table = block_table; p.slots = slots; p.q_start = q_start; p.ctx_len = ctx_len;
   p.item_seq = nullptr; p.item_q0 = nullptr;
   const long long work = (long long)num_seqs * Hkv * row_blocks * splits;

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
           const int pg = lane & 7;
           const int pidx = (t0 + i) * 8 + pg;
           const int page = pidx < npages ? bt[pidx] : 0;          // page 0 is the all-zero scratch page
-          const uint8_t* src = p.pool + ((size_t)page * p.Hkv + kh) * (size_t)(2 * Cfg::PAGE_BYTES);
+          const uint8_t* src = p.pool + (size_t)page * p.page_stride + (size_t)kh * p.head_stride;
           if (lane < 8) bulk_load(sK + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src, Cfg::PAGE_BYTES, &k_full[s]);
           else bulk_load(sV + s * Cfg::TILE_BYTES + pg * Cfg::PAGE_BYTES, src + Cfg::PAGE_BYTES, Cfg::PAGE_BYTES, &v_full[s]);
         }
@@ -369,14 +369,16 @@ __global__ void attn_combine_kernel(AttnParams p) {
 // Scratch needed for `splits` > 1: part_o = items*Hkv*splits*128*D floats, part_ml = items*Hkv*splits*128*2 floats.
 BLZ_API int blz_attn_tc(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
                         const int* q_start, const int* ctx_len, const int* item_seq, const int* item_q0, int num_items,
-                        int Hq, int Hkv, int D, int bt_stride, float scale, float k_scale, float v_scale, int splits,
-                        float* part_o, float* part_ml, int max_ctas, cudaStream_t stream) {
+                        int Hq, int Hkv, int D, int bt_stride, long long page_stride, long long head_stride, float scale, float k_scale,
+                        float v_scale, int splits, float* part_o, float* part_ml, int max_ctas, cudaStream_t stream) {
   using namespace blz;
   if (num_items <= 0) return 0;
   if (D != 128 || Hq % Hkv || 128 % (Hq / Hkv) || splits < 1 || (splits > 1 && (!part_o || !part_ml)))
     return (int)cudaErrorInvalidValue;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
+  p.page_stride = page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D;
+  p.head_stride = head_stride > 0 ? head_stride : (long long)2 * 16 * D;
   p.block_table = block_table; p.slots = slots; p.q_start = q_start; p.ctx_len = ctx_len;
   p.item_seq = item_seq; p.item_q0 = item_q0; p.part_o = part_o; p.part_ml = part_ml;
   p.num_items = num_items; p.Hq = Hq; p.Hkv = Hkv; p.bt_stride = bt_stride; p.splits = splits;

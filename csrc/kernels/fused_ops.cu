@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const __nv_bfloat16* __r
                                  const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
                                  const __nv_bfloat16* __restrict__ k_norm_w, int T, int Hq, int Hkv, int rot_dim,
                                  float eps, float rope_scale, int gated, int zero_centered, float k_scale_inv,
-                                 float v_scale_inv) {
+                                 float v_scale_inv, long long page_stride, long long head_stride) {
   pdl_trigger();
   pdl_wait();
   constexpr int VPL = D / 32;
@@ -497,7 +497,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const __nv_bfloat16* __r
     }
     const int page = slot >> 4, tp = slot & 15;
     const int kh = kind == 1 ? h - Hq : h - Hq - Hkv;
-    uint8_t* blk = kv_pool + ((size_t)page * Hkv + kh) * (size_t)(2 * 16 * D);
+    uint8_t* blk = kv_pool + (size_t)page * page_stride + (size_t)kh * head_stride;
     if (kind == 1) {
       // the lane's VPL dims are consecutive bytes of one 16-byte core-matrix row
       __align__(8) uint8_t b[VPL];
@@ -681,7 +681,8 @@ BLZ_API int blz_swiglu(const void* gu, void* out, void* q_out, void* sf_out, flo
 BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv_pool, const int* positions,
                           const int* slot_mapping, const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
                           int T, int Hq, int Hkv, int D, int rot_dim, float eps, float rope_scale, int gated,
-                          int zero_centered, float k_scale, float v_scale, cudaStream_t s) {
+                          int zero_centered, float k_scale, float v_scale, long long page_stride, long long head_stride,
+                          cudaStream_t s) {
   if (T == 0) return 0;
   const int half = rot_dim / 2, vpl = D / 32;
   if ((D != 64 && D != 128 && D != 256) || rot_dim > D || half % vpl || ((half / vpl) & (half / vpl - 1)) || half / vpl > 16)
@@ -691,7 +692,8 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
 #define BLZ_PREP(DD)                                                                                                 \
   launch_pdl(attn_prep_kernel<DD>, dim3(grid), dim3(wpb * 32), 0, s, (const bf16*)qkv, (bf16*)q_out, (bf16*)gate_out,  \
              (uint8_t*)kv_pool, positions, slot_mapping, inv_freq, (const bf16*)q_norm_w, (const bf16*)k_norm_w, T, Hq, \
-             Hkv, rot_dim, eps, rope_scale, gated, zero_centered, 1.f / k_scale, 1.f / v_scale)
+             Hkv, rot_dim, eps, rope_scale, gated, zero_centered, 1.f / k_scale, 1.f / v_scale,                         \
+             page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D, head_stride > 0 ? head_stride : (long long)2 * 16 * D)
   if (D == 64) BLZ_PREP(64); else if (D == 128) BLZ_PREP(128); else BLZ_PREP(256);
 #undef BLZ_PREP
   return (int)cudaGetLastError();

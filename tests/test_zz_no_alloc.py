@@ -26,14 +26,16 @@ def test_noalloc_matches_regular_entry_point_twice():
     lib = kernels()
     fn = lib.blz_attn_decode_noalloc
     fn.restype = ctypes.c_int
-    fn.argtypes = [VP, VP, VP, VP, VP, VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+    fn.argtypes = [VP, VP, VP, VP, VP, VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                   ctypes.c_longlong, ctypes.c_longlong, ctypes.c_float,
                    ctypes.c_float, ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, VP]
     lib.blz_attn_decode_noalloc_error.restype = ctypes.c_char_p
     lib.blz_attn_decode_noalloc_bytes.restype = ctypes.c_longlong
     lib.blz_attn_decode_noalloc_bytes.argtypes = [ctypes.c_int] * 4
     ref = lib.blz_attn_decode
     ref.restype = ctypes.c_int
-    ref.argtypes = [VP, VP, VP, VP, VP, VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+    ref.argtypes = [VP, VP, VP, VP, VP, VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                    ctypes.c_longlong, ctypes.c_longlong, ctypes.c_float,
                     ctypes.c_float, ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, VP, VP,
                     ctypes.c_int, VP, VP]
     dev = "cuda"
@@ -61,11 +63,11 @@ def test_noalloc_matches_regular_entry_point_twice():
         po = torch.empty(n * D, dtype=torch.float32, device=dev)
         pm = torch.empty(n * 2, dtype=torch.float32, device=dev)
         rc = ref(_p(q), _p(want), _p(kv.kv[0]), _p(kv.block_table), _p(batch.slots), _p(batch.q_start), _p(batch.ctx_len), B, Hq, Hkv, D,
-                 kv.block_table.stride(0), scale, 1.0, 1.0, 16, 1, 1, group, splits, _p(po), _p(pm), 0, VP(0), stream)
+                 kv.block_table.stride(0), kv.kv[0].stride(0), kv.kv[0].stride(1), scale, 1.0, 1.0, 16, 1, 1, group, splits, _p(po), _p(pm), 0, VP(0), stream)
         assert rc == 0
         got = torch.zeros_like(want)
         rc = fn(_p(q), _p(got), _p(kv.kv[0]), _p(kv.block_table), _p(batch.slots), _p(batch.q_start), _p(batch.ctx_len), B, Hq, Hkv, D,
-                kv.block_table.stride(0), scale, 1.0, 1.0, 1, 1, group, splits, 0, stream)
+                kv.block_table.stride(0), kv.kv[0].stride(0), kv.kv[0].stride(1), scale, 1.0, 1.0, 1, 1, group, splits, 0, stream)
         assert rc == 0, lib.blz_attn_decode_noalloc_error().decode()
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
@@ -73,5 +75,5 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert err <= 0.02 * want.float().abs().max().item() + 1e-3, f"call {call}: max abs err {err}"
     # a problem whose partials cannot fit the built-in array is refused with a message, not attempted
     rc = fn(_p(q), _p(got), _p(kv.kv[0]), _p(kv.block_table), _p(batch.slots), _p(batch.q_start), _p(batch.ctx_len), 4096, Hq, Hkv, D,
-            kv.block_table.stride(0), scale, 1.0, 1.0, 1, 1, group, 8, 0, stream)
+            kv.block_table.stride(0), kv.kv[0].stride(0), kv.kv[0].stride(1), scale, 1.0, 1.0, 1, 1, group, 8, 0, stream)
     assert rc != 0 and b"exceeds the built-in" in lib.blz_attn_decode_noalloc_error()
