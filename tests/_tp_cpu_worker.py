@@ -1,0 +1,91 @@
+"""Worker for test_tp_cpu.py: two gloo ranks on the CPU (run under torch.distributed.run)."""
+import datetime
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from blaze_b200.config import named_config  # noqa: E402
+from blaze_b200.llm import LLM  # noqa: E402
+from blaze_b200.models.qwen3 import TPInfo  # noqa: E402
+from blaze_b200.parallel.tp import TPGroup  # noqa: E402
+from blaze_b200.parallel.worker import Leader, follow  # noqa: E402
+from blaze_b200.sampler import SamplingParams  # noqa: E402
+
+
+def build(tp, **kw):
+    cfg = named_config("tiny")
+    base = dict(device="cpu", dtype=torch.float32, max_seqs=8, max_model_len=256, use_graphs=False, seed=0, tp=tp)
+    base.update(kw)
+    return LLM(cfg, **base)
+
+
+def main():
+    case = sys.argv[1]
+    timeout = datetime.timedelta(seconds=20 if case == "rank_leaves" else 120)
+    dist.init_process_group("gloo", rank=int(os.environ["RANK"]), world_size=int(os.environ["WORLD_SIZE"]), timeout=timeout)
+    group = TPGroup.from_env("cpu")
+    rank, world = group.rank, group.world
+    prompts = torch.randint(0, 1024, (4, 21), generator=torch.Generator().manual_seed(3)).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=10)
+
+    if case == "generate":
+        # the same requests through one process and through two tensor-parallel ranks (rank 0 plans, rank 1 follows)
+        solo = [o.token_ids for o in build(TPInfo()).generate(prompts, sp)] if rank == 0 else None
+        llm = build(TPInfo(rank, world, group), chunk=16)
+        if rank == 0:
+            lead = Leader(llm.engine, group)
+            got = [o.token_ids for o in llm.generate(prompts, sp)]
+            lead.quit()
+            same = sum(a == b for a, b in zip(sum(solo, []), sum(got, [])))
+            total = len(sum(solo, []))
+            print(f"[tp-cpu] tokens equal to the single-process run: {same}/{total}", flush=True)
+            assert same >= 0.9 * total
+            assert all(len(g) == 10 for g in got)
+        else:
+            assert follow(llm) == 0
+    elif case == "rank_leaves":
+        # rank 1 leaves between two steps; rank 0's next step must end with an error inside the group timeout, fail the
+        # requests of that step and leave the scheduler able to answer again (here: with an error, since the group is gone)
+        llm = build(TPInfo(rank, world, group))
+        if rank == 0:
+            Leader(llm.engine, group)
+            finished = []
+            from blaze_b200.sched import GenRequest
+            llm.sched.submit(GenRequest("r0", prompts[0], SamplingParams(temperature=0.0, max_tokens=50),
+                                        sink=lambda ev: finished.append(ev) if ev.finish is not None else None))
+            llm.sched.start()
+            import time
+            t0 = time.monotonic()
+            while not finished and time.monotonic() - t0 < 60:
+                time.sleep(0.05)
+            llm.sched.stop()
+            assert finished, "the request never finished after the peer left"
+            assert finished[0].finish.value == "error" and finished[0].error
+            print(f"[tp-cpu] peer left: request failed after {time.monotonic() - t0:.1f}s with {finished[0].error[:60]!r}", flush=True)
+            os._exit(0)
+        else:
+            # follow three steps, then leave with nothing in flight
+            eng = llm.engine
+            from blaze_b200.batch import SeqChunk
+            from blaze_b200.engine import Seq
+            for _ in range(3):
+                msg = group.broadcast_object(None, 0)
+                _, mode, raw, changed, gone, feedback = msg
+                for row, pg in changed.items():
+                    s = eng.seqs.setdefault(row, Seq(row=row))
+                    eng.kv.set_pages(row, pg[len(s.pages):], len(s.pages))
+                    s.pages = list(pg)
+                eng.forward([SeqChunk(a, b, c, d) for a, b, c, d in raw], mode, feedback=feedback)
+            os._exit(0)
+    else:
+        raise SystemExit(f"unknown case {case}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
