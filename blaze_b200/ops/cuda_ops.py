@@ -120,7 +120,14 @@ class CudaOps:
             pad[:N, :KB] = b
             b = pad
         kt = KP // 128
-        return b.view(NP // 128, 128, kt, 128).permute(0, 2, 1, 3).contiguous(), kt
+        t = b.view(NP // 128, 128, kt, 128).permute(0, 2, 1, 3).contiguous()
+        # store each tile as the 128-byte-swizzled shared-memory image the tensor core reads (16-byte chunk c of row r
+        # sits at chunk c ^ (r % 8)), so that the kernel fetches a whole 16 KB tile with ONE bulk copy
+        v = t.view(NP // 128, kt, 16, 8, 8, 16)
+        r = torch.arange(8, device=b.device).view(8, 1)
+        c = torch.arange(8, device=b.device).view(1, 8)
+        src = (c ^ r).view(1, 1, 1, 8, 8, 1).expand(NP // 128, kt, 16, 8, 8, 16)
+        return torch.gather(v, 4, src).contiguous().view(NP // 128, kt, 128, 128), kt
 
     @staticmethod
     def swiglu_order(n_rows: int) -> torch.Tensor:

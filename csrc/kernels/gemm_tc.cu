@@ -46,7 +46,8 @@ struct GemmParams {
   int wait_world;
   long long wait_limit;
   int act;                   // 1: B rows are [16 gate | 16 up] groups; the epilogue writes silu(gate) * up, bf16 [M, N/2]
-  int b_kt;                  // > 0: B is tile-major, [N/128][b_kt][128 rows][128 bytes] (dense weights repacked at load)
+  int b_kt;                  // > 0: B is tile-major, [N/128][b_kt][16 KB shared-memory image of a 128-row x 128-byte tile]
+  const uint8_t* b_raw;      // base of B for the tile-major form (fetched with plain bulk copies, one per tile)
   int* status;
 };
 
@@ -130,10 +131,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_expect_tx(&full[s], bytes);
         const int brow = ex * p.N + nt * BN;                  // first B row of this tile
         if (p.b_kt > 0) {
-          // tile-major weights: every 128-row x 128-byte tile is one contiguous 16 KB run of DRAM
+          // tile-major weights: every 128-row x 128-byte tile is stored as its swizzled shared-memory image, one
+          // contiguous 16 KB run that a single bulk copy brings in
 #pragma unroll
           for (int h = 0; h < BN / 128; ++h)
-            tma_load_2d(sB + s * Cfg::B_BYTES + h * 16384, &tmB, 0, ((nt * (BN / 128) + h) * p.b_kt + kt) * 128, &full[s]);
+            bulk_load(sB + s * Cfg::B_BYTES + h * 16384,
+                      p.b_raw + ((size_t)(nt * (BN / 128) + h) * p.b_kt + kt) * 16384, 16384, &full[s]);
         } else {
           tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, brow, &full[s]);
         }
@@ -495,6 +498,7 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   p.status = status_word();
   p.tile_expert = tile_expert;
   p.b_kt = b_kt;
+  p.b_raw = reinterpret_cast<const uint8_t*>(B);
   p.act = act;
   if (act && (out_f32 || N % 32 || (ldc & 7) || tile_expert)) return (int)cudaErrorInvalidValue;
   if (b_kt > 0 && tile_expert) return (int)cudaErrorInvalidValue;

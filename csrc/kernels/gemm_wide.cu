@@ -41,7 +41,8 @@ struct WideParams {
   float* ws;                  // [tiles * ksplit][128][BN] fp32 partial tiles (ksplit > 1)
   unsigned* ctr;              // [tiles] arrival counters, zero between launches
   int act;                    // 1 (plain orientation): columns are [16 gate | 16 up] groups; C = silu(gate) * up, bf16 [tokens, N/2]
-  int w_kt;                   // > 0: the weight operand is tile-major, [rows/128][w_kt][128][128 bytes]
+  int w_kt;                   // > 0: the weight operand is tile-major, [rows/128][w_kt][16 KB swizzled tile image]
+  const uint8_t* w_raw;       // its base (fetched with plain bulk copies)
   int* status;
 };
 
@@ -150,14 +151,15 @@ __global__ void __launch_bounds__(320, 1) gemm_wide_kernel(const __grid_constant
           mbar_expect_tx(&full[s], bytes);
           const int kc = (KIND == 0) ? kt * BK : kt * 128;
           if (p.w_kt > 0 && SWAP) {
-            tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, 0, (lt * p.w_kt + kt) * 128, &full[s]);
+            bulk_load(sA + s * Cfg::A_BYTES, p.w_raw + ((size_t)lt * p.w_kt + kt) * 16384, 16384, &full[s]);
           } else {
             tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, kc, lt * 128, &full[s]);
           }
           if (p.w_kt > 0 && !SWAP) {
 #pragma unroll
             for (int h = 0; h < Cfg::NB; ++h)
-              tma_load_2d(sB + s * Cfg::B_BYTES + h * 16384, &tmB, 0, ((ct * Cfg::NB + h) * p.w_kt + kt) * 128, &full[s]);
+              bulk_load(sB + s * Cfg::B_BYTES + h * 16384, p.w_raw + ((size_t)(ct * Cfg::NB + h) * p.w_kt + kt) * 16384, 16384,
+                        &full[s]);
           } else {
             tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, kc, ct * BN, &full[s]);
           }
@@ -470,6 +472,7 @@ BLZ_API int blz_gemm_wide(int kind, const void* X, long long ldx, const void* W,
   p.sf_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
   p.status = status_word();
   p.w_kt = w_kt;
+  p.w_raw = reinterpret_cast<const uint8_t*>(W);
   p.act = act;
   if (act && (swap || out_f32 || (ldc & 7))) return (int)cudaErrorInvalidValue;
   const void *A, *B;
