@@ -88,6 +88,7 @@ class Layer:
 
 
 _PROFILE_PHASES = os.environ.get("BLAZE_PROFILE_PHASES", "0") == "1"
+_FUSED_HEAD = os.environ.get("BLAZE_FUSED_HEAD", "1") != "0"
 
 
 class _PhaseTimer:
@@ -590,8 +591,15 @@ class Model:
         """Greedy token per row; under TP each rank reduces its shard and (value, index) pairs are merged
         (``model.rs:2669`` ``greedy_sharded``)."""
         h = self.final_hidden(x, rows)
+        tp = self.tp.world > 1 and self.tp.group is not None
+        if self.ops.is_cuda and _FUSED_HEAD:
+            # the logits never reach memory: the head GEMM's epilogue keeps each tile's best column
+            if tp:
+                idx, val = self.ops.linear_argmax(self.lm_head, h, index_offset=self.tp.rank * self.lm_head.N, want_values=True)
+                return self.tp.group.merge_pairs(idx, val)
+            return self.ops.linear_argmax(self.lm_head, h)
         logits = self.ops.linear(self.lm_head, h, out_dtype=torch.float32)
-        if self.tp.world > 1 and self.tp.group is not None:
+        if tp:
             return self.tp.group.argmax_sharded(self.ops, logits, self.lm_head.N)
         return self.ops.argmax(logits)
 

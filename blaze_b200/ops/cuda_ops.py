@@ -48,6 +48,8 @@ class CudaOps:
                                     _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_gemm_wait_flags.restype = _c.c_int
         lib.blz_gemm_wait_flags.argtypes = [VP, VP, _c.c_int, _c.c_int]
+        lib.blz_gemm_argmax_parts.argtypes = [VP, VP]
+        lib.blz_argmax_parts.argtypes = [VP, VP, _c.c_int, _c.c_int, VP, VP, _c.c_int, VP]
         lib.blz_gemm_wide.restype = _c.c_int
         lib.blz_gemm_wide.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
                                       _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_longlong, VP,
@@ -251,8 +253,24 @@ class CudaOps:
         act = self.linear(lin, x, swiglu=True)
         return self.quantize_rows(act, quant_for) if self._qmode(quant_for) else act
 
+    def linear_argmax(self, lin: Linear, x, index_offset: int = 0, want_values: bool = False):
+        """``argmax(x @ W^T)`` per row without writing the logits: the GEMM epilogue keeps the best (value, column) of each
+        128-column tile and a small kernel merges the tiles (ties to the lower column, like ``argmax``)."""
+        M = x.rows if isinstance(x, QuantAct) else x.shape[0]
+        tiles = (lin.N + 127) // 128
+        val = self._buf("amax_val", tiles * max(M, 1) * 4).view(torch.float32)
+        idx = self._buf("amax_idx", tiles * max(M, 1) * 4).view(torch.int32)
+        out = torch.empty(M, dtype=torch.int64, device=self.device)
+        vals = torch.empty(M, dtype=torch.float32, device=self.device) if want_values else None
+        if M == 0:
+            return (out, vals) if want_values else out
+        self.linear(lin, x, out_dtype=torch.float32, wide=False, argmax_parts=(val, idx))
+        self._check(self.lib.blz_argmax_parts(_ptr(val), _ptr(idx), tiles, M, _ptr(out), _ptr(vals), index_offset,
+                                              self._stream()), "argmax_parts")
+        return (out, vals) if want_values else out
+
     def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0,
-               wide: Optional[bool] = None, ksplit: int = 0, swiglu: bool = False):
+               wide: Optional[bool] = None, ksplit: int = 0, swiglu: bool = False, argmax_parts=None):
         """``wide``: None = choose; False = the 128-column kernel (needed by the fused all-reduce epilogue); True = insist on
         the wide-N kernel (raises when the shape is not covered)."""
         pk = self.pack(lin, swiglu=swiglu)
@@ -273,8 +291,13 @@ class CudaOps:
         else:
             a = x.contiguous()
             M, lda = a.shape[0], a.shape[1] * 2
-        if out is None:
+        if argmax_parts is not None:
+            out = argmax_parts[0]            # the logits are not written; any valid pointer will do
+            ld_out = n_out
+        elif out is None:
             out = torch.empty(M, n_out, dtype=torch.float32 if f32 else torch.bfloat16, device=self.device)
+        if argmax_parts is None:
+            ld_out = out.stride(0)
         if M == 0:
             return out
         w = pk["w"]
@@ -319,7 +342,11 @@ class CudaOps:
                                                int(f32), int(swap), ks, _ptr(ws), self.WIDE_WS_BYTES if ws is not None else 0,
                                                _ptr(ctr), max_ctas, kt, int(swiglu), self._stream()), f"gemm_wide kind {kind}")
             return out
-        self._check(self.lib.blz_gemm_tc(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), out.stride(0), M, lin.N, lin.K,
+        if argmax_parts is not None:
+            rc = self.lib.blz_gemm_argmax_parts(_ptr(argmax_parts[0]), _ptr(argmax_parts[1]))
+            if rc != 0:
+                raise CudaError(f"blz_gemm_argmax_parts failed: {rc}")
+        self._check(self.lib.blz_gemm_tc(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), ld_out, M, lin.N, lin.K,
                                          _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
                                          int(f32), bn, max_ctas, VP(0), 0, kt, int(swiglu), self._stream()), f"gemm kind {kind}")
         return out

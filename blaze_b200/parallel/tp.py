@@ -73,6 +73,10 @@ class TPGroup:
             m = logits == val.unsqueeze(1)
             ar = torch.arange(logits.shape[1], device=logits.device).expand_as(logits)
             idx = torch.where(m, ar, torch.full_like(ar, logits.shape[1])).min(1).values + off
+        return self.merge_pairs(idx, val)
+
+    def merge_pairs(self, idx: torch.Tensor, val: torch.Tensor) -> torch.Tensor:
+        """Merge every rank's per-row (global index, value) winner: largest value, lowest index among equals."""
         pair = torch.stack([val.double(), idx.double()], dim=1).contiguous()
         parts = [torch.empty_like(pair) for _ in range(self.world)]
         dist.all_gather(parts, pair, group=self.pg)

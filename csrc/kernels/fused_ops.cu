@@ -581,6 +581,33 @@ __global__ void argmax_kernel(const float* __restrict__ logits, long long* __res
   }
 }
 
+// Reduce the per-tile (value, column) pairs of the greedy head: one warp per row, ties to the lower column.
+__global__ void argmax_parts_kernel(const float* __restrict__ val, const int* __restrict__ idx, int tiles, int M,
+                                    long long* __restrict__ out, float* __restrict__ out_val, int index_offset) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int t = lane; t < tiles; t += 32) {
+    const float v = val[(size_t)t * M + row];
+    const int i = idx[(size_t)t * M + row];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) {
+    out[row] = (long long)bi + index_offset;
+    if (out_val) out_val[row] = bv;
+  }
+}
+
 }  // namespace blz
 
 using namespace blz;
@@ -725,4 +752,10 @@ BLZ_API int blz_argmax(const float* logits, long long* out, float* out_val, int 
   if (R == 0) return 0;
   launch_pdl(argmax_kernel, dim3(R), dim3(1024), 0, s, logits, out, out_val, V, ld, index_offset);
   return (int)cudaGetLastError();
+}
+
+BLZ_API int blz_argmax_parts(const float* val, const int* idx, int tiles, int M, long long* out, float* out_val, int index_offset,
+                             cudaStream_t s) {
+  if (M <= 0 || tiles <= 0) return 0;
+  return (int)launch_pdl(argmax_parts_kernel, dim3((M + 7) / 8), dim3(256), 0, s, val, idx, tiles, M, out, out_val, index_offset);
 }

@@ -45,6 +45,8 @@ struct GemmParams {
   const uint32_t* wait_epoch;  // the count to wait for (device word, advanced by the signalling kernel)
   int wait_world;
   long long wait_limit;
+  float* amax_val;           // arg-max epilogue (fp32 instantiation): per (N tile, row) best value ...
+  int* amax_idx;             // ... and its column; C is not written.  Layout [N tiles][M].
   int act;                   // 1: B rows are [16 gate | 16 up] groups; the epilogue writes silu(gate) * up, bf16 [M, N/2]
   int b_kt;                  // > 0: B is tile-major, [N/128][b_kt][16 KB shared-memory image of a 128-row x 128-byte tile]
   const uint8_t* b_raw;      // base of B for the tile-major form (fetched with plain bulk copies, one per tile)
@@ -286,12 +288,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         sbi[i] = (p.bias && col < p.N) ? bf2f(p.bias[(size_t)ex * p.N + col]) : 0.0f;
       }
       __syncwarp();
+      float best_v = -INFINITY;
+      int best_i = 0x7fffffff;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem + ab * BN + c * 32 + ((uint32_t)(q * 32) << 16), r);
         tmem_ld_wait();
         const int col0 = nt * BN + c * 32;
+        if (OUT_F32 && p.amax_val != nullptr) {
+          // greedy head: keep the largest logit of this row within the tile (first maximum = lowest column)
+          if (row < p.M && col0 < p.N) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = fmaf(__uint_as_float(r[i]) * rs, sal[c * 32 + i], sbi[c * 32 + i]);
+              if (col0 + i < p.N && v > best_v) { best_v = v; best_i = col0 + i; }
+            }
+          }
+          continue;
+        }
         if (row < p.M && col0 < p.N) {
           // vector stores need the whole 32-column group inside N and rows that start on a 16-byte boundary
           const bool whole = col0 + 32 <= p.N && (p.ldc & (OUT_F32 ? 3 : 7)) == 0;
@@ -371,6 +386,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
+      if (OUT_F32 && p.amax_val != nullptr && row < p.M) {
+        p.amax_val[(size_t)nt * p.M + row] = best_v;
+        p.amax_idx[(size_t)nt * p.M + row] = best_i;
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[ab]);
@@ -442,7 +461,22 @@ struct WaitArgs {
   long long limit = 0;
 };
 thread_local WaitArgs g_wait;
+struct AmaxArgs {
+  float* val = nullptr;
+  int* idx = nullptr;
+};
+thread_local AmaxArgs g_amax;
 }  // namespace
+
+// Arms the NEXT blz_gemm_tc call (fp32 output form, bn 128) on this thread as a greedy head: instead of writing the
+// logits it records, per 128-column tile and row, the largest value and its column in val / idx ([ceil(N/128)][M]);
+// blz_argmax_parts then reduces over the tiles.
+BLZ_API int blz_gemm_argmax_parts(void* val, void* idx) {
+  if (!val || !idx) return (int)cudaErrorInvalidValue;
+  g_amax.val = reinterpret_cast<float*>(val);
+  g_amax.idx = reinterpret_cast<int*>(idx);
+  return 0;
+}
 
 // Arms the NEXT blz_gemm_tc call on this thread to wait, inside its producer warp and after it has sent its first weight
 // tiles, for the A operand: arrival counter r of `counters` (uint32 per source rank, in this GPU's memory) must reach the
@@ -506,6 +540,10 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   p.wait_pad = g_wait.pad; p.wait_epoch = g_wait.epoch; p.wait_world = g_wait.world;
   p.wait_limit = g_wait.limit;
   g_wait.pad = nullptr;           // one-shot
+  p.amax_val = g_amax.val; p.amax_idx = g_amax.idx;
+  g_amax.val = nullptr; g_amax.idx = nullptr;
+  if (p.amax_val && (!out_f32 || tile_expert)) return (int)cudaErrorInvalidValue;
+  if (p.amax_val) bn = 128;
   if (g_fuse.mc_out) {
     if (out_f32 || (N % 32)) return (int)cudaErrorInvalidValue;
     p.mc_out = g_fuse.mc_out; p.done_ctr = g_fuse.done_ctr; p.epoch = g_fuse.epoch; p.spin_limit = g_fuse.spin_limit;

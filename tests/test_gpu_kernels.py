@@ -437,3 +437,19 @@ def test_host_kv_tier_roundtrip_on_device():
         assert torch.equal(kv.kv[i][dst], want[i])
     tier.drop(run)
     assert tier.free_pages == 32 and tier.free == [(0, 32)]
+
+
+@pytest.mark.parametrize("fmt,M,N,K", [("bf16", 256, 5000, 512), ("bf16", 3, 1000, 256), ("nvfp4", 130, 2048, 1024)])
+def test_head_argmax_in_the_gemm_epilogue(ops, fmt, M, N, K):
+    g = torch.Generator(device=DEV).manual_seed(24)
+    x = (torch.randn(M, K, generator=g, device=DEV)).bfloat16()
+    w = torch.randn(N, K, generator=g, device=DEV) * 0.05
+    w[7] = w[3]                                     # an exact tie between two columns: the lower one must win
+    lin = Linear.from_dense(w, {"bf16": Format.DENSE, "nvfp4": Format.NVFP4}[fmt])
+    logits = ops.linear(lin, x, out_dtype=torch.float32, wide=False)
+    want_i, want_v = ops.argmax(logits, index_offset=11, want_values=True)
+    got_i, got_v = ops.linear_argmax(lin, x, index_offset=11, want_values=True)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert torch.equal(got_i, want_i) and torch.equal(got_v, want_v)
+    assert torch.equal(ops.linear_argmax(lin, x), want_i - 11)
