@@ -7,8 +7,8 @@
 //     to NVFP4 / MXFP8 for the following GEMM, so that what crosses NVLink on the way back is the 4/8-bit
 //     activation, and the residual stream stays sharded by rows (sequence-parallel between the two collectives).
 //
-// Rank synchronisation is a flag barrier in symmetric memory: release stores to the peers' pads, acquire loads on the
-// own pad, a monotonically increasing epoch kept in device memory (so captured CUDA graphs replay correctly), and a
+// Rank synchronisation is a flag barrier in symmetric memory: relaxed system-scope stores to the peers' pads after one
+// system fence, relaxed polls of the own pad, a monotonically increasing epoch kept in device memory (so captured CUDA graphs replay correctly), and a
 // bounded spin that records an error in the status word instead of hanging.
 //
 // Reference counterparts: kernels/src/cuda/host_allreduce.cu — host_ar_kernel :171 (sums through pinned host slots
@@ -49,14 +49,6 @@ __device__ __forceinline__ void stamp(const CommParams& c, int k) {
   }
 }
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -17,16 +17,6 @@ def sampler():
     return CudaSampler(get_ops("cuda"))
 
 
-def test_eligibility_rules():
-    from blaze_b200.sampler import parse_pipeline
-    assert eligible(SamplingParams(temperature=0.8, top_k=40, top_p=0.9))
-    assert eligible(SamplingParams(temperature=0.0))
-    assert not eligible(SamplingParams(temperature=0.8, top_p=0.9))                      # no top_k: full sort needed
-    assert not eligible(SamplingParams(temperature=0.8, top_k=100))
-    assert not eligible(SamplingParams(temperature=0.8, top_k=10, pipeline=parse_pipeline("top_k,temperature")))
-    assert not eligible(SamplingParams(top_k=10, top_nsigma=0.5, pipeline=parse_pipeline("top_k,top_nsigma")))
-
-
 def test_sampler_matches_oracle(sampler):
     g = torch.Generator(device=DEV).manual_seed(31)
     V, Vpad = 5003, 5120

@@ -251,3 +251,14 @@ def test_steps_left_in_flight_give_the_same_results():
     second = llm.generate([base + [5, 6, 7] + first.token_ids[:4] + [9]], GREEDY)[0]
     cold = _llm(enable_prefix_caching=False).generate([base + [5, 6, 7] + first.token_ids[:4] + [9]], GREEDY)[0]
     assert second.cached_tokens >= 64 and second.token_ids == cold.token_ids
+
+
+def test_cuda_sampler_eligibility_rules():
+    from blaze_b200.sampler_cuda import eligible
+    from blaze_b200.sampler import parse_pipeline
+    assert eligible(SamplingParams(temperature=0.8, top_k=40, top_p=0.9))
+    assert eligible(SamplingParams(temperature=0.0))
+    assert not eligible(SamplingParams(temperature=0.8, top_p=0.9))                      # no top_k: full sort needed
+    assert not eligible(SamplingParams(temperature=0.8, top_k=100))
+    assert not eligible(SamplingParams(temperature=0.8, top_k=10, pipeline=parse_pipeline("top_k,temperature")))
+    assert not eligible(SamplingParams(top_k=10, top_nsigma=0.5, pipeline=parse_pipeline("top_k,top_nsigma")))
