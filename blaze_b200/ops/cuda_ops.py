@@ -41,6 +41,7 @@ class CudaOps:
         self.launches = 0
         self.attn_prof = None      # optional int64 [8*3*16] wait-cycle counters of the decode attention kernel
         self._scratch: Dict[str, torch.Tensor] = {}
+        self._retired: list = []
         self._sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         lib = self.lib
         lib.blz_gemm_tc.restype = _c.c_int
@@ -102,8 +103,12 @@ class CudaOps:
         return int(self.lib.blz_status_take())
 
     def _buf(self, key: str, nbytes: int) -> torch.Tensor:
+        """Scratch that only grows.  A buffer that is outgrown is kept alive: captured graphs of smaller steps still hold
+        its address, and handing that memory back to the allocator would let other tensors land under their writes."""
         b = self._scratch.get(key)
         if b is None or b.numel() < nbytes:
+            if b is not None:
+                self._retired.append(b)
             b = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self.device)
             self._scratch[key] = b
         return b
