@@ -47,6 +47,29 @@ class ChainDrafter:
                                                        kv_tokens=max_seqs * max_model_len, use_graphs=False))
         self.states: Dict[str, DraftState] = {}
         self.proposed = self.steps = 0
+        self.draft_ids: Optional[torch.Tensor] = None    # reduced draft vocabulary (token ids), or None = full head
+        self.draft_head: Optional[Linear] = None
+
+    def use_draft_vocab(self, ids: Sequence[int]) -> None:
+        """Draft over a reduced vocabulary: the head GEMM of every draft step then covers only ``ids`` (for instance the
+        32k most frequent tokens), which is most of a drafter's cost for a 150k-entry vocabulary; proposals outside the
+        subset are impossible, which only lowers acceptance — the target still decides every token
+        (``eagle.rs:694`` ``head_merged``, ``kernels/src/cuda/eagle.cu:76`` ``candidate_logits``)."""
+        ids_t = torch.as_tensor(sorted(set(int(i) for i in ids)), dtype=torch.long, device=self.target.device)
+        head = self.m.lm_head
+        w = head.dequant() if head.fmt != Format.DENSE else head.w
+        self.draft_head = Linear.from_dense(w.to(self.target.device)[ids_t].float(), Format.DENSE, dtype=self.target.dtype)
+        self.draft_ids = ids_t
+
+    def _greedy(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        if self.draft_head is None:
+            return self.m.greedy(x, rows)
+        h = self.m.final_hidden(x, rows)
+        if self.ops.is_cuda:
+            local = self.ops.linear_argmax(self.draft_head, h)
+        else:
+            local = self.ops.argmax(self.ops.linear(self.draft_head, h, out_dtype=torch.float32))
+        return self.draft_ids[local.long()]
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -161,7 +184,7 @@ class ChainDrafter:
         batch = eng._build(chunks)
         x = self.m.forward(batch, eng.kv, x_in)
         last = x[batch.logit_rows.long()]
-        cur_tok = self.m.greedy(x, batch.logit_rows)
+        cur_tok = self._greedy(x, batch.logit_rows)
         for a, k, st in todo:
             st.fed += len(st.pend_tokens)
             st.pend_hidden, st.pend_tokens = None, None
@@ -183,7 +206,7 @@ class ChainDrafter:
             batch = eng._build(chunks)
             x = self.m.forward(batch, eng.kv, x_in)
             last = x[batch.logit_rows.long()]
-            cur_tok = self.m.greedy(x, batch.logit_rows)
+            cur_tok = self._greedy(x, batch.logit_rows)
             toks_host = cur_tok.tolist()
         self.steps += 1
         self.proposed += sum(len(v) for v in out.values())

@@ -262,3 +262,18 @@ def test_cuda_sampler_eligibility_rules():
     assert not eligible(SamplingParams(temperature=0.8, top_k=100))
     assert not eligible(SamplingParams(temperature=0.8, top_k=10, pipeline=parse_pipeline("top_k,temperature")))
     assert not eligible(SamplingParams(top_k=10, top_nsigma=0.5, pipeline=parse_pipeline("top_k,top_nsigma")))
+
+
+def test_drafter_with_reduced_vocabulary_stays_exact():
+    """A drafter that can only propose a subset of the vocabulary changes acceptance, never the tokens."""
+    from blaze_b200.models.drafter import ChainDrafter
+    ps = _prompts(3, 24, seed=9)
+    sp = SamplingParams(temperature=0.0, max_tokens=14)
+    want = [o.token_ids for o in _llm().generate(ps, sp)]
+    llm = _llm(spec_method="mtp")
+    d = ChainDrafter.random_init(llm.model, seed=3, max_seqs=8, max_model_len=256, kv_dtype="fp32")
+    d.use_draft_vocab(range(0, 1024, 3))
+    llm.sched.drafter = d
+    got = llm.generate(ps, sp)
+    assert [o.token_ids for o in got] == want
+    assert d.proposed > 0 and d.draft_head.N == len(range(0, 1024, 3))
