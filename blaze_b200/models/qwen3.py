@@ -99,14 +99,24 @@ class _PhaseTimer:
     def __init__(self, device):
         self.on = torch.device(device).type == "cuda"
         self.marks = []
+        self.nvtx = self.on and os.environ.get("BLAZE_NVTX", "0") == "1"      # also open an NVTX range per phase
+        self._open = False
 
     def mark(self, name: str) -> None:
         if self.on:
+            if self.nvtx:
+                if self._open:
+                    torch.cuda.nvtx.range_pop()
+                torch.cuda.nvtx.range_push(name)
+                self._open = True
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
             self.marks.append((name, ev))
 
     def finish(self, **fields) -> None:
+        if self.nvtx and self._open:
+            torch.cuda.nvtx.range_pop()
+            self._open = False
         if not self.on or not self.marks:
             return
         end = torch.cuda.Event(enable_timing=True)

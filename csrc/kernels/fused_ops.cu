@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(512) swiglu_reg_kernel(const __nv_bfloat16* __
 // value heads.  qkv row layout: [q heads (x2 when gated: q | gate per head)] [k heads] [v heads].  The rotary
 // sine/cosine pairs of the token are computed once into shared memory and reused by every q and k head.
 template <int D>
-__global__ void __launch_bounds__(256) attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+__global__ void __launch_bounds__(512) attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                                  __nv_bfloat16* __restrict__ gate_out, uint8_t* __restrict__ kv_pool,
                                  const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                                  const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
@@ -625,8 +625,13 @@ static void configure_once() {
 }
 
 // threads and chunks per thread of the register-resident row kernels; chunks == 0: width not covered
-static inline void reg_shape(int W, int* threads, int* chunks) {
+// Few rows (a decode step) cannot fill the GPU with 256-thread CTAs: they get up to 512 threads per row, which shortens
+// each row's dependency chain; BLAZE_ROW_THREADS=256 restores one shape for all.
+static inline void reg_shape(int W, int T, int* threads, int* chunks) {
+  static int wide_rows = -1;
+  if (wide_rows < 0) { const char* e = getenv("BLAZE_ROW_THREADS"); wide_rows = (e && atoi(e) == 256) ? 0 : 1; }
   *threads = W <= 12288 ? 256 : 512;
+  if (wide_rows && T <= 1024 && W >= 4096) *threads = 512;
   const int ch = (W + *threads * 8 - 1) / (*threads * 8);
   *chunks = (W % 32 == 0 && ch <= 6) ? ch : 0;
 }
@@ -660,7 +665,7 @@ BLZ_API int blz_rmsnorm(void* x, void* residual, const void* w, void* out, void*
   const size_t sm = (size_t)H * 2;
   const int ct = quant == 1 ? (H + 63) / 64 : (H + 127) / 128;
   int rt, ch;
-  reg_shape(H, &rt, &ch);
+  reg_shape(H, T, &rt, &ch);
   if (ch) {
 #define BLZ_RN(C)                                                                                                              \
   if (quant == 0) launch_pdl(rmsnorm_reg_kernel<0, C>, dim3(T), dim3(rt), 0, s, (bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)out, (uint8_t*)nullptr, (uint8_t*)nullptr, (float*)nullptr, H, eps, zero_centered, 0, zero_src); \
@@ -689,7 +694,7 @@ BLZ_API int blz_swiglu(const void* gu, void* out, void* q_out, void* sf_out, flo
   const int ct = mode == 1 ? (I + 63) / 64 : (I + 127) / 128;
   configure_once();
   int rt, ch;
-  reg_shape(I, &rt, &ch);
+  reg_shape(I, T, &rt, &ch);
   if (ch) {
 #define BLZ_SW(C)                                                                                                              \
   if (mode == 0) launch_pdl(swiglu_reg_kernel<0, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)out, (uint8_t*)nullptr, (uint8_t*)nullptr, (float*)nullptr, I, src_is_act, 0); \
@@ -714,7 +719,10 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
   const int half = rot_dim / 2, vpl = D / 32;
   if ((D != 64 && D != 128 && D != 256) || rot_dim > D || half % vpl || ((half / vpl) & (half / vpl - 1)) || half / vpl > 16)
     return (int)cudaErrorInvalidValue;
-  const int wpb = (Hq + 2 * Hkv) >= 8 ? 8 : (Hq + 2 * Hkv);
+  // decode-sized steps: more warps per token shorten the per-token chain (launch bound of the kernel: 512 threads)
+  int wpb = (Hq + 2 * Hkv) >= 8 ? 8 : (Hq + 2 * Hkv);
+  { static int wide = -1; if (wide < 0) { const char* e = getenv("BLAZE_ROW_THREADS"); wide = (e && atoi(e) == 256) ? 0 : 1; }
+    if (wide && T <= 1024 && (Hq + 2 * Hkv) >= 16) wpb = 16; }
   const int grid = T;
 #define BLZ_PREP(DD)                                                                                                 \
   launch_pdl(attn_prep_kernel<DD>, dim3(grid), dim3(wpb * 32), 0, s, (const bf16*)qkv, (bf16*)q_out, (bf16*)gate_out,  \
