@@ -273,11 +273,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int ab = it % ACC;
       const uint32_t aph = (it / ACC) & 1;
       ++it;
-      if (!mbar_wait(&acc_full[ab], aph, abort_flag, p.status)) break;
-      tc_fence_after();
+      // the row scale and the per-column multipliers / bias of this tile are fetched (and staged once per warp) while
+      // the tile's MMAs are still running
       const int row = mt * BM + q * 32 + lane;
       const float rs = (p.row_scale && row < p.M) ? p.row_scale[row] : 1.0f;
-      // per-column multipliers and bias of this tile, staged once per warp
       float* sal = s_alpha[warp - 2];
       float* sbi = s_bias[warp - 2];
       __syncwarp();
@@ -288,6 +287,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         sbi[i] = (p.bias && col < p.N) ? bf2f(p.bias[(size_t)ex * p.N + col]) : 0.0f;
       }
       __syncwarp();
+      if (!mbar_wait(&acc_full[ab], aph, abort_flag, p.status)) break;
+      tc_fence_after();
       float best_v = -INFINITY;
       int best_i = 0x7fffffff;
 #pragma unroll 1
