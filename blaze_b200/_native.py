@@ -39,9 +39,7 @@ def _nvcc() -> Optional[str]:
 
 def _sources(sub: str, ext: str) -> List[str]:
     d = os.path.join(CSRC, sub)
-    skip = set()
-    # files that only single-GPU calls may use are listed in .gpurunignore.multi and may be absent
-    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(ext) and f not in skip) if os.path.isdir(d) else []
+    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(ext)) if os.path.isdir(d) else []
 
 
 def _digest(paths: List[str]) -> str:
