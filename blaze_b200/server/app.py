@@ -307,6 +307,14 @@ def create_app(st: ServerState) -> FastAPI:
             counter("blaze_preemptions_total", sc.stats.preemptions, "Recompute preemptions")
             counter("blaze_draft_tokens_total", sc.stats.draft_tokens, "Speculative tokens proposed")
             counter("blaze_accepted_draft_tokens_total", sc.stats.accepted_tokens, "Speculative tokens accepted")
+            counter("blaze_prefix_cache_lookups_total", sc.cache.lookups, "Prefix-cache lookups")
+            counter("blaze_prefix_cache_hits_total", sc.cache.hits, "Prefix-cache hits")
+            gauge("blaze_prefix_cache_entries", len(sc.cache.entries), "Snapshots held on the device")
+            if sc.cache.host is not None:
+                gauge("blaze_kv_host_entries", len(sc.cache.host_entries), "Snapshots parked in the host KV tier")
+                gauge("blaze_kv_host_pages_free", sc.cache.host.free_pages, "Free pages of the host KV tier")
+                counter("blaze_kv_host_hits_total", sc.cache.host_hits, "Prefix-cache hits served from the host KV tier")
+                counter("blaze_kv_host_spilled_pages_total", sc.cache.host.spilled_pages, "Pages copied to the host KV tier")
             lines.append(sc.ttft.render("blaze_time_to_first_token_seconds", "Time to first token"))
             lines.append(sc.tpot.render("blaze_time_per_output_token_seconds", "Time per output token"))
             lines.append(sc.step_ms.render("blaze_step_seconds", "Engine step time"))
