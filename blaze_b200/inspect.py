@@ -24,3 +24,20 @@ def inspect_checkpoint(model_dir: str, out=print) -> int:
         out(f"  {m:70s} {fmt:12s} {w[0]:8s} {tuple(w[1])}")
     out("formats: " + ", ".join(f"{k}={v}" for k, v in sorted(by_fmt.items())))
     return 0
+
+
+def compare_dumps(dir_a: str, dir_b: str) -> int:
+    """Compare two ``BLAZE_DUMP`` directories file by file (the counterpart of the reference's ``scripts/cmp_dumps.py``):
+    prints the largest and mean absolute difference of every tensor present in both, returns the number of files."""
+    import os
+
+    import torch
+    names = sorted(set(os.listdir(dir_a)) & set(os.listdir(dir_b)))
+    for n in names:
+        a, b = torch.load(os.path.join(dir_a, n)), torch.load(os.path.join(dir_b, n))
+        if a.shape != b.shape:
+            print(f"{n}: shapes differ {tuple(a.shape)} vs {tuple(b.shape)}")
+            continue
+        d = (a - b).abs()
+        print(f"{n}: max {d.max().item():.4g} mean {d.mean().item():.4g} (mean |a| {a.abs().mean().item():.4g})")
+    return len(names)

@@ -89,6 +89,17 @@ class Layer:
 
 _PROFILE_PHASES = os.environ.get("BLAZE_PROFILE_PHASES", "0") == "1"
 _FUSED_HEAD = os.environ.get("BLAZE_FUSED_HEAD", "1") != "0"
+_DUMP_DIR = os.environ.get("BLAZE_DUMP", "")       # directory for per-layer tensor dumps (``model.rs:2087`` ``BLAZE_DUMP``)
+_dump_step = [0]
+
+
+def _dump(name: str, t) -> None:
+    """Save a tensor of the current forward pass as fp32 for offline comparison (``inspect.compare_dumps``)."""
+    os.makedirs(_DUMP_DIR, exist_ok=True)
+    if hasattr(t, "dense") and getattr(t, "dense") is not None:
+        t = t.dense
+    if isinstance(t, torch.Tensor):
+        torch.save(t.detach().float().cpu(), os.path.join(_DUMP_DIR, f"step{_dump_step[0]:04d}_{name}.pt"))
 
 
 class _PhaseTimer:
@@ -470,8 +481,12 @@ class Model:
             h, residual = self._reduce_norm(x, residual, kind, L.post_norm, nxt, fused, defer=nxt is not None)
             if prof: prof.mark("mlp")
             x, kind = self._mlp(L.mlp, h, fused)
+            if _DUMP_DIR and kind == "full" and not (x.is_cuda and torch.cuda.is_current_stream_capturing()):
+                _dump(f"layer{gi:03d}_mlp_out", x)
         if prof:
             prof.finish(rows=int(batch.num_rows), layers=len(self.layers))
+        if _DUMP_DIR:
+            _dump_step[0] += 1
         return self._materialise(x, residual, kind, fused)
 
     def _fused(self):
