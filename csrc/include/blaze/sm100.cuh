@@ -232,6 +232,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Programmatic dependent launch: a kernel launched with the stream-serialization attribute may become resident while its
@@ -264,6 +270,14 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+// warp maximum through one redux instruction: floats are mapped to integers of the same order (and back)
+__device__ __forceinline__ float warp_max_redux(float v) {
+  int k = __float_as_int(v);
+  k ^= (k >> 31) & 0x7fffffff;
+  k = __reduce_max_sync(0xffffffffu, k);
+  k ^= (k >> 31) & 0x7fffffff;
+  return __int_as_float(k);
 }
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

@@ -282,8 +282,11 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
         const int ob = gj % NB;
         if (!TW(9, &o_full[ob], (gj / NB) & 1)) return false;
         tc_fence_after();
-        uint32_t o[NMAX];
-        tmem_ldn<NMAX>(tmem + NB * NMAX + ob * NMAX + lane_bits, o);
+        // only the first RMAX columns hold live rows: a plain decode step reads 4 of the 16
+        constexpr int LDN = RMAX <= 4 ? 4 : NMAX;
+        uint32_t o[LDN];
+        if constexpr (RMAX <= 4) tmem_ld4(tmem + NB * NMAX + ob * NMAX + lane_bits, o);
+        else tmem_ldn<NMAX>(tmem + NB * NMAX + ob * NMAX + lane_bits, o);
         tmem_ld_wait();
 #pragma unroll
         for (int r = 0; r < RMAX; ++r) {
@@ -300,8 +303,10 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
         const int gi = g + i, sb = gi % NB;
         if (!TW(7, &s_full[sb], (gi / NB) & 1)) { ok = false; break; }
         tc_fence_after();
-        uint32_t v[NMAX];
-        tmem_ldn<NMAX>(tmem + sb * NMAX + lane_bits, v);
+        constexpr int LDN = RMAX <= 4 ? 4 : NMAX;
+        uint32_t v[LDN];
+        if constexpr (RMAX <= 4) tmem_ld4(tmem + sb * NMAX + lane_bits, v);
+        else tmem_ldn<NMAX>(tmem + sb * NMAX + lane_bits, v);
         tmem_ld_wait();
         const int key = (t0 + i) * 128 + t;
         float x[RMAX];
@@ -309,7 +314,7 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
         for (int r = 0; r < RMAX; ++r) {
           if (r >= nrows) break;
           x[r] = key <= s_pos[qb][r] ? __uint_as_float(v[r]) * s_c[qb][r] : -INFINITY;
-          const float wm = warp_max(x[r]);
+          const float wm = warp_max_redux(x[r]);
           if (lane == 0) s_wmax[sb][qd][r] = wm;
         }
         __syncwarp();
