@@ -22,10 +22,11 @@ class Delta:
 
 class ChatResponseProcessor:
     def __init__(self, tokenizer, stop: Sequence[str] = (), include_stop: bool = False, skip_special_tokens: bool = True,
-                 reasoning: bool = False, starts_in_think: bool = False, tool_parser: Optional[ToolParser] = None):
+                 reasoning: bool = False, starts_in_think: bool = False, tool_parser: Optional[ToolParser] = None,
+                 think_parser: Optional[ThinkParser] = None):
         self.detok = Detok(tokenizer, skip_special_tokens)
         self.cut = StopCutter(stop, include_stop) if stop else None
-        self.think = ThinkParser(starts_in_think=starts_in_think) if reasoning else None
+        self.think = (think_parser or ThinkParser(starts_in_think=starts_in_think)) if reasoning else None
         self.tools = tool_parser
         self.text = ""
         self.reasoning_text = ""

@@ -52,3 +52,21 @@ class ThinkParser:
     def flush(self) -> Tuple[str, str]:
         out, self.buf = self.buf, ""
         return (out, "") if self.in_think else ("", out)
+
+
+#: reasoning markers per model family (reference: ``crates/blaze-chat/src/think/models`` — qwen3.rs, kimi_k3.rs;
+#: ``kimi_k3_format.rs`` for the channel markers)
+THINK_TAGS = {
+    "qwen3": ("<think>", "</think>"),
+    "deepseek": ("<think>", "</think>"),
+    "glm": ("<think>", "</think>"),
+    "kimi": ("<|open|>think<|sep|>", "<|close|>think<|sep|>"),
+}
+
+
+def get_think_parser(name: str = "qwen3", starts_in_think: bool = False) -> ThinkParser:
+    key = (name or "qwen3").lower()
+    for family, tags in THINK_TAGS.items():
+        if key.startswith(family):
+            return ThinkParser(tags[0], tags[1], starts_in_think)
+    raise ValueError(f"unknown reasoning parser {name!r}")

@@ -1,5 +1,8 @@
-"""Prompt rendering: the checkpoint's Jinja chat template when it has one, else a built-in ChatML renderer
-(Qwen style, with tools and thinking control).  Reference: ``crates/blaze-chat/src/render`` (``ChatFormatter``)."""
+"""Prompt rendering: the checkpoint's Jinja chat template when it has one, else a built-in renderer of the model
+family (ChatML for Qwen, with tools and thinking control; DeepSeek, GLM and Kimi turn markers).  Before either, the
+messages are normalised the way the family's template expects them (``normalize_messages``).
+Reference: ``crates/blaze-chat/src/render`` (``ChatFormatter``; ``render/models`` — qwen38.rs, deepseek_v4.rs, glm53.rs,
+kimi_k3.rs prepare the request for the family's template)."""
 from __future__ import annotations
 
 import json
@@ -28,8 +31,64 @@ def _text_of(content) -> str:
     return "".join(out)
 
 
+FAMILIES = ("chatml", "deepseek", "glm", "kimi")
+
+
+def family_of(model_name: str) -> str:
+    """Renderer family from a model or architecture name."""
+    n = (model_name or "").lower()
+    for key, fam in (("deepseek", "deepseek"), ("glm", "glm"), ("kimi", "kimi"), ("moonshot", "kimi")):
+        if key in n:
+            return fam
+    return "chatml"
+
+
+def normalize_messages(messages: List[Dict[str, Any]], family: str = "chatml", flatten: bool = False) -> List[Dict[str, Any]]:
+    """What the family templates rely on: ``developer`` is ``system``; assistant tool-call arguments are objects
+    (a JSON string is parsed, anything else is an error); ``content`` defaults to ""; with ``flatten`` the content
+    parts collapse to their text.  DeepSeek and Kimi always get a leading system message (theirs carries the tools),
+    and DeepSeek merges a user turn that follows a user or tool turn into one."""
+    out: List[Dict[str, Any]] = []
+    for m in messages:
+        m = dict(m)
+        if m.get("role") == "developer":
+            m["role"] = "system"
+        if m.get("content") is None:
+            m["content"] = ""
+        if flatten or family in ("deepseek", "kimi", "glm"):
+            m["content"] = _text_of(m["content"]) if not isinstance(m["content"], str) else m["content"]
+        if m.get("tool_calls"):
+            calls = []
+            for i, tc in enumerate(m["tool_calls"]):
+                fn = dict(tc.get("function", tc))
+                args = fn.get("arguments", {})
+                if isinstance(args, str):
+                    try:
+                        args = json.loads(args) if args.strip() else {}
+                    except ValueError:
+                        raise ValueError("assistant tool arguments must be a JSON object")
+                if not isinstance(args, dict):
+                    raise ValueError("assistant tool arguments must be a JSON object")
+                calls.append({"id": tc.get("id"), "index": tc.get("index", i), "type": "function",
+                              "function": {"name": fn.get("name"), "arguments": args}})
+            m["tool_calls"] = calls
+        elif "tool_calls" in m:
+            del m["tool_calls"]
+        if family == "deepseek" and out and m["role"] == "user" and out[-1]["role"] == "user":
+            out[-1] = dict(out[-1], content=out[-1]["content"] + "\n\n" + m["content"])
+            continue
+        out.append(m)
+    if family in ("deepseek", "kimi") and (not out or out[0]["role"] != "system"):
+        out.insert(0, {"role": "system", "content": ""})
+    return out
+
+
 class ChatFormatter:
-    def __init__(self, chat_template: Optional[str] = None, bos_token: str = "", eos_token: str = "<|im_end|>"):
+    def __init__(self, chat_template: Optional[str] = None, bos_token: str = "", eos_token: str = "<|im_end|>",
+                 family: str = "chatml"):
+        if family not in FAMILIES:
+            raise ValueError(f"unknown chat family {family!r}")
+        self.family = family
         self.template_src = chat_template
         self.bos_token, self.eos_token = bos_token, eos_token
         self._tpl = None
@@ -49,13 +108,126 @@ class ChatFormatter:
 
     def render(self, messages: List[Dict[str, Any]], tools: Optional[List[Dict[str, Any]]] = None,
                add_generation_prompt: bool = True, enable_thinking: Optional[bool] = None, **kwargs) -> str:
+        if self.family != "chatml":
+            messages = normalize_messages(messages, self.family)
         if self._tpl is not None:
             ctx = dict(messages=messages, tools=tools, add_generation_prompt=add_generation_prompt,
                        bos_token=self.bos_token, eos_token=self.eos_token, **kwargs)
             if enable_thinking is not None:
                 ctx["enable_thinking"] = enable_thinking
             return self._tpl.render(**ctx)
-        return self._chatml(messages, tools, add_generation_prompt, enable_thinking)
+        builtin = {"chatml": self._chatml, "deepseek": self._deepseek, "glm": self._glm, "kimi": self._kimi}[self.family]
+        return builtin(messages, tools, add_generation_prompt, enable_thinking)
+
+    # ---- built-in family renderers (used when the checkpoint ships no template) ----
+    @staticmethod
+    def _tool_lines(tools) -> str:
+        return "\n".join(json.dumps(t.get("function", t), ensure_ascii=False) for t in tools or [])
+
+    def _deepseek(self, messages, tools, add_generation_prompt, enable_thinking) -> str:
+        D = "｜DSML｜"
+        out = [self.bos_token or "<｜begin▁of▁sentence｜>"]
+        system = messages[0]["content"]
+        if tools:
+            system += (("\n\n" if system else "") + "## Tools\nYou can call these functions:\n<functions>\n"
+                       + self._tool_lines(tools) + f"\n</functions>\nCall them inside one <{D}tool_calls> block of "
+                       f'<{D}invoke name="..."> elements with <{D}parameter name="..." string="true|false"> children.')
+        out.append(system)
+        for m in messages[1:]:
+            role = m["role"]
+            if role == "assistant":
+                body = ""
+                if m.get("reasoning_content"):
+                    body += "<think>" + m["reasoning_content"] + "</think>"
+                body += m["content"]
+                if m.get("tool_calls"):
+                    body += f"\n\n<{D}tool_calls>\n"
+                    for tc in m["tool_calls"]:
+                        fn = tc["function"]
+                        body += f'<{D}invoke name="{fn["name"]}">\n'
+                        for k, v in fn["arguments"].items():
+                            is_str = isinstance(v, str)
+                            body += (f'<{D}parameter name="{k}" string="{"true" if is_str else "false"}">'
+                                     + (v if is_str else json.dumps(v, ensure_ascii=False)) + f"</{D}parameter>\n")
+                        body += f"</{D}invoke>\n"
+                    body += f"</{D}tool_calls>"
+                out.append("<｜Assistant｜>" + body + "<｜end▁of▁sentence｜>")
+            elif role == "tool":
+                out.append("<｜User｜><function_results>\n<result>" + m["content"] + "</result>\n</function_results>")
+            elif role == "system":
+                out.append("\n\n" + m["content"])
+            else:
+                out.append("<｜User｜>" + m["content"])
+        if add_generation_prompt:
+            out.append("<｜Assistant｜>" + ("</think>" if enable_thinking is False else "<think>"))
+        return "".join(out)
+
+    def _glm(self, messages, tools, add_generation_prompt, enable_thinking) -> str:
+        out = ["[gMASK]<sop>"]
+        if tools:
+            out.append("<|system|>\n# Tools\n\nYou may call one or more functions to assist with the user query.\n<tools>\n"
+                       + self._tool_lines(tools) + "\n</tools>\n\nFor each function call, output the function name and "
+                       "arguments within <tool_call>{function-name}\n<arg_key>{key}</arg_key>\n<arg_value>{value}</arg_value>\n"
+                       "...\n</tool_call>")
+        for m in messages:
+            role = m["role"]
+            if role == "assistant":
+                body = "\n<think>" + (m.get("reasoning_content") or "") + "</think>\n" + m["content"]
+                for tc in m.get("tool_calls") or []:
+                    fn = tc["function"]
+                    body += "\n<tool_call>" + fn["name"]
+                    for k, v in fn["arguments"].items():
+                        body += (f"\n<arg_key>{k}</arg_key>\n<arg_value>"
+                                 + (v if isinstance(v, str) else json.dumps(v, ensure_ascii=False)) + "</arg_value>")
+                    body += "\n</tool_call>"
+                out.append("<|assistant|>" + body)
+            elif role == "tool":
+                out.append("<|observation|>\n<tool_response>\n" + m["content"] + "\n</tool_response>")
+            else:
+                out.append(f"<|{role}|>\n" + m["content"] + ("/nothink" if role == "user" and enable_thinking is False else ""))
+        if add_generation_prompt:
+            out.append("<|assistant|>" + ("\n<think></think>\n" if enable_thinking is False else ""))
+        return "".join(out)
+
+    def _kimi(self, messages, tools, add_generation_prompt, enable_thinking) -> str:
+        O, C, S = "<|open|>", "<|close|>", "<|sep|>"
+
+        def esc(v: str) -> str:
+            return v.replace("&", "&amp;").replace('"', "&quot;")
+
+        out: List[str] = []
+        for i, m in enumerate(messages):
+            role = m["role"]
+            out.append(f'{O}message role="{role}"{S}')
+            if i == 0 and tools:
+                out.append(f"{O}tools{S}" + self._tool_lines(tools) + f"{C}tools{S}")
+            if role == "assistant":
+                if m.get("reasoning_content"):
+                    out.append(f"{O}think{S}" + m["reasoning_content"] + f"{C}think{S}")
+                if m["content"]:
+                    out.append(f"{O}response{S}" + m["content"] + f"{C}response{S}")
+                if m.get("tool_calls"):
+                    out.append(f"{O}tools{S}")
+                    for tc in m["tool_calls"]:
+                        fn = tc["function"]
+                        out.append(f'{O}call tool="{esc(fn["name"])}"' + (f' id="{esc(tc["id"])}"' if tc.get("id") else "") + S)
+                        for k, v in fn["arguments"].items():
+                            typ = ("string" if isinstance(v, str) else "boolean" if isinstance(v, bool) else
+                                   "number" if isinstance(v, (int, float)) else "null" if v is None else
+                                   "array" if isinstance(v, list) else "object")
+                            out.append(f'{O}argument key="{esc(k)}" type="{typ}"{S}'
+                                       + (v if isinstance(v, str) else json.dumps(v, ensure_ascii=False)) + f"{C}argument{S}")
+                        out.append(f"{C}call{S}")
+                    out.append(f"{C}tools{S}")
+            elif role == "tool":
+                out.append((f'{O}result id="{esc(m["tool_call_id"])}"{S}' if m.get("tool_call_id") else f"{O}result{S}")
+                           + m["content"] + f"{C}result{S}")
+            else:
+                out.append(m["content"])
+            out.append(f"{C}message{S}")
+        if add_generation_prompt:
+            out.append(f'{O}message role="assistant"{S}' + (f"{O}response{S}" if enable_thinking is False else f"{O}think{S}"))
+        return "".join(out)
 
     def _chatml(self, messages, tools, add_generation_prompt, enable_thinking) -> str:
         out: List[str] = []

@@ -84,6 +84,7 @@ def service_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--top-h", type=float, default=None)
     g.add_argument("--tool-call-parser", default="hermes")
     g.add_argument("--reasoning-parser", default="qwen3")
+    g.add_argument("--chat-family", default=None, choices=["chatml", "deepseek", "glm", "kimi"])
 
 
 def build_parser() -> argparse.ArgumentParser:

@@ -23,7 +23,7 @@ from fastapi import FastAPI, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from .. import __version__, log
-from ..chat import ChatFormatter, ChatResponseProcessor, get_tool_parser
+from ..chat import ChatFormatter, ChatResponseProcessor, get_think_parser, get_tool_parser
 from ..sampler import SamplingParams
 from ..sched import Finish, GenEvent, GenRequest, ThinkBudget
 from ..service import (MAX_COMPLETIONS_PER_REQUEST, RequestError, ServiceArgs, sampling_of, stop_strings_of,
@@ -65,7 +65,7 @@ class ServerState:
 
     def attach(self, llm, tokenizer, vision=None) -> None:
         self.tokenizer = tokenizer
-        self.formatter = ChatFormatter(getattr(tokenizer, "chat_template", None))
+        self.formatter = ChatFormatter(getattr(tokenizer, "chat_template", None), family=self.svc.chat_family or "chatml")
         cfg = llm.model.cfg
         eos = tuple(llm.sched.cfg.eos_ids) or tuple(getattr(tokenizer, "eos_ids", ()))
         llm.sched.cfg.eos_ids = eos
@@ -365,6 +365,10 @@ def create_app(st: ServerState) -> FastAPI:
             return None
         return ThinkBudget(budget, o, c, st.tokenizer.encode(THINK_CLOSING))
 
+    def _think_parser(st):
+        """Reasoning splitter of the configured family (None when reasoning parsing is off)."""
+        return get_think_parser(st.svc.reasoning_parser) if st.svc.reasoning_parser else None
+
     def _cache_point(prompt_ids: List[int]) -> Optional[int]:
         """Prefix-cache boundary: the last ``<|im_start|>`` (``server.rs:926-933``)."""
         ims = st.tokenizer.token_id("<|im_start|>")
@@ -430,7 +434,8 @@ def create_app(st: ServerState) -> FastAPI:
             cons = st.grammars.constraint(spec) if spec else None
             g = Gen(st, ids, p, cache_point=_cache_point(ids), constraint=cons, think=_think(b, enable_thinking), mm=mm)
             proc = ChatResponseProcessor(st.tokenizer, stops, include_stop, skip_special, reasoning=reasoning,
-                                         tool_parser=get_tool_parser(st.svc.tool_call_parser, tools) if tools else None)
+                                         tool_parser=get_tool_parser(st.svc.tool_call_parser, tools) if tools else None,
+                                         think_parser=_think_parser(st))
             return g, proc
         gens = [make(i) for i in range(n)]
 
@@ -694,7 +699,8 @@ def create_app(st: ServerState) -> FastAPI:
         cons = st.grammars.constraint(spec) if spec else None
         g = Gen(st, ids, params, cache_point=_cache_point(ids), constraint=cons, mm=mm)
         proc = ChatResponseProcessor(st.tokenizer, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
-                                     tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None)
+                                     tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None,
+                                     think_parser=_think_parser(st))
         stream = bool(b.get("stream", False))
 
         def build(status: str) -> Dict[str, Any]:
@@ -845,7 +851,8 @@ def create_app(st: ServerState) -> FastAPI:
         mid = "msg_" + uuid.uuid4().hex[:24]
         g = Gen(st, ids, params, cache_point=_cache_point(ids), mm=mm)
         proc = ChatResponseProcessor(st.tokenizer, stops, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
-                                     tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None)
+                                     tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None,
+                                     think_parser=_think_parser(st))
 
         def stop_reason():
             if proc.tool_calls:

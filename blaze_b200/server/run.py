@@ -17,7 +17,8 @@ def service_args_of(ns) -> ServiceArgs:
                        default_max_tokens=ns.default_max_tokens, log_level=ns.log_level, log_format=ns.log_format,
                        profile_prefill=ns.profile_prefill, generation_config=ns.generation_config, samplers=ns.samplers,
                        top_nsigma=ns.top_nsigma, top_h=ns.top_h, tool_call_parser=ns.tool_call_parser,
-                       reasoning_parser=ns.reasoning_parser or None)
+                       reasoning_parser=ns.reasoning_parser or None,
+                       chat_family=getattr(ns, "chat_family", None))
 
 
 def serve(ns) -> int:

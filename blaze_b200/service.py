@@ -48,6 +48,7 @@ class ServiceArgs:
     top_h: Optional[float] = None
     tool_call_parser: str = "hermes"
     reasoning_parser: Optional[str] = "qwen3"
+    chat_family: Optional[str] = None            # built-in renderer + message normalisation: chatml, deepseek, glm, kimi
     cors_origins: Tuple[str, ...] = ("*",)
     defaults: Dict[str, Any] = field(default_factory=dict)
 

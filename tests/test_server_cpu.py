@@ -113,3 +113,68 @@ def test_embeddings_responses_messages(client):
     with client.stream("POST", "/v1/messages", json={"max_tokens": 4, "stream": True, "messages": [{"role": "user", "content": "hi"}]}, headers=H) as s:
         ev = [l for l in s.iter_lines() if l.startswith("event: ")]
     assert ev[0] == "event: message_start" and ev[-1] == "event: message_stop"
+
+
+# ---------------------------------------------------------------------------------------------- chat families
+_FAMILY_TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+    "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}, "opts": {"type": "object"}}}}}]
+_FAMILY_CALL = {"id": "c1", "type": "function", "function": {
+    "name": "get_weather", "arguments": json.dumps({"city": "Paris & \"Lyon\"", "days": 3, "opts": {"unit": "C"}})}}
+
+
+def _stream(parser, text, step):
+    content, calls = "", []
+    for i in range(0, len(text), step):
+        c, k = parser.push(text[i:i + step])
+        content, calls = content + c, calls + k
+    c, k = parser.flush()
+    return content + c, calls + k
+
+
+@pytest.mark.parametrize("family,parser", [("chatml", "hermes"), ("deepseek", "deepseek"), ("glm", "glm"), ("kimi", "kimi")])
+def test_family_renderer_and_tool_parser_round_trip(family, parser):
+    """What a family's renderer writes for an assistant tool call, its parser reads back, at any delta size."""
+    from blaze_b200.chat import ChatFormatter, get_tool_parser
+    msgs = [{"role": "developer", "content": "Be brief."}, {"role": "user", "content": [{"type": "text", "text": "Weather?"}]},
+            {"role": "assistant", "content": "Looking.", "tool_calls": [_FAMILY_CALL, dict(_FAMILY_CALL, id="c2")]},
+            {"role": "tool", "tool_call_id": "c1", "content": "sunny"}]
+    fmt = ChatFormatter(family=family)
+    full = fmt.render(msgs, _FAMILY_TOOLS)
+    head = fmt.render(msgs[:2], _FAMILY_TOOLS, add_generation_prompt=False)
+    assert full.startswith(head) and "Be brief." in head and "get_weather" in head
+    turn = full[len(head):]
+    for step in (1, 3, 11, 10_000):
+        content, calls = _stream(get_tool_parser(parser, _FAMILY_TOOLS), turn, step)
+        assert [c.name for c in calls[:2]] == ["get_weather", "get_weather"], (family, step, turn)
+        assert json.loads(calls[0].arguments) == json.loads(_FAMILY_CALL["function"]["arguments"])
+        assert "Looking." in content and "get_weather" not in content.split("sunny")[0]
+
+
+def test_message_normalisation():
+    from blaze_b200.chat.template import family_of, normalize_messages
+    out = normalize_messages([{"role": "user", "content": "a"}, {"role": "user", "content": "b"},
+                              {"role": "assistant", "content": None, "tool_calls": [{"function": {"name": "f", "arguments": ""}}]}],
+                             "deepseek")
+    assert [m["role"] for m in out] == ["system", "user", "assistant"] and out[1]["content"] == "a\n\nb"
+    assert out[2]["content"] == "" and out[2]["tool_calls"][0]["function"]["arguments"] == {}
+    with pytest.raises(ValueError):
+        normalize_messages([{"role": "assistant", "tool_calls": [{"function": {"name": "f", "arguments": "[1]"}}]}])
+    assert family_of("DeepSeek-V3.2") == "deepseek" and family_of("Kimi-K2") == "kimi" and family_of("Qwen3-8B") == "chatml"
+
+
+def test_dsml_and_kimi_details():
+    from blaze_b200.chat import get_think_parser, get_tool_parser
+    M = "｜DSML｜"
+    spaced = (f'<{M} calls><{M} invoke name="f"><{M} parameter name="s" string="true"> keep </{M} parameter>'
+              f'<{M} parameter name="bad" string="false">{{oops</{M} parameter></{M} invoke></{M} calls>')
+    _, calls = _stream(get_tool_parser("deepseek_v41"), spaced, 5)
+    assert json.loads(calls[0].arguments) == {"s": " keep ", "bad": "{oops"}
+    kimi = ('<|open|>tools<|sep|><|open|>call id="x"<|sep|><|close|>call<|sep|>'           # no tool name: dropped
+            '<|open|>call tool="g" tool="h"<|sep|><|open|>argument key="v" type="array"<|sep|>[1, 2]<|close|>argument<|sep|>'
+            '<|close|>call<|sep|><|close|>tools<|sep|>')
+    _, calls = _stream(get_tool_parser("kimi"), kimi, 4)
+    assert [(c.name, json.loads(c.arguments)) for c in calls] == [("h", {"v": [1, 2]})]
+    think = get_think_parser("kimi_k3", starts_in_think=True)
+    r, c = think.push("plan<|close|>think<|sep|>answer")
+    fr, fc = think.flush()
+    assert (r + fr, c + fc) == ("plan", "answer")
