@@ -40,6 +40,7 @@ def engine_parser(p: argparse.ArgumentParser) -> None:
                    help="pinned host memory behind the prefix cache, in tokens: evicted snapshots wait there (0 = off)")
     g.add_argument("--kv-cache-dtype", default=None, choices=["fp8", "bf16", "fp32", "nvfp4", "nvfp4_4over6", "auto"])
     g.add_argument("--kv-host", action="store_true", help="keep cold KV pages in pinned host memory")
+    g.add_argument("--kv-rotate", action="store_true", help="randomised Hadamard rotation of q and k rows before the KV write")
     g.add_argument("--chunk", type=int, default=None, help="prefill tokens per iteration")
     g.add_argument("--vram-reserve", type=float, default=2.0, help="GiB kept free when sizing the KV pool")
     g.add_argument("--max-seqs", type=int, default=None)
@@ -181,7 +182,7 @@ def build_llm(ns: argparse.Namespace):
               chunk=ns.chunk or 2048, enable_prefix_caching=not ns.disable_prefix_caching,
               cache_slots=ns.prompt_cache_slots or 4, use_graphs=not ns.no_graphs,
               spec_method=ns.spec_method or "none", max_draft=min(ns.max_verify - 1, 8), seed=ns.seed,
-              kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"))
+              kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"), kv_rotate=bool(getattr(ns, "kv_rotate", False)))
     if group is not None and ns.comm == "fused" and device.startswith("cuda"):
         from .parallel.symm import SymmAllReduce
         group.fused = SymmAllReduce.create(group, device, max_rows=(ns.chunk or 2048) + (ns.max_seqs or 256) + 64,

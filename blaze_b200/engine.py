@@ -82,6 +82,7 @@ class EngineConfig:
     max_seqs: int = 256
     max_model_len: int = 4096
     kv_dtype: str = "bf16"             # fp32 | bf16 | fp8
+    kv_rotate: bool = False            # Hadamard-rotate q and k rows before the key is stored (fewer e4m3 outliers)
     chunk: int = 2048
     use_graphs: bool = True
     vram_reserve: int = 2 << 30
@@ -109,6 +110,9 @@ class Engine:
         self.num_pages = kv_tokens // PAGE + 1
         self.max_pages_per_seq = (ecfg.max_model_len + PAGE - 1) // PAGE
         layout = "umma" if (self.device.type == "cuda" and ecfg.kv_dtype == "fp8" and model.ops.is_cuda) else "logical"
+        if ecfg.kv_rotate and cfg.head_dim & (cfg.head_dim - 1):
+            raise ValueError("kv_rotate needs a power-of-two head_dim")
+        model.kv_rotate = bool(ecfg.kv_rotate)      # read by the attention prep of both op sets
         self.kv = KVCache(cfg, self.num_pages, ecfg.max_seqs, self.max_pages_per_seq, ecfg.kv_dtype, self.device,
                           layout, tpw, state_rows=ecfg.max_seqs + ecfg.snapshot_rows)
         self.pages = PageAllocator(self.num_pages)

@@ -66,7 +66,7 @@ class CudaOps:
         lib.blz_swiglu.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_attn_prep.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                       _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_float, _c.c_float, _c.c_longlong,
-                                      _c.c_longlong, VP]
+                                      _c.c_longlong, _c.c_int, VP]
         lib.blz_attn_tc.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                     _c.c_longlong, _c.c_longlong, _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
         lib.blz_attn_decode.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
@@ -412,7 +412,8 @@ class CudaOps:
                                            _ptr(batch.slot_mapping), _ptr(model.inv_freq), _ptr(attn.q_norm), _ptr(attn.k_norm),
                                            T, attn.heads, attn.kv_heads, D, cfg.rotary_dim, cfg.rms_norm_eps,
                                            model.rope_scale, int(cfg.attn_output_gate), int(cfg.zero_centered_norm),
-                                           1.0, 1.0, kv.kv[layer_idx].stride(0), kv.kv[layer_idx].stride(1), self._stream()), "attn_prep")
+                                           1.0, 1.0, kv.kv[layer_idx].stride(0), kv.kv[layer_idx].stride(1),
+                                           int(getattr(model, "kv_rotate", False)), self._stream()), "attn_prep")
         return q, gate
 
     def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0):

@@ -71,10 +71,30 @@ def apply_rope_neox(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> to
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], dim=-1)
 
 
+def hadamard_rotate(x: torch.Tensor) -> torch.Tensor:
+    """Randomised Hadamard rotation of the last dimension (a power of two): element i changes sign when bit 15 of
+    ``i * 2654435761 mod 2**32`` is set, then a Walsh-Hadamard transform scaled by 1/sqrt(D).  Orthogonal, so the dot
+    product of two rotated vectors is the dot product of the originals (reference: ``rht_kernel``,
+    kernels/src/cuda/nvfp4_kv.cu :356, behind ``--kv-rotate``)."""
+    D = x.shape[-1]
+    assert D & (D - 1) == 0
+    idx = torch.arange(D, dtype=torch.int64)
+    sign = 1.0 - 2.0 * (((idx * 2654435761) % (1 << 32)) >> 15 & 1).to(torch.float32)
+    y = x.float() * sign.to(x.device)
+    h = 1
+    while h < D:
+        y = y.reshape(*x.shape[:-1], D // (2 * h), 2, h)
+        y = torch.stack([y[..., 0, :] + y[..., 1, :], y[..., 0, :] - y[..., 1, :]], dim=-2)
+        h *= 2
+    return y.reshape(x.shape) * D ** -0.5
+
+
 def attn_prep(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
               q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
-              cos: torch.Tensor, sin: torch.Tensor, gated: bool = False, zero_centered: bool = False):
-    """Split qkv rows, per-head RMSNorm of q and k, rotary.  Returns (q, k, v, gate|None) as [T,H,D]."""
+              cos: torch.Tensor, sin: torch.Tensor, gated: bool = False, zero_centered: bool = False,
+              rotate: bool = False):
+    """Split qkv rows, per-head RMSNorm of q and k, rotary, optionally the Hadamard rotation of q and k.
+    Returns (q, k, v, gate|None) as [T,H,D]."""
     T = qkv.shape[0]
     dt = qkv.dtype
     qw = num_heads * head_dim * (2 if gated else 1)
@@ -96,9 +116,11 @@ def attn_prep(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: in
         y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * wf
         return y.to(dt).float()
 
-    q = apply_rope_neox(hn(q, q_norm_w), cos, sin).to(dt)
-    k = apply_rope_neox(hn(k, k_norm_w), cos, sin).to(dt)
-    return q, k, v.contiguous(), gate
+    q = apply_rope_neox(hn(q, q_norm_w), cos, sin)
+    k = apply_rope_neox(hn(k, k_norm_w), cos, sin)
+    if rotate:
+        q, k = hadamard_rotate(q), hadamard_rotate(k)
+    return q.to(dt), k.to(dt), v.contiguous(), gate
 
 
 # ----------------------------------------------------------------------------------- paged KV

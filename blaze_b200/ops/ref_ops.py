@@ -55,7 +55,7 @@ class RefOps:
         cos, sin = rope
         q, k, v, gate = ref.attn_prep(qkv, attn.heads, attn.kv_heads, cfg.head_dim, attn.q_norm, attn.k_norm,
                                       cfg.rms_norm_eps, cos, sin, gated=cfg.attn_output_gate,
-                                      zero_centered=cfg.zero_centered_norm)
+                                      zero_centered=cfg.zero_centered_norm, rotate=getattr(model, "kv_rotate", False))
         valid = batch.slot_mapping >= 0
         if kv.layout == "umma":
             kl, vl = kv.logical_kv(layer_idx)

@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(512) attn_prep_kernel(const __nv_bfloat16* __r
                                  const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
                                  const __nv_bfloat16* __restrict__ k_norm_w, int T, int Hq, int Hkv, int rot_dim,
                                  float eps, float rope_scale, int gated, int zero_centered, float k_scale_inv,
-                                 float v_scale_inv, long long page_stride, long long head_stride) {
+                                 float v_scale_inv, long long page_stride, long long head_stride, int rotate) {
   pdl_trigger();
   pdl_wait();
   constexpr int VPL = D / 32;
@@ -483,6 +483,31 @@ __global__ void __launch_bounds__(512) attn_prep_kernel(const __nv_bfloat16* __r
           const float2 c = cs[i < half ? i : i - half];
           v[j] = i < half ? v[j] * c.x - other * c.y : v[j] * c.x + other * c.y;
         }
+      }
+      // Optional randomised Hadamard rotation of q and k (the same orthogonal map on both keeps q.k; it spreads
+      // outliers over the head before the key is rounded to e4m3): sign flip by a fixed hash of the element index,
+      // then a Walsh-Hadamard transform over the D elements the warp holds, scaled by 1/sqrt(D).
+      if (rotate) {
+#pragma unroll
+        for (int j = 0; j < VPL; ++j)
+          if (((uint32_t)(lane * VPL + j) * 2654435761u >> 15) & 1u) v[j] = -v[j];
+#pragma unroll
+        for (int st = 1; st < VPL; st <<= 1) {
+#pragma unroll
+          for (int j = 0; j < VPL; ++j)
+            if (!(j & st)) { const float a = v[j], b = v[j | st]; v[j] = a + b; v[j | st] = a - b; }
+        }
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], m);
+            v[j] = (lane & m) ? other - v[j] : v[j] + other;
+          }
+        }
+        const float sc = rsqrtf((float)D);
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) v[j] *= sc;
       }
     }
     if (kind == 0) {
@@ -714,7 +739,7 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
                           const int* slot_mapping, const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
                           int T, int Hq, int Hkv, int D, int rot_dim, float eps, float rope_scale, int gated,
                           int zero_centered, float k_scale, float v_scale, long long page_stride, long long head_stride,
-                          cudaStream_t s) {
+                          int rotate, cudaStream_t s) {
   if (T == 0) return 0;
   const int half = rot_dim / 2, vpl = D / 32;
   if ((D != 64 && D != 128 && D != 256) || rot_dim > D || half % vpl || ((half / vpl) & (half / vpl - 1)) || half / vpl > 16)
@@ -728,7 +753,8 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
   launch_pdl(attn_prep_kernel<DD>, dim3(grid), dim3(wpb * 32), 0, s, (const bf16*)qkv, (bf16*)q_out, (bf16*)gate_out,  \
              (uint8_t*)kv_pool, positions, slot_mapping, inv_freq, (const bf16*)q_norm_w, (const bf16*)k_norm_w, T, Hq, \
              Hkv, rot_dim, eps, rope_scale, gated, zero_centered, 1.f / k_scale, 1.f / v_scale,                         \
-             page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D, head_stride > 0 ? head_stride : (long long)2 * 16 * D)
+             page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D, head_stride > 0 ? head_stride : (long long)2 * 16 * D, \
+             rotate)
   if (D == 64) BLZ_PREP(64); else if (D == 128) BLZ_PREP(128); else BLZ_PREP(256);
 #undef BLZ_PREP
   return (int)cudaGetLastError();

@@ -234,7 +234,7 @@ class _A:
     pass
 
 
-def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8):
+def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False):
     """Write random K/V through the prep kernel, then compare attention with the oracle over the same FP8 cache."""
     from blaze_b200.batch import SeqChunk, build_batch
     from blaze_b200.config import ModelConfig, RopeConfig, inv_freq
@@ -252,6 +252,7 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8):
     model.cfg = cfg
     model.inv_freq = torch.tensor(inv_freq(cfg), dtype=torch.float32, device=DEV)
     model.rope_scale = 1.0
+    model.kv_rotate = rotate
     attn = _A()
     attn.heads, attn.kv_heads = Hq, Hkv
     attn.q_norm = (1 + 0.1 * torch.randn(D, generator=g, device=DEV)).bfloat16()
@@ -275,7 +276,7 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8):
         q, _ = ops.attn_prep_store(qkv, attn, model, batch, kv, 0, None)
         # oracle prep on the same inputs
         cos, sin = ref.rope_cos_sin(batch.positions, model.inv_freq)
-        qr, kr, vr, _ = ref.attn_prep(qkv, Hq, Hkv, D, attn.q_norm, attn.k_norm, 1e-6, cos, sin)
+        qr, kr, vr, _ = ref.attn_prep(qkv, Hq, Hkv, D, attn.q_norm, attn.k_norm, 1e-6, cos, sin, rotate=rotate)
         assert (q.float() - qr.float()).abs().max().item() < 0.07
         if phase == 1:
             o = ops.attention(q, model, batch, kv, 0, D ** -0.5)
@@ -306,6 +307,17 @@ def test_attention(ops, Hq, Hkv, ctxs, qlens):
     mx, rel = _report(f"attention Hq{Hq} Hkv{Hkv} ctx{ctxs} q{qlens}", o, want)
     assert rel < 0.06
     assert torch.isfinite(o.float()).all()
+
+
+def test_attention_rotated_keys(ops):
+    """With the Hadamard rotation of q and k on, the prep kernel matches the rotated oracle, and the attention output
+    stays the output without rotation up to the rounding of the FP8 keys."""
+    o, want = _attention_case(ops, 32, 8, [1024, 300, 129, 17], [1, 1, 1, 1], rotate=True)
+    _, rel = _report("attention rotated q/k vs rotated oracle", o, want)
+    assert rel < 0.06
+    plain, _ = _attention_case(ops, 32, 8, [1024, 300, 129, 17], [1, 1, 1, 1], rotate=False)
+    _, rel = _report("attention rotated q/k vs unrotated kernel", o, plain)
+    assert rel < 0.08
 
 
 def test_attention_split_kv(ops):

@@ -69,3 +69,21 @@ def test_tiny_qwen3_greedy_matches_dense_reference():
     for s in seqs:
         eng.close(s)
     assert eng.pages.free_count == eng.num_pages - 1
+
+
+def test_kv_rotation_keeps_the_output():
+    """Rotating q and k by the same orthogonal map changes the stored keys but not the scores: generation with
+    ``kv_rotate`` gives the tokens of the plain run."""
+    from blaze_b200.llm import LLM
+    from blaze_b200.ops import ref
+    from blaze_b200.sampler import SamplingParams
+    x, y = torch.randn(4, 3, 64), torch.randn(4, 3, 64)
+    rx, ry = ref.hadamard_rotate(x), ref.hadamard_rotate(y)
+    assert torch.allclose((rx * ry).sum(-1), (x * y).sum(-1), atol=1e-4)
+    assert not torch.allclose(rx, x, atol=1e-2)
+    outs = []
+    for rot in (False, True):
+        llm = LLM("tiny", device="cpu", dtype=torch.float32, kv_cache_dtype="fp32", kv_rotate=rot, seed=3, max_seqs=4,
+                  max_model_len=128)
+        outs.append(llm.generate([[5, 6, 7, 8, 9, 10, 11], [40, 41, 42]], SamplingParams(max_tokens=12, temperature=0.0)))
+    assert [o.token_ids for o in outs[0]] == [o.token_ids for o in outs[1]]
