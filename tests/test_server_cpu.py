@@ -178,3 +178,22 @@ def test_dsml_and_kimi_details():
     r, c = think.push("plan<|close|>think<|sep|>answer")
     fr, fc = think.flush()
     assert (r + fr, c + fc) == ("plan", "answer")
+
+
+def test_server_with_another_chat_family():
+    """A server configured for the Kimi markers renders with them and answers a chat request that carries tools."""
+    st = ServerState(ServiceArgs(default_max_tokens=6, chat_family="kimi", tool_call_parser="kimi", reasoning_parser="kimi"), "tiny")
+    c = TestClient(create_app(st))
+    llm = LLM(named_config("tiny"), device="cpu", dtype=torch.float32, max_seqs=4, max_model_len=1024, use_graphs=False)
+    try:
+        st.attach(llm, ByteTokenizer(1024))
+        assert st.formatter.family == "kimi"
+        text = st.formatter.render([{"role": "user", "content": "hi"}])
+        assert text.startswith('<|open|>message role="system"<|sep|>') and text.endswith("<|open|>think<|sep|>")
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6,
+                                                  "temperature": 0, "tools": _FAMILY_TOOLS})
+        assert r.status_code == 200, r.text
+        msg = r.json()["choices"][0]["message"]
+        assert msg["role"] == "assistant" and r.json()["usage"]["completion_tokens"] == 6
+    finally:
+        llm.sched.stop()
