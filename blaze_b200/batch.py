@@ -24,6 +24,9 @@ class SeqChunk:
     tokens: Sequence[int]     # new token ids (1 for decode, k+1 for verify, a chunk for prefill)
     start_pos: int            # position of tokens[0]  (== KV length before this step)
     want_logits: int = 1      # how many trailing rows need logits (0 = headless prefill chunk)
+    parents: Optional[Sequence[int]] = None   # draft tree: parent row of each token within this chunk (-1 for the first,
+                                              # parents[i] < i).  Row i then sits at position start_pos + depth(i), its KV at
+                                              # slot start_pos + i, and it attends to the context plus its ancestors and itself.
 
 
 @dataclass
@@ -38,6 +41,8 @@ class StepBatch:
     logit_rows: torch.Tensor      # [R] int32 rows whose logits are wanted
     item_seq: Optional[torch.Tensor] = None   # [items] attention row-block items (None = one per sequence)
     item_q0: Optional[torch.Tensor] = None
+    tree_mask: Optional[torch.Tensor] = None  # [T] int32, set when a chunk carries a draft tree: bit j = the row may see the
+                                              # j-th new token of its sequence (causal rows: bits 0..own index)
     tiny_rows_max: int = 0        # largest q_len * group among sequences with at most TINY_ROWS rows (plain decode)
     num_tiny: int = 0
     small_rows_max: int = 0       # largest q_len * group among the other sequences handled by the decode attention kernel
@@ -62,6 +67,26 @@ class StepBatch:
         return self.max_q_len == 1
 
 
+def tree_depths(parents: Sequence[int]) -> np.ndarray:
+    """Depth of each row of a draft tree given as parent rows (-1 = the chunk's first token, depth 0)."""
+    d = np.zeros(len(parents), np.int32)
+    for i, p in enumerate(parents):
+        if p >= i:
+            raise ValueError("a draft tree lists parents before children")
+        d[i] = 0 if p < 0 else d[p] + 1
+    return d
+
+
+def tree_masks(parents: Sequence[int]) -> np.ndarray:
+    """Bit masks of a draft tree's rows: bit j of word i is set when row j is row i or one of its ancestors (at most 32 rows)."""
+    if len(parents) > 32:
+        raise ValueError("a draft tree has at most 32 rows")
+    m = np.zeros(len(parents), np.int64)
+    for i, p in enumerate(parents):
+        m[i] = (1 << i) | (0 if p < 0 else m[p])
+    return m.astype(np.uint32).view(np.int32) if len(parents) else m.astype(np.int32)
+
+
 def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device, pinned: Optional[torch.Tensor] = None,
                 pad_rows_to: int = 0, attn_group: int = 0) -> StepBatch:
     """Pack the step metadata into one int32 buffer and copy it to ``device`` once.
@@ -81,6 +106,8 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     q_start = np.zeros(B + 1, np.int32)
     ctx_len = np.zeros(B, np.int32)
     logit_rows: List[int] = []
+    has_tree = any(c.parents is not None for c in chunks)
+    tree_mask = np.zeros(Tp if has_tree else 0, np.int32)
     r = 0
     max_q = 1
     max_ctx = 0
@@ -88,7 +115,13 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
         n = len(c.tokens)
         tokens[r:r + n] = np.asarray(c.tokens, dtype=np.int64).astype(np.int32)
         pos = np.arange(c.start_pos, c.start_pos + n, dtype=np.int32)
-        positions[r:r + n] = pos
+        if c.parents is not None:
+            positions[r:r + n] = c.start_pos + tree_depths(c.parents)
+            tree_mask[r:r + n] = tree_masks(c.parents)
+        else:
+            positions[r:r + n] = pos
+            if has_tree:
+                tree_mask[r:r + n] = [-1 if j >= 31 else (2 << j) - 1 for j in range(n)]
         pages = block_table_host[c.slot, pos // PAGE]
         slot_map[r:r + n] = pages * PAGE + pos % PAGE
         seq_of_row[r:r + n] = b
@@ -121,7 +154,7 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
                 items_s.append(b)
                 items_q.append(q0)
     parts = [tokens, positions, slot_map, seq_of_row, slots, q_start, ctx_len, lr,
-             np.asarray(items_s, np.int32), np.asarray(items_q, np.int32)]
+             np.asarray(items_s, np.int32), np.asarray(items_q, np.int32), tree_mask]
     total = sum(p.size for p in parts)
     if pinned is not None and pinned.numel() >= total:
         stage = pinned[:total]
@@ -138,7 +171,7 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     v = [dev[o:o + n] for o, n in offs]
     return StepBatch(tokens=v[0], positions=v[1], slot_mapping=v[2], seq_of_row=v[3], slots=v[4], q_start=v[5],
                      ctx_len=v[6], logit_rows=v[7], item_seq=v[8] if items_s else None,
-                     item_q0=v[9] if items_s else None, h_slots=[int(s) for s in slots],
+                     item_q0=v[9] if items_s else None, tree_mask=v[10] if has_tree else None, h_slots=[int(s) for s in slots],
                      h_q_start=[int(x) for x in q_start], h_ctx_len=[int(x) for x in ctx_len],
                      h_logit_rows=logit_rows, tiny_rows_max=tiny_rows_max, num_tiny=num_tiny, small_rows_max=small_rows_max,
                      num_small=num_small, num_large=num_large, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)

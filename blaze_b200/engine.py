@@ -221,6 +221,44 @@ class Engine:
             s.length += len(toks)
         return chunks
 
+    def plan_tree(self, items: Sequence[Tuple[Seq, Sequence[int], Sequence[int]]]) -> List[SeqChunk]:
+        """items: (seq, tokens, parents) — a draft tree per sequence: ``tokens[0]`` is the last accepted token (parent -1),
+        ``tokens[i]`` a drafted token whose parent row is ``parents[i] < i``.  Every row gets logits.  Row i's KV lands at
+        slot ``length + i``; ``commit_tree`` moves the accepted path into place afterwards
+        (reference: ``Engine::verify_many_tree``, crates/blaze/src/engine.rs :1401)."""
+        if self.kv.gdn_layers:
+            raise ValueError("draft trees need a model without recurrent (linear-attention) layers")
+        group = max(self.model.cfg.num_heads // max(self.model.cfg.num_kv_heads, 1), 1)
+        chunks = []
+        for s, toks, parents in items:
+            if len(toks) != len(parents) or not toks or parents[0] >= 0:
+                raise ValueError("a draft tree needs one parent per token and a root with parent -1")
+            if len(toks) > min(32, max(64 // group, 1)):
+                raise ValueError(f"draft tree of {len(toks)} rows exceeds the verify attention's {min(32, max(64 // group, 1))}")
+            self.reserve(s, s.length + len(toks))
+            chunks.append(SeqChunk(slot=s.row, tokens=list(toks), start_pos=s.length, want_logits=len(toks),
+                                   parents=[int(p) for p in parents]))
+            s.length += len(toks)
+        return chunks
+
+    def commit_tree(self, items: Sequence[Tuple[Seq, int, Sequence[int]]]) -> None:
+        """items: (seq, length before the tree step, accepted rows) — keep the root row and the accepted path (tree row
+        indices, root excluded, in path order): their KV rows move to consecutive slots and the rest is dropped
+        (reference: ``Engine::commit_many_tree``, crates/blaze/src/engine.rs :1478)."""
+        moves = []
+        for s, base, path in items:
+            table = self.kv.block_table_host[s.row]
+            seq_moves = []
+            for k, node in enumerate(path, 1):
+                if node < k:
+                    raise ValueError("accepted rows must be a root-to-leaf path in row order")
+                a, b = base + node, base + k
+                seq_moves.append((int(table[a // PAGE]) * PAGE + a % PAGE, int(table[b // PAGE]) * PAGE + b % PAGE))
+            moves.append(seq_moves)
+        self.kv.move_rows(moves, self.model.ops)
+        for s, base, path in items:
+            self.truncate(s, base + 1 + len(path))
+
     def _bucket(self, rows: int) -> int:
         for b in self.ecfg.graph_buckets:
             if rows <= b:

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import os
 
-from typing import Dict, List, Optional
+from typing import Sequence, Dict, List, Optional
 
 import numpy as np
 import torch
@@ -135,6 +135,40 @@ class KVCache:
         for i in self.gdn_layers:
             self.conv_state[i][row].zero_()
             self.rec_state[i][row].zero_()
+
+    # ------------------------------------------------------------------ row moves (tree speculation)
+    def move_rows(self, moves: Sequence[Sequence[tuple]], ops=None) -> None:
+        """``moves[i]`` = ordered (src slot, dst slot) pairs of sequence i (flat slots: page * 16 + offset): copy the K/V
+        rows in every attention layer.  Within a sequence the pairs apply in order (a later pair may overwrite an earlier
+        pair's source); sequences share no slot.  With the CUDA op set and the kernel page layout this is one launch per
+        layer (reference: ``Model::tree_moves``, crates/blaze/src/model.rs :3387)."""
+        moves = [[(int(a), int(b)) for a, b in seq if a != b] for seq in moves]
+        moves = [m for m in moves if m]
+        if not moves:
+            return
+        D = self.cfg.head_dim
+        if self.layout == "umma" and ops is not None and getattr(ops, "is_cuda", False):
+            flat = [p for m in moves for p in m]
+            seg = np.cumsum([0] + [len(m) for m in moves])
+            src = torch.tensor([a for a, _ in flat], dtype=torch.int32, device=self.device)
+            dst = torch.tensor([b for _, b in flat], dtype=torch.int32, device=self.device)
+            segt = torch.tensor(seg.tolist(), dtype=torch.int32, device=self.device)
+            for i in self.attn_layers:
+                ops.kv_move_rows(self.kv[i], src, dst, segt, D)
+            return
+        for i in self.attn_layers:
+            for a, b in (p for m in moves for p in m):
+                sp, so, dp, do = a // PAGE, a % PAGE, b // PAGE, b % PAGE
+                if self.layout == "umma":
+                    buf = self.kv[i]
+                    H = buf.shape[1]
+                    for h in range(H):
+                        kview = buf[dp, h, 0].view(2, D // 16, 8, 16)
+                        kview[do // 8, :, do % 8] = buf[sp, h, 0].view(2, D // 16, 8, 16)[so // 8, :, so % 8].clone()
+                        buf[dp, h, 1].view(D, 16)[:, do] = buf[sp, h, 1].view(D, 16)[:, so].clone()
+                else:
+                    self.k[i][dp, :, do] = self.k[i][sp, :, so].clone()
+                    self.v[i][dp, :, do] = self.v[i][sp, :, so].clone()
 
     # ------------------------------------------------------------------ layout helpers (tests, host tier)
     @staticmethod

@@ -69,9 +69,10 @@ class CudaOps:
                                       _c.c_longlong, _c.c_int, VP]
         lib.blz_attn_tc.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                     _c.c_longlong, _c.c_longlong, _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
-        lib.blz_attn_decode.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
-                                        _c.c_longlong, _c.c_longlong, _c.c_float, _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
-                                        VP, VP, _c.c_int, VP, VP]
+        lib.blz_attn_decode_tree.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                             _c.c_longlong, _c.c_longlong, _c.c_float, _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_int,
+                                             _c.c_int, _c.c_int, VP, VP, _c.c_int, VP, VP, VP]
+        lib.blz_kv_move_rows.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_longlong, _c.c_longlong, VP]
         lib.blz_mul_sigmoid.argtypes = [VP, VP, _c.c_longlong, VP]
         lib.blz_add.argtypes = [VP, VP, VP, _c.c_longlong, VP]
         lib.blz_add_sigmoid_scaled.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
@@ -416,6 +417,11 @@ class CudaOps:
                                            int(getattr(model, "kv_rotate", False)), self._stream()), "attn_prep")
         return q, gate
 
+    def kv_move_rows(self, pool, src, dst, seg, D):
+        """Move KV rows between flat slots of one layer's pool (kernel page layout); ``seg`` = per-sequence move ranges."""
+        self._check(self.lib.blz_kv_move_rows(_ptr(pool), _ptr(src), _ptr(dst), _ptr(seg), seg.numel() - 1, pool.shape[1], D,
+                                              pool.stride(0), pool.stride(1), self._stream()), "kv_move_rows")
+
     def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0):
         """Sequences with few query rows (decode, verify) go to the decode kernel, the rest to the row-block kernel."""
         T, Hq, D = q.shape
@@ -443,11 +449,12 @@ class CudaOps:
                 n = B * Hkv * rb * sp * nmax
                 po = self._buf("attn_part_o", n * D * 4).view(torch.float32)
                 pm = self._buf("attn_part_ml", n * 2 * 4).view(torch.float32)
-            self._check(self.lib.blz_attn_decode(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
+            self._check(self.lib.blz_attn_decode_tree(_ptr(q), _ptr(out), _ptr(kv.kv[layer_idx]), _ptr(kv.block_table),
                                                  _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), B, Hq, Hkv, D,
                                                  kv.block_table.stride(0), kv.kv[layer_idx].stride(0), kv.kv[layer_idx].stride(1),
                                                  scale, 1.0, 1.0, nmax, rb, lo, hi, sp,
-                                                 _ptr(po), _ptr(pm), max_ctas, _ptr(self.attn_prof), self._stream()), "attn_decode")
+                                                 _ptr(po), _ptr(pm), max_ctas, _ptr(self.attn_prof),
+                                                 _ptr(getattr(batch, "tree_mask", None)), self._stream()), "attn_decode")
             if sp > 1:
                 self.launches += 1
         if batch.item_seq is not None:

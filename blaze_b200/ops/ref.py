@@ -138,7 +138,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     """Causal GQA attention of q ``[T, H, D]`` over the paged pools.
 
     Sequence ``b`` owns rows ``q_start[b]:q_start[b+1]``; its KV length *including* those rows is
-    ``ctx_len[b]``; row i attends to positions ``<= ctx_len - q_len + i``.
+    ``ctx_len[b]``; row i attends to positions ``<= ctx_len - q_len + i``.  With ``tree_mask`` (``[T]`` int32) row i
+    sees, among its sequence's own new tokens, only those whose bit is set in its word (a draft tree's ancestors).
     """
     T, H, D = q.shape
     KH = k_pool.shape[1]
@@ -158,6 +159,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         pos_q = torch.arange(n - ql, n, device=q.device).view(ql, 1)
         pos_k = torch.arange(n, device=q.device).view(1, n)
         mask = pos_k <= pos_q
+        if tree_mask is not None:
+            words = tree_mask[r0:r1].to(torch.int64).view(ql, 1) & 0xFFFFFFFF
+            own = ((words >> torch.arange(min(ql, 32), device=q.device).view(1, -1)) & 1).bool()      # [ql, min(ql, 32)]
+            mask = mask.clone()
+            mask[:, n - ql:n - ql + own.shape[1]] &= own
         s = s.masked_fill(~mask, float("-inf"))
         p = torch.softmax(s, dim=-1)
         o = torch.einsum("hgqn,hnd->hgqd", p, V)                               # [KH, g, ql, D]

@@ -73,7 +73,8 @@ class RefOps:
 
     def attention(self, q, model, batch, kv, layer_idx, scale):
         kl, vl = kv.logical_kv(layer_idx)
-        o = ref.paged_attention(q, kl, vl, kv.block_table, batch.h_slots, batch.h_q_start, batch.h_ctx_len, scale)
+        o = ref.paged_attention(q, kl, vl, kv.block_table, batch.h_slots, batch.h_q_start, batch.h_ctx_len, scale,
+                                tree_mask=getattr(batch, "tree_mask", None))
         return o.reshape(q.shape[0], -1)
 
     # -------------------------------------------------------------- MoE

@@ -25,6 +25,7 @@ import torch
 
 from . import log
 from .batch import PAGE, SeqChunk
+from .tree import DraftTree, merge_chains
 from .engine import Engine, OutOfPages, Seq, Snapshot
 from .sampler import Rng, SamplingParams, penalty_edits
 from .telemetry import Histogram
@@ -339,6 +340,29 @@ def ngram_propose(history: Sequence[int], k: int, min_n: int = 2, max_n: int = 4
     return []
 
 
+def ngram_propose_many(history: Sequence[int], k: int, width: int, min_n: int = 2, max_n: int = 4,
+                       window: int = 65536) -> List[List[int]]:
+    """Up to ``width`` different continuations of the suffix n-gram: the most recent occurrence first (the chain
+    ``ngram_propose`` gives), then earlier occurrences whose next token differs from the ones already taken."""
+    h = history[-window:]
+    L = len(h)
+    out: List[List[int]] = []
+    firsts = set()
+    for n in range(min(max_n, L - 1), min_n - 1, -1):
+        suf = h[L - n:]
+        for start in range(L - n - 1, -1, -1):
+            if h[start:start + n] == suf:
+                nxt = list(h[start + n:start + n + k])
+                if nxt and nxt[0] not in firsts:
+                    firsts.add(nxt[0])
+                    out.append(nxt)
+                    if len(out) >= width:
+                        return out
+        if out:
+            break                      # alternatives come from the same (longest matching) n-gram order
+    return out
+
+
 @dataclass
 class SchedConfig:
     chunk: int = 2048                  # prefill tokens per iteration
@@ -349,6 +373,7 @@ class SchedConfig:
     spec_method: str = "none"          # none | ngram | suffix | mtp | eagle
     max_draft: int = 4
     max_verify: int = 8
+    draft_tree_width: int = 1          # > 1: n-gram drafts branch into up to this many continuations, verified as a tree
     eos_ids: Tuple[int, ...] = ()
     max_model_len: int = 4096
     # "interleave": every step takes all decoding requests plus at most one prefill chunk (steady token flow for running
@@ -703,8 +728,9 @@ class Scheduler:
             drafts = self._draft(decoders)
         for a in decoders:
             d = drafts.get(id(a), [])
-            plan.append((a, [a.tokens[-1]] + d, 1 + len(d), d))
-            budget -= 1 + len(d)
+            drafted = d.token[1:] if isinstance(d, DraftTree) else d
+            plan.append((a, [a.tokens[-1]] + list(drafted), 1 + len(drafted), d))
+            budget -= 1 + len(drafted)
         chunk_left = min(cfg.chunk, max(budget, 0))
         dec_ids = {id(a) for a in decoders}
         for a in self.active:
@@ -747,7 +773,12 @@ class Scheduler:
                     return
         for a, toks, _, _ in plan:
             a.seq.length = a.computed            # plan() advances from here
-        chunks = eng.plan(items)
+        chunks = []
+        for (a, toks, want, d) in plan:
+            if isinstance(d, DraftTree):
+                chunks += eng.plan_tree([(a.seq, toks, d.parent)])
+            else:
+                chunks += eng.plan([(a.seq, toks, want)])
         want_any = any(w for _, _, w, _ in plan)
         need_logits = any(w and (a.req.params.needs_candidates() or a.req.constraint is not None or a.req.embed_only)
                           for a, _, w, _ in plan)
@@ -869,6 +900,31 @@ class Scheduler:
             new: List[int] = []
             lps: List[dict] = []
             accepted = 0
+            if isinstance(draft, DraftTree):
+                # walk from the root: sample the row of the current node, follow the child that drafted that token
+                node, path = 0, []
+                while True:
+                    if host_tokens is not None:
+                        tok, lp = host_tokens[row + node], None
+                    else:
+                        tok, lp = self._sample(a, logits[row + node], new)
+                    new.append(tok)
+                    if lp is not None:
+                        lps.append(lp)
+                    node = next((c for c in draft.children(node) if draft.token[c] == tok), None)
+                    if node is None:
+                        break
+                    path.append(node)
+                row += want
+                depth = max((draft.depth(i) for i in range(len(draft.token))), default=0)
+                a.acc.record(depth, len(path))
+                self.stats.draft_tokens += len(draft.token) - 1
+                self.stats.accepted_tokens += len(path)
+                base = a.computed - len(toks)
+                eng.commit_tree([(a.seq, base, path)])       # accepted rows move into place, the other branches go
+                a.computed = base + 1 + len(path)
+                self._append(a, new, lps)
+                continue
             for j in range(want):
                 if a.forced:
                     tok, lp = a.forced.popleft(), None
@@ -919,11 +975,22 @@ class Scheduler:
         want = self.cost.choose([a.acc for a in decoders], maxd)
         out: Dict[int, List[int]] = {}
         if cfg.spec_method == "ngram":
+            eng = self.engine
+            group = max(eng.model.cfg.num_heads // max(eng.model.cfg.num_kv_heads, 1), 1)
+            tree_rows = min(32, max(64 // group, 1)) if (cfg.draft_tree_width > 1 and not eng.kv.gdn_layers) else 0
             for a, k in zip(decoders, want):
-                if k > 0:
+                if k <= 0:
+                    continue
+                if tree_rows > 2:
+                    chains = ngram_propose_many(a.tokens, k, cfg.draft_tree_width)
+                    if len(chains) > 1:
+                        out[id(a)] = merge_chains(chains, tree_rows)
+                        continue
+                    d = chains[0] if chains else []
+                else:
                     d = ngram_propose(a.tokens, k)
-                    if d:
-                        out[id(a)] = d
+                if d:
+                    out[id(a)] = d
         elif cfg.spec_method == "suffix" and self.suffix is not None:
             for a, k in zip(decoders, want):
                 if k > 0:

@@ -74,3 +74,18 @@ def accept_walk(tree: DraftTree, chosen: Sequence[int]) -> Tuple[List[int], List
 def ranked(cands: Sequence[Tuple[int, float]], k: int) -> List[int]:
     """Top-k candidate ids by score, lower id first among equals."""
     return [i for i, _ in sorted(cands, key=lambda c: (-c[1], c[0]))[:k]]
+
+
+def merge_chains(chains: Sequence[Sequence[int]], max_nodes: int = 32) -> DraftTree:
+    """Draft tree of several candidate continuations: chains that start alike share their common rows."""
+    tree = DraftTree()
+    for chain in chains:
+        node = 0
+        for tok in chain:
+            nxt = next((c for c in tree.children(node) if tree.token[c] == tok), None)
+            if nxt is None:
+                if len(tree.token) >= max_nodes:
+                    break
+                nxt = tree.add(node, int(tok))
+            node = nxt
+    return tree

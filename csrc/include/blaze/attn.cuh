@@ -26,6 +26,7 @@ struct AttnParams {
   int row_blocks;              // decode kernel: row blocks of NMAX rows per (sequence, kv head)
   long long* prof;             // optional [blocks][16] wait-cycle counters (null = off)
   int* status;
+  const int* tree_mask = nullptr;   // decode kernel, verify rows: [T] bit j = this row may see the sequence's j-th new token
 };
 
 

@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ float s_c[2][NMAX];
   __shared__ int s_pos[2][NMAX];
+  __shared__ uint32_t s_mask[2][NMAX];   // tree verify: which of the sequence's new tokens a row may see (bit per token)
   __shared__ float s_wmax[Cfg::NB][4][NMAX];
   __shared__ float s_l[2][4][RMAX];                  // [set][warp][row] partial row sums
   __shared__ float s_m[RMAX];                        // set 1's row maxima
@@ -179,6 +180,7 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
         if (part == 0) {
           s_c[qb][rr] = p.scale_log2 * qscale;
           s_pos[qb][rr] = live ? ctx - qlen + tq : -1;
+          if constexpr (RMAX > 4) s_mask[qb][rr] = (live && p.tree_mask) ? (uint32_t)p.tree_mask[r0 + tq] : 0xFFFFFFFFu;
         }
         fence_async_smem();
         __syncwarp();
@@ -313,7 +315,13 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
 #pragma unroll
         for (int r = 0; r < RMAX; ++r) {
           if (r >= nrows) break;
-          x[r] = key <= s_pos[qb][r] ? __uint_as_float(v[r]) * s_c[qb][r] : -INFINITY;
+          bool vis = key <= s_pos[qb][r];
+          if constexpr (RMAX > 4) {
+            // tree verify: among the sequence's own new tokens (keys from ctx - qlen on) a row sees its ancestors only
+            const int j = key - (ctx - qlen);
+            if (vis && j >= 0) vis = (s_mask[qb][r] >> j) & 1u;
+          }
+          x[r] = vis ? __uint_as_float(v[r]) * s_c[qb][r] : -INFINITY;
           const float wm = warp_max_redux(x[r]);
           if (lane == 0) s_wmax[sb][qd][r] = wm;
         }
@@ -470,11 +478,14 @@ static cudaError_t launch_decode(const AttnParams& p, int max_ctas, cudaStream_t
 // Decode / verify attention for every sequence with min_rows <= q_len * (Hq / Hkv) <= max_rows.
 // nmax: 16 or 32 rows per work item; row_blocks = ceil(max rows of any processed sequence / nmax).
 // Scratch for splits > 1: part_o = B*Hkv*row_blocks*splits*nmax*128 floats, part_ml = ...*nmax*2 floats.
-BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
+// tree_mask (optional, [T] int32, indexed like q's rows): bit j of row i's word = row i may attend to the j-th new token
+// of its sequence (itself and its ancestors in a draft tree; at most 32 new tokens per sequence).  Null = causal rows.
+// Plain decode work items (at most 4 live rows per KV head) ignore it: a single new token sees only itself.
+BLZ_API int blz_attn_decode_tree(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
                             const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride, long long page_stride, long long head_stride,
                             float scale, float k_scale, float v_scale, int nmax, int row_blocks, int min_rows,
                             int max_rows, int splits, float* part_o, float* part_ml, int max_ctas, long long* prof,
-                            cudaStream_t stream) {
+                            const int* tree_mask, cudaStream_t stream) {
   using namespace blz;
   if (num_seqs <= 0) return 0;
   if (D != 128 || Hq % Hkv || (nmax != 16 && nmax != 32) || row_blocks < 1 || splits < 1 ||
@@ -491,11 +502,22 @@ BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const in
   p.tokens_per_block = 0; p.min_rows = min_rows; p.max_rows = max_rows; p.row_blocks = row_blocks;
   p.status = status_word();
   p.prof = prof;
+  p.tree_mask = tree_mask;
   if (nmax == 32) return (int)launch_decode<32, 32>(p, max_ctas, stream);
   const int live = max_rows < 16 ? max_rows : 16;     // most live rows of any work item
-  if (live <= 4) return (int)launch_decode<16, 4>(p, max_ctas, stream);
+  if (live <= 4 && !tree_mask) return (int)launch_decode<16, 4>(p, max_ctas, stream);
   if (live <= 8) return (int)launch_decode<16, 8>(p, max_ctas, stream);
   return (int)launch_decode<16, 16>(p, max_ctas, stream);
+}
+
+BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const int* block_table, const int* slots,
+                            const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride, long long page_stride, long long head_stride,
+                            float scale, float k_scale, float v_scale, int nmax, int row_blocks, int min_rows,
+                            int max_rows, int splits, float* part_o, float* part_ml, int max_ctas, long long* prof,
+                            cudaStream_t stream) {
+  return blz_attn_decode_tree(q, out, pool, block_table, slots, q_start, ctx_len, num_seqs, Hq, Hkv, D, bt_stride, page_stride,
+                              head_stride, scale, k_scale, v_scale, nmax, row_blocks, min_rows, max_rows, splits, part_o, part_ml,
+                              max_ctas, prof, nullptr, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------------

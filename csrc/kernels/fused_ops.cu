@@ -760,6 +760,39 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
   return (int)cudaGetLastError();
 }
 
+namespace blz {
+// Copy the K and V rows of KV slot src[m] to slot dst[m] in every KV head of one layer's pool (page layout of the
+// attention kernels: K as 8-row x 16-byte core matrices, V transposed).  Used after a draft tree has been verified: the
+// accepted path's rows move down to consecutive positions.  Moves seg[i] .. seg[i+1]-1 belong to sequence i and run in
+// list order inside one CTA (a later move may overwrite the source of an earlier one: row 2 -> 1, then row 5 -> 2);
+// different sequences never share a slot.  Reference: blz_move_rows (kernels/src/cuda/tree.cu :142).
+__global__ void kv_move_rows_kernel(uint8_t* pool, const int* __restrict__ src, const int* __restrict__ dst,
+                                    const int* __restrict__ seg, int D, long long page_stride, long long head_stride) {
+  for (int m = seg[blockIdx.x]; m < seg[blockIdx.x + 1]; ++m) {
+    const int s = src[m], d = dst[m];
+    if (s != d && s >= 0 && d >= 0) {
+      const uint8_t* sb = pool + (size_t)(s >> 4) * page_stride + (size_t)blockIdx.y * head_stride;
+      uint8_t* db = pool + (size_t)(d >> 4) * page_stride + (size_t)blockIdx.y * head_stride;
+      const int st = s & 15, dt = d & 15;
+      for (int c = threadIdx.x; c < D / 16; c += blockDim.x)
+        *reinterpret_cast<uint4*>(db + (dt >> 3) * 8 * D + c * 128 + (dt & 7) * 16) =
+            *reinterpret_cast<const uint4*>(sb + (st >> 3) * 8 * D + c * 128 + (st & 7) * 16);
+      for (int i = threadIdx.x; i < D; i += blockDim.x) db[16 * D + i * 16 + dt] = sb[16 * D + i * 16 + st];
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace blz
+BLZ_API int blz_kv_move_rows(void* pool, const int* src, const int* dst, const int* seg, int num_seqs, int Hkv, int D,
+                             long long page_stride, long long head_stride, cudaStream_t s) {
+  if (num_seqs <= 0) return 0;
+  if (D % 16 || Hkv <= 0 || page_stride <= 0 || head_stride <= 0 || page_stride % 16 || head_stride % 16)
+    return (int)cudaErrorInvalidValue;
+  blz::kv_move_rows_kernel<<<dim3(num_seqs, Hkv), 128, 0, s>>>((uint8_t*)pool, src, dst, seg, D, page_stride, head_stride);
+  return (int)cudaGetLastError();
+}
+
 BLZ_API int blz_mul_sigmoid(void* x, const void* gate, long long n, cudaStream_t s) {
   if (n == 0) return 0;
   mul_sigmoid_kernel<<<(int)((n + 1023) / 1024 > 4096 ? 4096 : (n + 1023) / 1024), 256, 0, s>>>((bf16*)x, (const bf16*)gate, (size_t)n);

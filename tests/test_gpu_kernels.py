@@ -234,7 +234,7 @@ class _A:
     pass
 
 
-def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False):
+def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=None):
     """Write random K/V through the prep kernel, then compare attention with the oracle over the same FP8 cache."""
     from blaze_b200.batch import SeqChunk, build_batch
     from blaze_b200.config import ModelConfig, RopeConfig, inv_freq
@@ -267,7 +267,7 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False):
             if phase == 0 and pre > 0:
                 chunks.append(SeqChunk(b, [0] * pre, 0))
             elif phase == 1:
-                chunks.append(SeqChunk(b, [0] * qlens[b], pre))
+                chunks.append(SeqChunk(b, [0] * qlens[b], pre, parents=parents[b] if parents else None))
         if not chunks:
             continue
         batch = build_batch(chunks, kv.block_table_host, DEV, attn_group=Hq // Hkv)
@@ -283,7 +283,8 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False):
             torch.cuda.synchronize()
             assert ops.take_status() == 0
             kl, vl = kv.logical_kv(0)
-            want = ref.paged_attention(qr, kl, vl, kv.block_table, batch.h_slots, batch.h_q_start, batch.h_ctx_len, D ** -0.5)
+            want = ref.paged_attention(qr, kl, vl, kv.block_table, batch.h_slots, batch.h_q_start, batch.h_ctx_len, D ** -0.5,
+                                       tree_mask=batch.tree_mask)
             outs = (o.view(T, Hq, D), want)
             # the cache itself: the newest token of sequence 0 must round-trip
             s0 = chunks[0]

@@ -1,5 +1,6 @@
 """BASELINE config 1: tiny Qwen3-architecture decoder on CPU fp32 through the engine's paged path,
 checked against a from-scratch dense recomputation (no KV cache, no paging)."""
+import pytest
 import torch
 
 from blaze_b200.config import named_config
@@ -87,3 +88,48 @@ def test_kv_rotation_keeps_the_output():
                   max_model_len=128)
         outs.append(llm.generate([[5, 6, 7, 8, 9, 10, 11], [40, 41, 42]], SamplingParams(max_tokens=12, temperature=0.0)))
     assert [o.token_ids for o in outs[0]] == [o.token_ids for o in outs[1]]
+
+
+def test_draft_tree_rows_match_their_chains_and_commit_compacts_the_path():
+    """A draft tree verified in one step: every node's logits equal those of its root-to-node chain run on its own, and
+    after ``commit_tree`` the sequence continues as if only the accepted path had ever been fed."""
+    from blaze_b200.config import named_config
+    from blaze_b200.engine import Engine, EngineConfig
+    from blaze_b200.models.qwen3 import Model
+    from blaze_b200.quant import Format
+    cfg = named_config("tiny")
+    model = Model.random_init(cfg, Format.DENSE, 0, "cpu", torch.float32)
+    eng = Engine(model, EngineConfig(max_seqs=8, max_model_len=128, kv_dtype="fp32", kv_tokens=1024, use_graphs=False))
+    prompt = list(range(7, 30))                       # 23 tokens: the tree straddles a page boundary
+    toks = [100, 201, 202, 301, 302, 303]             # root, two children, then 301 under 201, 302 and 303 under 202
+    parents = [-1, 0, 0, 1, 2, 2]
+
+    def chain_logits(path_tokens):
+        s = eng.open_from()
+        eng.forward(eng.plan([(s, prompt, 0)]), "none")
+        out = eng.forward(eng.plan([(s, path_tokens, len(path_tokens))]), "logits")
+        return s, out
+
+    seq = eng.open_from()
+    eng.forward(eng.plan([(seq, prompt, 0)]), "none")
+    base = seq.length
+    tree_logits = eng.forward(eng.plan_tree([(seq, toks, parents)]), "logits")
+    assert tree_logits.shape[0] == len(toks) and seq.length == base + len(toks)
+    for node in range(len(toks)):
+        path, i = [], node
+        while i >= 0:
+            path.append(i)
+            i = parents[i]
+        path = path[::-1]
+        s, want = chain_logits([toks[i] for i in path])
+        assert torch.allclose(tree_logits[node], want[-1], atol=2e-4), node
+        eng.close(s)
+    # accept root -> 202 -> 303 (rows 2 and 5), then decode one more token
+    eng.commit_tree([(seq, base, [2, 5])])
+    assert seq.length == base + 3
+    nxt = eng.forward(eng.plan([(seq, [400], 1)]), "logits")
+    s, _ = chain_logits([100, 202, 303])
+    want = eng.forward(eng.plan([(s, [400], 1)]), "logits")
+    assert torch.allclose(nxt, want, atol=2e-4)
+    with pytest.raises(ValueError):
+        eng.plan_tree([(seq, [1, 2], [0, 0])])
