@@ -182,7 +182,8 @@ def build_llm(ns: argparse.Namespace):
               chunk=ns.chunk or 2048, enable_prefix_caching=not ns.disable_prefix_caching,
               cache_slots=ns.prompt_cache_slots or 4, use_graphs=not ns.no_graphs,
               spec_method=ns.spec_method or "none", max_draft=min(ns.max_verify - 1, 8), seed=ns.seed,
-              kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"), kv_rotate=bool(getattr(ns, "kv_rotate", False)))
+              kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"), kv_rotate=bool(getattr(ns, "kv_rotate", False)),
+              draft_tree_width=int(getattr(ns, "draft_tree_width", 1) or 1))
     if group is not None and ns.comm == "fused" and device.startswith("cuda"):
         from .parallel.symm import SymmAllReduce
         group.fused = SymmAllReduce.create(group, device, max_rows=(ns.chunk or 2048) + (ns.max_seqs or 256) + 64,

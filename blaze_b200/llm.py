@@ -42,7 +42,8 @@ class LLM:
                  max_model_len: int = 4096, chunk: int = 2048, enable_prefix_caching: bool = True, cache_slots: int = 4,
                  use_graphs: bool = True, spec_method: str = "none", max_draft: int = 4, seed: int = 0,
                  eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192, warm_graphs: bool = False,
-                 kv_host_tokens: int = 0, schedule: str = "interleave", kv_rotate: bool = False):
+                 kv_host_tokens: int = 0, schedule: str = "interleave", kv_rotate: bool = False,
+                 draft_tree_width: int = 1):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -69,6 +70,7 @@ class LLM:
         eos = tuple(eos_ids) or tuple(cfg.eos_token_ids)
         self.sched = Scheduler(self.engine, SchedConfig(chunk=chunk, max_seqs=max_seqs, prefix_cache=enable_prefix_caching,
                                                         cache_slots=cache_slots, spec_method=spec_method, max_draft=max_draft,
+                                                        draft_tree_width=draft_tree_width,
                                                         eos_ids=eos, max_model_len=max_model_len,
                                                         max_step_tokens=max_step_tokens, kv_host_pages=kv_host_tokens // 16, schedule=schedule),
                                drafter=drafter)

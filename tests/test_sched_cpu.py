@@ -277,3 +277,24 @@ def test_drafter_with_reduced_vocabulary_stays_exact():
     got = llm.generate(ps, sp)
     assert [o.token_ids for o in got] == want
     assert d.proposed > 0 and d.draft_head.N == len(range(0, 1024, 3))
+
+
+def test_ngram_tree_speculation_is_exact():
+    """With branching n-gram drafts (several continuations of the same suffix, verified as one tree) greedy and seeded
+    sampled outputs stay those of plain decoding, and some branch rows are accepted."""
+    from blaze_b200.sched import ngram_propose_many
+    from blaze_b200.tree import merge_chains
+    assert ngram_propose_many([1, 2, 7, 7, 1, 2, 8, 8, 1, 2], 2, 3) == [[8, 8], [7, 7]]
+    t = merge_chains([[5, 6, 7], [5, 9], [4]])
+    assert t.token[1:] == [5, 6, 7, 9, 4] and t.parent == [-1, 0, 1, 2, 1, 0]
+    # a history where "3 4" continues in two ways keeps offering a two-branch tree
+    rep = [3, 4, 5, 6, 3, 4, 9, 6] * 5
+    ps = [rep, _prompts(1, 30, seed=4)[0], [3, 4, 5, 3, 4, 7, 3, 4, 5, 3, 4]]
+    for sp in (SamplingParams(temperature=0.0, max_tokens=24), SamplingParams(temperature=0.7, top_k=8, seed=11, max_tokens=16)):
+        want = [o.token_ids for o in _llm().generate(ps, sp)]
+        spec = _llm(spec_method="ngram", draft_tree_width=3)
+        got = spec.generate(ps, sp)
+        assert [o.token_ids for o in got] == want
+        if sp.temperature == 0.0:
+            assert spec.sched.stats.draft_tokens > 0
+    assert spec.engine.pages.free_count > 0
