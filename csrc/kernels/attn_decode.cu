@@ -98,6 +98,8 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
     *abort_flag = 0;
     mbar_fence_init();
   }
+  for (int i = threadIdx.x; i < 2 * Cfg::Q_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
   if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -139,8 +141,14 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
       const int npages = (kv_end + 15) >> 4;
       if (n > 0) {
         // ---- this item's Q rows → e4m3 in the K-major core-matrix layout, plus the per-row constants
-        constexpr int LPR = 32 / NMAX == 0 ? 1 : 32 / NMAX;        // lanes per row (2 for NMAX 16, 1 for NMAX 32)
+        // Plain decode items (at most 4 live rows) are prepared by the K half of the warp alone, 4 lanes per row: the
+        // two halves then never meet, and this half moves on to the next item's Q rows and K tiles while the V half is
+        // still waiting for ring slots of this one.  (Rows 4..15 of both Q buffers are zeroed once, before the loop.)
+        constexpr bool HALF = RMAX <= 4;
+        constexpr int LPR = HALF ? 4 : (32 / NMAX == 0 ? 1 : 32 / NMAX);   // lanes per row (2 for NMAX 16, 1 for NMAX 32)
         constexpr int DPL = D / LPR;                               // dims per lane
+        constexpr uint32_t QMASK = HALF ? 0x0000FFFFu : 0xFFFFFFFFu;
+        if (!HALF || lane < 16) {
         const int qb = item_it & 1;
         const int rr = lane / LPR, part = lane % LPR;
         const int R = row0 + rr;
@@ -159,7 +167,8 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
             for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(bf2f(e[k])));
           }
         }
-        if (LPR == 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        if (LPR >= 2) amax = fmaxf(amax, __shfl_xor_sync(QMASK, amax, 1));
+        if (LPR == 4) amax = fmaxf(amax, __shfl_xor_sync(QMASK, amax, 2));
         const float qscale = fmaxf(amax, 1e-12f) / 448.f;
         const float qinv = 1.f / qscale;
         if (!TW(10, &q_empty[qb], ((item_it >> 1) & 1) ^ 1)) break;
@@ -183,11 +192,13 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
           if constexpr (RMAX > 4) s_mask[qb][rr] = (live && p.tree_mask) ? (uint32_t)p.tree_mask[r0 + tq] : 0xFFFFFFFFu;
         }
         fence_async_smem();
-        __syncwarp();
+        __syncwarp(QMASK);
         if (lane == 0) mbar_arrive(&q_full[qb]);
+        }
       }
       // The lower half of the warp streams K tiles, the upper half V^T tiles: the two rings are released at different
-      // times (K after S^T = K Q^T, V two tiles later after O^T = V^T P^T), so each half waits only for its own ring.
+      // times (K after S^T = K Q^T, V two tiles later after O^T = V^T P^T), so each half waits only for its own ring
+      // (and, for plain decode items, runs through the work items at its own pace).
       // (the page number of the next tile is fetched before the wait for its ring slot, off the critical path)
       if (lane < 16) {
         int page = 0;
@@ -225,7 +236,7 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
           page = next;
         }
       }
-      __syncwarp();
+      if constexpr (RMAX > 4) __syncwarp();
     } else if (warp == 1) {
       // -------------------------------------------------------------- MMA issuer
       if (lane == 0 && n > 0) {
