@@ -141,11 +141,12 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
       const int npages = (kv_end + 15) >> 4;
       if (n > 0) {
         // ---- this item's Q rows → e4m3 in the K-major core-matrix layout, plus the per-row constants
-        // Plain decode items (at most 4 live rows) are prepared by the K half of the warp alone, 4 lanes per row: the
-        // two halves then never meet, and this half moves on to the next item's Q rows and K tiles while the V half is
-        // still waiting for ring slots of this one.  (Rows 4..15 of both Q buffers are zeroed once, before the loop.)
-        constexpr bool HALF = RMAX <= 4;
-        constexpr int LPR = HALF ? 4 : (32 / NMAX == 0 ? 1 : 32 / NMAX);   // lanes per row (2 for NMAX 16, 1 for NMAX 32)
+        // Items of at most 8 live rows (plain decode at group 4 or 8, two verify rows) are prepared by the K half of the
+        // warp alone, 4 or 2 lanes per row: the two halves then never meet, and this half moves on to the next item's Q
+        // rows and K tiles while the V half is still waiting for ring slots of this one.  (The rows beyond RMAX of both Q
+        // buffers are zeroed once, before the loop.)
+        constexpr bool HALF = RMAX <= 8;
+        constexpr int LPR = RMAX <= 4 ? 4 : RMAX <= 8 ? 2 : (32 / NMAX == 0 ? 1 : 32 / NMAX);   // lanes per row
         constexpr int DPL = D / LPR;                               // dims per lane
         constexpr uint32_t QMASK = HALF ? 0x0000FFFFu : 0xFFFFFFFFu;
         if (!HALF || lane < 16) {
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
           page = next;
         }
       }
-      if constexpr (RMAX > 4) __syncwarp();
+      if constexpr (RMAX > 8) __syncwarp();
     } else if (warp == 1) {
       // -------------------------------------------------------------- MMA issuer
       if (lane == 0 && n > 0) {

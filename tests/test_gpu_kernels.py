@@ -299,6 +299,7 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=Non
 @pytest.mark.parametrize("Hq,Hkv,ctxs,qlens", [
     (8, 2, [40], [1]),
     (32, 8, [1024, 300, 129, 17], [1, 1, 1, 1]),
+    (16, 2, [513, 100, 31], [1, 1, 1]),      # plain decode at group 8 (8 rows per KV head)
     (8, 2, [200, 96], [200, 96]),            # pure prefill
     (8, 1, [700, 64, 333], [5, 64, 77]),     # verify rows + chunked prefill with history
     (4, 4, [300], [150]),                    # MHA (group 1)
