@@ -1,4 +1,5 @@
 """Scheduler / LLM API on CPU: batching, chunked prefill, prefix cache, preemption, n-gram speculation exactness."""
+import pytest
 import torch
 
 from blaze_b200.config import named_config
@@ -298,3 +299,20 @@ def test_ngram_tree_speculation_is_exact():
         if sp.temperature == 0.0:
             assert spec.sched.stats.draft_tokens > 0
     assert spec.engine.pages.free_count > 0
+
+
+def test_tree_rows_in_the_step_batch():
+    """Depth positions, row-order KV slots and ancestor bit masks of a draft tree; causal masks for the other rows."""
+    import numpy as np
+    from blaze_b200.batch import SeqChunk, build_batch, tree_depths, tree_masks
+    parents = [-1, 0, 0, 1, 2, 2]
+    assert tree_depths(parents).tolist() == [0, 1, 1, 2, 2, 2]
+    assert [int(m) & 0xFFFFFFFF for m in tree_masks(parents)] == [0b1, 0b11, 0b101, 0b1011, 0b10101, 0b100101]
+    table = np.arange(1, 9, dtype=np.int32).reshape(2, 4)
+    b = build_batch([SeqChunk(0, [9] * 6, 14, want_logits=6, parents=parents), SeqChunk(1, [7, 8], 3, want_logits=2)], table, "cpu")
+    assert b.positions.tolist() == [14, 15, 15, 16, 16, 16, 3, 4]
+    assert b.slot_mapping.tolist() == [1 * 16 + 14, 1 * 16 + 15, 2 * 16, 2 * 16 + 1, 2 * 16 + 2, 2 * 16 + 3, 5 * 16 + 3, 5 * 16 + 4]
+    assert b.tree_mask.tolist() == [0b1, 0b11, 0b101, 0b1011, 0b10101, 0b100101, 0b1, 0b11]
+    assert build_batch([SeqChunk(1, [7, 8], 3)], table, "cpu").tree_mask is None
+    with pytest.raises(ValueError):
+        tree_depths([-1, 1])
