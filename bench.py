@@ -188,9 +188,17 @@ def main():
     host_tok = [torch.empty(B, dtype=torch.int64, pin_memory=True) for _ in range(2)]
     zeros = [0] * B
 
+    host_ev = [None, None]
+
     def decode_step_fed(k):
+        # the host stays at most one step ahead of the GPU, as the scheduler's run-ahead loop does: before step k is
+        # issued, the token copy of step k-2 (same pinned buffer) must have landed
+        if host_ev[k & 1] is not None:
+            host_ev[k & 1].synchronize()
         out = eng.forward(eng.plan([(seqs[j], zeros[j:j + 1], 1) for j in range(B)]), "greedy", feedback=True)
         host_tok[k & 1].copy_(out, non_blocking=True)
+        host_ev[k & 1] = torch.cuda.Event()
+        host_ev[k & 1].record()
         return out
 
     for _ in range(max(W, 3)):

@@ -419,6 +419,7 @@ class _Graph:
         self.static = torch.zeros(self.total, dtype=torch.int32, device=dev)
         # two staging buffers: with token feedback the host may fill step k+1 while the copy of step k is still queued
         self.stages = [torch.zeros(self.total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.stage_ev = [None, None]      # recorded after the copy out of each stage; waited on before that stage is refilled
         self.turn = 0
         o = 0
         v = []
@@ -446,6 +447,10 @@ class _Graph:
         n, B = self.bucket, len(chunks)
         self.turn ^= 1
         stage = self.stages[self.turn]
+        ev = self.stage_ev[self.turn]
+        if ev is not None:
+            # the copy queued from this stage two fills ago may not have run yet when the host runs far ahead of the GPU
+            ev.synchronize()
         s = stage.numpy()
         bt = self.eng.kv.block_table_host
         tok = np.fromiter((c.tokens[0] for c in chunks), np.int32, B)
@@ -471,6 +476,9 @@ class _Graph:
         else:
             self.static.copy_(stage, non_blocking=True)
             self.eng.h2d_bytes += self.total * 4
+        ev = torch.cuda.Event()
+        ev.record()
+        self.stage_ev[self.turn] = ev
         return B
 
     def replay(self, chunks: Sequence[SeqChunk], feedback: bool = False):

@@ -11,12 +11,13 @@
 //
 // How: the partial outputs and (max, sum) pairs live in ONE file-scope `static __device__ __align__(256)` array of
 // BLZ_ATTN_NOALLOC_SCRATCH_BYTES (16.5 MiB); every GPU that loads the library holds it until the process exits.
-// The first call on a device looks the array's device address up (cudaGetSymbolAddress) and configures the kernel's
-// shared-memory limit; make that first call outside of any stream capture.  Later calls on that device only launch.
+// The first call on a device (under a lock, so threads may race to it) looks the array's device address up
+// (cudaGetSymbolAddress) and sets the kernel's shared-memory limit for that device; make that first call outside of any
+// stream capture.  Later calls on that device only launch.
 // The function never calls cudaMalloc / cudaFree or any allocating library routine.
 //
-// Limits: seqs * kv_heads * row_blocks * splits * 16 rows of 130 floats must fit the array, otherwise the call returns
-// cudaErrorInvalidValue and `blz_attn_decode_noalloc_error()` explains what was too large.  All calls share the array:
+// Limits: seqs * kv_heads * row_blocks * splits * 16 rows of 130 floats must fit the array, and row_blocks * 16 must cover
+// max_rows; otherwise the call returns cudaErrorInvalidValue and `blz_attn_decode_noalloc_error()` explains what was too large.  All calls share the array:
 // it keeps the last call's contents (nothing in it has to start at zero — every slot that is read is written first by
 // the same call), and two calls that overlap on the GPU (different streams, or concurrent graphs) race on it.
 #pragma once
@@ -34,6 +35,11 @@ int blz_attn_decode_noalloc(const void* q, void* out, const void* pool, const in
                             const int* q_start, const int* ctx_len, int num_seqs, int Hq, int Hkv, int D, int bt_stride,
                             long long page_stride, long long head_stride, float scale, float k_scale, float v_scale, int row_blocks, int min_rows, int max_rows, int splits,
                             int max_ctas, cudaStream_t stream);
+
+// The kernels' waits are bounded; one that runs out records 1 in a status word inside the library instead of hanging, and
+// the call's output is then not valid.  This reads and clears that word for the current device (0 = fine, -1 = no call was
+// made on this device yet).  It synchronises the device, so call it between steps, not per launch.  Allocates nothing.
+int blz_attn_decode_noalloc_status(void);
 
 // Text of the last size / set-up error of this thread ("" when the last call succeeded).
 const char* blz_attn_decode_noalloc_error(void);

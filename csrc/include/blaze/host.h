@@ -47,14 +47,36 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// SM count of the current device (cached per device: a process may drive several GPUs).
 inline int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  static int n[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!n[dev]) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    n[dev] = v;
   }
-  return n;
+  return n[dev];
 }
+
+// cudaFuncSetAttribute applies to the current device only: remember per device whether a kernel has been configured.
+// One instance per kernel instantiation (a function-local static of the launcher).
+struct PerDeviceOnce {
+  bool done[64] = {false};
+  // Sets the dynamic shared-memory limit of `kernel` on the current device the first time it is launched there.
+  template <typename K>
+  cudaError_t smem_limit(K kernel, int bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done[dev] = true;   // idempotent: two threads racing here both set the same value
+    return e;
+  }
+};
 
 }  // namespace blz

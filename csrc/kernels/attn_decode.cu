@@ -330,8 +330,9 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
           bool vis = key <= s_pos[qb][r];
           if constexpr (RMAX > 4) {
             // tree verify: among the sequence's own new tokens (keys from ctx - qlen on) a row sees its ancestors only
+            // (a word covers the first 32 new tokens; plain causal rows - no tree mask - may be longer and are not masked)
             const int j = key - (ctx - qlen);
-            if (vis && j >= 0) vis = (s_mask[qb][r] >> j) & 1u;
+            if (vis && p.tree_mask != nullptr && j >= 0 && j < 32) vis = (s_mask[qb][r] >> j) & 1u;
           }
           x[r] = vis ? __uint_as_float(v[r]) * s_c[qb][r] : -INFINITY;
           const float wm = warp_max_redux(x[r]);
@@ -470,11 +471,10 @@ __global__ void attn_decode_combine_kernel(AttnParams p) {
 template <int NMAX, int RMAX>
 static cudaError_t launch_decode(const AttnParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = DecCfg<NMAX, RMAX>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NMAX, RMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  static PerDeviceOnce configured;
+  {
+    cudaError_t e = configured.smem_limit(attn_decode_kernel<NMAX, RMAX>, Cfg::SMEM);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   const int total = p.num_items * p.Hkv * p.row_blocks * p.splits;
   const int cap = Cfg::CTAS_PER_SM * sm_count();
@@ -503,6 +503,8 @@ BLZ_API int blz_attn_decode_tree(const void* q, void* out, const void* pool, con
   if (D != 128 || Hq % Hkv || (nmax != 16 && nmax != 32) || row_blocks < 1 || splits < 1 ||
       (splits > 1 && (!part_o || !part_ml)))
     return (int)cudaErrorInvalidValue;
+  // every processed sequence has at most max_rows rows per kv head: the row blocks must cover them, or rows would be skipped
+  if (max_rows < (1 << 29) && (long long)row_blocks * nmax < max_rows) return (int)cudaErrorInvalidValue;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
   p.page_stride = page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D;
@@ -535,6 +537,7 @@ BLZ_API int blz_attn_decode(const void* q, void* out, const void* pool, const in
 // ------------------------------------------------------------------------------------------------------------------
 // Allocation-free variant (see blaze/attn_noalloc.h): the split-KV partials live in a library-owned device array.
 #include <cstdio>
+#include <mutex>
 
 #include "blaze/attn_noalloc.h"
 
@@ -549,8 +552,28 @@ struct NoAllocDev {
   int* status = nullptr;
 };
 NoAllocDev g_noalloc_dev[64];
+std::mutex g_noalloc_mu;          // guards the first-call set-up of a device
 thread_local char g_noalloc_err[256] = "";
 }  // namespace
+
+// Reads and clears the status word that blz_attn_decode_noalloc's kernels report into on the current device (0 = fine,
+// 1 = a bounded wait inside the kernel ran out and the call's output is not valid).  Synchronises the device; returns -1
+// when no call has been made on this device yet or the copy fails.  Allocates nothing.
+extern "C" __attribute__((visibility("default"))) int blz_attn_decode_noalloc_status(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_dev[dev].ready) return -1;
+  }
+  int h = 0;
+  if (cudaMemcpyFromSymbol(&h, g_noalloc_status, sizeof(int)) != cudaSuccess) return -1;
+  if (h != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_noalloc_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+  }
+  return h;
+}
 
 extern "C" __attribute__((visibility("default"))) const char* blz_attn_decode_noalloc_error(void) { return g_noalloc_err; }
 
@@ -572,6 +595,11 @@ extern "C" __attribute__((visibility("default"))) int blz_attn_decode_noalloc(
              Hkv, row_blocks, splits);
     return (int)cudaErrorInvalidValue;
   }
+  if (max_rows < (1 << 29) && (long long)row_blocks * 16 < max_rows) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "row_blocks %d x 16 rows do not cover max_rows %d: rows would be skipped",
+             row_blocks, max_rows);
+    return (int)cudaErrorInvalidValue;
+  }
   const long long need = blz_attn_decode_noalloc_bytes(num_seqs, Hkv, row_blocks, splits);
   if (splits > 1 && need > (long long)BLZ_ATTN_NOALLOC_SCRATCH_BYTES) {
     snprintf(g_noalloc_err, sizeof(g_noalloc_err),
@@ -587,6 +615,7 @@ extern "C" __attribute__((visibility("default"))) int blz_attn_decode_noalloc(
     return (int)(e != cudaSuccess ? e : cudaErrorInvalidDevice);
   }
   NoAllocDev& d = g_noalloc_dev[dev];
+  std::unique_lock<std::mutex> setup_lock(g_noalloc_mu);
   if (!d.ready) {
     // first call on this device, with this device current: resolve the device addresses of the library-owned arrays.
     // In host code the array names are host-side stand-ins, never device pointers.
@@ -602,6 +631,7 @@ extern "C" __attribute__((visibility("default"))) int blz_attn_decode_noalloc(
     d.status = reinterpret_cast<int*>(p_status);
     d.ready = true;
   }
+  setup_lock.unlock();
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
   p.page_stride = page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D;

@@ -386,11 +386,10 @@ BLZ_API int blz_attn_tc(const void* q, void* out, const void* pool, const int* b
   p.tokens_per_block = 128 / (Hq / Hkv);
   p.status = status_word();
   p.min_rows = 0; p.max_rows = 1 << 30; p.row_blocks = 1; p.prof = nullptr;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<128>::SMEM);
+  static PerDeviceOnce configured;
+  {
+    cudaError_t e = configured.smem_limit(attn_tc_kernel<128>, AttnCfg<128>::SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
   }
   const int total = num_items * Hkv * splits;
   int grid = total < sm_count() ? total : sm_count();

@@ -431,11 +431,10 @@ static cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
                           cudaStream_t stream) {
   using Cfg = GemmCfg<KIND, BN>;
   auto kern = gemm_tc_kernel<KIND, BN, OUT_F32>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  static PerDeviceOnce configured;
+  {
+    cudaError_t e = configured.smem_limit(kern, Cfg::SMEM);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
   int grid = tiles < sm_count() ? tiles : sm_count();
@@ -468,6 +467,18 @@ struct AmaxArgs {
 };
 thread_local AmaxArgs g_amax;
 }  // namespace
+
+namespace blz {
+// The one-shot arming (fused all-reduce, peer wait, arg-max epilogue) applies to exactly one GEMM call of this thread.
+// Any GEMM entry point clears it on entry; an entry that cannot honour it reports whether something was armed.
+bool gemm_oneshot_take_unsupported() {
+  const bool armed = g_fuse.mc_out != nullptr || g_wait.pad != nullptr || g_amax.val != nullptr;
+  g_fuse.mc_out = nullptr;
+  g_wait.pad = nullptr;
+  g_amax.val = nullptr; g_amax.idx = nullptr;
+  return armed;
+}
+}  // namespace blz
 
 // Arms the NEXT blz_gemm_tc call (fp32 output form, bn 128) on this thread as a greedy head: instead of writing the
 // logits it records, per 128-column tile and row, the largest value and its column in val / idx ([ceil(N/128)][M]);
@@ -516,6 +527,13 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
                         const void* sfa, const void* sfb, int out_f32, int bn, int max_ctas, const int* tile_expert,
                         int num_experts, int b_kt, int act, cudaStream_t stream) {
   using namespace blz;
+  // snapshot and clear the one-shot arming first: an early return below must not leave it armed for an unrelated GEMM
+  const FuseArgs fuse = g_fuse;
+  const WaitArgs wait = g_wait;
+  const AmaxArgs amax = g_amax;
+  g_fuse.mc_out = nullptr;
+  g_wait.pad = nullptr;
+  g_amax.val = nullptr; g_amax.idx = nullptr;
   if (M <= 0 || N <= 0 || K <= 0 || kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
   const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
   if (K % kmma) return (int)cudaErrorInvalidValue;
@@ -538,19 +556,16 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   if (act && (out_f32 || N % 32 || (ldc & 7) || tile_expert)) return (int)cudaErrorInvalidValue;
   if (b_kt > 0 && tile_expert) return (int)cudaErrorInvalidValue;
   p.mc_out = nullptr; p.done_ctr = nullptr; p.epoch = nullptr; p.spin_limit = 0; p.rank = 0; p.world = 1;
-  p.wait_pad = g_wait.pad; p.wait_epoch = g_wait.epoch; p.wait_world = g_wait.world;
-  p.wait_limit = g_wait.limit;
-  g_wait.pad = nullptr;           // one-shot
-  p.amax_val = g_amax.val; p.amax_idx = g_amax.idx;
-  g_amax.val = nullptr; g_amax.idx = nullptr;
+  p.wait_pad = wait.pad; p.wait_epoch = wait.epoch; p.wait_world = wait.world;
+  p.wait_limit = wait.limit;
+  p.amax_val = amax.val; p.amax_idx = amax.idx;
   if (p.amax_val && (!out_f32 || tile_expert)) return (int)cudaErrorInvalidValue;
   if (p.amax_val) bn = 128;
-  if (g_fuse.mc_out) {
+  if (fuse.mc_out) {
     if (out_f32 || (N % 32)) return (int)cudaErrorInvalidValue;
-    p.mc_out = g_fuse.mc_out; p.done_ctr = g_fuse.done_ctr; p.epoch = g_fuse.epoch; p.spin_limit = g_fuse.spin_limit;
-    p.rank = g_fuse.rank; p.world = g_fuse.world;
-    for (int r = 0; r < g_fuse.world; ++r) p.peer_pad[r] = g_fuse.peer_pad[r];
-    g_fuse.mc_out = nullptr;      // one-shot: applies to this launch only
+    p.mc_out = fuse.mc_out; p.done_ctr = fuse.done_ctr; p.epoch = fuse.epoch; p.spin_limit = fuse.spin_limit;
+    p.rank = fuse.rank; p.world = fuse.world;
+    for (int r = 0; r < fuse.world; ++r) p.peer_pad[r] = fuse.peer_pad[r];
   }
   const uint64_t b_rows = (uint64_t)N * (tile_expert ? (num_experts > 0 ? num_experts : 1) : 1);
   if (tile_expert && N % bn) return (int)cudaErrorInvalidValue;

@@ -24,6 +24,8 @@
 
 namespace blz {
 
+bool gemm_oneshot_take_unsupported();   // gemm_tc.cu
+
 struct WideParams {
   int lanes_total;            // rows of the lane operand (tokens when plain, features when swapped)
   int cols_total;             // rows of the column operand
@@ -415,11 +417,10 @@ static cudaError_t launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, c
                                cudaStream_t stream) {
   using Cfg = WideCfg<KIND, BN>;
   auto kern = gemm_wide_kernel<KIND, BN, SWAP>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  static PerDeviceOnce configured;
+  {
+    cudaError_t e = configured.smem_limit(kern, Cfg::SMEM);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   int grid = units < sm_count() ? units : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
@@ -452,6 +453,8 @@ BLZ_API int blz_gemm_wide(int kind, const void* X, long long ldx, const void* W,
                           const void* sfw, int out_f32, int swap, int ksplit, void* ws, long long ws_bytes, void* ctr,
                           int max_ctas, int w_kt, int act, cudaStream_t stream) {
   using namespace blz;
+  // this kernel has no fused all-reduce / peer-wait / arg-max epilogue: a call armed for one is refused (and disarmed)
+  if (gemm_oneshot_take_unsupported()) return (int)cudaErrorNotSupported;
   if (M <= 0 || N <= 0 || K <= 0 || kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
   const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
   if (K % kmma) return (int)cudaErrorInvalidValue;

@@ -125,10 +125,15 @@ bool parse_file(Dir& d, int fi, std::string& err) {
       ps.eat(',');
     }
     ps.eat(',');
-    int64_t n = 1;
-    for (int64_t s : t.shape) n *= s;
+    if (t.shape.size() > 8) { err = f.path + ": tensor " + t.name + " has more than 8 dimensions"; return false; }
     const int es = dtype_size(t.dtype);
-    if (!es || t.end - t.begin != n * es || f.data_off + t.end > f.size) { err = f.path + ": tensor " + t.name + " has inconsistent offsets"; return false; }
+    int64_t n = es;
+    bool sane = es > 0 && t.begin >= 0 && t.begin <= t.end;
+    for (int64_t s : t.shape) {
+      // every dimension is bounded by the file size, and the running product is checked for overflow
+      if (s < 0 || __builtin_mul_overflow(n, s, &n)) { sane = false; break; }
+    }
+    if (!sane || t.end - t.begin != n || t.end > f.size - f.data_off) { err = f.path + ": tensor " + t.name + " has inconsistent offsets"; return false; }
     d.tensors.push_back(std::move(t));
   }
   if (!ps.ok) { err = f.path + ": malformed header"; return false; }
@@ -166,7 +171,11 @@ extern "C" void* blz_st_open(const char* dir, char* err, int err_len) {
     f.path = std::string(dir) + "/" + names[i];
     f.fd = open(f.path.c_str(), O_RDONLY);
     struct stat st;
-    if (f.fd < 0 || fstat(f.fd, &st) != 0 || st.st_size < 8) { blz_st_close(d); return fail(f.path + ": cannot open"); }
+    if (f.fd < 0 || fstat(f.fd, &st) != 0 || st.st_size < 8) {
+      if (f.fd >= 0) close(f.fd);       // not yet owned by d->files
+      blz_st_close(d);
+      return fail(f.path + ": cannot open");
+    }
     f.size = st.st_size;
     d->files.push_back(f);
     if (!parse_file(*d, (int)i, e)) { blz_st_close(d); return fail(e); }
