@@ -24,6 +24,8 @@ class SeqChunk:
     tokens: Sequence[int]     # new token ids (1 for decode, k+1 for verify, a chunk for prefill)
     start_pos: int            # position of tokens[0]  (== KV length before this step)
     want_logits: int = 1      # how many trailing rows need logits (0 = headless prefill chunk)
+    defer_state: bool = False # recurrent (GDN) layers read this sequence's state but do not store the advanced state:
+                              # the rows are speculative and the accepted prefix is replayed afterwards (Engine.commit_state)
     parents: Optional[Sequence[int]] = None   # draft tree: parent row of each token within this chunk (-1 for the first,
                                               # parents[i] < i).  Row i then sits at position start_pos + depth(i), its KV at
                                               # slot start_pos + i, and it attends to the context plus its ancestors and itself.
@@ -41,6 +43,8 @@ class StepBatch:
     logit_rows: torch.Tensor      # [R] int32 rows whose logits are wanted
     item_seq: Optional[torch.Tensor] = None   # [items] attention row-block items (None = one per sequence)
     item_q0: Optional[torch.Tensor] = None
+    gdn_defer: Optional[torch.Tensor] = None  # [B] int32, set when a chunk defers its recurrent state: 1 = do not store
+    h_gdn_defer: Optional[List[int]] = None
     tree_mask: Optional[torch.Tensor] = None  # [T] int32, set when a chunk carries a draft tree: bit j = the row may see the
                                               # j-th new token of its sequence (causal rows: bits 0..own index)
     tiny_rows_max: int = 0        # largest q_len * group among sequences with at most TINY_ROWS rows (plain decode)
@@ -153,8 +157,10 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
             for q0 in range(0, len(c.tokens), tpb):
                 items_s.append(b)
                 items_q.append(q0)
+    has_defer = any(c.defer_state for c in chunks)
+    defer = np.asarray([1 if c.defer_state else 0 for c in chunks] if has_defer else [], np.int32)
     parts = [tokens, positions, slot_map, seq_of_row, slots, q_start, ctx_len, lr,
-             np.asarray(items_s, np.int32), np.asarray(items_q, np.int32), tree_mask]
+             np.asarray(items_s, np.int32), np.asarray(items_q, np.int32), tree_mask, defer]
     total = sum(p.size for p in parts)
     if pinned is not None and pinned.numel() >= total:
         stage = pinned[:total]
@@ -171,7 +177,8 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     v = [dev[o:o + n] for o, n in offs]
     return StepBatch(tokens=v[0], positions=v[1], slot_mapping=v[2], seq_of_row=v[3], slots=v[4], q_start=v[5],
                      ctx_len=v[6], logit_rows=v[7], item_seq=v[8] if items_s else None,
-                     item_q0=v[9] if items_s else None, tree_mask=v[10] if has_tree else None, h_slots=[int(s) for s in slots],
+                     item_q0=v[9] if items_s else None, tree_mask=v[10] if has_tree else None,
+                     gdn_defer=v[11] if has_defer else None, h_gdn_defer=[int(x) for x in defer] if has_defer else None, h_slots=[int(s) for s in slots],
                      h_q_start=[int(x) for x in q_start], h_ctx_len=[int(x) for x in ctx_len],
                      h_logit_rows=logit_rows, tiny_rows_max=tiny_rows_max, num_tiny=num_tiny, small_rows_max=small_rows_max,
                      num_small=num_small, num_large=num_large, num_rows=Tp, max_q_len=max_q, max_ctx=max_ctx, h2d_bytes=total * 4)

@@ -117,11 +117,12 @@ def bench_gemm(a):
     x = torch.randn(a.m, a.k, device="cuda").bfloat16()
     xin = ops.quantize_rows(x, lin0) if ops._qmode(lin0) else x
     wide = {"auto": None, "on": True, "off": False}[a.wide]
+    sk = None if a.sk == "auto" else (False if a.sk == "off" else (True if a.sk == "on" else int(a.sk)))
     out = torch.empty(a.m, a.n, dtype=torch.float32 if a.f32 else torch.bfloat16, device="cuda")
 
     def run():
         for lin in lins:
-            ops.linear(lin, xin, out=out, bn=a.bn, wide=wide, ksplit=a.ksplit, out_dtype=torch.float32 if a.f32 else None)
+            ops.linear(lin, xin, out=out, bn=a.bn, wide=wide, ksplit=a.ksplit, out_dtype=torch.float32 if a.f32 else None, sk=sk)
 
     run()
     torch.cuda.synchronize()
@@ -132,7 +133,7 @@ def bench_gemm(a):
     med, best = med / copies, best / copies
     flops = 2.0 * a.m * a.n * a.k
     pk = peaks()
-    print(json.dumps({"kernel": f"gemm {a.kind}", "m": a.m, "n": a.n, "k": a.k, "bn": a.bn, "wide": a.wide, "ksplit": a.ksplit,
+    print(json.dumps({"kernel": f"gemm {a.kind}", "m": a.m, "n": a.n, "k": a.k, "bn": a.bn, "wide": a.wide, "ksplit": a.ksplit, "sk": a.sk,
                       "copies": copies, "us_median": med * 1e3, "us_best": best * 1e3,
                       "tflops": flops / med / 1e9, "x_bf16_cublas_" + pk["src"]: flops / med / 1e9 / pk["bf16_tflops"],
                       "weight_gbs": wbytes / med / 1e6, "x_hbm_" + pk["src"]: wbytes / med / 1e6 / pk["hbm_gbs"],
@@ -176,6 +177,7 @@ def main(argv=None):
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--wide", default="auto", choices=["auto", "on", "off"])
     p.add_argument("--ksplit", type=int, default=0)
+    p.add_argument("--sk", default="auto", help="cluster split-K kernel: auto | on | off | a K-slice count 1..8")
     p.add_argument("--f32", action="store_true")
     p.add_argument("--iters", type=int, default=10)
     p = sub.add_parser("norm")

@@ -61,6 +61,9 @@ def engine_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--draft-tree-width", type=int, default=1)
     g.add_argument("--draft-tree-depth", type=int, default=None)
     g.add_argument("--no-graphs", action="store_true")
+    g.add_argument("--tune", action="store_true",
+                   help="time the GEMM kernel variants for this model's layer shapes at start-up (cached per device under "
+                        "~/.cache/blaze_b200) and route each linear layer to the measured winner")
     g.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--device", default=None)
@@ -162,7 +165,7 @@ def build_llm(ns: argparse.Namespace):
     spec_defaults(ns)
     device = ns.device or ("cuda" if torch.cuda.is_available() else "cpu")
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if ns.tp > 1 and world != ns.tp:
+    if ns.tp > 1 and world != ns.tp * max(getattr(ns, "pp", 1), 1):
         raise SystemExit(f"--tp {ns.tp}: launch one process per GPU, e.g. python -m torch.distributed.run "
                          f"--nproc-per-node {ns.tp} --master-addr 127.0.0.1 -m blaze_b200 …")
     group = None
@@ -175,7 +178,13 @@ def build_llm(ns: argparse.Namespace):
     tp = TPInfo(group.rank, group.world, group, ep=ns.ep) if group else TPInfo()
     kv = ns.kv_cache_dtype or "auto"
     if kv.startswith("nvfp4"):
-        kv = "fp8"     # 4-bit KV pools are not built; FP8 pages are the compact format here
+        raise SystemExit(f"--kv-cache-dtype {kv}: 4-bit KV pages are not built; use fp8 (the compact format here), bf16 or fp32")
+    if getattr(ns, "kv_host", False):
+        raise SystemExit("--kv-host (live sequences in pinned host memory) is not built; --kv-host-tokens N gives the prefix "
+                         "cache a pinned-host tier of N tokens")
+    if getattr(ns, "pp", 1) > 1 and world != ns.pp * max(ns.tp, 1):
+        raise SystemExit(f"--pp {ns.pp} --tp {ns.tp}: launch {ns.pp * max(ns.tp, 1)} processes (one per GPU), e.g. python -m "
+                         f"torch.distributed.run --nproc-per-node {ns.pp * max(ns.tp, 1)} --master-addr 127.0.0.1 -m blaze_b200 …")
     kv_tokens = 0 if str(ns.kv_tokens) == "auto" else int(ns.kv_tokens)
     llm = LLM(ns.model or "tiny", weight_format=ns.weights or "dense", device=device, tp=tp, kv_cache_dtype=kv,
               kv_tokens=kv_tokens, max_seqs=ns.max_seqs or 256, max_model_len=ns.max_model_len or 4096,
@@ -183,7 +192,9 @@ def build_llm(ns: argparse.Namespace):
               cache_slots=ns.prompt_cache_slots or 4, use_graphs=not ns.no_graphs,
               spec_method=ns.spec_method or "none", max_draft=min(ns.max_verify - 1, 8), seed=ns.seed,
               kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"), kv_rotate=bool(getattr(ns, "kv_rotate", False)),
-              draft_tree_width=int(getattr(ns, "draft_tree_width", 1) or 1))
+              draft_tree_width=int(getattr(ns, "draft_tree_width", 1) or 1),
+              tune=bool(getattr(ns, "tune", False)), draft_model=getattr(ns, "draft_model", None), draft_head_vocab=int(getattr(ns, "mtp_head_vocab", 0) or 0),
+              draft_tree_depth=int(ns.draft_tree_depth or 4), max_verify=int(ns.max_verify or 8))
     if group is not None and ns.comm == "fused" and device.startswith("cuda"):
         from .parallel.symm import SymmAllReduce
         group.fused = SymmAllReduce.create(group, device, max_rows=(ns.chunk or 2048) + (ns.max_seqs or 256) + 64,

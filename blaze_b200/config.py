@@ -256,6 +256,15 @@ def named_config(name: str) -> ModelConfig:
     if n in ("tiny", "tiny-qwen3"):
         c = ModelConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
                         intermediate_size=512, rope=RopeConfig(theta=1e6))
+    elif n in ("tiny-hybrid",):
+        # two Gated DeltaNet layers and two gated-attention layers with a small MoE: the Qwen3-Next layer pattern in miniature
+        c = ModelConfig(architecture="Qwen3NextForCausalLM", model_type="qwen3_next", vocab_size=1024, hidden_size=256,
+                        num_layers=4, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=512, num_experts=8,
+                        num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=128,
+                        linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=64,
+                        linear_conv_kernel_dim=4, attn_output_gate=True, zero_centered_norm=True,
+                        rope=RopeConfig(theta=1e6, partial_rotary_factor=0.25))
+        c.layer_types = ["linear_attention", "full_attention", "linear_attention", "full_attention"]
     elif n in ("qwen3-8b",):
         c = ModelConfig(vocab_size=151936, hidden_size=4096, num_layers=36, num_heads=32, num_kv_heads=8,
                         head_dim=128, intermediate_size=12288, rope=RopeConfig(theta=1e6))

@@ -27,6 +27,17 @@ class OutOfPages(RuntimeError):
     pass
 
 
+class DeviceStepError(RuntimeError):
+    """A kernel of the step reported a failure through the device status word (a bounded wait ran out: a peer rank that
+    never raised its flag, a pipeline that stalled).  The step's results are not valid; the context stays usable."""
+
+    def __init__(self, code: int):
+        names = {1: "an in-kernel barrier wait ran out", 2: "a peer rank's flag never arrived", 3: "bad kernel argument",
+                 4: "a bounded device buffer overflowed"}
+        super().__init__(f"device status {code}: {names.get(code, 'unknown error')}")
+        self.code = code
+
+
 class PageAllocator:
     """Ref-counted 16-token pages.  Page 0 is reserved as the scratch target of padded rows."""
 
@@ -127,9 +138,20 @@ class Engine:
         self._pinned_ev = [None, None]
         self._pin_turn = 0
         self._last_greedy = None            # output of the last greedy decode step (source of token feedback)
+        self._deferred: Dict[int, Tuple[int, int, int]] = {}   # slot -> (first row, first position, rows) of the last deferring step
         self.attn_group = 0
         if model.ops.is_cuda:
             self.attn_group = max(max(cfg.num_heads // tpw, 1) // max(cfg.num_kv_heads // tpw, 1), 1)
+        # Device status word, watched without a synchronisation of its own: after every step a 4-byte copy into this pinned
+        # word is queued behind the step's kernels; whoever takes the step's results (and has synchronised for that)
+        # calls check_status().  `status_source` replaces the device word in tests.
+        self._status_host = None
+        if self.device.type == "cuda" and model.ops.is_cuda:
+            self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self.status_source = None
+        self.status_errors = 0
+        self.hangs = 0
+        self._watchdog: Optional[threading.Thread] = None
         self.steps = 0
         self.last_step_started = 0.0
         self.last_step_what = ""
@@ -212,14 +234,34 @@ class Engine:
         s.length = length
 
     # ================================================================== stepping
-    def plan(self, items: Sequence[Tuple[Seq, Sequence[int], int]]) -> List[SeqChunk]:
-        """items: (seq, new tokens, rows wanting logits).  Reserves pages and advances lengths."""
+    def plan(self, items: Sequence[Tuple[Seq, Sequence[int], int]], defer_state: bool = False) -> List[SeqChunk]:
+        """items: (seq, new tokens, rows wanting logits).  Reserves pages and advances lengths.  ``defer_state``: the rows
+        are speculative — models with recurrent layers leave those sequences' state as it was, and ``commit_state`` advances
+        it over the accepted rows afterwards."""
         chunks = []
+        defer = bool(defer_state and self.kv.gdn_layers)
         for s, toks, want in items:
             self.reserve(s, s.length + len(toks))
-            chunks.append(SeqChunk(slot=s.row, tokens=list(toks), start_pos=s.length, want_logits=want))
+            chunks.append(SeqChunk(slot=s.row, tokens=list(toks), start_pos=s.length, want_logits=want, defer_state=defer))
             s.length += len(toks)
         return chunks
+
+    def commit_state(self, items: Sequence[Tuple[Seq, int]]) -> None:
+        """items: (seq, rows kept) for sequences of the last step that ran with ``defer_state``: advance their recurrent
+        state over the first ``rows kept`` rows of that step (the accepted tokens), reading the inputs the layers recorded
+        (reference: ``Model::pre_verify`` / ``commit_replay``, crates/blaze/src/model.rs:3364, :3484)."""
+        if not self.kv.gdn_layers or not items:
+            return
+        chunks, rows = [], []
+        for s, keep in items:
+            r0, p0, n = self._deferred[s.row]
+            if keep < 1 or keep > n:
+                raise ValueError("rows kept must be between 1 and the rows of the deferred step")
+            chunks.append(SeqChunk(slot=s.row, tokens=[0] * keep, start_pos=p0, want_logits=0))
+            rows += list(range(r0, r0 + keep))
+        batch = build_batch(chunks, self.kv.block_table_host, self.device, None)
+        self.h2d_bytes += batch.h2d_bytes
+        self.model.gdn_replay(batch, torch.tensor(rows, dtype=torch.int32, device=self.device), self.kv)
 
     def plan_tree(self, items: Sequence[Tuple[Seq, Sequence[int], Sequence[int]]]) -> List[SeqChunk]:
         """items: (seq, tokens, parents) — a draft tree per sequence: ``tokens[0]`` is the last accepted token (parent -1),
@@ -275,6 +317,12 @@ class Engine:
         self.last_step_started = time.monotonic()
         self.last_step_what = f"{mode} rows={sum(len(c.tokens) for c in chunks)} seqs={len(chunks)}"
         decode_only = all(len(c.tokens) == 1 for c in chunks)
+        if any(c.defer_state for c in chunks):
+            self._deferred, r = {}, 0
+            for c in chunks:
+                if c.defer_state:
+                    self._deferred[c.slot] = (r, c.start_pos, len(c.tokens))
+                r += len(c.tokens)
         graphable = (self.ecfg.use_graphs and self.device.type == "cuda" and decode_only and mode == "greedy"
                      and self.model.is_first_stage and self.model.is_last_stage and self.model.ops.is_cuda)
         try:
@@ -289,6 +337,8 @@ class Engine:
                 out = self._run(batch, mode, hidden_in)
             if mode == "greedy" and decode_only:
                 self._last_greedy = out
+            if self._status_host is not None:
+                self.model.ops.status_peek(self._status_host)
         finally:
             self.steps += 1
             self.last_step_started = 0.0
@@ -388,15 +438,36 @@ class Engine:
         """Kernels of this library inside one captured decode step (the largest captured bucket)."""
         return max((g.kernels for g in self._graphs.values()), default=0)
 
-    # ================================================================== watchdog
+    # ================================================================== failure detection
+    def check_status(self) -> None:
+        """Raise ``DeviceStepError`` when a kernel of a step whose results the caller has just synchronised with reported a
+        failure.  The word is cleared, so the next step starts clean (the reference fails the step's requests and keeps
+        serving: ``crates/blaze/src/sched.rs:1067-1075``)."""
+        if self.status_source is not None:
+            code = int(self.status_source())
+        elif self._status_host is not None:
+            code = int(self._status_host[0])
+            if code:
+                self.model.ops.take_status()          # clear the device word (synchronises; this is the error path)
+                self._status_host[0] = 0
+        else:
+            return
+        if code:
+            self.status_errors += 1
+            raise DeviceStepError(code)
+
     def start_watchdog(self, on_hang=None) -> threading.Thread:
         """Report (never kill) a step that runs longer than ``hang_secs`` (``engine.rs:582-656``)."""
+        if self._watchdog is not None and self._watchdog.is_alive():
+            return self._watchdog
+
         def loop():
             while True:
                 time.sleep(min(self.ecfg.hang_secs / 4, 1.0))
                 t0 = self.last_step_started
                 if t0 and time.monotonic() - t0 > self.ecfg.hang_secs:
                     msg = f"engine hang: step {self.steps} ({self.last_step_what}) running {time.monotonic() - t0:.1f}s"
+                    self.hangs += 1
                     if on_hang:
                         on_hang(msg)
                     else:
@@ -405,6 +476,7 @@ class Engine:
                     self.last_step_started = 0.0
         th = threading.Thread(target=loop, name="blaze-watchdog", daemon=True)
         th.start()
+        self._watchdog = th
         return th
 
 

@@ -24,6 +24,7 @@ class Health:
         self.mean_s = 0.0
         self.steps = 0
         self.outliers = 0
+        self.errors = 0                 # steps that failed (device status, sampler, model exception)
         self.last_tick = time.monotonic()
         self.tokens_since_tick = 0
         self.steps_since_tick = 0

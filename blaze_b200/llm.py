@@ -43,7 +43,8 @@ class LLM:
                  use_graphs: bool = True, spec_method: str = "none", max_draft: int = 4, seed: int = 0,
                  eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192, warm_graphs: bool = False,
                  kv_host_tokens: int = 0, schedule: str = "interleave", kv_rotate: bool = False,
-                 draft_tree_width: int = 1):
+                 draft_tree_width: int = 1, draft_model: Optional[str] = None, draft_head_vocab: int = 0,
+                 draft_tree_depth: int = 4, watchdog: bool = False, max_verify: int = 8, tune: bool = False):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -60,6 +61,11 @@ class LLM:
             else:
                 self.model = Model.random_init(named_config(model), fmt, seed, self.device, dtype, tpi)
         cfg = self.model.cfg
+        if tune and self.model.ops.is_cuda:
+            # time the GEMM kernel variants of this model's layer shapes once per device (cached on disk) and route by the result
+            from .tune import tune_model
+            with log.Stage("tune"):
+                tune_model(self.model, rows=sorted({min(max_seqs, 256), min(max_seqs, 64)}))
         if kv_cache_dtype == "auto":
             kv_cache_dtype = "fp8" if (self.device.type == "cuda" and self.model.ops.is_cuda) else \
                 ("fp32" if dtype == torch.float32 else "bf16")
@@ -68,9 +74,18 @@ class LLM:
                                                           kv_dtype=kv_cache_dtype, chunk=chunk, use_graphs=use_graphs,
                                                           kv_rotate=kv_rotate))
         eos = tuple(eos_ids) or tuple(cfg.eos_token_ids)
+        if drafter is None and spec_method in ("mtp", "eagle", "dflash"):
+            from .models.drafter import build_drafter
+            with log.Stage("drafter"):
+                drafter = build_drafter(self.model, spec_method, model if isinstance(model, str) else None, draft_model,
+                                        max_seqs, max_model_len, draft_head_vocab, seed + 7, draft_tree_width, draft_tree_depth)
+        self.drafter = drafter
+        if watchdog:
+            self.engine.start_watchdog()
         self.sched = Scheduler(self.engine, SchedConfig(chunk=chunk, max_seqs=max_seqs, prefix_cache=enable_prefix_caching,
                                                         cache_slots=cache_slots, spec_method=spec_method, max_draft=max_draft,
-                                                        draft_tree_width=draft_tree_width,
+                                                        draft_tree_width=draft_tree_width, max_verify=max_verify,
+                                                        draft_tree_depth=draft_tree_depth,
                                                         eos_ids=eos, max_model_len=max_model_len,
                                                         max_step_tokens=max_step_tokens, kv_host_pages=kv_host_tokens // 16, schedule=schedule),
                                drafter=drafter)

@@ -235,3 +235,54 @@ def kind_of(architectures: Sequence[str]) -> str:
     if "DFlash" in a:
         return "dflash"
     return "mtp"
+
+
+def build_drafter(target: Model, method: str, model_dir: Optional[str] = None, draft_model: Optional[str] = None,
+                  max_seqs: int = 256, max_model_len: int = 4096, head_vocab: int = 0, seed: int = 7,
+                  tree_width: int = 1, tree_depth: int = 4):
+    """The drafter a serving configuration asks for (``--spec-method mtp|eagle|dflash``, ``--draft-model DIR``,
+    ``--mtp-head-vocab N``), built next to the target (reference: the serve flow of ``crates/blaze/src/main.rs:933-947`` and
+    ``Drafter`` dispatch by architecture in ``drafter.rs:26``).
+
+    * ``mtp``: the ``mtp.*`` tensors of the target's own checkpoint; a random-init head for random-init targets.
+    * ``eagle`` / ``dflash``: a separate checkpoint directory (``draft_model``) whose ``architectures`` decide the kind; a
+      random-init drafter of that kind when no directory is given (benchmarks, tests).
+    ``head_vocab`` > 0 drafts over the first ``head_vocab`` token ids only (a reduced head)."""
+    import json
+    import os
+    kv_dtype = "bf16" if target.dtype != torch.float32 else "fp32"
+    if target.ops.is_cuda:
+        kv_dtype = "fp8"
+    d = None
+    if method == "mtp":
+        has_mtp = False
+        if model_dir and os.path.isdir(model_dir):
+            from ..weights import Checkpoint
+            ck = Checkpoint.open(model_dir)
+            has_mtp = "mtp.fc.weight" in ck or "mtp.fc.weight_packed" in ck
+            if has_mtp:
+                d = ChainDrafter.load_mtp(target, ck, max_seqs, max_model_len, kv_dtype)
+            else:
+                raise ValueError(f"--spec-method mtp: {model_dir} has no mtp.* tensors")
+        else:
+            d = ChainDrafter.random_init(target, seed, max_seqs, max_model_len, kv_dtype)
+    elif method in ("eagle", "dflash"):
+        kind = method
+        if draft_model:
+            with open(os.path.join(draft_model, "config.json")) as fh:
+                kind = kind_of(json.load(fh).get("architectures", []))
+            if kind == "mtp":
+                kind = method
+        cls = EagleDrafter if kind == "eagle" else DFlashDrafter
+        if draft_model:
+            d = cls.load(target, draft_model, max_seqs, max_model_len, kv_dtype)
+        else:
+            d = cls.random_init(target, seed, max_seqs, max_model_len, kv_dtype)
+        if kind == "eagle":
+            d.tree_width, d.tree_depth = max(int(tree_width), 1), max(int(tree_depth), 1)
+    else:
+        raise ValueError(f"unknown drafter kind {method!r}")
+    if head_vocab and head_vocab < target.cfg.vocab_size:
+        d.use_draft_vocab(range(head_vocab))
+    target.capture_layers = sorted(set(target.capture_layers) | set(d.capture_layers))
+    return d

@@ -166,6 +166,7 @@ class Model:
         self.gdn_chunked = False
         self.capture_layers: List[int] = []                   # hidden states kept for drafters
         self.captured: Dict[int, torch.Tensor] = {}
+        self.gdn_records: Dict[int, tuple] = {}               # per GDN layer: inputs of the last step that deferred state
         self.weight_format = Format.DENSE
 
     @property
@@ -567,8 +568,28 @@ class Model:
         nz = G.v_heads * dv
         mixed, z = proj[:, :nq], proj[:, nq:nq + nz]
         b, a = proj[:, nq + nz:nq + nz + G.v_heads], proj[:, nq + nz + G.v_heads:]
+        if batch.gdn_defer is not None:
+            # speculative rows: keep what the recurrence consumed, so that the accepted prefix can be replayed
+            # (the reference's verify records, crates/blaze/src/model.rs:1322, :3364)
+            self.gdn_records[gi] = (mixed, b, a)
         o = ops.gdn(mixed, z, b, a, G, self, batch, kv, gi)
         return self._row_cut(G.out_proj, o, o.shape[0], fused)
+
+    def gdn_replay(self, batch: StepBatch, rows: torch.Tensor, kv: KVCache) -> None:
+        """Advance the recurrent state of every GDN layer over ``rows`` (indices into the recorded step's rows, grouped by
+        sequence as ``batch`` describes) — the accepted prefix of a verify step whose state update was deferred
+        (reference: ``commit_replay``, crates/blaze/src/model.rs:3484)."""
+        idx = rows.long()
+        for li, L in enumerate(self.layers):
+            gi = self.first_layer + li
+            if L.gdn is None:
+                continue
+            rec = self.gdn_records.get(gi)
+            if rec is None:
+                raise RuntimeError("no deferred step to replay")
+            mixed, b, a = rec
+            ba = torch.stack([b[idx], a[idx]]).contiguous()      # one buffer: the kernels take a common row stride
+            self.ops.gdn(mixed[idx].contiguous(), None, ba[0], ba[1], L.gdn, self, batch, kv, gi, state_only=True)
 
     def _mlp(self, M, h, fused=None):
         """Returns (output, kind) with kind as in :meth:`forward`."""

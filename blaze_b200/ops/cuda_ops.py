@@ -55,6 +55,16 @@ class CudaOps:
         lib.blz_gemm_wide.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
                                       _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP, _c.c_longlong, VP,
                                       _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_gemm_sk.restype = _c.c_int
+        lib.blz_gemm_sk.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
+                                    _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_gemm_sk_default_ks.restype = _c.c_int
+        lib.blz_gemm_sk_default_ks.argtypes = [_c.c_int] * 4
+        # decode-sized GEMMs (few output tiles) take the cluster split-K kernel; BLAZE_GEMM_SK=0 keeps them on the
+        # one-CTA-per-tile kernel (A/B timing)
+        self._sk_ok = os.environ.get("BLAZE_GEMM_SK", "1") != "0"
+        self.SK_MAX_ROWS = 512
+        self.tuning = None         # optional tune.Tuning: per-shape kernel choices measured on this device
         lib.blz_gemm_wide_ksplit.restype = _c.c_int
         lib.blz_gemm_wide_ksplit.argtypes = [_c.c_int, _c.c_int, _c.c_int]
         self._wide_ok = os.environ.get("BLAZE_GEMM_WIDE", "1") != "0"
@@ -84,11 +94,13 @@ class CudaOps:
                                         _c.c_int, VP]
         lib.blz_moe_combine.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
         self._route_counts = None
-        lib.blz_gdn_conv.argtypes = [VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
-        lib.blz_gdn_recurrent.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
+        lib.blz_gdn_conv.argtypes = [VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_gdn_recurrent.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
                                           _c.c_int, _c.c_int, VP]
         lib.blz_gated_rmsnorm.argtypes = [VP, VP, _c.c_longlong, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_float, _c.c_int, VP]
         lib.blz_status_take.restype = _c.c_int
+        lib.blz_status_peek_async.restype = _c.c_int
+        lib.blz_status_peek_async.argtypes = [VP, VP]
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> VP:
@@ -102,6 +114,12 @@ class CudaOps:
     def take_status(self) -> int:
         """Read and clear the device status word (non-zero = a bounded device wait ran out)."""
         return int(self.lib.blz_status_take())
+
+    def status_peek(self, host_word: torch.Tensor) -> None:
+        """Queue a copy of the status word into ``host_word`` (pinned int32) behind the work already on the stream."""
+        rc = self.lib.blz_status_peek_async(VP(host_word.data_ptr()), self._stream())
+        if rc != 0:
+            raise CudaError(f"blz_status_peek_async failed: {rc}")
 
     def _buf(self, key: str, nbytes: int) -> torch.Tensor:
         """Scratch that only grows.  A buffer that is outgrown is kept alive: captured graphs of smaller steps still hold
@@ -276,9 +294,10 @@ class CudaOps:
         return (out, vals) if want_values else out
 
     def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0,
-               wide: Optional[bool] = None, ksplit: int = 0, swiglu: bool = False, argmax_parts=None):
+               wide: Optional[bool] = None, ksplit: int = 0, swiglu: bool = False, argmax_parts=None, sk=None):
         """``wide``: None = choose; False = the 128-column kernel (needed by the fused all-reduce epilogue); True = insist on
-        the wide-N kernel (raises when the shape is not covered)."""
+        the wide-N kernel (raises when the shape is not covered).  ``sk``: None = choose; False = never; True or a K-slice
+        count 1..8 = the cluster split-K kernel (bf16 output, row-major weights)."""
         pk = self.pack(lin, swiglu=swiglu)
         kind = pk["kind"]
         f32 = out_dtype == torch.float32
@@ -320,6 +339,29 @@ class CudaOps:
             if rc != 0:
                 raise CudaError(f"blz_gemm_wait_flags failed: {rc}")
             x.wait = None
+        sk_able = not f32 and argmax_parts is None and pending is None and not kt
+        if sk is None:
+            sk = False
+            if self._sk_ok and sk_able and wide is None and bn == 0 and M <= self.SK_MAX_ROWS:
+                # Measured on B200 (NVFP4, 256 rows, captured-graph timing): splitting K over a cluster pays when the K range
+                # is long and the tiles are few (4096 x 12288: 23.7 -> 22.2 us); for the other decode shapes the exchange of
+                # fp32 partials through distributed shared memory (about 5 us per 64 KB tile) costs what the split saves.
+                # A tuning table measured on this device (tune.tune_linear) overrides the rule.
+                tiles = ((M + 127) // 128) * ((lin.N + 127) // 128)
+                sk = lin.K >= 8192 and tiles <= 2 * self._sm // 2
+                if self.tuning is not None:
+                    from ..tune import bucket
+                    hit = self.tuning.get(f"gemm{kind}", lin.N, lin.K, bucket(M))
+                    if hit is not None:
+                        sk = False if hit.get("kernel") != "sk" else (hit.get("ks") or True)
+        if sk is not False and sk is not None:
+            if not sk_able:
+                raise CudaError("the split-K GEMM writes bf16 from row-major weights and has no arg-max / peer-wait epilogue")
+            ks = 0 if sk is True else int(sk)
+            self._check(self.lib.blz_gemm_sk(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), ld_out, M, lin.N, lin.K,
+                                             _ptr(rs), _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]),
+                                             ks, int(swiglu), self._stream()), f"gemm_sk kind {kind}")
+            return out
         if wide is None:
             # Measured on B200 (Qwen3-8B shapes, captured-graph timing): 256-feature tiles win for block-scaled prefill GEMMs
             # (NVFP4 2048x24576x4096: 156 -> 119 us); the swapped orientation wins for the very wide bf16 head
@@ -593,8 +635,9 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ Gated DeltaNet
-    def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx):
-        """Causal conv + SiLU → gated delta rule (gates computed in the kernel) → gated RMSNorm."""
+    def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx, state_only: bool = False):
+        """Causal conv + SiLU → gated delta rule (gates computed in the kernel) → gated RMSNorm.  Sequences flagged in
+        ``batch.gdn_defer`` leave their state untouched; ``state_only`` advances the states and returns nothing."""
         cfg = model.cfg
         dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         hk, hv = gdn.k_heads, gdn.v_heads
@@ -603,12 +646,15 @@ class CudaOps:
         B = batch.slots.numel()
         conv = torch.empty(T, C, dtype=torch.bfloat16, device=self.device)
         self._check(self.lib.blz_gdn_conv(_ptr(mixed_qkv), mixed_qkv.stride(0), _ptr(conv), _ptr(kv.conv_state[layer_idx]),
-                                          _ptr(gdn.conv_w), _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len), B, C,
-                                          gdn.conv_w.shape[1], self._stream()), "gdn_conv")
-        o = torch.empty(T, hv, dv, dtype=torch.bfloat16, device=self.device)
+                                          _ptr(gdn.conv_w), _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len),
+                                          _ptr(batch.gdn_defer), B, C, gdn.conv_w.shape[1], self._stream()), "gdn_conv")
+        o = None if state_only else torch.empty(T, hv, dv, dtype=torch.bfloat16, device=self.device)
         self._check(self.lib.blz_gdn_recurrent(_ptr(conv), _ptr(a), _ptr(b), a.stride(0), _ptr(gdn.A_log), _ptr(gdn.dt_bias),
                                                _ptr(kv.rec_state[layer_idx]), _ptr(o), _ptr(batch.slots), _ptr(batch.q_start),
-                                               _ptr(batch.ctx_len), B, hk, hv, dk, dv, self._stream()), "gdn_recurrent")
+                                               _ptr(batch.ctx_len), _ptr(batch.gdn_defer), B, hk, hv, dk, dv, self._stream()),
+                    "gdn_recurrent")
+        if state_only:
+            return None
         y = torch.empty(T, hv * dv, dtype=torch.bfloat16, device=self.device)
         self._check(self.lib.blz_gated_rmsnorm(_ptr(o), _ptr(z), z.stride(0), _ptr(gdn.norm_w), _ptr(y), T, hv, dv,
                                                cfg.rms_norm_eps, 0, self._stream()), "gated_rmsnorm")

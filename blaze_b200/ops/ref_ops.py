@@ -86,24 +86,28 @@ class RefOps:
         return ref.moe_forward(x, topk_w, topk_id, experts.forward_one, experts.num_experts)
 
     # -------------------------------------------------------------- GDN
-    def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx):
-        """Causal conv + gates + delta-rule recurrence + gated norm, one sequence at a time."""
+    def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx, state_only: bool = False):
+        """Causal conv + gates + delta-rule recurrence + gated norm, one sequence at a time.  Sequences flagged in
+        ``batch.h_gdn_defer`` leave their state untouched; ``state_only`` advances the states and returns nothing."""
         cfg = model.cfg
         dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         hk, hv = gdn.k_heads, gdn.v_heads
         T = mixed_qkv.shape[0]
         out = torch.empty(T, hv * dv, dtype=mixed_qkv.dtype, device=mixed_qkv.device)
         conv_state, rec_state = kv.conv_state[layer_idx], kv.rec_state[layer_idx]
+        defer = getattr(batch, "h_gdn_defer", None)
         for bidx, slot in enumerate(batch.h_slots):
             r0, r1 = batch.h_q_start[bidx], batch.h_q_start[bidx + 1]
             if r1 == r0:
                 continue
             fresh = batch.h_ctx_len[bidx] - (r1 - r0) == 0
+            keep = not (defer is not None and defer[bidx])
             if fresh:
                 conv_state[slot].zero_()
                 rec_state[slot].zero_()
             y, cs = ref.gdn_conv(mixed_qkv[r0:r1], conv_state[slot], gdn.conv_w)
-            conv_state[slot].copy_(cs)
+            if keep:
+                conv_state[slot].copy_(cs)
             q = y[:, :hk * dk].view(-1, hk, dk)
             k = y[:, hk * dk:2 * hk * dk].view(-1, hk, dk)
             v = y[:, 2 * hk * dk:].view(-1, hv, dv)
@@ -112,11 +116,14 @@ class RefOps:
                 o, S = ref.gdn_chunked(q, k, v, g, beta, rec_state[slot])
             else:
                 o, S = ref.gdn_recurrent(q, k, v, g, beta, rec_state[slot])
-            rec_state[slot].copy_(S)
+            if keep:
+                rec_state[slot].copy_(S)
+            if state_only:
+                continue
             zz = z[r0:r1].view(-1, hv, dv)
             on = ref.gated_rmsnorm(o, zz, gdn.norm_w, cfg.rms_norm_eps, zero_centered=False)
             out[r0:r1] = on.reshape(r1 - r0, hv * dv)
-        return out
+        return None if state_only else out
 
     # -------------------------------------------------------------- head
     def argmax(self, logits):

@@ -28,6 +28,7 @@ from .batch import PAGE, SeqChunk
 from .tree import DraftTree, merge_chains
 from .engine import Engine, OutOfPages, Seq, Snapshot
 from .sampler import Rng, SamplingParams, penalty_edits
+from .health import StepShape
 from .telemetry import Histogram
 
 
@@ -374,6 +375,7 @@ class SchedConfig:
     max_draft: int = 4
     max_verify: int = 8
     draft_tree_width: int = 1          # > 1: n-gram drafts branch into up to this many continuations, verified as a tree
+    draft_tree_depth: int = 4          # deepest level of a draft tree (n-gram continuations are cut, drafter trees grown, to it)
     eos_ids: Tuple[int, ...] = ()
     max_model_len: int = 4096
     # "interleave": every step takes all decoding requests plus at most one prefill chunk (steady token flow for running
@@ -472,6 +474,9 @@ class Scheduler:
             self._cuda_sampler = CudaSampler(ops)
         from .suffix import SuffixIndex
         self.suffix = SuffixIndex() if cfg.spec_method == "suffix" else None
+        from .health import Health
+        self.health = Health()
+        self.raise_step_errors = False     # debugging aid: let a failing step raise instead of failing its requests
 
     # ================================================================== public
     def submit(self, req: GenRequest) -> None:
@@ -496,8 +501,34 @@ class Scheduler:
     def run_until_idle(self, max_steps: int = 1 << 30) -> None:
         n = 0
         while not self.idle and n < max_steps:
-            self.step()
+            self.safe_step()
             n += 1
+
+    def safe_step(self) -> None:
+        """One step; a step that fails (a kernel reported an error through the device status word, a sampler error, an
+        exception in the model) fails the requests that were running and leaves the scheduler ready for the next ones
+        (``crates/blaze/src/sched.rs:1067-1075``)."""
+        try:
+            self.step()
+        except Exception as e:
+            if self.raise_step_errors:
+                raise
+            log.error("sched.step_failed", error=repr(e))
+            self._ahead = self._pending = None
+            blamed = list(self.active)
+            for a in blamed:
+                self._retire(a, Finish.ERROR, error=repr(e))
+            if not blamed:
+                # the failure came before any request ran (admission): fail the request at the head of the queue, so that a
+                # failure that repeats cannot keep the loop spinning on the same request
+                if self.preempted:
+                    a = self.preempted.popleft()
+                    self._emit(a, GenEvent(a.req.request_id, finish=Finish.ERROR, error=repr(e), prompt_tokens=a.n_prompt))
+                elif self.waiting:
+                    req = self.waiting.popleft()
+                    self._emit(req, GenEvent(req.request_id, finish=Finish.ERROR, error=repr(e), prompt_tokens=len(req.prompt)))
+            self.stats.failed += 1
+            self.health.errors += 1
 
     def _loop(self) -> None:
         while not self._stop.is_set():
@@ -506,14 +537,8 @@ class Scheduler:
                     self.waiting.append(self.inbox.get(timeout=0.05))
                 except queue.Empty:
                     continue
-            try:
-                self.step()
-            except Exception as e:  # a failed step fails the active requests but keeps the loop alive
-                log.error("sched.step_failed", error=repr(e))
-                self._ahead = self._pending = None
-                for a in list(self.active):
-                    self._retire(a, Finish.ERROR, error=repr(e))
-                self.stats.failed += 1
+            self.safe_step()
+            self.health.tick(active=len(self.active), waiting=len(self.waiting), kv_pages_free=self.engine.pages.free_count)
 
     # ================================================================== admission
     def _reserved(self) -> int:
@@ -679,6 +704,7 @@ class Scheduler:
     def _consume_ahead(self, ah: _Ahead) -> None:
         if ah.event is not None:
             ah.event.synchronize()
+        self.engine.check_status()
         toks = ah.tokens.tolist()
         n = 0
         for a, tok in zip(ah.actives, toks):
@@ -691,6 +717,7 @@ class Scheduler:
         dt = (time.monotonic() - ah.t0) * 1e3
         self.step_ms.observe(dt / 1e3)
         self.stats.steps += 1
+        self.health.step(dt / 1e3, StepShape(rows=n, seqs=n))
         if self.on_step:
             self.on_step(dt, n)
 
@@ -778,7 +805,7 @@ class Scheduler:
             if isinstance(d, DraftTree):
                 chunks += eng.plan_tree([(a.seq, toks, d.parent)])
             else:
-                chunks += eng.plan([(a.seq, toks, want)])
+                chunks += eng.plan([(a.seq, toks, want)], defer_state=bool(d))
         want_any = any(w for _, _, w, _ in plan)
         need_logits = any(w and (a.req.params.needs_candidates() or a.req.constraint is not None or a.req.embed_only)
                           for a, _, w, _ in plan)
@@ -859,6 +886,10 @@ class Scheduler:
             logits = out
         elif mode == "both":
             logits, hidden = out
+        if mode != "greedy" and out is not None and eng.device.type == "cuda":
+            torch.cuda.current_stream(eng.device).synchronize()     # logits / hidden rows are read on the host next
+        if mode != "none":
+            eng.check_status()       # the step's results are on their way to the host: was any of its kernels in trouble?
         # rows whose chain the batched CUDA sampler covers are drawn with one launch and one copy for the whole step
         pre: Dict[int, object] = {}
         if logits is not None and self._cuda_sampler is not None:
@@ -948,6 +979,8 @@ class Scheduler:
                 self.stats.accepted_tokens += accepted
                 # KV of rejected draft rows is dropped; the last emitted token's KV is computed next step
                 a.computed = a.computed - len(toks) + 1 + accepted
+                if eng.kv.gdn_layers:
+                    eng.commit_state([(a.seq, 1 + accepted)])     # recurrent layers advance over the accepted rows only
                 eng.truncate(a.seq, a.computed)
             self._append(a, new, lps)
         if self.drafter is not None and hidden is not None:
@@ -961,6 +994,7 @@ class Scheduler:
         self.cost.observe(rows_total, dt)
         self.step_ms.observe(dt / 1e3)
         self.stats.steps += 1
+        self.health.step(dt / 1e3, StepShape(rows=rows_total, seqs=len(plan)))
         if self.on_step:
             self.on_step(dt, rows_total)
 

@@ -72,6 +72,7 @@ class ServerState:
         self.grammars = Grammars.load(tokenizer, cfg.vocab_size, eos)
         self.vision = vision
         self.llm = llm
+        llm.engine.start_watchdog()
         if llm.sched._thread is None:
             llm.sched.start()
 
@@ -315,6 +316,12 @@ def create_app(st: ServerState) -> FastAPI:
                 gauge("blaze_kv_host_pages_free", sc.cache.host.free_pages, "Free pages of the host KV tier")
                 counter("blaze_kv_host_hits_total", sc.cache.host_hits, "Prefix-cache hits served from the host KV tier")
                 counter("blaze_kv_host_spilled_pages_total", sc.cache.host.spilled_pages, "Pages copied to the host KV tier")
+            eng = st.llm.engine
+            counter("blaze_failed_steps_total", sc.stats.failed, "Engine steps that failed (their requests ended with an error)")
+            counter("blaze_device_status_errors_total", eng.status_errors, "Steps in which a kernel reported an error through the device status word")
+            counter("blaze_engine_hangs_total", eng.hangs, "Steps the watchdog reported as hung")
+            counter("blaze_slow_steps_total", sc.health.outliers, "Steps flagged as latency outliers")
+            gauge("blaze_mean_step_seconds", round(sc.health.mean_s, 6), "Running mean of the engine step time")
             lines.append(sc.ttft.render("blaze_time_to_first_token_seconds", "Time to first token"))
             lines.append(sc.tpot.render("blaze_time_per_output_token_seconds", "Time per output token"))
             lines.append(sc.step_ms.render("blaze_step_seconds", "Engine step time"))

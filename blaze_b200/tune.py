@@ -77,10 +77,17 @@ class Tuning:
         return self.table[self.key(kind, *shape)]
 
 
-def gemm_candidates(kind: int, N: int):
-    out = [{"bn": 128, "max_ctas": 0}]
-    if N % 256 == 0:
-        out.append({"bn": 256, "max_ctas": 0})
+def gemm_candidates(kind: int, N: int, K: int, rows: int):
+    """Kernel variants worth timing for one linear layer at ``rows`` rows: the one-CTA-per-tile kernel with 128- or
+    256-column tiles, and for decode-sized steps the cluster split-K kernel with its K-slice counts."""
+    out = [{"kernel": "tc", "bn": 128}]
+    if N % 256 == 0 and rows > 128:
+        out.append({"kernel": "tc", "bn": 256})
+    if rows <= 512:
+        bk = {0: 64, 1: 256}.get(kind, 128)
+        for ks in (1, 2, 3, 4, 6, 8):
+            if ks <= (K + bk - 1) // bk:
+                out.append({"kernel": "sk", "ks": ks})
     return out
 
 
@@ -91,14 +98,62 @@ def tune_linear(ops, lin, rows: int, tuning: Tuning, iters: int = 5) -> Dict:
     x = torch.randn(rows, lin.K, device=ops.device).bfloat16()
     xin = ops.quantize_rows(x, lin) if ops._qmode(lin) else x
 
+    out = torch.empty(rows, lin.N, dtype=torch.bfloat16, device=ops.device)
+
+    def call(cfg):
+        if cfg["kernel"] == "sk":
+            ops.linear(lin, xin, out=out, sk=cfg["ks"])
+        else:
+            ops.linear(lin, xin, out=out, bn=cfg["bn"], wide=False, sk=False)
+
     def run(cfg):
-        for _ in range(2):
-            ops.linear(lin, xin, bn=cfg["bn"], max_ctas=cfg["max_ctas"])
+        # a captured graph of back-to-back calls: a single small launch timed from the host measures the host
+        call(cfg)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                call(cfg)
+        g.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(iters):
-            ops.linear(lin, xin, bn=cfg["bn"], max_ctas=cfg["max_ctas"])
+        g.replay()
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters
-    return tuning.tune(f"gemm{pk['kind']}", (lin.N, lin.K, bucket(rows)), gemm_candidates(pk["kind"], lin.N), run)
+    return tuning.tune(f"gemm{pk['kind']}", (lin.N, lin.K, bucket(rows)), gemm_candidates(pk["kind"], lin.N, lin.K, rows), run)
+
+
+def tune_model(model, rows: Iterable[int] = (256,), tuning: Optional[Tuning] = None, save: bool = True) -> Tuning:
+    """Time the kernel variants of every distinct linear shape of ``model`` at the given row counts and install the table
+    on its op set (``ops.tuning``), so that ``CudaOps.linear`` picks the measured winner per (format, N, K, row bucket).
+    The table is kept in the JSON cache of this device, so later runs only load it (reference: the start-up GEMV tuning of
+    ``crates/blaze/src/model.rs:1568-1590`` and ``tune.rs:243``)."""
+    ops = model.ops
+    if not getattr(ops, "is_cuda", False):
+        return tuning or Tuning()
+    import torch
+    props = torch.cuda.get_device_properties(ops.device)
+    t = tuning or Tuning(cache_path(props.major * 10 + props.minor, props.multi_processor_count, model.tp.rank))
+    seen = set()
+    for L in model.layers:
+        lins = []
+        if L.attn is not None:
+            lins += [L.attn.qkv, L.attn.o]
+        if L.gdn is not None:
+            lins += [L.gdn.in_proj, L.gdn.out_proj]
+        mlp = L.mlp
+        if hasattr(mlp, "down") and hasattr(mlp, "gate_up") and not hasattr(mlp, "experts"):
+            lins += [mlp.down]          # gate_up runs with the SwiGLU epilogue, which has one variant
+        for lin in lins:
+            for r in rows:
+                key = (int(lin.fmt.value if hasattr(lin.fmt, "value") and isinstance(lin.fmt.value, int) else hash(lin.fmt) & 0xff),
+                       lin.N, lin.K, bucket(r))
+                if key in seen:
+                    continue
+                seen.add(key)
+                tune_linear(ops, lin, r, t)
+    if save:
+        t.save()
+    ops.tuning = t
+    return t

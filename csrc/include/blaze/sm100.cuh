@@ -92,6 +92,60 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// ------------------------------------------------------------------------------------------ thread-block clusters
+// Distributed shared memory between the CTAs of a cluster: a shared-memory address of this CTA is mapped to the same offset
+// in CTA `rank`'s shared memory with mapa; loads / mbarrier arrives on the mapped address reach the peer.  (Clusters are
+// used for sharing through DSMEM only; no TMA load here is ever cluster-multicast.)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Hardware cluster barrier, split in two so that the work between arrive and wait overlaps the peers' start-up.  Every
+// thread of every CTA of the cluster must execute both, unconditionally (they are used once, right after barrier set-up,
+// where no role can have failed yet; everything later uses bounded mbarrier waits).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+// arrive on an mbarrier of a peer CTA (address from mapa_shared); releases this thread's earlier writes at cluster scope
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t mapped_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(mapped_bar) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t mapped_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(mapped_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_dsmem_f4(uint32_t mapped_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(mapped_addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+// Bounded wait on a local mbarrier whose arrivals come from peer CTAs (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  long long t0 = clock64();
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
+        : "memory");
+    if (ok) return true;
+    if (clock64() - t0 > kSpinLimit) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, kOk, kErrMbarTimeout);
+      return false;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ fences
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

@@ -17,7 +17,7 @@ template <int KW>
 __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y,
                                 __nv_bfloat16* __restrict__ conv_state, const __nv_bfloat16* __restrict__ w,
                                 const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ ctx_len,
-                                int C) {
+                                const int* __restrict__ no_store, int C) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
   if (c >= C) return;
@@ -41,6 +41,7 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, long long l
 #pragma unroll
     for (int j = 0; j < KW - 1; ++j) h[j] = h[j + 1];
   }
+  if (no_store != nullptr && no_store[b]) return;      // speculative rows: the state advances when they are replayed
 #pragma unroll
   for (int j = 0; j < KW - 1; ++j) st[j] = __float2bfloat16(h[j]);
 }
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(
     const __nv_bfloat16* __restrict__ conv, const __nv_bfloat16* __restrict__ a_in, const __nv_bfloat16* __restrict__ b_in,
     long long ld_ab, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ rec_state,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ slots, const int* __restrict__ q_start,
-    const int* __restrict__ ctx_len, int Hk, int Hv, int DV) {
+    const int* __restrict__ ctx_len, const int* __restrict__ no_store, int Hk, int Hv, int DV) {
   constexpr int PER = DK / 4;
   const int b = blockIdx.x, hv = blockIdx.y, slice = blockIdx.z;
   const int tid = threadIdx.x, c = tid & 31, qt = tid >> 5;
@@ -101,9 +102,10 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(
     for (int i = 0; i < PER; ++i) { S[i] += s_k[qt * PER + i] * delta; po += S[i] * s_q[qt * PER + i]; }
     s_red[1][qt][c] = po;
     __syncthreads();
-    if (qt == 0)
+    if (qt == 0 && out != nullptr)
       out[(row * Hv + hv) * DV + col] = __float2bfloat16(s_red[1][0][c] + s_red[1][1][c] + s_red[1][2][c] + s_red[1][3][c]);
   }
+  if (no_store != nullptr && no_store[b]) return;
 #pragma unroll
   for (int i = 0; i < PER; ++i) st[(size_t)(qt * PER + i) * DV + col] = S[i];
 }
@@ -133,11 +135,13 @@ __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ o, const 
 using namespace blz;
 typedef __nv_bfloat16 bf16;
 
+// no_store (both kernels, optional [B]): 1 = read the sequence's state but leave it as it was (speculative rows).
+// blz_gdn_recurrent: out may be null (state advance only, used when accepted rows are replayed).
 BLZ_API int blz_gdn_conv(const void* x, long long ldx, void* y, void* conv_state, const void* w, const int* slots,
-                         const int* q_start, const int* ctx_len, int B, int C, int kw, cudaStream_t s) {
+                         const int* q_start, const int* ctx_len, const int* no_store, int B, int C, int kw, cudaStream_t s) {
   if (B == 0) return 0;
   dim3 grid((C + 127) / 128, B);
-#define BLZ_CONV(K) gdn_conv_kernel<K><<<grid, 128, 0, s>>>((const bf16*)x, ldx, (bf16*)y, (bf16*)conv_state, (const bf16*)w, slots, q_start, ctx_len, C)
+#define BLZ_CONV(K) gdn_conv_kernel<K><<<grid, 128, 0, s>>>((const bf16*)x, ldx, (bf16*)y, (bf16*)conv_state, (const bf16*)w, slots, q_start, ctx_len, no_store, C)
   switch (kw) {
     case 2: BLZ_CONV(2); break;
     case 3: BLZ_CONV(3); break;
@@ -151,12 +155,12 @@ BLZ_API int blz_gdn_conv(const void* x, long long ldx, void* y, void* conv_state
 
 BLZ_API int blz_gdn_recurrent(const void* conv, const void* a_in, const void* b_in, long long ld_ab, const float* A_log,
                               const float* dt_bias, float* rec_state, void* out, const int* slots, const int* q_start,
-                              const int* ctx_len, int B, int Hk, int Hv, int DK, int DV, cudaStream_t s) {
+                              const int* ctx_len, const int* no_store, int B, int Hk, int Hv, int DK, int DV, cudaStream_t s) {
   if (B == 0) return 0;
   if (DK != 128 || DV % 32 || Hv % Hk) return (int)cudaErrorInvalidValue;
   dim3 grid(B, Hv, DV / 32);
   gdn_recurrent_kernel<128><<<grid, 128, 0, s>>>((const bf16*)conv, (const bf16*)a_in, (const bf16*)b_in, ld_ab, A_log, dt_bias,
-                                                 rec_state, (bf16*)out, slots, q_start, ctx_len, Hk, Hv, DV);
+                                                 rec_state, (bf16*)out, slots, q_start, ctx_len, no_store, Hk, Hv, DV);
   return (int)cudaGetLastError();
 }
 

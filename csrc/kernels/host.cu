@@ -69,6 +69,14 @@ BLZ_API int blz_status_take() {
   return h;
 }
 
+// Queue a copy of the status word into `host_dst` (pinned host memory) behind the work already on `stream`: the host reads
+// it once it has synchronised with the step anyway (when it takes the step's tokens), so watching the word costs no
+// synchronisation of its own.
+BLZ_API int blz_status_peek_async(int* host_dst, cudaStream_t stream) {
+  if (!host_dst) return (int)cudaErrorInvalidValue;
+  return (int)cudaMemcpyAsync(host_dst, blz::status_word(), sizeof(int), cudaMemcpyDeviceToHost, stream);
+}
+
 BLZ_API void* blz_status_ptr() { return blz::status_word(); }
 
 BLZ_API int blz_version() { return 1; }

@@ -112,6 +112,40 @@ def test_gemm_wide(ops, fmt, M, N, K, ksplit):
     assert rel < 0.05
 
 
+@pytest.mark.parametrize("fmt,M,N,K,ks", [
+    ("nvfp4", 256, 6144, 4096, 0), ("nvfp4", 256, 4096, 4096, 4), ("nvfp4", 256, 768, 4096, 8), ("nvfp4", 256, 4096, 512, 2),
+    ("nvfp4", 200, 1024, 12288, 3), ("nvfp4", 77, 520, 1024, 4), ("nvfp4", 1, 384, 512, 2), ("nvfp4", 130, 256, 320, 5),
+    ("nvfp4", 384, 1000, 2048, 6), ("mxfp8", 256, 1024, 2048, 4), ("mxfp8", 40, 384, 1024, 7), ("mxfp8", 300, 512, 2048, 1),
+    ("bf16", 256, 1000, 1024, 2), ("bf16", 19, 131, 320, 3), ("fp8", 192, 384, 512, 2), ("fp8", 64, 256, 4096, 8)])
+def test_gemm_cluster_split_k(ops, fmt, M, N, K, ks):
+    """Decode GEMM whose K range is split over a thread-block cluster and reduced through distributed shared memory."""
+    g = torch.Generator(device=DEV).manual_seed(31)
+    x = (torch.randn(M, K, generator=g, device=DEV)).bfloat16()
+    w = torch.randn(N, K, generator=g, device=DEV) * 0.02
+    f = {"nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "bf16": Format.DENSE, "fp8": Format.FP8_CHANNEL}[fmt]
+    lin = Linear.from_dense(w, f)
+    if fmt == "bf16":
+        lin.bias = (torch.randn(N, generator=g, device=DEV) * 0.1).bfloat16()
+        lin.cuda_pack = None
+    xin = ops.quantize_rows(x, lin) if ops._qmode(lin) else x
+    guard = torch.full((M + 2, N + 8), 7.0, dtype=torch.bfloat16, device=DEV)     # poison around the output
+    out = guard[1:M + 1, :N]
+    l0 = ops.launches
+    y = ops.linear(lin, xin, sk=ks if ks else True, out=out)
+    assert ops.launches == l0 + 1
+    y_tc = ops.linear(lin, xin, wide=False, sk=False)
+    again = ops.linear(lin, xin, sk=ks if ks else True)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert torch.equal(y, again), "the cluster reduction must be deterministic"
+    assert (guard[0] == 7).all() and (guard[M + 1] == 7).all() and (guard[:, N:] == 7).all(), "wrote outside the output"
+    _, rel = _report(f"gemm_sk {fmt} {M}x{N}x{K} ks{ks} vs 128-column kernel", y, y_tc.float())
+    assert rel < 2e-3
+    want = lin.ref(x, torch.float32)
+    _, rel = _report(f"gemm_sk {fmt} vs oracle", y, want)
+    assert rel < 0.05
+
+
 @pytest.mark.parametrize("fmt,M,N,K", [("nvfp4", 300, 512, 1024), ("nvfp4", 64, 384, 576 * 2), ("bf16", 100, 200, 320),
                                        ("mxfp8", 130, 256, 640)])
 def test_gemm_tile_major_weights(ops, fmt, M, N, K):
@@ -467,3 +501,30 @@ def test_head_argmax_in_the_gemm_epilogue(ops, fmt, M, N, K):
     assert ops.take_status() == 0
     assert torch.equal(got_i, want_i) and torch.equal(got_v, want_v)
     assert torch.equal(ops.linear_argmax(lin, x), want_i - 11)
+
+
+def test_autotuner_routes_linear_layers(ops, tmp_path, monkeypatch):
+    """The tuner times the kernel variants of a layer shape, keeps the winner in its JSON cache, and ``CudaOps.linear`` follows
+    the table; a second tuner instance reads the cache instead of timing again."""
+    from blaze_b200 import tune
+    g = torch.Generator(device=DEV).manual_seed(41)
+    lin = Linear.from_dense(torch.randn(512, 8192, generator=g, device=DEV) * 0.02, Format.NVFP4)
+    x = torch.randn(256, 8192, generator=g, device=DEV).bfloat16()
+    t = tune.Tuning(str(tmp_path / "tune.json"))
+    best = tune.tune_linear(ops, lin, 256, t, iters=3)
+    assert best["kernel"] in ("tc", "sk") and best["ms"] > 0
+    t.save()
+    t2 = tune.Tuning(str(tmp_path / "tune.json"))
+    assert t2.get("gemm1", 512, 8192, 256) == best
+    want = ops.linear(lin, x, wide=False, sk=False)
+    ops.tuning = t2
+    try:
+        l0 = ops.launches
+        got = ops.linear(lin, x)
+        assert ops.launches == l0 + 2                    # activation quantisation + one GEMM, whichever kernel was chosen
+    finally:
+        ops.tuning = None
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    _, rel = _report("tuned route vs one-CTA-per-tile kernel", got, want.float())
+    assert rel < 2e-3

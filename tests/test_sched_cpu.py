@@ -316,3 +316,57 @@ def test_tree_rows_in_the_step_batch():
     assert build_batch([SeqChunk(1, [7, 8], 3)], table, "cpu").tree_mask is None
     with pytest.raises(ValueError):
         tree_depths([-1, 1])
+
+
+def test_speculation_on_a_recurrent_hybrid_is_exact():
+    """Gated DeltaNet layers carry a recurrent state: verify rows must not advance it past rejected drafts.  The state
+    update of speculative rows is deferred and replayed over the accepted rows, so n-gram speculation gives the tokens of
+    plain decoding, rejected drafts included."""
+    def hy(**kw):
+        base = dict(device="cpu", dtype=torch.float32, max_seqs=8, max_model_len=256, use_graphs=False, seed=0)
+        base.update(kw)
+        return LLM(named_config("tiny-hybrid"), **base)
+    rep = [3, 4, 5, 6, 7, 8] * 6
+    ps = [rep, _prompts(1, 30, seed=4)[0], [9, 9, 9, 9, 9, 9, 9, 9, 9, 9, 9, 9]]
+    sp = SamplingParams(temperature=0.0, max_tokens=24)
+    want = [o.token_ids for o in hy().generate(ps, sp)]
+    spec = hy(spec_method="ngram")
+    got = spec.generate(ps, sp)
+    assert [o.token_ids for o in got] == want
+    st = spec.sched.stats
+    assert st.draft_tokens > 0 and st.accepted_tokens < st.draft_tokens, "the test needs rejected drafts to mean anything"
+
+
+def test_device_status_error_fails_the_step_and_serving_continues():
+    """A kernel that gives up on a bounded wait leaves a code in the device status word.  The engine reads the word with
+    every step's results: the running requests end with an error, the word is cleared, and the next request is served.
+    (The device word is replaced by a host-side stand-in here; the kernels' side is tested against a silent peer on the GPU.)"""
+    llm = _llm()
+    ps = _prompts(2, 20, seed=9)
+    want = [o.token_ids for o in llm.generate(ps, GREEDY)]
+    codes = [0, 0, 2]          # the third status read of the next run reports "a peer rank's flag never arrived"
+
+    def status():
+        return codes.pop(0) if codes else 0
+    llm.engine.status_source = status
+    bad = llm.generate(ps, GREEDY)
+    assert all(o.finish_reason == "error" and "device status 2" in (o.error or "") for o in bad)
+    assert llm.sched.stats.failed == 1 and llm.engine.status_errors == 1 and llm.sched.health.errors == 1
+    assert not llm.sched.active and llm.engine.pages.free_count == llm.engine.num_pages - 1 - sum(len(e.snap.pages) for e in llm.sched.cache.entries)
+    good = llm.generate(ps, GREEDY)
+    assert [o.token_ids for o in good] == want and all(o.finish_reason == "length" for o in good)
+
+
+def test_watchdog_reports_a_step_that_does_not_return():
+    import time
+    llm = _llm()
+    llm.engine.ecfg.hang_secs = 0.2
+    seen = []
+    llm.engine.start_watchdog(on_hang=seen.append)
+    llm.engine.last_step_started = time.monotonic() - 1.0      # a step that has been running for a second
+    llm.engine.last_step_what = "greedy rows=1 seqs=1"
+    for _ in range(40):
+        if seen:
+            break
+        time.sleep(0.05)
+    assert seen and "engine hang" in seen[0] and llm.engine.hangs == 1
