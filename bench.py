@@ -25,8 +25,10 @@ import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-REFERENCE_UNAVAILABLE = ("the reference is a Rust/CMake project (Cargo.toml, no setup.py/pyproject.toml): pip cannot "
-                         "install it and no Rust toolchain (cargo/rustc) exists in this image")
+REFERENCE_UNAVAILABLE = ("the reference engine is a Rust workspace (Cargo.toml, no setup.py/pyproject.toml): pip cannot install it "
+                         "and no Rust toolchain (cargo/rustc) exists in this image, so its serving step cannot run; its CUDA kernel "
+                         "library does build (baseline/build_reference_kernels.sh) and is timed kernel by kernel against this "
+                         "library by `python -m blaze_b200.benchmarks.reference_kernels`")
 
 
 def clocks_sampler(path, gpu_index):
