@@ -89,10 +89,43 @@ def main(argv=None):
         y = fused.gemm_allreduce(ops, lin, xk, T)
         ops.norm(y, res_full, w, 1e-6, False, quant_for=nxt, zero_src=True)
 
+    def gemm_push_then_rn():
+        fused.reduce_norm(fused.gemm_push(ops, lin, xk, T), res_shard, w, 1e-6, False, quant_for=nxt)
+
+    def gemm_push_rn_next_gemm():
+        qa = fused.reduce_norm(fused.gemm_push(ops, lin, xk, T), res_shard, w, 1e-6, False, quant_for=qkv)
+        ops.linear(qkv, qa)
+
+    def gemm_rn_next_gemm():
+        ops.linear(lin, xk, out=fused.next_input(T, H))
+        qa = fused.reduce_norm(fused.next_input(T, H), res_shard, w, 1e-6, False, quant_for=qkv)
+        ops.linear(qkv, qa)
+
+    def gemm_push_only():
+        fused.gemm_push(ops, lin, xk, T)
+
+    import ctypes as _ct
+    _loc = fused.arena.local.data_ptr()
+
+    def gemm_push_local():
+        # the same epilogue with every owner's slot buffer in local memory: what the push costs without NVLink
+        b = fused.push_cur ^ 1
+        fused.push_cur = b
+        VPn = _ct.c_void_p
+        slots = (VPn * world)(*[VPn(_loc + fused.off_slot[b])] * world)
+        flags = (VPn * world)(*[VPn(_loc + fused.off_slot_flag + 2048 + 64 * b)] * world)
+        fused.lib.blz_gemm_push_rs(slots, flags, VPn(fused.push_state.data_ptr() + 8), VPn(fused.push_state.data_ptr() + 12), rank, world,
+                                   fused.rows_per(T))
+        ops.linear(lin, xk, out=fused.arena.view(fused.off_in[0], T * H * 2).view(torch.bfloat16).view(T, H), wide=False, sk=False)
+
     cases = [("nccl_allreduce", nccl_ar), ("nccl_allreduce+norm_quant", nccl_ar_norm), ("fused_allreduce", fused_ar),
              ("fused_allreduce_norm_quant", fused_rn), ("gemm", gemm_only), ("gemm+fused_allreduce_norm_quant", gemm_then_rn),
              ("fused_allreduce_norm_quant+next_gemm", rn_then_gemm),
-             ("fused_allreduce_norm_quant(signal only)+next_gemm(waits)", rn_signal_then_gemm_waits)]
+             ("fused_allreduce_norm_quant(signal only)+next_gemm(waits)", rn_signal_then_gemm_waits),
+             ("gemm(push reduce-scatter) alone", gemm_push_only), ("gemm(push, local slots only)", gemm_push_local),
+             ("gemm(push reduce-scatter)+slots_norm_quant", gemm_push_then_rn),
+             ("gemm+fused_allreduce_norm_quant+next_gemm", gemm_rn_next_gemm),
+             ("gemm(push reduce-scatter)+slots_norm_quant+next_gemm", gemm_push_rn_next_gemm)]
     if fused.use_mc:
         cases.append(("gemm_allreduce_one_kernel+norm_quant", gemm_ar))
     out = {}
@@ -127,7 +160,8 @@ def main(argv=None):
         buf = torch.zeros(8, dtype=torch.int64, device=dev)
         fused.lib.blz_comm_set_prof.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         fused.lib.blz_comm_set_prof(fused.comm, ctypes.c_void_p(buf.data_ptr()))
-        for name, fn in (("fused_allreduce", fused_ar), ("fused_allreduce_norm_quant", fused_rn)):
+        for name, fn in (("fused_allreduce", fused_ar), ("fused_allreduce_norm_quant", fused_rn),
+                         ("gemm(push reduce-scatter)+slots_norm_quant", gemm_push_then_rn)):
             acc = torch.zeros(4, dtype=torch.float64)
             n = 0
             for _ in range(10):

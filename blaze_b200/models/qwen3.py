@@ -499,7 +499,7 @@ class Model:
         may then take over the wait for the peers' rows."""
         ops, cfg = self.ops, self.cfg
         eps, zc = cfg.rms_norm_eps, cfg.zero_centered_norm
-        if fused is not None and fused.mode == "reduce_norm":
+        if fused is not None and fused.mode in ("reduce_norm", "rs_push"):
             if residual is None:                       # first norm of the stage: shard the residual stream by rows
                 residual = fused.shard_rows(x)
                 h, _ = ops.norm(x, None, w, eps, zc, quant_for=quant_for)
@@ -525,7 +525,7 @@ class Model:
     def _materialise(self, x, residual, kind, fused, keep: bool = False):
         """The complete residual stream on every rank."""
         ops = self.ops
-        if fused is not None and fused.mode == "reduce_norm" and residual is not None:
+        if fused is not None and fused.mode in ("reduce_norm", "rs_push") and residual is not None:
             if kind != "partial":
                 x = self._as_partial(x, fused)
             res = residual.clone() if keep else residual
@@ -546,6 +546,9 @@ class Model:
             return ops.linear(lin, a), ("partial" if self.tp.world > 1 else "full")
         if fused.mode == "gemm_red":
             return fused.gemm_allreduce(ops, lin, a, rows), "acc"
+        if fused.mode == "rs_push" and lin.N % 32 == 0 and fused.group.world * fused.rows_per(rows) * lin.N * 2 <= fused.slot_bytes:
+            # the GEMM's epilogue scatters the partial rows to their owner ranks; reduce_norm picks them up from the slots
+            return fused.gemm_push(ops, lin, a, rows), "partial"
         return ops.linear(lin, a, out=fused.next_input(rows, lin.N)), "partial"
 
     def _out_buf(self, fused, rows, cols):

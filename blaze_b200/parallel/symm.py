@@ -67,6 +67,18 @@ class SymmArena:
         return self.mc + off if self.mc else 0
 
 
+class PushedRows:
+    """Partial sums that a row-cut GEMM scattered into the owner ranks' slot buffers (``SymmAllReduce.gemm_push``)."""
+    __slots__ = ("buf", "rows", "cols")
+
+    def __init__(self, buf: int, rows: int, cols: int):
+        self.buf, self.rows, self.cols = buf, rows, cols
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+
 class SymmAllReduce:
     def __init__(self, group, device, max_rows: int, hidden: int, use_multicast: bool = True, timeout_ms: int = 0):
         self.group, self.device = group, torch.device(device)
@@ -79,6 +91,10 @@ class SymmAllReduce:
         lib.blz_comm_allreduce_norm.argtypes = [VP] + [VP] * 8 + [VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                                   ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                                   ctypes.c_int, VP]
+        lib.blz_comm_slots_norm.argtypes = [VP] + [VP] * 9 + [VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                              ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                              ctypes.c_int, VP]
+        lib.blz_gemm_push_rs.argtypes = [VP, VP, VP, VP, ctypes.c_int, ctypes.c_int, ctypes.c_int]
         self.max_rows, self.hidden = max_rows, hidden
         row_tiles = (max_rows + 127) // 128
         self.in_bytes = max_rows * hidden * 2
@@ -86,7 +102,10 @@ class SymmAllReduce:
         self.sf_bytes = row_tiles * ((hidden + 63) // 64) * 512
         self.rs_bytes = max_rows * 4
         pad_bytes = int(lib.blz_comm_pad_bytes())
-        total = 4 * self.in_bytes + self.in_bytes + self.q_bytes + self.sf_bytes + self.rs_bytes + pad_bytes + 40 * 4096
+        # reduce-scatter by push: per rank two slot buffers [world][rows_per][hidden] that the peers' GEMM epilogues fill
+        self.slot_bytes = group.world * ((max_rows + group.world - 1) // group.world) * hidden * 2
+        total = (4 * self.in_bytes + self.in_bytes + self.q_bytes + self.sf_bytes + self.rs_bytes + pad_bytes + 2 * self.slot_bytes
+                 + 48 * 4096)
         self.arena = SymmArena(group, device, total)
         a = self.arena
         self.off_in = [a.carve(self.in_bytes), a.carve(self.in_bytes)]
@@ -104,6 +123,11 @@ class SymmAllReduce:
         a.view(self.off_pad2, 4096).zero_()
         self.off_sig = a.carve(4096)               # arrival counters of kernels that signal instead of waiting
         a.view(self.off_sig, 4096).zero_()
+        self.off_slot = [a.carve(self.slot_bytes), a.carve(self.slot_bytes)]
+        self.off_slot_flag = a.carve(4096)         # two flag rows (one per slot buffer), 64 bytes apart
+        a.view(self.off_slot_flag, 4096).zero_()
+        self.push_state = torch.zeros(4, dtype=torch.int32, device=self.device)     # [finished CTAs, epoch]
+        self.push_cur = 0
         self.sig_expect = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.gemm_state = torch.zeros(4, dtype=torch.int32, device=self.device)     # [done counter, epoch]
         self.acc_cur = 0
@@ -122,6 +146,13 @@ class SymmAllReduce:
         # "reduce_norm": GEMM writes partial sums, one kernel reduces + norms + quantises a row slice per rank.
         # measured on 2 B200s (Qwen3-8B, 256 rows): reduce_norm 21 us per reduction against 55 us for gemm_red, whose
         # epilogue also collapses on prefill-sized tiles; gemm_red stays available for experiments
+        # "rs_push": the row-cut GEMM's epilogue sends each partial row into its owner rank's slot buffer through peer memory
+        # (bulk copies from shared memory) and raises a flag; the owner's reduce + norm + quantise kernel starts without a rank
+        # barrier (it waits for the flags and sums the slots from local memory).  Measured on 2 B200s (Qwen3-8B, 256 rows):
+        # the flag-started reduction takes 9.8 us against 21.9 us, but the pushing GEMM takes 25.5 us against 15.3 us (the
+        # same with every slot in local memory, so it is not NVLink: the per-CTA system-scope fence and the drain of the
+        # asynchronous stores at the end of the kernel), 39.0 us against 35.9 us for the pair and 7.09 against 6.71 ms per
+        # decode step - so it is opt-in.
         default = "reduce_norm"
         self.mode = os.environ.get("BLAZE_TP_FUSION", default)
         if self.mode == "gemm_red" and not self.use_mc:
@@ -199,6 +230,26 @@ class SymmAllReduce:
         self.launches += 1
         return out
 
+    def gemm_push(self, ops, lin: Linear, x, rows: int):
+        """Row-cut projection whose epilogue scatters the partial sums to their owner ranks (reduce-scatter by push): returns
+        a token for :meth:`reduce_norm` instead of a tensor — the sums only exist once the owners have reduced their slots."""
+        per = self.rows_per(rows)
+        if self.group.world * per * lin.N * 2 > self.slot_bytes or lin.N % 32:
+            raise ValueError("slot buffer too small (or N not a multiple of 32) for the pushed reduce-scatter")
+        self.push_cur ^= 1
+        b = self.push_cur
+        a = self.arena
+        rc = self.lib.blz_gemm_push_rs(_arr(a.peers(self.off_slot[b])), _arr(a.peers(self.off_slot_flag + 64 * b)),
+                                       VP(self.push_state.data_ptr()), VP(self.push_state.data_ptr() + 4), self.group.rank,
+                                       self.group.world, per)
+        if rc != 0:
+            raise RuntimeError(f"blz_gemm_push_rs failed: {rc}")
+        # C is not written in this mode; any valid [rows, N] bf16 view serves as the output argument
+        dummy = a.view(self.off_in[0], rows * lin.N * 2).view(torch.bfloat16).view(rows, lin.N)
+        ops.linear(lin, x, out=dummy, wide=False, sk=False)
+        self.launches += 1
+        return PushedRows(b, rows, lin.N)
+
     def rows_per(self, T: int) -> int:
         return (T + self.group.world - 1) // self.group.world
 
@@ -222,12 +273,16 @@ class SymmAllReduce:
         ``defer``: the caller promises that the result's first consumer is ``ops.linear``; for quantised results of
         decode-sized steps the kernel then only signals the peers on its way out and the GEMM waits for their flags
         after it has started fetching its weights (``QuantAct.wait``)."""
-        T, H = partial.shape
-        i = self._which(partial)
-        if i is None:
-            buf = self.next_input(T, H)
-            buf.copy_(partial)
-            partial, i = buf, self.cur
+        pushed = partial if isinstance(partial, PushedRows) else None
+        if pushed is not None:
+            T, H, i = pushed.rows, pushed.cols, 0
+        else:
+            T, H = partial.shape
+            i = self._which(partial)
+            if i is None:
+                buf = self.next_input(T, H)
+                buf.copy_(partial)
+                partial, i = buf, self.cur
         mode = 0
         if quant_for is not None and quant_for.act_quant and norm_w is not None:
             mode = 1 if quant_for.fmt == Format.NVFP4 else (2 if quant_for.fmt in (Format.MXFP8, Format.FP8_BLOCK) else 0)
@@ -238,14 +293,28 @@ class SymmAllReduce:
         per = self.rows_per(T)
         blocks = max(1, min(per, 512))
         defer = bool(defer and self.defer_ok and mode != 0 and T <= 256)
-        rc = self.lib.blz_comm_allreduce_norm(
+        if pushed is not None:
+            rc = self.lib.blz_comm_slots_norm(
+                self.comm, VP(a.local.data_ptr() + self.off_slot[pushed.buf]), VP(a.local.data_ptr() + self.off_slot_flag + 64 * pushed.buf),
+                VP(self.push_state.data_ptr() + 4), _arr(a.peers(off_out)), _arr(a.peers(self.off_sf)), _arr(a.peers(self.off_rs)),
+                VP(a.mcast(off_out) if mc else 0), VP(a.mcast(self.off_sf) if mc else 0), VP(a.mcast(self.off_rs) if mc else 0),
+                VP(residual.data_ptr() if residual is not None else 0), VP(norm_w.data_ptr() if norm_w is not None else 0),
+                T, H, per, eps, int(zero_centered), mode, blocks, int(defer), self._stream())
+        else:
+            rc = self._allreduce_norm(a, off_in, off_out, mc, residual, norm_w, T, H, per, eps, zero_centered, mode, blocks, defer)
+        if rc != 0:
+            raise RuntimeError(f"fused reduce + norm failed: {rc}")
+        return self._result(a, off_out, mode, T, H, defer)
+
+    def _allreduce_norm(self, a, off_in, off_out, mc, residual, norm_w, T, H, per, eps, zero_centered, mode, blocks, defer):
+        return self.lib.blz_comm_allreduce_norm(
             self.comm, _arr(a.peers(off_in)), _arr(a.peers(off_out)), _arr(a.peers(self.off_sf)), _arr(a.peers(self.off_rs)),
             VP(a.mcast(off_in) if mc else 0), VP(a.mcast(off_out) if mc else 0), VP(a.mcast(self.off_sf) if mc else 0),
             VP(a.mcast(self.off_rs) if mc else 0), VP(residual.data_ptr() if residual is not None else 0),
             VP(norm_w.data_ptr() if norm_w is not None else 0), T, H, per, eps, int(zero_centered), mode, blocks, int(defer),
             self._stream())
-        if rc != 0:
-            raise RuntimeError(f"blz_comm_allreduce_norm failed: {rc}")
+
+    def _result(self, a, off_out, mode, T, H, defer):
         self.launches += 1
         if mode == 0:
             return a.view(off_out, T * H * 2).view(torch.bfloat16).view(T, H)

@@ -147,6 +147,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 }
 
 // ------------------------------------------------------------------------------------------ fences
+// Release / acquire fence at system scope (other GPUs included).  This is what a flag protocol needs: the writes before it
+// (of this thread, and of the threads it has synchronised with) are visible to whoever acquires the flag written after
+// it.  __threadfence_system() is the sequentially-consistent fence, which costs several microseconds more per use when
+// peer writes are in flight and orders nothing that these protocols rely on.
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -177,6 +182,12 @@ __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.b
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// 1-D bulk copy shared → global (the destination may be a peer GPU's memory); both addresses 16-byte aligned, size a
+// multiple of 16.  Completion is tracked by the bulk async-group of the issuing thread (tma_store_commit / _wait_*).
+__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)), "r"(bytes)
                : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {

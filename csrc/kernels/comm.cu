@@ -39,6 +39,11 @@ struct CommParams {
   uint32_t* peer_sig[kMaxWorld];  // arrival counters of every rank, [kMaxWorld] uint32 each (slot = source rank)
   uint32_t* sig_expect;           // local: the count a consumer of a signalling kernel's result must wait for
   long long* prof;                // optional [8] nanosecond stamps of block 0 (entry, after each phase); null = off
+  // reduce-scatter by push: the partial rows this rank owns arrive in its LOCAL slot buffer [world][rows_per][H] (stored
+  // there by every rank's GEMM epilogue), announced by flag [source rank] reaching the value in *slot_epoch
+  const __nv_bfloat16* slots;     // null = the partial sums are in peer_in / mc_in and a rank barrier opens the kernel
+  const uint32_t* slot_flags;     // [world] local
+  const uint32_t* slot_epoch;     // local word, advanced by this rank's own producing GEMM
 };
 
 __device__ __forceinline__ void stamp(const CommParams& c, int k) {
@@ -85,7 +90,7 @@ __device__ __forceinline__ bool rank_barrier(const CommParams& c, int* ok_smem, 
   const uint32_t e = s_epoch;
   if (threadIdx.x < c.world) {
     const int peer = threadIdx.x;
-    if (phase >= 1) __threadfence_system();
+    if (phase >= 1) fence_acq_rel_sys();
     if (phase == 2) {
       // one arrival per block on every peer's counter; the consumer polls `world` words instead of one flag per block
       asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(c.peer_sig[peer] + c.rank), "r"(1u) : "memory");
@@ -101,7 +106,34 @@ __device__ __forceinline__ bool rank_barrier(const CommParams& c, int* ok_smem, 
         break;
       }
     }
-    if (phase == 0) __threadfence_system();
+    if (phase == 0) fence_acq_rel_sys();
+  }
+  __syncthreads();
+  return *ok_smem != 0;
+}
+
+// Entry of a kernel whose inputs were pushed into this rank's slot buffer: no barrier, no traffic - wait (bounded) until every
+// source rank's flag has reached the epoch of the reduction.  Keeps the barrier epochs in step for the exit phase.
+__device__ __forceinline__ bool wait_slots(const CommParams& c, int* ok_smem) {
+  if (threadIdx.x == 0) {
+    c.epoch[blockIdx.x] += 2;
+    *ok_smem = 1;
+  }
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const uint32_t want = *c.slot_epoch;
+    const uint32_t* f = c.slot_flags + threadIdx.x;
+    const long long t0 = clock64();
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if ((int32_t)(v - want) >= 0) break;
+      if (clock64() - t0 > c.spin_limit) {
+        atomicCAS(c.status, kOk, kErrFlagTimeout);
+        *ok_smem = 0;
+        break;
+      }
+    }
   }
   __syncthreads();
   return *ok_smem != 0;
@@ -257,7 +289,11 @@ __global__ void __launch_bounds__(1024) allreduce_norm_kernel(CommParams c, __nv
   pdl_wait();
   stamp(c, 0);
   if (defer_exit && blockIdx.x == 0 && threadIdx.x == 0) *c.sig_expect += gridDim.x;
-  if (!rank_barrier(c, &ok, 0)) return;
+  if (c.slots != nullptr) {
+    if (!wait_slots(c, &ok)) return;
+  } else if (!rank_barrier(c, &ok, 0)) {
+    return;
+  }
   stamp(c, 1);
   const int lo = c.rank * rows_per, hi = min(T, lo + rows_per);
   const int lane = threadIdx.x & 31;
@@ -271,7 +307,19 @@ __global__ void __launch_bounds__(1024) allreduce_norm_kernel(CommParams c, __nv
       u[ch] = make_uint4(0, 0, 0, 0);
       if (i < H) {
         float f[8];
-        reduce8<MC>(c, ((size_t)t * H + i) * 2, f);
+        if (c.slots != nullptr) {
+          // the partial rows of every source rank, from local memory, summed in rank order
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = 0.f;
+          for (int r = 0; r < c.world; ++r) {
+            const uint4 v = *reinterpret_cast<const uint4*>(c.slots + ((size_t)r * rows_per + (t - lo)) * H + i);
+            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] += bf2f(e[j]);
+          }
+        } else {
+          reduce8<MC>(c, ((size_t)t * H + i) * 2, f);
+        }
         __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&u[ch]);
         if (rr) {
           const uint4 ur = *reinterpret_cast<const uint4*>(rr + i);
@@ -438,16 +486,10 @@ BLZ_API int blz_comm_allreduce(void* h, void* const* in, void* const* out, void*
 // Fused all-reduce + residual + RMSNorm (+ quantise).  quant: 0 bf16 rows, 1 NVFP4, 2 MXFP8.
 // defer_exit: the kernel signals the peers and returns without waiting for theirs; the consumer of the result must wait
 // for this rank's arrival counters to reach the expected count (blz_comm_set_signals, blz_gemm_wait_flags).
-BLZ_API int blz_comm_allreduce_norm(void* h, void* const* in, void* const* out, void* const* sf, void* const* rs, void* mc_in,
-                                    void* mc_out, void* mc_sf, void* mc_rs, void* residual, const void* norm_w, int T, int H,
-                                    int rows_per, float eps, int zero_centered, int quant, int blocks, int defer_exit,
-                                    cudaStream_t s) {
-  BlzComm* c = reinterpret_cast<BlzComm*>(h);
-  if (!c || H % 128 || blocks < 1 || blocks > kMaxBlocks || quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
-  CommParams p = c->p;
-  fill(p, p.world, in, out, sf, rs, mc_in, mc_out, mc_sf, mc_rs);
+static int launch_norm(CommParams& p, bool mc, void* residual, const void* norm_w, int T, int H, int rows_per, float eps,
+                       int zero_centered, int quant, int blocks, int defer_exit, cudaStream_t s) {
+  if (H % 128 || blocks < 1 || blocks > kMaxBlocks || quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
   if (defer_exit && !p.sig_expect) return (int)cudaErrorInvalidValue;
-  const bool mc = mc_in && mc_out && (quant == 0 || mc_sf) && (quant != 1 || mc_rs);
   // threads: a multiple of 32 covering H/8 chunks in at most 4 rounds
   int ch = (H / 8 + 1023) / 1024;
   if (ch > 4) return (int)cudaErrorInvalidValue;
@@ -463,4 +505,36 @@ BLZ_API int blz_comm_allreduce_norm(void* h, void* const* in, void* const* out, 
 #undef BLZ_ARN2
 #undef BLZ_ARN3
   return (int)cudaGetLastError();
+}
+
+BLZ_API int blz_comm_allreduce_norm(void* h, void* const* in, void* const* out, void* const* sf, void* const* rs, void* mc_in,
+                                    void* mc_out, void* mc_sf, void* mc_rs, void* residual, const void* norm_w, int T, int H,
+                                    int rows_per, float eps, int zero_centered, int quant, int blocks, int defer_exit,
+                                    cudaStream_t s) {
+  BlzComm* c = reinterpret_cast<BlzComm*>(h);
+  if (!c) return (int)cudaErrorInvalidValue;
+  CommParams p = c->p;
+  fill(p, p.world, in, out, sf, rs, mc_in, mc_out, mc_sf, mc_rs);
+  p.slots = nullptr;
+  const bool mc = mc_in && mc_out && (quant == 0 || mc_sf) && (quant != 1 || mc_rs);
+  return launch_norm(p, mc, residual, norm_w, T, H, rows_per, eps, zero_centered, quant, blocks, defer_exit, s);
+}
+
+// The same reduction + residual + RMSNorm (+ quantise) for partial sums that every rank's GEMM pushed into this rank's slot
+// buffer (blz_gemm_push_rs): `slots` = the LOCAL buffer [world][rows_per][H], `flags` = the local flag row [world], `epoch` =
+// the local epoch word the producing GEMM advanced.  No entry barrier: the kernel waits (bounded) for the flags.  The results
+// are broadcast as in blz_comm_allreduce_norm (out / sf / rs per rank, or their multicast views).
+BLZ_API int blz_comm_slots_norm(void* h, const void* slots, const void* flags, const void* epoch, void* const* out,
+                                void* const* sf, void* const* rs, void* mc_out, void* mc_sf, void* mc_rs, void* residual,
+                                const void* norm_w, int T, int H, int rows_per, float eps, int zero_centered, int quant, int blocks,
+                                int defer_exit, cudaStream_t s) {
+  BlzComm* c = reinterpret_cast<BlzComm*>(h);
+  if (!c || !slots || !flags || !epoch) return (int)cudaErrorInvalidValue;
+  CommParams p = c->p;
+  fill(p, p.world, nullptr, out, sf, rs, nullptr, mc_out, mc_sf, mc_rs);
+  p.slots = reinterpret_cast<const __nv_bfloat16*>(slots);
+  p.slot_flags = reinterpret_cast<const uint32_t*>(flags);
+  p.slot_epoch = reinterpret_cast<const uint32_t*>(epoch);
+  const bool mc = mc_out && (quant == 0 || mc_sf) && (quant != 1 || mc_rs);
+  return launch_norm(p, mc, residual, norm_w, T, H, rows_per, eps, zero_centered, quant, blocks, defer_exit, s);
 }

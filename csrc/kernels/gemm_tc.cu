@@ -19,6 +19,13 @@
 
 namespace blz {
 
+__device__ __forceinline__ long long gt_now() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define GT_STAMP(i) do { if (p.stamps) p.stamps[(size_t)blockIdx.x * 8 + (i)] = gt_now(); } while (0)
+
 struct GemmParams {
   int M, N, K;               // K in elements
   void* C;                   // bf16 or fp32 [M, ldc]
@@ -38,6 +45,14 @@ struct GemmParams {
   uint32_t* epoch;           // local barrier epoch
   long long spin_limit;
   int rank, world;
+  // fused reduce-scatter by push (push_rows_per > 0): rank o owns rows [o * push_rows_per, (o + 1) * push_rows_per) of the
+  // summed output.  The epilogue stores each bf16 partial row straight into its owner's slot buffer
+  // [source rank][push_rows_per][N] through peer memory; the last CTA of this rank then raises flag [source rank] on every
+  // owner (release, system scope).  Nobody waits here: the owner's reduction kernel waits for its `world` flags.
+  __nv_bfloat16* push_slot[8];
+  uint32_t* push_flag[8];
+  int push_rows_per;
+  long long* stamps;         // optional diagnostics: [gridDim.x][8] global-timer stamps of the pushed epilogue (null = off)
   const int* tile_expert;    // grouped GEMM: expert of every 128-row M tile (-1 = skip); B / alpha / sfb rows are offset by expert * N
   // activations still in flight from the peers (fused all-reduce + norm that signals instead of waiting): the producer
   // sends the first weight tiles, then waits until counter[r] >= *wait_expect for every rank r, then loads A
@@ -71,11 +86,13 @@ struct GemmCfg {
   static constexpr int SFA_BYTES = SF_ATOMS * 512;
   static constexpr int SFB_BYTES = SF_ATOMS * 512 * (BN / 128);
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (SF_ATOMS ? 5 : 6);
+  static constexpr int STAGES = (BN == 256) ? 4 : 5;
   static constexpr int ACC_BUFS = (BN == 256 && SF_ATOMS) ? 1 : 2;
   static constexpr int SF_COLS_PER_STAGE = SF_ATOMS * 4 * (1 + BN / 128);
   static constexpr int SF_COL0 = ACC_BUFS * BN;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;   // + 8*BN*4 static
+  static constexpr int PUSH_ROW = 272;                                  // 256 bytes of a tile row + 16 (no bank conflicts)
+  static constexpr int PUSH_STAGE = (BN == 128) ? 4 * 32 * PUSH_ROW : 0; // per-warp [32 rows] staging of the pushed epilogue
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + PUSH_STAGE;   // + 8*BN*4 static
   static_assert(SF_COL0 + STAGES * SF_COLS_PER_STAGE <= 512, "TMEM budget");
 };
 
@@ -98,6 +115,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* acc_empty = acc_full + ACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* push_stage = reinterpret_cast<uint8_t*>(bars) + 256;   // [4 warps][32 rows][PUSH_ROW bytes]
   __shared__ __align__(16) float s_alpha[4][BN];
   __shared__ __align__(16) float s_bias[4][BN];
 
@@ -119,6 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (threadIdx.x == 0) GT_STAMP(0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -289,6 +308,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       __syncwarp();
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, p.status)) break;
       tc_fence_after();
+      if (threadIdx.x == 64) GT_STAMP(1);
       float best_v = -INFINITY;
       int best_i = 0x7fffffff;
 #pragma unroll 1
@@ -362,7 +382,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const float o2 = fmaf(__uint_as_float(r[i + 2]) * rs, a0.z, b0.z), o3 = fmaf(__uint_as_float(r[i + 3]) * rs, a0.w, b0.w);
               const float o4 = fmaf(__uint_as_float(r[i + 4]) * rs, a1.x, b1.x), o5 = fmaf(__uint_as_float(r[i + 5]) * rs, a1.y, b1.y);
               const float o6 = fmaf(__uint_as_float(r[i + 6]) * rs, a1.z, b1.z), o7 = fmaf(__uint_as_float(r[i + 7]) * rs, a1.w, b1.w);
-              if (p.mc_out != nullptr) {
+              if (p.push_rows_per > 0) {
+                // staged per warp as plain tile rows (272-byte pitch: the 16-byte stores of eight rows fall on distinct banks)
+                if constexpr (BN == 128)
+                  *reinterpret_cast<uint4*>(push_stage + ((warp - 2) * 32 + lane) * Cfg::PUSH_ROW + (c * 32 + i) * 2) =
+                      make_uint4(pack_bf16x2(o0, o1), pack_bf16x2(o2, o3), pack_bf16x2(o4, o5), pack_bf16x2(o6, o7));
+              } else if (p.mc_out != nullptr) {
                 if (whole) {
                   const size_t off = ((size_t)row * p.ldc + col0 + i) * 2;
                   asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1,%2,%3,%4};"
@@ -386,6 +411,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
         }
+        if constexpr (!OUT_F32 && BN == 128) {
+          if (p.push_rows_per > 0 && c == BN / 32 - 1) {
+            // the warp's 32 rows of the tile are staged: each lane sends its row (256 contiguous bytes) into the owner rank's
+            // slot buffer with one bulk copy - asynchronous, so the SM does not sit on NVLink write round trips
+            fence_async_smem();
+            __syncwarp();
+            if (threadIdx.x == 64) GT_STAMP(2);
+            const int colt = nt * BN;
+            if (row < p.M && colt < p.N) {
+              const int owner = row / p.push_rows_per;
+              __nv_bfloat16* prow = p.push_slot[owner] +
+                                    ((size_t)p.rank * p.push_rows_per + (row - owner * p.push_rows_per)) * p.N + colt;
+              const int bytes = min(BN, p.N - colt) * 2;
+              bulk_store(prow, push_stage + ((warp - 2) * 32 + lane) * Cfg::PUSH_ROW, (uint32_t)bytes);
+            }
+            tma_store_commit();
+            tma_store_wait_read();      // the staging rows may be overwritten by the next tile
+            __syncwarp();
+            if (threadIdx.x == 64) GT_STAMP(3);
+          }
+        }
       }
       if (OUT_F32 && p.amax_val != nullptr && row < p.M) {
         p.amax_val[(size_t)nt * p.M + row] = best_v;
@@ -396,21 +442,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (lane == 0) mbar_arrive(&acc_empty[ab]);
     }
   }
+  if (p.push_rows_per > 0 && warp >= 2) tma_store_wait_all();   // this thread's pushed rows have been written
+  if (threadIdx.x == 64) GT_STAMP(4);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) GT_STAMP(5);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
-  if (p.mc_out != nullptr && threadIdx.x == 0) {
-    // every CTA's reductions are ordered before its count; the last CTA of this rank tells the peers and waits for them
-    __threadfence_system();
+  if (p.push_rows_per > 0 && threadIdx.x == 0) {
+    // every CTA's peer stores are ordered before its count; the last CTA of this rank raises its flag on every owner
+    fence_acq_rel_sys();
+    GT_STAMP(6);
     const unsigned prev = atomicAdd(p.done_ctr, 1u);
     if (prev == gridDim.x - 1) {
       *p.done_ctr = 0;
       const uint32_t e = *p.epoch + 1;
       *p.epoch = e;
-      __threadfence_system();
+      fence_acq_rel_sys();
+      for (int r = 0; r < p.world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r] + p.rank), "r"(e) : "memory");
+    }
+  } else if (p.mc_out != nullptr && threadIdx.x == 0) {
+    // every CTA's reductions are ordered before its count; the last CTA of this rank tells the peers and waits for them
+    fence_acq_rel_sys();
+    const unsigned prev = atomicAdd(p.done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.done_ctr = 0;
+      const uint32_t e = *p.epoch + 1;
+      *p.epoch = e;
+      fence_acq_rel_sys();
       for (int r = 0; r < p.world; ++r)
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_pad[r] + p.rank), "r"(e) : "memory");
       for (int r = 0; r < p.world; ++r) {
@@ -454,6 +516,15 @@ struct FuseArgs {
   int rank = 0, world = 1;
 };
 thread_local FuseArgs g_fuse;
+struct PushArgs {
+  __nv_bfloat16* slot[8] = {nullptr};
+  uint32_t* flag[8] = {nullptr};
+  unsigned* done_ctr = nullptr;
+  uint32_t* epoch = nullptr;
+  int rank = 0, world = 1, rows_per = 0;
+};
+thread_local PushArgs g_push;
+thread_local long long* g_stamps = nullptr;
 struct WaitArgs {
   const uint32_t* pad = nullptr;
   const uint32_t* epoch = nullptr;
@@ -472,8 +543,9 @@ namespace blz {
 // The one-shot arming (fused all-reduce, peer wait, arg-max epilogue) applies to exactly one GEMM call of this thread.
 // Any GEMM entry point clears it on entry; an entry that cannot honour it reports whether something was armed.
 bool gemm_oneshot_take_unsupported() {
-  const bool armed = g_fuse.mc_out != nullptr || g_wait.pad != nullptr || g_amax.val != nullptr;
+  const bool armed = g_fuse.mc_out != nullptr || g_wait.pad != nullptr || g_amax.val != nullptr || g_push.rows_per > 0;
   g_fuse.mc_out = nullptr;
+  g_push.rows_per = 0;
   g_wait.pad = nullptr;
   g_amax.val = nullptr; g_amax.idx = nullptr;
   return armed;
@@ -518,6 +590,28 @@ BLZ_API int blz_gemm_fuse_allreduce(void* mc_out, void* done_ctr, void* const* p
   return 0;
 }
 
+// Diagnostics: the NEXT blz_gemm_tc call records global-timer stamps per CTA in stamps[blockIdx.x][8]: 0 set-up done,
+// 1 first accumulator complete, 2 tile staged, 3 rows handed to the copy engine, 4 pushed rows written, 5 CTA joined,
+// 6 system fence done (pushed epilogue only for 2-6).
+BLZ_API int blz_gemm_debug_stamps(void* stamps) { g_stamps = reinterpret_cast<long long*>(stamps); return 0; }
+
+// Arms the NEXT blz_gemm_tc call on this thread as a fused GEMM + reduce-scatter by push: the bf16 output rows are not
+// written to C but stored into the slot buffer of the rank that owns them (slots[o] = rank o's buffer
+// [world][rows_per][N], bf16; row r belongs to rank r / rows_per), and when this rank's last CTA is done it writes the
+// advanced epoch to flags[o][rank] on every owner.  done_ctr / epoch: zero-initialised local device words; the epoch word is
+// what the owner's reduction kernel compares its flags with (blz_comm_slots_norm).  Needs N % 32 == 0.
+BLZ_API int blz_gemm_push_rs(void* const* slots, void* const* flags, void* done_ctr, void* epoch, int rank, int world, int rows_per) {
+  if (!slots || !flags || !done_ctr || !epoch || world < 1 || world > 8 || rows_per < 1) return (int)cudaErrorInvalidValue;
+  for (int r = 0; r < world; ++r) {
+    g_push.slot[r] = reinterpret_cast<__nv_bfloat16*>(slots[r]);
+    g_push.flag[r] = reinterpret_cast<uint32_t*>(flags[r]);
+  }
+  g_push.done_ctr = reinterpret_cast<unsigned*>(done_ctr);
+  g_push.epoch = reinterpret_cast<uint32_t*>(epoch);
+  g_push.rank = rank; g_push.world = world; g_push.rows_per = rows_per;
+  return 0;
+}
+
 // kind: 0 bf16, 1 nvfp4, 2 mxfp8, 3 fp8.  A [M, K] and B [N, K] row-major (packed bytes for 4/8-bit kinds);
 // lda / ldb in BYTES.  out_f32: C is fp32, else bf16; ldc in elements.  bn: 128 or 256 (0 = choose).
 // act = 1: B's rows come in groups of [16 gate | 16 up] features and C is bf16 [M, N/2] = silu(gate) * up (ldc % 8 == 0).
@@ -531,6 +625,8 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   const FuseArgs fuse = g_fuse;
   const WaitArgs wait = g_wait;
   const AmaxArgs amax = g_amax;
+  const PushArgs push = g_push;
+  g_push.rows_per = 0;
   g_fuse.mc_out = nullptr;
   g_wait.pad = nullptr;
   g_amax.val = nullptr; g_amax.idx = nullptr;
@@ -556,16 +652,29 @@ BLZ_API int blz_gemm_tc(int kind, const void* A, long long lda, const void* B, l
   if (act && (out_f32 || N % 32 || (ldc & 7) || tile_expert)) return (int)cudaErrorInvalidValue;
   if (b_kt > 0 && tile_expert) return (int)cudaErrorInvalidValue;
   p.mc_out = nullptr; p.done_ctr = nullptr; p.epoch = nullptr; p.spin_limit = 0; p.rank = 0; p.world = 1;
+  p.push_rows_per = 0;
+  p.stamps = g_stamps;
+  g_stamps = nullptr;
+  if (push.rows_per > 0) {
+    if (out_f32 || (N % 8) || act || tile_expert || fuse.mc_out || amax.val ||
+        (long long)push.rows_per * push.world < M)
+      return (int)cudaErrorInvalidValue;
+    p.push_rows_per = push.rows_per;
+    for (int r = 0; r < push.world; ++r) { p.push_slot[r] = push.slot[r]; p.push_flag[r] = push.flag[r]; }
+  }
   p.wait_pad = wait.pad; p.wait_epoch = wait.epoch; p.wait_world = wait.world;
   p.wait_limit = wait.limit;
   p.amax_val = amax.val; p.amax_idx = amax.idx;
   if (p.amax_val && (!out_f32 || tile_expert)) return (int)cudaErrorInvalidValue;
-  if (p.amax_val) bn = 128;
+  if (p.amax_val || push.rows_per > 0) bn = 128;
   if (fuse.mc_out) {
     if (out_f32 || (N % 32)) return (int)cudaErrorInvalidValue;
     p.mc_out = fuse.mc_out; p.done_ctr = fuse.done_ctr; p.epoch = fuse.epoch; p.spin_limit = fuse.spin_limit;
     p.rank = fuse.rank; p.world = fuse.world;
     for (int r = 0; r < fuse.world; ++r) p.peer_pad[r] = fuse.peer_pad[r];
+  }
+  if (push.rows_per > 0) {
+    p.done_ctr = push.done_ctr; p.epoch = push.epoch; p.rank = push.rank; p.world = push.world;
   }
   const uint64_t b_rows = (uint64_t)N * (tile_expert ? (num_experts > 0 ? num_experts : 1) : 1);
   if (tile_expert && N % bn) return (int)cudaErrorInvalidValue;

@@ -103,6 +103,43 @@ def main():
                 xd = quant.mxfp8_dequantize(out.data.view(torch.float8_e4m3fn), sf)
                 e = (xd - want_h.float()).abs().mean().item()
                 assert e < 0.04, f"mxfp8 rows err {e}"
+    elif case == "push_reduce_norm":
+        from blaze_b200.ops import get_ops
+        ops = get_ops(dev)
+        w = (1 + 0.1 * torch.randn(H, generator=torch.Generator(device=dev).manual_seed(7), device=dev)).bfloat16()
+        res_full = torch.randn(512, H, generator=torch.Generator(device=dev).manual_seed(11), device=dev).bfloat16()
+        for it, (fmt, M, K, qfmt) in enumerate(((Format.DENSE, 200, 1024, None), (Format.NVFP4, 256, 2048, Format.NVFP4),
+                                                (Format.NVFP4, 77, 1024, Format.MXFP8), (Format.DENSE, 300, 512, None),
+                                                (Format.NVFP4, 256, 2048, Format.NVFP4))):
+            lin = Linear.from_dense(torch.randn(H, K, generator=g, device=dev) * 0.05, fmt)
+            x = torch.randn(M, K, generator=g, device=dev).bfloat16()
+            local = ops.linear(lin, x, wide=False, sk=False)                  # this rank's partial sums, bf16
+            tot = local.float().clone()
+            dist.all_reduce(tot)
+            tot = tot.bfloat16()
+            res = fused.shard_rows(res_full[:M])
+            nxt = Linear.from_dense(torch.randn(64, H, device=dev) * 0.02, qfmt) if qfmt else None
+            pushed = fused.gemm_push(ops, lin, x, M)
+            out = fused.reduce_norm(pushed, res, w, 1e-6, False, nxt)
+            torch.cuda.synchronize()
+            want_h, want_res = ref.rmsnorm(tot, w, 1e-6, res_full[:M])
+            per = fused.rows_per(M)
+            lo, hi = rank * per, min(M, rank * per + per)
+            tol = 0.07 * max(1.0, want_res.float().abs().max().item() / 4)
+            assert (res[:hi - lo].float() - want_res[lo:hi].float()).abs().max().item() < tol, f"case {it}: residual shard"
+            if qfmt is None:
+                assert (out.float() - want_h.float()).abs().max().item() < 0.1, f"case {it}: normed rows"
+            elif qfmt == Format.NVFP4:
+                sf = quant.unswizzle_sf_128x4(out.sf, M, H // 16).view(torch.float8_e4m3fn)
+                xd = quant.nvfp4_dequantize(out.data, sf, out.row_scale)
+                e = (xd - want_h.float()).abs().mean().item()
+                assert e < 0.12, f"case {it}: nvfp4 rows err {e}"
+            else:
+                sf = quant.unswizzle_sf_128x4(out.sf, M, H // 32)
+                xd = quant.mxfp8_dequantize(out.data.view(torch.float8_e4m3fn), sf)
+                e = (xd - want_h.float()).abs().mean().item()
+                assert e < 0.04, f"case {it}: mxfp8 rows err {e}"
+            dist.barrier()
     elif case == "model":
         cfg = ModelConfig(vocab_size=2048, hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2, head_dim=128,
                           intermediate_size=1024, rope=RopeConfig(theta=1e6))
