@@ -169,13 +169,14 @@ def build_llm(ns: argparse.Namespace):
         raise SystemExit(f"--tp {ns.tp}: launch one process per GPU, e.g. python -m torch.distributed.run "
                          f"--nproc-per-node {ns.tp} --master-addr 127.0.0.1 -m blaze_b200 …")
     group = None
+    pp = max(int(getattr(ns, "pp", 1) or 1), 1)
     if world > 1:
         local = int(os.environ.get("LOCAL_RANK", "0"))
         if device.startswith("cuda"):
             torch.cuda.set_device(local)
             device = f"cuda:{local}"
-        group = TPGroup.from_env(device)
-    tp = TPInfo(group.rank, group.world, group, ep=ns.ep) if group else TPInfo()
+        group = TPGroup.from_env(device, pp=pp)
+    tp = TPInfo(group.rank, group.world, group if group.world > 1 else None, ep=ns.ep) if group else TPInfo()
     kv = ns.kv_cache_dtype or "auto"
     if kv.startswith("nvfp4"):
         raise SystemExit(f"--kv-cache-dtype {kv}: 4-bit KV pages are not built; use fp8 (the compact format here), bf16 or fp32")
@@ -186,7 +187,14 @@ def build_llm(ns: argparse.Namespace):
         raise SystemExit(f"--pp {ns.pp} --tp {ns.tp}: launch {ns.pp * max(ns.tp, 1)} processes (one per GPU), e.g. python -m "
                          f"torch.distributed.run --nproc-per-node {ns.pp * max(ns.tp, 1)} --master-addr 127.0.0.1 -m blaze_b200 …")
     kv_tokens = 0 if str(ns.kv_tokens) == "auto" else int(ns.kv_tokens)
+    stage_range = None
+    if group is not None and group.stages > 1:
+        from .config import ModelConfig, named_config
+        from .parallel.pp import stage_layers
+        mcfg = ModelConfig.load(ns.model) if (ns.model and os.path.isdir(ns.model)) else named_config(ns.model or "tiny")
+        stage_range = stage_layers(mcfg.num_layers, group.stages, group.stage)
     llm = LLM(ns.model or "tiny", weight_format=ns.weights or "dense", device=device, tp=tp, kv_cache_dtype=kv,
+              stage_layers=stage_range,
               kv_tokens=kv_tokens, max_seqs=ns.max_seqs or 256, max_model_len=ns.max_model_len or 4096,
               chunk=ns.chunk or 2048, enable_prefix_caching=not ns.disable_prefix_caching,
               cache_slots=ns.prompt_cache_slots or 4, use_graphs=not ns.no_graphs,
@@ -195,7 +203,11 @@ def build_llm(ns: argparse.Namespace):
               draft_tree_width=int(getattr(ns, "draft_tree_width", 1) or 1),
               tune=bool(getattr(ns, "tune", False)), draft_model=getattr(ns, "draft_model", None), draft_head_vocab=int(getattr(ns, "mtp_head_vocab", 0) or 0),
               draft_tree_depth=int(ns.draft_tree_depth or 4), max_verify=int(ns.max_verify or 8))
-    if group is not None and ns.comm == "fused" and device.startswith("cuda"):
+    llm.group = group
+    if group is not None:
+        from .parallel.worker import attach
+        attach(llm, group, int(getattr(ns, "pp_chunk", 512) or 512))
+    if group is not None and group.world > 1 and ns.comm == "fused" and device.startswith("cuda"):
         from .parallel.symm import SymmAllReduce
         group.fused = SymmAllReduce.create(group, device, max_rows=(ns.chunk or 2048) + (ns.max_seqs or 256) + 64,
                                            hidden=llm.model.cfg.hidden_size)
@@ -214,10 +226,30 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if ns.command == "serve":
         from .server.run import serve
         return serve(ns)
+    if ns.command in ("generate", "score"):
+        llm = build_llm(ns)
+        grp = getattr(llm, "group", None)
+        if grp is not None and grp.global_rank != 0:
+            from .parallel.worker import follow
+            return follow(llm)            # the other ranks execute the steps that rank 0 plans
+        try:
+            return _run_offline(ns, llm)
+        finally:
+            if getattr(llm, "leader", None) is not None:
+                llm.leader.quit()
+    if ns.command == "stage-worker":
+        from .remote import serve_stage
+        return serve_stage(ns)
+    if ns.command == "vision-check":
+        from .models.vision import check_reference
+        return check_reference(ns.model, ns.image)
+    return 2
+
+
+def _run_offline(ns, llm) -> int:
     if ns.command == "generate":
         from .sampler import SamplingParams
         from .text import load_tokenizer
-        llm = build_llm(ns)
         tok = load_tokenizer(ns.model if ns.model and os.path.isdir(ns.model) else None, llm.model.cfg.vocab_size)
         ids = [int(x) for x in ns.prompt_ids.split(",")] if ns.prompt_ids else tok.encode(ns.prompt or "hello")
         out = llm.generate([ids], SamplingParams(temperature=ns.temperature, max_tokens=ns.max_tokens))[0]
@@ -225,7 +257,6 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         return 0
     if ns.command == "score":
         import torch
-        llm = build_llm(ns)
         ids = [int(x) for x in ns.prompt_ids.split(",")]
         s = llm.engine.open_from()
         logits = llm.engine.forward(llm.engine.plan([(s, ids, len(ids))]), "logits")
@@ -233,10 +264,4 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         scores = [float(lp[i, ids[i + 1]]) for i in range(len(ids) - 1)]
         print(json.dumps({"logprobs": scores, "sum": sum(scores)}))
         return 0
-    if ns.command == "stage-worker":
-        from .remote import serve_stage
-        return serve_stage(ns)
-    if ns.command == "vision-check":
-        from .models.vision import check_reference
-        return check_reference(ns.model, ns.image)
     return 2

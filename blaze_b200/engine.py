@@ -70,6 +70,19 @@ class PageAllocator:
                 raise RuntimeError(f"page {p} released twice")
 
 
+def make_page_allocator(num_pages: int):
+    """The page allocator of the host runtime library (C++, ``csrc/runtime/repack_pages.cpp``) when that library is
+    built, else the Python twin above; both have the same interface and the same allocation order."""
+    import os
+    if os.environ.get("BLAZE_NATIVE_PAGES", "1") != "0":
+        try:
+            from .runtime import NativePages
+            return NativePages(num_pages)
+        except Exception:
+            pass
+    return PageAllocator(num_pages)
+
+
 @dataclass
 class Seq:
     """A live sequence row: its block-table row, pages and KV length (``engine.rs:24``)."""
@@ -125,8 +138,9 @@ class Engine:
             raise ValueError("kv_rotate needs a power-of-two head_dim")
         model.kv_rotate = bool(ecfg.kv_rotate)      # read by the attention prep of both op sets
         self.kv = KVCache(cfg, self.num_pages, ecfg.max_seqs, self.max_pages_per_seq, ecfg.kv_dtype, self.device,
-                          layout, tpw, state_rows=ecfg.max_seqs + ecfg.snapshot_rows)
-        self.pages = PageAllocator(self.num_pages)
+                          layout, tpw, state_rows=ecfg.max_seqs + ecfg.snapshot_rows,
+                          layers=(model.first_layer, model.last_layer))
+        self.pages = make_page_allocator(self.num_pages)
         self.free_rows: List[int] = list(range(ecfg.max_seqs - 1, -1, -1))
         self.free_state_rows: List[int] = list(range(ecfg.max_seqs + ecfg.snapshot_rows - 1, ecfg.max_seqs - 1, -1))
         self.seqs: Dict[int, Seq] = {}

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import os
 
-from typing import Sequence, Dict, List, Optional
+from typing import Tuple, Sequence, Dict, List, Optional
 
 import numpy as np
 import torch
@@ -39,15 +39,16 @@ HEAD_MAJOR = os.environ.get("BLAZE_KV_HEAD_MAJOR", "0") == "1"
 class KVCache:
     def __init__(self, cfg: ModelConfig, num_pages: int, max_seqs: int, max_pages_per_seq: int,
                  kv_dtype: str = "bf16", device="cpu", layout: str = "logical", tp_world: int = 1,
-                 state_rows: Optional[int] = None):
+                 state_rows: Optional[int] = None, layers: Optional[Tuple[int, int]] = None):
         self.cfg, self.num_pages, self.max_seqs = cfg, num_pages, max_seqs
         self.max_pages_per_seq = max_pages_per_seq
         self.kv_dtype, self.layout, self.device = kv_dtype, layout, torch.device(device)
         self.kv_heads = max(cfg.num_kv_heads // tp_world, 1)
         D = cfg.head_dim
         tdt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[kv_dtype]
-        self.attn_layers = [i for i in range(cfg.num_layers) if cfg.layer_type(i) == "full_attention"]
-        self.gdn_layers = [i for i in range(cfg.num_layers) if cfg.layer_type(i) == "linear_attention"]
+        lo, hi = layers if layers is not None else (0, cfg.num_layers)      # a pipeline stage holds the caches of its layers only
+        self.attn_layers = [i for i in range(lo, hi) if cfg.layer_type(i) == "full_attention"]
+        self.gdn_layers = [i for i in range(lo, hi) if cfg.layer_type(i) == "linear_attention"]
         self.k: Dict[int, torch.Tensor] = {}
         self.v: Dict[int, torch.Tensor] = {}
         self.kv: Dict[int, torch.Tensor] = {}

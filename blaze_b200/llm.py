@@ -44,22 +44,24 @@ class LLM:
                  eos_ids: Sequence[int] = (), drafter=None, max_step_tokens: int = 8192, warm_graphs: bool = False,
                  kv_host_tokens: int = 0, schedule: str = "interleave", kv_rotate: bool = False,
                  draft_tree_width: int = 1, draft_model: Optional[str] = None, draft_head_vocab: int = 0,
-                 draft_tree_depth: int = 4, watchdog: bool = False, max_verify: int = 8, tune: bool = False):
+                 draft_tree_depth: int = 4, watchdog: bool = False, max_verify: int = 8, tune: bool = False,
+                 stage_layers: Optional[tuple] = None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
         tpi = tp if isinstance(tp, TPInfo) else TPInfo()
         fmt = {"dense": Format.DENSE, "bf16": Format.DENSE, "nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8,
                "fp8_block": Format.FP8_BLOCK, "fp8": Format.FP8_CHANNEL}[weight_format]
+        lo, hi = stage_layers if stage_layers is not None else (0, None)     # this rank's pipeline stage
         with log.Stage("model"):
             if isinstance(model, Model):
                 self.model = model
             elif isinstance(model, ModelConfig):
-                self.model = Model.random_init(model, fmt, seed, self.device, dtype, tpi)
+                self.model = Model.random_init(model, fmt, seed, self.device, dtype, tpi, first_layer=lo, last_layer=hi)
             elif os.path.isdir(model):
-                self.model = Model.load(model, self.device, dtype, tpi)
+                self.model = Model.load(model, self.device, dtype, tpi, first_layer=lo, last_layer=hi)
             else:
-                self.model = Model.random_init(named_config(model), fmt, seed, self.device, dtype, tpi)
+                self.model = Model.random_init(named_config(model), fmt, seed, self.device, dtype, tpi, first_layer=lo, last_layer=hi)
         cfg = self.model.cfg
         if tune and self.model.ops.is_cuda:
             # time the GEMM kernel variants of this model's layer shapes once per device (cached on disk) and route by the result

@@ -22,13 +22,25 @@ class TPGroup:
         self.bytes_reduced = 0
         self.calls = 0
 
+    # pipeline layout (one stage unless from_env is given pp > 1): ranks are stage-major, global rank = stage * world + rank
+    stage, stages = 0, 1
+
+    @property
+    def global_rank(self) -> int:
+        return self.stage * self.world + self.rank
+
     @classmethod
-    def from_env(cls, device=None, backend: Optional[str] = None) -> Optional["TPGroup"]:
-        """Join the process group described by RANK / WORLD_SIZE / MASTER_* (torchrun)."""
+    def from_env(cls, device=None, backend: Optional[str] = None, pp: int = 1) -> Optional["TPGroup"]:
+        """Join the process group described by RANK / WORLD_SIZE / MASTER_* (torchrun).  With ``pp`` pipeline stages the
+        WORLD_SIZE ranks form ``pp`` stages of ``WORLD_SIZE / pp`` tensor-parallel ranks each; the returned group does the
+        collectives of this rank's stage, ``ctrl`` spans every rank (step plans), and point-to-point hand-offs between
+        stages use the default group."""
         world = int(os.environ.get("WORLD_SIZE", "1"))
         if world == 1:
             return None
         rank = int(os.environ["RANK"])
+        if pp > 1:
+            return cls._from_env_pp(device, backend, pp, rank, world)
         if not dist.is_initialized():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", "29500")
@@ -43,6 +55,30 @@ class TPGroup:
             # Control messages (step plans, quit) travel over a host-side group: an object broadcast over NCCL is ordered
             # behind the kernels already queued on the stream and would make every rank wait for the GPU each step.
             g.ctrl = dist.new_group(backend="gloo")
+        return g
+
+    @classmethod
+    def _from_env_pp(cls, device, backend, pp: int, grank: int, gworld: int) -> "TPGroup":
+        if gworld % pp:
+            raise ValueError(f"{gworld} ranks do not split into {pp} pipeline stages")
+        tpw = gworld // pp
+        if not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29500")
+            if backend is None:
+                backend = "nccl" if (device is not None and torch.device(device).type == "cuda") else "gloo"
+            kw = {"device_id": torch.device(device)} if backend == "nccl" else {}
+            dist.init_process_group(backend, rank=grank, world_size=gworld, **kw)
+        stage, tpr = grank // tpw, grank % tpw
+        mine = None
+        for s in range(pp):                       # every rank takes part in the creation of every stage's group
+            ranks = list(range(s * tpw, (s + 1) * tpw))
+            pg = dist.new_group(ranks) if tpw > 1 else None
+            if s == stage:
+                mine = pg
+        g = cls(tpr, tpw, mine, device)
+        g.stage, g.stages = stage, pp
+        g.ctrl = dist.new_group(backend="gloo") if dist.get_backend() == "nccl" else dist.group.WORLD
         return g
 
     # ------------------------------------------------------------------ collectives
@@ -91,4 +127,5 @@ class TPGroup:
         return box[0]
 
     def barrier(self):
-        dist.barrier(group=self.pg)
+        if self.pg is not None or self.stages == 1:
+            dist.barrier(group=self.pg)

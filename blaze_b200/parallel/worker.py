@@ -20,6 +20,17 @@ class Leader:
         self._forward = engine.forward
         self._sent = {}          # row -> page list as the followers know it
         engine.forward = self.forward
+        ct, cs = engine.commit_tree, engine.commit_state
+
+        def commit_tree(items):
+            self.call("commit_tree", [(s.row, base, list(path)) for s, base, path in items])
+            return ct(items)
+
+        def commit_state(items):
+            if engine.kv.gdn_layers and items:
+                self.call("commit_state", [(s.row, keep) for s, keep in items])
+            return cs(items)
+        engine.commit_tree, engine.commit_state = commit_tree, commit_state
 
     def forward(self, chunks, mode="greedy", hidden_in=None, feedback=False):
         # only the rows whose page list changed since the last step travel (a decode step changes one row in sixteen)
@@ -32,9 +43,14 @@ class Leader:
         gone = [r for r in self._sent if r not in live]
         for r in gone:
             del self._sent[r]
-        plan = ("step", mode, [(c.slot, list(c.tokens), c.start_pos, c.want_logits) for c in chunks], changed, gone, feedback)
+        plan = ("step", mode, [(c.slot, list(c.tokens), c.start_pos, c.want_logits, c.parents, c.defer_state) for c in chunks],
+                changed, gone, feedback)
         self.group.broadcast_object(plan, 0)
         return self._forward(chunks, mode, hidden_in, feedback)
+
+    def call(self, method: str, *args):
+        """Mirror an engine call that is not a step (KV row moves after a tree step, replay of deferred recurrent state)."""
+        self.group.broadcast_object(("call", method, args), 0)
 
     def quit(self):
         self.group.broadcast_object(("quit",), 0)
@@ -42,12 +58,20 @@ class Leader:
 
 def follow(llm) -> int:
     """Follower loop: mirror rank 0's sequence table and run the same steps."""
-    eng, group = llm.engine, llm.model.tp.group
+    eng = llm.engine
+    group = getattr(llm, "group", None) or llm.model.tp.group
     from ..engine import Seq
     while True:
         msg = group.broadcast_object(None, 0)
         if msg[0] == "quit":
             return 0
+        if msg[0] == "call":
+            _, method, args = msg
+            if method == "commit_tree":
+                eng.commit_tree([(eng.seqs[row], base, path) for row, base, path in args[0]])
+            elif method == "commit_state":
+                eng.commit_state([(eng.seqs[row], keep) for row, keep in args[0]])
+            continue
         _, mode, raw, changed, gone, feedback = msg
         # mirror the page tables (same allocator decisions are implied by copying rank 0's)
         for row, pg in changed.items():
@@ -63,5 +87,24 @@ def follow(llm) -> int:
                 s.pages = list(pg)
         for row in gone:
             eng.seqs.pop(row, None)
-        chunks = [SeqChunk(slot, toks, start, want) for slot, toks, start, want in raw]
+        chunks = [SeqChunk(slot, toks, start, want, parents=parents, defer_state=defer) for slot, toks, start, want, parents, defer in raw]
+        for c in chunks:                      # the follower's sequence lengths follow the plan (tree commits read them)
+            s = eng.seqs.get(c.slot)
+            if s is not None:
+                s.length = c.start_pos + len(c.tokens)
         eng.forward(chunks, mode, feedback=feedback)
+
+
+def attach(llm, group, pp_chunk: int = 512):
+    """Connect one rank's engine to the others: pipeline stages first (``engine.forward`` then runs this stage's part of
+    a step), then the step protocol — global rank 0 gets a :class:`Leader` and returns it, every other rank should call
+    :func:`follow`."""
+    if group is None:
+        return None
+    if getattr(group, "stages", 1) > 1:
+        from .pp import Pipeline
+        llm.pipeline = Pipeline(llm.engine, group, pp_chunk)
+    if group.global_rank == 0:
+        llm.leader = Leader(llm.engine, group)
+        return llm.leader
+    return None

@@ -34,9 +34,7 @@ def serve(ns) -> int:
     def load():
         try:
             llm = build_llm(ns)
-            if llm.model.tp.world > 1:
-                from ..parallel.worker import Leader
-                st.leader = Leader(llm.engine, llm.model.tp.group)
+            st.leader = getattr(llm, "leader", None)       # build_llm attached the step protocol when there are other ranks
             tok = load_tokenizer(ns.model if ns.model and os.path.isdir(ns.model) else None, llm.model.cfg.vocab_size)
             vision = None
             if llm.model.cfg.vision_config and ns.model and os.path.isdir(ns.model):

@@ -80,12 +80,23 @@ class Checkpoint:
         if not paths:
             raise FileNotFoundError(f"no *.safetensors under {model_dir}")
         self.files = [_File(p) for p in paths]
+        # Large tensors are read by the C++ reader of the host runtime library (several pread threads per tensor into
+        # pinned staging memory, csrc/runtime/safetensors.cpp) when it is built; small ones are views of the mapping.
+        self.native = None
+        if os.environ.get("BLAZE_NATIVE_READER", "1") != "0":
+            try:
+                from .runtime import NativeCheckpoint
+                self.native = NativeCheckpoint(model_dir)
+            except Exception:
+                self.native = None
         self.index: Dict[str, TensorInfo] = {}
         for f in self.files:
             for k, v in f.tensors.items():
                 if k in self.index:
                     raise ValueError(f"tensor {k} appears in two shards")
                 self.index[k] = v
+
+    NATIVE_MIN_BYTES = 1 << 20
 
     @classmethod
     def open(cls, model_dir: str) -> "Checkpoint":
@@ -104,6 +115,9 @@ class Checkpoint:
         info = self.index.get(name)
         if info is None:
             raise KeyError(f"tensor {name} not in checkpoint {self.dir}")
+        if self.native is not None and info.end - info.begin >= self.NATIVE_MIN_BYTES and name in self.native:
+            t = self.native.get(name, pin=torch.cuda.is_available())
+            return t.view(torch.uint8) if info.dtype == "F8_E8M0" else t
         return info.file.read(info)
 
     def get_opt(self, name: str) -> Optional[torch.Tensor]:

@@ -47,6 +47,27 @@ def main():
             assert all(len(g) == 10 for g in got)
         else:
             assert follow(llm) == 0
+    elif case == "pipeline":
+        # two pipeline stages (one rank each): layers split in half, hidden rows handed over in micro-batches of 8 rows,
+        # the last stage returns the tokens to rank 0; outputs must equal the single-process run exactly
+        from blaze_b200.parallel.pp import stage_layers
+        from blaze_b200.parallel.worker import attach
+        pg = TPGroup.from_env("cpu", pp=2)
+        assert (pg.stage, pg.stages, pg.world, pg.global_rank) == (rank, 2, 1, rank)
+        cfg = named_config("tiny")
+        solo = [o.token_ids for o in build(TPInfo()).generate(prompts, sp)] if rank == 0 else None
+        llm = build(TPInfo(), chunk=16, stage_layers=stage_layers(cfg.num_layers, 2, pg.stage))
+        llm.group = pg
+        lead = attach(llm, pg, pp_chunk=8)
+        if rank == 0:
+            got = [o.token_ids for o in llm.generate(prompts, sp)]
+            lead.quit()
+            assert got == solo, (got, solo)
+            assert llm.pipeline.micro_batches > llm.sched.stats.steps      # prompt steps were cut into several micro-batches
+            print(f"[pp-cpu] two stages give the single-process tokens; {llm.pipeline.micro_batches} micro-batches in "
+                  f"{llm.sched.stats.steps} steps", flush=True)
+        else:
+            assert follow(llm) == 0
     elif case == "rank_leaves":
         # rank 1 leaves between two steps; rank 0's next step must end with an error inside the group timeout, fail the
         # requests of that step and leave the scheduler able to answer again (here: with an error, since the group is gone)
@@ -79,7 +100,7 @@ def main():
                     s = eng.seqs.setdefault(row, Seq(row=row))
                     eng.kv.set_pages(row, pg[len(s.pages):], len(s.pages))
                     s.pages = list(pg)
-                eng.forward([SeqChunk(a, b, c, d) for a, b, c, d in raw], mode, feedback=feedback)
+                eng.forward([SeqChunk(a, b, c, d) for a, b, c, d, _, _ in raw], mode, feedback=feedback)
             os._exit(0)
     else:
         raise SystemExit(f"unknown case {case}")

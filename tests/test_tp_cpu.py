@@ -30,3 +30,9 @@ def test_two_rank_generation_matches_one_rank():
 def test_rank_leaving_between_steps_fails_the_step_not_the_server():
     r = _run("rank_leaves")
     assert "peer left: request failed" in r.stdout
+
+
+def test_two_pipeline_stages_match_one_process():
+    r = _run("pipeline")
+    assert r.returncode == 0
+    assert "two stages give the single-process tokens" in r.stdout
