@@ -24,6 +24,11 @@ class SeqChunk:
     tokens: Sequence[int]     # new token ids (1 for decode, k+1 for verify, a chunk for prefill)
     start_pos: int            # position of tokens[0]  (== KV length before this step)
     want_logits: int = 1      # how many trailing rows need logits (0 = headless prefill chunk)
+    pos3: Optional[Sequence[Sequence[int]]] = None   # M-RoPE: rotary positions (temporal, height, width) of the rows, 3 x n;
+                                                     # None = all three equal start_pos + i + rope_delta
+    rope_delta: int = 0       # added to the rotary position of text rows after image blocks (KV slots still follow start_pos)
+    embeds: Optional[Sequence] = None                # (row offset in this chunk, tensor [k, hidden]) blocks that replace the
+                                                     # token embeddings of those rows (image tokens)
     defer_state: bool = False # recurrent (GDN) layers read this sequence's state but do not store the advanced state:
                               # the rows are speculative and the accepted prefix is replayed afterwards (Engine.commit_state)
     parents: Optional[Sequence[int]] = None   # draft tree: parent row of each token within this chunk (-1 for the first,
@@ -43,6 +48,8 @@ class StepBatch:
     logit_rows: torch.Tensor      # [R] int32 rows whose logits are wanted
     item_seq: Optional[torch.Tensor] = None   # [items] attention row-block items (None = one per sequence)
     item_q0: Optional[torch.Tensor] = None
+    positions3: Optional[torch.Tensor] = None # [3, T] int32 rotary positions when a chunk carries M-RoPE positions
+    embed_over: Optional[List] = None         # (first row, tensor) blocks that overwrite token embeddings (image tokens)
     gdn_defer: Optional[torch.Tensor] = None  # [B] int32, set when a chunk defers its recurrent state: 1 = do not store
     h_gdn_defer: Optional[List[int]] = None
     tree_mask: Optional[torch.Tensor] = None  # [T] int32, set when a chunk carries a draft tree: bit j = the row may see the
@@ -112,6 +119,9 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     logit_rows: List[int] = []
     has_tree = any(c.parents is not None for c in chunks)
     tree_mask = np.zeros(Tp if has_tree else 0, np.int32)
+    has_p3 = any(c.pos3 is not None or c.rope_delta for c in chunks)
+    pos3 = np.zeros((3, Tp) if has_p3 else (0,), np.int32)
+    embed_over: List = []
     r = 0
     max_q = 1
     max_ctx = 0
@@ -126,6 +136,14 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
             positions[r:r + n] = pos
             if has_tree:
                 tree_mask[r:r + n] = [-1 if j >= 31 else (2 << j) - 1 for j in range(n)]
+        if has_p3:
+            if c.pos3 is not None:
+                pos3[:, r:r + n] = np.asarray(c.pos3, dtype=np.int32).reshape(3, n)
+            else:
+                pos3[:, r:r + n] = positions[r:r + n] + c.rope_delta
+        if c.embeds:
+            for off, t in c.embeds:
+                embed_over.append((r + int(off), t))
         pages = block_table_host[c.slot, pos // PAGE]
         slot_map[r:r + n] = pages * PAGE + pos % PAGE
         seq_of_row[r:r + n] = b
@@ -160,7 +178,7 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     has_defer = any(c.defer_state for c in chunks)
     defer = np.asarray([1 if c.defer_state else 0 for c in chunks] if has_defer else [], np.int32)
     parts = [tokens, positions, slot_map, seq_of_row, slots, q_start, ctx_len, lr,
-             np.asarray(items_s, np.int32), np.asarray(items_q, np.int32), tree_mask, defer]
+             np.asarray(items_s, np.int32), np.asarray(items_q, np.int32), tree_mask, defer, pos3.reshape(-1)]
     total = sum(p.size for p in parts)
     if pinned is not None and pinned.numel() >= total:
         stage = pinned[:total]
@@ -178,6 +196,7 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
     return StepBatch(tokens=v[0], positions=v[1], slot_mapping=v[2], seq_of_row=v[3], slots=v[4], q_start=v[5],
                      ctx_len=v[6], logit_rows=v[7], item_seq=v[8] if items_s else None,
                      item_q0=v[9] if items_s else None, tree_mask=v[10] if has_tree else None,
+                     positions3=v[12].view(3, Tp) if has_p3 else None, embed_over=embed_over or None,
                      gdn_defer=v[11] if has_defer else None, h_gdn_defer=[int(x) for x in defer] if has_defer else None, h_slots=[int(s) for s in slots],
                      h_q_start=[int(x) for x in q_start], h_ctx_len=[int(x) for x in ctx_len],
                      h_logit_rows=logit_rows, tiny_rows_max=tiny_rows_max, num_tiny=num_tiny, small_rows_max=small_rows_max,

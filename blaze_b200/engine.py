@@ -337,7 +337,8 @@ class Engine:
                 if c.defer_state:
                     self._deferred[c.slot] = (r, c.start_pos, len(c.tokens))
                 r += len(c.tokens)
-        graphable = (self.ecfg.use_graphs and self.device.type == "cuda" and decode_only and mode == "greedy"
+        plain = not any(c.rope_delta or c.pos3 is not None or c.embeds for c in chunks)     # captured steps carry text rows only
+        graphable = (plain and self.ecfg.use_graphs and self.device.type == "cuda" and decode_only and mode == "greedy"
                      and self.model.is_first_stage and self.model.is_last_stage and self.model.ops.is_cuda)
         try:
             if graphable:

@@ -460,6 +460,10 @@ class Model:
             x = hidden_in
         else:
             x = ops.embed(self.embed, batch.tokens)
+            if batch.embed_over:
+                # image tokens: the vision tower's rows take the place of the pad tokens' embeddings
+                for r0, t in batch.embed_over:
+                    x[r0:r0 + t.shape[0]] = t.to(device=x.device, dtype=x.dtype)
         fused = self._fused()
         rope = ops.rope_tables(self, batch)
         residual = None          # full rows, or this rank's row shard on the reduce+norm path

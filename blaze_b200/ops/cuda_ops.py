@@ -76,7 +76,7 @@ class CudaOps:
         lib.blz_swiglu.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_attn_prep.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                       _c.c_float, _c.c_float, _c.c_int, _c.c_int, _c.c_float, _c.c_float, _c.c_longlong,
-                                      _c.c_longlong, _c.c_int, VP]
+                                      _c.c_longlong, _c.c_int, _c.c_longlong, _c.c_int, _c.c_int, VP]
         lib.blz_attn_tc.argtypes = [VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                     _c.c_longlong, _c.c_longlong, _c.c_float, _c.c_float, _c.c_float, _c.c_int, VP, VP, _c.c_int, VP]
         lib.blz_attn_decode_tree.argtypes = [VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
@@ -451,12 +451,22 @@ class CudaOps:
             raise CudaError("the CUDA attention path needs the FP8 'umma' KV layout (kv_dtype='fp8')")
         q = torch.empty(T, attn.heads, D, dtype=torch.bfloat16, device=self.device)
         gate = torch.empty(T, attn.heads, D, dtype=torch.bfloat16, device=self.device) if cfg.attn_output_gate else None
-        self._check(self.lib.blz_attn_prep(_ptr(qkv), _ptr(q), _ptr(gate), _ptr(kv.kv[layer_idx]), _ptr(batch.positions),
+        # M-RoPE: three position streams [3, T]; frequency i reads stream 0 / 1 / 2 by the model's section sizes
+        pos, pos_stride, m0, m1 = batch.positions, 0, 0, 0
+        sec = cfg.rope.mrope_section
+        if getattr(batch, "positions3", None) is not None:
+            pos, pos_stride = batch.positions3, batch.positions3.stride(0)
+            if sec:
+                m0, m1 = int(sec[0]), int(sec[0]) + int(sec[1])
+            else:
+                m0 = m1 = cfg.rotary_dim // 2          # no sections: every frequency follows the first stream
+        self._check(self.lib.blz_attn_prep(_ptr(qkv), _ptr(q), _ptr(gate), _ptr(kv.kv[layer_idx]), _ptr(pos),
                                            _ptr(batch.slot_mapping), _ptr(model.inv_freq), _ptr(attn.q_norm), _ptr(attn.k_norm),
                                            T, attn.heads, attn.kv_heads, D, cfg.rotary_dim, cfg.rms_norm_eps,
                                            model.rope_scale, int(cfg.attn_output_gate), int(cfg.zero_centered_norm),
                                            1.0, 1.0, kv.kv[layer_idx].stride(0), kv.kv[layer_idx].stride(1),
-                                           int(getattr(model, "kv_rotate", False)), self._stream()), "attn_prep")
+                                           int(getattr(model, "kv_rotate", False)), pos_stride, m0, m1, self._stream()),
+                    "attn_prep")
         return q, gate
 
     def kv_move_rows(self, pool, src, dst, seg, D):

@@ -48,7 +48,8 @@ class RefOps:
     # -------------------------------------------------------------- attention
     def rope_tables(self, model, batch):
         inv = model.inv_freq
-        return ref.rope_cos_sin(batch.positions, inv, model.rope_scale, model.cfg.rope.mrope_section)
+        pos = batch.positions3 if getattr(batch, "positions3", None) is not None else batch.positions
+        return ref.rope_cos_sin(pos, inv, model.rope_scale, model.cfg.rope.mrope_section)
 
     def attn_prep_store(self, qkv, attn, model, batch, kv, layer_idx, rope):
         cfg = model.cfg

@@ -415,6 +415,14 @@ class Active:
         self.forced: Deque[int] = collections.deque()
         self.admitted_at = time.monotonic()
         self.snap_points: List[int] = []
+        # multimodal requests: rotary positions of the prompt rows (3 x prompt) and what text rows after it add to their index
+        self.mm_pos = None
+        self.rope_delta = 0
+        self.cache_key_tokens: Optional[List[int]] = None     # prompt with image pads replaced by content keys
+        if req.mm is not None:
+            self.mm_pos = req.mm.positions3(self.tokens[:self.n_prompt])
+            self.rope_delta = int(self.mm_pos.max().item()) + 1 - self.n_prompt if self.n_prompt else 0
+            self.cache_key_tokens = req.mm.cache_tokens(self.tokens[:self.n_prompt])
 
     @property
     def generated(self) -> List[int]:
@@ -585,6 +593,11 @@ class Scheduler:
 
     def _try_admit(self, req: GenRequest, resume: Optional[Active] = None):
         eng = self.engine
+        if req.mm is not None and not resume and not getattr(req, "_mm_expanded", False):
+            # one placeholder per image in the rendered prompt becomes as many pad tokens as the image has embedding rows
+            if sum(1 for t in req.prompt if t == req.mm.image_pad_id) == len(req.mm.images):
+                req.prompt = req.mm.expand(req.prompt)
+            req._mm_expanded = True
         tokens = resume.tokens if resume else req.prompt
         if len(self.active) >= self.cfg.max_seqs or not eng.free_rows:
             return False
@@ -597,7 +610,9 @@ class Scheduler:
                                      error=f"prompt of {len(tokens)} tokens exceeds the context limit {limit}"))
             self.stats.failed += 1
             return None
-        entry = self.cache.lookup(tokens)
+        # images take part in prefix matching through their content keys, not through the (identical) pad tokens
+        key_tokens = req.mm.cache_tokens(tokens) if req.mm is not None else tokens
+        entry = self.cache.lookup(key_tokens)
         cached = len(entry.tokens) if entry else 0
         need = len(tokens) - cached + 16 + self._reserved()
         while eng.free_tokens < need:
@@ -667,7 +682,7 @@ class Scheduler:
     def _plain_greedy(self, a: Active) -> bool:
         p, r = a.req.params, a.req
         return not (p.needs_candidates() or r.constraint is not None or r.embed_only or r.think is not None or a.forced
-                    or p.logprobs is not None)
+                    or p.logprobs is not None or r.mm is not None)
 
     def _continues(self, a: Active, in_flight: int) -> bool:
         """True when ``a`` certainly wants another token after the ``in_flight`` tokens that are not appended yet."""
@@ -806,6 +821,7 @@ class Scheduler:
                 chunks += eng.plan_tree([(a.seq, toks, d.parent)])
             else:
                 chunks += eng.plan([(a.seq, toks, want)], defer_state=bool(d))
+            self._mm_fill(a, chunks[-1])
         want_any = any(w for _, _, w, _ in plan)
         need_logits = any(w and (a.req.params.needs_candidates() or a.req.constraint is not None or a.req.embed_only)
                           for a, _, w, _ in plan)
@@ -837,6 +853,33 @@ class Scheduler:
         else:
             self._consume(pend)
 
+    def _key_tokens(self, a: Active, n: int) -> List[int]:
+        """The first ``n`` tokens of ``a`` as the prefix cache sees them (image pads replaced by image content keys)."""
+        if a.cache_key_tokens is None:
+            return a.tokens[:n]
+        k = a.cache_key_tokens
+        return k[:n] if n <= len(k) else k + a.tokens[len(k):n]
+
+    def _mm_fill(self, a: Active, ch: SeqChunk) -> None:
+        """Rotary positions and image-embedding rows of a chunk of a multimodal request."""
+        if a.req.mm is None:
+            return
+        n, p0 = len(ch.tokens), ch.start_pos
+        ch.rope_delta = a.rope_delta
+        if p0 < a.n_prompt:
+            m = min(n, a.n_prompt - p0)
+            pos = torch.empty(3, n, dtype=torch.int32)
+            pos[:, :m] = a.mm_pos[:, p0:p0 + m]
+            if n > m:
+                pos[:, m:] = torch.arange(p0 + m, p0 + n, dtype=torch.int32) + a.rope_delta
+            ch.pos3 = pos.tolist()
+            blocks = []
+            for s0, e0, k in a.req.mm.segments(a.tokens[:a.n_prompt]):
+                lo, hi = max(s0, p0), min(e0, p0 + n)
+                if lo < hi and k < len(a.req.mm.images):
+                    blocks.append((lo - p0, a.req.mm.images[k].embeds[lo - s0:hi - s0]))
+            ch.embeds = blocks or None
+
     def _may_stay_in_flight(self, pend: "_Pending") -> bool:
         """Plain greedy / headless steps without drafts: nothing the host decides next depends on their tokens, except
         for the requests in the step themselves, and those sit out until the tokens are read."""
@@ -861,7 +904,7 @@ class Scheduler:
             a._started = True
             if a.computed in a.snap_points and a.computed <= a.n_prompt:
                 kind = SnapKind.POINT if a.req.cache_point and a.computed <= a.req.cache_point else SnapKind.PROMPT
-                self.cache.remember(a.tokens[:a.computed], a.seq, kind)
+                self.cache.remember(self._key_tokens(a, a.computed), a.seq, kind)
 
     def _consume(self, pend: "_Pending") -> None:
         eng = self.engine
@@ -1129,7 +1172,7 @@ class Scheduler:
                 # keep the finished conversation for follow-up turns
                 n = a.seq.length - a.seq.length % PAGE
                 if n >= PAGE and not self.engine.kv.gdn_layers:
-                    self.cache.remember(a.tokens[:n], a.seq, SnapKind.FINISH)
+                    self.cache.remember(self._key_tokens(a, n), a.seq, SnapKind.FINISH)
             self.engine.close(a.seq)
             a.seq = None
         self.stats.finished += 1

@@ -415,7 +415,8 @@ __global__ void __launch_bounds__(512) attn_prep_kernel(const __nv_bfloat16* __r
                                  const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
                                  const __nv_bfloat16* __restrict__ k_norm_w, int T, int Hq, int Hkv, int rot_dim,
                                  float eps, float rope_scale, int gated, int zero_centered, float k_scale_inv,
-                                 float v_scale_inv, long long page_stride, long long head_stride, int rotate) {
+                                 float v_scale_inv, long long page_stride, long long head_stride, int rotate,
+                                 long long pos_stride, int mrope0, int mrope1) {
   pdl_trigger();
   pdl_wait();
   constexpr int VPL = D / 32;
@@ -425,8 +426,13 @@ __global__ void __launch_bounds__(512) attn_prep_kernel(const __nv_bfloat16* __r
   const int heads = Hq + 2 * Hkv;
   const int half = rot_dim / 2;
   {
-    const float pos = (float)positions[t];
+    // M-RoPE (pos_stride > 0): positions is [3, T]; frequency i follows the temporal stream below mrope0, the height stream
+    // below mrope1, the width stream above (reference: attn_prep_kernel<MROPE>, kernels/src/cuda/ops_basic.cu:102)
+    const float p0 = (float)positions[t];
+    const float p1 = pos_stride > 0 ? (float)positions[pos_stride + t] : p0;
+    const float p2 = pos_stride > 0 ? (float)positions[2 * pos_stride + t] : p0;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float pos = pos_stride > 0 ? (i < mrope0 ? p0 : (i < mrope1 ? p1 : p2)) : p0;
       float s, c;
       sincosf(pos * inv_freq[i], &s, &c);
       cs[i] = make_float2(c * rope_scale, s * rope_scale);
@@ -739,7 +745,7 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
                           const int* slot_mapping, const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
                           int T, int Hq, int Hkv, int D, int rot_dim, float eps, float rope_scale, int gated,
                           int zero_centered, float k_scale, float v_scale, long long page_stride, long long head_stride,
-                          int rotate, cudaStream_t s) {
+                          int rotate, long long pos_stride, int mrope0, int mrope1, cudaStream_t s) {
   if (T == 0) return 0;
   const int half = rot_dim / 2, vpl = D / 32;
   if ((D != 64 && D != 128 && D != 256) || rot_dim > D || half % vpl || ((half / vpl) & (half / vpl - 1)) || half / vpl > 16)
@@ -754,7 +760,7 @@ BLZ_API int blz_attn_prep(const void* qkv, void* q_out, void* gate_out, void* kv
              (uint8_t*)kv_pool, positions, slot_mapping, inv_freq, (const bf16*)q_norm_w, (const bf16*)k_norm_w, T, Hq, \
              Hkv, rot_dim, eps, rope_scale, gated, zero_centered, 1.f / k_scale, 1.f / v_scale,                         \
              page_stride > 0 ? page_stride : (long long)Hkv * 2 * 16 * D, head_stride > 0 ? head_stride : (long long)2 * 16 * D, \
-             rotate)
+             rotate, pos_stride, mrope0, mrope1)
   if (D == 64) BLZ_PREP(64); else if (D == 128) BLZ_PREP(128); else BLZ_PREP(256);
 #undef BLZ_PREP
   return (int)cudaGetLastError();

@@ -53,3 +53,52 @@ def test_prefill_first_with_steps_in_flight_matches_interleave():
     want = [o.token_ids for o in a.generate(ps, sp)]
     got = [o.token_ids for o in b.generate(ps, sp)]
     assert _agree(got, want) >= 0.85, _agree(got, want)
+
+
+def _logit_stats(got, want):
+    g, w = got.float(), want.float()
+    cos = torch.nn.functional.cosine_similarity(g, w, dim=1)
+    top2 = w.topk(2, dim=1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0.02 * w.abs().max(dim=1).values        # rows whose arg-max is not a near-tie
+    same = (g.argmax(1) == w.argmax(1))
+    return cos, clear, same
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8", "dense"])
+def test_model_logits_match_the_oracle_on_the_same_quantised_weights(fmt):
+    """The whole decoder through the kernels against the PyTorch oracle ops on identical (quantised) weights: prefill logits
+    of every prompt row, then decode logits over the KV the kernels wrote.  What differs is what the kernels do differently
+    on purpose (their own activation quantiser, e4m3 queries and probabilities inside attention), so the logits agree to a
+    cosine near one and the arg-max agrees wherever the oracle's own top-2 margin is not a near-tie."""
+    from blaze_b200.engine import Engine, EngineConfig
+    from blaze_b200.models.qwen3 import Model
+    from blaze_b200.ops.ref_ops import RefOps
+    from blaze_b200.quant import Format
+    f = {"nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "dense": Format.DENSE}[fmt]
+    cfg = _cfg()
+    mk = Model.random_init(cfg, fmt=f, seed=5, device="cuda")
+    mr = Model.random_init(cfg, fmt=f, seed=5, device="cuda", ops=RefOps())
+    assert mk.ops.is_cuda and not mr.ops.is_cuda
+    ek = Engine(mk, EngineConfig(max_seqs=4, max_model_len=256, kv_dtype="fp8", kv_tokens=2048, use_graphs=False))
+    er = Engine(mr, EngineConfig(max_seqs=4, max_model_len=256, kv_dtype="fp8", kv_tokens=2048, use_graphs=False))
+    prompts = _prompts(3, 70, 11)
+    sk = [ek.open_from() for _ in prompts]
+    sr = [er.open_from() for _ in prompts]
+    lk = ek.forward(ek.plan([(s, p, len(p)) for s, p in zip(sk, prompts)]), "logits")
+    lr = er.forward(er.plan([(s, p, len(p)) for s, p in zip(sr, prompts)]), "logits")
+    cos, clear, same = _logit_stats(lk, lr)
+    print(f"[logits {fmt}] prefill rows {lk.shape[0]}: cosine min {cos.min().item():.5f} mean {cos.mean().item():.5f}; "
+          f"arg-max equal on {int((same & clear).sum())}/{int(clear.sum())} clear rows, {int(same.sum())}/{same.numel()} of all")
+    assert cos.min().item() >= 0.99 and cos.mean().item() >= 0.997
+    assert (same | ~clear).all(), "arg-max differs on a row that is not a near-tie"
+    toks = lr[[len(p) - 1 + sum(len(q) for q in prompts[:i]) for i, p in enumerate(prompts)]].argmax(1).tolist()
+    for step in range(3):
+        lk = ek.forward(ek.plan([(s, [t], 1) for s, t in zip(sk, toks)]), "logits")
+        lr = er.forward(er.plan([(s, [t], 1) for s, t in zip(sr, toks)]), "logits")
+        cos, clear, same = _logit_stats(lk, lr)
+        print(f"[logits {fmt}] decode step {step}: cosine min {cos.min().item():.5f}")
+        assert cos.min().item() >= 0.99
+        assert (same | ~clear).all()
+        toks = lr.argmax(1).tolist()
+    torch.cuda.synchronize()
+    assert mk.ops.take_status() == 0

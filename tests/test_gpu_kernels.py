@@ -528,3 +528,46 @@ def test_autotuner_routes_linear_layers(ops, tmp_path, monkeypatch):
     assert ops.take_status() == 0
     _, rel = _report("tuned route vs one-CTA-per-tile kernel", got, want.float())
     assert rel < 2e-3
+
+
+@pytest.mark.parametrize("D,rot,gated", [(128, 128, False), (256, 64, True), (64, 64, False)])
+def test_attn_prep_mrope_positions(ops, D, rot, gated):
+    """q/k-norm + rotary + page write with three position streams (M-RoPE): every frequency follows the stream its section
+    names; also head_dim 256 with partial rotary and the output gate split (the Qwen3-Next attention shape)."""
+    from blaze_b200.batch import SeqChunk, build_batch
+    from blaze_b200.config import ModelConfig, RopeConfig, inv_freq
+    Hq, Hkv, T = 4, 2, 37
+    half = rot // 2
+    sec = [half // 4, half // 4 + 2, half - (half // 4) * 2 - 2]
+    cfg = ModelConfig(hidden_size=Hq * D, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, num_layers=1, attn_output_gate=gated,
+                      rope=RopeConfig(theta=1e6, partial_rotary_factor=rot / D, mrope_section=sec))
+    cfg.layer_types = ["full_attention"]
+    g = torch.Generator(device=DEV).manual_seed(51)
+    kv = KVCache(cfg, 8, 1, 4, "fp8", DEV, "umma")
+    kv.set_pages(0, [3, 1, 5])
+    p3 = torch.stack([torch.arange(T), torch.randint(0, 50, (T,)), torch.randint(0, 50, (T,))]).tolist()
+    batch = build_batch([SeqChunk(0, [0] * T, 0, pos3=p3)], kv.block_table_host, DEV, attn_group=Hq // Hkv)
+    assert batch.positions3 is not None and batch.positions3.shape == (3, T)
+    model = _A()
+    model.cfg = cfg
+    model.inv_freq = torch.tensor(inv_freq(cfg), dtype=torch.float32, device=DEV)
+    model.rope_scale, model.kv_rotate = 1.0, False
+    attn = _A()
+    attn.heads, attn.kv_heads = Hq, Hkv
+    attn.q_norm = (1 + 0.1 * torch.randn(D, generator=g, device=DEV)).bfloat16()
+    attn.k_norm = (1 + 0.1 * torch.randn(D, generator=g, device=DEV)).bfloat16()
+    qkv = torch.randn(T, (Hq * (2 if gated else 1) + 2 * Hkv) * D, generator=g, device=DEV).bfloat16()
+    q, gate = ops.attn_prep_store(qkv, attn, model, batch, kv, 0, None)
+    cos, sin = ref.rope_cos_sin(batch.positions3, model.inv_freq, 1.0, sec)
+    qr, kr, vr, gr = ref.attn_prep(qkv, Hq, Hkv, D, attn.q_norm, attn.k_norm, 1e-6, cos, sin, gated=gated)
+    torch.cuda.synchronize()
+    assert (q.float() - qr.float()).abs().max().item() < 0.07
+    if gated:
+        assert torch.equal(gate.view(T, Hq, D), gr.view(T, Hq, D).to(gate.dtype))
+    # with one stream only the result must differ (the sections are really used)
+    cos1, sin1 = ref.rope_cos_sin(batch.positions, model.inv_freq)
+    q1, _, _, _ = ref.attn_prep(qkv, Hq, Hkv, D, attn.q_norm, attn.k_norm, 1e-6, cos1, sin1, gated=gated)
+    assert (q.float() - q1.float()).abs().max().item() > 0.2
+    kl, vl = kv.logical_kv(0)
+    page, off = kv.block_table_host[0, (T - 1) // 16], (T - 1) % 16
+    assert (kl[page, :, off].float() - kr[T - 1].float()).abs().max().item() <= 0.07 * kr[T - 1].float().abs().max().item() + 0.02

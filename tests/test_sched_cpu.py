@@ -370,3 +370,45 @@ def test_watchdog_reports_a_step_that_does_not_return():
             break
         time.sleep(0.05)
     assert seen and "engine hang" in seen[0] and llm.engine.hangs == 1
+
+
+def test_multimodal_request_gets_mrope_positions_and_image_rows():
+    """An image in the prompt: its pad tokens take the vision tower's rows as embeddings, rotary positions follow the
+    three-axis layout (text after the image resumes from the block's largest position + 1), chunked prefill cuts through
+    the image without changing the result, and the prefix cache tells two different images apart."""
+    from blaze_b200.config import named_config
+    from blaze_b200.mm import ImageEmbeds, MmInput
+    from blaze_b200.sched import GenRequest
+    cfg = named_config("tiny")
+    cfg.rope.mrope_section = [8, 12, 12]                       # half of head_dim 64
+    PAD = 1000
+
+    def run(chunk, img_seed, cache=False):
+        llm = LLM(cfg, device="cpu", dtype=torch.float32, max_seqs=4, max_model_len=256, use_graphs=False, seed=0, chunk=chunk,
+                  enable_prefix_caching=cache)
+        g = torch.Generator().manual_seed(img_seed)
+        emb = torch.randn(12, cfg.hidden_size, generator=g) * 0.05          # a 3 x 4 grid of image tokens
+        outs = []
+        for rep in range(2 if cache else 1):
+            mm = MmInput([ImageEmbeds(emb, (3, 4), 7000 + img_seed)], PAD)
+            got = []
+            llm.sched.submit(GenRequest(f"mm{rep}", [5, 6, 7, PAD, 8, 9, 10, 11], SamplingParams(temperature=0.0, max_tokens=8),
+                                        mm=mm, sink=lambda ev: got.extend(ev.tokens or [])))
+            llm.sched.run_until_idle()
+            outs.append(got)
+        return llm, outs
+    llm, (a,) = run(64, 1)
+    _, (b,) = run(5, 1)                       # prefill chunks of 5 rows cut through the 12-row image block
+    assert a == b and len(a) == 8
+    _, (c,) = run(64, 2)
+    assert c != a, "a different image must change the continuation"
+    # the rotary positions: 3 text rows, a 3 x 4 image block at temporal position 3, text resumes at 3 + max(3, 4) = 7
+    mm = MmInput([ImageEmbeds(torch.zeros(12, 4), (3, 4), 1)], PAD)
+    toks = mm.expand([5, 6, 7, PAD, 8, 9])
+    p3 = mm.positions3(toks)
+    assert p3[:, :3].tolist() == [[0, 1, 2]] * 3
+    assert p3[0, 3:15].tolist() == [3] * 12 and p3[1, 3:15].tolist() == [3, 3, 3, 3, 4, 4, 4, 4, 5, 5, 5, 5]
+    assert p3[2, 3:15].tolist() == [3, 4, 5, 6] * 3 and p3[:, 15].tolist() == [7, 7, 7]
+    # same image twice: the second request reuses the cached prefix and gives the same tokens
+    llm2, (x, y) = run(64, 1, cache=True)
+    assert x == y == a
