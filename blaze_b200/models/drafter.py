@@ -129,6 +129,10 @@ class ChainDrafter:
         return d
 
     # ------------------------------------------------------------------ scheduler hooks
+    def hidden_source(self, model: Model, hidden: torch.Tensor) -> torch.Tensor:
+        """The rows the drafter consumes from a target step: the residual stream after the last layer."""
+        return hidden
+
     def open(self, request_id: str) -> None:
         self.states[request_id] = DraftState(self.engine.open_from())
 
@@ -213,19 +217,377 @@ class ChainDrafter:
         return [out[id(a)] for a in actives]
 
 
-class EagleDrafter(ChainDrafter):
-    """EAGLE-style: the fused input reads the hidden states of several target layers (``capture_layers``)."""
+class _Shell:
+    """What the attention ops read from a model: config, rotary tables, the op set."""
+
+    def __init__(self, cfg, target: Model):
+        from ..config import inv_freq
+        self.cfg, self.ops, self.device, self.dtype = cfg, target.ops, target.device, target.dtype
+        self.tp = TPInfo()
+        self.inv_freq = torch.tensor(inv_freq(cfg), dtype=torch.float32, device=target.device)
+        self.rope_scale = cfg.rope.rope_scale()
+        self.first_layer, self.last_layer = 0, 1
+        self.is_first_stage = self.is_last_stage = True
+        self.kv_rotate = False
+
+
+class EagleDrafter:
+    """EAGLE-style drafter: one decoder layer whose attention reads ``[norm(embed(token)) | norm(hidden)]`` (2H wide), fed
+    with the target's hidden states of several layers fused by ``fc``; a low-rank candidate head picks a short list of
+    tokens whose exact logits come from the full head; chains, or trees grown level by level from the top-k candidates.
+
+    Reference: ``crates/blaze/src/eagle.rs`` — tensors ``fc``, ``fc_norm.{i}``, one ``layers.0`` block with a 2H-wide
+    qkv, ``norm``, ``efficient_lm_head_down_proj`` + ``efficient_lm_head`` (:265-360); data flow of ``layer_with`` (:888);
+    ``run`` chains (:565); ``run_tree`` / ``grow`` (:601-690: every level expands the K frontier rows, adds each row's
+    top-K candidates as children and keeps the best K by path probability); ``head_merged`` (:694)."""
+
     kind = "eagle"
+
+    def __init__(self, target: Model, cfg: ModelConfig, w: Dict[str, object], max_seqs: int, max_model_len: int, kv_dtype: str,
+                 capture_layers: Sequence[int], candidates: int = 128, norm_output: bool = False):
+        self.target, self.ops, self.cfg, self.w = target, target.ops, cfg, w
+        self.capture_layers = list(capture_layers)
+        self.candidates, self.norm_output = candidates, norm_output
+        self.shell = _Shell(cfg, target)
+        self.engine = Engine(self.shell, EngineConfig(max_seqs=max_seqs, max_model_len=max_model_len, kv_dtype=kv_dtype,
+                                                      kv_tokens=max_seqs * max_model_len, use_graphs=False))
+        from .qwen3 import Attn
+        self.attn = Attn()
+        self.attn.heads, self.attn.kv_heads = cfg.num_heads, cfg.num_kv_heads
+        self.states: Dict[str, DraftState] = {}
+        self.tree_width, self.tree_depth = 1, 4
+        self.proposed = self.steps = 0
+        self.draft_ids: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def random_init(cls, target: Model, seed: int = 7, max_seqs: int = 256, max_model_len: int = 4096, kv_dtype: str = "bf16",
+                    n_capture: int = 3, rank: int = 64, candidates: int = 64):
+        tc = target.cfg
+        cfg = ModelConfig(**{**vars(tc), "num_layers": 1, "layer_types": ["full_attention"], "num_experts": 0,
+                             "attn_output_gate": False, "qk_norm": False})
+        cfg.rope = tc.rope
+        H, D, I, V = cfg.hidden_size, cfg.head_dim, cfg.intermediate_size, cfg.vocab_size
+        dev, dt = target.device, target.dtype
+        g = torch.Generator(device=dev).manual_seed(seed)
+
+        def lin(n, k):
+            return Linear.from_dense(torch.randn(n, k, generator=g, device=dev) * 0.02, Format.DENSE, dtype=dt)
+        one = lambda: torch.ones(H, dtype=dt, device=dev)      # noqa: E731
+        L = tc.num_layers
+        caps = sorted({min(L - 1, max(0, (i + 1) * L // (n_capture + 1))) for i in range(n_capture)})
+        w = {"fc": lin(H, len(caps) * H), "fc_norm": [one() for _ in caps], "input_ln": one(), "hidden_ln": one(),
+             "qkv": lin((cfg.num_heads + 2 * cfg.num_kv_heads) * D, 2 * H), "o": lin(H, cfg.num_heads * D), "post_ln": one(),
+             "gate_up": lin(2 * I, H), "down": lin(H, I), "norm": one(), "lr_down": lin(rank, H), "lr_head": lin(V, rank),
+             "lm_head": target.lm_head, "embed": target.embed}
+        return cls(target, cfg, w, max_seqs, max_model_len, kv_dtype, caps, candidates)
+
+    @classmethod
+    def load(cls, target: Model, draft_dir: str, max_seqs: int, max_model_len: int, kv_dtype: str = "bf16"):
+        """A drafter checkpoint directory (``config.json`` + safetensors) with the tensor names of ``eagle.rs:265-360``."""
+        import json
+        import os
+        from ..weights import Checkpoint
+        with open(os.path.join(draft_dir, "config.json")) as fh:
+            raw = json.load(fh)
+        ck = Checkpoint.open(draft_dir)
+        tc = target.cfg
+        cfg = ModelConfig(**{**vars(tc), "num_layers": 1, "layer_types": ["full_attention"], "num_experts": 0,
+                             "attn_output_gate": False, "qk_norm": False,
+                             "num_heads": int(raw.get("num_attention_heads", tc.num_heads)),
+                             "num_kv_heads": int(raw.get("num_key_value_heads", tc.num_kv_heads)),
+                             "head_dim": int(raw.get("head_dim", tc.head_dim)),
+                             "intermediate_size": int(raw.get("intermediate_size", tc.intermediate_size))})
+        cfg.rope = tc.rope
+        dev, dt = target.device, target.dtype
+        if int(raw.get("hidden_size", tc.hidden_size)) != tc.hidden_size or int(raw.get("vocab_size", tc.vocab_size)) != tc.vocab_size:
+            raise ValueError("the drafter's hidden size / vocabulary differ from the target's")
+        aux = (raw.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids") or []
+        caps = [int(l) + 1 for l in aux] or [tc.num_layers - 1]         # the input of the layer after each aux layer
+
+        def vec(name):
+            return ck.get(name).to(dt).to(dev)
+
+        def lin(*mods):
+            return Linear.load(ck, list(mods), Cut.ALL, 0, 1, dt, dev)
+        p = "layers.0." if "layers.0.self_attn.q_proj.weight" in ck else "midlayer."
+        w = {"fc": lin("fc"), "fc_norm": [vec(f"fc_norm.{i}.weight") for i in range(len(caps))] if "fc_norm.0.weight" in ck else None,
+             "input_ln": vec(p + "input_layernorm.weight"), "hidden_ln": vec(p + "hidden_norm.weight"),
+             "qkv": lin(p + "self_attn.q_proj", p + "self_attn.k_proj", p + "self_attn.v_proj"), "o": lin(p + "self_attn.o_proj"),
+             "post_ln": vec(p + "post_attention_layernorm.weight"), "gate_up": lin(p + "mlp.gate_proj", p + "mlp.up_proj"),
+             "down": lin(p + "mlp.down_proj"), "norm": vec("norm.weight"),
+             "lr_down": lin("efficient_lm_head_down_proj") if "efficient_lm_head_down_proj.weight" in ck else None,
+             "lr_head": lin("efficient_lm_head") if "efficient_lm_head.weight" in ck else None,
+             "lm_head": lin("lm_head") if "lm_head.weight" in ck else target.lm_head,
+             "embed": vec("embed_tokens.weight") if "embed_tokens.weight" in ck else target.embed}
+        head = raw.get("efficient_lm_head_config") or {}
+        return cls(target, cfg, w, max_seqs, max_model_len, kv_dtype, caps, int(head.get("num_candidates", 128)),
+                   bool(raw.get("norm_output", False)))
+
+    def use_draft_vocab(self, ids: Sequence[int]) -> None:
+        """Restrict proposals to ``ids`` (candidates outside are dropped before the exact logits are taken)."""
+        self.draft_ids = torch.as_tensor(sorted(set(int(i) for i in ids)), dtype=torch.long, device=self.target.device)
+
+    # ------------------------------------------------------------------ scheduler hooks
+    def hidden_source(self, model: Model, hidden: torch.Tensor) -> torch.Tensor:
+        """The rows the drafter consumes from a target step: the captured inputs of its capture layers, side by side."""
+        return torch.cat([model.captured[l] for l in self.capture_layers], dim=1)
+
+    def open(self, request_id: str) -> None:
+        self.states[request_id] = DraftState(self.engine.open_from())
+
+    def close(self, request_id: str) -> None:
+        st = self.states.pop(request_id, None)
+        if st is not None:
+            self.engine.close(st.seq)
+
+    observe = ChainDrafter.observe
+
+    # ------------------------------------------------------------------ the layer
+    def _fuse(self, hidden_cat: torch.Tensor) -> torch.Tensor:
+        ops, eps = self.ops, self.cfg.rms_norm_eps
+        H = self.cfg.hidden_size
+        parts = []
+        for i in range(len(self.capture_layers)):
+            h = hidden_cat[:, i * H:(i + 1) * H].contiguous()
+            if self.w["fc_norm"] is not None:
+                h, _ = ops.norm(h, None, self.w["fc_norm"][i], eps, False)
+            parts.append(h)
+        return ops.linear(self.w["fc"], torch.cat(parts, dim=1).contiguous())
+
+    def _layer(self, batch, tokens: torch.Tensor, hin: torch.Tensor):
+        """One pass of the drafter's layer over the rows of ``batch``: returns (hidden for the next step, normed rows)."""
+        ops, eps, w = self.ops, self.cfg.rms_norm_eps, self.w
+        e = ops.embed(w["embed"], tokens)
+        a, _ = ops.norm(e, None, w["input_ln"], eps, False)
+        b, _ = ops.norm(hin.contiguous(), None, w["hidden_ln"], eps, False)
+        qkv = ops.linear(w["qkv"], torch.cat([a, b], dim=1).contiguous())
+        rope = ops.rope_tables(self.shell, batch)
+        q, _ = ops.attn_prep_store(qkv, self.attn, self.shell, batch, self.engine.kv, 0, rope)
+        o = ops.attention(q, self.shell, batch, self.engine.kv, 0, self.cfg.head_dim ** -0.5)
+        x = ops.add(hin.contiguous(), ops.linear(w["o"], o))
+        h2, _ = ops.norm(x, None, w["post_ln"], eps, False)
+        x = ops.add(x, ops.linear(w["down"], ops.silu_mul(ops.linear(w["gate_up"], h2))))
+        normed, _ = ops.norm(x, None, w["norm"], eps, False)
+        return (normed if self.norm_output else x), normed
+
+    def _head_topk(self, normed: torch.Tensor, k: int):
+        """Top ``k`` tokens per row with their probabilities: low-rank scores over the vocabulary pick ``candidates`` ids, the
+        full head gives those ids' exact logits, a softmax over the candidates gives the probabilities."""
+        ops, w = self.ops, self.w
+        nf = normed.float()
+        if w["lr_down"] is not None:
+            scores = ops.linear(w["lr_head"], ops.linear(w["lr_down"], normed), out_dtype=torch.float32)
+        else:
+            scores = ops.linear(w["lm_head"], normed, out_dtype=torch.float32)
+        if self.draft_ids is not None:
+            keep = torch.full_like(scores, float("-inf"))
+            keep[:, self.draft_ids] = scores[:, self.draft_ids]
+            scores = keep
+        C = min(self.candidates, scores.shape[1])
+        cand = scores.topk(C, dim=1).indices                                   # [R, C]
+        head = w["lm_head"]
+        hw = (head.dequant() if head.fmt != Format.DENSE else head.w).to(nf.device)
+        exact = torch.einsum("rh,rch->rc", nf, hw[cand].float())                # exact logits of the candidates
+        probs = torch.softmax(exact, dim=1)
+        top = probs.topk(min(k, C), dim=1)
+        return cand.gather(1, top.indices), top.values
+
+    def _extend(self, todo):
+        """Feed the confirmed (hidden, next token) pairs of every request in ``todo``; returns per request the drafter's
+        last hidden row and normed row (the state a chain or a tree starts from)."""
+        eng, dev = self.engine, self.target.device
+        for a, st in todo:
+            eng.truncate(st.seq, st.fed)
+        items, toks, hids = [], [], []
+        for a, st in todo:
+            items.append((st.seq, st.pend_tokens, 1))
+            toks += st.pend_tokens
+            hids.append(st.pend_hidden)
+        chunks = eng.plan(items)
+        batch = eng._build(chunks)
+        x, normed = self._layer(batch, torch.tensor(toks, dtype=torch.int32, device=dev), self._fuse(torch.cat(hids)))
+        rows = batch.logit_rows.long()
+        for a, st in todo:
+            st.fed += len(st.pend_tokens)
+            st.pend_hidden, st.pend_tokens = None, None
+        return x[rows], normed[rows]
+
+    # ------------------------------------------------------------------ chains
+    def propose(self, actives, ks: Sequence[int]) -> List[List[int]]:
+        eng, dev = self.engine, self.target.device
+        todo = [(a, self.states.get(a.req.request_id)) for a in actives]
+        live = [(a, k, st) for (a, st), k in zip(todo, ks) if st is not None and st.pend_tokens]
+        out: Dict[int, List[int]] = {id(a): [] for a in actives}
+        if not live:
+            return [out[id(a)] for a in actives]
+        hid, normed = self._extend([(a, st) for a, k, st in live])
+        depth = 0
+        while live:
+            tok, _ = self._head_topk(normed, 1)
+            tok = tok[:, 0]
+            for (a, k, st), t in zip(live, tok.tolist()):
+                out[id(a)].append(int(t))
+            depth += 1
+            keep = [i for i, (a, k, st) in enumerate(live) if k > depth]
+            if not keep:
+                break
+            live = [live[i] for i in keep]
+            idx = torch.tensor(keep, device=dev)
+            hid, tok = hid[idx], tok[idx]
+            chunks = eng.plan([(st.seq, [int(t)], 1) for (a, k, st), t in zip(live, tok.tolist())])
+            batch = eng._build(chunks)
+            hid, normed = self._layer(batch, tok.to(torch.int32), hid)
+        self.steps += 1
+        self.proposed += sum(len(v) for v in out.values())
+        return [out[id(a)] for a in actives]
+
+    # ------------------------------------------------------------------ trees
+    def propose_tree(self, actives, width: int, depth: int, max_nodes: int = 16):
+        """One draft tree per request (``tree.DraftTree``; node 0 = the last accepted token).  Level 1 = the top ``width``
+        candidates after the confirmed rows; every further level runs the ``width`` frontier nodes (each sees the committed
+        context and its own path), adds every frontier node's top ``width`` candidates as children, and keeps the best
+        ``width`` of them by path probability as the next frontier.  ``max_nodes`` caps the rows handed to verification:
+        the best nodes by path probability, parents before children."""
+        from ..tree import DraftTree
+        eng, dev = self.engine, self.target.device
+        sts = [self.states.get(a.req.request_id) for a in actives]
+        live = [(i, a, st) for i, (a, st) in enumerate(zip(actives, sts)) if st is not None and st.pend_tokens]
+        result: List[Optional[DraftTree]] = [None] * len(actives)
+        if not live:
+            return result
+        hid0, normed0 = self._extend([(a, st) for _, a, st in live])
+        K = max(1, width)
+        toks, probs = self._head_topk(normed0, K)
+        # per request: nodes[n] = (token, parent node or -1, path probability); hid[n] = the layer's output row of node n
+        trees = []
+        for j in range(len(live)):
+            nodes = [(int(toks[j, c]), -1, float(probs[j, c])) for c in range(toks.shape[1])]
+            trees.append({"nodes": nodes, "frontier": list(range(len(nodes))), "hid": {-1: hid0[j]}})
+        group = max(self.cfg.num_heads // max(self.cfg.num_kv_heads, 1), 1)
+        row_cap = min(32, max(64 // group, 1))                    # rows of one sequence the verify attention takes
+        for level in range(2, max(depth, 1) + 1):
+            # one pass over, for every request, the path closure of its frontier (node ids grow with depth, so sorting puts
+            # parents first): a level-1 node is a root of the chunk (it sees the committed context), deeper nodes see
+            # their ancestors among the chunk's rows as well
+            chunks, tok_rows, hid_rows, spans = [], [], [], []
+            for (i, a, st), t in zip(live, trees):
+                need = set()
+                for n in t["frontier"]:
+                    m = n
+                    while m >= 0:
+                        need.add(m)
+                        m = t["nodes"][m][1]
+                order = sorted(need)
+                if len(order) > row_cap:
+                    order = order[:row_cap]
+                    t["frontier"] = [n for n in t["frontier"] if n in set(order)]
+                row_of = {n: r for r, n in enumerate(order)}
+                eng.truncate(st.seq, st.fed)
+                tokens = [t["nodes"][n][0] for n in order]
+                parents = [-1 if t["nodes"][n][1] < 0 else row_of[t["nodes"][n][1]] for n in order]
+                chunks += eng.plan_tree([(st.seq, tokens, parents)])
+                tok_rows += tokens
+                hid_rows += [t["hid"][t["nodes"][n][1]] for n in order]
+                spans.append((order, row_of))
+            batch = eng._build(chunks)
+            x, normed = self._layer(batch, torch.tensor(tok_rows, dtype=torch.int32, device=dev), torch.stack(hid_rows))
+            r0 = 0
+            for t, (order, row_of) in zip(trees, spans):
+                for n in order:
+                    t["hid"][n] = x[r0 + row_of[n]]
+                if t["frontier"]:
+                    ct, cp = self._head_topk(normed[torch.tensor([r0 + row_of[n] for n in t["frontier"]], device=dev)], K)
+                    cands = []
+                    for fi, n in enumerate(t["frontier"]):
+                        for c in range(ct.shape[1]):
+                            cands.append((t["nodes"][n][2] * float(cp[fi, c]), int(ct[fi, c]), n))
+                    cands.sort(key=lambda z: (-z[0], z[1]))
+                    front = []
+                    for score, tok, n in cands:
+                        t["nodes"].append((tok, n, score))
+                        if len(front) < K:
+                            front.append(len(t["nodes"]) - 1)
+                    t["frontier"] = front
+                r0 += len(order)
+        for (i, a, st), t in zip(live, trees):
+            eng.truncate(st.seq, st.fed)
+            # the rows handed to verification: best nodes by path probability, closed under parents, parents first
+            ranked = sorted(range(len(t["nodes"])), key=lambda n: (-t["nodes"][n][2], n))
+            chosen = set()
+            for n in ranked:
+                path, m = [], n
+                while m >= 0 and m not in chosen:
+                    path.append(m)
+                    m = t["nodes"][m][1]
+                if len(chosen) + len(path) + 1 <= max_nodes:
+                    chosen.update(path)
+            tree = DraftTree()
+            idx = {}
+            for n in sorted(chosen):
+                tok, par, _ = t["nodes"][n]
+                idx[n] = tree.add(0 if par < 0 else idx[par], tok)
+            result[i] = tree if len(tree.token) > 1 else None
+            self.proposed += len(tree.token) - 1
+        self.steps += 1
+        return result
 
 
 class DFlashDrafter(ChainDrafter):
-    """DFlash-style block drafter: proposes the whole block from one pass by feeding the last hidden state at every
-    block position (no per-token chain), trading acceptance for one launch per proposal."""
+    """DFlash-style block drafter: the whole block of ``k`` tokens comes from ONE pass over ``k`` rows that all read the last
+    confirmed hidden state (row j stands for position p + 1 + j and feeds the last confirmed token), instead of ``k``
+    dependent passes; rows attend causally to the rows before them.  Cheaper per proposal than a chain, lower acceptance at
+    depth (reference: ``crates/blaze/src/dflash.rs`` ``run`` :342, ``block`` :416, ``candidates`` :571)."""
     kind = "dflash"
 
-    def propose(self, actives, ks):
-        base = super().propose(actives, [1 if k > 0 else 0 for k in ks])
-        return [b * 1 for b in base]
+    def propose(self, actives, ks: Sequence[int]) -> List[List[int]]:
+        eng, dev = self.engine, self.target.device
+        todo = [(a, k, self.states.get(a.req.request_id)) for a, k in zip(actives, ks)]
+        todo = [(a, k, st) for a, k, st in todo if st is not None and st.pend_tokens and k > 0]
+        out: Dict[int, List[int]] = {id(a): [] for a in actives}
+        if not todo:
+            return [out[id(a)] for a in actives]
+        for a, k, st in todo:
+            eng.truncate(st.seq, st.fed)
+        # context pass: the confirmed pairs (their KV is what the block attends to)
+        items, toks, hids = [], [], []
+        for a, k, st in todo:
+            items.append((st.seq, st.pend_tokens, 1))
+            toks += st.pend_tokens
+            hids.append(st.pend_hidden)
+        batch = eng._build(eng.plan(items))
+        x = self.m.forward(batch, eng.kv, self._fuse(torch.tensor(toks, dtype=torch.int32, device=dev), torch.cat(hids)))
+        last = x[batch.logit_rows.long()]
+        first = self._greedy(x, batch.logit_rows)
+        for a, k, st in todo:
+            st.fed += len(st.pend_tokens)
+            st.pend_hidden, st.pend_tokens = None, None
+        # block pass: k - 1 more rows per request, all fed with the first proposal and the last hidden row
+        blk = [(a, k, st, j) for j, (a, k, st) in enumerate(todo) if k > 1]
+        for (a, k, st), t in zip(todo, first.tolist()):
+            out[id(a)].append(int(t))
+        if blk:
+            items, toks, hids = [], [], []
+            for a, k, st, j in blk:
+                t0 = int(first[j])
+                items.append((st.seq, [t0] * (k - 1), k - 1))
+                toks += [t0] * (k - 1)
+                hids.append(last[j].unsqueeze(0).expand(k - 1, -1))
+            batch = eng._build(eng.plan(items))
+            x = self.m.forward(batch, eng.kv, self._fuse(torch.tensor(toks, dtype=torch.int32, device=dev), torch.cat(hids).contiguous()))
+            more = self._greedy(x, batch.logit_rows).tolist()
+            r = 0
+            for a, k, st, j in blk:
+                out[id(a)] += [int(t) for t in more[r:r + k - 1]]
+                r += k - 1
+        self.steps += 1
+        self.proposed += sum(len(v) for v in out.values())
+        return [out[id(a)] for a in actives]
+
+    @classmethod
+    def load(cls, target: Model, draft_dir: str, max_seqs: int, max_model_len: int, kv_dtype: str = "bf16"):
+        """A DFlash checkpoint uses the one-layer head tensors under the ``mtp.`` names of ``load_mtp``."""
+        return cls.load_mtp(target, draft_dir, max_seqs, max_model_len, kv_dtype)
 
 
 def kind_of(architectures: Sequence[str]) -> str:

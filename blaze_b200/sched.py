@@ -1027,6 +1027,8 @@ class Scheduler:
                 eng.truncate(a.seq, a.computed)
             self._append(a, new, lps)
         if self.drafter is not None and hidden is not None:
+            if hasattr(self.drafter, "hidden_source"):
+                hidden = self.drafter.hidden_source(eng.model, hidden)
             for a, r0, p0, n in seen:
                 if a.seq is None or a.req.embed_only:
                     continue
@@ -1076,7 +1078,16 @@ class Scheduler:
                         out[id(a)] = d
         elif self.drafter is not None:
             reqs = [(a, k) for a, k in zip(decoders, want) if k > 0]
-            if reqs:
+            if reqs and cfg.draft_tree_width > 1 and hasattr(self.drafter, "propose_tree") and not self.engine.kv.gdn_layers:
+                # trees grown by the drafter itself (EAGLE): verified with the tree rows of the target's attention
+                eng = self.engine
+                group = max(eng.model.cfg.num_heads // max(eng.model.cfg.num_kv_heads, 1), 1)
+                cap = min(32, max(64 // group, 1), cfg.max_verify)
+                ts = self.drafter.propose_tree([a for a, _ in reqs], cfg.draft_tree_width, min(cfg.draft_tree_depth, cfg.max_draft), cap)
+                for (a, _), t in zip(reqs, ts):
+                    if t is not None:
+                        out[id(a)] = t
+            elif reqs:
                 ds = self.drafter.propose([a for a, _ in reqs], [k for _, k in reqs])
                 for (a, _), d in zip(reqs, ds):
                     if d:

@@ -412,3 +412,22 @@ def test_multimodal_request_gets_mrope_positions_and_image_rows():
     # same image twice: the second request reuses the cached prefix and gives the same tokens
     llm2, (x, y) = run(64, 1, cache=True)
     assert x == y == a
+
+
+@pytest.mark.parametrize("kind,tree", [("eagle", 1), ("eagle", 3), ("dflash", 1)])
+def test_eagle_and_dflash_drafters_keep_outputs_exact(kind, tree):
+    """EAGLE-style (chains and level-by-level trees from its low-rank candidate head) and DFlash-style (one block pass)
+    drafters through the product path (``LLM(spec_method=...)``): greedy and seeded sampled outputs are those of plain
+    decoding, drafts are proposed, the drafter's pages are all returned."""
+    ps = _prompts(3, 24, seed=21) + [[3, 4, 5, 6] * 6]
+    for sp in (SamplingParams(temperature=0.0, max_tokens=14), SamplingParams(temperature=0.8, top_k=10, seed=5, max_tokens=10)):
+        want = [o.token_ids for o in _llm().generate(ps, sp)]
+        llm = _llm(spec_method=kind, draft_tree_width=tree, draft_tree_depth=3)
+        assert llm.drafter is not None and llm.drafter.kind == kind
+        got = llm.generate(ps, sp)
+        assert [o.token_ids for o in got] == want
+        assert llm.sched.stats.draft_tokens > 0 and llm.drafter.proposed > 0
+        d = llm.drafter
+        assert not d.states and d.engine.pages.free_count == d.engine.num_pages - 1
+    if kind == "eagle":
+        assert llm.model.capture_layers == d.capture_layers and len(d.capture_layers) >= 1
