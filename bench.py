@@ -79,6 +79,13 @@ def main():
     ap.add_argument("--schedule", default="prefill_first", choices=["interleave", "prefill_first"],
                     help="scheduler policy of the end-to-end run (LLM(schedule=...)): prompts first, or decode rows + one chunk per step")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collectives: in-kernel peer memory, or NCCL")
+    ap.add_argument("--spec", default=None, choices=["mtp", "eagle", "dflash"],
+                    help="speculative-decoding benchmark: a one-layer drafter proposing --draft-k tokens, verify steps through the "
+                         "scheduler, acceptance imposed by a seeded pattern (first j of k accepted, j uniform in 0..k), prompts "
+                         "sharing --shared-prefix tokens through the prefix cache; exactness against plain decoding is checked")
+    ap.add_argument("--draft-k", type=int, default=4)
+    ap.add_argument("--shared-prefix", type=int, default=0)
+    ap.add_argument("--out-tokens", type=int, default=0, help="output tokens per request of the --spec run (0 = 512)")
     ap.add_argument("--cuda-profiler", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="bracket the timed decode steps (or the second prefill chunk) with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off)")
@@ -133,6 +140,8 @@ def main():
         cfg.layer_types = cfg.layer_types[:args.layers]
         invalid = f"truncated to {args.layers} layers"
     B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
+    if args.spec:
+        return spec_bench(args, cfg, dev, tp, group, comm, rank)
     out_tokens = args.e2e_out or 256
     max_len = P + max(out_tokens, K + W) + 32
     kv_tokens = B * (max_len + 16)
@@ -285,6 +294,58 @@ def main():
         sys.stdout.flush()
         sys.stderr.flush()
         eng._graphs.clear()
+        sync_all()
+        os._exit(0)
+    return 0
+
+
+def spec_bench(args, cfg, dev, tp, group, comm, rank):
+    """``--spec``: BASELINE config 5's shape of run (drafter k tokens, shared prefix, verify-timed, seeded acceptance)."""
+    import torch
+    from blaze_b200.benchmarks import spec
+    from blaze_b200.llm import LLM
+    B, P = args.batch, args.prompt_len
+    out_tokens = args.out_tokens or 512
+    shared = min(args.shared_prefix, P)
+    max_len = P + out_tokens + 64
+    llm = LLM(cfg, weight_format=args.weights, device=dev, tp=tp, kv_cache_dtype="fp8", kv_tokens=B * (max_len + 16) + shared + 4096,
+              max_seqs=B, max_model_len=max_len, chunk=4096, enable_prefix_caching=shared > 0, cache_slots=8, use_graphs=not args.no_graphs,
+              seed=4, max_step_tokens=B * (args.draft_k + 1) + 4096, spec_method=args.spec, max_draft=args.draft_k,
+              max_verify=args.draft_k + 1, schedule=args.schedule)
+    g = torch.Generator().manual_seed(4)
+    head = torch.randint(0, cfg.vocab_size, (shared,), generator=g).tolist()
+    prompts = [head + torch.randint(0, cfg.vocab_size, (P - shared,), generator=g).tolist() for _ in range(B)]
+
+    def sync_all():
+        if group is not None:
+            group.barrier()
+        torch.cuda.synchronize()
+    clk_path = os.path.join(tempfile.gettempdir(), f"blaze_clocks_spec_{rank}.csv")
+    sampler = clocks_sampler(clk_path, int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
+    r = spec.run(llm, prompts, out_tokens, args.draft_k, seed=4, sync=sync_all)
+    if sampler is not None:
+        time.sleep(0.15)
+        sampler.terminate()
+    t = torch.tensor([r["spec_ms"], r["plain_ms"]], device=dev)
+    if group is not None:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    spec_ms, plain_ms = float(t[0]), float(t[1])
+    status = llm.model.ops.take_status()
+    if rank == 0:
+        line = {"metric": "output tok/s (speculative decoding end to end: prefill + draft + verify, max over ranks)",
+                "value": r["output_tokens"] / (spec_ms / 1e3), "unit": "tok/s", "n_gpus": args.gpus, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "impl": "ours", "dtype": f"{args.weights} weights, fp8 KV, bf16 activations",
+                "data": "synthetic token ids, random-init N(0,0.02) weights, acceptance imposed by a seeded pattern",
+                "config": {"model": args.model, "global_batch": B, "seq_len": P, "shared_prefix": shared, "out_tokens": out_tokens,
+                           "parallelism": f"tp{args.gpus}", "collectives": comm, "drafter": args.spec, "draft_k": args.draft_k},
+                "plain_tok_s": r["output_tokens"] / (plain_ms / 1e3), "spec_ms": spec_ms, "plain_ms": plain_ms,
+                "exact_vs_plain_decoding": r["exact"], "acceptance": r["acceptance"], "accepted_per_step_hist": r["accepted_per_step_hist"],
+                "draft_tokens": r["draft_tokens"], "accepted_tokens": r["accepted_tokens"], "target_steps": r["steps"],
+                "cached_prompt_tokens": r["cached_prompt_tokens_spec"], "clocks": clocks_summary(clk_path), "device_status": status}
+        print(json.dumps(line))
+    if group is not None:
+        sys.stdout.flush()
+        llm.engine._graphs.clear()
         sync_all()
         os._exit(0)
     return 0

@@ -431,3 +431,19 @@ def test_eagle_and_dflash_drafters_keep_outputs_exact(kind, tree):
         assert not d.states and d.engine.pages.free_count == d.engine.num_pages - 1
     if kind == "eagle":
         assert llm.model.capture_layers == d.capture_layers and len(d.capture_layers) >= 1
+
+
+def test_spec_benchmark_harness_imposes_acceptance_and_checks_exactness():
+    """The speculative benchmark's synthetic acceptance: the drafter still runs, its proposals are rewritten so that the first
+    j are right (j seeded, uniform in 0..k), the streams equal the non-speculative ones, and a shared prompt prefix is
+    served from the prefix cache."""
+    from blaze_b200.benchmarks import spec
+    llm = _llm(spec_method="mtp", max_draft=4, cache_slots=8)
+    g = torch.Generator().manual_seed(2)
+    shared = torch.randint(0, 1024, (64,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 1024, (9,), generator=g).tolist() for _ in range(5)]
+    r = spec.run(llm, prompts, out_tokens=20, k=4, seed=4)
+    assert r["exact"] and r["output_tokens"] == 100
+    assert r["draft_tokens"] > 0 and 0.2 < r["acceptance"] < 0.8            # uniform j in 0..4 accepts half of the drafts on average
+    assert sum(r["accepted_per_step_hist"]) > 0 and r["cached_prompt_tokens_spec"] >= 4 * 64
+    assert r["steps"] < 5 * 20            # fewer target steps than tokens
