@@ -322,7 +322,7 @@ def spec_bench(args, cfg, dev, tp, group, comm, rank):
         torch.cuda.synchronize()
     clk_path = os.path.join(tempfile.gettempdir(), f"blaze_clocks_spec_{rank}.csv")
     sampler = clocks_sampler(clk_path, int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
-    r = spec.run(llm, prompts, out_tokens, args.draft_k, seed=4, sync=sync_all)
+    r = spec.run(llm, prompts, out_tokens, args.draft_k, seed=4, sync=sync_all, shared=shared)
     if sampler is not None:
         time.sleep(0.15)
         sampler.terminate()
@@ -339,9 +339,9 @@ def spec_bench(args, cfg, dev, tp, group, comm, rank):
                 "config": {"model": args.model, "global_batch": B, "seq_len": P, "shared_prefix": shared, "out_tokens": out_tokens,
                            "parallelism": f"tp{args.gpus}", "collectives": comm, "drafter": args.spec, "draft_k": args.draft_k},
                 "plain_tok_s": r["output_tokens"] / (plain_ms / 1e3), "spec_ms": spec_ms, "plain_ms": plain_ms,
-                "exact_vs_plain_decoding": r["exact"], "acceptance": r["acceptance"], "accepted_per_step_hist": r["accepted_per_step_hist"],
+                "exact_vs_plain_decoding": r["exact"], "agreement_with_plain_decoding": r["agreement"], "acceptance": r["acceptance"], "accepted_per_step_hist": r["accepted_per_step_hist"],
                 "draft_tokens": r["draft_tokens"], "accepted_tokens": r["accepted_tokens"], "target_steps": r["steps"],
-                "cached_prompt_tokens": r["cached_prompt_tokens_spec"], "clocks": clocks_summary(clk_path), "device_status": status}
+                "cached_prompt_tokens": r["cached_prompt_tokens_spec"], "cached_prompt_tokens_plain": r["cached_prompt_tokens_plain"], "clocks": clocks_summary(clk_path), "device_status": status}
         print(json.dumps(line))
     if group is not None:
         sys.stdout.flush()

@@ -257,10 +257,16 @@ class Acceptance:
             self.hit[d] = self.hit[d] * 0.9 + (1.0 if d < accepted else 0.0)
 
     def rate(self, d: int) -> float:
-        prev = 0.7 if d == 0 else self.rate(d - 1)
-        if d >= len(self.hit):
-            return prev
-        return (self.hit[d] + 2.0 * prev) / (self.tried[d] + 2.0)
+        return self.rates(d + 1)[d]
+
+    def rates(self, n: int) -> List[float]:
+        """Shrunk acceptance rates of depths 0..n-1 (each shrunk towards the depth before it; 0.7 before depth 0)."""
+        out, prev = [], 0.7
+        for d in range(n):
+            if d < len(self.hit):
+                prev = (self.hit[d] + 2.0 * prev) / (self.tried[d] + 2.0)
+            out.append(prev)
+        return out
 
 
 class SpecCost:
@@ -292,31 +298,30 @@ class SpecCost:
         return self.step_ms[lo] * (1.0 + 0.15 * max(0, (b // max(lo, 1)) - 1))
 
     def choose(self, acc: Sequence[Acceptance], max_draft: Sequence[int]) -> List[int]:
+        import heapq
         n = len(acc)
+        rates = [acc[i].rates(max_draft[i]) if max_draft[i] > 0 else [] for i in range(n)]
+        # greedy marginal allocation: always extend the sequence whose next draft token is most likely to be accepted
+        # (ties go to the lower index); a sequence's gain only shrinks as its draft grows, so a heap gives the arg-max order
+        heap = [(-rates[i][0], i) for i in range(n) if rates[i]]
+        heapq.heapify(heap)
         k = [0] * n
-        prob = [1.0] * n
         order: List[int] = []
-        while True:
-            best, gain = -1, 0.0
-            for i in range(n):
-                if k[i] < max_draft[i]:
-                    gi = prob[i] * acc[i].rate(k[i])
-                    if gi > gain:
-                        best, gain = i, gi
-            if best < 0 or gain < 0.05:
+        gains: List[float] = []
+        while heap:
+            g, i = heapq.heappop(heap)
+            if -g < 0.05:
                 break
-            prob[best] *= acc[best].rate(k[best])
-            k[best] += 1
-            order.append(best)
+            order.append(i)
+            gains.append(-g)
+            k[i] += 1
+            if k[i] < len(rates[i]):
+                heapq.heappush(heap, (g * rates[i][k[i]], i))
         # pick the prefix of `order` with the best expected tokens per millisecond
         best_rate, best_len = n / self.time_for(n), 0
         exp_tokens = float(n)
-        kk = [0] * n
-        pp = [1.0] * n
-        for j, i in enumerate(order):
-            pp[i] *= acc[i].rate(kk[i])
-            kk[i] += 1
-            exp_tokens += pp[i]
+        for j, g in enumerate(gains):
+            exp_tokens += g
             r = exp_tokens / self.time_for(n + j + 1)
             if r > best_rate:
                 best_rate, best_len = r, j + 1

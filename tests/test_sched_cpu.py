@@ -442,8 +442,9 @@ def test_spec_benchmark_harness_imposes_acceptance_and_checks_exactness():
     g = torch.Generator().manual_seed(2)
     shared = torch.randint(0, 1024, (64,), generator=g).tolist()
     prompts = [shared + torch.randint(0, 1024, (9,), generator=g).tolist() for _ in range(5)]
-    r = spec.run(llm, prompts, out_tokens=20, k=4, seed=4)
-    assert r["exact"] and r["output_tokens"] == 100
+    r = spec.run(llm, prompts, out_tokens=20, k=4, seed=4, shared=64)
+    assert r["exact"] and r["agreement"] == 1.0 and r["output_tokens"] == 100
     assert r["draft_tokens"] > 0 and 0.2 < r["acceptance"] < 0.8            # uniform j in 0..4 accepts half of the drafts on average
-    assert sum(r["accepted_per_step_hist"]) > 0 and r["cached_prompt_tokens_spec"] >= 4 * 64
+    assert sum(r["accepted_per_step_hist"]) > 0 and r["cached_prompt_tokens_spec"] >= 5 * 64
+    assert r["cached_prompt_tokens_plain"] >= 5 * 64          # the shared head is in the cache before either timed pass
     assert r["steps"] < 5 * 20            # fewer target steps than tokens
