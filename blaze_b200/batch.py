@@ -99,8 +99,12 @@ def tree_masks(parents: Sequence[int]) -> np.ndarray:
 
 
 def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device, pinned: Optional[torch.Tensor] = None,
-                pad_rows_to: int = 0, attn_group: int = 0) -> StepBatch:
+                pad_rows_to: int = 0, attn_group: int = 0, all_items: bool = False) -> StepBatch:
     """Pack the step metadata into one int32 buffer and copy it to ``device`` once.
+
+    ``attn_group`` > 0 sorts the sequences into the attention kernels' tiers (decode kernel: tiny / small row counts; row-block
+    kernel: the rest, cut into items of 128 rows); ``all_items`` sends every sequence to the row-block kernel (models whose
+    head_dim the decode kernel does not cover).
 
     ``pad_rows_to`` pads T (with rows of a dummy sequence that writes to slot -1 … never; rows are
     clamped to the last real row's data but flagged by ``seq_of_row = -1``) so that CUDA-graph
@@ -163,6 +167,8 @@ def build_batch(chunks: Sequence[SeqChunk], block_table_host: np.ndarray, device
         tpb = max(128 // attn_group, 1)
         for b, c in enumerate(chunks):
             rows = len(c.tokens) * attn_group
+            if all_items:
+                rows = SMALL_ROWS + 1
             if rows <= TINY_ROWS:
                 tiny_rows_max = max(tiny_rows_max, rows)
                 num_tiny += 1

@@ -101,7 +101,10 @@ def bench_gemm(a):
     from ..ops import get_ops
     from ..quant import Format
     ops = get_ops("cuda")
-    fmt = {"bf16": Format.DENSE, "nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "fp8": Format.FP8_CHANNEL}[a.kind]
+    fmt = {"bf16": Format.DENSE, "nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "fp8": Format.FP8_CHANNEL,
+           "fp8_block": Format.FP8_BLOCK, "fp8_block_mx": Format.FP8_BLOCK}[a.kind]
+    if a.kind.startswith("fp8_block"):          # exact per-K-block promotion, or the weight re-expressed in MXFP8
+        ops._fp8_block_exact = a.kind == "fp8_block"
     w = torch.randn(a.n, a.k, device="cuda") * 0.02
     lin0 = Linear.from_dense(w, fmt)
     del w
@@ -116,6 +119,10 @@ def bench_gemm(a):
         lins.append(c)
     x = torch.randn(a.m, a.k, device="cuda").bfloat16()
     xin = ops.quantize_rows(x, lin0) if ops._qmode(lin0) else x
+    if a.kind == "fp8_block" and not a.with_quant:
+        from ..linear import QuantAct
+        q, sc = ops.quantize_fp8_block(x)
+        xin = QuantAct(Format.FP8_BLOCK, q, sc, None, a.m, a.k, dense=x)
     wide = {"auto": None, "on": True, "off": False}[a.wide]
     sk = None if a.sk == "auto" else (False if a.sk == "off" else (True if a.sk == "on" else int(a.sk)))
     out = torch.empty(a.m, a.n, dtype=torch.float32 if a.f32 else torch.bfloat16, device="cuda")
@@ -179,6 +186,7 @@ def main(argv=None):
     p.add_argument("--ksplit", type=int, default=0)
     p.add_argument("--sk", default="auto", help="cluster split-K kernel: auto | on | off | a K-slice count 1..8")
     p.add_argument("--f32", action="store_true")
+    p.add_argument("--with-quant", action="store_true", help="fp8_block: time the 1x128 activation quantiser with the GEMM")
     p.add_argument("--iters", type=int, default=10)
     p = sub.add_parser("norm")
     p.add_argument("--rows", type=int, default=256)

@@ -156,6 +156,8 @@ class Engine:
         self.attn_group = 0
         if model.ops.is_cuda:
             self.attn_group = max(max(cfg.num_heads // tpw, 1) // max(cfg.num_kv_heads // tpw, 1), 1)
+        # the decode attention kernel covers head_dim 128; other head sizes run every sequence through the row-block kernel
+        self.attn_all_items = bool(model.ops.is_cuda and cfg.head_dim != 128)
         # Device status word, watched without a synchronisation of its own: after every step a 4-byte copy into this pinned
         # word is queued behind the step's kernels; whoever takes the step's results (and has synchronised for that)
         # calls check_status().  `status_source` replaces the device word in tests.
@@ -370,7 +372,8 @@ class Engine:
             if ev is not None:
                 ev.synchronize()
             pinned = self._pinned[self._pin_turn]
-        batch = build_batch(chunks, self.kv.block_table_host, self.device, pinned, attn_group=self.attn_group)
+        batch = build_batch(chunks, self.kv.block_table_host, self.device, pinned, attn_group=self.attn_group,
+                            all_items=self.attn_all_items)
         if pinned is not None:
             ev = torch.cuda.Event()
             ev.record()
@@ -522,7 +525,11 @@ class _Graph:
         self.batch.max_ctx = eng.ecfg.max_model_len
         from .batch import TINY_ROWS
         g = max(eng.attn_group, 1)
-        if g <= TINY_ROWS:
+        if eng.attn_all_items:
+            self.batch.item_seq = torch.arange(n, dtype=torch.int32, device=dev)     # one row-block item per sequence
+            self.batch.item_q0 = torch.zeros(n, dtype=torch.int32, device=dev)
+            self.batch.num_large = n
+        elif g <= TINY_ROWS:
             self.batch.tiny_rows_max, self.batch.num_tiny = g, n
         else:
             self.batch.small_rows_max, self.batch.num_small = g, n

@@ -58,6 +58,15 @@ class CudaOps:
         lib.blz_gemm_sk.restype = _c.c_int
         lib.blz_gemm_sk.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int,
                                     _c.c_int, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_gemm_fp8_block.restype = _c.c_int
+        lib.blz_gemm_fp8_block.argtypes = [VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int, _c.c_int,
+                                           VP, _c.c_longlong, VP, VP, _c.c_int, VP]
+        lib.blz_quant_fp8_block.restype = _c.c_int
+        lib.blz_quant_fp8_block.argtypes = [VP, _c.c_longlong, VP, VP, _c.c_longlong, _c.c_int, _c.c_int, VP]
+        # FP8 checkpoints with 128x128 fp32 block scales: "exact" keeps the stored codes and scales and promotes every K block
+        # in fp32 (blz_gemm_fp8_block); "mx" re-quantises the weight once to e4m3 with e8m0 scales per 32 elements and runs the
+        # hardware block-scaled MMA (faster, but only exact when the stored scales are powers of two)
+        self._fp8_block_exact = os.environ.get("BLAZE_FP8_BLOCK", "exact") != "mx"
         lib.blz_gemm_sk_default_ks.restype = _c.c_int
         lib.blz_gemm_sk_default_ks.argtypes = [_c.c_int] * 4
         # decode-sized GEMMs (few output tiles) take the cluster split-K kernel; BLAZE_GEMM_SK=0 keeps them on the
@@ -163,7 +172,7 @@ class CudaOps:
         g = torch.arange(I).view(I // 16, 16)
         return torch.cat([g, g + I], dim=1).reshape(-1)
 
-    def pack(self, lin: Linear, tiled: Optional[bool] = None, swiglu: bool = False):
+    def pack(self, lin: Linear, tiled: Optional[bool] = None, swiglu: bool = False, exact_fp8: bool = True):
         """``tiled`` (default: off unless BLAZE_TILED_WEIGHTS=1): store the weight tile-major (see ``tile_major``); the grouped
         expert GEMM asks for row-major.  ``swiglu``: interleave the gate and up rows for the GEMM's SwiGLU epilogue (the
         packed weight is then only valid for ``linear_swiglu``)."""
@@ -171,7 +180,7 @@ class CudaOps:
             if bool(lin.cuda_pack.get("swiglu")) != bool(swiglu):
                 raise CudaError("this weight was packed for the other epilogue (plain / SwiGLU)")
             return lin.cuda_pack
-        pk = self._pack(lin, self.swiglu_order(lin.N).to(self.device) if swiglu else None)
+        pk = self._pack(lin, self.swiglu_order(lin.N).to(self.device) if swiglu else None, exact_fp8=exact_fp8)
         pk["swiglu"] = bool(swiglu)
         if tiled is None:
             tiled = self._tiled_ok
@@ -181,8 +190,9 @@ class CudaOps:
         lin.cuda_pack = pk
         return pk
 
-    def _pack(self, lin: Linear, order: Optional[torch.Tensor] = None):
-        """``order``: optional permutation of the output rows applied to the weight, its scales, alpha and bias."""
+    def _pack(self, lin: Linear, order: Optional[torch.Tensor] = None, exact_fp8: bool = True):
+        """``order``: optional permutation of the output rows applied to the weight, its scales, alpha and bias.
+        ``exact_fp8`` = False: an FP8 block-scale weight is re-expressed in MXFP8 (what the grouped expert GEMM consumes)."""
         dev = self.device
 
         def perm(t):
@@ -196,6 +206,10 @@ class CudaOps:
             sf[:lin.N] = perm(lin.sf.to(dev).view(torch.uint8))
             pk = {"kind": 1, "w": perm(lin.w.to(dev)).contiguous(), "sf": quant.swizzle_sf_128x4(sf),
                   "alpha": perm(lin.alpha.to(dev, torch.float32)).contiguous()}
+        elif lin.fmt == Format.FP8_BLOCK and self._fp8_block_exact and exact_fp8 and order is None and tuple(lin.block) == (128, 128) \
+                and lin.K % 128 == 0 and tuple(lin.sf.shape) == ((lin.N + 127) // 128, lin.K // 128):
+            pk = {"kind": 4, "w": lin.w.to(dev).view(torch.uint8).contiguous(), "sf": lin.sf.to(dev, torch.float32).contiguous(),
+                  "alpha": None}
         elif lin.fmt in (Format.MXFP8, Format.FP8_BLOCK):
             if lin.fmt == Format.FP8_BLOCK:
                 # 128x128 fp32 block scales have no native MMA mode: re-express the weight as e4m3 with one e8m0
@@ -227,15 +241,30 @@ class CudaOps:
             rs = None
         return QuantAct(fmt, data, sf, rs, T, K)
 
-    @staticmethod
-    def _qmode(lin: Optional[Linear]) -> int:
+    def _qmode(self, lin: Optional[Linear]) -> int:
+        """Activation format the producer's epilogue should emit for ``lin``: 0 bf16, 1 NVFP4, 2 MXFP8.  (The exact FP8
+        block-scale GEMM quantises its bf16 input itself, to e4m3 with one fp32 scale per 1x128 group.)"""
         if lin is None or not lin.act_quant:
             return 0
         if lin.fmt == Format.NVFP4:
             return 1
-        if lin.fmt in (Format.MXFP8, Format.FP8_BLOCK):
+        if lin.fmt == Format.MXFP8:
             return 2
+        if lin.fmt == Format.FP8_BLOCK:
+            pk = lin.cuda_pack
+            return 0 if (pk["kind"] == 4 if pk is not None else self._fp8_block_exact) else 2
         return 0
+
+    def quantize_fp8_block(self, x: torch.Tensor):
+        """bf16 ``[T, K]`` -> (e4m3 codes ``[T, K]``, fp32 scales ``[K / 128, T4]``) with one scale per row and 128 columns."""
+        T, K = x.shape
+        ld = (T + 3) // 4 * 4
+        q = torch.empty(T, K, dtype=torch.uint8, device=self.device)
+        sc = torch.empty(K // 128, ld, dtype=torch.float32, device=self.device)
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        self._check(self.lib.blz_quant_fp8_block(_ptr(x), x.stride(0), _ptr(q), _ptr(sc), ld, T, K, self._stream()), "quant_fp8_block")
+        return q, sc
 
     def quantize_rows(self, x: torch.Tensor, lin: Linear) -> QuantAct:
         """bf16 ``[T, K]`` → the activation format ``lin`` consumes."""
@@ -272,7 +301,8 @@ class CudaOps:
     def linear_swiglu(self, lin: Linear, x, quant_for: Optional[Linear] = None):
         """``silu(x @ Wg^T) * (x @ Wu^T)`` for a stacked ``[gate; up]`` weight with the activation computed in the GEMM's
         epilogue (the ``[T, 2I]`` intermediate never reaches memory); quantised for ``quant_for`` when that GEMM wants it."""
-        if lin.N % 32 or (lin.N // 2) % 8:
+        exact8 = lin.fmt == Format.FP8_BLOCK and (lin.cuda_pack["kind"] == 4 if lin.cuda_pack is not None else self._fp8_block_exact)
+        if lin.N % 32 or (lin.N // 2) % 8 or exact8:
             return self.silu_mul(self.linear(lin, x), quant_for=quant_for)
         act = self.linear(lin, x, swiglu=True)
         return self.quantize_rows(act, quant_for) if self._qmode(quant_for) else act
@@ -293,6 +323,29 @@ class CudaOps:
                                               self._stream()), "argmax_parts")
         return (out, vals) if want_values else out
 
+    def _linear_fp8_block(self, lin, pk, x, f32, out, swiglu, argmax_parts, wide, sk):
+        if swiglu or argmax_parts is not None or wide or (sk is not None and sk is not False):
+            raise CudaError("the FP8 block-scale GEMM has the plain epilogue only (bf16 / fp32 output, optional bias)")
+        q = sc = None
+        if isinstance(x, QuantAct):
+            if x.wait is not None:
+                raise CudaError("an activation with a pending peer wait cannot feed the FP8 block-scale GEMM")
+            if x.fmt == Format.FP8_BLOCK:
+                q, sc = x.data, x.sf              # already in 1x128 groups (quantize_fp8_block)
+            else:
+                x = x.dense
+        M = q.shape[0] if q is not None else x.shape[0]
+        if out is None:
+            out = torch.empty(M, lin.N, dtype=torch.float32 if f32 else torch.bfloat16, device=self.device)
+        if M == 0:
+            return out
+        if q is None:
+            q, sc = self.quantize_fp8_block(x)
+        self._check(self.lib.blz_gemm_fp8_block(_ptr(q), lin.K, _ptr(pk["w"]), lin.K, _ptr(out), out.stride(0), M, lin.N, lin.K,
+                                                _ptr(sc), sc.stride(0), _ptr(pk["sf"]), _ptr(pk["bias"]), int(f32), self._stream()),
+                    "gemm_fp8_block")
+        return out
+
     def linear(self, lin: Linear, x, out_dtype=None, out: Optional[torch.Tensor] = None, bn: int = 0, max_ctas: int = 0,
                wide: Optional[bool] = None, ksplit: int = 0, swiglu: bool = False, argmax_parts=None, sk=None):
         """``wide``: None = choose; False = the 128-column kernel (needed by the fused all-reduce epilogue); True = insist on
@@ -303,6 +356,8 @@ class CudaOps:
         f32 = out_dtype == torch.float32
         n_out = lin.N // 2 if swiglu else lin.N
         sfa = rs = None
+        if kind == 4:
+            return self._linear_fp8_block(lin, pk, x, f32, out, swiglu, argmax_parts, wide, sk)
         if kind in (1, 2):
             if not isinstance(x, QuantAct):
                 x = self.quantize_rows(x.contiguous(), lin)
@@ -485,11 +540,17 @@ class CudaOps:
         # the decode kernel runs once per row tier: plain decode rows (<= 8 rows per kv head) take its two-CTAs-per-SM
         # configuration, short multi-token sequences (verify rows, prompt tails) the wider one
         tiers = []
+        if D != 128:
+            # the decode kernel is built for head_dim 128: every sequence is a row-block item here (engine.attn_all_items)
+            if batch.item_seq is None or batch.tiny_rows_max or batch.small_rows_max:
+                raise CudaError(f"head_dim {D}: the batch must send every sequence to the row-block attention kernel")
+            if getattr(batch, "tree_mask", None) is not None:
+                raise CudaError(f"head_dim {D}: draft trees are verified by the decode kernel, which covers head_dim 128 only")
         if batch.tiny_rows_max:
             tiers.append((1, batch.tiny_rows_max, batch.num_tiny))
         if batch.small_rows_max:
             tiers.append((batch.tiny_rows_max + 1 if batch.tiny_rows_max else 1, batch.small_rows_max, batch.num_small))
-        if not tiers and not batch.num_large:
+        if not tiers and not batch.num_large and D == 128:
             tiers.append((1, group * batch.max_q_len, B))
         for lo, hi, count in tiers:
             nmax = 16
@@ -555,10 +616,10 @@ class CudaOps:
             return ex.cuda_pack
 
         def stack(lins):
-            pk0 = self.pack(lins[0], tiled=False)
+            pk0 = self.pack(lins[0], tiled=False, exact_fp8=False)
             kind = pk0["kind"]
-            w = torch.cat([self.pack(l, tiled=False)["w"] for l in lins])
-            alpha = torch.cat([self.pack(l, tiled=False)["alpha"] for l in lins]) if pk0["alpha"] is not None else None
+            w = torch.cat([self.pack(l, tiled=False, exact_fp8=False)["w"] for l in lins])
+            alpha = torch.cat([self.pack(l, tiled=False, exact_fp8=False)["alpha"] for l in lins]) if pk0["alpha"] is not None else None
             sf = None
             if kind in (1, 2):
                 l0 = lins[0]
@@ -568,7 +629,7 @@ class CudaOps:
                 if kind == 1:
                     raw = torch.cat([l.sf.to(self.device).view(torch.uint8) for l in lins])
                 else:
-                    raw = torch.cat([quant.unswizzle_sf_128x4(self.pack(l, tiled=False)["sf"], (l.N + 255) // 256 * 256, per)[:l.N] for l in lins])
+                    raw = torch.cat([quant.unswizzle_sf_128x4(self.pack(l, tiled=False, exact_fp8=False)["sf"], (l.N + 255) // 256 * 256, per)[:l.N] for l in lins])
                 rows = (raw.shape[0] + 255) // 256 * 256
                 buf = torch.zeros(rows, per, dtype=torch.uint8, device=self.device)
                 buf[:raw.shape[0]] = raw

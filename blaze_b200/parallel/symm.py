@@ -285,7 +285,10 @@ class SymmAllReduce:
                 partial, i = buf, self.cur
         mode = 0
         if quant_for is not None and quant_for.act_quant and norm_w is not None:
-            mode = 1 if quant_for.fmt == Format.NVFP4 else (2 if quant_for.fmt in (Format.MXFP8, Format.FP8_BLOCK) else 0)
+            # (an FP8 block-scale consumer takes MXFP8 rows only when its weight was re-expressed in MXFP8; its exact kernel
+            # quantises bf16 rows itself)
+            mx = quant_for.fmt == Format.MXFP8 or (quant_for.fmt == Format.FP8_BLOCK and (quant_for.cuda_pack or {}).get("kind") == 2)
+            mode = 1 if quant_for.fmt == Format.NVFP4 else (2 if mx else 0)
         a = self.arena
         off_in = self.off_in[i]
         off_out = self.off_out if mode == 0 else self.off_q

@@ -11,14 +11,20 @@
 // tensor core with no register pass.  The online-softmax state (max, sum, output row) stays in registers:
 // one thread per query row.
 //
-// Roles (192 threads): warp 0 loads pages (block-table walk + bulk copies), warp 1 issues MMAs, warps 2-5
+// Roles, head_dim 128 (192 threads): warp 0 loads pages (block-table walk + bulk copies), warp 1 issues MMAs, warps 2-5
 // run softmax / accumulation on TMEM lane quadrant (warp & 3).
+// head_dim 256 (384 threads = three warpgroups): an output row has 256 fp32 accumulators, too many for one thread, so
+// warps 0-3 run softmax and accumulate output columns 0-127, warps 4-7 accumulate columns 128-255 (they get each tile's
+// rescale factor and the final row sum through shared memory), warp 8 loads, warp 9 issues MMAs.  The register file is
+// re-divided between the warpgroups with setmaxnreg (240 / 200 / 64 per thread).  The 256-column output accumulator is
+// single-buffered in TMEM (S stays double-buffered): 2 x 128 + 256 = 512 columns.
 //
 // Reference counterparts: kernels/src/cuda/mha_nvfp4.cu mha_decode_kernel :259 + mha_combine_kernel :572
 // (mma.sync, register dequant), mha_verify.cu :50, mha_prefill.cu prefill_kernel :118 (FA2 style, D=256 only).
 #include "blaze/host.h"
 #include "blaze/sm100.cuh"
 #include "blaze/attn.cuh"
+#include <type_traits>
 
 namespace blz {
 
@@ -30,20 +36,33 @@ struct AttnCfg {
   static constexpr int STAGES = D == 128 ? 4 : 2;
   static constexpr int Q_BYTES = 128 * D;
   static constexpr int P_BYTES = 128 * 128;
-  static constexpr int SMEM = Q_BYTES + STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 1024 + 512;
+  static constexpr bool WIDE = D > 128;            // two accumulator warpgroups, one output buffer in TMEM
+  static constexpr int THREADS = WIDE ? 384 : 192;
+  static constexpr int OBUF = WIDE ? 1 : 2;
+  static constexpr int XCH_BYTES = WIDE ? (4 * 128 + 2 * 128 * 2) * 4 : 0;   // rescale factors [4][128], (max, sum) [2][128][2]
+  static constexpr int SMEM = Q_BYTES + STAGES * 2 * TILE_BYTES + 2 * P_BYTES + XCH_BYTES + 1024 + 512;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
 };
 
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 template <int D>
-__global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
+__global__ void __launch_bounds__(AttnCfg<D>::THREADS, 1) attn_tc_kernel(AttnParams p) {
   using Cfg = AttnCfg<D>;
   constexpr int ST = Cfg::STAGES;
+  constexpr bool WIDE = Cfg::WIDE;
+  constexpr int OBUF = Cfg::OBUF;
+  constexpr int ACC = WIDE ? 128 : D;              // output columns accumulated by one thread
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::Q_BYTES;
   uint8_t* sV = sK + ST * Cfg::TILE_BYTES;
   uint8_t* sP = sV + ST * Cfg::TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::P_BYTES);
+  float* s_alpha = reinterpret_cast<float*>(sP + 2 * Cfg::P_BYTES);     // WIDE: [4][128] rescale factor of (tile & 3, row)
+  float* s_fin = s_alpha + 4 * 128;                                     // WIDE: [2][128][2] (max, sum) of (item & 1, row)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::P_BYTES + Cfg::XCH_BYTES);
   uint64_t* k_full = bars;                 // [ST]
   uint64_t* v_full = k_full + ST;          // [ST]
   uint64_t* kv_empty = v_full + ST;        // [ST]
@@ -54,31 +73,45 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
   uint64_t* o_empty = o_full + 2;          // [2]
   uint64_t* q_full = o_empty + 2;          // [1]
   uint64_t* q_empty = q_full + 1;          // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + 1);
+  uint64_t* fin_full = q_empty + 1;        // [2] WIDE: the softmax warps have published (max, sum) of an item
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fin_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // role of this warp
+  const bool is_loader = warp == (WIDE ? 8 : 0), is_mma = warp == (WIDE ? 9 : 1);
+  const bool is_softmax = WIDE ? warp < 4 : (warp >= 2 && warp < 6);
   if (threadIdx.x == 0) {
     for (int i = 0; i < ST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&p_full[i], 4);
-      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4);
+      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], WIDE ? 8 : 4);
+      mbar_init(&fin_full[i], 4);
     }
     mbar_init(q_full, 4); mbar_init(q_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  if (is_mma) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // output accumulator buffer, its barrier index and barrier parity for global tile number gj
+  auto o_buf = [&](int gj) -> int { return OBUF == 2 ? (gj & 1) : 0; };
+  auto o_par = [&](int gj) -> uint32_t { return (uint32_t)(OBUF == 2 ? ((gj >> 1) & 1) : (gj & 1)); };
 
   const int group = p.Hq / p.Hkv;
   const int total = p.num_items * p.Hkv * p.splits;
+
+  // One role's whole pass over this CTA's work items.  Every role walks the same item list with its own copy of the
+  // counters; the loop lives inside the role (not the roles inside one loop) so that each role's code follows its own
+  // setmaxnreg and is compiled against that register budget.
+  constexpr int R_LOAD = 0, R_MMA = 1, R_SOFTMAX = 2, R_UPPER = 3;
+  auto run = [&](auto role_tag) {
+  constexpr int ROLE = decltype(role_tag)::value;
   int g = 0;      // tiles processed by this CTA so far (drives stage / phase bookkeeping in every role)
   int item_it = 0;
-
   for (int w = blockIdx.x; w < total; w += gridDim.x) {
     // ---- decode the work item (identical in every role)
     const int split = w % p.splits;
@@ -101,7 +134,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
     const int n = max(t1 - t0, 0);
     const int slot = p.slots[b];
 
-    if (warp == 0) {
+    if constexpr (ROLE == R_LOAD) {
       // -------------------------------------------------------------- page loader
       const int* bt = p.block_table + (size_t)slot * p.bt_stride;
       const int npages = (kv_end + 15) >> 4;
@@ -123,7 +156,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
         }
         __syncwarp();
       }
-    } else if (warp == 1) {
+    } else if constexpr (ROLE == R_MMA) {
       // -------------------------------------------------------------- MMA issuer
       if (lane == 0 && n > 0) {
         bool ok = mbar_wait(q_full, item_it & 1, abort_flag, p.status);
@@ -133,15 +166,16 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
           const int s = gj % ST, pb = gj & 1;
           if (!mbar_wait(&v_full[s], (gj / ST) & 1, abort_flag, p.status)) return false;
           if (!mbar_wait(&p_full[pb], (gj >> 1) & 1, abort_flag, p.status)) return false;
-          if (!mbar_wait(&o_empty[pb], ((gj >> 1) & 1) ^ 1, abort_flag, p.status)) return false;
+          const int ob = o_buf(gj);
+          if (!mbar_wait(&o_empty[ob], o_par(gj) ^ 1, abort_flag, p.status)) return false;
           tc_fence_after();
           const uint32_t pa = smem_u32(sP + pb * Cfg::P_BYTES), va = smem_u32(sV + s * Cfg::TILE_BYTES);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            mma_f8(tmem + 256 + pb * 128, make_smem_desc(pa + ks * 256, 128, 1024, kSwzNone),
+            mma_f8(tmem + 256 + ob * 128, make_smem_desc(pa + ks * 256, 128, 1024, kSwzNone),
                    make_smem_desc(va + ks * 2 * Cfg::PAGE_BYTES, Cfg::PAGE_BYTES, 128, kSwzNone),
                    make_idesc(0, 0, 128, D), ks > 0);
-          mma_commit(&o_full[pb]);
+          mma_commit(&o_full[ob]);
           mma_commit(&kv_empty[s]);
           return true;
         };
@@ -161,6 +195,54 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
         if (ok) ok = issue_pv(g + n - 1);
         if (ok) mma_commit(q_empty);
       }
+    } else if constexpr (ROLE == R_UPPER) {
+      // -------------------------------------------------------------- output columns 128..255 (head_dim 256 only)
+      const int qd = warp & 3;
+      const int r = qd * 32 + lane;
+      const bool live = r < nrows;
+      const int tq = q0 + r / group;
+      const int hq = kh * group + r % group;
+      float acc[ACC];
+#pragma unroll
+      for (int i = 0; i < ACC; ++i) acc[i] = 0.f;
+      bool ok = true;
+      for (int i = 0; i < n && ok; ++i) {
+        const int gj = g + i;
+        ok = __all_sync(0xffffffffu, mbar_wait(&o_full[0], o_par(gj), abort_flag, p.status));
+        if (!ok) break;
+        tc_fence_after();
+        const float alpha = s_alpha[(gj & 3) * 128 + r];     // written before the row's probabilities were handed over
+#pragma unroll
+        for (int cch = 0; cch < ACC / 32; ++cch) {
+          uint32_t v[32];
+          tmem_ld32(tmem + 256 + 128 + cch * 32 + ((uint32_t)(qd * 32) << 16), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) acc[cch * 32 + k] = acc[cch * 32 + k] * alpha + __uint_as_float(v[k]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_empty[0]);
+      }
+      if (n > 0 && ok) ok = mbar_wait(&fin_full[item_it & 1], (uint32_t)((item_it >> 1) & 1), abort_flag, p.status);
+      if (ok && live && n > 0) {
+        const float m_fin = s_fin[((item_it & 1) * 128 + r) * 2], l_fin = s_fin[((item_it & 1) * 128 + r) * 2 + 1];
+        if (p.splits == 1) {
+          const float inv = l_fin > 0.f ? p.v_scale / l_fin : 0.f;
+          __nv_bfloat16* orow = p.out + ((size_t)(r0 + tq) * p.Hq + hq) * D + 128;
+#pragma unroll
+          for (int j = 0; j < ACC; j += 8) {
+            uint4 u = make_uint4(pack_bf16x2(acc[j] * inv, acc[j + 1] * inv), pack_bf16x2(acc[j + 2] * inv, acc[j + 3] * inv),
+                                 pack_bf16x2(acc[j + 4] * inv, acc[j + 5] * inv), pack_bf16x2(acc[j + 6] * inv, acc[j + 7] * inv));
+            *reinterpret_cast<uint4*>(orow + j) = u;
+          }
+        } else {
+          float* po = p.part_o + ((size_t)w * 128 + r) * D + 128;
+#pragma unroll
+          for (int j = 0; j < ACC; j += 4) *reinterpret_cast<float4*>(po + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          (void)m_fin;
+        }
+      }
     } else {
       // -------------------------------------------------------------- softmax + accumulate (one row per thread)
       const int qd = warp & 3;
@@ -169,9 +251,9 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
       const int tq = q0 + r / group;                      // token within the sequence's rows
       const int hq = kh * group + r % group;
       const int pos_q = ctx - qlen + tq;                  // last visible key position
-      float acc[D];
+      float acc[ACC];
 #pragma unroll
-      for (int i = 0; i < D; ++i) acc[i] = 0.f;
+      for (int i = 0; i < ACC; ++i) acc[i] = 0.f;
       float m_run = -INFINITY, l_run = 0.f, qscale = 1.f;
       if (n > 0) {
         // ---- Q row → e4m3 in the K-major core-matrix layout
@@ -212,11 +294,12 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
       float alpha_prev = 1.f;
       bool ok = true;
       auto accumulate = [&](int gj, float alpha) -> bool {
-        const int ob = gj & 1;
-        if (!mbar_wait(&o_full[ob], (gj >> 1) & 1, abort_flag, p.status)) return false;
+        const int ob = o_buf(gj);
+        // tcgen05.ld is warp-collective: the wait's outcome is made warp-uniform before any lane loads
+        if (!__all_sync(0xffffffffu, mbar_wait(&o_full[ob], o_par(gj), abort_flag, p.status))) return false;
         tc_fence_after();
 #pragma unroll
-        for (int cch = 0; cch < D / 32; ++cch) {
+        for (int cch = 0; cch < ACC / 32; ++cch) {
           uint32_t v[32];
           tmem_ld32(tmem + 256 + ob * 128 + cch * 32 + ((uint32_t)(qd * 32) << 16), v);
           tmem_ld_wait();
@@ -230,7 +313,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
       };
       for (int i = 0; i < n && ok; ++i) {
         const int gi = g + i, sb = gi & 1;
-        if (!mbar_wait(&s_full[sb], (gi >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (gi >> 1) & 1, abort_flag, p.status))) { ok = false; break; }
         tc_fence_after();
         const int k0 = (t0 + i) * 128;
         const int lim = min(pos_q, kv_end - 1) - k0;        // columns <= lim are visible to this row
@@ -285,6 +368,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
         }
         l_run = l_run * alpha + rs;
         m_run = m_new;
+        if constexpr (WIDE) s_alpha[(gi & 3) * 128 + r] = alpha;   // for the warps that accumulate the other output half
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
@@ -293,13 +377,21 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
         alpha_prev = alpha;
       }
       if (ok && n > 0) ok = accumulate(g + n - 1, alpha_prev);
+      if constexpr (WIDE) {
+        if (n > 0) {           // (also after a failed wait: the other warpgroup's bounded wait then ends at once, via the abort flag)
+          s_fin[((item_it & 1) * 128 + r) * 2] = m_run;
+          s_fin[((item_it & 1) * 128 + r) * 2 + 1] = l_run;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&fin_full[item_it & 1]);
+        }
+      }
       // ---- write out
       if (ok && live) {
         if (p.splits == 1) {
           const float inv = l_run > 0.f ? p.v_scale / l_run : 0.f;
           __nv_bfloat16* orow = p.out + ((size_t)(r0 + tq) * p.Hq + hq) * D;
 #pragma unroll
-          for (int j = 0; j < D; j += 8) {
+          for (int j = 0; j < ACC; j += 8) {
             uint4 u = make_uint4(pack_bf16x2(acc[j] * inv, acc[j + 1] * inv), pack_bf16x2(acc[j + 2] * inv, acc[j + 3] * inv),
                                  pack_bf16x2(acc[j + 4] * inv, acc[j + 5] * inv), pack_bf16x2(acc[j + 6] * inv, acc[j + 7] * inv));
             *reinterpret_cast<uint4*>(orow + j) = u;
@@ -307,7 +399,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
         } else {
           float* po = p.part_o + ((size_t)w * 128 + r) * D;
 #pragma unroll
-          for (int j = 0; j < D; j += 4) *reinterpret_cast<float4*>(po + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          for (int j = 0; j < ACC; j += 4) *reinterpret_cast<float4*>(po + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
           p.part_ml[((size_t)w * 128 + r) * 2] = m_run;
           p.part_ml[((size_t)w * 128 + r) * 2 + 1] = l_run;
         }
@@ -317,9 +409,29 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(AttnParams p) {
     if (n > 0) ++item_it;
     if (*abort_flag) break;
   }
+  };   // run
+
+  if constexpr (WIDE) {
+    // 384 threads start with 168 registers each; the loader / MMA warpgroup hands most of its share to the other two
+    if (warp >= 8) {
+      reg_dec<64>();
+      if (is_loader) run(std::integral_constant<int, R_LOAD>{});
+      else if (is_mma) run(std::integral_constant<int, R_MMA>{});
+    } else if (warp >= 4) {
+      reg_inc<200>();
+      run(std::integral_constant<int, R_UPPER>{});
+    } else {
+      reg_inc<240>();
+      run(std::integral_constant<int, R_SOFTMAX>{});
+    }
+  } else {
+    if (is_loader) run(std::integral_constant<int, R_LOAD>{});
+    else if (is_mma) run(std::integral_constant<int, R_MMA>{});
+    else if (is_softmax) run(std::integral_constant<int, R_SOFTMAX>{});
+  }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (is_mma) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -373,7 +485,7 @@ BLZ_API int blz_attn_tc(const void* q, void* out, const void* pool, const int* b
                         float v_scale, int splits, float* part_o, float* part_ml, int max_ctas, cudaStream_t stream) {
   using namespace blz;
   if (num_items <= 0) return 0;
-  if (D != 128 || Hq % Hkv || 128 % (Hq / Hkv) || splits < 1 || (splits > 1 && (!part_o || !part_ml)))
+  if ((D != 128 && D != 256) || Hq % Hkv || 128 % (Hq / Hkv) || splits < 1 || (splits > 1 && (!part_o || !part_ml)))
     return (int)cudaErrorInvalidValue;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.pool = (const uint8_t*)pool;
@@ -386,19 +498,22 @@ BLZ_API int blz_attn_tc(const void* q, void* out, const void* pool, const int* b
   p.tokens_per_block = 128 / (Hq / Hkv);
   p.status = status_word();
   p.min_rows = 0; p.max_rows = 1 << 30; p.row_blocks = 1; p.prof = nullptr;
-  static PerDeviceOnce configured;
+  static PerDeviceOnce configured, configured_wide;
   {
-    cudaError_t e = configured.smem_limit(attn_tc_kernel<128>, AttnCfg<128>::SMEM);
+    cudaError_t e = D == 128 ? configured.smem_limit(attn_tc_kernel<128>, AttnCfg<128>::SMEM)
+                             : configured_wide.smem_limit(attn_tc_kernel<256>, AttnCfg<256>::SMEM);
     if (e != cudaSuccess) return (int)e;
   }
   const int total = num_items * Hkv * splits;
   int grid = total < sm_count() ? total : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  attn_tc_kernel<128><<<grid, 192, AttnCfg<128>::SMEM, stream>>>(p);
+  if (D == 128) attn_tc_kernel<128><<<grid, AttnCfg<128>::THREADS, AttnCfg<128>::SMEM, stream>>>(p);
+  else attn_tc_kernel<256><<<grid, AttnCfg<256>::THREADS, AttnCfg<256>::SMEM, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (splits > 1) {
-    attn_combine_kernel<128><<<num_items * Hkv, 256, 0, stream>>>(p);
+    if (D == 128) attn_combine_kernel<128><<<num_items * Hkv, 256, 0, stream>>>(p);
+    else attn_combine_kernel<256><<<num_items * Hkv, 256, 0, stream>>>(p);
     e = cudaGetLastError();
   }
   return (int)e;

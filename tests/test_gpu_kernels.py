@@ -146,6 +146,56 @@ def test_gemm_cluster_split_k(ops, fmt, M, N, K, ks):
     assert rel < 0.05
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 1024, 2048), (1, 384, 512), (77, 448, 1024), (300, 520, 384), (130, 256, 128),
+                                   (1000, 2048, 5120)])
+def test_gemm_fp8_block_scale_exact(ops, M, N, K):
+    """FP8 weights with 128x128 fp32 block scales that are NOT powers of two and 1x128 activation groups: every K block is
+    promoted in fp32 with its own (row, block) scale, so the result matches the fp32 oracle on the stored codes to bf16
+    rounding, and the activation quantiser reproduces the oracle's codes and scales."""
+    from blaze_b200 import quant
+    g = torch.Generator(device=DEV).manual_seed(41)
+    x = (torch.randn(M, K, generator=g, device=DEV) * (1 + 3 * torch.rand(M, 1, generator=g, device=DEV))).bfloat16()
+    w = torch.randn(N, K, generator=g, device=DEV) * 0.02
+    w = w * (0.3 + 2 * torch.rand((N + 127) // 128, 1, K // 128, 1, generator=g, device=DEV)).expand(-1, 128, -1, 128) \
+        .reshape(-1, K)[:N]                                                  # very different magnitudes per block
+    lin = Linear.from_dense(w, Format.FP8_BLOCK)
+    lin.bias = (torch.randn(N, generator=g, device=DEV) * 0.1).bfloat16()
+    assert ops.pack(lin)["kind"] == 4 and ops._qmode(lin) == 0
+    # the quantiser against the oracle's 1x128 groups
+    q, sc = ops.quantize_fp8_block(x)
+    xg = x.float().view(M, K // 128, 128)
+    s_want = (xg.abs().amax(-1) / quant.FP8_MAX).clamp_min(1e-12)
+    s_got = sc[:, :M].t().contiguous()
+    assert torch.allclose(s_got, s_want, rtol=1e-6, atol=0)          # (a division by 448 against a multiplication by 1/448)
+    q_want = quant.to_e4m3(xg / s_got.unsqueeze(-1)).view(M, K)
+    assert torch.equal(q.view(torch.float8_e4m3fn).float(), q_want.float())
+    guard = torch.full((M + 2, N + 8), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = guard[1:M + 1, :N]
+    y = ops.linear(lin, x, out=out)
+    y32 = ops.linear(lin, x, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert (guard[0] == 7).all() and (guard[M + 1] == 7).all() and (guard[:, N:] == 7).all(), "wrote outside the output"
+    want = (q_want.float().view(M, K // 128, 128) * s_got.unsqueeze(-1)).view(M, K) @ lin.dequant().t() + lin.bias.float()
+    _, rel = _report(f"gemm_fp8_block {M}x{N}x{K} fp32 out vs oracle", y32, want)
+    assert rel < 1e-5
+    _, rel = _report(f"gemm_fp8_block {M}x{N}x{K} bf16 out vs oracle", y, want)
+    assert rel < 4e-3
+    # the re-expressed (MXFP8) path of the same layer loses the stored scales' mantissas: the exact path must be closer
+    lin2 = Linear.from_dense(w, Format.FP8_BLOCK)
+    lin2.bias = lin.bias
+    old, ops._fp8_block_exact = ops._fp8_block_exact, False
+    try:
+        y_mx = ops.linear(lin2, x, out_dtype=torch.float32)
+    finally:
+        ops._fp8_block_exact = old
+    dense = x.float() @ lin.dequant().t() + lin.bias.float()
+    e_exact = ((y32 - dense).norm() / dense.norm()).item()
+    e_mx = ((y_mx - dense).norm() / dense.norm()).item()
+    print(f"[gemm_fp8_block] error against unquantised activations: exact path {e_exact:.4f}, MXFP8 re-expression {e_mx:.4f}")
+    assert e_exact <= e_mx * 1.05
+
+
 @pytest.mark.parametrize("fmt,M,N,K", [("nvfp4", 300, 512, 1024), ("nvfp4", 64, 384, 576 * 2), ("bf16", 100, 200, 320),
                                        ("mxfp8", 130, 256, 640)])
 def test_gemm_tile_major_weights(ops, fmt, M, N, K):
