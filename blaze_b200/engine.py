@@ -113,6 +113,8 @@ class EngineConfig:
     snapshot_rows: int = 8
     hang_secs: float = 30.0
     graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+    verify_graphs: bool = True         # chain-verify steps of equal-length chains replay captured graphs too
+    verify_graph_rows: int = 1024      # ... up to this many rows per step (bucket x rows per sequence)
     feedback_eager: bool = False       # allow token feedback on uncaptured decode steps too (CPU tests of the run-ahead loop)
 
 
@@ -342,9 +344,16 @@ class Engine:
         plain = not any(c.rope_delta or c.pos3 is not None or c.embeds for c in chunks)     # captured steps carry text rows only
         graphable = (plain and self.ecfg.use_graphs and self.device.type == "cuda" and decode_only and mode == "greedy"
                      and self.model.is_first_stage and self.model.is_last_stage and self.model.ops.is_cuda)
+        # verify steps of equal-length chains (the scheduler pads drafts to one length) replay a captured graph as well
+        L = len(chunks[0].tokens) if chunks else 0
+        verify_graph = (not graphable and not feedback and plain and L > 1 and mode in ("greedy", "greedy_hidden")
+                        and self.device.type == "cuda" and self.verify_graphable(len(chunks), L)
+                        and all(len(c.tokens) == L and c.want_logits == L and c.parents is None and not c.defer_state for c in chunks))
         try:
             if graphable:
                 out = self._forward_graph(chunks, feedback)
+            elif verify_graph:
+                out = self._forward_graph(chunks, False, L, mode)
             else:
                 batch = self._build(chunks)
                 if feedback:
@@ -382,6 +391,16 @@ class Engine:
         return batch
 
     def _run(self, batch: StepBatch, mode: str, hidden_in=None):
+        hold = getattr(self.model.ops, "hold_stream", None)
+        if hold is None:
+            return self._run_held(batch, mode, hidden_in)
+        hold()
+        try:
+            return self._run_held(batch, mode, hidden_in)
+        finally:
+            self.model.ops.release_stream()
+
+    def _run_held(self, batch: StepBatch, mode: str, hidden_in=None):
         m = self.model
         x = m.forward(batch, self.kv, hidden_in)
         if not m.is_last_stage:
@@ -409,10 +428,20 @@ class Engine:
         return (self.ecfg.use_graphs and self.device.type == "cuda" and self.model.ops.is_cuda and self.model.is_first_stage
                 and self.model.is_last_stage and ("decode", self._bucket(n_rows)) in self._graphs)
 
-    def _forward_graph(self, chunks: Sequence[SeqChunk], feedback: bool = False):
+    def verify_graphable(self, seqs: int, rows_per_seq: int) -> bool:
+        """True when a step of ``seqs`` sequences with ``rows_per_seq`` rows each (chain verify) can replay a captured graph:
+        the rows of one sequence must fit the decode attention kernel's row tiers and the model must keep no recurrent state."""
+        from .batch import SMALL_ROWS
+        return bool(self.ecfg.use_graphs and self.ecfg.verify_graphs and self.device.type == "cuda" and self.model.ops.is_cuda
+                    and self.model.is_first_stage and self.model.is_last_stage and not self.kv.gdn_layers
+                    and not self.attn_all_items and rows_per_seq >= 1
+                    and max(self.attn_group, 1) * rows_per_seq <= SMALL_ROWS
+                    and self._bucket(seqs) * rows_per_seq <= self.ecfg.verify_graph_rows)
+
+    def _forward_graph(self, chunks: Sequence[SeqChunk], feedback: bool = False, rows_per_seq: int = 1, mode: str = "greedy"):
         B = len(chunks)
         bucket = self._bucket(B)
-        key = ("decode", bucket)
+        key = ("decode", bucket) if rows_per_seq == 1 and mode == "greedy" else ("verify", bucket, rows_per_seq, mode)
         g = self._graphs.get(key)
         if g is None:
             seen = self._seen.get(key, 0)
@@ -420,8 +449,8 @@ class Engine:
             if feedback:
                 raise RuntimeError("token feedback needs a captured decode step")
             if seen == 0:   # first sight: run eagerly (also warms allocator and lazy inits)
-                return self._run(self._build(chunks), "greedy")
-            g = _Graph(self, bucket)
+                return self._run(self._build(chunks), mode)
+            g = _Graph(self, bucket, rows_per_seq, mode)
             self._graphs[key] = g
         return g.replay(chunks, feedback)
 
@@ -499,13 +528,17 @@ class Engine:
 
 
 class _Graph:
-    """A captured decode step for a fixed row bucket; inputs live in static buffers."""
+    """A captured step for a fixed sequence bucket with ``L`` rows per sequence (1 = decode, more = chain verify); inputs live
+    in static buffers."""
 
-    def __init__(self, eng: Engine, bucket: int):
-        self.eng, self.bucket = eng, bucket
+    def __init__(self, eng: Engine, bucket: int, rows_per_seq: int = 1, mode: str = "greedy"):
+        self.eng, self.bucket, self.L, self.mode = eng, bucket, rows_per_seq, mode
         dev = eng.device
-        n = bucket
-        self.total = 4 * n + n + (n + 1) + n + n
+        n, L = bucket, rows_per_seq
+        T = n * L
+        self.T = T
+        self.sizes = (T, T, T, T, n, n + 1, n, T)      # tokens, positions, slot map, sequence of row, slots, q_start, ctx_len, logit rows
+        self.total = sum(self.sizes)
         self.static = torch.zeros(self.total, dtype=torch.int32, device=dev)
         # two staging buffers: with token feedback the host may fill step k+1 while the copy of step k is still queued
         self.stages = [torch.zeros(self.total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
@@ -513,18 +546,20 @@ class _Graph:
         self.turn = 0
         o = 0
         v = []
-        for size in (n, n, n, n, n, n + 1, n, n):
+        self.offs = []
+        for size in self.sizes:
             v.append(self.static[o:o + size])
+            self.offs.append(o)
             o += size
         self.batch = StepBatch(tokens=v[0], positions=v[1], slot_mapping=v[2], seq_of_row=v[3], slots=v[4],
-                               q_start=v[5], ctx_len=v[6], logit_rows=v[7], num_rows=n, max_q_len=1)
+                               q_start=v[5], ctx_len=v[6], logit_rows=v[7], num_rows=T, max_q_len=L)
         self.batch.h_slots = [0] * n
-        self.batch.h_q_start = list(range(n + 1))
-        self.batch.h_ctx_len = [1] * n
-        self.batch.h_logit_rows = list(range(n))
+        self.batch.h_q_start = [i * L for i in range(n + 1)]
+        self.batch.h_ctx_len = [L] * n
+        self.batch.h_logit_rows = list(range(T))
         self.batch.max_ctx = eng.ecfg.max_model_len
         from .batch import TINY_ROWS
-        g = max(eng.attn_group, 1)
+        g = max(eng.attn_group, 1) * L
         if eng.attn_all_items:
             self.batch.item_seq = torch.arange(n, dtype=torch.int32, device=dev)     # one row-block item per sequence
             self.batch.item_q0 = torch.zeros(n, dtype=torch.int32, device=dev)
@@ -547,21 +582,29 @@ class _Graph:
             ev.synchronize()
         s = stage.numpy()
         bt = self.eng.kv.block_table_host
-        tok = np.fromiter((c.tokens[0] for c in chunks), np.int32, B)
-        pos = np.fromiter((c.start_pos for c in chunks), np.int32, B)
+        L, T = self.L, self.T
+        o_tok, o_pos, o_map, o_seq, o_slot, o_qs, o_ctx, o_lr = self.offs
+        start = np.fromiter((c.start_pos for c in chunks), np.int32, B)
         slot = np.fromiter((c.slot for c in chunks), np.int32, B)
+        R = B * L
         s[:] = 0
-        s[0:B] = tok
-        s[n:n + B] = pos
-        s[2 * n:3 * n] = -1
-        s[2 * n:2 * n + B] = bt[slot, pos // PAGE] * PAGE + pos % PAGE
-        s[3 * n:4 * n] = -1
-        s[3 * n:3 * n + B] = np.arange(B, dtype=np.int32)
-        s[4 * n:4 * n + B] = slot
-        qs = np.minimum(np.arange(n + 1, dtype=np.int32), B)
-        s[5 * n:6 * n + 1] = qs
-        s[6 * n + 1:6 * n + 1 + B] = pos + 1
-        s[7 * n + 1:8 * n + 1] = np.minimum(np.arange(n, dtype=np.int32), max(B - 1, 0))
+        if L == 1:
+            s[o_tok:o_tok + B] = np.fromiter((c.tokens[0] for c in chunks), np.int32, B)
+            pos = start
+            rslot = slot
+        else:
+            s[o_tok:o_tok + R] = np.asarray([c.tokens for c in chunks], np.int32).reshape(-1)
+            pos = (start[:, None] + np.arange(L, dtype=np.int32)[None, :]).reshape(-1)
+            rslot = np.repeat(slot, L)
+        s[o_pos:o_pos + R] = pos
+        s[o_map:o_map + T] = -1
+        s[o_map:o_map + R] = bt[rslot, pos // PAGE] * PAGE + pos % PAGE
+        s[o_seq:o_seq + T] = -1
+        s[o_seq:o_seq + R] = np.repeat(np.arange(B, dtype=np.int32), L) if L > 1 else np.arange(B, dtype=np.int32)
+        s[o_slot:o_slot + B] = slot
+        s[o_qs:o_qs + n + 1] = np.minimum(np.arange(n + 1, dtype=np.int32) * L, R)
+        s[o_ctx:o_ctx + B] = start + L
+        s[o_lr:o_lr + T] = np.minimum(np.arange(T, dtype=np.int32), max(R - 1, 0))
         if feedback:
             # everything but the tokens comes from the host; the tokens are the previous step's output, still on the device
             self.static[n:].copy_(stage[n:], non_blocking=True)
@@ -576,7 +619,7 @@ class _Graph:
         return B
 
     def replay(self, chunks: Sequence[SeqChunk], feedback: bool = False):
-        if feedback and self.graph is None:
+        if feedback and (self.graph is None or self.L != 1):
             raise RuntimeError("token feedback needs a captured decode step")
         B = self._fill(chunks, feedback)
         if self.graph is None:
@@ -584,7 +627,10 @@ class _Graph:
             self.graph = torch.cuda.CUDAGraph()
             l0 = self.eng.model.ops.launches
             with torch.cuda.graph(self.graph):
-                self.out = self.eng._run(self.batch, "greedy")
+                self.out = self.eng._run(self.batch, self.mode)
             self.kernels = self.eng.model.ops.launches - l0
         self.graph.replay()
-        return self.out[:B]
+        R = B * self.L
+        if self.mode == "greedy_hidden":
+            return self.out[0][:R], self.out[1][:R]
+        return self.out[:R]

@@ -39,6 +39,8 @@ class CudaOps:
         self.device = torch.device(device)
         self.lib = kernels()
         self.launches = 0
+        self._held_stream = None
+        self._held_depth = 0
         self.attn_prof = None      # optional int64 [8*3*16] wait-cycle counters of the decode attention kernel
         self._scratch: Dict[str, torch.Tensor] = {}
         self._retired: list = []
@@ -113,7 +115,20 @@ class CudaOps:
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> VP:
-        return VP(torch.cuda.current_stream(self.device).cuda_stream)
+        s = self._held_stream
+        return s if s is not None else VP(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def hold_stream(self) -> None:
+        """Look the current stream up once for the launches that follow (a step of the engine issues hundreds, and the
+        look-up costs more host time than the launch itself); ``release_stream`` ends it.  Calls nest."""
+        if self._held_depth == 0:
+            self._held_stream = VP(torch.cuda.current_stream(self.device).cuda_stream)
+        self._held_depth += 1
+
+    def release_stream(self) -> None:
+        self._held_depth = max(self._held_depth - 1, 0)
+        if self._held_depth == 0:
+            self._held_stream = None
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1

@@ -380,6 +380,7 @@ class SchedConfig:
     max_draft: int = 4
     max_verify: int = 8
     draft_tree_width: int = 1          # > 1: n-gram drafts branch into up to this many continuations, verified as a tree
+    uniform_verify: bool = True        # pad chain drafts to one length when the verify step can then replay a captured graph
     draft_tree_depth: int = 4          # deepest level of a draft tree (n-gram continuations are cut, drafter trees grown, to it)
     eos_ids: Tuple[int, ...] = ()
     max_model_len: int = 4096
@@ -450,10 +451,11 @@ class _Ahead:
 
 class _Pending:
     """A launched step whose results the host has not consumed yet."""
-    __slots__ = ("plan", "mode", "out", "t0", "seen", "host", "event")
+    __slots__ = ("plan", "mode", "out", "t0", "seen", "host", "event", "real_k")
 
     def __init__(self, plan, mode, out, t0):
         self.plan, self.mode, self.out, self.t0 = plan, mode, out, t0
+        self.real_k: Dict[int, int] = {}  # request -> length of its own draft when the drafts were padded to one length
         self.seen: List[tuple] = []      # (request, first row, first position, rows)
         self.host = None                 # pinned copy of the greedy tokens when the step is left in flight
         self.event = None
@@ -771,8 +773,10 @@ class Scheduler:
             self._last_decode = t0
         spec = cfg.spec_method != "none" and decoders
         drafts: Dict[int, List[int]] = {}
+        real_k: Dict[int, int] = {}
         if spec:
             drafts = self._draft(decoders)
+            real_k = self._pad_drafts(decoders, drafts)
         for a in decoders:
             d = drafts.get(id(a), [])
             drafted = d.token[1:] if isinstance(d, DraftTree) else d
@@ -840,6 +844,7 @@ class Scheduler:
             self._ahead = self._hand_off([a for a, _, _, _ in plan], out, t0)
             return
         pend = _Pending(plan, mode, out, t0)
+        pend.real_k = real_k
         self._advance(pend)
         # The step before this one may still be unread: its results are taken now, while the GPU works on the new step.
         prev, self._pending = self._pending, None
@@ -1022,9 +1027,12 @@ class Scheduler:
                 break
             row += want
             if draft:
-                a.acc.record(len(draft), accepted)
-                self.stats.draft_tokens += len(draft)
-                self.stats.accepted_tokens += accepted
+                # chains padded to one length for a captured verify step: only the drafter's own tokens count as drafted
+                real = pend.real_k.get(id(a), len(draft)) if pend.real_k else len(draft)
+                if real:
+                    a.acc.record(real, min(accepted, real))
+                self.stats.draft_tokens += real
+                self.stats.accepted_tokens += min(accepted, real)
                 # KV of rejected draft rows is dropped; the last emitted token's KV is computed next step
                 a.computed = a.computed - len(toks) + 1 + accepted
                 if eng.kv.gdn_layers:
@@ -1049,6 +1057,34 @@ class Scheduler:
             self.on_step(dt, rows_total)
 
     # ------------------------------------------------------------------ helpers
+    def _pad_drafts(self, decoders: List[Active], drafts: Dict[int, List[int]]) -> Dict[int, int]:
+        """Make a chain-verify step uniform so that it can replay a captured graph: when every running request decodes, all
+        sample greedily and the engine can capture ``len(decoders) x (k + 1)`` rows, every draft is padded to the longest
+        one with filler tokens (verification rejects them like any wrong draft; the rare filler that happens to be right is
+        simply accepted).  Returns the drafts' own lengths by request (empty when nothing was padded)."""
+        eng, cfg = self.engine, self.cfg
+        if not cfg.uniform_verify or not drafts or len(decoders) != len(self.active) or not hasattr(eng, "verify_graphable"):
+            return {}
+        if any(isinstance(d, DraftTree) for d in drafts.values()):
+            return {}
+        k = max(len(d) for d in drafts.values())
+        if k <= 0 or not eng.verify_graphable(len(decoders), k + 1):
+            return {}
+        limit = min(cfg.max_model_len, eng.max_pages_per_seq * PAGE)
+        for a in decoders:
+            room = a.req.params.max_tokens - len(a.generated) - 1
+            if (room < k or len(a.tokens) + k + 1 > limit or not self._plain_greedy(a) or a.req.constraint is not None or a.forced
+                    or a.req.embed_only or a.req.mm is not None):
+                return {}
+        real = {}
+        for a in decoders:
+            d = list(drafts.get(id(a), []))
+            real[id(a)] = len(d)
+            if len(d) < k:
+                d += [d[-1] if d else a.tokens[-1]] * (k - len(d))
+            drafts[id(a)] = d
+        return real
+
     def _draft(self, decoders: List[Active]) -> Dict[int, List[int]]:
         cfg = self.cfg
         maxd = []

@@ -318,11 +318,10 @@ class _A:
     pass
 
 
-def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=None):
+def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=None, D=128):
     """Write random K/V through the prep kernel, then compare attention with the oracle over the same FP8 cache."""
     from blaze_b200.batch import SeqChunk, build_batch
     from blaze_b200.config import ModelConfig, RopeConfig, inv_freq
-    D = 128
     cfg = ModelConfig(hidden_size=Hq * D, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, num_layers=1, rope=RopeConfig(theta=1e6))
     cfg.layer_types = ["full_attention"]
     g = torch.Generator(device=DEV).manual_seed(seed)
@@ -354,7 +353,7 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=Non
                 chunks.append(SeqChunk(b, [0] * qlens[b], pre, parents=parents[b] if parents else None))
         if not chunks:
             continue
-        batch = build_batch(chunks, kv.block_table_host, DEV, attn_group=Hq // Hkv)
+        batch = build_batch(chunks, kv.block_table_host, DEV, attn_group=Hq // Hkv, all_items=D != 128)
         T = batch.num_rows
         qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g, device=DEV).bfloat16()
         q, _ = ops.attn_prep_store(qkv, attn, model, batch, kv, 0, None)
@@ -391,6 +390,21 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=Non
 def test_attention(ops, Hq, Hkv, ctxs, qlens):
     o, want = _attention_case(ops, Hq, Hkv, ctxs, qlens)
     mx, rel = _report(f"attention Hq{Hq} Hkv{Hkv} ctx{ctxs} q{qlens}", o, want)
+    assert rel < 0.06
+    assert torch.isfinite(o.float()).all()
+
+
+@pytest.mark.parametrize("Hq,Hkv,ctxs,qlens", [
+    (16, 2, [513, 100, 31], [1, 1, 1]),      # decode rows through the row-block kernel (group 8)
+    (8, 2, [200, 96], [200, 96]),            # pure prefill
+    (8, 1, [700, 64, 333], [5, 64, 77]),     # verify rows + chunked prefill with history
+    (4, 4, [300], [150]),                    # MHA (group 1): more than one row block per sequence
+    (16, 2, [2000, 1500, 40], [1, 1, 1]),    # few items: the KV range is split and merged
+])
+def test_attention_head_dim_256(ops, Hq, Hkv, ctxs, qlens):
+    """head_dim 256 (two accumulator warpgroups, one 256-column output accumulator in tensor memory)."""
+    o, want = _attention_case(ops, Hq, Hkv, ctxs, qlens, D=256)
+    mx, rel = _report(f"attention D256 Hq{Hq} Hkv{Hkv} ctx{ctxs} q{qlens}", o, want)
     assert rel < 0.06
     assert torch.isfinite(o.float()).all()
 

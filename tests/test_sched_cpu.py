@@ -70,6 +70,31 @@ def test_ngram_speculation_is_exact():
     assert spec.sched.stats.draft_tokens > 0
 
 
+def test_chain_drafts_padded_to_one_length_stay_exact():
+    """When the engine says that a uniform verify step can replay a captured graph, the scheduler pads every draft of the
+    step to the longest one.  The filler rows are verified like any draft, so the streams do not change, and only the
+    drafter's own tokens are counted as drafted."""
+    rep = [3, 4, 5, 6, 7, 8] * 6
+    ps = [rep, _prompts(1, 30, seed=4)[0], rep[2:] + rep[:2]]
+    sp = SamplingParams(temperature=0.0, max_tokens=24)
+    want = [o.token_ids for o in _llm().generate(ps, sp)]
+    plain = _llm(spec_method="ngram")
+    plain.generate(ps, sp)
+    spec = _llm(spec_method="ngram")
+    asked = []
+    spec.engine.verify_graphable = lambda seqs, rows: (asked.append((seqs, rows)), True)[1]
+    shapes = []
+    fwd = spec.engine.forward
+    spec.engine.forward = lambda chunks, mode="greedy", hidden_in=None, feedback=False: (
+        shapes.append([len(c.tokens) for c in chunks]), fwd(chunks, mode, hidden_in, feedback))[1]
+    got = spec.generate(ps, sp)
+    assert [o.token_ids for o in got] == want
+    assert asked and any(len(set(sh)) == 1 and sh[0] > 1 and len(sh) == 3 for sh in shapes), "no uniform verify step was planned"
+    # the second prompt has nothing to look up: without padding its steps would have had one row
+    assert spec.sched.stats.draft_tokens <= plain.sched.stats.draft_tokens + 3 * 24
+    assert spec.sched.stats.accepted_tokens <= spec.sched.stats.draft_tokens
+
+
 def test_sampled_generation_is_seeded():
     ps = _prompts(2, 16, seed=5)
     sp = SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=7, max_tokens=8)
