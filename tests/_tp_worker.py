@@ -18,11 +18,55 @@ from blaze_b200.parallel.tp import TPGroup  # noqa: E402
 from blaze_b200.quant import Format  # noqa: E402
 
 
+def pipeline_case(dev):
+    """Two pipeline stages on two GPUs (one rank each, NCCL hand-off of hidden rows in micro-batches): the tokens must be the
+    single-process tokens; near-ties may flip where the stage split changes nothing but the launch shapes, so most must agree."""
+    from blaze_b200.config import ModelConfig, RopeConfig
+    from blaze_b200.llm import LLM
+    from blaze_b200.parallel.pp import stage_layers
+    from blaze_b200.parallel.worker import attach, follow
+    from blaze_b200.sampler import SamplingParams
+    pg = TPGroup.from_env(dev, pp=2)
+    rank = pg.global_rank
+    assert (pg.stages, pg.world) == (2, 1)
+    cfg = ModelConfig(vocab_size=2048, hidden_size=512, num_layers=4, num_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, rope=RopeConfig(theta=1e6))
+    cfg.layer_types = ["full_attention"] * 4
+    prompts = torch.randint(0, 2048, (5, 70), generator=torch.Generator().manual_seed(3)).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    base = dict(weight_format="nvfp4", device=dev, max_seqs=8, max_model_len=256, use_graphs=False, seed=2,
+                enable_prefix_caching=False, chunk=128)
+    solo = [o.token_ids for o in LLM(cfg, **base).generate(prompts, sp)] if rank == 0 else None
+    llm = LLM(cfg, stage_layers=stage_layers(cfg.num_layers, 2, pg.stage), **base)
+    llm.group = pg
+    lead = attach(llm, pg, pp_chunk=64)
+    if rank == 0:
+        got = [o.token_ids for o in llm.generate(prompts, sp)]
+        lead.quit()
+        same = sum(a == b for a, b in zip(sum(solo, []), sum(got, [])))
+        total = len(sum(solo, []))
+        print(f"[pp-gpu] tokens equal to the single-process run: {same}/{total}; {llm.pipeline.micro_batches} micro-batches in "
+              f"{llm.sched.stats.steps} steps", flush=True)
+        assert all(len(g) == 10 for g in got) and same >= 0.85 * total
+        assert llm.pipeline.micro_batches > llm.sched.stats.steps
+    else:
+        assert follow(llm) == 0
+    torch.cuda.synchronize()
+    from blaze_b200.ops import get_ops
+    assert get_ops(dev).take_status() == 0
+    dist.barrier()
+    if rank == 0:
+        print("[worker] pipeline ok", flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     case = sys.argv[1]
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = f"cuda:{local}"
+    if case == "pipeline":
+        return pipeline_case(dev)
     group = TPGroup.from_env(dev)
     rank, world = group.rank, group.world
     use_mc = os.environ.get("BLAZE_TEST_MULTICAST", "1") == "1"

@@ -52,3 +52,8 @@ def test_gemm_push_reduce_scatter(multicast):
 @pytest.mark.parametrize("fusion", ["gemm_red", "reduce_norm", "rs_push"])
 def test_tp2_model_fused_matches_tp1(fusion):
     _run("model", fusion=fusion)
+
+
+def test_two_pipeline_stages_over_nccl():
+    """Layers split over two GPUs, hidden rows handed over with isend / irecv in micro-batches, tokens returned to rank 0."""
+    _run("pipeline")
