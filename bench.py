@@ -79,6 +79,8 @@ def main():
     ap.add_argument("--schedule", default="prefill_first", choices=["interleave", "prefill_first"],
                     help="scheduler policy of the end-to-end run (LLM(schedule=...)): prompts first, or decode rows + one chunk per step")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collectives: in-kernel peer memory, or NCCL")
+    ap.add_argument("--ep", action="store_true", help="mixture-of-experts models: whole experts per rank (expert parallel) instead "
+                    "of every expert cut over the ranks")
     ap.add_argument("--spec", default=None, choices=["mtp", "eagle", "dflash"],
                     help="speculative-decoding benchmark: a one-layer drafter proposing --draft-k tokens, verify steps through the "
                          "scheduler, acceptance imposed by a seeded pattern (first j of k accepted, j uniform in 0..k), prompts "
@@ -120,7 +122,7 @@ def main():
     torch.cuda.set_device(local)
     dev = f"cuda:{local}"
     group = TPGroup.from_env(dev)
-    tp = TPInfo(rank, world, group)
+    tp = TPInfo(rank, world, group, ep=bool(args.ep and world > 1))
     cfg = named_config(args.model)
     comm = "none"
     if group is not None:
@@ -278,7 +280,7 @@ def main():
             "n_gpus": args.gpus, "steps": K, "warmup": max(W, 3), "ms_per_step": ms / K, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": f"{args.weights} weights, fp8 KV, bf16 activations",
             "data": "synthetic token ids, random-init N(0,0.02) weights", "impl": "ours",
-            "config": {"model": args.model, "global_batch": B, "seq_len": P, "parallelism": f"tp{args.gpus}", "collectives": comm,
+            "config": {"model": args.model, "global_batch": B, "seq_len": P, "parallelism": (f"tp{args.gpus} attention + ep{args.gpus} experts" if args.ep and args.gpus > 1 else f"tp{args.gpus}"), "collectives": comm,
                        "kv": "fp8 e4m3, 16-token pages", "l2": "inputs larger than L2 (KV + weights read per step >> 126 MB)",
                        "layers": cfg.num_layers, "schedule": args.schedule, "decode_tokens": "fed back on the device, copied to the host every step" if feed else "read by the host every step"},
             "clocks": clocks_summary(clk_path),

@@ -342,11 +342,11 @@ class Engine:
                     self._deferred[c.slot] = (r, c.start_pos, len(c.tokens))
                 r += len(c.tokens)
         plain = not any(c.rope_delta or c.pos3 is not None or c.embeds for c in chunks)     # captured steps carry text rows only
-        graphable = (plain and self.ecfg.use_graphs and self.device.type == "cuda" and decode_only and mode == "greedy"
-                     and self.model.is_first_stage and self.model.is_last_stage and self.model.ops.is_cuda)
+        graphable = (plain and hidden_in is None and self.ecfg.use_graphs and self.device.type == "cuda" and decode_only
+                     and mode == "greedy" and self.model.is_first_stage and self.model.is_last_stage and self.model.ops.is_cuda)
         # verify steps of equal-length chains (the scheduler pads drafts to one length) replay a captured graph as well
         L = len(chunks[0].tokens) if chunks else 0
-        verify_graph = (not graphable and not feedback and plain and L > 1 and mode in ("greedy", "greedy_hidden")
+        verify_graph = (not graphable and not feedback and plain and hidden_in is None and L > 1 and mode in ("greedy", "greedy_hidden")
                         and self.device.type == "cuda" and self.verify_graphable(len(chunks), L)
                         and all(len(c.tokens) == L and c.want_logits == L and c.parents is None and not c.defer_state for c in chunks))
         try:

@@ -55,6 +55,8 @@ class ChainDrafter:
         32k most frequent tokens), which is most of a drafter's cost for a 150k-entry vocabulary; proposals outside the
         subset are impossible, which only lowers acceptance — the target still decides every token
         (``eagle.rs:694`` ``head_merged``, ``kernels/src/cuda/eagle.cu:76`` ``candidate_logits``)."""
+        if self.target.tp.world > 1:
+            return          # the head is cut over the ranks: every rank reduces its own vocabulary shard, the pairs are merged
         ids_t = torch.as_tensor(sorted(set(int(i) for i in ids)), dtype=torch.long, device=self.target.device)
         head = self.m.lm_head
         w = head.dequant() if head.fmt != Format.DENSE else head.w
@@ -78,7 +80,10 @@ class ChainDrafter:
         """A random-init one-layer drafter shaped like the target (``mtp_num_hidden_layers = 1``)."""
         cfg = ModelConfig(**{**vars(target.cfg), "num_layers": 1, "layer_types": ["full_attention"], "num_experts": 0})
         cfg.rope = target.cfg.rope
-        lm = Model.random_init(cfg, fmt, seed, target.device, target.dtype, TPInfo(), ops=target.ops)
+        # cut over the tensor-parallel ranks like the target's layers (every rank draws the full matrices from the seed and
+        # keeps its part), so the drafter's steps run the target's collectives and its head is the target's sharded head
+        tp = target.tp if target.tp.world > 1 else TPInfo()
+        lm = Model.random_init(cfg, fmt, seed, target.device, target.dtype, tp, ops=target.ops)
         lm.embed, lm.lm_head = target.embed, target.lm_head          # shared with the target
         H = cfg.hidden_size
         g = torch.Generator(device=target.device).manual_seed(seed + 1)
@@ -97,26 +102,28 @@ class ChainDrafter:
         cfg = ModelConfig(**{**vars(target.cfg), "num_layers": 1, "layer_types": ["full_attention"]})
         cfg.rope = target.cfg.rope
         dev, dt = target.device, target.dtype
-        lm = Model(cfg, dev, dt, TPInfo(), ops=target.ops)
+        tp = target.tp if target.tp.world > 1 else TPInfo()
+        tpr, tpw = tp.rank, tp.world
+        lm = Model(cfg, dev, dt, tp, ops=target.ops)
         from .qwen3 import Attn, DenseMlp, Layer, _load_stacked_heads
         L = Layer()
         p = "mtp.layers.0."
         L.input_norm = ck.get(p + "input_layernorm.weight").to(dt).to(dev)
         L.post_norm = ck.get(p + "post_attention_layernorm.weight").to(dt).to(dev)
         A = Attn()
-        A.heads, A.kv_heads = cfg.num_heads, cfg.num_kv_heads
+        A.heads, A.kv_heads = max(cfg.num_heads // tpw, 1), max(cfg.num_kv_heads // tpw, 1)
         D = cfg.head_dim
         A.qkv = _load_stacked_heads(ck, [p + "self_attn.q_proj", p + "self_attn.k_proj", p + "self_attn.v_proj"],
                                     [D * (2 if cfg.attn_output_gate else 1), D, D], [cfg.num_heads, cfg.num_kv_heads, cfg.num_kv_heads],
-                                    0, 1, dt, dev)
-        A.o = Linear.load(ck, [p + "self_attn.o_proj"], Cut.ALL, 0, 1, dt, dev)
+                                    tpr, tpw, dt, dev)
+        A.o = Linear.load(ck, [p + "self_attn.o_proj"], Cut.COLS if tpw > 1 else Cut.ALL, tpr, tpw, dt, dev)
         if (p + "self_attn.q_norm.weight") in ck:
             A.q_norm = ck.get(p + "self_attn.q_norm.weight").to(dt).to(dev)
             A.k_norm = ck.get(p + "self_attn.k_norm.weight").to(dt).to(dev)
         L.attn = A
         mlp = DenseMlp()
-        mlp.gate_up = Linear.load(ck, [p + "mlp.gate_proj", p + "mlp.up_proj"], Cut.ALL, 0, 1, dt, dev)
-        mlp.down = Linear.load(ck, [p + "mlp.down_proj"], Cut.ALL, 0, 1, dt, dev)
+        mlp.gate_up = Linear.load(ck, [p + "mlp.gate_proj", p + "mlp.up_proj"], Cut.ROWS if tpw > 1 else Cut.ALL, tpr, tpw, dt, dev)
+        mlp.down = Linear.load(ck, [p + "mlp.down_proj"], Cut.COLS if tpw > 1 else Cut.ALL, tpr, tpw, dt, dev)
         L.mlp = mlp
         lm.layers = [L]
         lm.final_norm = ck.get("mtp.norm.weight").to(dt).to(dev)
@@ -166,6 +173,21 @@ class ChainDrafter:
         nh, _ = ops.norm(hidden.contiguous(), None, self.norm_h, eps, zc)
         return ops.linear(self.fc, torch.cat([ne, nh], dim=1).contiguous())
 
+    def _step(self, chunks, x_in: torch.Tensor):
+        """One pass of the drafter's layer over ``chunks`` → (greedy token, pre-norm hidden row) of every chunk's last row.
+        The pass goes through the drafter engine's ``forward`` so that, under tensor parallelism, the other ranks run it too."""
+        eng = self.engine
+        if self.draft_head is not None:          # reduced draft vocabulary (single rank): head GEMM over the subset only
+            batch = eng._build(chunks)
+            x = self.m.forward(batch, eng.kv, x_in)
+            return self._greedy(x, batch.logit_rows), x[batch.logit_rows.long()]
+        ends, r = [], 0
+        for c in chunks:
+            r += len(c.tokens)
+            ends.append(r - 1)
+        toks, x = eng.forward(chunks, "greedy_hidden", hidden_in=x_in)
+        return toks, x[torch.tensor(ends, dtype=torch.long, device=x.device)]
+
     def propose(self, actives, ks: Sequence[int]) -> List[List[int]]:
         """Feed the pending confirmed pairs, then draft ``ks[i]`` tokens for ``actives[i]`` greedily."""
         eng = self.engine
@@ -185,10 +207,7 @@ class ChainDrafter:
             hids.append(st.pend_hidden)
         chunks = eng.plan(items)
         x_in = self._fuse(torch.tensor(toks, dtype=torch.int32, device=dev), torch.cat(hids))
-        batch = eng._build(chunks)
-        x = self.m.forward(batch, eng.kv, x_in)
-        last = x[batch.logit_rows.long()]
-        cur_tok = self._greedy(x, batch.logit_rows)
+        cur_tok, last = self._step(chunks, x_in)
         for a, k, st in todo:
             st.fed += len(st.pend_tokens)
             st.pend_hidden, st.pend_tokens = None, None
@@ -207,10 +226,7 @@ class ChainDrafter:
             last, cur_tok = last[idx], cur_tok[idx]
             chunks = eng.plan([(st.seq, [int(t)], 1) for (a, k, st), t in zip(live, cur_tok.tolist())])
             x_in = self._fuse(cur_tok.to(torch.int32), last)
-            batch = eng._build(chunks)
-            x = self.m.forward(batch, eng.kv, x_in)
-            last = x[batch.logit_rows.long()]
-            cur_tok = self._greedy(x, batch.logit_rows)
+            cur_tok, last = self._step(chunks, x_in)
             toks_host = cur_tok.tolist()
         self.steps += 1
         self.proposed += sum(len(v) for v in out.values())

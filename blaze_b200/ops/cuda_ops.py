@@ -100,7 +100,14 @@ class CudaOps:
         lib.blz_gather_rows.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, VP]
         lib.blz_argmax.argtypes = [VP, VP, VP, _c.c_int, _c.c_int, _c.c_longlong, _c.c_int, VP]
         lib.blz_moe_route.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
-        lib.blz_moe_plan.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_moe_plan.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
+        lib.blz_moe_gemm.restype = _c.c_int
+        lib.blz_moe_gemm.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int, _c.c_int,
+                                     _c.c_int, VP, VP, VP, VP, VP, VP, _c.c_int, VP]
+        lib.blz_swiglu_live.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP, VP]
+        # routed rows per expert below this: the expert GEMMs put the features on the tensor-core lanes and only the live rows
+        # on its columns (blz_moe_gemm); above it the 128-row tiles of the grouped GEMM are full enough (BLAZE_MOE_NARROW=0: never)
+        self.MOE_NARROW_ROWS = 48 if os.environ.get("BLAZE_MOE_NARROW", "1") != "0" else 0
         lib.blz_moe_scatter.argtypes = [_c.c_int, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                         _c.c_int, VP]
         lib.blz_moe_combine.argtypes = [VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
@@ -690,9 +697,11 @@ class CudaOps:
         offsets = torch.empty(n_exp, dtype=torch.int32, device=dev)
         fill = torch.empty(n_exp, dtype=torch.int32, device=dev)
         tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+        tile_rows = torch.empty(max_tiles, dtype=torch.int32, device=dev)
         row_map = torch.empty(T, k, dtype=torch.int32, device=dev)
-        self._check(self.lib.blz_moe_plan(_ptr(counts), _ptr(offsets), _ptr(fill), _ptr(tile_expert), n_exp, max_tiles,
-                                          self._stream()), "moe_plan")
+        self._check(self.lib.blz_moe_plan(_ptr(counts), _ptr(offsets), _ptr(fill), _ptr(tile_expert), _ptr(tile_rows), n_exp,
+                                          max_tiles, self._stream()), "moe_plan")
+        narrow = T * k <= self.MOE_NARROW_ROWS * n_exp and gu["kind"] in (0, 1, 2) and gu["N"] % 128 == 0 and dn["N"] % 128 == 0
         mode = 1 if (gu["fmt"] == Format.NVFP4 and gu["act_quant"]) else (2 if gu["kind"] == 2 else 0)
         if mode:
             proxy = Linear(gu["fmt"], gu["N"], gu["K"])
@@ -708,17 +717,51 @@ class CudaOps:
                                                  _ptr(offsets), _ptr(fill), _ptr(row_map), T, H, k, first, n_exp, self._stream()),
                         "moe_scatter")
         g = torch.empty(M_pad, gu["N"], dtype=torch.bfloat16, device=dev)
-        self._grouped_gemm(gu, a, M_pad, tile_expert, n_exp, g)
         proxy_d = Linear(dn["fmt"], dn["N"], dn["K"])
         proxy_d.act_quant = dn["act_quant"]
-        act = self.silu_mul(g, quant_for=proxy_d if dn["kind"] in (1, 2) else None)
         y = torch.empty(M_pad, dn["N"], dtype=torch.bfloat16, device=dev)
-        self._grouped_gemm(dn, act, M_pad, tile_expert, n_exp, y)
+        if narrow:
+            self._moe_gemm(gu, a, max_tiles, tile_expert, tile_rows, n_exp, g)
+            act = self._silu_mul_live(g, proxy_d if dn["kind"] in (1, 2) else None, tile_rows)
+            self._moe_gemm(dn, act, max_tiles, tile_expert, tile_rows, n_exp, y)
+        else:
+            self._grouped_gemm(gu, a, M_pad, tile_expert, n_exp, g)
+            act = self.silu_mul(g, quant_for=proxy_d if dn["kind"] in (1, 2) else None)
+            self._grouped_gemm(dn, act, M_pad, tile_expert, n_exp, y)
         out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         self._check(self.lib.blz_moe_combine(_ptr(y), _ptr(topk_w.contiguous()), _ptr(row_map), _ptr(out), T, H, k, self._stream()),
                     "moe_combine")
         self._route_counts = None
         return out
+
+    def _moe_gemm(self, pk, a, row_tiles, tile_expert, tile_rows, n_exp, out):
+        """Expert GEMM over the padded row space with the features on the MMA lanes and only each tile's live rows on its columns."""
+        kind = pk["kind"]
+        if isinstance(a, QuantAct):
+            data, sfa, rs = a.data, a.sf, a.row_scale
+            lda = data.shape[1]
+        else:
+            data, sfa, rs = a, None, None
+            lda = a.shape[1] * 2
+        w = pk["w"]
+        self._check(self.lib.blz_moe_gemm(kind, _ptr(data), lda, _ptr(w), w.shape[1] * w.element_size(), _ptr(out), out.stride(0),
+                                          row_tiles, pk["N"], pk["K"], n_exp, _ptr(rs), _ptr(pk["alpha"]), _ptr(sfa), _ptr(pk["sf"]),
+                                          _ptr(tile_expert), _ptr(tile_rows), 0, self._stream()), f"moe_gemm kind {kind}")
+
+    def _silu_mul_live(self, gu, quant_for, tile_rows):
+        """``silu_mul`` over the padded row space of the routed rows: padding rows are skipped."""
+        T, I2 = gu.shape
+        I = I2 // 2
+        mode = self._qmode(quant_for)
+        if mode == 0:
+            out = torch.empty(T, I, dtype=torch.bfloat16, device=self.device)
+            self._check(self.lib.blz_swiglu_live(_ptr(gu), _ptr(out), VP(0), VP(0), VP(0), T, I, 0, 0, _ptr(tile_rows), self._stream()),
+                        "swiglu_live")
+            return out
+        qa = self._alloc_qact(Format.NVFP4 if mode == 1 else Format.MXFP8, T, I)
+        self._check(self.lib.blz_swiglu_live(_ptr(gu), VP(0), _ptr(qa.data), _ptr(qa.sf), _ptr(qa.row_scale), T, I, mode, 0,
+                                             _ptr(tile_rows), self._stream()), "swiglu_live_q")
+        return qa
 
     # ------------------------------------------------------------------ Gated DeltaNet
     def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx, state_only: bool = False):

@@ -121,6 +121,11 @@ class TPGroup:
         cand = torch.where(allp[:, :, 0] == best_val.unsqueeze(0), allp[:, :, 1], torch.full_like(allp[:, :, 1], 1e18))
         return cand.min(dim=0).values.long()
 
+    def broadcast(self, t, src: int = 0):
+        """Broadcast a tensor from tensor-parallel rank ``src`` of this stage over the data group."""
+        dist.broadcast(t, src=dist.get_global_rank(self.pg, src) if self.pg is not None else src, group=self.pg)
+        return t
+
     def broadcast_object(self, obj, src: int = 0):
         box = [obj]
         dist.broadcast_object_list(box, src=src, group=getattr(self, "ctrl", None) or self.pg)

@@ -13,10 +13,12 @@ from ..batch import SeqChunk
 
 
 class Leader:
-    """Wraps rank 0's engine so that every ``forward`` is mirrored on the followers."""
+    """Wraps rank 0's engine so that every ``forward`` is mirrored on the followers.  ``tag`` names the engine on the
+    followers' side: 0 = the served model, 1 = the drafter's one-layer model (cut over the ranks like the target, so its
+    steps run the same collectives and must be launched on every rank)."""
 
-    def __init__(self, engine, group):
-        self.engine, self.group = engine, group
+    def __init__(self, engine, group, tag: int = 0):
+        self.engine, self.group, self.tag = engine, group, tag
         self._forward = engine.forward
         self._sent = {}          # row -> page list as the followers know it
         engine.forward = self.forward
@@ -43,9 +45,14 @@ class Leader:
         gone = [r for r in self._sent if r not in live]
         for r in gone:
             del self._sent[r]
+        hid = None if hidden_in is None else (tuple(hidden_in.shape), str(hidden_in.dtype).replace("torch.", ""))
         plan = ("step", mode, [(c.slot, list(c.tokens), c.start_pos, c.want_logits, c.parents, c.defer_state) for c in chunks],
-                changed, gone, feedback)
+                changed, gone, feedback, self.tag, hid)
         self.group.broadcast_object(plan, 0)
+        if hidden_in is not None:
+            # input rows that only rank 0 has computed (the drafter's fused embedding + hidden rows) follow the plan
+            hidden_in = hidden_in.contiguous()
+            self.group.broadcast(hidden_in, 0)
         return self._forward(chunks, mode, hidden_in, feedback)
 
     def call(self, method: str, *args):
@@ -58,10 +65,15 @@ class Leader:
 
 def follow(llm) -> int:
     """Follower loop: mirror rank 0's sequence table and run the same steps."""
-    eng = llm.engine
+    import torch
+    engines = {0: llm.engine}
+    drafter = getattr(llm, "drafter", None)
+    if drafter is not None and hasattr(drafter, "engine"):
+        engines[1] = drafter.engine
     group = getattr(llm, "group", None) or llm.model.tp.group
     from ..engine import Seq
     while True:
+        eng = engines[0]
         msg = group.broadcast_object(None, 0)
         if msg[0] == "quit":
             return 0
@@ -72,7 +84,12 @@ def follow(llm) -> int:
             elif method == "commit_state":
                 eng.commit_state([(eng.seqs[row], keep) for row, keep in args[0]])
             continue
-        _, mode, raw, changed, gone, feedback = msg
+        _, mode, raw, changed, gone, feedback, tag, hid = msg
+        eng = engines[tag]
+        hidden_in = None
+        if hid is not None:
+            hidden_in = torch.empty(hid[0], dtype=getattr(torch, hid[1]), device=eng.device)
+            group.broadcast(hidden_in, 0)
         # mirror the page tables (same allocator decisions are implied by copying rank 0's)
         for row, pg in changed.items():
             s = eng.seqs.get(row)
@@ -92,7 +109,7 @@ def follow(llm) -> int:
             s = eng.seqs.get(c.slot)
             if s is not None:
                 s.length = c.start_pos + len(c.tokens)
-        eng.forward(chunks, mode, feedback=feedback)
+        eng.forward(chunks, mode, hidden_in=hidden_in, feedback=feedback)
 
 
 def attach(llm, group, pp_chunk: int = 512):
@@ -106,5 +123,8 @@ def attach(llm, group, pp_chunk: int = 512):
         llm.pipeline = Pipeline(llm.engine, group, pp_chunk)
     if group.global_rank == 0:
         llm.leader = Leader(llm.engine, group)
+        drafter = getattr(llm, "drafter", None)
+        if drafter is not None and hasattr(drafter, "engine") and group.world > 1:
+            llm.draft_leader = Leader(drafter.engine, group, tag=1)
         return llm.leader
     return None

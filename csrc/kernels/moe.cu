@@ -66,7 +66,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, float* __rest
 
 // Single block.  offsets[e] = first row of expert e in the padded row space; tile_expert[m_tile] = local expert or -1.
 __global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ fill,
-                                int* __restrict__ tile_expert, int local_n, int max_tiles) {
+                                int* __restrict__ tile_expert, int* __restrict__ tile_rows, int local_n, int max_tiles) {
   __shared__ int s_off[513];
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -93,6 +93,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict_
       ex = lo;
     }
     tile_expert[tl] = ex;
+    if (tile_rows) tile_rows[tl] = ex < 0 ? 0 : min(128, counts[ex] - (row - s_off[ex]));     // live rows of the tile
   }
 }
 
@@ -170,9 +171,9 @@ BLZ_API int blz_moe_route(const float* logits, float* topk_w, int* topk_id, int*
   return (int)cudaGetLastError();
 }
 
-BLZ_API int blz_moe_plan(const int* counts, int* offsets, int* fill, int* tile_expert, int local_n, int max_tiles,
-                         cudaStream_t s) {
-  moe_plan_kernel<<<1, 256, 0, s>>>(counts, offsets, fill, tile_expert, local_n, max_tiles);
+BLZ_API int blz_moe_plan(const int* counts, int* offsets, int* fill, int* tile_expert, int* tile_rows, int local_n,
+                         int max_tiles, cudaStream_t s) {
+  moe_plan_kernel<<<1, 256, 0, s>>>(counts, offsets, fill, tile_expert, tile_rows, local_n, max_tiles);
   return (int)cudaGetLastError();
 }
 

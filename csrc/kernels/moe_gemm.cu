@@ -1,0 +1,291 @@
+// Grouped expert GEMM for decode-sized routing (a few rows per expert), features on the tensor-core lanes:
+//     C[row, f] = (X[row, :] · W_e[f, :]) * row_scale[row] * alpha[e * N + f]      for the rows routed to expert e
+// The routed rows sit in a padded row space where every expert starts on a 128-row boundary (moe_plan / moe_scatter), so a
+// "row tile" (128 rows) belongs to one expert and holds `tile_rows[mt]` live rows, usually 8-32.  One CTA computes one
+// (row tile, 128-feature tile): the weight tile is the MMA's 128-lane operand, the live rows, rounded up to 32, are its
+// column operand (N = 32 .. 128), so a tile with 16 live rows costs 16 KB of weights + 4 KB of activations per K block
+// instead of 16 KB + 16 KB of mostly padding, and a quarter of the tensor-core time.  Expert weights are read exactly once
+// per step whatever the routing.
+//
+// Epilogue variants: plain bf16 rows, or (act = 1) SwiGLU on a weight whose rows are interleaved [16 gate | 16 up]: the
+// gate and up value of one feature sit 16 lanes apart in the same warp, one shuffle joins them and the [rows, 2I]
+// intermediate never reaches memory.
+//
+// 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue.  Two CTAs per SM (3-stage ring).  Every
+// wait is a bounded mbarrier wait; no TMA load is cluster-multicast.
+//
+// Reference counterparts: kernels/src/cuda/moe_narrow.cu (per-expert small-m kernels, :171-484) and moe_wide.cu (:125-313).
+#include "blaze/host.h"
+#include "blaze/sm100.cuh"
+
+namespace blz {
+
+struct MoeGemmParams {
+  int N, K;                  // features per expert, reduction length (elements)
+  __nv_bfloat16* C;          // [padded rows, ldc]
+  long long ldc;
+  const float* row_scale;    // [padded rows] or null
+  const float* alpha;        // [experts * N] or null
+  const uint8_t* sfw;        // weight scale factors, 128x4-tiled over [experts * N] rows
+  const uint8_t* sfx;        // activation scale factors, 128x4-tiled over the padded rows
+  int sf_col_tiles;
+  const int* tile_expert;    // [row tiles] expert of the tile, -1 = unused
+  const int* tile_rows;      // [row tiles] live rows of the tile
+  int act;                   // 1: SwiGLU epilogue, C is [rows, N / 2]
+  int* status;
+};
+
+template <int KIND> struct MgKind;
+template <> struct MgKind<0> { static constexpr int KMMA = 16, SF_ATOMS = 0; };
+template <> struct MgKind<1> { static constexpr int KMMA = 64, SF_ATOMS = 4; };
+template <> struct MgKind<2> { static constexpr int KMMA = 32, SF_ATOMS = 1; };
+
+template <int KIND>
+struct MgCfg {
+  static constexpr int KMMA = MgKind<KIND>::KMMA;
+  static constexpr int BK = KMMA * 4;                  // 128 bytes per operand row per stage
+  static constexpr int W_BYTES = 128 * 128, X_BYTES = 128 * 128;
+  static constexpr int SF_ATOMS = MgKind<KIND>::SF_ATOMS;
+  static constexpr int SF_BYTES = SF_ATOMS * 512;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;
+  static constexpr int STAGES = 3;
+  static constexpr int SF_COLS_PER_STAGE = SF_ATOMS * 4 * 2;
+  static constexpr int SF_COL0 = 128;
+  static constexpr int TMEM_COLS = 256;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256 + 128 * 4;
+  static_assert(SF_COL0 + STAGES * SF_COLS_PER_STAGE <= TMEM_COLS, "TMEM budget");
+  static_assert(2 * (SMEM + 1024) <= 228 * 1024, "two CTAs per SM");
+};
+
+__device__ __forceinline__ float mg_silu_mul(float g, float u) {
+  g = bf2f(__float2bfloat16(g));
+  u = bf2f(__float2bfloat16(u));
+  return g / (1.f + __expf(-g)) * u;
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(192, 2)
+moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, MoeGemmParams p) {
+  using Cfg = MgCfg<KIND>;
+  constexpr int BK = Cfg::BK, STAGES = Cfg::STAGES;
+  const int tiles_n = p.N / 128;
+  const int ft = blockIdx.x % tiles_n, mt = blockIdx.x / tiles_n;
+  const int ex = p.tile_expert[mt];
+  const int rows = ex < 0 ? 0 : min(p.tile_rows[mt], 128);
+  if (rows <= 0) return;                    // whole CTA, before anything is allocated
+  const int ncols = (rows + 31) & ~31;      // MMA N: 32, 64, 96 or 128
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sW = smem;
+  uint8_t* sX = sW + STAGES * Cfg::W_BYTES;
+  uint8_t* sSFW = sX + STAGES * Cfg::X_BYTES;
+  uint8_t* sSFX = sSFW + STAGES * Cfg::SF_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSFX + STAGES * Cfg::SF_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_rs = reinterpret_cast<float*>(bars) + 64;       // [128] row scales of this tile (after 256 bytes of barriers)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (p.K + BK - 1) / BK;
+  const size_t wrow0 = (size_t)ex * p.N + (size_t)ft * 128;     // first weight row of this tile
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmW);
+    prefetch_tmap(&tmX);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_trigger();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      auto issue = [&](int s, int kt, int what) {
+        int atoms = 0;
+        if constexpr (Cfg::SF_ATOMS > 0) atoms = min(Cfg::SF_ATOMS, p.sf_col_tiles - kt * Cfg::SF_ATOMS);
+        const int kc = (KIND == 0) ? kt * BK : kt * 128;
+        if (what & 1) {       // weights: do not depend on the kernel before this one
+          mbar_expect_tx(&full[s], Cfg::W_BYTES + (uint32_t)ncols * 128u + (uint32_t)atoms * 1024u);
+          tma_load_2d(sW + s * Cfg::W_BYTES, &tmW, kc, (int)wrow0, &full[s]);
+          if constexpr (Cfg::SF_ATOMS > 0)
+            bulk_load(sSFW + s * Cfg::SF_BYTES, p.sfw + ((wrow0 >> 7) * p.sf_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512,
+                      atoms * 512, &full[s]);
+        }
+        if (what & 2) {       // routed rows, 32 at a time
+          for (int c = 0; c < ncols; c += 32)
+            tma_load_2d(sX + s * Cfg::X_BYTES + c * 128, &tmX, kc, mt * 128 + c, &full[s]);
+          if constexpr (Cfg::SF_ATOMS > 0)
+            bulk_load(sSFX + s * Cfg::SF_BYTES, p.sfx + ((size_t)mt * p.sf_col_tiles + (size_t)kt * Cfg::SF_ATOMS) * 512,
+                      atoms * 512, &full[s]);
+        }
+      };
+      const int pre = min(STAGES, nkb);
+      for (int i = 0; i < pre; ++i) issue(i, i, 1);
+      pdl_wait();
+      int s = 0; uint32_t ph = 0;
+      for (int i = 0; i < nkb; ++i) {
+        if (i < pre) {
+          issue(s, i, 2);
+        } else {
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status)) break;
+          issue(s, i, 3);
+        }
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      int s = 0; uint32_t ph = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        if (!mbar_wait(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t w_addr = smem_u32(sW + s * Cfg::W_BYTES), x_addr = smem_u32(sX + s * Cfg::X_BYTES);
+        const int nblk = min(4, (p.K - i * BK + Cfg::KMMA - 1) / Cfg::KMMA);
+        const uint32_t sf_t = tmem + Cfg::SF_COL0 + s * Cfg::SF_COLS_PER_STAGE;      // weights' scales, then the rows' scales
+        if constexpr (Cfg::SF_ATOMS > 0) {
+          const int atoms = min(Cfg::SF_ATOMS, p.sf_col_tiles - i * Cfg::SF_ATOMS);
+          for (int a = 0; a < atoms; ++a) {
+            tmem_cp_sf(sf_t + a * 4, make_smem_desc(smem_u32(sSFW + s * Cfg::SF_BYTES + a * 512), 0, 128, kSwzNone));
+            tmem_cp_sf(sf_t + Cfg::SF_ATOMS * 4 + a * 4,
+                       make_smem_desc(smem_u32(sSFX + s * Cfg::SF_BYTES + a * 512), 0, 128, kSwzNone));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < nblk) {
+            const uint64_t dw = desc_sw128(w_addr + j * 32), dx = desc_sw128(x_addr + j * 32);
+            const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
+            if constexpr (KIND == 0) {
+              mma_f16(tmem, dw, dx, make_idesc(1, 1, 128, ncols), acc);
+            } else if constexpr (KIND == 1) {
+              mma_nvfp4(tmem, dw, dx, make_idesc_bs(1, 1, 0, 128, ncols), sf_t + j * 4, sf_t + Cfg::SF_ATOMS * 4 + j * 4, acc);
+            } else {
+              mma_mxf8(tmem, dw, dx, make_idesc_bs(0, 0, 1, 128, ncols, j, j), sf_t, sf_t + Cfg::SF_ATOMS * 4, acc);
+            }
+          }
+        }
+        mma_commit(&empty[s]);
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+      if (ok) mma_commit(acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: lane = feature, column = routed row
+    const int q = warp & 3;
+    const int fl = q * 32 + lane;                       // feature of this thread inside the tile
+    const float al = p.alpha ? __ldg(p.alpha + wrow0 + fl) : 1.0f;
+    pdl_wait();
+    s_rs[fl] = (p.row_scale && fl < rows) ? p.row_scale[(size_t)mt * 128 + fl] : 1.0f;
+    bar_sync(1, 128);
+    const bool got = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, p.status));
+    tc_fence_after();
+    if (got) {
+      for (int c = 0; c < ncols; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem + c + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        if (p.act) {
+          // lanes 0-15 hold the gate, lanes 16-31 the up value of 16 features: one exchange joins them
+          const int fo = (ft * 128 + q * 32) / 2 + (lane & 15);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = __uint_as_float(r[j]) * al * s_rs[c + j];
+            const float o = __shfl_xor_sync(0xffffffffu, v, 16);
+            if (lane < 16 && c + j < rows) p.C[((size_t)mt * 128 + c + j) * p.ldc + fo] = __float2bfloat16(mg_silu_mul(v, o));
+          }
+        } else {
+          const int f = ft * 128 + fl;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c + j < rows) p.C[((size_t)mt * 128 + c + j) * p.ldc + f] = __float2bfloat16(__uint_as_float(r[j]) * al * s_rs[c + j]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+template <int KIND>
+static cudaError_t launch_moe_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const MoeGemmParams& p, int row_tiles,
+                                   cudaStream_t stream) {
+  auto kern = moe_gemm_kernel<KIND>;
+  static PerDeviceOnce configured;
+  cudaError_t e = configured.smem_limit(kern, MgCfg<KIND>::SMEM);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(row_tiles * (p.N / 128)));
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = MgCfg<KIND>::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
+}
+
+}  // namespace blz
+
+// kind: 0 bf16, 1 nvfp4, 2 mxfp8.  X: routed rows [row_tiles * 128, K] in the padded row space (packed bytes for 4/8-bit
+// kinds, ldx in bytes); W: stacked expert weights [experts * N, K] (ldw in bytes); C bf16 [row_tiles * 128, ldc].
+// N % 128 == 0.  act = 1: SwiGLU on [16 gate | 16 up] interleaved weight rows, C is [rows, N / 2].
+BLZ_API int blz_moe_gemm(int kind, const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc,
+                         int row_tiles, int N, int K, int experts, const float* row_scale, const float* alpha, const void* sfx,
+                         const void* sfw, const int* tile_expert, const int* tile_rows, int act, cudaStream_t stream) {
+  using namespace blz;
+  if (row_tiles <= 0) return 0;
+  if (N <= 0 || K <= 0 || kind < 0 || kind > 2 || N % 128 || experts <= 0 || !tile_expert || !tile_rows)
+    return (int)cudaErrorInvalidValue;
+  const int kmma = kind == 0 ? 16 : kind == 1 ? 64 : 32;
+  if (K % kmma) return (int)cudaErrorInvalidValue;
+  if ((kind == 1 || kind == 2) && (!sfx || !sfw)) return (int)cudaErrorInvalidValue;
+  MoeGemmParams p;
+  p.N = N; p.K = K; p.C = reinterpret_cast<__nv_bfloat16*>(C); p.ldc = ldc;
+  p.row_scale = row_scale; p.alpha = alpha;
+  p.sfw = reinterpret_cast<const uint8_t*>(sfw); p.sfx = reinterpret_cast<const uint8_t*>(sfx);
+  p.sf_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
+  p.tile_expert = tile_expert; p.tile_rows = tile_rows; p.act = act;
+  p.status = status_word();
+  CUtensorMap tmW, tmX;
+  cudaError_t e;
+  const uint64_t w_rows = (uint64_t)experts * N, x_rows = (uint64_t)row_tiles * 128;
+  if (kind == 0) {
+    e = encode_tmap(&tmW, W, 2, K, w_rows, ldw, 64, 128, 3);
+    if (e != cudaSuccess) return (int)e;
+    e = encode_tmap(&tmX, X, 2, K, x_rows, ldx, 64, 32, 3);
+  } else {
+    const uint64_t kbytes = kind == 1 ? K / 2 : K;
+    e = encode_tmap(&tmW, W, 1, kbytes, w_rows, ldw, 128, 128, 3);
+    if (e != cudaSuccess) return (int)e;
+    e = encode_tmap(&tmX, X, 1, kbytes, x_rows, ldx, 128, 32, 3);
+  }
+  if (e != cudaSuccess) return (int)e;
+  switch (kind) {
+    case 0: return (int)launch_moe_gemm<0>(tmW, tmX, p, row_tiles, stream);
+    case 1: return (int)launch_moe_gemm<1>(tmW, tmX, p, row_tiles, stream);
+    default: return (int)launch_moe_gemm<2>(tmW, tmX, p, row_tiles, stream);
+  }
+}

@@ -47,6 +47,27 @@ def main():
             assert all(len(g) == 10 for g in got)
         else:
             assert follow(llm) == 0
+    elif case == "mtp":
+        # a one-layer chain drafter cut over the two ranks like the target: its steps are mirrored on rank 1 (with the fused
+        # input rows broadcast from rank 0), its head is the target's sharded head; the streams equal plain decoding
+        from blaze_b200.parallel.worker import attach
+        sp4 = SamplingParams(temperature=0.0, max_tokens=14)
+        solo = [o.token_ids for o in build(TPInfo()).generate(prompts, sp4)] if rank == 0 else None
+        llm = build(TPInfo(rank, world, group), chunk=16, spec_method="mtp", max_draft=4)
+        assert llm.drafter is not None and llm.drafter.m.tp.world == 2
+        lead = attach(llm, group)
+        if rank == 0:
+            assert llm.draft_leader is not None
+            got = [o.token_ids for o in llm.generate(prompts, sp4)]
+            lead.quit()
+            same = sum(a == b for a, b in zip(sum(solo, []), sum(got, [])))
+            total = len(sum(solo, []))
+            st = llm.sched.stats
+            print(f"[tp-cpu] MTP k=4 under TP 2: tokens equal to plain single-process decoding {same}/{total}; drafted "
+                  f"{st.draft_tokens}, accepted {st.accepted_tokens}", flush=True)
+            assert same >= 0.9 * total and st.draft_tokens > 0 and llm.drafter.proposed > 0
+        else:
+            assert follow(llm) == 0
     elif case == "pipeline":
         # two pipeline stages (one rank each): layers split in half, hidden rows handed over in micro-batches of 8 rows,
         # the last stage returns the tokens to rank 0; outputs must equal the single-process run exactly

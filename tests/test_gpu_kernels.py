@@ -456,6 +456,42 @@ def test_moe_routed_experts(ops, fmt, T, E, k):
     assert rel < (0.02 if fmt == Format.DENSE else 0.08)
 
 
+@pytest.mark.parametrize("fmt,T,E,k", [(Format.DENSE, 37, 8, 2), (Format.NVFP4, 200, 16, 4), (Format.MXFP8, 64, 8, 8),
+                                       (Format.NVFP4, 256, 32, 8), (Format.NVFP4, 3, 16, 4), (Format.NVFP4, 700, 4, 2)])
+def test_moe_narrow_expert_gemm(ops, fmt, T, E, k):
+    """Decode-sized routing: expert GEMMs with the features on the tensor-core lanes and only the live rows of every 128-row
+    tile as columns (32 .. 128), padding rows skipped by the activation kernel.  Same result as the padded grouped GEMM (the
+    products are the same, only the tile orientation differs) and as the oracle; experts with no row, with more than 128
+    rows (several tiles) and with row counts that are not multiples of 32 all occur."""
+    H, I = 512, 256
+    ex = _experts(E, H, I, fmt, 23)
+    g = torch.Generator(device=DEV).manual_seed(24)
+    x = torch.randn(T, H, generator=g, device=DEV).bfloat16()
+    logits = torch.randn(T, E, generator=g, device=DEV)
+    logits[:, 1] -= 30.0                                   # expert 1 is never chosen
+    keep = ops.MOE_NARROW_ROWS
+    try:
+        ops.MOE_NARROW_ROWS = 0
+        w, ids = ops.router_topk(logits, k, True, 0, E)
+        wide = ops.moe(x, w, ids, ex)
+        ops.MOE_NARROW_ROWS = 1 << 20
+        w, ids = ops.router_topk(logits, k, True, 0, E)
+        l0 = ops.launches
+        narrow = ops.moe(x, w, ids, ex)
+        used = ops.launches - l0
+    finally:
+        ops.MOE_NARROW_ROWS = keep
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    wr, idr = ref.router_topk(logits, k, True)
+    want = ref.moe_forward(x, wr, idr, ex.forward_one, E)
+    _, rel = _report(f"moe narrow {fmt.value} T{T} E{E} k{k} vs oracle ({used} launches)", narrow, want)
+    assert rel < (0.02 if fmt == Format.DENSE else 0.08)
+    _, rel = _report("moe narrow vs padded grouped GEMM", narrow, wide)
+    assert rel < 5e-3
+    assert torch.isfinite(narrow.float()).all()
+
+
 def test_moe_expert_parallel_partials_sum_to_full(ops):
     H, I, E, k, T = 512, 256, 8, 2, 50
     full = _experts(E, H, I, Format.DENSE, 31)

@@ -32,6 +32,12 @@ def test_rank_leaving_between_steps_fails_the_step_not_the_server():
     assert "peer left: request failed" in r.stdout
 
 
+def test_mtp_drafter_under_two_tensor_parallel_ranks():
+    r = _run("mtp")
+    assert r.returncode == 0
+    assert "MTP k=4 under TP 2" in r.stdout
+
+
 def test_two_pipeline_stages_match_one_process():
     r = _run("pipeline")
     assert r.returncode == 0
