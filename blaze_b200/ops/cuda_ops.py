@@ -104,6 +104,16 @@ class CudaOps:
         lib.blz_moe_gemm.restype = _c.c_int
         lib.blz_moe_gemm.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int, _c.c_int,
                                      _c.c_int, VP, VP, VP, VP, VP, VP, _c.c_int, VP]
+        lib.blz_gemm_narrow.restype = _c.c_int
+        lib.blz_gemm_narrow.argtypes = [_c.c_int, VP, _c.c_longlong, VP, _c.c_longlong, VP, _c.c_longlong, _c.c_int, _c.c_int, _c.c_int,
+                                        VP, VP, VP, VP, VP, _c.c_int, _c.c_int, VP]
+        # dense layers with few rows (single-user decoding, verify steps) and a large weight take the features-on-lanes kernel
+        # with the K range split over a cluster (blz_gemm_narrow).  Measured on B200, NVFP4, captured-graph timing, against the
+        # one-CTA-per-tile kernel: 1-32 rows 24576x4096 21 -> 16 us, 4096x12288 19 -> 16 us, 17408x5120 18 -> 16 us, 6144x4096
+        # equal, 4096x4096 11.3 -> 12.0 us (loses); at 64 rows only the 24576-wide layer still wins, at 128 rows none does: both
+        # kernels sit on a floor of about 10 us (launch, set-up, first load, reduction) at these sizes.  0 = never.
+        self.NARROW_ROWS = int(os.environ.get("BLAZE_GEMM_NARROW_ROWS", "64"))
+        self.NARROW_ALWAYS = os.environ.get("BLAZE_GEMM_NARROW_ALWAYS", "0") == "1"
         lib.blz_swiglu_live.argtypes = [VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP, VP]
         # routed rows per expert below this: the expert GEMMs put the features on the tensor-core lanes and only the live rows
         # on its columns (blz_moe_gemm); above it the 128-row tiles of the grouped GEMM are full enough (BLAZE_MOE_NARROW=0: never)
@@ -416,6 +426,15 @@ class CudaOps:
             if rc != 0:
                 raise CudaError(f"blz_gemm_wait_flags failed: {rc}")
             x.wait = None
+        big = self.NARROW_ALWAYS or (lin.N * lin.K >= 6144 * 4096 if M <= 32 else lin.N >= 16384)
+        narrow = (M <= self.NARROW_ROWS and big and kind in (0, 1, 2) and lin.N % 128 == 0 and not f32 and argmax_parts is None
+                  and pending is None and not kt and wide is None and bn == 0 and (sk is None or sk is False)
+                  and (not swiglu or ld_out % 8 == 0) and (sfa is None or sfa.numel() >= 512))
+        if narrow:
+            self._check(self.lib.blz_gemm_narrow(kind, _ptr(a), lda, _ptr(w), ldb, _ptr(out), ld_out, M, lin.N, lin.K, _ptr(rs),
+                                                 _ptr(pk["alpha"]), _ptr(pk["bias"]), _ptr(sfa), _ptr(pk["sf"]), 0, int(swiglu),
+                                                 self._stream()), f"gemm_narrow kind {kind}")
+            return out
         sk_able = not f32 and argmax_parts is None and pending is None and not kt
         if sk is None:
             sk = False
@@ -722,7 +741,7 @@ class CudaOps:
         y = torch.empty(M_pad, dn["N"], dtype=torch.bfloat16, device=dev)
         if narrow:
             self._moe_gemm(gu, a, max_tiles, tile_expert, tile_rows, n_exp, g)
-            act = self._silu_mul_live(g, proxy_d if dn["kind"] in (1, 2) else None, tile_rows)
+            act = self._silu_mul_live(g, proxy_d if dn["kind"] in (1, 2) else None, row_map)
             self._moe_gemm(dn, act, max_tiles, tile_expert, tile_rows, n_exp, y)
         else:
             self._grouped_gemm(gu, a, M_pad, tile_expert, n_exp, g)
@@ -748,19 +767,21 @@ class CudaOps:
                                           row_tiles, pk["N"], pk["K"], n_exp, _ptr(rs), _ptr(pk["alpha"]), _ptr(sfa), _ptr(pk["sf"]),
                                           _ptr(tile_expert), _ptr(tile_rows), 0, self._stream()), f"moe_gemm kind {kind}")
 
-    def _silu_mul_live(self, gu, quant_for, tile_rows):
-        """``silu_mul`` over the padded row space of the routed rows: padding rows are skipped."""
+    def _silu_mul_live(self, gu, quant_for, row_list):
+        """``silu_mul`` over the padded row space of the routed rows: only the rows named in ``row_list`` (-1 = none) are
+        touched, one CTA each."""
         T, I2 = gu.shape
         I = I2 // 2
+        n = row_list.numel()
         mode = self._qmode(quant_for)
         if mode == 0:
             out = torch.empty(T, I, dtype=torch.bfloat16, device=self.device)
-            self._check(self.lib.blz_swiglu_live(_ptr(gu), _ptr(out), VP(0), VP(0), VP(0), T, I, 0, 0, _ptr(tile_rows), self._stream()),
+            self._check(self.lib.blz_swiglu_live(_ptr(gu), _ptr(out), VP(0), VP(0), VP(0), n, I, 0, 0, _ptr(row_list), self._stream()),
                         "swiglu_live")
             return out
         qa = self._alloc_qact(Format.NVFP4 if mode == 1 else Format.MXFP8, T, I)
-        self._check(self.lib.blz_swiglu_live(_ptr(gu), VP(0), _ptr(qa.data), _ptr(qa.sf), _ptr(qa.row_scale), T, I, mode, 0,
-                                             _ptr(tile_rows), self._stream()), "swiglu_live_q")
+        self._check(self.lib.blz_swiglu_live(_ptr(gu), VP(0), _ptr(qa.data), _ptr(qa.sf), _ptr(qa.row_scale), n, I, mode, 0,
+                                             _ptr(row_list), self._stream()), "swiglu_live_q")
         return qa
 
     # ------------------------------------------------------------------ Gated DeltaNet

@@ -125,6 +125,9 @@ def attach(llm, group, pp_chunk: int = 512):
         llm.leader = Leader(llm.engine, group)
         drafter = getattr(llm, "drafter", None)
         if drafter is not None and hasattr(drafter, "engine") and group.world > 1:
+            if getattr(drafter, "kind", "mtp") != "mtp":
+                # their passes do not go through the drafter engine's forward yet, so the followers would not run them
+                raise RuntimeError(f"the {drafter.kind} drafter is not available with tensor-parallel follower ranks; use --spec-method mtp")
             llm.draft_leader = Leader(drafter.engine, group, tag=1)
         return llm.leader
     return None

@@ -154,12 +154,13 @@ __global__ void rmsnorm_kernel(__nv_bfloat16* __restrict__ x, __nv_bfloat16* __r
 template <int MODE>
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                               uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out, float* __restrict__ row_scale,
-                              int I, int src_is_act, int sf_col_tiles, const int* __restrict__ tile_rows) {
+                              int I, int src_is_act, int sf_col_tiles, const int* __restrict__ row_list) {
   extern __shared__ __align__(16) uint8_t dyn[];
   __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(dyn);
   __shared__ float red[32];
-  const int t = blockIdx.x;
-  if (tile_rows && (t & 127) >= tile_rows[t >> 7]) return;     // padding row of a 128-row tile (routed expert rows)
+  // row_list (optional): the rows to process, one per CTA, -1 = none (routed expert rows in their padded row space)
+  const int t = row_list ? row_list[blockIdx.x] : (int)blockIdx.x;
+  if (t < 0) return;
   const __nv_bfloat16* g = gu + (size_t)t * (src_is_act ? I : 2 * I);
   const __nv_bfloat16* u = g + I;
   float amax = 0.f;
@@ -358,12 +359,13 @@ template <int MODE, int CH>
 __global__ void __launch_bounds__(512) swiglu_reg_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                                            uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out,
                                                            float* __restrict__ row_scale, int I, int src_is_act, int sf_col_tiles,
-                                                           const int* __restrict__ tile_rows) {
+                                                           const int* __restrict__ row_list) {
   pdl_trigger();
   pdl_wait();
   __shared__ float red[32];
-  const int t = blockIdx.x;
-  if (tile_rows && (t & 127) >= tile_rows[t >> 7]) return;     // padding row of a 128-row tile (routed expert rows)
+  // row_list (optional): the rows to process, one per CTA, -1 = none (routed expert rows in their padded row space)
+  const int t = row_list ? row_list[blockIdx.x] : (int)blockIdx.x;
+  if (t < 0) return;
   const __nv_bfloat16* g = gu + (size_t)t * (src_is_act ? I : 2 * I);
   const __nv_bfloat16* up = g + I;
   uint4 a[CH], b[CH];
@@ -718,20 +720,20 @@ BLZ_API int blz_rmsnorm(void* x, void* residual, const void* w, void* out, void*
   return (int)cudaGetLastError();
 }
 
-// mode as `quant` above; src_is_act = 1 quantises the [T, I] input as is (no SwiGLU).  tile_rows (optional): live rows of
-// every 128-row tile; the other rows are skipped (row space of the routed expert rows).
+// mode as `quant` above; src_is_act = 1 quantises the [T, I] input as is (no SwiGLU).  blz_swiglu_live: T entries of row_list
+// name the rows to process (-1 = skip): the live rows of the routed experts' padded row space.
 static int swiglu_impl(const void* gu, void* out, void* q_out, void* sf_out, float* row_scale, int T, int I,
-                       int mode, int src_is_act, const int* tile_rows, cudaStream_t s);
+                       int mode, int src_is_act, const int* row_list, cudaStream_t s);
 BLZ_API int blz_swiglu(const void* gu, void* out, void* q_out, void* sf_out, float* row_scale, int T, int I,
                        int mode, int src_is_act, cudaStream_t s) {
   return swiglu_impl(gu, out, q_out, sf_out, row_scale, T, I, mode, src_is_act, nullptr, s);
 }
 BLZ_API int blz_swiglu_live(const void* gu, void* out, void* q_out, void* sf_out, float* row_scale, int T, int I,
-                            int mode, int src_is_act, const int* tile_rows, cudaStream_t s) {
-  return swiglu_impl(gu, out, q_out, sf_out, row_scale, T, I, mode, src_is_act, tile_rows, s);
+                            int mode, int src_is_act, const int* row_list, cudaStream_t s) {
+  return swiglu_impl(gu, out, q_out, sf_out, row_scale, T, I, mode, src_is_act, row_list, s);
 }
 static int swiglu_impl(const void* gu, void* out, void* q_out, void* sf_out, float* row_scale, int T, int I,
-                       int mode, int src_is_act, const int* tile_rows, cudaStream_t s) {
+                       int mode, int src_is_act, const int* row_list, cudaStream_t s) {
   if (I % 32 || T < 0) return (int)cudaErrorInvalidValue;
   if (T == 0) return 0;
   const int thr = norm_threads(I);
@@ -742,16 +744,16 @@ static int swiglu_impl(const void* gu, void* out, void* q_out, void* sf_out, flo
   reg_shape(I, T, &rt, &ch);
   if (ch) {
 #define BLZ_SW(C)                                                                                                              \
-  if (mode == 0) launch_pdl(swiglu_reg_kernel<0, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)out, (uint8_t*)nullptr, (uint8_t*)nullptr, (float*)nullptr, I, src_is_act, 0, tile_rows); \
-  else if (mode == 1) launch_pdl(swiglu_reg_kernel<1, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, tile_rows); \
-  else launch_pdl(swiglu_reg_kernel<2, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, tile_rows)
+  if (mode == 0) launch_pdl(swiglu_reg_kernel<0, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)out, (uint8_t*)nullptr, (uint8_t*)nullptr, (float*)nullptr, I, src_is_act, 0, row_list); \
+  else if (mode == 1) launch_pdl(swiglu_reg_kernel<1, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, row_list); \
+  else launch_pdl(swiglu_reg_kernel<2, C>, dim3(T), dim3(rt), 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, row_list)
     BLZ_CH_SWITCH(ch, BLZ_SW)
 #undef BLZ_SW
     return (int)cudaGetLastError();
   }
-  if (mode == 0) swiglu_kernel<0><<<T, thr, 0, s>>>((const bf16*)gu, (bf16*)out, nullptr, nullptr, nullptr, I, src_is_act, 0, tile_rows);
-  else if (mode == 1) swiglu_kernel<1><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, tile_rows);
-  else swiglu_kernel<2><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, tile_rows);
+  if (mode == 0) swiglu_kernel<0><<<T, thr, 0, s>>>((const bf16*)gu, (bf16*)out, nullptr, nullptr, nullptr, I, src_is_act, 0, row_list);
+  else if (mode == 1) swiglu_kernel<1><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, row_list);
+  else swiglu_kernel<2><<<T, thr, sm, s>>>((const bf16*)gu, nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, row_list);
   return (int)cudaGetLastError();
 }
 

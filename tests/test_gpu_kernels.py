@@ -196,6 +196,73 @@ def test_gemm_fp8_block_scale_exact(ops, M, N, K):
     assert e_exact <= e_mx * 1.05
 
 
+@pytest.mark.parametrize("fmt,M,N,K,ks", [
+    ("nvfp4", 1, 6144, 4096, 0), ("nvfp4", 2, 4096, 12288, 8), ("nvfp4", 32, 1024, 2048, 4), ("nvfp4", 33, 512, 1024, 2),
+    ("nvfp4", 64, 768, 4096, 0), ("nvfp4", 100, 256, 512, 2), ("nvfp4", 128, 1280, 2048, 3), ("mxfp8", 5, 1024, 2048, 0),
+    ("mxfp8", 48, 384, 1024, 8), ("bf16", 7, 1024, 1024, 0), ("bf16", 96, 256, 320, 5), ("bf16", 16, 2048, 512, 1)])
+def test_gemm_narrow_small_batch(ops, fmt, M, N, K, ks):
+    """Dense layer at small batch: features on the tensor-core lanes, rows as 32..128 MMA columns, K split over a cluster
+    and reduced through distributed shared memory.  Against the one-CTA-per-tile kernel and the oracle."""
+    import ctypes
+    g = torch.Generator(device=DEV).manual_seed(51)
+    x = (torch.randn(M, K, generator=g, device=DEV)).bfloat16()
+    w = torch.randn(N, K, generator=g, device=DEV) * 0.02
+    f = {"nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "bf16": Format.DENSE}[fmt]
+    lin = Linear.from_dense(w, f)
+    lin.bias = (torch.randn(N, generator=g, device=DEV) * 0.1).bfloat16()
+    xin = ops.quantize_rows(x, lin) if ops._qmode(lin) else x
+    pk = ops.pack(lin)
+    guard = torch.full((M + 2, N + 8), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = guard[1:M + 1, :N]
+    VP = ctypes.c_void_p
+    ptr = lambda t: VP(0) if t is None else VP(t.data_ptr())      # noqa: E731
+    if isinstance(xin, torch.Tensor):
+        a, lda, sfa, rs = xin, K * 2, None, None
+    else:
+        a, lda, sfa, rs = xin.data, xin.data.shape[1], xin.sf, xin.row_scale
+    wt = pk["w"]
+    for _ in range(2):
+        rc = ops.lib.blz_gemm_narrow(pk["kind"], ptr(a), lda, ptr(wt), wt.shape[1] * wt.element_size(), ptr(out), out.stride(0), M, N, K,
+                                     ptr(rs), ptr(pk["alpha"]), ptr(pk["bias"]), ptr(sfa), ptr(pk["sf"]), ks, 0,
+                                     VP(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+    y_tc = ops.linear(lin, xin, wide=False, sk=False)
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert (guard[0] == 7).all() and (guard[M + 1] == 7).all() and (guard[:, N:] == 7).all(), "wrote outside the output"
+    _, rel = _report(f"gemm_narrow {fmt} {M}x{N}x{K} ks{ks} vs 128-column kernel", out, y_tc.float())
+    assert rel < 2e-3
+    want = lin.ref(x, torch.float32)
+    _, rel = _report(f"gemm_narrow {fmt} vs oracle", out, want)
+    assert rel < 0.05
+    if M <= ops.NARROW_ROWS:
+        l0 = ops.launches
+        ops.NARROW_ALWAYS = True
+        try:
+            y = ops.linear(lin, xin)                    # the router's own call of the kernel (K slices chosen by the launcher)
+        finally:
+            ops.NARROW_ALWAYS = False
+        assert ops.launches == l0 + 1
+        assert (y.float() - out.float()).abs().max().item() <= 0.02 * out.float().abs().max().item()
+
+
+def test_gemm_narrow_swiglu_epilogue(ops):
+    g = torch.Generator(device=DEV).manual_seed(52)
+    M, I, K = 24, 768, 1024
+    x = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    lin = Linear.from_dense(torch.randn(2 * I, K, generator=g, device=DEV) * 0.03, Format.NVFP4, segments=[I, I])
+    ops.NARROW_ALWAYS = True
+    try:
+        y = ops.linear_swiglu(lin, x)
+    finally:
+        ops.NARROW_ALWAYS = False
+    want = ref.silu_mul(lin.ref(x, torch.float32).bfloat16()).float()
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    _, rel = _report("gemm_narrow SwiGLU epilogue vs oracle", y, want)
+    assert y.shape == (M, I) and rel < 0.05
+
+
 @pytest.mark.parametrize("fmt,M,N,K", [("nvfp4", 300, 512, 1024), ("nvfp4", 64, 384, 576 * 2), ("bf16", 100, 200, 320),
                                        ("mxfp8", 130, 256, 640)])
 def test_gemm_tile_major_weights(ops, fmt, M, N, K):
