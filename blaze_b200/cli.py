@@ -108,6 +108,21 @@ def build_parser() -> argparse.ArgumentParser:
     sc = sub.add_parser("score", help="per-token log-probabilities of a token sequence")
     engine_parser(sc)
     sc.add_argument("--prompt-ids", required=True)
+    ss = sub.add_parser("self-spec", help="test of the verify / commit path: greedy decode, then the same continuation through "
+                                          "verify rounds whose drafts are that decode with a wrong token every few positions")
+    engine_parser(ss)
+    ss.add_argument("--prompt", default=None)
+    ss.add_argument("--prompt-ids", default=None, help="comma-separated token ids")
+    ss.add_argument("--max-tokens", type=int, default=96)
+    ss.add_argument("--draft", type=int, default=7, help="draft tokens per round")
+    et = sub.add_parser("eagle-test", help="drafter test (needs --spec-method mtp / eagle / dflash or --draft-model): greedy decode, "
+                                           "then the same prompt through draft + verify rounds; prints accepted tokens per round, "
+                                           "the speed of both and where the outputs part")
+    engine_parser(et)
+    et.add_argument("--prompt", default=None)
+    et.add_argument("--prompt-ids", default=None, help="comma-separated token ids")
+    et.add_argument("--max-tokens", type=int, default=200)
+    et.add_argument("--draft", type=int, default=6, help="draft tokens per round")
     w = sub.add_parser("stage-worker", help="serve one pipeline stage for a remote coordinator")
     engine_parser(w)
     w.add_argument("--listen", default="127.0.0.1:7000")
@@ -226,7 +241,12 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if ns.command == "serve":
         from .server.run import serve
         return serve(ns)
-    if ns.command in ("generate", "score"):
+    if ns.command == "eagle-test":
+        ns.max_draft = ns.draft
+        if getattr(ns, "spec_method", "none") in (None, "none") and not getattr(ns, "draft_model", None):
+            print("eagle-test needs --spec-method mtp / eagle / dflash or --draft-model", file=sys.stderr)
+            return 2
+    if ns.command in ("generate", "score", "self-spec", "eagle-test"):
         llm = build_llm(ns)
         grp = getattr(llm, "group", None)
         if grp is not None and grp.global_rank != 0:
@@ -255,6 +275,11 @@ def _run_offline(ns, llm) -> int:
         out = llm.generate([ids], SamplingParams(temperature=ns.temperature, max_tokens=ns.max_tokens))[0]
         print(json.dumps({"token_ids": out.token_ids, "text": tok.decode(out.token_ids), "finish_reason": out.finish_reason}))
         return 0
+    if ns.command in ("self-spec", "eagle-test"):
+        from .text import load_tokenizer
+        tok = load_tokenizer(ns.model if ns.model and os.path.isdir(ns.model) else None, llm.model.cfg.vocab_size)
+        ids = [int(x) for x in ns.prompt_ids.split(",")] if ns.prompt_ids else tok.encode(ns.prompt or "hello")
+        return self_spec(llm, ids, ns.max_tokens, ns.draft) if ns.command == "self-spec" else eagle_test(llm, ids, ns.max_tokens)
     if ns.command == "score":
         import torch
         ids = [int(x) for x in ns.prompt_ids.split(",")]
@@ -265,3 +290,78 @@ def _run_offline(ns, llm) -> int:
         print(json.dumps({"logprobs": scores, "sum": sum(scores)}))
         return 0
     return 2
+
+
+def self_spec(llm, ids, max_tokens: int, draft: int) -> int:
+    """Greedy reference decode through the engine, then the same continuation through verify rounds whose drafts are the
+    reference with a wrong token at pseudo-random places; accepted rows are committed, rejected ones truncated.  Prints how
+    many tokens match (reference: ``Command::SelfSpec``, crates/blaze/src/main.rs:831-880)."""
+    import time
+    eng = llm.engine
+    vocab = llm.model.cfg.vocab_size
+
+    def prefill():
+        s = eng.open_from()
+        return s, int(eng.forward(eng.plan([(s, ids, 1)]), "greedy")[0])
+    s, first = prefill()
+    reference = [first]
+    t0 = time.perf_counter()
+    while len(reference) < max_tokens:
+        reference.append(int(eng.forward(eng.plan([(s, [reference[-1]], 1)]), "greedy")[0]))
+    plain = (max_tokens - 1) / max(time.perf_counter() - t0, 1e-9)
+    eng.close(s)
+    s, first = prefill()
+    out, rounds, lcg = [first], 0, 12345
+    t0 = time.perf_counter()
+    while len(out) < max_tokens:
+        pos = len(out)
+        drafts = [reference[pos + j] if pos + j < len(reference) else 0 for j in range(draft)]
+        lcg = (lcg * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        wrong = (lcg >> 33) % (draft + 3)
+        if wrong < draft:
+            drafts[wrong] = (drafts[wrong] + 1) % min(vocab, 1000)
+        rows = [out[-1]] + drafts
+        base = s.length
+        picks = eng.forward(eng.plan([(s, rows, len(rows))], defer_state=True), "greedy").tolist()
+        acc = 0
+        while acc < draft and picks[acc] == drafts[acc]:
+            acc += 1
+        out.extend(int(t) for t in picks[:acc + 1])
+        if eng.kv.gdn_layers:
+            eng.commit_state([(s, acc + 1)])
+        eng.truncate(s, base + acc + 1)
+        rounds += 1
+    dt = max(time.perf_counter() - t0, 1e-9)
+    out = out[:max_tokens]
+    same = next((i for i, (a, b) in enumerate(zip(out, reference)) if a != b), min(len(out), len(reference)))
+    eng.close(s)
+    print(f"{same}/{max_tokens} tokens match the reference; {rounds} rounds ({len(out) / max(rounds, 1):.2f} tokens per round, "
+          f"{len(out) / dt:.1f} tok/s; plain decode {plain:.1f} tok/s)")
+    return 0 if same == max_tokens else 1
+
+
+def eagle_test(llm, ids, max_tokens: int) -> int:
+    """Greedy decode without the drafter, then the same prompt through the scheduler's draft + verify rounds; prints the
+    accepted tokens per round, both speeds and the first position where the outputs part (near-ties may flip between step
+    shapes).  Reference: ``Command::EagleTest``, crates/blaze/src/main.rs:692-830."""
+    import time
+    from .sampler import SamplingParams
+    sp = SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True)
+    sched = llm.sched
+    drafter, method = sched.drafter, sched.cfg.spec_method
+    sched.drafter, sched.cfg.spec_method = None, "none"
+    t0 = time.perf_counter()
+    plain = llm.generate([ids], sp)[0].token_ids
+    t_plain = time.perf_counter() - t0
+    sched.drafter, sched.cfg.spec_method = drafter, method
+    sched.cache.clear()
+    d0, a0, s0 = sched.stats.draft_tokens, sched.stats.accepted_tokens, sched.stats.steps
+    t0 = time.perf_counter()
+    spec = llm.generate([ids], sp)[0].token_ids
+    t_spec = time.perf_counter() - t0
+    drafted, accepted, rounds = sched.stats.draft_tokens - d0, sched.stats.accepted_tokens - a0, sched.stats.steps - s0
+    same = next((i for i, (a, b) in enumerate(zip(spec, plain)) if a != b), min(len(spec), len(plain)))
+    print(json.dumps({"tokens": len(spec), "match_until": same, "rounds": rounds, "drafted": drafted, "accepted": accepted,
+                      "accepted_per_round": accepted / max(rounds, 1), "plain_tok_s": len(plain) / max(t_plain, 1e-9),
+                      "spec_tok_s": len(spec) / max(t_spec, 1e-9), "drafter": method}))
+    return 0

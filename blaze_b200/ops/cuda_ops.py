@@ -125,6 +125,12 @@ class CudaOps:
         lib.blz_gdn_conv.argtypes = [VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_gdn_recurrent.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
                                           _c.c_int, _c.c_int, VP]
+        lib.blz_gdn_recurrent_upto.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
+                                               _c.c_int, _c.c_int, _c.c_int, VP]
+        lib.blz_gdn_chunk.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
+                                      _c.c_int, _c.c_int, _c.c_int, VP]
+        # Gated DeltaNet: sequences with at least this many new tokens in a step take the chunked tensor-core kernel (0 = never)
+        self.GDN_CHUNK_MIN = int(os.environ.get("BLAZE_GDN_CHUNK_MIN", "64"))
         lib.blz_gated_rmsnorm.argtypes = [VP, VP, _c.c_longlong, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_float, _c.c_int, VP]
         lib.blz_status_take.restype = _c.c_int
         lib.blz_status_peek_async.restype = _c.c_int
@@ -799,10 +805,20 @@ class CudaOps:
                                           _ptr(gdn.conv_w), _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len),
                                           _ptr(batch.gdn_defer), B, C, gdn.conv_w.shape[1], self._stream()), "gdn_conv")
         o = None if state_only else torch.empty(T, hv, dv, dtype=torch.bfloat16, device=self.device)
-        self._check(self.lib.blz_gdn_recurrent(_ptr(conv), _ptr(a), _ptr(b), a.stride(0), _ptr(gdn.A_log), _ptr(gdn.dt_bias),
+        # long token runs (prompt chunks) go through the chunked tensor-core kernel, short ones (decode, verify, replay)
+        # through the token-by-token kernel; both walk the same batch and each takes its own sequences
+        chunked = (self.GDN_CHUNK_MIN > 0 and not state_only and dk == 128 and dv == 128 and batch.max_q_len >= self.GDN_CHUNK_MIN)
+        if chunked:
+            self._check(self.lib.blz_gdn_chunk(_ptr(conv), _ptr(a), _ptr(b), a.stride(0), _ptr(gdn.A_log), _ptr(gdn.dt_bias),
                                                _ptr(kv.rec_state[layer_idx]), _ptr(o), _ptr(batch.slots), _ptr(batch.q_start),
-                                               _ptr(batch.ctx_len), _ptr(batch.gdn_defer), B, hk, hv, dk, dv, self._stream()),
-                    "gdn_recurrent")
+                                               _ptr(batch.ctx_len), _ptr(batch.gdn_defer), B, hk, hv, dk, dv, self.GDN_CHUNK_MIN,
+                                               self._stream()), "gdn_chunk")
+        if not chunked or batch.num_rows > batch.max_q_len or B > 1:
+            self._check(self.lib.blz_gdn_recurrent_upto(_ptr(conv), _ptr(a), _ptr(b), a.stride(0), _ptr(gdn.A_log), _ptr(gdn.dt_bias),
+                                                        _ptr(kv.rec_state[layer_idx]), _ptr(o), _ptr(batch.slots), _ptr(batch.q_start),
+                                                        _ptr(batch.ctx_len), _ptr(batch.gdn_defer), B, hk, hv, dk, dv,
+                                                        self.GDN_CHUNK_MIN - 1 if chunked else 0x7fffffff, self._stream()),
+                        "gdn_recurrent")
         if state_only:
             return None
         y = torch.empty(T, hv * dv, dtype=torch.bfloat16, device=self.device)

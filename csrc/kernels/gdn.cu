@@ -53,12 +53,12 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(
     const __nv_bfloat16* __restrict__ conv, const __nv_bfloat16* __restrict__ a_in, const __nv_bfloat16* __restrict__ b_in,
     long long ld_ab, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ rec_state,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ slots, const int* __restrict__ q_start,
-    const int* __restrict__ ctx_len, const int* __restrict__ no_store, int Hk, int Hv, int DV) {
+    const int* __restrict__ ctx_len, const int* __restrict__ no_store, int Hk, int Hv, int DV, int max_rows) {
   constexpr int PER = DK / 4;
   const int b = blockIdx.x, hv = blockIdx.y, slice = blockIdx.z;
   const int tid = threadIdx.x, c = tid & 31, qt = tid >> 5;
   const int r0 = q_start[b], n = q_start[b + 1] - r0;
-  if (n <= 0) return;
+  if (n <= 0 || n > max_rows) return;          // longer runs belong to the chunked kernel
   const bool fresh = ctx_len[b] - n == 0;
   const int hk = hv / (Hv / Hk);
   const int C = 2 * Hk * DK + Hv * DV;                      // conv channels: [q | k | v]
@@ -153,14 +153,33 @@ BLZ_API int blz_gdn_conv(const void* x, long long ldx, void* y, void* conv_state
   return (int)cudaGetLastError();
 }
 
+static int gdn_recurrent_impl(const void* conv, const void* a_in, const void* b_in, long long ld_ab, const float* A_log,
+                              const float* dt_bias, float* rec_state, void* out, const int* slots, const int* q_start,
+                              const int* ctx_len, const int* no_store, int B, int Hk, int Hv, int DK, int DV, int max_rows,
+                              cudaStream_t s);
 BLZ_API int blz_gdn_recurrent(const void* conv, const void* a_in, const void* b_in, long long ld_ab, const float* A_log,
                               const float* dt_bias, float* rec_state, void* out, const int* slots, const int* q_start,
                               const int* ctx_len, const int* no_store, int B, int Hk, int Hv, int DK, int DV, cudaStream_t s) {
+  return gdn_recurrent_impl(conv, a_in, b_in, ld_ab, A_log, dt_bias, rec_state, out, slots, q_start, ctx_len, no_store, B, Hk, Hv,
+                            DK, DV, 0x7fffffff, s);
+}
+// as above, for the sequences with at most max_rows new tokens (the chunked kernel takes the others)
+BLZ_API int blz_gdn_recurrent_upto(const void* conv, const void* a_in, const void* b_in, long long ld_ab, const float* A_log,
+                                   const float* dt_bias, float* rec_state, void* out, const int* slots, const int* q_start,
+                                   const int* ctx_len, const int* no_store, int B, int Hk, int Hv, int DK, int DV, int max_rows,
+                                   cudaStream_t s) {
+  return gdn_recurrent_impl(conv, a_in, b_in, ld_ab, A_log, dt_bias, rec_state, out, slots, q_start, ctx_len, no_store, B, Hk, Hv,
+                            DK, DV, max_rows, s);
+}
+static int gdn_recurrent_impl(const void* conv, const void* a_in, const void* b_in, long long ld_ab, const float* A_log,
+                              const float* dt_bias, float* rec_state, void* out, const int* slots, const int* q_start,
+                              const int* ctx_len, const int* no_store, int B, int Hk, int Hv, int DK, int DV, int max_rows,
+                              cudaStream_t s) {
   if (B == 0) return 0;
   if (DK != 128 || DV % 32 || Hv % Hk) return (int)cudaErrorInvalidValue;
   dim3 grid(B, Hv, DV / 32);
   gdn_recurrent_kernel<128><<<grid, 128, 0, s>>>((const bf16*)conv, (const bf16*)a_in, (const bf16*)b_in, ld_ab, A_log, dt_bias,
-                                                 rec_state, (bf16*)out, slots, q_start, ctx_len, no_store, Hk, Hv, DV);
+                                                 rec_state, (bf16*)out, slots, q_start, ctx_len, no_store, Hk, Hv, DV, max_rows);
   return (int)cudaGetLastError();
 }
 

@@ -628,6 +628,67 @@ def test_gdn_layer(ops):
     assert (outs["cuda"][2] - outs["ref"][2]).abs().max().item() < 0.02
 
 
+@pytest.mark.parametrize("decay_scale", [1.0, 0.1])
+def test_gdn_chunked_kernel_matches_the_recurrence(ops, decay_scale):
+    """The chunked tensor-core form of the gated delta rule (128-token chunks, WY / UT transform, state carried in tensor
+    memory) against the token-by-token kernel on the same inputs: 4096-token and ragged prompts, then a second step that
+    starts from the state the first one left (a 300-token continuation next to a decode row), outputs and final states."""
+    from blaze_b200.batch import SeqChunk, build_batch
+    from blaze_b200.config import named_config
+    cfg = named_config("qwen3-next-80b-a3b")
+    cfg.linear_num_key_heads, cfg.linear_num_value_heads = 2, 4
+    cfg.num_layers, cfg.layer_types = 1, ["linear_attention"]
+    hk, hv, dk, dv = 2, 4, 128, 128
+    g = torch.Generator(device=DEV).manual_seed(43)
+
+    class G:
+        pass
+    gd = G()
+    gd.k_heads, gd.v_heads = hk, hv
+    C = 2 * hk * dk + hv * dv
+    gd.conv_w = (torch.randn(C, 4, generator=g, device=DEV) * 0.3).bfloat16()
+    gd.A_log = torch.log(torch.linspace(1, 4, hv, device=DEV) * decay_scale)        # strong and weak decay per token
+    gd.dt_bias = torch.randn(hv, generator=g, device=DEV) * 0.1
+    gd.norm_w = (1 + 0.1 * torch.randn(dv, generator=g, device=DEV)).bfloat16()
+
+    class M:
+        pass
+    m = M()
+    m.cfg, m.gdn_chunked = cfg, False
+    steps = ([4096, 200, 5, 129], [300, 64, 1, 128])
+    outs = {}
+    keep = ops.GDN_CHUNK_MIN
+    try:
+        for name, chunk_min in (("chunked", 64), ("recurrent", 0)):
+            ops.GDN_CHUNK_MIN = chunk_min
+            kv = KVCache(cfg, 4, 4, 8, "bf16", DEV, "logical")
+            gi = torch.Generator(device=DEV).manual_seed(44)
+            res = []
+            for step, lens in enumerate(steps):
+                chunks = [SeqChunk(b, [0] * n, sum(l[b] for l in steps[:step])) for b, n in enumerate(lens)]
+                batch = build_batch(chunks, kv.block_table_host, DEV)
+                T = batch.num_rows
+                mixed = torch.randn(T, C, generator=gi, device=DEV).bfloat16()
+                z = torch.randn(T, hv * dv, generator=gi, device=DEV).bfloat16()
+                bb = torch.randn(T, hv, generator=gi, device=DEV).bfloat16()
+                aa = torch.randn(T, hv, generator=gi, device=DEV).bfloat16()
+                l0 = ops.launches
+                res.append(ops.gdn(mixed, z, bb, aa, gd, m, batch, kv, 0).float())
+                if name == "chunked":
+                    assert ops.launches - l0 == 4          # conv, chunked rule, token-by-token rule for the short rows, gated norm
+            outs[name] = (torch.cat(res), kv.rec_state[0].clone())
+    finally:
+        ops.GDN_CHUNK_MIN = keep
+    torch.cuda.synchronize()
+    assert ops.take_status() == 0
+    assert torch.isfinite(outs["chunked"][0]).all()
+    _, rel = _report(f"gdn chunked vs recurrent, output (decay x{decay_scale})", outs["chunked"][0], outs["recurrent"][0])
+    assert rel < 0.02
+    st_c, st_r = outs["chunked"][1], outs["recurrent"][1]
+    _, rel = _report("gdn chunked vs recurrent, final state", st_c, st_r)
+    assert rel < 0.02
+
+
 def test_host_kv_tier_roundtrip_on_device():
     """Spill a set of FP8 pages to pinned host memory and restore them into other pages: bytes come back identical."""
     from blaze_b200.config import ModelConfig, RopeConfig
