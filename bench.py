@@ -255,8 +255,21 @@ def main():
         steps0 = llm.sched.stats.steps
         sync_all()
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # With several ranks the public path is the served one: rank 0 schedules (its decisions depend on wall-clock time, so
+        # they cannot be re-derived on every rank) and publishes each step, the other ranks replay the steps.
+        lead = None
+        if group is not None:
+            from blaze_b200.parallel.worker import attach, follow
+            lead = attach(llm, group)
+            sync_all()
         a0.record()
-        outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=out_tokens, ignore_eos=True))
+        if rank == 0:
+            outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=out_tokens, ignore_eos=True))
+            if lead is not None:
+                lead.quit()
+        else:
+            follow(llm)
+            outs = []
         a1.record()
         sync_all()
         ems = a0.elapsed_time(a1)
@@ -324,7 +337,20 @@ def spec_bench(args, cfg, dev, tp, group, comm, rank):
         torch.cuda.synchronize()
     clk_path = os.path.join(tempfile.gettempdir(), f"blaze_clocks_spec_{rank}.csv")
     sampler = clocks_sampler(clk_path, int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
-    r = spec.run(llm, prompts, out_tokens, args.draft_k, seed=4, sync=sync_all, shared=shared)
+    # several ranks: rank 0 schedules and drafts (its draft lengths follow measured step times), the others replay its steps
+    if group is not None:
+        from blaze_b200.parallel.worker import attach, follow
+        lead = attach(llm, group)
+        sync_all()
+        if rank == 0:
+            r = spec.run(llm, prompts, out_tokens, args.draft_k, seed=4, sync=torch.cuda.synchronize, shared=shared)
+            lead.quit()
+        else:
+            follow(llm)
+            r = {"spec_ms": 0.0, "plain_ms": 0.0}
+        sync_all()
+    else:
+        r = spec.run(llm, prompts, out_tokens, args.draft_k, seed=4, sync=sync_all, shared=shared)
     if sampler is not None:
         time.sleep(0.15)
         sampler.terminate()

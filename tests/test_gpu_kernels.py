@@ -661,7 +661,7 @@ def test_gdn_chunked_kernel_matches_the_recurrence(ops, decay_scale):
     try:
         for name, chunk_min in (("chunked", 64), ("recurrent", 0)):
             ops.GDN_CHUNK_MIN = chunk_min
-            kv = KVCache(cfg, 4, 4, 8, "bf16", DEV, "logical")
+            kv = KVCache(cfg, 4, 4, 320, "bf16", DEV, "logical")
             gi = torch.Generator(device=DEV).manual_seed(44)
             res = []
             for step, lens in enumerate(steps):
