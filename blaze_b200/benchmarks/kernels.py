@@ -164,6 +164,51 @@ def bench_norm(a):
                       "gbs": nbytes / med / 1e6, "frac_hbm_" + pk["src"]: nbytes / med / 1e6 / pk["hbm_gbs"]}))
 
 
+def bench_gdn(a):
+    """Gated DeltaNet layer core (conv + gated delta rule + gated norm) over prompts: the chunked tensor-core kernel against
+    the token-by-token kernel on the same inputs."""
+    from ..batch import SeqChunk, build_batch
+    from ..config import named_config
+    from ..kv import KVCache
+    from ..ops import get_ops
+    ops = get_ops("cuda")
+    cfg = named_config("qwen3-next-80b-a3b")
+    hk, hv, dk, dv = a.hk, a.hv, 128, 128
+    cfg.linear_num_key_heads, cfg.linear_num_value_heads = hk, hv
+    cfg.num_layers, cfg.layer_types = 1, ["linear_attention"]
+
+    class G:
+        pass
+    gd = G()
+    gd.k_heads, gd.v_heads = hk, hv
+    C = 2 * hk * dk + hv * dv
+    gd.conv_w = (torch.randn(C, 4, device="cuda") * 0.3).bfloat16()
+    gd.A_log = torch.log(torch.linspace(1, 4, hv, device="cuda") * 0.1)
+    gd.dt_bias = torch.randn(hv, device="cuda") * 0.1
+    gd.norm_w = torch.ones(dv, device="cuda").bfloat16()
+
+    class M:
+        pass
+    m = M()
+    m.cfg = cfg
+    kv = KVCache(cfg, 4, a.seqs, (a.tokens + 15) // 16 + 1, "bf16", "cuda", "logical")
+    batch = build_batch([SeqChunk(b, [0] * a.tokens, 0) for b in range(a.seqs)], kv.block_table_host, "cuda")
+    T = batch.num_rows
+    mixed = torch.randn(T, C, device="cuda").bfloat16()
+    z = torch.randn(T, hv * dv, device="cuda").bfloat16()
+    bb = torch.randn(T, hv, device="cuda").bfloat16()
+    aa = torch.randn(T, hv, device="cuda").bfloat16()
+    res = {}
+    for name, cm in (("chunked", 64), ("token_by_token", 0)):
+        ops.GDN_CHUNK_MIN = cm
+        med, best = timeit(lambda: ops.gdn(mixed, z, bb, aa, gd, m, batch, kv, 0), a.iters, flush=False)
+        res[name + "_ms"] = med
+    res["status"] = ops.take_status()
+    print(json.dumps({"kernel": "gdn layer core", "seqs": a.seqs, "tokens": a.tokens, "k_heads": hk, "v_heads": hv, **res,
+                      "speedup": res["token_by_token_ms"] / res["chunked_ms"],
+                      "us_per_token_chunked": res["chunked_ms"] * 1e3 / a.tokens}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="blaze_b200.benchmarks.kernels")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -192,8 +237,14 @@ def main(argv=None):
     p.add_argument("--rows", type=int, default=256)
     p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--iters", type=int, default=10)
+    p = sub.add_parser("gdn")
+    p.add_argument("--seqs", type=int, default=1)
+    p.add_argument("--tokens", type=int, default=4096)
+    p.add_argument("--hk", type=int, default=16)
+    p.add_argument("--hv", type=int, default=32)
+    p.add_argument("--iters", type=int, default=5)
     a = ap.parse_args(argv)
-    {"attention": bench_attention, "gemm": bench_gemm, "norm": bench_norm}[a.cmd](a)
+    {"attention": bench_attention, "gemm": bench_gemm, "norm": bench_norm, "gdn": bench_gdn}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -48,7 +48,8 @@ class SyntheticAcceptance:
         return out
 
 
-def run(llm, prompts: List[List[int]], out_tokens: int, k: int, seed: int = 4, sync=None, shared: int = 0) -> dict:
+def run(llm, prompts: List[List[int]], out_tokens: int, k: int, seed: int = 4, sync=None, shared: int = 0,
+        max_passes: int = 3) -> dict:
     """Plain pass (oracle + timing), then the speculative pass with imposed acceptance; returns timings and statistics.
 
     ``shared``: the first ``shared`` tokens are common to every prompt (a system prompt).  Before each timed pass the prefix
@@ -96,31 +97,53 @@ def run(llm, prompts: List[List[int]], out_tokens: int, k: int, seed: int = 4, s
     plain, plain_ms = timed("plain")
     cached_plain = sched.stats.cached_tokens - cached0
     sched.drafter, sched.cfg.spec_method = None, "none"          # (the warm-up of the second pass runs without the drafter too)
-    streams = {f"spec-{i}": plain[f"plain-{i}"] for i in range(len(prompts))}
-    wrapped = SyntheticAcceptance(drafter, streams, llm.model.cfg.vocab_size, seed)
     real_warm = warm
 
-    def warm():                                    # noqa: F811  the drafter goes in after the untimed warm-up request
-        real_warm()
-        sched.drafter, sched.cfg.spec_method, sched.cfg.max_draft = wrapped, method, k
-    d0, a0, s0 = sched.stats.draft_tokens, sched.stats.accepted_tokens, sched.stats.steps
-    cached1 = sched.stats.cached_tokens
-    spec, spec_ms = timed("spec")
-    exact = all(spec[f"spec-{i}"] == plain[f"plain-{i}"] for i in range(len(prompts)))
-    # share of emitted tokens before a stream's first difference from plain decoding (1.0 when exact): on a GPU the verify
-    # rows and the decode rows go through different kernels, so near-ties of random-init logits can flip
-    same = total = 0
-    for i in range(len(prompts)):
-        a, b = spec[f"spec-{i}"], plain[f"plain-{i}"]
-        n = 0
-        while n < min(len(a), len(b)) and a[n] == b[n]:
-            n += 1
-        same += n
-        total += max(len(b), 1)
+    def agreement(x: Dict[str, List[int]], xt: str, y: Dict[str, List[int]], yt: str) -> float:
+        """Share of emitted tokens before a stream's first difference from the other run's stream (1.0 when equal)."""
+        same = total = 0
+        for i in range(len(prompts)):
+            u, v = x[f"{xt}-{i}"], y[f"{yt}-{i}"]
+            n = 0
+            while n < min(len(u), len(v)) and u[n] == v[n]:
+                n += 1
+            same += n
+            total += max(len(v), 1)
+        return same / max(total, 1)
+
+    # The drafts follow a known continuation.  The first speculative pass takes the plain pass's streams.  On a GPU the
+    # verify rows and the decode rows go through different kernels and split the KV range differently, so near-ties of
+    # random-init logits flip and the speculative stream leaves the plain one early; the imposed pattern then no longer
+    # describes it.  Verify steps, however, reproduce verify steps (every step has the same shape), so the pass is repeated
+    # with the previous speculative pass's own streams as the continuation until the two agree (at most `max_passes` times).
+    # Every pass is a full, really verified run; the last one is reported.
+    oracle, otag = plain, "plain"
+    passes = 0
+    while True:
+        tag = f"spec{passes}"
+        streams = {f"{tag}-{i}": oracle[f"{otag}-{i}"] for i in range(len(prompts))}
+        wrapped = SyntheticAcceptance(drafter, streams, llm.model.cfg.vocab_size, seed)
+
+        def warm():                                    # noqa: F811  the drafter goes in after the untimed warm-up request
+            sched.drafter, sched.cfg.spec_method = None, "none"
+            real_warm()
+            sched.drafter, sched.cfg.spec_method, sched.cfg.max_draft = wrapped, method, k
+        d0, a0, s0 = sched.stats.draft_tokens, sched.stats.accepted_tokens, sched.stats.steps
+        cached1 = sched.stats.cached_tokens
+        spec, spec_ms = timed(tag)
+        passes += 1
+        agree_oracle = agreement(spec, tag, oracle, otag)
+        if agree_oracle >= 0.9 or passes >= max_passes:
+            break
+        oracle, otag = spec, tag
+    stag = tag
+    exact = all(spec[f"{stag}-{i}"] == plain[f"plain-{i}"] for i in range(len(prompts)))
+    agree_plain = agreement(spec, stag, plain, "plain")
     n_out = sum(len(v) for v in spec.values())
     drafted, accepted = sched.stats.draft_tokens - d0, sched.stats.accepted_tokens - a0
     return {"plain_ms": plain_ms, "spec_ms": spec_ms, "output_tokens": n_out, "exact": exact,
             "plain_tok_s": n_out / (plain_ms / 1e3), "spec_tok_s": n_out / (spec_ms / 1e3),
             "draft_tokens": drafted, "accepted_tokens": accepted, "acceptance": accepted / max(drafted, 1),
-            "accepted_per_step_hist": wrapped.hist[:k + 1], "steps": sched.stats.steps - s0, "agreement": same / max(total, 1),
+            "accepted_per_step_hist": wrapped.hist[:k + 1], "steps": sched.stats.steps - s0, "agreement": agree_plain,
+            "agreement_with_continuation": agree_oracle, "passes": passes,
             "cached_prompt_tokens_plain": cached_plain, "cached_prompt_tokens_spec": sched.stats.cached_tokens - cached1}

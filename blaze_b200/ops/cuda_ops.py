@@ -125,6 +125,7 @@ class CudaOps:
         lib.blz_gdn_conv.argtypes = [VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_gdn_recurrent.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
                                           _c.c_int, _c.c_int, VP]
+        lib.blz_gdn_conv_runs.argtypes = [VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_gdn_recurrent_upto.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
                                                _c.c_int, _c.c_int, _c.c_int, VP]
         lib.blz_gdn_chunk.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
@@ -801,9 +802,10 @@ class CudaOps:
         C = 2 * hk * dk + hv * dv
         B = batch.slots.numel()
         conv = torch.empty(T, C, dtype=torch.bfloat16, device=self.device)
-        self._check(self.lib.blz_gdn_conv(_ptr(mixed_qkv), mixed_qkv.stride(0), _ptr(conv), _ptr(kv.conv_state[layer_idx]),
-                                          _ptr(gdn.conv_w), _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len),
-                                          _ptr(batch.gdn_defer), B, C, gdn.conv_w.shape[1], self._stream()), "gdn_conv")
+        self._check(self.lib.blz_gdn_conv_runs(_ptr(mixed_qkv), mixed_qkv.stride(0), _ptr(conv), _ptr(kv.conv_state[layer_idx]),
+                                               _ptr(gdn.conv_w), _ptr(batch.slots), _ptr(batch.q_start), _ptr(batch.ctx_len),
+                                               _ptr(batch.gdn_defer), B, C, gdn.conv_w.shape[1], int(batch.max_q_len),
+                                               self._stream()), "gdn_conv")
         o = None if state_only else torch.empty(T, hv, dv, dtype=torch.bfloat16, device=self.device)
         # long token runs (prompt chunks) go through the chunked tensor-core kernel, short ones (decode, verify, replay)
         # through the token-by-token kernel; both walk the same batch and each takes its own sequences

@@ -17,12 +17,12 @@ template <int KW>
 __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y,
                                 __nv_bfloat16* __restrict__ conv_state, const __nv_bfloat16* __restrict__ w,
                                 const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ ctx_len,
-                                const int* __restrict__ no_store, int C) {
+                                const int* __restrict__ no_store, int C, int max_rows) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
   if (c >= C) return;
   const int r0 = q_start[b], n = q_start[b + 1] - r0;
-  if (n <= 0) return;
+  if (n <= 0 || n > max_rows) return;
   const bool fresh = ctx_len[b] - n == 0;
   __nv_bfloat16* st = conv_state + ((size_t)slots[b] * C + c) * (KW - 1);
   float h[KW];
@@ -44,6 +44,48 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, long long l
   if (no_store != nullptr && no_store[b]) return;      // speculative rows: the state advances when they are replayed
 #pragma unroll
   for (int j = 0; j < KW - 1; ++j) st[j] = __float2bfloat16(h[j]);
+}
+
+// Long token runs (prompts): the same convolution with the tokens spread over the grid.  grid (ceil(C / 128), B, segments):
+// segment z handles tokens [z * SEG, (z + 1) * SEG) of the sequence; the k-1 inputs before its first token come from the input
+// itself (or from the state for the run's first tokens); the CTA that holds the run's last token writes the new state.
+template <int KW>
+__global__ void gdn_conv_par_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y,
+                                    __nv_bfloat16* __restrict__ conv_state, const __nv_bfloat16* __restrict__ w,
+                                    const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ ctx_len,
+                                    const int* __restrict__ no_store, int C, int seg, int min_rows) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (c >= C) return;
+  const int r0 = q_start[b], n = q_start[b + 1] - r0;
+  if (n < min_rows) return;                        // short runs belong to the sequential kernel
+  const int t0 = blockIdx.z * seg, t1 = min(n, t0 + seg);
+  if (t0 >= n) return;
+  const bool fresh = ctx_len[b] - n == 0;
+  __nv_bfloat16* st = conv_state + ((size_t)slots[b] * C + c) * (KW - 1);
+  float h[KW];
+  float wt[KW];
+#pragma unroll
+  for (int j = 0; j < KW - 1; ++j) {
+    const int t = t0 - (KW - 1) + j;              // input position of history slot j (negative: before this run)
+    h[j] = t >= 0 ? bf2f(x[(size_t)(r0 + t) * ldx + c]) : (fresh ? 0.f : bf2f(st[KW - 1 + t]));
+  }
+#pragma unroll
+  for (int j = 0; j < KW; ++j) wt[j] = bf2f(w[(size_t)c * KW + j]);
+  for (int t = t0; t < t1; ++t) {
+    h[KW - 1] = bf2f(x[(size_t)(r0 + t) * ldx + c]);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < KW; ++j) acc += h[j] * wt[j];
+    const float r = bf2f(__float2bfloat16(acc));
+    y[(size_t)(r0 + t) * C + c] = __float2bfloat16(r / (1.f + __expf(-r)));
+#pragma unroll
+    for (int j = 0; j < KW - 1; ++j) h[j] = h[j + 1];
+  }
+  if (t1 == n && !(no_store != nullptr && no_store[b])) {
+#pragma unroll
+    for (int j = 0; j < KW - 1; ++j) st[j] = __float2bfloat16(h[j]);
+  }
 }
 
 // grid (B, Hv, DV / 32), 128 threads: thread = (dv column c = tid % 32, dk quarter qt = tid / 32); the state slice
@@ -137,11 +179,25 @@ typedef __nv_bfloat16 bf16;
 
 // no_store (both kernels, optional [B]): 1 = read the sequence's state but leave it as it was (speculative rows).
 // blz_gdn_recurrent: out may be null (state advance only, used when accepted rows are replayed).
-BLZ_API int blz_gdn_conv(const void* x, long long ldx, void* y, void* conv_state, const void* w, const int* slots,
-                         const int* q_start, const int* ctx_len, const int* no_store, int B, int C, int kw, cudaStream_t s) {
+// max_q: the longest token run of the batch (host knowledge).  Runs of at least 64 tokens are convolved with the tokens
+// spread over the grid (64-token segments), the others by one thread per channel walking the run.
+static int gdn_conv_impl(const void* x, long long ldx, void* y, void* conv_state, const void* w, const int* slots,
+                         const int* q_start, const int* ctx_len, const int* no_store, int B, int C, int kw, int max_q,
+                         cudaStream_t s) {
   if (B == 0) return 0;
+  constexpr int SEG = 64, LONG = 64;
+  const bool par = max_q >= LONG;
   dim3 grid((C + 127) / 128, B);
-#define BLZ_CONV(K) gdn_conv_kernel<K><<<grid, 128, 0, s>>>((const bf16*)x, ldx, (bf16*)y, (bf16*)conv_state, (const bf16*)w, slots, q_start, ctx_len, no_store, C)
+  dim3 grid_par((C + 127) / 128, B, par ? (max_q + SEG - 1) / SEG : 1);
+#define BLZ_CONV(K)                                                                                                         \
+  do {                                                                                                                      \
+    if (par)                                                                                                                \
+      gdn_conv_par_kernel<K><<<grid_par, 128, 0, s>>>((const bf16*)x, ldx, (bf16*)y, (bf16*)conv_state, (const bf16*)w, slots, \
+                                                      q_start, ctx_len, no_store, C, SEG, LONG);                            \
+    if (!par || B > 1)                                                                                                      \
+      gdn_conv_kernel<K><<<grid, 128, 0, s>>>((const bf16*)x, ldx, (bf16*)y, (bf16*)conv_state, (const bf16*)w, slots,      \
+                                              q_start, ctx_len, no_store, C, par ? LONG - 1 : 0x7fffffff);                  \
+  } while (0)
   switch (kw) {
     case 2: BLZ_CONV(2); break;
     case 3: BLZ_CONV(3); break;
@@ -151,6 +207,15 @@ BLZ_API int blz_gdn_conv(const void* x, long long ldx, void* y, void* conv_state
   }
 #undef BLZ_CONV
   return (int)cudaGetLastError();
+}
+BLZ_API int blz_gdn_conv(const void* x, long long ldx, void* y, void* conv_state, const void* w, const int* slots,
+                         const int* q_start, const int* ctx_len, const int* no_store, int B, int C, int kw, cudaStream_t s) {
+  return gdn_conv_impl(x, ldx, y, conv_state, w, slots, q_start, ctx_len, no_store, B, C, kw, 0, s);
+}
+BLZ_API int blz_gdn_conv_runs(const void* x, long long ldx, void* y, void* conv_state, const void* w, const int* slots,
+                              const int* q_start, const int* ctx_len, const int* no_store, int B, int C, int kw, int max_q,
+                              cudaStream_t s) {
+  return gdn_conv_impl(x, ldx, y, conv_state, w, slots, q_start, ctx_len, no_store, B, C, kw, max_q, s);
 }
 
 static int gdn_recurrent_impl(const void* conv, const void* a_in, const void* b_in, long long ld_ab, const float* A_log,

@@ -46,6 +46,7 @@ struct GdnChunkParams {
   int Hk, Hv;
   int min_rows;                // sequences with fewer new tokens are left to the token-by-token kernel
   int* status;
+  long long* prof;             // optional [CTAs][16]: cycles thread 0 spent in each phase, summed over the chunks (diagnostics)
 };
 
 constexpr int GC = 128;                       // chunk length = head dims
@@ -129,6 +130,18 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
   const uint32_t T_S = tmem + lane_base, T_1 = tmem + 128 + lane_base, T_2 = tmem + 256 + lane_base, T_3 = tmem + 384 + lane_base;
   uint32_t phase = 0;
   bool ok = true;
+  long long t_ph[12];
+#pragma unroll
+  for (int i = 0; i < 12; ++i) t_ph[i] = 0;
+  long long t_last = clock64();
+  // phase timer (thread 0 only matters): adds the cycles since the last mark to slot i
+  auto mark = [&](int i) {
+    if (p.prof) {
+      const long long t = clock64();
+      t_ph[i] += t - t_last;
+      t_last = t;
+    }
+  };
 
   // issue one product D[128 x 128] (+)= A[128 x 128] * B[128 x 128]^T (both K-major in shared memory)
   auto mma = [&](uint32_t d_col, const uint8_t* A, const uint8_t* B, bool accumulate) {
@@ -176,6 +189,7 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
   const float Aexp = __expf(p.A_log[hv]);
   const float dtb = p.dt_bias[hv];
 
+  mark(0);
   for (int c0 = 0; c0 < n && ok; c0 += GC) {
     const int L = min(GC, n - c0);
     const bool live = tid < L;
@@ -257,9 +271,11 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
         for (int q = 0; q < 8; ++q) *reinterpret_cast<__nv_bfloat16*>(bVT + op_off(j * 8 + q, tid)) = e[q];
       }
     }
+    mark(1);
     // ---- D1 = K K^T, D2 = Q K^T
     run([&] { mma(128, bK, bK, false); mma(256, bQ, bK, false); });
     if (!ok) break;
+    mark(2);
     // ---- A = strictly lower( beta_i D1_ij e^{G_i - G_j} ) into the fp32 scratch (over bK + bT: K rows are no longer needed)
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
@@ -273,6 +289,7 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
       }
     }
     __syncthreads();
+    mark(3);
     // ---- T = (I + A)^{-1} in place.  Diagonal 16 x 16 blocks by substitution: thread (block bb, column cc) solves one column.
     {
       const int bb = tid >> 4, cc = tid & 15, o = bb * 16;
@@ -297,6 +314,7 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
     tri_product<32, true>(Mf, tid, 32, 0, 32, 32, 0, 32, -1.f);
     tri_product<64, false>(Mf, tid, 0, 64, 64, 0, 0, 0, 1.f);
     tri_product<64, true>(Mf, tid, 64, 0, 64, 64, 0, 64, -1.f);
+    mark(4);
     // ---- row tid of T into registers (columns above the diagonal are scratch: masked), then the scratch is free again
     float trow[GC];
 #pragma unroll
@@ -314,12 +332,14 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
       }
     };
     write_T(false);
+    mark(5);
     run([&] { mma(128, bT, bVT, false); });
     if (!ok) break;
     // ---- W = (T diag(beta gamma)) K  -> T_3
     write_T(true);
     run([&] { mma(384, bT, bKT, false); });
     if (!ok) break;
+    mark(6);
     // ---- W rows -> bK; P = lower( D2 .* e^{G_i - G_j} ) rows -> bT; Q rows scaled by gamma_i; K^T columns by e^{G_C - G_j}
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
@@ -361,9 +381,11 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
         *e = __float2bfloat16(bf2f(*e) * kap);
       }
     }
+    mark(7);
     // ---- D5 = W S0 -> T_3;  O = (gamma Q) S0 -> T_2
     run([&] { mma(384, bK, bST, false); mma(256, bQ, bST, false); });
     if (!ok) break;
+    mark(8);
     // ---- D = U - D5 -> D^T (bf16) over V^T;  state in tensor memory scaled by e^{G_C}
     {
       const float dec = __expf(G_C);
@@ -384,9 +406,11 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
       }
       tmem_st_wait();
     }
+    mark(9);
     // ---- O += P D;   S^T += D^T (K scaled)   (A = D^T [dv x tokens], B = scaled K^T [dk x tokens])
     run([&] { mma(256, bT, bVT, true); mma(0, bVT, bKT, true); });
     if (!ok) break;
+    mark(10);
     // ---- outputs of the chunk; bf16 copy of the new state for the next chunk's products
     const bool last = c0 + GC >= n;
 #pragma unroll 1
@@ -417,6 +441,11 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
       }
     }
     __syncthreads();
+    mark(11);
+  }
+  if (p.prof && tid == 0) {
+#pragma unroll
+    for (int i = 0; i < 12; ++i) p.prof[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 + i] = t_ph[i];
   }
   tc_fence_before();
   __syncthreads();
@@ -427,6 +456,12 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(GdnChunkParams p) {
 }
 
 }  // namespace blz
+
+namespace { thread_local long long* g_gdn_prof = nullptr; }
+// Diagnostics: the NEXT blz_gdn_chunk call on this thread records, per CTA (index head * sequences + sequence) in prof[..][16],
+// the cycles thread 0 spent in: 0 set-up + state load, 1 gates + operand loads, 2 K K^T / Q K^T, 3 A, 4 inverse, 5 T rows,
+// 6 U and W products, 7 W / P / scaling passes, 8 W S0 and Q S0, 9 D and state decay, 10 P D and state update, 11 outputs.
+BLZ_API int blz_gdn_chunk_profile(void* prof) { g_gdn_prof = reinterpret_cast<long long*>(prof); return 0; }
 
 // Gated delta rule over every sequence of the batch that has at least `min_rows` new tokens (the others are left to
 // blz_gdn_recurrent, which takes the complementary `max_rows`).  Head dims 128 / 128.  Arguments as blz_gdn_recurrent.
@@ -443,6 +478,8 @@ BLZ_API int blz_gdn_chunk(const void* conv, const void* a_in, const void* b_in, 
   p.slots = slots; p.q_start = q_start; p.ctx_len = ctx_len; p.no_store = no_store; p.Hk = Hk; p.Hv = Hv;
   p.min_rows = min_rows < 1 ? 1 : min_rows;
   p.status = status_word();
+  p.prof = g_gdn_prof;
+  g_gdn_prof = nullptr;
   static PerDeviceOnce configured;
   cudaError_t e = configured.smem_limit(gdn_chunk_kernel, GDN_SMEM);
   if (e != cudaSuccess) return (int)e;
