@@ -349,8 +349,11 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
           if (r >= nrows) break;
           const float mt = fmaxf(fmaxf(s_wmax[sb][0][r], s_wmax[sb][1][r]), fmaxf(s_wmax[sb][2][r], s_wmax[sb][3][r]));
           const float m_new = fmaxf(m_run[r], mt);
-          const float alpha = ex2(m_run[r] - m_new);                   // ex2(-inf) = 0 on the first tile
-          const float pr = ex2(x[r] - m_new + 8.f);                    // masked keys: ex2(-inf) = 0; P scaled by 2^8
+          // A row may see no key of this tile (an earlier chain row when the new tokens straddle a tile boundary); if that
+          // is the first tile this warp set handles for the row, both maxima are -inf and their difference is not a number.
+          const bool none = m_new == -INFINITY;
+          const float alpha = none ? 1.f : ex2(m_run[r] - m_new);     // ex2(-inf) = 0 on the first tile with visible keys
+          const float pr = none ? 0.f : ex2(x[r] - m_new + 8.f);      // masked keys: ex2(-inf) = 0; P scaled by 2^8
           l_part[r] = l_part[r] * alpha + pr;
           acc[r] *= alpha;
           m_run[r] = m_new;
@@ -385,7 +388,8 @@ __global__ void __launch_bounds__(320, (DecCfg<NMAX, RMAX>::CTAS_PER_SM)) attn_d
             if (r >= nrows) break;
             const float mb = s_m[r];
             const float m = fmaxf(m_run[r], mb);
-            const float fa = ex2(m_run[r] - m), fb = ex2(mb - m);      // set 0 always has at least one tile
+            // (a set that saw no visible key of the row has maximum -inf and contributes nothing)
+            const float fa = m_run[r] == -INFINITY ? 0.f : ex2(m_run[r] - m), fb = mb == -INFINITY ? 0.f : ex2(mb - m);
             const float l = (s_l[0][0][r] + s_l[0][1][r] + s_l[0][2][r] + s_l[0][3][r]) * fa +
                             (s_l[1][0][r] + s_l[1][1][r] + s_l[1][2][r] + s_l[1][3][r]) * fb;
             const float o = acc[r] * fa + s_acc[r][t] * fb;

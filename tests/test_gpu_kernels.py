@@ -385,7 +385,7 @@ class _A:
     pass
 
 
-def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=None, D=128):
+def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=None, D=128, splits=0):
     """Write random K/V through the prep kernel, then compare attention with the oracle over the same FP8 cache."""
     from blaze_b200.batch import SeqChunk, build_batch
     from blaze_b200.config import ModelConfig, RopeConfig, inv_freq
@@ -429,7 +429,7 @@ def _attention_case(ops, Hq, Hkv, ctxs, qlens, seed=8, rotate=False, parents=Non
         qr, kr, vr, _ = ref.attn_prep(qkv, Hq, Hkv, D, attn.q_norm, attn.k_norm, 1e-6, cos, sin, rotate=rotate)
         assert (q.float() - qr.float()).abs().max().item() < 0.07
         if phase == 1:
-            o = ops.attention(q, model, batch, kv, 0, D ** -0.5)
+            o = ops.attention(q, model, batch, kv, 0, D ** -0.5, splits=splits)
             torch.cuda.synchronize()
             assert ops.take_status() == 0
             kl, vl = kv.logical_kv(0)
@@ -474,6 +474,21 @@ def test_attention_head_dim_256(ops, Hq, Hkv, ctxs, qlens):
     mx, rel = _report(f"attention D256 Hq{Hq} Hkv{Hkv} ctx{ctxs} q{qlens}", o, want)
     assert rel < 0.06
     assert torch.isfinite(o.float()).all()
+
+
+@pytest.mark.parametrize("Hq,Hkv,q,splits", [(32, 8, 5, 1), (32, 8, 5, 3), (64, 8, 5, 1), (32, 8, 4, 1), (16, 2, 8, 1), (32, 8, 2, 1)])
+def test_attention_verify_rows_without_kv_split(ops, Hq, Hkv, q, splits):
+    """Chain-verify rows (a few query rows per sequence, several 16-row blocks per KV head) with the KV range in ONE piece,
+    as a large batch runs them, and with a forced split: both must match the oracle row by row, later chain rows included."""
+    ctxs = [700, 64, 333, 1024, 129, 17, 500, 260]
+    o, want = _attention_case(ops, Hq, Hkv, ctxs, [q] * len(ctxs), splits=splits)
+    T = o.shape[0]
+    err = (o.float() - want.float()).abs().amax(dim=(1, 2)).view(len(ctxs), q)
+    print(f"[attention verify rows Hq{Hq} Hkv{Hkv} q{q} splits{splits}] max error by chain row: {err.amax(0).tolist()}")
+    mx, rel = _report("attention verify rows", o, want)
+    assert rel < 0.06
+    ref_mag = want.float().abs().amax().item()
+    assert err.max().item() < 0.25 * ref_mag, "a chain row is off by more than rounding"
 
 
 def test_attention_rotated_keys(ops):
