@@ -476,11 +476,13 @@ def test_attention_head_dim_256(ops, Hq, Hkv, ctxs, qlens):
     assert torch.isfinite(o.float()).all()
 
 
-@pytest.mark.parametrize("Hq,Hkv,q,splits", [(32, 8, 5, 1), (32, 8, 5, 3), (64, 8, 5, 1), (32, 8, 4, 1), (16, 2, 8, 1), (32, 8, 2, 1)])
+@pytest.mark.parametrize("Hq,Hkv,q,splits", [(32, 8, 5, 1), (32, 8, 5, 3), (64, 8, 5, 1), (32, 8, 4, 1), (16, 2, 8, 1), (32, 8, 2, 1),
+                                             (32, 8, 1, 1), (32, 8, 1, 2), (32, 8, 1, 3), (32, 8, 1, 5), (32, 8, 1, 8),
+                                             (64, 8, 1, 3), (32, 8, 4, 3), (32, 8, 2, 3)])
 def test_attention_verify_rows_without_kv_split(ops, Hq, Hkv, q, splits):
     """Chain-verify rows (a few query rows per sequence, several 16-row blocks per KV head) with the KV range in ONE piece,
     as a large batch runs them, and with a forced split: both must match the oracle row by row, later chain rows included."""
-    ctxs = [700, 64, 333, 1024, 129, 17, 500, 260]
+    ctxs = [700, 64, 333, 1024, 129, 17, 500, 260, 1030, 1089, 1153, 385]
     o, want = _attention_case(ops, Hq, Hkv, ctxs, [q] * len(ctxs), splits=splits)
     T = o.shape[0]
     err = (o.float() - want.float()).abs().amax(dim=(1, 2)).view(len(ctxs), q)
