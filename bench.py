@@ -130,7 +130,8 @@ def main():
         if args.comm == "fused":
             try:
                 from blaze_b200.parallel.symm import SymmAllReduce
-                group.fused = SymmAllReduce.create(group, dev, max_rows=args.batch + 4096 + 64, hidden=cfg.hidden_size)
+                spec_rows = args.batch * (args.draft_k + 1) if args.spec else 0
+                group.fused = SymmAllReduce.create(group, dev, max_rows=max(args.batch, spec_rows) + 4096 + 64, hidden=cfg.hidden_size)
                 comm = "fused peer-memory kernels (" + ("multimem" if group.fused.use_mc else "p2p") + ")"
             except Exception as e:  # the NCCL path stays available
                 if rank == 0:

@@ -188,6 +188,60 @@ class ChainDrafter:
         toks, x = eng.forward(chunks, "greedy_hidden", hidden_in=x_in)
         return toks, x[torch.tensor(ends, dtype=torch.long, device=x.device)]
 
+    MAX_FEED_ROWS = 4096          # rows per catch-up pass (a step's rows must fit the tensor-parallel exchange buffers)
+
+    def _feed(self, states, dev):
+        """Run the pending confirmed (token, hidden) pairs of ``states`` through the drafter's layer, at most MAX_FEED_ROWS rows
+        per pass (a request's rows may be cut over passes) → (first draft token, pre-norm hidden of the last row) per state."""
+        eng = self.engine
+        if self.draft_head is not None or sum(len(st.pend_tokens) for st in states) <= self.MAX_FEED_ROWS:
+            items, toks, hids = [], [], []
+            for st in states:
+                items.append((st.seq, st.pend_tokens, 1))
+                toks += st.pend_tokens
+                hids.append(st.pend_hidden)
+            x_in = self._fuse(torch.tensor(toks, dtype=torch.int32, device=dev), torch.cat(hids))
+            return self._step(eng.plan(items), x_in)
+        out_tok: List[Optional[torch.Tensor]] = [None] * len(states)
+        out_hid: List[Optional[torch.Tensor]] = [None] * len(states)
+        batch, rows = [], 0                       # (state index, first row, last row, is the request's last piece)
+
+        def flush():
+            nonlocal batch, rows
+            if not batch:
+                return
+            items, toks, hids, finals, ends, r = [], [], [], [], [], 0
+            for i, a, b, fin in batch:
+                st = states[i]
+                items.append((st.seq, st.pend_tokens[a:b], 1 if fin else 0))
+                toks += st.pend_tokens[a:b]
+                hids.append(st.pend_hidden[a:b])
+                r += b - a
+                if fin:
+                    finals.append(i)
+                    ends.append(r - 1)
+            x_in = self._fuse(torch.tensor(toks, dtype=torch.int32, device=dev), torch.cat(hids))
+            chunks = eng.plan(items)
+            if finals:
+                tk, x = eng.forward(chunks, "greedy_hidden", hidden_in=x_in)
+                for j, i in enumerate(finals):
+                    out_tok[i] = tk[j:j + 1]
+                    out_hid[i] = x[ends[j]:ends[j] + 1]
+            else:
+                eng.forward(chunks, "none", hidden_in=x_in)
+            batch, rows = [], 0
+        for i, st in enumerate(states):
+            n, a = len(st.pend_tokens), 0
+            while a < n:
+                b = min(n, a + self.MAX_FEED_ROWS - rows)
+                batch.append((i, a, b, b == n))
+                rows += b - a
+                a = b
+                if rows >= self.MAX_FEED_ROWS:
+                    flush()
+        flush()
+        return torch.cat(out_tok), torch.cat(out_hid)
+
     def propose(self, actives, ks: Sequence[int]) -> List[List[int]]:
         """Feed the pending confirmed pairs, then draft ``ks[i]`` tokens for ``actives[i]`` greedily."""
         eng = self.engine
@@ -200,14 +254,7 @@ class ChainDrafter:
         for a, k, st in todo:
             eng.truncate(st.seq, st.fed)
         dev = self.target.device
-        items, toks, hids = [], [], []
-        for a, k, st in todo:
-            items.append((st.seq, st.pend_tokens, 1))
-            toks += st.pend_tokens
-            hids.append(st.pend_hidden)
-        chunks = eng.plan(items)
-        x_in = self._fuse(torch.tensor(toks, dtype=torch.int32, device=dev), torch.cat(hids))
-        cur_tok, last = self._step(chunks, x_in)
+        cur_tok, last = self._feed([st for _, _, st in todo], dev)
         for a, k, st in todo:
             st.fed += len(st.pend_tokens)
             st.pend_hidden, st.pend_tokens = None, None

@@ -150,6 +150,29 @@ def test_mtp_drafter_keeps_outputs_exact():
     assert not d.states and d.engine.pages.free_count == d.engine.num_pages - 1
 
 
+def test_mtp_drafter_catch_up_feed_in_pieces():
+    """The drafter's first pass over a prompt's confirmed (token, hidden) pairs is cut into passes of bounded rows (a step
+    must fit the tensor-parallel exchange buffers); the pieces, including requests cut in the middle, give the same drafts."""
+    from blaze_b200.models.drafter import ChainDrafter
+    ps = _prompts(3, 37, seed=9)
+    sp = SamplingParams(temperature=0.0, max_tokens=10)
+    outs = []
+    for limit in (4096, 4):
+        llm = _llm(spec_method="mtp")
+        d = ChainDrafter.random_init(llm.model, seed=3, max_seqs=8, max_model_len=256, kv_dtype="fp32")
+        d.MAX_FEED_ROWS = limit
+        llm.sched.drafter = d
+        fed = []
+        fwd = d.engine.forward
+        d.engine.forward = lambda chunks, mode="greedy", hidden_in=None, feedback=False: (
+            fed.append(sum(len(c.tokens) for c in chunks)), fwd(chunks, mode, hidden_in, feedback))[1]
+        toks = [o.token_ids for o in llm.generate(ps, sp)]
+        outs.append((toks, llm.sched.stats.draft_tokens, llm.sched.stats.accepted_tokens, max(fed)))
+    assert outs[0][0] == outs[1][0]
+    assert outs[0][1:3] == outs[1][1:3]                      # same drafts, same acceptance
+    assert outs[0][3] > 4 >= outs[1][3]
+
+
 def _ahead_llm(**kw):
     llm = _llm(**kw)
     llm.engine.ecfg.feedback_eager = True        # token feedback without captured graphs, so the loop runs on CPU
