@@ -164,6 +164,43 @@ def bench_norm(a):
                       "gbs": nbytes / med / 1e6, "frac_hbm_" + pk["src"]: nbytes / med / 1e6 / pk["hbm_gbs"]}))
 
 
+def bench_moe(a):
+    """Routed experts of one layer (scatter, two expert GEMMs, activation, combine) at decode-sized routing."""
+    from ..linear import Linear
+    from ..models.qwen3 import Experts
+    from ..ops import get_ops
+    from ..quant import Format
+    ops = get_ops("cuda")
+    fmt = {"nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8, "bf16": Format.DENSE}[a.kind]
+    ex = Experts()
+    ex.num_experts, ex.first, ex.count = a.experts, 0, a.experts
+    for _ in range(a.experts):
+        ex.gate_up.append(Linear.from_dense(torch.randn(2 * a.inter, a.hidden, device="cuda") * 0.05, fmt, segments=[a.inter, a.inter]))
+        ex.down.append(Linear.from_dense(torch.randn(a.hidden, a.inter, device="cuda") * 0.05, fmt))
+    x = torch.randn(a.tokens, a.hidden, device="cuda").bfloat16()
+    logits = torch.randn(a.tokens, a.experts, device="cuda")
+    wbytes = sum(l.nbytes() for l in ex.gate_up) + sum(l.nbytes() for l in ex.down)
+
+    def run():
+        w, ids = ops.router_topk(logits, a.topk, True, 0, a.experts)
+        return ops.moe(x, w, ids, ex)
+    res = {}
+    for name, rows in (("narrow", 48), ("padded_128_row_tiles", 0)):
+        ops.MOE_NARROW_ROWS = rows
+        run()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        med, best = timeit(g.replay, a.iters, flush=True)
+        res[name + "_us"] = med * 1e3
+    pk = peaks()
+    print(json.dumps({"kernel": f"moe layer {a.kind}", "tokens": a.tokens, "experts": a.experts, "topk": a.topk, "hidden": a.hidden,
+                      "inter": a.inter, **res, "expert_weight_mb": wbytes / 1e6,
+                      "weight_gbs_narrow": wbytes / res["narrow_us"] / 1e3,
+                      "x_hbm_" + pk["src"]: wbytes / res["narrow_us"] / 1e3 / pk["hbm_gbs"], "status": ops.take_status()}))
+
+
 def bench_gdn(a):
     """Gated DeltaNet layer core (conv + gated delta rule + gated norm) over prompts: the chunked tensor-core kernel against
     the token-by-token kernel on the same inputs."""
@@ -237,6 +274,14 @@ def main(argv=None):
     p.add_argument("--rows", type=int, default=256)
     p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--iters", type=int, default=10)
+    p = sub.add_parser("moe")
+    p.add_argument("--kind", default="nvfp4")
+    p.add_argument("--tokens", type=int, default=256)
+    p.add_argument("--experts", type=int, default=128)
+    p.add_argument("--topk", type=int, default=8)
+    p.add_argument("--hidden", type=int, default=2048)
+    p.add_argument("--inter", type=int, default=768)
+    p.add_argument("--iters", type=int, default=5)
     p = sub.add_parser("gdn")
     p.add_argument("--seqs", type=int, default=1)
     p.add_argument("--tokens", type=int, default=4096)
@@ -244,7 +289,7 @@ def main(argv=None):
     p.add_argument("--hv", type=int, default=32)
     p.add_argument("--iters", type=int, default=5)
     a = ap.parse_args(argv)
-    {"attention": bench_attention, "gemm": bench_gemm, "norm": bench_norm, "gdn": bench_gdn}[a.cmd](a)
+    {"attention": bench_attention, "gemm": bench_gemm, "norm": bench_norm, "gdn": bench_gdn, "moe": bench_moe}[a.cmd](a)
 
 
 if __name__ == "__main__":
