@@ -3,14 +3,17 @@
 // A8 / B8 are e4m3.  The hardware block-scaled MMA modes only take power-of-two (e8m0) scales per 32 elements, so a
 // checkpoint's fp32 block scales cannot ride along with the operands.  Instead every 128-deep K block is multiplied on
 // the tensor cores into its own TMEM accumulator (tcgen05.mma kind::f8f6f4, fp32 accumulate, overwrite mode), and the
-// four epilogue warps promote it: read the 128x128 partial from TMEM, multiply by the block's (row scale x tile scale)
-// and add it to fp32 accumulators held in registers (128 per thread: one output row, 128 columns).  Two TMEM buffers
-// alternate, so the tensor cores compute block kb+1 while block kb is being promoted: per block the MMA needs about
-// 256 cycles and the promotion about 200, so the two pipelines stay balanced.
+// epilogue warps promote it: read the 128x128 partial from TMEM, multiply by the block's (row scale x tile scale)
+// and add it to fp32 accumulators held in registers (64 per thread: one output row, 64 columns).  Two TMEM buffers
+// take turns, so the tensor cores compute block kb+1 while block kb is being promoted (four buffers measured the same; so
+// did polling instead of the suspended barrier wait, which was slower: the spinning warps take issue slots): per block the MMA needs about
+// 256 cycles and the promotion (split over eight warps) about 100 of issue plus its TMEM load latency.
 //
-// 192 threads: warp 0 = TMA producer (one 128-byte-swizzled 128x128 e4m3 tile of A and of B per stage, 6 stages), warp 1
-// = MMA issuer, warps 2-5 = promotion + store.  Every wait is a bounded mbarrier wait that reports through the status word.
-// No TMA load is cluster-multicast.
+// 320 threads: warp 0 = TMA producer (one 128-byte-swizzled 128x128 e4m3 tile of A and of B per stage, 6 stages), warp 1
+// = MMA issuer, warps 2-9 = promotion + store: two warps per TMEM lane quadrant, each owning 64 of the 128 columns, so that
+// every scheduler has two promotion warps and the latency of one warp's TMEM loads hides behind the other's FMAs (with one
+// warp per scheduler the tensor pipe sat at 32 % and the FMA pipe at 19 %).  Every wait is a bounded mbarrier wait that
+// reports through the status word.  No TMA load is cluster-multicast.
 //
 // Reference counterpart: the FP8 block-scale linear of kernels/src/cuda/fp8_linear.cu (fp8_block_* kernels: dequantise to
 // bf16 and run a bf16 GEMM, or 1x128-quantised activations with per-block fp32 rescale on mma.sync), routed from
@@ -36,12 +39,13 @@ struct FbCfg {
   static constexpr int BM = 128, BN = 128, BK = 128;
   static constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK;
   static constexpr int STAGES = 6;
-  static constexpr int TMEM_COLS = 256;                // two 128-column partial accumulators
+  static constexpr int NBUF = 2;                       // partial accumulators in flight (128 TMEM columns each)
+  static constexpr int TMEM_COLS = NBUF * 128;
   static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, FbParams p) {
   using Cfg = FbCfg;
   constexpr int BM = Cfg::BM, BN = Cfg::BN, STAGES = Cfg::STAGES;
@@ -52,9 +56,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * Cfg::B_BYTES);
   uint64_t* full = bars;                      // [STAGES] operands of a k block have landed
   uint64_t* empty = bars + STAGES;            // [STAGES] the MMAs reading a stage have completed
-  uint64_t* part_full = bars + 2 * STAGES;    // [2] a k block's partial products are complete in TMEM buffer b
-  uint64_t* part_empty = part_full + 2;       // [2] the promotion warps have read buffer b (4 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty + 2);
+  constexpr int NBUF = Cfg::NBUF;
+  uint64_t* part_full = bars + 2 * STAGES;    // [NBUF] a k block's partial products are complete in TMEM buffer b
+  uint64_t* part_empty = part_full + NBUF;    // [NBUF] the promotion warps have read buffer b (8 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty + NBUF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -64,7 +69,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&part_full[i], 1); mbar_init(&part_empty[i], 4); }
+    for (int i = 0; i < NBUF; ++i) { mbar_init(&part_full[i], 1); mbar_init(&part_empty[i], 8); }
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmA);
@@ -103,9 +108,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (elect_one()) {
       int s = 0; uint32_t ph = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int b = i & 1;
-        // buffer b was last filled for block i - 2: its promotion is completion number (i / 2 - 1) of part_empty[b]
-        if (i >= 2 && !mbar_wait(&part_empty[b], (uint32_t)(((i >> 1) - 1) & 1), abort_flag, p.status)) break;
+        const int b = i % NBUF;
+        // buffer b was last filled for block i - NBUF: its promotion is completion number (i / NBUF - 1) of part_empty[b]
+        if (i >= NBUF && !mbar_wait(&part_empty[b], (uint32_t)((i / NBUF - 1) & 1), abort_flag, p.status)) break;
         if (!mbar_wait(&full[s], ph, abort_flag, p.status)) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES), b_addr = smem_u32(sB + s * Cfg::B_BYTES);
@@ -118,39 +123,38 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
   } else {
-    // ------------------------------------------------------------------ promotion + store (128 threads)
+    // ------------------------------------------------------------------ promotion + store (256 threads)
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;       // which 64 columns of the tile this warp owns
     const int rl = q * 32 + lane;
     const int row = mt * BM + rl;
     const bool in_range = row < p.M;
     const float* sb = p.sb + (size_t)nt * nkb;
-    float acc[BN];
+    constexpr int HC = BN / 2;
+    float acc[HC];
 #pragma unroll
-    for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+    for (int i = 0; i < HC; ++i) acc[i] = 0.f;
     pdl_wait();                             // the activation scales come from the kernel before this one
     float sa_next = in_range ? p.sa[row] : 0.f;
     bool ok = true;
 #pragma unroll 1
     for (int i = 0; i < nkb; ++i) {
-      const int b = i & 1;
+      const int b = i % NBUF;
       const float s = sa_next * __ldg(sb + i);
       if (i + 1 < nkb) sa_next = in_range ? p.sa[(size_t)(i + 1) * p.ld_sa + row] : 0.f;
       // tcgen05.ld is warp-collective: the outcome of the wait is made warp-uniform before any lane loads
-      ok = __all_sync(0xffffffffu, mbar_wait(&part_full[b], (uint32_t)((i >> 1) & 1), abort_flag, p.status));
+      ok = __all_sync(0xffffffffu, mbar_wait(&part_full[b], (uint32_t)((i / NBUF) & 1), abort_flag, p.status));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t t0 = tmem + b * BN + ((uint32_t)(q * 32) << 16);
+      const uint32_t t0 = tmem + b * BN + half * HC + ((uint32_t)(q * 32) << 16);
+      uint32_t r0[32], r1[32];
+      tmem_ld32(t0, r0);
+      tmem_ld32(t0 + 32, r1);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < BN / 64; ++c) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(t0 + c * 64, r0);
-        tmem_ld32(t0 + c * 64 + 32, r1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          acc[c * 64 + j] = fmaf(__uint_as_float(r0[j]), s, acc[c * 64 + j]);
-          acc[c * 64 + 32 + j] = fmaf(__uint_as_float(r1[j]), s, acc[c * 64 + 32 + j]);
-        }
+      for (int j = 0; j < 32; ++j) {
+        acc[j] = fmaf(__uint_as_float(r0[j]), s, acc[j]);
+        acc[32 + j] = fmaf(__uint_as_float(r1[j]), s, acc[32 + j]);
       }
       tc_fence_before();
       __syncwarp();
@@ -158,8 +162,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
     if (ok && in_range) {
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        const int col0 = nt * BN + c * 8;
+      for (int c = 0; c < HC / 8; ++c) {
+        const int col0 = nt * BN + half * HC + c * 8;
         if (col0 >= p.N) break;
         float v[8];
 #pragma unroll
@@ -253,7 +257,7 @@ BLZ_API int blz_gemm_fp8_block(const void* A, long long lda, const void* B, long
   if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(((M + 127) / 128) * ((N + 127) / 128));
-  cfg.blockDim = dim3(192);
+  cfg.blockDim = dim3(320);
   cfg.dynamicSmemBytes = FbCfg::SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
