@@ -18,6 +18,10 @@
 // memory: every CTA owns a slice of the row columns, receives all peers' partials of that slice with posted remote stores,
 // sums them in CTA-rank order (bit-reproducible) and writes the result.
 //
+// A CTA of the expert GEMM computes `ft_per` feature tiles of its row tile one after the other: the operand ring keeps
+// streaming across them, and while the epilogue drains one accumulator (64 TMEM columns when the tile has at most 64 live
+// rows) the MMAs of the next tile fill the other, so set-up and drain are paid once per CTA instead of once per 8 K blocks.
+//
 // 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue.  Two CTAs per SM (3-stage ring).  Every
 // wait is a bounded mbarrier wait; the hardware cluster barrier is used once, right after barrier initialisation, where no
 // role can have failed yet.  No TMA load is cluster-multicast.
@@ -42,6 +46,7 @@ struct MoeGemmParams {
   int rows;                  // dense layer: rows of the activation matrix (<= 128)
   const __nv_bfloat16* bias; // [N] or null (dense layers)
   int ks;                    // cluster size = K slices (1 = no cluster)
+  int ft_per;                // feature tiles one CTA computes one after the other (1 when ks > 1)
   int act;                   // 1: SwiGLU epilogue, C is [rows, N / 2]
   int* status;
 };
@@ -85,11 +90,14 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const int ks = p.ks;
   const int unit = blockIdx.x / ks;                      // (row tile, feature tile); the cluster's CTAs share it
   const int kr = ks > 1 ? (int)cluster_ctarank() : 0;
-  const int ft = unit % tiles_n, mt = unit / tiles_n;
+  const int groups_n = (tiles_n + p.ft_per - 1) / p.ft_per;
+  const int ft0 = (unit % groups_n) * p.ft_per, mt = unit / groups_n;
+  const int nf = min(p.ft_per, tiles_n - ft0);           // feature tiles of this CTA
   const int ex = p.tile_expert ? p.tile_expert[mt] : 0;
   const int rows = ex < 0 ? 0 : min(p.tile_expert ? p.tile_rows[mt] : p.rows, 128);
   if (rows <= 0) return;                    // whole cluster, before anything is allocated
   const int ncols = (rows + 31) & ~31;      // MMA N: 32, 64, 96 or 128
+  const int nb = ncols <= 64 ? 2 : 1;       // accumulators in flight (64 TMEM columns apart)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -100,8 +108,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(sSFX + STAGES * Cfg::SF_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
-  uint64_t* acc_full = bars + 2 * STAGES;
-  uint64_t* part_ready = acc_full + 1;      // every CTA of the cluster has parked its partials (ks remote arrivals)
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2] a feature tile's accumulator is complete
+  uint64_t* acc_empty = acc_full + 2;       // [2] the epilogue has read it (4 arrivals)
+  uint64_t* part_ready = acc_empty + 2;     // every CTA of the cluster has parked its partials (ks remote arrivals)
   uint64_t* ring_free = part_ready + 1;     // every CTA of the cluster has finished its main loop (its ring may be written)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -111,11 +120,11 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const int k_tiles = (p.K + BK - 1) / BK;
   const int kb0 = (int)((long long)kr * k_tiles / ks), kb1 = (int)((long long)(kr + 1) * k_tiles / ks);
   const int nkb = kb1 - kb0;                // >= 1: the launcher keeps ks <= k_tiles
-  const size_t wrow0 = (size_t)ex * p.N + (size_t)ft * 128;     // first weight row of this tile
+  const size_t wbase = (size_t)ex * p.N;    // first weight row of this expert
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    mbar_init(acc_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
     mbar_init(part_ready, ks);
     mbar_init(ring_free, ks);
     *abort_flag = 0;
@@ -134,7 +143,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      auto issue = [&](int s, int kt, int what) {
+      auto issue = [&](int s, int kt, int what, size_t wrow0) {
         int atoms = 0;
         if constexpr (Cfg::SF_ATOMS > 0) atoms = min(Cfg::SF_ATOMS, p.sf_col_tiles - kt * Cfg::SF_ATOMS);
         const int kc = (KIND == 0) ? kt * BK : kt * 128;
@@ -154,17 +163,21 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         }
       };
       const int pre = min(STAGES, nkb);
-      for (int i = 0; i < pre; ++i) issue(i, kb0 + i, 1);
+      for (int i = 0; i < pre; ++i) issue(i, kb0 + i, 1, wbase + (size_t)ft0 * 128);
       pdl_wait();
       int s = 0; uint32_t ph = 0;
-      for (int i = 0; i < nkb; ++i) {
-        if (i < pre) {
-          issue(s, kb0 + i, 2);
-        } else {
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status)) break;
-          issue(s, kb0 + i, 3);
+      bool ok = true;
+      for (int fi = 0; fi < nf && ok; ++fi) {
+        const size_t wrow0 = wbase + (size_t)(ft0 + fi) * 128;
+        for (int i = 0; i < nkb; ++i) {
+          if (fi == 0 && i < pre) {
+            issue(s, kb0 + i, 2, wrow0);
+          } else {
+            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+            issue(s, kb0 + i, 3, wrow0);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -172,39 +185,46 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     if (elect_one()) {
       int s = 0; uint32_t ph = 0;
       bool ok = true;
-      for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
+      for (int fi = 0; fi < nf && ok; ++fi) {
+        const int ab = fi % nb;
+        // accumulator ab was last filled for tile fi - nb: its read-out is completion number (fi / nb - 1) of acc_empty[ab]
+        if (fi >= nb && !mbar_wait(&acc_empty[ab], (uint32_t)((fi / nb - 1) & 1), abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t w_addr = smem_u32(sW + s * Cfg::W_BYTES), x_addr = smem_u32(sX + s * Cfg::X_BYTES);
-        const int kt = kb0 + i;
-        const int nblk = min(4, (p.K - kt * BK + Cfg::KMMA - 1) / Cfg::KMMA);
-        const uint32_t sf_t = tmem + Cfg::SF_COL0 + s * Cfg::SF_COLS_PER_STAGE;      // weights' scales, then the rows' scales
-        if constexpr (Cfg::SF_ATOMS > 0) {
-          const int atoms = min(Cfg::SF_ATOMS, p.sf_col_tiles - kt * Cfg::SF_ATOMS);
-          for (int a = 0; a < atoms; ++a) {
-            tmem_cp_sf(sf_t + a * 4, make_smem_desc(smem_u32(sSFW + s * Cfg::SF_BYTES + a * 512), 0, 128, kSwzNone));
-            tmem_cp_sf(sf_t + Cfg::SF_ATOMS * 4 + a * 4,
-                       make_smem_desc(smem_u32(sSFX + s * Cfg::SF_BYTES + a * 512), 0, 128, kSwzNone));
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (j < nblk) {
-            const uint64_t dw = desc_sw128(w_addr + j * 32), dx = desc_sw128(x_addr + j * 32);
-            const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
-            if constexpr (KIND == 0) {
-              mma_f16(tmem, dw, dx, make_idesc(1, 1, 128, ncols), acc);
-            } else if constexpr (KIND == 1) {
-              mma_nvfp4(tmem, dw, dx, make_idesc_bs(1, 1, 0, 128, ncols), sf_t + j * 4, sf_t + Cfg::SF_ATOMS * 4 + j * 4, acc);
-            } else {
-              mma_mxf8(tmem, dw, dx, make_idesc_bs(0, 0, 1, 128, ncols, j, j), sf_t, sf_t + Cfg::SF_ATOMS * 4, acc);
+        const uint32_t d_tmem = tmem + ab * 64;
+        for (int i = 0; i < nkb; ++i) {
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t w_addr = smem_u32(sW + s * Cfg::W_BYTES), x_addr = smem_u32(sX + s * Cfg::X_BYTES);
+          const int kt = kb0 + i;
+          const int nblk = min(4, (p.K - kt * BK + Cfg::KMMA - 1) / Cfg::KMMA);
+          const uint32_t sf_t = tmem + Cfg::SF_COL0 + s * Cfg::SF_COLS_PER_STAGE;      // weights' scales, then the rows' scales
+          if constexpr (Cfg::SF_ATOMS > 0) {
+            const int atoms = min(Cfg::SF_ATOMS, p.sf_col_tiles - kt * Cfg::SF_ATOMS);
+            for (int a = 0; a < atoms; ++a) {
+              tmem_cp_sf(sf_t + a * 4, make_smem_desc(smem_u32(sSFW + s * Cfg::SF_BYTES + a * 512), 0, 128, kSwzNone));
+              tmem_cp_sf(sf_t + Cfg::SF_ATOMS * 4 + a * 4,
+                         make_smem_desc(smem_u32(sSFX + s * Cfg::SF_BYTES + a * 512), 0, 128, kSwzNone));
             }
           }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (j < nblk) {
+              const uint64_t dw = desc_sw128(w_addr + j * 32), dx = desc_sw128(x_addr + j * 32);
+              const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
+              if constexpr (KIND == 0) {
+                mma_f16(d_tmem, dw, dx, make_idesc(1, 1, 128, ncols), acc);
+              } else if constexpr (KIND == 1) {
+                mma_nvfp4(d_tmem, dw, dx, make_idesc_bs(1, 1, 0, 128, ncols), sf_t + j * 4, sf_t + Cfg::SF_ATOMS * 4 + j * 4, acc);
+              } else {
+                mma_mxf8(d_tmem, dw, dx, make_idesc_bs(0, 0, 1, 128, ncols, j, j), sf_t, sf_t + Cfg::SF_ATOMS * 4, acc);
+              }
+            }
+          }
+          mma_commit(&empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        mma_commit(&empty[s]);
-        if (++s == STAGES) { s = 0; ph ^= 1; }
+        if (ok) mma_commit(&acc_full[ab]);
       }
-      if (ok) mma_commit(acc_full);
     }
   }
   __syncwarp();
@@ -213,13 +233,14 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     // ------------------------------------------------------------------ epilogue: lane = feature, column = routed row
     const int q = warp & 3;
     const int fl = q * 32 + lane;                       // feature of this thread inside the tile
-    const float al = p.alpha ? __ldg(p.alpha + wrow0 + fl) : 1.0f;
-    const float bs = p.bias ? bf2f(p.bias[ft * 128 + fl]) : 0.0f;
+    int ft = ft0;                                       // feature tile being finished
+    float al = p.alpha ? __ldg(p.alpha + wbase + (size_t)ft * 128 + fl) : 1.0f;
+    float bs = p.bias ? bf2f(p.bias[ft * 128 + fl]) : 0.0f;
     pdl_wait();
     s_rs[fl] = (p.row_scale && fl < rows) ? p.row_scale[(size_t)mt * 128 + fl] : 1.0f;
     bar_sync(1, 128);
     // tcgen05.ld is warp-collective: the outcome of the wait is made warp-uniform, only the stores are predicated
-    const bool got = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, p.status));
+    bool got = __all_sync(0xffffffffu, mbar_wait(&acc_full[0], 0, abort_flag, p.status));
     tc_fence_after();
     // finished sums of this thread's feature for the row columns [c0, c0 + n): scales, bias, activation, store.
     // Called by all lanes of a warp with the same c0 and n.
@@ -243,11 +264,25 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       }
     };
     if (ks == 1) {
-      if (got) {
+      for (int fi = 0; fi < nf && got; ++fi) {
+        const int ab = fi % nb;
+        if (fi > 0) {
+          ft = ft0 + fi;
+          al = p.alpha ? __ldg(p.alpha + wbase + (size_t)ft * 128 + fl) : 1.0f;
+          bs = p.bias ? bf2f(p.bias[ft * 128 + fl]) : 0.0f;
+          got = __all_sync(0xffffffffu, mbar_wait(&acc_full[ab], (uint32_t)((fi / nb) & 1), abort_flag, p.status));
+          tc_fence_after();
+          if (!got) break;
+        }
         for (int c = 0; c < ncols; c += 32) {
           uint32_t r[32];
-          tmem_ld32(tmem + c + ((uint32_t)(q * 32) << 16), r);
+          tmem_ld32(tmem + ab * 64 + c + ((uint32_t)(q * 32) << 16), r);
           tmem_ld_wait();
+          if (c + 32 >= ncols) {       // the accumulator is in registers: hand it back before the stores
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[ab]);
+          }
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -327,7 +362,8 @@ static cudaError_t launch_moe_gemm(const CUtensorMap& tmW, const CUtensorMap& tm
   cudaError_t e = configured.smem_limit(kern, MgCfg<KIND>::SMEM);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(row_tiles * (p.N / 128) * ks));
+  const int groups_n = (p.N / 128 + p.ft_per - 1) / p.ft_per;
+  cfg.gridDim = dim3((unsigned)(row_tiles * groups_n * ks));
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = MgCfg<KIND>::SMEM;
   cfg.stream = stream;
@@ -372,6 +408,14 @@ BLZ_API int blz_moe_gemm(int kind, const void* X, long long ldx, const void* W, 
   p.sf_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
   p.tile_expert = tile_expert; p.tile_rows = tile_rows; p.act = act;
   p.rows = 0; p.bias = nullptr; p.ks = 1;
+  {
+    // feature tiles per CTA: long enough streams to amortise a CTA's set-up, still at least four CTAs per row tile
+    static int forced = -1;
+    if (forced < 0) { const char* e = getenv("BLAZE_MOE_FT_PER"); forced = e ? atoi(e) : 0; }
+    const int tiles_n = N / 128;
+    p.ft_per = forced > 0 ? forced : (tiles_n >= 12 ? (tiles_n % 4 == 0 ? 4 : 3) : (tiles_n >= 6 ? 2 : 1));
+    if (p.ft_per > tiles_n) p.ft_per = tiles_n;
+  }
   p.status = status_word();
   CUtensorMap tmW, tmX;
   cudaError_t e;
@@ -421,7 +465,7 @@ BLZ_API int blz_gemm_narrow(int kind, const void* X, long long ldx, const void* 
   p.sfw = reinterpret_cast<const uint8_t*>(sfw); p.sfx = reinterpret_cast<const uint8_t*>(sfx);
   p.sf_col_tiles = kind == 1 ? (K + 63) / 64 : kind == 2 ? (K + 127) / 128 : 0;
   p.tile_expert = nullptr; p.tile_rows = nullptr; p.rows = M; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  p.ks = ks; p.act = act;
+  p.ks = ks; p.act = act; p.ft_per = 1;
   p.status = status_word();
   CUtensorMap tmW, tmX;
   cudaError_t e;
