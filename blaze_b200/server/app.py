@@ -10,6 +10,7 @@ last 256 Responses objects (``server/responses.rs``).
 from __future__ import annotations
 
 import asyncio
+import contextvars
 import base64
 import hmac
 import json
@@ -35,6 +36,10 @@ RESPONSES_KEPT = 256
 THINK_CLOSING = "\n\nConsidering the limited time, I have to give the solution based on the thinking directly now.\n</think>\n\n"
 
 
+# the HTTP request being served (set by the middleware): generations poll it to notice a client that went away
+_current_request: "contextvars.ContextVar[Optional[Request]]" = contextvars.ContextVar("blaze_current_request", default=None)
+
+
 def _err(status: int, message: str, typ: str = "invalid_request_error", param=None, code=None) -> JSONResponse:
     return JSONResponse({"error": {"message": message, "type": typ, "param": param, "code": code}}, status_code=status)
 
@@ -44,6 +49,7 @@ class Totals:
         self.requests = self.errors = self.prompt_tokens = self.cached_tokens = self.output_tokens = 0
         self.e2e = Histogram.latency()
         self.inflight = 0
+        self.cancelled = 0
 
 
 class ServerState:
@@ -103,6 +109,7 @@ class Gen:
         self.finish: Optional[Finish] = None
         self.error: Optional[str] = None
         self.n_out = 0
+        self.http_request = _current_request.get()
         st.llm.sched.submit(self.req)
 
     def _sink(self, ev: GenEvent) -> None:
@@ -113,13 +120,32 @@ class Gen:
 
     async def events(self) -> AsyncIterator[GenEvent]:
         deadline = time.monotonic() + self.st.svc.request_timeout_s
+        last_probe = time.monotonic()
+
+        async def client_gone() -> bool:
+            """A client that closed its connection (streaming or not) ends the generation; probed twice a second."""
+            nonlocal last_probe
+            last_probe = time.monotonic()
+            req = self.http_request
+            try:
+                return req is not None and await req.is_disconnected()
+            except Exception:
+                return False
         while True:
             try:
-                ev = await asyncio.wait_for(self.q.get(), timeout=max(deadline - time.monotonic(), 0.01))
+                ev = await asyncio.wait_for(self.q.get(), timeout=min(max(deadline - time.monotonic(), 0.01), 0.5))
             except asyncio.TimeoutError:
-                self.st.llm.sched.abort(self.rid)
-                self.finish, self.error = Finish.ABORT, "request deadline exceeded"
+                if time.monotonic() >= deadline:
+                    self.st.llm.sched.abort(self.rid)
+                    self.finish, self.error = Finish.ABORT, "request deadline exceeded"
+                    return
+                ev = None
+            if (ev is None or time.monotonic() - last_probe > 0.5) and await client_gone():
+                self.abort(cancelled=True)
+                self.finish, self.error = Finish.ABORT, "client disconnected"
                 return
+            if ev is None:
+                continue
             self.cached = ev.cached_tokens
             self.n_out += len(ev.tokens)
             if ev.tokens or ev.hidden is not None:
@@ -128,7 +154,11 @@ class Gen:
                 self.finish, self.error = ev.finish, ev.error
                 return
 
-    def abort(self) -> None:
+    def abort(self, cancelled: bool = True) -> None:
+        """End the request early.  ``cancelled``: the client went away (counted as such); False: a stop string matched."""
+        if cancelled and not getattr(self, "_counted_cancel", False):
+            self._counted_cancel = True
+            self.st.totals.cancelled += 1
         self.st.llm.sched.abort(self.rid)
 
 
@@ -162,7 +192,9 @@ def create_app(st: ServerState) -> FastAPI:
     # ------------------------------------------------------------------ middleware: request id, CORS, auth, loading, admission
     @app.middleware("http")
     async def control(request: Request, call_next):
-        rid = request.headers.get("x-request-id") or uuid.uuid4().hex
+        rid = request.headers.get("x-request-id") or ""
+        if not rid or len(rid) > 128 or not all(c.isalnum() or c in "-_.:" for c in rid):
+            rid = uuid.uuid4().hex          # absent or not a plain token: the server names the request
         path = request.url.path
         cors = {"access-control-allow-origin": ",".join(st.svc.cors_origins), "access-control-allow-headers": "*",
                 "access-control-allow-methods": "GET,POST,DELETE,OPTIONS", "x-request-id": rid}
@@ -205,6 +237,7 @@ def create_app(st: ServerState) -> FastAPI:
                 st.sem.release()
                 st.totals.inflight -= 1
                 st.totals.e2e.observe(time.monotonic() - t0)
+        _current_request.set(request)
         try:
             resp = await call_next(request)
         except Exception:
@@ -237,7 +270,17 @@ def create_app(st: ServerState) -> FastAPI:
     @app.exception_handler(RequestError)
     async def on_request_error(request: Request, e: RequestError):
         st.totals.errors += 1
-        return _err(e.status, e.message, e.code if e.code != "invalid_request_error" else "invalid_request_error", e.param)
+        return _err(e.status, e.message, "invalid_request_error" if e.status < 500 else "server_error", e.param,
+                    code=None if e.code == "invalid_request_error" else e.code)
+
+    from starlette.exceptions import HTTPException as _HTTPException
+
+    @app.exception_handler(_HTTPException)
+    async def on_http_error(request: Request, e: _HTTPException):
+        # unknown routes and wrong methods answer with the OpenAI error object too
+        msg = {404: f"no route {request.method} {request.url.path}", 405: f"method {request.method} is not allowed on {request.url.path}"}.get(
+            e.status_code, str(e.detail))
+        return _err(e.status_code, msg, "invalid_request_error", code={404: "not_found", 405: "method_not_allowed"}.get(e.status_code))
 
     @app.exception_handler(ConstraintError)
     async def on_constraint_error(request: Request, e: ConstraintError):
@@ -282,7 +325,12 @@ def create_app(st: ServerState) -> FastAPI:
                 "active": len(llm.sched.active), "waiting": len(llm.sched.waiting), "preempted": len(llm.sched.preempted),
                 "stats": vars(s), "prefix_cache": {"entries": len(llm.sched.cache.entries), "hits": llm.sched.cache.hits,
                                                    "lookups": llm.sched.cache.lookups},
-                "weights": llm.model.weight_format.value, "kernels": llm.model.ops.name}
+                "weights": llm.model.weight_format.value, "kernels": llm.model.ops.name,
+                "sampling_defaults": dict(st.svc.defaults), "default_max_tokens": st.svc.default_max_tokens,
+                "scheduler": {"schedule": llm.sched.cfg.schedule, "chunk": llm.sched.cfg.chunk, "max_seqs": llm.sched.cfg.max_seqs,
+                              "max_step_tokens": llm.sched.cfg.max_step_tokens, "spec_method": llm.sched.cfg.spec_method,
+                              "max_draft": llm.sched.cfg.max_draft, "prefix_cache": llm.sched.cfg.prefix_cache},
+                "config": {k: ("[REDACTED]" if "key" in k else v) for k, v in st.svc.public_config().items()}}
 
     @app.get("/metrics")
     async def metrics():
@@ -300,6 +348,9 @@ def create_app(st: ServerState) -> FastAPI:
         counter("blaze_cached_prompt_tokens_total", t.cached_tokens, "Prompt tokens served from the prefix cache")
         counter("blaze_generation_tokens_total", t.output_tokens, "Tokens generated")
         gauge("blaze_requests_in_flight", t.inflight, "Requests being served")
+        gauge("blaze_requests_running", t.inflight, "Requests being served (same as blaze_requests_in_flight)")
+        counter("blaze_requests_cancelled_total", t.cancelled, "Requests whose client went away before the end")
+        counter("blaze_prefill_tokens_total", t.prompt_tokens - t.cached_tokens, "Prompt tokens computed (not served from the prefix cache)")
         gauge("blaze_requests_waiting", st.waiting, "Requests waiting for admission")
         if st.ready:
             sc = st.llm.sched
@@ -333,20 +384,29 @@ def create_app(st: ServerState) -> FastAPI:
     async def tokenize(request: Request):
         b = await _body(request)
         if "messages" in b:
-            text = st.formatter.render(b["messages"], b.get("tools"), b.get("add_generation_prompt", True))
+            # what a chat request with the same body would use as its prompt (tools, tool_choice, template arguments)
+            tools = b.get("tools")
+            if b.get("tool_choice", "auto" if tools else "none") == "none":
+                tools = None
+            ctk = b.get("chat_template_kwargs") or {}
+            text = st.formatter.render(b["messages"], tools, b.get("add_generation_prompt", True),
+                                       ctk.get("enable_thinking", b.get("enable_thinking")))
         else:
             text = b.get("prompt", b.get("text"))
         if not isinstance(text, str):
             raise RequestError("prompt must be a string", "prompt")
         ids = st.tokenizer.encode(text, add_special_tokens=bool(b.get("add_special_tokens", False)))
-        return {"tokens": ids, "count": len(ids), "max_model_len": st.max_len}
+        out = {"tokens": ids, "count": len(ids), "max_model_len": st.max_len}
+        if b.get("return_token_strs"):
+            out["token_strs"] = [st.tokenizer.decode([t], skip_special_tokens=False) for t in ids]
+        return out
 
     @app.post("/detokenize")
     async def detokenize(request: Request):
         b = await _body(request)
         ids = b.get("tokens")
-        if not isinstance(ids, list) or any(not isinstance(t, int) or t < 0 for t in ids):
-            raise RequestError("tokens must be a list of token ids", "tokens")
+        if not isinstance(ids, list) or any(isinstance(t, bool) or not isinstance(t, int) or not 0 <= t < st.vocab for t in ids):
+            raise RequestError("tokens must be a list of token ids of this model's vocabulary", "tokens")
         return {"prompt": st.tokenizer.decode(ids, skip_special_tokens=bool(b.get("skip_special_tokens", False)))}
 
     # ------------------------------------------------------------------ helpers shared by the generation routes
@@ -455,7 +515,7 @@ def create_app(st: ServerState) -> FastAPI:
                     if ev.logprobs:
                         lps.extend(ev.logprobs)
                     if d.stopped:
-                        g.abort()
+                        g.abort(cancelled=False)
                         break
                 proc.finish()
                 _account(g)
@@ -505,7 +565,7 @@ def create_app(st: ServerState) -> FastAPI:
                         for c in chunks_of(d, ev.logprobs if want_lp else None):
                             yield c
                         if d.stopped:
-                            g.abort()
+                            g.abort(cancelled=False)
                             break
                     for c in chunks_of(proc.finish()):
                         yield c
@@ -544,6 +604,11 @@ def create_app(st: ServerState) -> FastAPI:
         params = sampling_of(b, st.svc, st.vocab)
         if len(prompts) * params.n > MAX_COMPLETIONS_PER_REQUEST:
             raise RequestError(f"at most {MAX_COMPLETIONS_PER_REQUEST} generations per request", "n")
+        keep = b.get("truncate_prompt_tokens")
+        if keep is not None:
+            if isinstance(keep, bool) or not isinstance(keep, int) or keep < 1:
+                raise RequestError("truncate_prompt_tokens must be a positive integer", "truncate_prompt_tokens")
+            prompts = [p[-keep:] for p in prompts]          # the tail of an over-long prompt is what is kept
         for p in prompts:
             if any(t < 0 or t >= st.vocab for t in p):
                 raise RequestError("prompt token id outside the vocabulary", "prompt")
@@ -551,6 +616,8 @@ def create_app(st: ServerState) -> FastAPI:
         stops = stop_strings_of(b)
         include_stop = bool(b.get("include_stop_str_in_output", False))
         echo = bool(b.get("echo", False))
+        if echo and params.logprobs is not None:
+            raise RequestError("echo with logprobs is not supported (prompt log-probabilities are not computed)", "echo")
         stream = bool(b.get("stream", False))
         spec = grammar_of(b)
         created, cid = int(time.time()), "cmpl-" + uuid.uuid4().hex[:24]
@@ -562,11 +629,15 @@ def create_app(st: ServerState) -> FastAPI:
                 gens.append((Gen(st, p, sp, constraint=cons), ChatResponseProcessor(
                     st.tokenizer, stops, include_stop, bool(b.get("skip_special_tokens", True))), p))
 
-        def lp_obj(lps):
+        def lp_obj(lps, offset0=0):
             toks = [st.tokenizer.token_bytes(l["token"]).decode("utf-8", errors="replace") for l in lps]
+            offs, o = [], offset0
+            for t in toks:
+                offs.append(o)
+                o += len(t)
             return {"tokens": toks, "token_logprobs": [max(l["logprob"], -9999.0) for l in lps],
                     "top_logprobs": [{st.tokenizer.token_bytes(t).decode("utf-8", errors="replace"): max(v, -9999.0)
-                                      for t, v in l.get("top", [])} for l in lps]}
+                                      for t, v in l.get("top", [])} for l in lps], "text_offset": offs}
 
         if not stream:
             choices = []
@@ -577,7 +648,7 @@ def create_app(st: ServerState) -> FastAPI:
                     if ev.logprobs:
                         lps.extend(ev.logprobs)
                     if d.stopped:
-                        g.abort()
+                        g.abort(cancelled=False)
                         break
                 proc.finish()
                 _account(g)
@@ -599,17 +670,28 @@ def create_app(st: ServerState) -> FastAPI:
                 for i, (g, proc, p) in enumerate(gens):
                     if echo:
                         yield _sse({**base, "choices": [{"index": i, "text": st.tokenizer.decode(p), "finish_reason": None}]})
+                    sent = 0                     # characters of this choice's text already sent (text_offset of the next token)
+                    pend_lp = []
                     async for ev in g.events():
                         d = proc.push(ev.tokens)
-                        if d.content:
-                            yield _sse({**base, "choices": [{"index": i, "text": d.content, "finish_reason": None}]})
+                        if ev.logprobs and params.logprobs is not None:
+                            pend_lp.extend(ev.logprobs)
+                        if d.content or pend_lp:
+                            ch = {"index": i, "text": d.content or "", "finish_reason": None}
+                            if params.logprobs is not None:
+                                ch["logprobs"] = lp_obj(pend_lp, sent)
+                                pend_lp = []
+                            sent += len(d.content or "")
+                            yield _sse({**base, "choices": [ch]})
                         if d.stopped:
-                            g.abort()
+                            g.abort(cancelled=False)
                             break
                     d = proc.finish()
                     _account(g)
-                    yield _sse({**base, "choices": [{"index": i, "text": d.content,
-                                                     "finish_reason": finish_reason(g.finish, False, proc.stopped)}]})
+                    ch = {"index": i, "text": d.content, "finish_reason": finish_reason(g.finish, False, proc.stopped)}
+                    if params.logprobs is not None:
+                        ch["logprobs"] = lp_obj(pend_lp, sent)
+                    yield _sse({**base, "choices": [ch]})
                 if include_usage:
                     yield _sse({**base, "choices": [], "usage": _usage(sum(len(p) for _, _, p in gens), sum(g.n_out for g, _, _ in gens))})
                 yield b"data: [DONE]\n\n"
@@ -886,7 +968,7 @@ def create_app(st: ServerState) -> FastAPI:
             async for ev in g.events():
                 d = proc.push(ev.tokens)
                 if d.stopped:
-                    g.abort()
+                    g.abort(cancelled=False)
                     break
             proc.finish()
             _account(g)
@@ -930,7 +1012,7 @@ def create_app(st: ServerState) -> FastAPI:
                     for c in await emit(d):
                         yield c
                     if d.stopped:
-                        g.abort()
+                        g.abort(cancelled=False)
                         break
                 for c in await emit(proc.finish()):
                     yield c

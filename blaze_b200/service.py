@@ -52,6 +52,17 @@ class ServiceArgs:
     cors_origins: Tuple[str, ...] = ("*",)
     defaults: Dict[str, Any] = field(default_factory=dict)
 
+    def public_config(self) -> Dict[str, Any]:
+        """The service flags as the info route may show them (flag spelling; keys are never shown)."""
+        out: Dict[str, Any] = {}
+        for k, v in vars(self).items():
+            if k == "api_keys":
+                if v:
+                    out["api-key"] = "[REDACTED]"
+                continue
+            out[k.replace("_", "-")] = list(v) if isinstance(v, tuple) else v
+        return out
+
     def __post_init__(self):
         env = os.environ.get("BLAZE_API_KEY")
         if env and not self.api_keys:
@@ -122,8 +133,9 @@ def sampling_of(body: Dict[str, Any], svc: ServiceArgs, vocab_size: int, max_tok
             raise RequestError("logit_bias values must be in [-100, 100]", "logit_bias")
         lb[tid] = float(v)
     stop_ids = b.get("stop_token_ids") or []
-    if not isinstance(stop_ids, list) or len(stop_ids) > MAX_STOP_IDS or any(not isinstance(t, int) for t in stop_ids):
-        raise RequestError(f"stop_token_ids must be a list of at most {MAX_STOP_IDS} token ids", "stop_token_ids")
+    if not isinstance(stop_ids, list) or len(stop_ids) > MAX_STOP_IDS or any(
+            isinstance(t, bool) or not isinstance(t, int) or not 0 <= t < vocab_size for t in stop_ids):
+        raise RequestError(f"stop_token_ids must be a list of at most {MAX_STOP_IDS} token ids of the vocabulary", "stop_token_ids")
     bad = b.get("bad_words_ids") or []
     if not isinstance(bad, list) or len(bad) > MAX_STOP_IDS:
         raise RequestError(f"bad_words_ids must be a list of at most {MAX_STOP_IDS} id lists", "bad_words_ids")
@@ -136,8 +148,12 @@ def sampling_of(body: Dict[str, Any], svc: ServiceArgs, vocab_size: int, max_tok
     elif logprobs is not None:
         want_lp = _num(b, "logprobs", 0, lo=0, hi=MAX_TOP_LOGPROBS, integer=True)
     seed = b.get("seed")
-    if seed is not None and (isinstance(seed, bool) or not isinstance(seed, int)):
-        raise RequestError("seed must be an integer", "seed")
+    if seed is not None and (isinstance(seed, bool) or not isinstance(seed, int) or not 0 <= seed < 2 ** 64):
+        raise RequestError("seed must be a non-negative integer", "seed")
+    if lp is not None and (isinstance(lp, bool) or not isinstance(lp, int)):
+        raise RequestError("top_logprobs must be an integer", "top_logprobs")
+    if "stream" in body and body["stream"] is not None and not isinstance(body["stream"], bool):
+        raise RequestError("stream must be a boolean", "stream")
     return SamplingParams(
         temperature=_num(b, "temperature", 1.0, lo=0.0),
         top_p=_num(b, "top_p", 1.0, lo=0.0, hi=1.0, lo_open=True),

@@ -197,3 +197,43 @@ def test_server_with_another_chat_family():
         assert msg["role"] == "assistant" and r.json()["usage"]["completion_tokens"] == 6
     finally:
         llm.sched.stop()
+
+
+def test_protocol_details_clients_rely_on(client):
+    """Behaviours that OpenAI-style clients and the reference's own API test client check: error objects on unknown routes
+    and wrong methods, request ids, metric names, the info route, range checks, token strings, prompt truncation."""
+    r = client.get("/v1/nope", headers=H)
+    assert r.status_code == 404 and r.json()["error"]["type"] == "invalid_request_error"
+    assert client.get("/v1/chat/completions", headers=H).status_code == 405
+    r = client.get("/v1/models", headers={**H, "x-request-id": "trace-42"})
+    assert r.headers["x-request-id"] == "trace-42"
+    r = client.get("/v1/models", headers={**H, "x-request-id": "not a valid id"})
+    assert r.headers["x-request-id"] and r.headers["x-request-id"] != "not a valid id"
+    m = client.get("/metrics").text
+    for name in ("blaze_requests_total", "blaze_requests_running", "blaze_requests_waiting", "blaze_requests_cancelled_total",
+                 "blaze_prefill_tokens_total"):
+        assert name in m, name
+    info = client.get("/server_info", headers=H).json()
+    assert "sampling_defaults" in info and "scheduler" in info and info["config"].get("api-key") == "[REDACTED]"
+    assert "secret" not in json.dumps(info)
+    for extra in ({"seed": -1}, {"stop_token_ids": [2 ** 64 - 1]}, {"stop_token_ids": ["bad"]}, {"top_logprobs": "many"},
+                  {"stream": "yes"}, {"top_k": 1.5}, {"max_tokens": "ten"}, {"logit_bias": {"0": 101}}, {"echo": True, "logprobs": 1}):
+        r = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 2, **extra}, headers=H)
+        assert r.status_code == 400 and "error" in r.json(), extra
+    t = client.post("/tokenize", json={"prompt": "Hi", "return_token_strs": True}, headers=H).json()
+    assert "".join(t["token_strs"]) == "Hi"
+    assert client.post("/detokenize", json={"tokens": [10 ** 9]}, headers=H).status_code == 400
+    # the chat form of /tokenize counts what the chat route uses as its prompt
+    body = {"messages": [{"role": "user", "content": "Say hi."}], "chat_template_kwargs": {"enable_thinking": False}}
+    n = client.post("/tokenize", json=body, headers=H).json()["count"]
+    r = client.post("/v1/chat/completions", json={**body, "max_tokens": 2}, headers=H).json()
+    assert r["usage"]["prompt_tokens"] == n
+    big = "the " * 600
+    r = client.post("/v1/completions", json={"prompt": big, "max_tokens": 3}, headers=H)
+    assert r.status_code == 400 and r.json()["error"]["code"] == "context_length_exceeded"
+    r = client.post("/v1/completions", json={"prompt": big, "max_tokens": 3, "truncate_prompt_tokens": 100}, headers=H)
+    assert r.status_code == 200 and r.json()["usage"]["prompt_tokens"] == 100
+    r = client.post("/v1/completions", json={"prompt": "Count: 1, 2,", "max_tokens": 5, "temperature": 0, "logprobs": 2}, headers=H).json()
+    lp = r["choices"][0]["logprobs"]
+    assert len(lp["tokens"]) == len(lp["token_logprobs"]) == len(lp["top_logprobs"]) == len(lp["text_offset"]) >= 2
+    assert lp["text_offset"][0] == 0
