@@ -203,7 +203,8 @@ def bench_moe(a):
 
 def bench_gdn(a):
     """Gated DeltaNet layer core (conv + gated delta rule + gated norm) over prompts: the chunked tensor-core kernel against
-    the token-by-token kernel on the same inputs."""
+    (preparation of all chunks in parallel + sequential scan, and the one fused kernel) against the token-by-token kernel
+    on the same inputs."""
     from ..batch import SeqChunk, build_batch
     from ..config import named_config
     from ..kv import KVCache
@@ -236,8 +237,8 @@ def bench_gdn(a):
     bb = torch.randn(T, hv, device="cuda").bfloat16()
     aa = torch.randn(T, hv, device="cuda").bfloat16()
     res = {}
-    for name, cm in (("chunked", 64), ("token_by_token", 0)):
-        ops.GDN_CHUNK_MIN = cm
+    for name, cm, split in (("chunked", 64, True), ("chunked_one_kernel", 64, False), ("token_by_token", 0, False)):
+        ops.GDN_CHUNK_MIN, ops.GDN_SPLIT = cm, split
         med, best = timeit(lambda: ops.gdn(mixed, z, bb, aa, gd, m, batch, kv, 0), a.iters, flush=False)
         res[name + "_ms"] = med
     res["status"] = ops.take_status()

@@ -132,6 +132,13 @@ class CudaOps:
                                       _c.c_int, _c.c_int, _c.c_int, VP]
         # Gated DeltaNet: sequences with at least this many new tokens in a step take the chunked tensor-core kernel (0 = never)
         self.GDN_CHUNK_MIN = int(os.environ.get("BLAZE_GDN_CHUNK_MIN", "64"))
+        lib.blz_gdn_chunk_split.argtypes = [VP, VP, VP, _c.c_longlong, VP, VP, VP, VP, VP, VP, VP, VP, _c.c_int, _c.c_int, _c.c_int,
+                                            _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, VP, VP]
+        lib.blz_gdn_chunk_ws_bytes.restype = _c.c_longlong
+        lib.blz_gdn_chunk_ws_bytes.argtypes = [_c.c_int, _c.c_int]
+        # chunk-parallel preparation + sequential scan (two kernels) instead of the one fused kernel; 0 keeps the fused one
+        self.GDN_SPLIT = os.environ.get("BLAZE_GDN_SPLIT", "1") != "0"
+        self.GDN_SPLIT_MAX_WS = 4 << 30
         lib.blz_gated_rmsnorm.argtypes = [VP, VP, _c.c_longlong, VP, VP, _c.c_int, _c.c_int, _c.c_int, _c.c_float, _c.c_int, VP]
         lib.blz_status_take.restype = _c.c_int
         lib.blz_status_peek_async.restype = _c.c_int
@@ -810,7 +817,16 @@ class CudaOps:
         # long token runs (prompt chunks) go through the chunked tensor-core kernel, short ones (decode, verify, replay)
         # through the token-by-token kernel; both walk the same batch and each takes its own sequences
         chunked = (self.GDN_CHUNK_MIN > 0 and not state_only and dk == 128 and dv == 128 and batch.max_q_len >= self.GDN_CHUNK_MIN)
-        if chunked:
+        n_chunks = T // 128 + B                    # upper bound of the sum over sequences of ceil(new tokens / 128)
+        ws_bytes = int(self.lib.blz_gdn_chunk_ws_bytes(n_chunks, hv)) if chunked and self.GDN_SPLIT else 0
+        if chunked and self.GDN_SPLIT and ws_bytes <= self.GDN_SPLIT_MAX_WS:
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
+            self._check(self.lib.blz_gdn_chunk_split(_ptr(conv), _ptr(a), _ptr(b), a.stride(0), _ptr(gdn.A_log), _ptr(gdn.dt_bias),
+                                                     _ptr(kv.rec_state[layer_idx]), _ptr(o), _ptr(batch.slots), _ptr(batch.q_start),
+                                                     _ptr(batch.ctx_len), _ptr(batch.gdn_defer), B, hk, hv, dk, dv, self.GDN_CHUNK_MIN,
+                                                     int(batch.max_q_len), n_chunks, _ptr(ws), self._stream()), "gdn_chunk_split")
+            self.launches += 1                     # two kernels behind the one call
+        elif chunked:
             self._check(self.lib.blz_gdn_chunk(_ptr(conv), _ptr(a), _ptr(b), a.stride(0), _ptr(gdn.A_log), _ptr(gdn.dt_bias),
                                                _ptr(kv.rec_state[layer_idx]), _ptr(o), _ptr(batch.slots), _ptr(batch.q_start),
                                                _ptr(batch.ctx_len), _ptr(batch.gdn_defer), B, hk, hv, dk, dv, self.GDN_CHUNK_MIN,

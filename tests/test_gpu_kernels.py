@@ -648,7 +648,7 @@ def test_gdn_layer(ops):
 @pytest.mark.parametrize("decay_scale", [1.0, 0.1])
 def test_gdn_chunked_kernel_matches_the_recurrence(ops, decay_scale):
     """The chunked tensor-core form of the gated delta rule (128-token chunks, WY / UT transform, state carried in tensor
-    memory) against the token-by-token kernel on the same inputs: 4096-token and ragged prompts, then a second step that
+    memory), as one fused kernel and as chunk-parallel preparation + sequential scan, against the token-by-token kernel on the same inputs: 4096-token and ragged prompts, then a second step that
     starts from the state the first one left (a 300-token continuation next to a decode row), outputs and final states."""
     from blaze_b200.batch import SeqChunk, build_batch
     from blaze_b200.config import named_config
@@ -674,10 +674,10 @@ def test_gdn_chunked_kernel_matches_the_recurrence(ops, decay_scale):
     m.cfg, m.gdn_chunked = cfg, False
     steps = ([4096, 200, 5, 129], [300, 64, 1, 128])
     outs = {}
-    keep = ops.GDN_CHUNK_MIN
+    keep = ops.GDN_CHUNK_MIN, ops.GDN_SPLIT
     try:
-        for name, chunk_min in (("chunked", 64), ("recurrent", 0)):
-            ops.GDN_CHUNK_MIN = chunk_min
+        for name, chunk_min, split in (("chunked", 64, False), ("split", 64, True), ("recurrent", 0, False)):
+            ops.GDN_CHUNK_MIN, ops.GDN_SPLIT = chunk_min, split
             kv = KVCache(cfg, 4, 4, 320, "bf16", DEV, "logical")
             gi = torch.Generator(device=DEV).manual_seed(44)
             res = []
@@ -691,19 +691,20 @@ def test_gdn_chunked_kernel_matches_the_recurrence(ops, decay_scale):
                 aa = torch.randn(T, hv, generator=gi, device=DEV).bfloat16()
                 l0 = ops.launches
                 res.append(ops.gdn(mixed, z, bb, aa, gd, m, batch, kv, 0).float())
-                if name == "chunked":
-                    assert ops.launches - l0 == 4          # conv, chunked rule, token-by-token rule for the short rows, gated norm
+                if name != "recurrent":
+                    # conv, chunked rule (one kernel, or preparation + scan), token-by-token rule for the short rows, gated norm
+                    assert ops.launches - l0 == (5 if split else 4)
             outs[name] = (torch.cat(res), kv.rec_state[0].clone())
     finally:
-        ops.GDN_CHUNK_MIN = keep
+        ops.GDN_CHUNK_MIN, ops.GDN_SPLIT = keep
     torch.cuda.synchronize()
     assert ops.take_status() == 0
-    assert torch.isfinite(outs["chunked"][0]).all()
-    _, rel = _report(f"gdn chunked vs recurrent, output (decay x{decay_scale})", outs["chunked"][0], outs["recurrent"][0])
-    assert rel < 0.02
-    st_c, st_r = outs["chunked"][1], outs["recurrent"][1]
-    _, rel = _report("gdn chunked vs recurrent, final state", st_c, st_r)
-    assert rel < 0.02
+    for name in ("chunked", "split"):
+        assert torch.isfinite(outs[name][0]).all()
+        _, rel = _report(f"gdn {name} vs recurrent, output (decay x{decay_scale})", outs[name][0], outs["recurrent"][0])
+        assert rel < 0.02
+        _, rel = _report(f"gdn {name} vs recurrent, final state", outs[name][1], outs["recurrent"][1])
+        assert rel < 0.02
 
 
 def test_host_kv_tier_roundtrip_on_device():
