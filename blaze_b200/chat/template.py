@@ -83,12 +83,25 @@ def normalize_messages(messages: List[Dict[str, Any]], family: str = "chatml", f
     return out
 
 
+THINK_OPENERS = ("<think>", "<think>\n", "<|open|>think<|sep|>")
+
+
 class ChatFormatter:
+    """Prompt renderer of one checkpoint.  ``encoder`` names a family request encoder: "deepseek_v4", "deepseek_v41" and
+    "kimi_k3" build the prompt without a template; "glm53" and "qwen38" (recognised from the template text) prepare the
+    request for the checkpoint's template.  Without one, ``render`` runs the template (or the built-in family layout) on
+    the messages as given."""
+
     def __init__(self, chat_template: Optional[str] = None, bos_token: str = "", eos_token: str = "<|im_end|>",
-                 family: str = "chatml"):
+                 family: str = "chatml", encoder: Optional[str] = None, effort_profile: str = "preview"):
         if family not in FAMILIES:
             raise ValueError(f"unknown chat family {family!r}")
         self.family = family
+        self.encoder, self.effort_profile = encoder, effort_profile
+        if encoder is None and chat_template:
+            from . import templated
+            self.encoder = ("glm53" if templated.is_glm53(chat_template) else
+                            "qwen38" if templated.is_qwen38(chat_template) else None)
         self.template_src = chat_template
         self.bos_token, self.eos_token = bos_token, eos_token
         self._tpl = None
@@ -98,13 +111,68 @@ class ChatFormatter:
             def raise_exception(msg):
                 raise ValueError(msg)
 
-            def tojson(v, ensure_ascii=False, indent=None):
-                return json.dumps(v, ensure_ascii=ensure_ascii, indent=indent)
+            def tojson(v, ensure_ascii=False, indent=None, separators=None, sort_keys=False):
+                return json.dumps(v, ensure_ascii=ensure_ascii, indent=indent, separators=separators, sort_keys=sort_keys)
 
-            env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
+            def strftime_now(fmt):
+                import datetime
+                return datetime.datetime.now().strftime(fmt)
+
+            env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, extensions=["jinja2.ext.loopcontrols"])
             env.globals["raise_exception"] = raise_exception
+            env.globals["strftime_now"] = strftime_now
             env.filters["tojson"] = tojson
             self._tpl = env.from_string(chat_template)
+
+    def render_prepared(self, messages: List[Dict[str, Any]], tools: Optional[List[Dict[str, Any]]], args: Dict[str, Any],
+                        add_generation_prompt: bool = True) -> str:
+        """Run the template on messages a family encoder has already prepared (no normalisation here)."""
+        if self._tpl is None:
+            raise ValueError("the checkpoint has no chat template")
+        ctx = dict(bos_token=self.bos_token, eos_token=self.eos_token)
+        ctx.update(args)
+        ctx.update(messages=messages, tools=tools, add_generation_prompt=add_generation_prompt)
+        from jinja2.exceptions import TemplateError
+        try:
+            return self._tpl.render(**ctx)
+        except TemplateError as e:
+            raise ValueError(f"chat template error: {e}")
+
+    @classmethod
+    def for_checkpoint(cls, model_name: str, config: Optional[Dict[str, Any]], chat_template: Optional[str] = None,
+                       family: Optional[str] = None, bos_token: str = "", eos_token: str = "<|im_end|>") -> "ChatFormatter":
+        """The formatter a checkpoint gets from its name, ``config.json`` fields and template
+        (``crates/blaze-chat/src/render/selection.rs``)."""
+        from .families import encoder_of
+        config = config or {}
+        return cls(chat_template, bos_token, eos_token, family or family_of(model_name), encoder_of(model_name, config),
+                   str(config.get("dsv4_reasoning_effort_profile") or "preview"))
+
+    def render_request(self, request: Dict[str, Any], defaults: Optional[Dict[str, Any]] = None):
+        """``(prompt, continuation prefix, thinking)`` of a chat-completions request body.  ``prefix`` is the text of a final
+        assistant turn to continue (tokenised on its own after the prompt); ``thinking`` says whether the prompt leaves the
+        model inside its reasoning channel.  ``defaults`` are server-side template arguments a request may override."""
+        if self.encoder in ("deepseek_v4", "deepseek_v41"):
+            from . import deepseek
+            prompt, prefix = deepseek.render_request(request, defaults, self.encoder == "deepseek_v41", self.effort_profile)
+        elif self.encoder == "kimi_k3":
+            from . import kimi
+            prompt, prefix = kimi.render_request(request, defaults)
+        elif self.encoder in ("glm53", "qwen38"):
+            from . import templated
+            prompt, prefix = templated.render_request(self, request, defaults, self.encoder)
+        else:
+            tools = request.get("tools")
+            if request.get("tool_choice", "auto" if tools else "none") == "none":
+                tools = None
+            kw = dict(defaults or {})
+            kw.update(request.get("chat_template_kwargs") or {})
+            think = kw.pop("enable_thinking", request.get("enable_thinking"))
+            for k in ("messages", "tools", "add_generation_prompt"):
+                kw.pop(k, None)
+            prompt = self.render(request.get("messages") or [], tools, bool(request.get("add_generation_prompt", True)), think, **kw)
+            return prompt, "", think
+        return prompt, prefix, prompt.endswith(THINK_OPENERS) and not prefix
 
     def render(self, messages: List[Dict[str, Any]], tools: Optional[List[Dict[str, Any]]] = None,
                add_generation_prompt: bool = True, enable_thinking: Optional[bool] = None, **kwargs) -> str:
@@ -115,7 +183,11 @@ class ChatFormatter:
                        bos_token=self.bos_token, eos_token=self.eos_token, **kwargs)
             if enable_thinking is not None:
                 ctx["enable_thinking"] = enable_thinking
-            return self._tpl.render(**ctx)
+            from jinja2.exceptions import TemplateError
+            try:
+                return self._tpl.render(**ctx)
+            except TemplateError as e:
+                raise ValueError(f"chat template error: {e}")
         builtin = {"chatml": self._chatml, "deepseek": self._deepseek, "glm": self._glm, "kimi": self._kimi}[self.family]
         return builtin(messages, tools, add_generation_prompt, enable_thinking)
 

@@ -89,6 +89,8 @@ def service_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--tool-call-parser", default="hermes")
     g.add_argument("--reasoning-parser", default="qwen3")
     g.add_argument("--chat-family", default=None, choices=["chatml", "deepseek", "glm", "kimi"])
+    g.add_argument("--chat-template-kwargs", default=None, metavar="JSON",
+                   help="default template arguments (e.g. '{\"thinking\": true}'); a request's chat_template_kwargs override them")
 
 
 def build_parser() -> argparse.ArgumentParser:

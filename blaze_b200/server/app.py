@@ -71,8 +71,10 @@ class ServerState:
 
     def attach(self, llm, tokenizer, vision=None) -> None:
         self.tokenizer = tokenizer
-        self.formatter = ChatFormatter(getattr(tokenizer, "chat_template", None), family=self.svc.chat_family or "chatml")
         cfg = llm.model.cfg
+        self.formatter = ChatFormatter.for_checkpoint(
+            self.model_name, {"model_type": cfg.model_type, "architectures": [cfg.architecture]},
+            getattr(tokenizer, "chat_template", None), self.svc.chat_family or None)
         eos = tuple(llm.sched.cfg.eos_ids) or tuple(getattr(tokenizer, "eos_ids", ()))
         llm.sched.cfg.eos_ids = eos
         self.grammars = Grammars.load(tokenizer, cfg.vocab_size, eos)
@@ -385,12 +387,7 @@ def create_app(st: ServerState) -> FastAPI:
         b = await _body(request)
         if "messages" in b:
             # what a chat request with the same body would use as its prompt (tools, tool_choice, template arguments)
-            tools = b.get("tools")
-            if b.get("tool_choice", "auto" if tools else "none") == "none":
-                tools = None
-            ctk = b.get("chat_template_kwargs") or {}
-            text = st.formatter.render(b["messages"], tools, b.get("add_generation_prompt", True),
-                                       ctk.get("enable_thinking", b.get("enable_thinking")))
+            text = _render_chat(b)[0]
         else:
             text = b.get("prompt", b.get("text"))
         if not isinstance(text, str):
@@ -432,9 +429,10 @@ def create_app(st: ServerState) -> FastAPI:
             return None
         return ThinkBudget(budget, o, c, st.tokenizer.encode(THINK_CLOSING))
 
-    def _think_parser(st):
-        """Reasoning splitter of the configured family (None when reasoning parsing is off)."""
-        return get_think_parser(st.svc.reasoning_parser) if st.svc.reasoning_parser else None
+    def _think_parser(st, in_think: Optional[bool] = None):
+        """Reasoning splitter of the configured family (None when reasoning parsing is off).  ``in_think``: the prompt
+        ended inside the reasoning channel (None: the family's default)."""
+        return get_think_parser(st.svc.reasoning_parser, starts_in_think=in_think) if st.svc.reasoning_parser else None
 
     def _cache_point(prompt_ids: List[int]) -> Optional[int]:
         """Prefix-cache boundary: the last ``<|im_start|>`` (``server.rs:926-933``)."""
@@ -458,6 +456,14 @@ def create_app(st: ServerState) -> FastAPI:
     def _sse(obj) -> bytes:
         return ("data: " + json.dumps(obj, ensure_ascii=False, separators=(",", ":")) + "\n\n").encode()
 
+    def _render_chat(b: Dict[str, Any]):
+        """(prompt text, continuation prefix, thinking) of a chat request body; request errors of the family encoders
+        become 400s."""
+        try:
+            return st.formatter.render_request(b, st.svc.chat_template_kwargs)
+        except (ValueError, TypeError, IndexError, KeyError) as e:
+            raise RequestError(f"cannot render the chat prompt: {e}", "messages")
+
     # ------------------------------------------------------------------ /v1/chat/completions
     async def _prepare_chat(b: Dict[str, Any]):
         _check_model(b)
@@ -470,10 +476,10 @@ def create_app(st: ServerState) -> FastAPI:
             tools_for_prompt = None
         else:
             tools_for_prompt = tools
-        ctk = b.get("chat_template_kwargs") or {}
-        enable_thinking = ctk.get("enable_thinking", b.get("enable_thinking"))
-        text = st.formatter.render(msgs, tools_for_prompt, True, enable_thinking)
+        text, prefix, enable_thinking = _render_chat(b)
         ids = st.tokenizer.encode(text)
+        if prefix:
+            ids = ids + st.tokenizer.encode(prefix, add_special_tokens=False)      # the continued turn is tokenised on its own
         mm = None
         if st.vision is not None:
             from .media import collect_images
@@ -481,12 +487,13 @@ def create_app(st: ServerState) -> FastAPI:
         params = sampling_of(b, st.svc, st.vocab)
         _check_len(len(ids), params)
         spec = grammar_of(b)
-        return ids, params, tools_for_prompt, enable_thinking, spec, mm
+        in_think = text.rstrip("\n").endswith(("<think>", "<|open|>think<|sep|>")) and not prefix
+        return ids, params, tools_for_prompt, enable_thinking, spec, mm, in_think
 
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
         b = await _body(request)
-        ids, params, tools, enable_thinking, spec, mm = await _prepare_chat(b)
+        ids, params, tools, enable_thinking, spec, mm, in_think = await _prepare_chat(b)
         stops = stop_strings_of(b)
         include_stop = bool(b.get("include_stop_str_in_output", b.get("no_stop_trim", False)))
         skip_special = bool(b.get("skip_special_tokens", True))
@@ -502,7 +509,7 @@ def create_app(st: ServerState) -> FastAPI:
             g = Gen(st, ids, p, cache_point=_cache_point(ids), constraint=cons, think=_think(b, enable_thinking), mm=mm)
             proc = ChatResponseProcessor(st.tokenizer, stops, include_stop, skip_special, reasoning=reasoning,
                                          tool_parser=get_tool_parser(st.svc.tool_call_parser, tools) if tools else None,
-                                         think_parser=_think_parser(st))
+                                         think_parser=_think_parser(st, in_think))
             return g, proc
         gens = [make(i) for i in range(n)]
 
@@ -783,13 +790,13 @@ def create_app(st: ServerState) -> FastAPI:
         tf = (b.get("text") or {}).get("format")
         if isinstance(tf, dict) and tf.get("type") in ("json_schema", "json_object"):
             cb["response_format"] = {"type": tf["type"], "json_schema": {"schema": tf.get("schema", {})}}
-        ids, params, tools_p, enable_thinking, spec, mm = await _prepare_chat(cb)
+        ids, params, tools_p, enable_thinking, spec, mm, in_think = await _prepare_chat(cb)
         rid, created = "resp_" + uuid.uuid4().hex[:24], int(time.time())
         cons = st.grammars.constraint(spec) if spec else None
         g = Gen(st, ids, params, cache_point=_cache_point(ids), constraint=cons, mm=mm)
         proc = ChatResponseProcessor(st.tokenizer, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
                                      tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None,
-                                     think_parser=_think_parser(st))
+                                     think_parser=_think_parser(st, in_think))
         stream = bool(b.get("stream", False))
 
         def build(status: str) -> Dict[str, Any]:
@@ -920,14 +927,16 @@ def create_app(st: ServerState) -> FastAPI:
                 out["thinking_token_budget"] = th["budget_tokens"]
         elif th.get("type") == "disabled":
             out["enable_thinking"] = False
+        if "enable_thinking" in out:       # the families' templates read one of the two names
+            out["chat_template_kwargs"] = {"enable_thinking": out["enable_thinking"], "thinking": out["enable_thinking"]}
         return out
 
     @app.post("/v1/messages/count_tokens")
     async def count_tokens(request: Request):
         b = await _body(request)
         cb = _anthropic_to_chat(b)
-        text = st.formatter.render(cb["messages"], cb.get("tools"), True)
-        return {"input_tokens": len(st.tokenizer.encode(text))}
+        text, prefix, _ = _render_chat(cb)
+        return {"input_tokens": len(st.tokenizer.encode(text)) + (len(st.tokenizer.encode(prefix, add_special_tokens=False)) if prefix else 0)}
 
     @app.post("/v1/messages")
     async def messages(request: Request):
@@ -935,13 +944,13 @@ def create_app(st: ServerState) -> FastAPI:
         if not isinstance(b.get("max_tokens"), int):
             raise RequestError("max_tokens is required", "max_tokens")
         cb = _anthropic_to_chat(b)
-        ids, params, tools_p, enable_thinking, spec, mm = await _prepare_chat(cb)
+        ids, params, tools_p, enable_thinking, spec, mm, in_think = await _prepare_chat(cb)
         stops = stop_strings_of(cb)
         mid = "msg_" + uuid.uuid4().hex[:24]
         g = Gen(st, ids, params, cache_point=_cache_point(ids), mm=mm)
         proc = ChatResponseProcessor(st.tokenizer, stops, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
                                      tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None,
-                                     think_parser=_think_parser(st))
+                                     think_parser=_think_parser(st, in_think))
 
         def stop_reason():
             if proc.tool_calls:

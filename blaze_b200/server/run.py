@@ -18,7 +18,21 @@ def service_args_of(ns) -> ServiceArgs:
                        profile_prefill=ns.profile_prefill, generation_config=ns.generation_config, samplers=ns.samplers,
                        top_nsigma=ns.top_nsigma, top_h=ns.top_h, tool_call_parser=ns.tool_call_parser,
                        reasoning_parser=ns.reasoning_parser or None,
-                       chat_family=getattr(ns, "chat_family", None))
+                       chat_family=getattr(ns, "chat_family", None),
+                       chat_template_kwargs=_json_object(getattr(ns, "chat_template_kwargs", None), "--chat-template-kwargs"))
+
+
+def _json_object(text, flag):
+    if not text:
+        return {}
+    import json
+    try:
+        v = json.loads(text)
+    except ValueError as e:
+        raise SystemExit(f"{flag}: not JSON ({e})")
+    if not isinstance(v, dict):
+        raise SystemExit(f"{flag}: expected a JSON object")
+    return v
 
 
 def serve(ns) -> int:

@@ -49,6 +49,7 @@ class ServiceArgs:
     tool_call_parser: str = "hermes"
     reasoning_parser: Optional[str] = "qwen3"
     chat_family: Optional[str] = None            # built-in renderer + message normalisation: chatml, deepseek, glm, kimi
+    chat_template_kwargs: Dict[str, Any] = field(default_factory=dict)    # template arguments a request may override
     cors_origins: Tuple[str, ...] = ("*",)
     defaults: Dict[str, Any] = field(default_factory=dict)
 
