@@ -74,13 +74,16 @@ class ToolParser:
                 self.inside = False
                 continue
             i = self.buf.find(self.OPEN)
+            keep = not (self.DROP_TEXT_AFTER_CALLS and self.calls)
             if i >= 0:
-                content += self.buf[:i].rstrip("\n") if not self.buf[:i].strip() else self.buf[:i]
+                if keep:
+                    content += self.buf[:i].rstrip("\n") if not self.buf[:i].strip() else self.buf[:i]
                 self.buf = self.buf[i + len(self.OPEN):]
                 self.inside = True
                 continue
             h = self._hold(self.OPEN)
-            content += self.buf[:len(self.buf) - h]
+            if keep:
+                content += self.buf[:len(self.buf) - h]
             self.buf = self.buf[len(self.buf) - h:]
             break
         return content, done
@@ -92,7 +95,9 @@ class ToolParser:
             self.calls.extend(calls)
             return "", calls
         out, self.buf = self.buf, ""
-        return out, []
+        return ("" if self.DROP_TEXT_AFTER_CALLS and self.calls else out), []
+
+    DROP_TEXT_AFTER_CALLS = False        # families whose answer text ends where the first call begins
 
 
 class HermesToolParser(ToolParser):
@@ -115,43 +120,135 @@ class HermesToolParser(ToolParser):
         return ToolCall(name, args if isinstance(args, str) else json.dumps(args, ensure_ascii=False))
 
 
+def _schema_kind(spec: Any) -> Optional[str]:
+    """The JSON type a parameter's schema asks for: its ``type`` (the first one that is not "null" of a list), the first
+    typed alternative of ``anyOf`` / ``oneOf``, a non-string member of ``allOf``, "enum" for an enumeration, and object /
+    array where only ``properties`` / ``items`` say so."""
+    if not isinstance(spec, dict):
+        return None
+    t = spec.get("type")
+    if isinstance(t, list):
+        t = next((x for x in t if x != "null"), t[0] if t else None)
+    if isinstance(t, str):
+        return t.strip().lower()
+    for key in ("anyOf", "oneOf"):
+        for alt in spec.get(key) or []:
+            k = _schema_kind(alt)
+            if k and k != "null":
+                return k
+    kinds = [k for k in (_schema_kind(a) for a in spec.get("allOf") or []) if k]
+    if kinds:
+        return next((k for k in kinds if k not in ("string", "null")), kinds[0])
+    if "enum" in spec:
+        return "enum"
+    if "properties" in spec:
+        return "object"
+    if "items" in spec:
+        return "array"
+    return None
+
+
+def _typed_value(raw: str, spec: Any) -> Any:
+    """A parameter's text as the value its schema asks for (``_schema_kind``); text that does not read as that type stays
+    a string.  Integers and numbers read as Python does (underscores, any Unicode digits, inf / nan); a number written
+    without a point or exponent becomes an integer; objects, arrays and untyped values read as JSON, then as a Python
+    literal (single quotes, tuples, None / True / False)."""
+    import ast
+    if raw.lower() == "null":
+        return None
+    kind = _schema_kind(spec)
+    if kind is None or kind in ("string", "str", "text", "varchar", "char"):
+        return raw
+    if kind == "enum":
+        try:
+            v = json.loads(raw)
+        except ValueError:
+            return raw
+        return v if any(v == e and type(v) is type(e) for e in spec["enum"]) else raw
+    if kind.startswith(("int", "uint", "long", "short", "unsigned")):
+        try:
+            return int(raw)
+        except ValueError:
+            return raw
+    if kind.startswith(("num", "float", "double")):
+        try:
+            f = float(raw)
+        except ValueError:
+            return raw
+        whole = "." not in raw and "e" not in raw.lower()
+        return int(f) if whole and f == f and f not in (float("inf"), float("-inf")) and f.is_integer() else f
+    if kind in ("boolean", "bool", "binary"):
+        return raw.lower() == "true"
+    depth = deepest = 0
+    for ch in raw:
+        if ch in "[({":
+            depth += 1
+            deepest = max(deepest, depth)
+        elif ch in "])}":
+            depth -= 1
+    if deepest > 200:                    # nesting beyond what a literal may have
+        return raw
+    if kind in ("object", "array", "dict", "list", "arr", "map"):
+        try:
+            return json.loads(raw)
+        except (ValueError, RecursionError):
+            pass
+    try:
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")      # odd escapes in the text are not this process's concern
+            v = ast.literal_eval(raw)
+        json.dumps(v)                    # sets, bytes, complex numbers have no JSON form
+        return v
+    except (ValueError, SyntaxError, TypeError, MemoryError, RecursionError):
+        return raw
+
+
 class Qwen3CoderToolParser(ToolParser):
-    FN = re.compile(r"<function=([^>\s]+)>(.*?)(?:</function>|$)", re.S)
-    PARAM = re.compile(r"<parameter=([^>\s]+)>(.*?)(?:</parameter>|(?=<parameter=)|$)", re.S)
+    """``<tool_call>`` around one or more ``<function=name>`` elements with ``<parameter=key>`` children; values are typed
+    by the request's tool schemas (``_typed_value``)."""
+    DROP_TEXT_AFTER_CALLS = True
+    FN = re.compile(r"<function=([^>\s]+)>(.*?)(?:</function>|(?=<function=)|$)", re.S)
+    PARAM = re.compile(r"<parameter=([^>]+)>(.*?)(?:</parameter>|(?=<parameter=)|$)", re.S)
 
     def _schema(self, fn: str) -> Dict[str, Any]:
         for t in self.tools:
             f = t.get("function", t)
             if f.get("name") == fn:
-                return (f.get("parameters") or {}).get("properties") or {}
+                params = f.get("parameters")
+                if not isinstance(params, dict):
+                    return {}
+                if isinstance(params.get("properties"), dict):
+                    return params["properties"]
+                merged: Dict[str, Any] = {}
+                for alt in (params.get("anyOf") or []) + (params.get("oneOf") or []):     # first alternative that has the key
+                    for k, v in ((alt.get("properties") or {}) if isinstance(alt, dict) else {}).items():
+                        merged.setdefault(k, v)
+                return merged or params
         return {}
 
-    def parse_body(self, body: str) -> Optional[ToolCall]:
-        m = self.FN.search(body)
-        if not m:
-            return None
-        name, inner = m.group(1), m.group(2)
-        props = self._schema(name)
-        args: Dict[str, Any] = {}
-        for pm in self.PARAM.finditer(inner):
-            key, raw = pm.group(1), pm.group(2)
-            raw = raw[1:] if raw.startswith("\n") else raw
-            raw = raw[:-1] if raw.endswith("\n") else raw
-            typ = (props.get(key) or {}).get("type", "string")
-            val: Any = raw
-            if typ in ("integer", "number", "boolean", "object", "array", "null") or typ != "string":
-                try:
-                    val = json.loads(raw)
-                except ValueError:
-                    low = raw.strip().lower()
-                    val = True if low == "true" else False if low == "false" else raw
-            args[key] = val
-        return ToolCall(name, json.dumps(args, ensure_ascii=False))
+    def parse_body(self, body: str):
+        out = []
+        for m in self.FN.finditer(body):
+            name, inner = m.group(1), m.group(2)
+            props = self._schema(name)
+            args: Dict[str, Any] = {}
+            for pm in self.PARAM.finditer(inner):
+                key, raw = pm.group(1), pm.group(2)
+                raw = raw[1:] if raw.startswith("\n") else raw
+                raw = raw[:-1] if raw.endswith("\n") else raw
+                args[key] = _typed_value(raw, props.get(key))
+            out.append(ToolCall(name, json.dumps(args, ensure_ascii=False)))
+        return out
 
 
 class DsmlToolParser(ToolParser):
-    """DeepSeek's DSML block.  ``strip_strings`` trims string values (the first tag set); the second tag set
-    (names that start with a space: ``｜DSML｜ calls``) keeps them as written."""
+    """DeepSeek's DSML calls: ``<｜DSML｜tool_calls>`` around ``<｜DSML｜invoke name="...">`` elements whose arguments are
+    ``<｜DSML｜parameter name="..." string="true|false">`` children (``string="false"`` values are JSON) or one JSON object
+    as the element's text.  V4.1 spells the tags with a space (``｜DSML｜ calls``, ``｜DSML｜ invoke``).  Text before the
+    first call is the answer (trailing white space dropped once a call follows); text after the calls is dropped; a bare
+    invoke without the wrapper counts; an invoke with a malformed parameter is dropped.  ``parse`` (whole output) keeps only
+    calls to the request's tools, the stream keeps all (the caller validates names)."""
     MARK = "｜DSML｜"
 
     def __init__(self, tools=None, spaced: bool = False):
@@ -159,19 +256,82 @@ class DsmlToolParser(ToolParser):
         block, inv, par = (" calls", " invoke", " parameter") if spaced else ("tool_calls", "invoke", "parameter")
         m = re.escape(self.MARK)
         self.OPEN, self.CLOSE = f"<{self.MARK}{block}>", f"</{self.MARK}{block}>"
-        self.strip_strings = not spaced
-        self.INVOKE = re.compile(rf'<{m}{re.escape(inv)}\s+name="([^"]+)"\s*(?:/>|>(.*?)(?:</{m}{re.escape(inv)}>|$))', re.S)
-        self.PARAM = re.compile(rf'<{m}{re.escape(par)}\s+name="([^"]+)"\s+string="([^"]+)"\s*>(.*?)</{m}{re.escape(par)}>', re.S)
+        self.INV_OPEN = f"<{self.MARK}{inv}"
+        self.INVOKE = re.compile(rf'<{m}{re.escape(inv)}\s+name="([^"]+)"\s*(?:/>|>(.*?)</{m}{re.escape(inv)}>)', re.S)
+        self.PARAM = re.compile(rf'<{m}{re.escape(par)}\s+name="([^"]+)"\s+string="(true|false)"\s*>(.*?)</{m}{re.escape(par)}>', re.S)
+        self.ANY_PARAM = f"<{self.MARK}{par}"
+        self.names = {(t.get("function") or t).get("name") for t in self.tools if isinstance(t, dict)}
+        self.started = False            # a call marker was seen: the answer text is over
+        self.space = ""                 # trailing white space of the answer, held until more text or a call follows
 
-    def parse_body(self, body: str):
-        out = []
-        for m in self.INVOKE.finditer(body):
-            args: Dict[str, Any] = {}
-            for pm in self.PARAM.finditer(m.group(2) or ""):
-                key, is_str, raw = pm.group(1), pm.group(2) == "true", pm.group(3)
-                args[key] = (raw.strip() if self.strip_strings else raw) if is_str else _json_or_text(raw.strip())
-            out.append(ToolCall(m.group(1), json.dumps(args, ensure_ascii=False)))
-        return out
+    def _call_of(self, m, verbatim: bool) -> Optional[ToolCall]:
+        body = m.group(2) or ""
+        params = self.PARAM.findall(body)
+        if body.count(self.ANY_PARAM) != len(params):
+            return None                 # a parameter without the string attribute, or cut
+        if not params and body.strip().startswith("{"):
+            try:
+                obj = json.loads(body.strip())
+            except ValueError:
+                return None
+            if not isinstance(obj, dict):
+                return None
+            return ToolCall(m.group(1), body.strip() if verbatim else json.dumps(obj, ensure_ascii=False))
+        args: Dict[str, Any] = {}
+        for key, is_str, raw in params:
+            args[key] = raw if is_str == "true" else _json_or_text(raw.strip())
+        return ToolCall(m.group(1), json.dumps(args, ensure_ascii=False))
+
+    def _first_marker(self, text: str) -> int:
+        found = [i for i in (text.find(self.OPEN), text.find(self.INV_OPEN)) if i >= 0]
+        return min(found) if found else -1
+
+    def parse(self, text: str) -> Tuple[str, List[ToolCall]]:
+        """The whole output at once."""
+        i = self._first_marker(text)
+        if i < 0:
+            return text, []
+        calls = [c for c in (self._call_of(m, False) for m in self.INVOKE.finditer(text, i)) if c is not None]
+        return text[:i].strip(), [c for c in calls if not self.names or c.name in self.names]
+
+    def push(self, text: str) -> Tuple[str, List[ToolCall]]:
+        self.buf += text
+        content, done = "", []
+        if not self.started:
+            i = self._first_marker(self.buf)
+            if i >= 0:
+                content, self.buf, self.started, self.space = self.space + self.buf[:i], self.buf[i:], True, ""
+                content = content.rstrip()
+            else:
+                hold = max(_partial_tail(self.buf, self.OPEN), _partial_tail(self.buf, self.INV_OPEN))
+                out, self.buf = self.space + self.buf[:len(self.buf) - hold], self.buf[len(self.buf) - hold:]
+                kept = out.rstrip()
+                content, self.space = kept, out[len(kept):]
+                return content, done
+        while True:
+            m = self.INVOKE.search(self.buf)
+            if m is None:
+                break
+            call = self._call_of(m, True)
+            if call is not None:
+                done.append(call)
+                self.calls.append(call)
+            self.buf = self.buf[m.end():]
+        return content, done
+
+    def flush(self) -> Tuple[str, List[ToolCall]]:
+        out, self.buf = self.buf, ""
+        if self.started:
+            return "", []               # a cut call, or text after the calls
+        out, self.space = self.space + out, ""
+        return out, []
+
+
+def _partial_tail(text: str, marker: str) -> int:
+    for k in range(min(len(marker) - 1, len(text)), 0, -1):
+        if text.endswith(marker[:k]):
+            return k
+    return 0
 
 
 class KimiToolParser(ToolParser):
@@ -227,25 +387,55 @@ class KimiToolParser(ToolParser):
             text = text.replace(w, "")
         return text
 
+    def parse(self, text: str):
+        """The whole output at once: without a tools channel the text is returned as it is; with one, the answer is the
+        response channel's text before it and the calls are those of the first channel."""
+        from .reasoning import _k_unwrap
+        i = text.find(self.OPEN)
+        if i < 0:
+            return text, []
+        body = text[i + len(self.OPEN):]
+        j = body.find(self.CLOSE)
+        return _k_unwrap(text[:i]), _as_list(self.parse_body(body if j < 0 else body[:j]))
+
     def push(self, text: str):
-        content, calls = super().push(text)
-        # a wrapper marker cut by the delta boundary stays in the buffer until it is whole
-        content = self._held + content
-        keep = 0
-        for w in self.WRAPPERS:
-            for k in range(min(len(w) - 1, len(content)), keep, -1):
-                if content.endswith(w[:k]):
-                    keep = k
+        self.buf += text
+        content, done = "", []
+        while self.buf:
+            if self.inside:
+                i = self.buf.find(self.CLOSE)
+                if i < 0:
                     break
-        self._held = content[len(content) - keep:] if keep else ""
-        return self._unwrap(content[:len(content) - keep] if keep else content), calls
+                calls = _as_list(self.parse_body(self.buf[:i]))
+                done.extend(calls)
+                self.calls.extend(calls)
+                self.buf, self.inside, self.after = self.buf[i + len(self.CLOSE):], False, True
+                continue
+            i = self.buf.find(self.OPEN)
+            if i >= 0:
+                if not self.after:
+                    content += self.buf[:i]
+                self.buf, self.inside = self.buf[i + len(self.OPEN):], True
+                continue
+            # a marker cut by the delta boundary stays in the buffer until it is whole
+            hold = max(_partial_tail(self.buf, m) for m in (self.OPEN,) + self.WRAPPERS)
+            if not self.after:
+                content += self.buf[:len(self.buf) - hold]
+            self.buf = self.buf[len(self.buf) - hold:]
+            break
+        return self._unwrap(content), done
 
     def flush(self):
-        content, calls = super().flush()
-        content, self._held = self._held + content, ""
-        return self._unwrap(content), calls
+        from .reasoning import _k_strip_cut
+        out, self.buf = self.buf, ""
+        if self.inside:                  # the channel was never closed: the calls that are whole still count
+            self.inside = False
+            calls = _as_list(self.parse_body(out))
+            self.calls.extend(calls)
+            return "", calls
+        return ("" if self.after else _k_strip_cut(self._unwrap(out))), []
 
-    _held = ""
+    after = False                        # a tools channel has closed: later text is not part of the answer
 
 
 class GlmToolParser(ToolParser):
