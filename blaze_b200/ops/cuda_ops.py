@@ -759,7 +759,8 @@ class CudaOps:
             self._moe_gemm(dn, act, max_tiles, tile_expert, tile_rows, n_exp, y)
         else:
             self._grouped_gemm(gu, a, M_pad, tile_expert, n_exp, g)
-            act = self.silu_mul(g, quant_for=proxy_d if dn["kind"] in (1, 2) else None)
+            # only the routed rows: the padded row space is up to (1 + experts * 128 / routed rows) times larger
+            act = self._silu_mul_live(g, proxy_d if dn["kind"] in (1, 2) else None, row_map)
             self._grouped_gemm(dn, act, M_pad, tile_expert, n_exp, y)
         out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         self._check(self.lib.blz_moe_combine(_ptr(y), _ptr(topk_w.contiguous()), _ptr(row_map), _ptr(out), T, H, k, self._stream()),

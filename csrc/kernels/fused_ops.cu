@@ -409,6 +409,61 @@ __global__ void __launch_bounds__(512) swiglu_reg_kernel(const __nv_bfloat16* __
   }
 }
 
+// Rows of at most 1024 activations (expert intermediates): several rows per CTA, `tpr` threads each (a multiple of 32, so
+// a warp never spans two rows), instead of one mostly idle 256-thread CTA per row.  Entry r of the launch handles row
+// row_list[r] (or r); -1 and entries beyond n_rows are skipped.
+template <int MODE>
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                                            uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out,
+                                                            float* __restrict__ row_scale, int I, int src_is_act, int sf_col_tiles,
+                                                            const int* __restrict__ row_list, int n_rows, int tpr) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[8];
+  const int sub = threadIdx.x / tpr, in_row = threadIdx.x - sub * tpr;
+  const int r = blockIdx.x * (blockDim.x / tpr) + sub;
+  int t = -1;
+  if (r < n_rows) t = row_list ? row_list[r] : r;
+  const bool live = t >= 0;
+  const int i = in_row * 8;
+  const bool valid = live && i < I;
+  uint4 a = make_uint4(0, 0, 0, 0), b = a;
+  if (valid) {
+    const __nv_bfloat16* g = gu + (size_t)t * (src_is_act ? I : 2 * I);
+    a = *reinterpret_cast<const uint4*>(g + i);
+    if (!src_is_act) b = *reinterpret_cast<const uint4*>(g + I + i);
+  }
+  __nv_bfloat16* eg = reinterpret_cast<__nv_bfloat16*>(&a);
+  const __nv_bfloat16* eu = reinterpret_cast<const __nv_bfloat16*>(&b);
+  float amax = 0.f;
+  if (!src_is_act) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float x = bf2f(eg[j]);
+      eg[j] = __float2bfloat16(x / (1.f + __expf(-x)) * bf2f(eu[j]));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(bf2f(eg[j])));
+  if (MODE == 0) {
+    if (valid) *reinterpret_cast<uint4*>(out + (size_t)t * I + i) = a;
+    return;
+  }
+  float gs = 1.f;
+  if (MODE == 1) {
+    // the row's largest magnitude: over the warp, then over the row's warps
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    float m = 0.f;
+    for (int k = 0; k < (tpr >> 5); ++k) m = fmaxf(m, red[((sub * tpr) >> 5) + k]);
+    gs = fmaxf(m / (6.f * 448.f), 1e-30f);
+    if (live && in_row == 0) row_scale[t] = gs;
+  }
+  quant_store8<MODE>(a, valid, live ? t : 0, i, I, gs, q_out, sf_out, sf_col_tiles);
+}
+
 // ---------------------------------------------------------------------------------------------- attention prep
 // One CTA per token; its warps walk the token's heads.  Heads 0..Hq-1 are query heads, then Hkv key heads, then Hkv
 // value heads.  qkv row layout: [q heads (x2 when gated: q | gate per head)] [k heads] [v heads].  The rotary
@@ -740,6 +795,16 @@ static int swiglu_impl(const void* gu, void* out, void* q_out, void* sf_out, flo
   const size_t sm = (size_t)I * 2;
   const int ct = mode == 1 ? (I + 63) / 64 : (I + 127) / 128;
   configure_once();
+  {
+    const int tpr = (I / 8 + 31) / 32 * 32, rows_per = tpr <= 128 ? 256 / tpr : 1;
+    if (I <= 1024 && rows_per >= 2) {
+      const dim3 grid((T + rows_per - 1) / rows_per), block(rows_per * tpr);
+      if (mode == 0) launch_pdl(swiglu_rows_kernel<0>, grid, block, 0, s, (const bf16*)gu, (bf16*)out, (uint8_t*)nullptr, (uint8_t*)nullptr, (float*)nullptr, I, src_is_act, 0, row_list, T, tpr);
+      else if (mode == 1) launch_pdl(swiglu_rows_kernel<1>, grid, block, 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, row_list, T, tpr);
+      else launch_pdl(swiglu_rows_kernel<2>, grid, block, 0, s, (const bf16*)gu, (bf16*)nullptr, (uint8_t*)q_out, (uint8_t*)sf_out, row_scale, I, src_is_act, ct, row_list, T, tpr);
+      return (int)cudaGetLastError();
+    }
+  }
   int rt, ch;
   reg_shape(I, T, &rt, &ch);
   if (ch) {
