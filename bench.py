@@ -76,9 +76,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the line invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--chunk", type=int, default=0,
-                    help="prompt tokens per prefill step; 0 = 8192 on one GPU (measured, Qwen3-8B NVFP4: 4096 -> 153 k, "
-                         "8192 -> 156 k, 16384 -> 153 k prompt tok/s), 4096 with tensor parallelism (the size its exchange "
-                         "buffers were measured with)")
+                    help="prompt tokens per prefill step; 0 = 8192 on one or two GPUs (measured, Qwen3-8B NVFP4, one GPU: 4096 -> "
+                         "153 k, 8192 -> 158 k, 16384 -> 153 k prompt tok/s; two GPUs: 19.1 -> 20.5 k tok/s end to end), 4096 on "
+                         "more (the size the exchange buffers were measured with there)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--schedule", default="prefill_first", choices=["interleave", "prefill_first"],
                     help="scheduler policy of the end-to-end run (LLM(schedule=...)): prompts first, or decode rows + one chunk per step")
@@ -97,7 +97,7 @@ def main():
                          "(for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.chunk <= 0:
-        args.chunk = 8192 if args.gpus == 1 else 4096
+        args.chunk = 8192 if args.gpus <= 2 else 4096
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
