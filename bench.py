@@ -270,6 +270,7 @@ def main():
             lead = attach(llm, group)
             sync_all()
         a0.record()
+        t_start = time.monotonic()
         if rank == 0:
             outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=out_tokens, ignore_eos=True))
             if lead is not None:
@@ -286,11 +287,17 @@ def main():
         ems = float(t.item())
         n_out = sum(len(o.token_ids) for o in outs)
         nsteps = max(llm.sched.stats.steps - steps0, 1)
-        ttfts = sorted(o.t_first for o in outs)
+        # per-request latencies on rank 0's host clock (when the request's events reached the caller), not histogram edges
+        ttfts = sorted((o.t_first - t_start) * 1e3 for o in outs if o.t_first)
+        tpots = sorted((o.t_done - o.t_first) * 1e3 / (len(o.token_ids) - 1) for o in outs
+                       if o.t_done and o.t_first and len(o.token_ids) > 1)
+
+        def p50(v):
+            return round(v[len(v) // 2], 3) if v else None
         e2e = {"value": n_out / (ems / 1e3), "unit": "output tok/s (prefill + decode, through LLM.generate)",
                "h2d_bytes_per_step": eng.h2d_bytes // nsteps, "d2h_bytes_per_step": eng.d2h_bytes // nsteps,
                "total_ms": ems, "output_tokens": n_out, "steps": nsteps,
-               "ttft_p50_ms": llm.sched.ttft.quantile(0.5) * 1e3, "tpot_p50_ms": llm.sched.tpot.quantile(0.5) * 1e3}
+               "ttft_p50_ms": p50(ttfts), "tpot_p50_ms": p50(tpots), "latency_clock": "host, rank 0, per request"}
         status = status or ops.take_status()
 
     if rank == 0:
