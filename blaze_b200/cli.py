@@ -38,6 +38,9 @@ def engine_parser(p: argparse.ArgumentParser) -> None:
                         "at most every 0.25 s while prompts are waiting")
     g.add_argument("--kv-host-tokens", type=int, default=0,
                    help="pinned host memory behind the prefix cache, in tokens: evicted snapshots wait there (0 = off)")
+    g.add_argument("--expert-heat", default=None, metavar="PATH",
+                   help="mixture-of-experts models: keep per-expert routing statistics in this profile file (loaded at start, "
+                        "written back periodically and at exit; shown by the info route and `inspect --expert-heat`)")
     g.add_argument("--kv-cache-dtype", default=None, choices=["fp8", "bf16", "fp32", "nvfp4", "nvfp4_4over6", "auto"])
     g.add_argument("--kv-host", action="store_true", help="keep cold KV pages in pinned host memory")
     g.add_argument("--kv-rotate", action="store_true", help="randomised Hadamard rotation of q and k rows before the KV write")
@@ -105,8 +108,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prompt-ids", default=None, help="comma-separated token ids")
     g.add_argument("--max-tokens", type=int, default=32)
     g.add_argument("--temperature", type=float, default=0.0)
-    i = sub.add_parser("inspect", help="list checkpoint tensors and their formats")
-    i.add_argument("--model", required=True)
+    i = sub.add_parser("inspect", help="list checkpoint tensors and their formats; with --expert-heat, report a routing profile")
+    i.add_argument("--model", required=True, help="checkpoint directory (or a named shape with --expert-heat)")
+    i.add_argument("--expert-heat", default=None, metavar="PATH", help="routing profile written by a run with --expert-heat")
+    i.add_argument("--ranks", type=int, default=8, help="expert-parallel ranks the placement report is computed for")
     sc = sub.add_parser("score", help="per-token log-probabilities of a token sequence")
     engine_parser(sc)
     sc.add_argument("--prompt-ids", required=True)
@@ -219,7 +224,8 @@ def build_llm(ns: argparse.Namespace):
               kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"), kv_rotate=bool(getattr(ns, "kv_rotate", False)),
               draft_tree_width=int(getattr(ns, "draft_tree_width", 1) or 1),
               tune=bool(getattr(ns, "tune", False)), draft_model=getattr(ns, "draft_model", None), draft_head_vocab=int(getattr(ns, "mtp_head_vocab", 0) or 0),
-              draft_tree_depth=int(ns.draft_tree_depth or 4), max_verify=int(ns.max_verify or 8))
+              draft_tree_depth=int(ns.draft_tree_depth or 4), max_verify=int(ns.max_verify or 8),
+              expert_heat=getattr(ns, "expert_heat", None))
     llm.group = group
     if group is not None:
         from .parallel.worker import attach
@@ -238,6 +244,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if hasattr(ns, "log_level"):
         log.configure(level=ns.log_level, fmt=ns.log_format)
     if ns.command == "inspect":
+        if getattr(ns, "expert_heat", None):
+            from .inspect import inspect_expert_heat
+            return inspect_expert_heat(ns.model, ns.expert_heat, ns.ranks)
         from .inspect import inspect_checkpoint
         return inspect_checkpoint(ns.model)
     if ns.command == "serve":

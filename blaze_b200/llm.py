@@ -45,7 +45,7 @@ class LLM:
                  kv_host_tokens: int = 0, schedule: str = "interleave", kv_rotate: bool = False,
                  draft_tree_width: int = 1, draft_model: Optional[str] = None, draft_head_vocab: int = 0,
                  draft_tree_depth: int = 4, watchdog: bool = False, max_verify: int = 8, tune: bool = False,
-                 stage_layers: Optional[tuple] = None):
+                 stage_layers: Optional[tuple] = None, expert_heat: Union[str, bool, None] = None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -63,6 +63,12 @@ class LLM:
             else:
                 self.model = Model.random_init(named_config(model), fmt, seed, self.device, dtype, tpi, first_layer=lo, last_layer=hi)
         cfg = self.model.cfg
+        self.heat = None
+        if expert_heat:
+            # routing statistics of a mixture-of-experts model: a path keeps the profile across restarts, True keeps it in memory
+            from .expert_heat import attach as attach_heat
+            self.heat = attach_heat(self.model, expert_heat if isinstance(expert_heat, str) else None)
+            self._heat_writer = tpi.rank == 0          # the ranks of a stage see the same routing: one of them writes
         if tune and self.model.ops.is_cuda:
             # time the GEMM kernel variants of this model's layer shapes once per device (cached on disk) and route by the result
             from .tune import tune_model
@@ -91,10 +97,21 @@ class LLM:
                                                         eos_ids=eos, max_model_len=max_model_len,
                                                         max_step_tokens=max_step_tokens, kv_host_pages=kv_host_tokens // 16, schedule=schedule),
                                drafter=drafter)
+        if self.heat is not None:
+            # counters move to the host every 256 steps and the profile is written every 8192, on the scheduler's thread
+            self.sched.housekeeping = ((256, self.heat.fold), (8192, self.save_expert_heat))
         if warm_graphs:
             with log.Stage("graphs"):
                 self.engine.capture_decode_graphs()
         self._n = 0
+
+    def save_expert_heat(self) -> None:
+        """Fold the routing counters collected so far into the profile and write it back (no-op without ``expert_heat``)."""
+        if self.heat is not None:
+            if self.heat.path and self._heat_writer:
+                self.heat.save()
+            else:
+                self.heat.fold()
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  on_event=None) -> List[RequestOutput]:

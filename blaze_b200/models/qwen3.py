@@ -485,7 +485,7 @@ class Model:
             if prof: prof.mark("reduce+norm")
             h, residual = self._reduce_norm(x, residual, kind, L.post_norm, nxt, fused, defer=nxt is not None)
             if prof: prof.mark("mlp")
-            x, kind = self._mlp(L.mlp, h, fused)
+            x, kind = self._mlp(L.mlp, h, fused, gi)
             if _DUMP_DIR and kind == "full" and not (x.is_cuda and torch.cuda.is_current_stream_capturing()):
                 _dump(f"layer{gi:03d}_mlp_out", x)
         if prof:
@@ -598,7 +598,9 @@ class Model:
             ba = torch.stack([b[idx], a[idx]]).contiguous()      # one buffer: the kernels take a common row stride
             self.ops.gdn(mixed[idx].contiguous(), None, ba[0], ba[1], L.gdn, self, batch, kv, gi, state_only=True)
 
-    def _mlp(self, M, h, fused=None):
+    heat = None          # expert_heat.ExpertHeat when routing statistics are collected
+
+    def _mlp(self, M, h, fused=None, layer: int = 0):
         """Returns (output, kind) with kind as in :meth:`forward`."""
         ops = self.ops
         tp = self.tp.world > 1
@@ -611,6 +613,8 @@ class Model:
             w, ids = ops.router_topk(logits, M.top_k, M.renorm, M.experts.first, M.experts.count)
         else:
             w, ids = ops.router_topk(logits, M.top_k, M.renorm)
+        if self.heat is not None:
+            self.heat.observe(layer, ids)
         # Tokens are replicated across the ranks, so expert parallelism needs no dispatch: every rank runs the routed
         # pairs whose expert it holds and the partial outputs are summed by the reduce + norm that follows.
         y = ops.moe(hd, w, ids, M.experts)

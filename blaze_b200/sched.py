@@ -500,6 +500,9 @@ class Scheduler:
     def abort(self, request_id: str) -> None:
         self.aborts.put(request_id)
 
+    #: (every n steps, callable) pairs run on the scheduler thread between steps (statistics that must not race the GPU work)
+    housekeeping: tuple = ()
+
     def start(self) -> None:
         self._thread = threading.Thread(target=self._loop, name="blaze-sched", daemon=True)
         self._thread.start()
@@ -525,6 +528,9 @@ class Scheduler:
         (``crates/blaze/src/sched.rs:1067-1075``)."""
         try:
             self.step()
+            for every, fn in self.housekeeping:
+                if self.stats.steps % every == 0:
+                    fn()
         except Exception as e:
             if self.raise_step_errors:
                 raise

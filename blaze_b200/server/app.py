@@ -332,7 +332,8 @@ def create_app(st: ServerState) -> FastAPI:
                 "scheduler": {"schedule": llm.sched.cfg.schedule, "chunk": llm.sched.cfg.chunk, "max_seqs": llm.sched.cfg.max_seqs,
                               "max_step_tokens": llm.sched.cfg.max_step_tokens, "spec_method": llm.sched.cfg.spec_method,
                               "max_draft": llm.sched.cfg.max_draft, "prefix_cache": llm.sched.cfg.prefix_cache},
-                "config": {k: ("[REDACTED]" if "key" in k else v) for k, v in st.svc.public_config().items()}}
+                "config": {k: ("[REDACTED]" if "key" in k else v) for k, v in st.svc.public_config().items()},
+                **({"expert_heat": llm.heat.report(max(llm.model.tp.world, 8))} if getattr(llm, "heat", None) is not None else {})}
 
     @app.get("/metrics")
     async def metrics():

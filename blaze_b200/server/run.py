@@ -75,5 +75,6 @@ def serve(ns) -> int:
         st.shutting_down = True
         if st.llm is not None:
             st.llm.sched.stop()
+            st.llm.save_expert_heat()
     server.run()
     return 0
