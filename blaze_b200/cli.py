@@ -41,6 +41,9 @@ def engine_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--expert-heat", default=None, metavar="PATH",
                    help="mixture-of-experts models: keep per-expert routing statistics in this profile file (loaded at start, "
                         "written back periodically and at exit; shown by the info route and `inspect --expert-heat`)")
+    g.add_argument("--expert-placement", default="contiguous", choices=["contiguous", "heat"],
+                   help="with --ep: which experts a rank holds.  contiguous: experts r*E/ranks ..; heat: spread by the routing "
+                        "profile of --expert-heat (heaviest first onto the least loaded rank)")
     g.add_argument("--kv-cache-dtype", default=None, choices=["fp8", "bf16", "fp32", "nvfp4", "nvfp4_4over6", "auto"])
     g.add_argument("--kv-host", action="store_true", help="keep cold KV pages in pinned host memory")
     g.add_argument("--kv-rotate", action="store_true", help="randomised Hadamard rotation of q and k rows before the KV write")
@@ -225,7 +228,7 @@ def build_llm(ns: argparse.Namespace):
               draft_tree_width=int(getattr(ns, "draft_tree_width", 1) or 1),
               tune=bool(getattr(ns, "tune", False)), draft_model=getattr(ns, "draft_model", None), draft_head_vocab=int(getattr(ns, "mtp_head_vocab", 0) or 0),
               draft_tree_depth=int(ns.draft_tree_depth or 4), max_verify=int(ns.max_verify or 8),
-              expert_heat=getattr(ns, "expert_heat", None))
+              expert_heat=getattr(ns, "expert_heat", None), expert_placement=getattr(ns, "expert_placement", "contiguous"))
     llm.group = group
     if group is not None:
         from .parallel.worker import attach

@@ -134,6 +134,12 @@ class ExpertHeat:
                 held[r] += 1
         return out
 
+    @staticmethod
+    def order_for(where: np.ndarray) -> np.ndarray:
+        """Slot order that realises placement ``where`` (``[layers, experts]`` ranks) with contiguous slots per rank:
+        slot j of a layer holds expert ``order[layer][j]``; experts keep their relative order inside a rank."""
+        return np.stack([np.argsort(where[l], kind="stable") for l in range(where.shape[0])]).astype(np.int64)
+
     def contiguous(self, world: int) -> np.ndarray:
         """The placement expert parallelism uses: expert e on rank ``e // (experts / world)``."""
         if world <= 0 or self.E % world:

@@ -45,7 +45,8 @@ class LLM:
                  kv_host_tokens: int = 0, schedule: str = "interleave", kv_rotate: bool = False,
                  draft_tree_width: int = 1, draft_model: Optional[str] = None, draft_head_vocab: int = 0,
                  draft_tree_depth: int = 4, watchdog: bool = False, max_verify: int = 8, tune: bool = False,
-                 stage_layers: Optional[tuple] = None, expert_heat: Union[str, bool, None] = None):
+                 stage_layers: Optional[tuple] = None, expert_heat: Union[str, bool, None] = None,
+                 expert_placement: str = "contiguous"):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -53,6 +54,20 @@ class LLM:
         fmt = {"dense": Format.DENSE, "bf16": Format.DENSE, "nvfp4": Format.NVFP4, "mxfp8": Format.MXFP8,
                "fp8_block": Format.FP8_BLOCK, "fp8": Format.FP8_CHANNEL}[weight_format]
         lo, hi = stage_layers if stage_layers is not None else (0, None)     # this rank's pipeline stage
+        if expert_placement not in ("contiguous", "heat"):
+            raise ValueError(f"unknown expert placement {expert_placement!r}")
+        if expert_placement == "heat" and tpi.ep and tpi.world > 1 and tpi.expert_order is None and not isinstance(model, Model):
+            # expert parallelism with the experts spread by the routing profile: every rank reads the same file
+            from .expert_heat import ExpertHeat
+            mc = model if isinstance(model, ModelConfig) else (ModelConfig.load(model) if os.path.isdir(model) else named_config(model))
+            E = int(getattr(mc, "num_experts", 0) or 0)
+            prof = ExpertHeat.load(expert_heat, mc.num_layers, E) if (E and isinstance(expert_heat, str)) else None
+            if prof is not None and prof.longterm.sum() > 0 and E % tpi.world == 0:
+                tpi.expert_order = ExpertHeat.order_for(prof.placement(tpi.world, recent=False))
+                log.info("experts.placed", ranks=tpi.world, worst_before=float(prof.imbalance(tpi.world, recent=False).max()),
+                         worst_after=float(prof.imbalance(tpi.world, prof.placement(tpi.world, recent=False), recent=False).max()))
+            else:
+                log.info("experts.placement_skipped", reason="no routing profile with observations for this model")
         with log.Stage("model"):
             if isinstance(model, Model):
                 self.model = model

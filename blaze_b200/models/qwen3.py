@@ -143,8 +143,12 @@ class _PhaseTimer:
 class TPInfo:
     """Rank layout.  ``group`` does the collectives (None on one rank)."""
 
-    def __init__(self, rank: int = 0, world: int = 1, group=None, ep: bool = False):
+    def __init__(self, rank: int = 0, world: int = 1, group=None, ep: bool = False, expert_order=None):
         self.rank, self.world, self.group, self.ep = rank, world, group, ep
+        # [layers, experts]: slot j of a layer holds checkpoint expert expert_order[layer][j].  The router's rows and the
+        # experts are stored in slot order, so expert parallelism (contiguous slots per rank) realises any placement
+        # without a change to routing or kernels (expert_heat.ExpertHeat.order_for turns a placement into this table).
+        self.expert_order = expert_order
 
 
 class Model:
@@ -281,7 +285,9 @@ class Model:
             if cfg.is_moe:
                 M = MoeMlp()
                 M.top_k, M.renorm = cfg.num_experts_per_tok, cfg.norm_topk_prob
-                M.router = _tag(Linear.from_dense(rnd(cfg.num_experts, H, base + 20, router_std or std), Format.DENSE, dtype=dtype), Cut.ALL)
+                order = m._expert_slots(i)
+                rw = rnd(cfg.num_experts, H, base + 20, router_std or std)
+                M.router = _tag(Linear.from_dense(rw if order is None else rw[order], Format.DENSE, dtype=dtype), Cut.ALL)
                 E = Experts()
                 E.num_experts = cfg.num_experts
                 I = cfg.moe_intermediate_size
@@ -291,7 +297,8 @@ class Model:
                 else:
                     E.first, E.count = 0, cfg.num_experts
                 gen.manual_seed((seed * 1000003 + base + 21) & 0x7FFFFFFF)
-                for e in range(E.first, E.first + E.count):
+                for slot in range(E.first, E.first + E.count):
+                    e = slot if order is None else int(order[slot])
                     gen.manual_seed((seed * 1000003 + (base + 21) * 4099 + e) & 0x7FFFFFFF)
                     wg = torch.randn(2 * I, H, generator=gen, device=device) * std
                     wd = torch.randn(H, I, generator=gen, device=device) * std
@@ -402,6 +409,13 @@ class Model:
                 M = MoeMlp()
                 M.top_k, M.renorm = cfg.num_experts_per_tok, cfg.norm_topk_prob
                 M.router = Linear.load(ck, [mp + "gate"], Cut.ALL, 0, 1, dtype, device)
+                order = m._expert_slots(i)
+                if order is not None:
+                    if M.router.fmt != Format.DENSE:
+                        raise ValueError("an expert placement needs an unquantised router weight")
+                    M.router.w = M.router.w[order.to(M.router.w.device)].contiguous()
+                    if getattr(M.router, "bias", None) is not None:
+                        M.router.bias = M.router.bias[order.to(M.router.bias.device)].contiguous()
                 E = Experts()
                 E.num_experts = cfg.num_experts
                 if m.tp.ep:
@@ -409,7 +423,8 @@ class Model:
                     E.count = end - E.first
                 else:
                     E.first, E.count = 0, cfg.num_experts
-                for e in range(E.first, E.first + E.count):
+                for slot in range(E.first, E.first + E.count):
+                    e = slot if order is None else int(order[slot])
                     ep = f"{mp}experts.{e}."
                     if m.tp.ep or tpw == 1:
                         E.gate_up.append(Linear.load(ck, [ep + "gate_proj", ep + "up_proj"], Cut.ALL, 0, 1, dtype, device))
@@ -599,6 +614,17 @@ class Model:
             self.ops.gdn(mixed[idx].contiguous(), None, ba[0], ba[1], L.gdn, self, batch, kv, gi, state_only=True)
 
     heat = None          # expert_heat.ExpertHeat when routing statistics are collected
+    _order_dev = None    # tp.expert_order on the device (slot -> checkpoint expert), for the statistics
+
+    def _expert_slots(self, layer: int):
+        """Slot order of ``layer``'s experts (a LongTensor), or None when experts keep their checkpoint order."""
+        eo = self.tp.expert_order
+        if eo is None:
+            return None
+        row = torch.as_tensor(eo[layer]).long()
+        if sorted(row.tolist()) != list(range(self.cfg.num_experts)):
+            raise ValueError(f"expert order of layer {layer} is not a permutation of {self.cfg.num_experts} experts")
+        return row
 
     def _mlp(self, M, h, fused=None, layer: int = 0):
         """Returns (output, kind) with kind as in :meth:`forward`."""
@@ -614,7 +640,12 @@ class Model:
         else:
             w, ids = ops.router_topk(logits, M.top_k, M.renorm)
         if self.heat is not None:
-            self.heat.observe(layer, ids)
+            if self.tp.expert_order is not None:
+                if self._order_dev is None:
+                    self._order_dev = torch.as_tensor(self.tp.expert_order).long().to(ids.device)
+                self.heat.observe(layer, self._order_dev[layer][ids.long()])      # the profile is in checkpoint numbering
+            else:
+                self.heat.observe(layer, ids)
         # Tokens are replicated across the ranks, so expert parallelism needs no dispatch: every rank runs the routed
         # pairs whose expert it holds and the partial outputs are summed by the reduce + norm that follows.
         y = ops.moe(hd, w, ids, M.experts)

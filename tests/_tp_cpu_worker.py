@@ -47,6 +47,46 @@ def main():
             assert all(len(g) == 10 for g in got)
         else:
             assert follow(llm) == 0
+    elif case == "expert_placement":
+        # expert parallelism over two ranks with the experts spread by a routing profile: same tokens as one process with
+        # the experts in checkpoint order, and the statistics collected under the placement stay in checkpoint numbering
+        import numpy as np
+        from blaze_b200.expert_heat import ExpertHeat
+        cfg = named_config("tiny-hybrid")
+        path = sys.argv[2]
+        kw = dict(device="cpu", dtype=torch.float32, max_seqs=8, max_model_len=256, use_graphs=False, seed=0, chunk=16)
+        if rank == 0:
+            solo_llm = LLM(cfg, expert_heat=True, **kw)
+            solo = [o.token_ids for o in solo_llm.generate(prompts, sp)]
+            solo_llm.save_expert_heat()
+            prof = ExpertHeat(cfg.num_layers, cfg.num_experts)
+            load = np.ones(cfg.num_experts)
+            load[:cfg.num_experts // 2] = 50.0          # the hot half is what rank 0 would hold in checkpoint order
+            prof.longterm[:] = load
+            prof.recent[:] = load
+            prof.save(path)
+        dist.barrier()
+        llm = LLM(cfg, tp=TPInfo(rank, world, group, ep=True), expert_heat=path, expert_placement="heat", **kw)
+        order = llm.model.tp.expert_order
+        assert order is not None and sorted(order[0].tolist()) == list(range(cfg.num_experts))
+        half = cfg.num_experts // 2
+        hot_on_rank0 = sum(1 for e in order[0][:half] if e < half)
+        assert hot_on_rank0 == half // 2, "the hot experts must be split evenly over the two ranks"
+        if rank == 0:
+            before = llm.heat.longterm.copy()
+            lead = Leader(llm.engine, group)
+            got = [o.token_ids for o in llm.generate(prompts, sp)]
+            lead.quit()
+            same = sum(a == b for a, b in zip(sum(solo, []), sum(got, [])))
+            total = len(sum(solo, []))
+            print(f"[tp-cpu] tokens equal to the single-process run: {same}/{total}", flush=True)
+            assert same >= 0.9 * total
+            llm.heat.fold()
+            if same == total:
+                assert np.array_equal(llm.heat.longterm - before, solo_llm.heat.longterm), "statistics must be in checkpoint numbering"
+                print("[tp-cpu] routing statistics equal to the single-process run", flush=True)
+        else:
+            assert follow(llm) == 0
     elif case == "mtp":
         # a one-layer chain drafter cut over the two ranks like the target: its steps are mirrored on rank 1 (with the fused
         # input rows broadcast from rank 0), its head is the target's sharded head; the streams equal plain decoding

@@ -8,12 +8,12 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(case, timeout=240):
+def _run(case, timeout=240, extra=()):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(HERE, "_tp_cpu_worker.py"), case]
+           "--master-port", str(port), os.path.join(HERE, "_tp_cpu_worker.py"), case, *extra]
     env = dict(os.environ, OMP_NUM_THREADS="2")
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
     print(r.stdout[-2000:])
@@ -42,3 +42,9 @@ def test_two_pipeline_stages_match_one_process():
     r = _run("pipeline")
     assert r.returncode == 0
     assert "two stages give the single-process tokens" in r.stdout
+
+
+def test_expert_parallel_ranks_with_a_heat_aware_placement(tmp_path):
+    r = _run("expert_placement", extra=(str(tmp_path / "heat.bin"),))
+    assert r.returncode == 0
+    assert "tokens equal to the single-process run" in r.stdout
