@@ -58,6 +58,20 @@ def engine_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--ep", action="store_true", help="shard MoE experts across the tensor-parallel ranks")
     g.add_argument("--yarn-factor", type=float, default=None)
     g.add_argument("--draft-model", default=None, help="EAGLE / DFlash drafter checkpoint")
+    g.add_argument("--mtp-model", default=None, help="checkpoint holding the MTP drafter's `mtp.*` tensors (default: the target's own)")
+    # Flags of the reference engine whose job is done differently here.  Their neutral values are accepted so that launch
+    # scripts carry over; any other value is refused with the reason (``check_compat``).
+    c = p.add_argument_group("accepted for compatibility")
+    c.add_argument("--gemm", default="auto", help="auto | nvfp4: the weight format decides the kernel here; bf16 (widened weights through a library GEMM) is not offered")
+    c.add_argument("--attn-f16-acc", default="auto", help="auto | off: attention accumulates in fp32 in tensor memory")
+    c.add_argument("--prefill-attention", default="auto", help="auto: one prefill attention kernel")
+    c.add_argument("--verify-attention", default="auto", help="auto: verify rows go through the decode / row-block kernels")
+    c.add_argument("--prefill-a16", default="none", help="none: activations follow the weight format on prefill as on decode")
+    c.add_argument("--l2-prefetch-mib", type=float, default=None, help="0: there is no L2 weight prefetch between kernels")
+    c.add_argument("--draft-head-vram", default="auto", help="auto | on: a drafter's LM head is always in device memory")
+    c.add_argument("--pp-remote", default=None, help="not offered: pipeline stages are ranks of one torch.distributed job")
+    c.add_argument("--ple-threads", type=int, default=None, help="not offered: per-layer n-gram embeddings are not built")
+    c.add_argument("--ple-cache-gib", type=float, default=None, help="not offered: per-layer n-gram embeddings are not built")
     g.add_argument("--spec-method", default=None, choices=["none", "ngram", "suffix", "mtp", "eagle", "dflash"])
     g.add_argument("--max-verify", type=int, default=None)
     g.add_argument("--suffix-assist", action="store_true")
@@ -170,6 +184,36 @@ def resolve(argv: Sequence[str]) -> argparse.Namespace:
     return ns
 
 
+_COMPAT = {
+    # flag attribute: (accepted values, why anything else is refused)
+    "gemm": (("auto", "nvfp4"), "the GEMM kernel follows the weight format; there is no widened-weight library path"),
+    "attn_f16_acc": (("auto", "off"), "attention accumulates in fp32 (tensor memory); there is no fp16 accumulation mode"),
+    "prefill_attention": (("auto",), "there is one prefill attention kernel"),
+    "verify_attention": (("auto",), "verify rows use the decode / row-block attention kernels; there are no alternatives to pick"),
+    "prefill_a16": (("none",), "prefill quantises activations like decode does; 16-bit prefill inputs are not built"),
+    "l2_prefetch_mib": ((None, 0, 0.0), "there is no L2 weight prefetch between kernels"),
+    "draft_head_vram": (("auto", "on"), "a drafter's LM head always lives in device memory"),
+    "pp_remote": ((None,), "pipeline stages are ranks of one torch.distributed job: launch every stage with torch.distributed.run "
+                           "(--nnodes / --node-rank for several machines) and --pp"),
+    "ple_threads": ((None,), "per-layer n-gram embeddings (PLE) are not built"),
+    "ple_cache_gib": ((None,), "per-layer n-gram embeddings (PLE) are not built"),
+}
+
+
+def check_compat(ns: argparse.Namespace) -> None:
+    """Refuse, with the reason, a reference-engine flag set to something this engine cannot honour."""
+    for attr, (ok, why) in _COMPAT.items():
+        v = getattr(ns, attr, ok[0])
+        if v not in ok:
+            raise SystemExit(f"--{attr.replace('_', '-')} {v}: {why}")
+    if getattr(ns, "mtp_model", None):
+        if getattr(ns, "spec_method", None) not in (None, "mtp"):
+            raise SystemExit("--mtp-model goes with --spec-method mtp")
+        if getattr(ns, "draft_model", None) and ns.draft_model != ns.mtp_model:
+            raise SystemExit("--mtp-model and --draft-model name different checkpoints")
+        ns.spec_method, ns.draft_model = "mtp", ns.mtp_model
+
+
 def spec_defaults(ns: argparse.Namespace) -> None:
     """``--spec-method mtp`` implies its window / candidate settings; PP with a drafter is refused (``main.rs:203-254``)."""
     if getattr(ns, "spec_method", None) in (None, "none") and getattr(ns, "draft_model", None):
@@ -187,6 +231,7 @@ def build_llm(ns: argparse.Namespace):
     from .llm import LLM
     from .models.qwen3 import TPInfo
     from .parallel.tp import TPGroup
+    check_compat(ns)
     spec_defaults(ns)
     device = ns.device or ("cuda" if torch.cuda.is_available() else "cpu")
     world = int(os.environ.get("WORLD_SIZE", "1"))
