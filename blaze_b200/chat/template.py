@@ -165,12 +165,32 @@ class ChatFormatter:
             tools = request.get("tools")
             if request.get("tool_choice", "auto" if tools else "none") == "none":
                 tools = None
+            from .request import effort_of, thinking_requested
             kw = dict(defaults or {})
             kw.update(request.get("chat_template_kwargs") or {})
+            # reasoning_effort / reasoning.{effort,enabled} switch thinking and name the effort the template may announce;
+            # explicit template arguments win (``crates/blaze/src/server/chat.rs:176-188``)
+            t, e = thinking_requested(request), effort_of(request)
+            if t is not None:
+                kw.setdefault("thinking", t)
+                kw.setdefault("enable_thinking", t)
+            if e is not None:
+                kw.setdefault("reasoning_effort", e)
             think = kw.pop("enable_thinking", request.get("enable_thinking"))
             for k in ("messages", "tools", "add_generation_prompt"):
                 kw.pop(k, None)
-            prompt = self.render(request.get("messages") or [], tools, bool(request.get("add_generation_prompt", True)), think, **kw)
+            messages = request.get("messages") or []
+            if request.get("continue_final_message") not in (None, False, 0):
+                # the final assistant turn is rendered closed and the prompt is cut after its text, which leaves it open
+                tail = _text_of(messages[-1].get("content")) if messages else ""
+                if not tail:
+                    raise ValueError("the last message has no text to continue")
+                prompt = self.render(messages, tools, False, think, **kw)
+                at = prompt.rfind(tail)
+                if at < 0:
+                    raise ValueError("the last message's text is not in the rendered prompt")
+                return prompt[:at + len(tail)], "", False
+            prompt = self.render(messages, tools, bool(request.get("add_generation_prompt", True)), think, **kw)
             return prompt, "", think
         return prompt, prefix, prompt.endswith(THINK_OPENERS) and not prefix
 

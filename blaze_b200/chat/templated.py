@@ -167,4 +167,7 @@ def render_request(formatter, request: Dict[str, Any], defaults: Optional[Dict[s
         raise IndexError("list index out of range")
     for m in messages:
         _join_text_parts(m)
-    return formatter.render_prepared(messages, tools, args), prefix
+    # without a generation prompt the template ends after the last turn (not combined with a continued turn, whose prefix
+    # already stands for the opened assistant turn)
+    gen = request.get("add_generation_prompt") is not False or bool(prefix)
+    return formatter.render_prepared(messages, tools, args, add_generation_prompt=gen), prefix

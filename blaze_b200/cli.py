@@ -109,6 +109,11 @@ def service_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--tool-call-parser", default="hermes")
     g.add_argument("--reasoning-parser", default="qwen3")
     g.add_argument("--chat-family", default=None, choices=["chatml", "deepseek", "glm", "kimi"])
+    g.add_argument("--grammar-whitespace", type=int, default=64,
+                   help="longest white-space run between JSON tokens of structured outputs, characters (0: unbounded; requests "
+                        "override it with whitespace_pattern or disable_any_whitespace)")
+    g.add_argument("--chat-template", default=None, metavar="FILE",
+                   help="Jinja chat template to use instead of the checkpoint's (a file path)")
     g.add_argument("--chat-template-kwargs", default=None, metavar="JSON",
                    help="default template arguments (e.g. '{\"thinking\": true}'); a request's chat_template_kwargs override them")
 

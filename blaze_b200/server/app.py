@@ -29,7 +29,7 @@ from ..sampler import SamplingParams
 from ..sched import Finish, GenEvent, GenRequest, ThinkBudget
 from ..service import (MAX_COMPLETIONS_PER_REQUEST, RequestError, ServiceArgs, sampling_of, stop_strings_of,
                        thinking_budget_of)
-from ..structured import ConstraintError, Grammars, grammar_of
+from ..structured import forced_call_grammar, ConstraintError, Grammars, grammar_of
 from ..telemetry import Histogram
 
 RESPONSES_KEPT = 256
@@ -457,9 +457,45 @@ def create_app(st: ServerState) -> FastAPI:
     def _sse(obj) -> bytes:
         return ("data: " + json.dumps(obj, ensure_ascii=False, separators=(",", ":")) + "\n\n").encode()
 
+    def _check_tool_choice(tools, choice) -> Optional[List[str]]:
+        """Validate ``tool_choice`` against ``tools``; returns the tool names a forced call may use (``required``: all of
+        them, a named function: that one), or None when nothing is forced."""
+        names = [(t.get("function") or {}).get("name") for t in tools or [] if isinstance(t, dict)]
+        if isinstance(choice, str):
+            if choice not in ("auto", "none", "required"):
+                raise RequestError('tool_choice must be "auto", "none", "required" or a named function', "tool_choice")
+            if choice == "required":
+                if not names:
+                    raise RequestError('tool_choice is "required" but tools is empty', "tool_choice")
+                return names
+            return None
+        if isinstance(choice, dict):
+            name = (choice.get("function") or {}).get("name")
+            if name not in names:
+                raise RequestError(f'tool named "{name}" in tool_choice is not present in tools', "tool_choice")
+            return [name]
+        if choice is not None:
+            raise RequestError('tool_choice must be "auto", "none", "required" or a named function', "tool_choice")
+        return None
+
+    def _check_continuation(b, msgs) -> None:
+        cont = b.get("continue_final_message")
+        if cont in (None, False, 0):
+            return
+        if b.get("add_generation_prompt") is True:
+            raise RequestError("continue_final_message and add_generation_prompt cannot both be true", "continue_final_message")
+        last = msgs[-1] if msgs else {}
+        if not isinstance(last, dict) or str(last.get("role", "")).lower() != "assistant":
+            raise RequestError("continue_final_message needs the last message to be an assistant message", "continue_final_message")
+
     def _render_chat(b: Dict[str, Any]):
         """(prompt text, continuation prefix, thinking) of a chat request body; request errors of the family encoders
         become 400s."""
+        msgs = b.get("messages")
+        if isinstance(msgs, list) and any(isinstance(m, dict) and "reasoning" in m and "reasoning_content" not in m for m in msgs):
+            # agent frameworks replay an assistant turn's reasoning under either name
+            b = {**b, "messages": [({**m, "reasoning_content": m["reasoning"]} if isinstance(m, dict) and isinstance(m.get("reasoning"), str)
+                                    and "reasoning_content" not in m else m) for m in msgs]}
         try:
             return st.formatter.render_request(b, st.svc.chat_template_kwargs)
         except (ValueError, TypeError, IndexError, KeyError) as e:
@@ -473,6 +509,14 @@ def create_app(st: ServerState) -> FastAPI:
             raise RequestError("messages must be a non-empty list", "messages")
         tools = b.get("tools")
         tool_choice = b.get("tool_choice", "auto" if tools else "none")
+        forced = _check_tool_choice(tools, tool_choice)
+        _check_continuation(b, msgs)
+        if st.vision is None:
+            for m in msgs:
+                for part in (m.get("content") if isinstance(m, dict) and isinstance(m.get("content"), list) else []):
+                    kind = part.get("type") if isinstance(part, dict) else None
+                    if kind in ("image_url", "image", "input_image", "video_url", "video", "audio_url", "input_audio"):
+                        raise RequestError(f"this model only takes text input; received a content part of type {kind!r}", "messages")
         if tool_choice == "none":
             tools_for_prompt = None
         else:
@@ -487,8 +531,14 @@ def create_app(st: ServerState) -> FastAPI:
             mm = await collect_images(msgs, st.vision)
         params = sampling_of(b, st.svc, st.vocab)
         _check_len(len(ids), params)
-        spec = grammar_of(b)
+        spec = grammar_of(b, st.svc.grammar_whitespace)
         in_think = text.rstrip("\n").endswith(("<think>", "<|open|>think<|sep|>")) and not prefix
+        if forced and spec is None and not in_think and not prefix and st.grammars.ll_tok is not None:
+            # tool_choice forces a call: the answer must be calls to the named tools in the parser's syntax.  Where the
+            # syntax is not known, or the prompt leaves the model inside its reasoning, the model is only asked.
+            g = forced_call_grammar(st.svc.tool_call_parser, forced, b.get("parallel_tool_calls") is False)
+            if g is not None:
+                spec = {"kind": "grammar", "grammar": g}
         return ids, params, tools_for_prompt, enable_thinking, spec, mm, in_think
 
     @app.post("/v1/chat/completions")
@@ -500,7 +550,7 @@ def create_app(st: ServerState) -> FastAPI:
         skip_special = bool(b.get("skip_special_tokens", True))
         n = params.n
         stream = bool(b.get("stream", False))
-        reasoning = st.svc.reasoning_parser is not None and enable_thinking is not False
+        reasoning = st.svc.reasoning_parser is not None and enable_thinking is not False and b.get("separate_reasoning") is not False
         created, cid = int(time.time()), "chatcmpl-" + uuid.uuid4().hex[:24]
         want_lp = params.logprobs is not None
 
@@ -627,7 +677,7 @@ def create_app(st: ServerState) -> FastAPI:
         if echo and params.logprobs is not None:
             raise RequestError("echo with logprobs is not supported (prompt log-probabilities are not computed)", "echo")
         stream = bool(b.get("stream", False))
-        spec = grammar_of(b)
+        spec = grammar_of(b, st.svc.grammar_whitespace)
         created, cid = int(time.time()), "cmpl-" + uuid.uuid4().hex[:24]
         gens = []
         for pi, p in enumerate(prompts):
@@ -788,6 +838,11 @@ def create_app(st: ServerState) -> FastAPI:
         tools = [{"type": "function", "function": {k: v for k, v in t.items() if k != "type"}} for t in (b.get("tools") or [])
                  if t.get("type") == "function"] or None
         cb = {**b, "messages": msgs, "tools": tools, "max_tokens": b.get("max_output_tokens")}
+        effort = (b.get("reasoning") or {}).get("effort") if isinstance(b.get("reasoning"), dict) else None
+        if effort is not None:
+            # "minimal": as little as possible, i.e. no thinking section for a model that has one
+            cb.pop("reasoning", None)
+            cb["reasoning_effort"] = "none" if effort == "minimal" else effort
         tf = (b.get("text") or {}).get("format")
         if isinstance(tf, dict) and tf.get("type") in ("json_schema", "json_object"):
             cb["response_format"] = {"type": tf["type"], "json_schema": {"schema": tf.get("schema", {})}}

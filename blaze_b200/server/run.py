@@ -18,7 +18,7 @@ def service_args_of(ns) -> ServiceArgs:
                        profile_prefill=ns.profile_prefill, generation_config=ns.generation_config, samplers=ns.samplers,
                        top_nsigma=ns.top_nsigma, top_h=ns.top_h, tool_call_parser=ns.tool_call_parser,
                        reasoning_parser=ns.reasoning_parser or None,
-                       chat_family=getattr(ns, "chat_family", None),
+                       chat_family=getattr(ns, "chat_family", None), grammar_whitespace=int(getattr(ns, "grammar_whitespace", 64)),
                        chat_template_kwargs=_json_object(getattr(ns, "chat_template_kwargs", None), "--chat-template-kwargs"))
 
 
@@ -50,6 +50,9 @@ def serve(ns) -> int:
             llm = build_llm(ns)
             st.leader = getattr(llm, "leader", None)       # build_llm attached the step protocol when there are other ranks
             tok = load_tokenizer(ns.model if ns.model and os.path.isdir(ns.model) else None, llm.model.cfg.vocab_size)
+            if getattr(ns, "chat_template", None):
+                with open(ns.chat_template, encoding="utf-8") as f:
+                    tok.chat_template = f.read()
             vision = None
             if llm.model.cfg.vision_config and ns.model and os.path.isdir(ns.model):
                 from ..models.vision import Vision

@@ -50,6 +50,7 @@ class ServiceArgs:
     reasoning_parser: Optional[str] = "qwen3"
     chat_family: Optional[str] = None            # built-in renderer + message normalisation: chatml, deepseek, glm, kimi
     chat_template_kwargs: Dict[str, Any] = field(default_factory=dict)    # template arguments a request may override
+    grammar_whitespace: int = 64                 # longest white-space run between JSON tokens of structured outputs (0: unbounded)
     cors_origins: Tuple[str, ...] = ("*",)
     defaults: Dict[str, Any] = field(default_factory=dict)
 

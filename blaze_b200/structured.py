@@ -97,6 +97,30 @@ class LLGuidanceConstraint(Constraint):
         return self.m.is_stopped()
 
 
+class _AsGuidanceTokenizer:
+    """The view of a tokenizer that ``llguidance.TokenizerWrapper`` asks for: the bytes of every token id, the ids of the
+    special tokens (never produced from text), the end-of-sequence id and an encode call."""
+
+    def __init__(self, tokenizer, vocab_size: int, eos_ids: Sequence[int]):
+        self._tok = tokenizer
+        self.eos_token_id = int(eos_ids[0])
+        self.bos_token_id = None
+        n = min(vocab_size, getattr(tokenizer, "vocab_size", vocab_size))
+        control = set(getattr(tokenizer, "control", ())) | set(int(e) for e in eos_ids)
+        self.special_token_ids = sorted(t for t in control if t < vocab_size)
+        self.tokens = []
+        for i in range(vocab_size):
+            b = tokenizer.token_bytes(i) if i < n else b""
+            if i in control:
+                b = b"\xff" + (b or f"<{i}>".encode())          # the marker llguidance uses for special tokens
+            self.tokens.append(b or f"<unused{i}>".encode())
+
+    def __call__(self, text) -> List[int]:
+        if isinstance(text, (bytes, bytearray)):
+            text = bytes(text).decode("utf-8", errors="replace")
+        return self._tok.encode(text)
+
+
 class Grammars:
     """Builds constraints for requests; owns the (expensive) llguidance tokenizer."""
 
@@ -106,11 +130,15 @@ class Grammars:
         self.error: Optional[str] = None
         try:
             import llguidance
-            import llguidance.hf
             inner = getattr(tokenizer, "tk", None)
             if inner is not None:
+                import llguidance.hf
                 self.ll_tok = llguidance.LLTokenizer(llguidance.hf.from_tokenizer(inner, n_vocab=vocab_size)) \
                     if hasattr(llguidance.hf, "from_tokenizer") else None
+            elif hasattr(tokenizer, "token_bytes") and self.eos:
+                # any tokenizer that can name the bytes of its tokens (the byte-level stand-in of synthetic models)
+                self.ll_tok = llguidance.LLTokenizer(llguidance.TokenizerWrapper(_AsGuidanceTokenizer(tokenizer, vocab_size, self.eos)),
+                                                     n_vocab=vocab_size)
         except Exception as e:  # fall back to the built-in engine
             self.error = repr(e)
 
@@ -140,30 +168,111 @@ class Grammars:
         return LLGuidanceConstraint(self.ll_tok, g, self.V)
 
 
-def grammar_of(body: Dict[str, Any]) -> Optional[Dict[str, Any]]:
-    """Map request fields to a constraint spec (``structured.rs:128``): ``response_format`` (json_object /
-    json_schema), ``structured_outputs`` / ``guided_json|regex|choice|grammar``."""
+def grammar_of(body: Dict[str, Any], max_ws: int = 64) -> Optional[Dict[str, Any]]:
+    """Map request fields to a constraint spec (``structured.rs:118-190``): OpenAI ``response_format`` (json_object /
+    json_schema), vLLM ``structured_outputs`` / ``guided_decoding`` {json, regex, choice, grammar, json_object} and the older
+    ``guided_json|regex|choice|grammar``, SGLang ``regex`` / ``json_schema``.
+
+    White space between JSON tokens: the grammar engine allows any run of it, and a model that would rather answer in words
+    finds white space the likeliest allowed token before ``{`` again and again, to the end of ``max_tokens``.  Runs are bounded
+    to ``max_ws`` characters (0: unbounded); a request's ``whitespace_pattern`` / ``guided_whitespace_pattern`` or
+    ``disable_any_whitespace`` (compact JSON) win, as does a schema's own ``x-guidance``."""
+    so = body.get("structured_outputs") if isinstance(body.get("structured_outputs"), dict) else body.get("guided_decoding")
+    so = so if isinstance(so, dict) else {}
+
+    def opt(k):
+        v = so.get(k)
+        return v if v is not None else body.get(k)
+
+    pattern = opt("whitespace_pattern") if opt("whitespace_pattern") is not None else opt("guided_whitespace_pattern")
+    if pattern is not None:
+        ws = {"whitespace_pattern": pattern}
+    elif opt("disable_any_whitespace") is True:
+        ws = {"whitespace_flexible": False}
+    elif max_ws > 0:
+        ws = {"whitespace_pattern": "[\\x20\\x0A\\x0D\\x09]{1,%d}" % max_ws}
+    else:
+        ws = None
+
+    def schema_spec(v):
+        if isinstance(v, str):
+            v = json.loads(v)
+        if not isinstance(v, dict):
+            raise ConstraintError("a JSON schema must be an object")
+        if ws is not None and "x-guidance" not in v:
+            v = {**v, "x-guidance": ws}
+        return {"kind": "json_schema", "schema": v}
+
     rf = body.get("response_format")
     if isinstance(rf, dict):
         t = rf.get("type")
         if t == "json_object":
-            return {"kind": "json_object"}
+            return schema_spec({"type": "object"})
         if t == "json_schema":
-            js = rf.get("json_schema") or {}
-            schema = js.get("schema", js)
+            js = rf.get("json_schema")
+            schema = js.get("schema") if isinstance(js, dict) and "schema" in js else (js if isinstance(js, dict) and js and "name" not in js else rf.get("schema"))
             if not isinstance(schema, dict):
-                raise ConstraintError("response_format.json_schema.schema must be an object")
-            return {"kind": "json_schema", "schema": schema}
+                raise ConstraintError("response_format of type json_schema needs json_schema.schema (an object)")
+            return schema_spec(schema)
         if t not in (None, "text"):
             raise ConstraintError(f"unknown response_format type {t!r}")
-    so = body.get("structured_outputs") or {}
-    for key, kind, field in (("json", "json_schema", "schema"), ("regex", "regex", "regex"), ("choice", "choice", "choices"),
-                             ("grammar", "grammar", "grammar")):
-        v = so.get(key, body.get(f"guided_{key}"))
-        if v is not None:
-            if kind == "json_schema" and isinstance(v, str):
-                v = json.loads(v)
-            if kind == "choice" and (not isinstance(v, list) or not v):
-                raise ConstraintError("choice needs a non-empty list of strings")
-            return {"kind": kind, field: v}
+
+    def field(k, old):
+        v = so.get(k)
+        return v if v is not None else body.get(old)
+
+    v = field("json", "guided_json")
+    if v is None:
+        v = body.get("json_schema")
+    if v is not None:
+        return schema_spec(v)
+    if so.get("json_object") is True:
+        return schema_spec({"type": "object"})
+    v = field("regex", "guided_regex")
+    if v is None:
+        v = body.get("regex")
+    if v is not None:
+        if not isinstance(v, str):
+            raise ConstraintError("regex must be a string")
+        return {"kind": "regex", "regex": v}
+    v = field("choice", "guided_choice")
+    if v is not None:
+        if not isinstance(v, list) or not v or not all(isinstance(c, str) for c in v):
+            raise ConstraintError("choice needs a non-empty list of strings")
+        return {"kind": "choice", "choices": v}
+    v = field("grammar", "guided_grammar")
+    if v is not None:
+        if not isinstance(v, str):
+            raise ConstraintError("grammar must be a string")
+        return {"kind": "grammar", "grammar": v}
     return None
+
+
+#: call syntax per tool-call parser: (opening tag, text before the tool's name, text after it, closing tag)
+_CALL_SYNTAX = {
+    "qwen3_coder": ("<tool_call>", "<function=", ">", "</tool_call>"),
+    "qwen3-coder": ("<tool_call>", "<function=", ">", "</tool_call>"),
+    "hermes": ("<tool_call>", '{"name": "', '"', "</tool_call>"),
+    "qwen": ("<tool_call>", '{"name": "', '"', "</tool_call>"),
+    "qwen25": ("<tool_call>", '{"name": "', '"', "</tool_call>"),
+}
+
+
+def forced_call_grammar(parser: Optional[str], names: Sequence[str], single: bool = False) -> Optional[str]:
+    """Lark grammar of an answer that must consist of tool calls (``tool_choice`` "required" or a named function): the
+    parser's call syntax around one of ``names``, then whatever the model writes for the arguments up to the closing tag;
+    ``single`` allows one call only (``parallel_tool_calls`` false).  None for parsers whose syntax is not listed (the model
+    is then only asked).  White space around the calls is bounded: an unbounded ``ws*`` would let a model that prefers to
+    answer in words emit white space forever under greedy decoding.  Reference: ``crates/blaze/src/server/chat.rs:81-103``
+    (``forced_call_grammar``)."""
+    syn = _CALL_SYNTAX.get((parser or "").lower())
+    if syn is None or not names:
+        return None
+    opening, before, after, closing = (json.dumps(t) for t in syn)
+    alts = " | ".join(json.dumps(n) for n in names)
+    # the arguments are free text that ends with the closing tag (a lexeme with a suffix: the shortest such text)
+    return (f"start: ws call{'' if single else ' (ws call)*'} ws\n"
+            f"call: {opening} ws {before} name {after} body\n"
+            f"name: {alts}\n"
+            "ws: /[ \\t\\r\\n]{0,4}/\n"
+            f"body[suffix={closing}]: /(?s:.*)/\n")

@@ -237,3 +237,96 @@ def test_protocol_details_clients_rely_on(client):
     lp = r["choices"][0]["logprobs"]
     assert len(lp["tokens"]) == len(lp["token_logprobs"]) == len(lp["top_logprobs"]) == len(lp["text_offset"]) >= 2
     assert lp["text_offset"][0] == 0
+
+
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {"city": {"type": "string"}}}}},
+         {"type": "function", "function": {"name": "search", "parameters": {"type": "object", "properties": {"q": {"type": "string"}}}}}]
+
+
+def test_tool_choice_and_continuation_are_validated(client):
+    chat = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0}
+
+    def err(extra):
+        r = client.post("/v1/chat/completions", json={**chat, **extra}, headers=H)
+        assert r.status_code == 400, r.text
+        return r.json()["error"]
+
+    assert err({"tool_choice": "required"})["param"] == "tool_choice"
+    assert "not present in tools" in err({"tools": TOOLS, "tool_choice": {"type": "function", "function": {"name": "nope"}}})["message"]
+    assert err({"tools": TOOLS, "tool_choice": "sometimes"})["param"] == "tool_choice"
+    assert err({"continue_final_message": True})["param"] == "continue_final_message"          # last message is not the assistant's
+    both = {"messages": chat["messages"] + [{"role": "assistant", "content": "It is"}], "continue_final_message": True,
+            "add_generation_prompt": True}
+    assert "cannot both be true" in err(both)["message"]
+    # a continued assistant turn: the prompt ends with its text, the turn left open
+    body = {"messages": chat["messages"] + [{"role": "assistant", "content": "It is"}], "continue_final_message": True}
+    toks = client.post("/tokenize", json=body, headers=H).json()["tokens"]
+    text = client.post("/detokenize", json={"tokens": toks, "skip_special_tokens": False}, headers=H).json()["prompt"]
+    assert text.endswith("<|im_start|>assistant\nIt is")
+    r = client.post("/v1/chat/completions", json={**chat, **body}, headers=H)
+    assert r.status_code == 200 and r.json()["usage"]["prompt_tokens"] == len(toks)
+
+
+def test_structured_output_on_the_byte_tokenizer(client):
+    """Grammar constraints run through llguidance with any tokenizer that can name its tokens' bytes."""
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 24, "temperature": 0,
+                                                  "chat_template_kwargs": {"enable_thinking": False},
+                                                  "guided_regex": "(yes|no), [0-9]{3}!"}, headers=H)
+    assert r.status_code == 200, r.text
+    import re
+    assert re.fullmatch(r"(yes|no), [0-9]{3}!", r.json()["choices"][0]["message"]["content"]), r.json()
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 200, "temperature": 0,
+                                                  "chat_template_kwargs": {"enable_thinking": False},
+                                                  "response_format": {"type": "json_schema", "json_schema": {"name": "s", "schema": {
+                                                      "x-guidance": {"whitespace_flexible": False},     # a random model would pad forever
+                                                      "type": "object", "properties": {"ok": {"type": "boolean"}, "n": {"type": "integer", "minimum": 0, "maximum": 9}},
+                                                      "required": ["ok", "n"], "additionalProperties": False}}}}, headers=H)
+    assert r.status_code == 200, r.text
+    obj = json.loads(r.json()["choices"][0]["message"]["content"])
+    assert set(obj) == {"ok", "n"} and isinstance(obj["ok"], bool) and 0 <= obj["n"] <= 9
+
+
+def test_forced_tool_call_is_constrained_to_the_call_syntax():
+    """``tool_choice`` naming a function (or "required") constrains the answer to calls of the listed tools in the parser's
+    syntax, so even a random-init model answers with a call to the right tool."""
+    st = ServerState(ServiceArgs(default_max_tokens=8, tool_call_parser="qwen3_coder", reasoning_parser=None), "tiny")
+    c = TestClient(create_app(st))
+    llm = LLM(named_config("tiny"), device="cpu", dtype=torch.float32, max_seqs=4, max_model_len=1024, use_graphs=False)
+    st.attach(llm, ByteTokenizer(1024))
+    try:
+        body = {"messages": [{"role": "user", "content": "weather?"}], "tools": TOOLS, "max_tokens": 48, "temperature": 0,
+                "chat_template_kwargs": {"enable_thinking": False}, "parallel_tool_calls": False}
+        r = c.post("/v1/chat/completions", json={**body, "tool_choice": {"type": "function", "function": {"name": "search"}}})
+        assert r.status_code == 200, r.text
+        msg = r.json()["choices"][0]["message"]
+        assert msg.get("tool_calls") and msg["tool_calls"][0]["function"]["name"] == "search", r.json()
+        r = c.post("/v1/chat/completions", json={**body, "tool_choice": "required"})
+        names = [t["function"]["name"] for t in r.json()["choices"][0]["message"]["tool_calls"]]
+        assert names and set(names) <= {"get_weather", "search"}
+    finally:
+        llm.sched.stop()
+
+
+def test_structured_output_fields_and_bounded_white_space():
+    """``grammar_of``: every spelling of a structured-output request, and the white-space policy for JSON."""
+    from blaze_b200.structured import ConstraintError, grammar_of
+    ws64 = {"whitespace_pattern": "[\\x20\\x0A\\x0D\\x09]{1,64}"}
+    assert grammar_of({"response_format": {"type": "json_object"}}) == {"kind": "json_schema", "schema": {"type": "object", "x-guidance": ws64}}
+    s = {"type": "object", "properties": {"a": {"type": "integer"}}}
+    for body in ({"response_format": {"type": "json_schema", "json_schema": {"name": "x", "schema": s}}}, {"guided_json": s},
+                 {"structured_outputs": {"json": s}}, {"guided_decoding": {"json": json.dumps(s)}}, {"json_schema": s}):
+        assert grammar_of(body)["schema"] == {**s, "x-guidance": ws64}, body
+    assert grammar_of({"guided_json": s}, max_ws=0)["schema"] == s                                   # unbounded: the schema as given
+    assert grammar_of({"guided_json": s, "disable_any_whitespace": True})["schema"]["x-guidance"] == {"whitespace_flexible": False}
+    assert grammar_of({"structured_outputs": {"json": s, "whitespace_pattern": "[ ]?"}})["schema"]["x-guidance"] == {"whitespace_pattern": "[ ]?"}
+    own = {**s, "x-guidance": {"whitespace_flexible": True}}
+    assert grammar_of({"guided_json": own})["schema"] == own                                          # a schema's own setting wins
+    assert grammar_of({"structured_outputs": {"json_object": True}})["schema"]["type"] == "object"
+    assert grammar_of({"regex": "a+"}) == {"kind": "regex", "regex": "a+"}
+    assert grammar_of({"structured_outputs": {"choice": ["a", "b"]}}) == {"kind": "choice", "choices": ["a", "b"]}
+    assert grammar_of({"guided_grammar": 'start: "x"'})["kind"] == "grammar"
+    assert grammar_of({"response_format": {"type": "text"}}) is None and grammar_of({}) is None
+    for bad in ({"response_format": {"type": "json_schema"}}, {"response_format": {"type": "json_schema", "json_schema": {"name": "x"}}},
+                {"response_format": {"type": "yaml"}}, {"guided_choice": []}, {"guided_regex": 5}):
+        with pytest.raises(ConstraintError):
+            grammar_of(bad)
