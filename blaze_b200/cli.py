@@ -109,6 +109,31 @@ def service_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--tool-call-parser", default="hermes")
     g.add_argument("--reasoning-parser", default="qwen3")
     g.add_argument("--chat-family", default=None, choices=["chatml", "deepseek", "glm", "kimi"])
+    g.add_argument("--temperature", type=float, default=None, help="default sampling of requests that do not set it (also --top-p, "
+                                                                     "--top-k, --min-p, --presence-penalty)")
+    g.add_argument("--top-p", type=float, default=None)
+    g.add_argument("--top-k", type=int, default=None)
+    g.add_argument("--min-p", type=float, default=None)
+    g.add_argument("--presence-penalty", type=float, default=None)
+    g.add_argument("--max-tokens", type=int, default=None, help="default max_tokens of chat requests (same as --default-max-tokens)")
+    g.add_argument("--step-tokens", "--max-num-batched-tokens", dest="step_tokens", type=int, default=None,
+                   help="tokens of one step (decode tokens + the prefill chunk)")
+    g.add_argument("--spec-ngram", type=int, default=None, help="draft tokens per verify of the n-gram / suffix drafts, 0 off")
+    g.add_argument("--spec-fixed", action="store_true", help="always verify the whole draft (by default drafts are cut or skipped "
+                                                             "by the measured verify cost)")
+    g.add_argument("--thinking-budget", type=int, default=None,
+                   help="default thinking budget in tokens of chat requests (requests override it with thinking_token_budget)")
+    g.add_argument("--vision", default="auto", choices=["auto", "gpu", "cpu", "off"], help="where the vision tower runs; off: no image input")
+    g.add_argument("--vision-threads", type=int, default=None, help="CPU threads of a vision tower that runs on the CPU")
+    g.add_argument("--mm-processor-kwargs", default=None, metavar="JSON",
+                   help="image processor settings over the checkpoint's (min_pixels, max_pixels, size.shortest_edge / longest_edge); "
+                        "requests override them with mm_processor_kwargs")
+    g.add_argument("--limit-mm-per-prompt", default="", help="most images per request, as JSON ({\"image\": 4}) or image=4")
+    g.add_argument("--mm-low-detail-pixels", type=int, default=512 * 512,
+                   help="image_url.detail \"low\": cap of the image's pixels; 0 ignores detail")
+    g.add_argument("--image-fetch-timeout", type=float, default=5.0, help="seconds the http(s) image downloads of one request may take")
+    g.add_argument("--image-fetch-max-mib", type=int, default=64, help="largest image fetched from an http(s) URL, MiB")
+    g.add_argument("--allowed-media-domains", default="", help="hosts http(s) image URLs may name, comma separated (default: any)")
     g.add_argument("--grammar-whitespace", type=int, default=64,
                    help="longest white-space run between JSON tokens of structured outputs, characters (0: unbounded; requests "
                         "override it with whitespace_pattern or disable_any_whitespace)")
@@ -262,6 +287,7 @@ def build_llm(ns: argparse.Namespace):
         raise SystemExit(f"--pp {ns.pp} --tp {ns.tp}: launch {ns.pp * max(ns.tp, 1)} processes (one per GPU), e.g. python -m "
                          f"torch.distributed.run --nproc-per-node {ns.pp * max(ns.tp, 1)} --master-addr 127.0.0.1 -m blaze_b200 …")
     kv_tokens = 0 if str(ns.kv_tokens) == "auto" else int(ns.kv_tokens)
+    spec_ngram = getattr(ns, "spec_ngram", None)           # draft tokens per verify; 0 switches speculation off
     stage_range = None
     if group is not None and group.stages > 1:
         from .config import ModelConfig, named_config
@@ -273,7 +299,10 @@ def build_llm(ns: argparse.Namespace):
               kv_tokens=kv_tokens, max_seqs=ns.max_seqs or 256, max_model_len=ns.max_model_len or 4096,
               chunk=ns.chunk or 2048, enable_prefix_caching=not ns.disable_prefix_caching,
               cache_slots=ns.prompt_cache_slots or 4, use_graphs=not ns.no_graphs,
-              spec_method=ns.spec_method or "none", max_draft=min(ns.max_verify - 1, 8), seed=ns.seed,
+              spec_method=("none" if spec_ngram == 0 else ns.spec_method or "none"),
+              max_draft=min(ns.max_verify - 1, 8) if not spec_ngram else max(1, min(int(spec_ngram), ns.max_verify - 1)), seed=ns.seed,
+              spec_fixed=bool(getattr(ns, "spec_fixed", False)),
+              **({"max_step_tokens": int(ns.step_tokens)} if getattr(ns, "step_tokens", None) else {}),
               kv_host_tokens=getattr(ns, "kv_host_tokens", 0) or 0, schedule=getattr(ns, "schedule", "interleave"), kv_rotate=bool(getattr(ns, "kv_rotate", False)),
               draft_tree_width=int(getattr(ns, "draft_tree_width", 1) or 1),
               tune=bool(getattr(ns, "tune", False)), draft_model=getattr(ns, "draft_model", None), draft_head_vocab=int(getattr(ns, "mtp_head_vocab", 0) or 0),

@@ -46,7 +46,7 @@ class LLM:
                  draft_tree_width: int = 1, draft_model: Optional[str] = None, draft_head_vocab: int = 0,
                  draft_tree_depth: int = 4, watchdog: bool = False, max_verify: int = 8, tune: bool = False,
                  stage_layers: Optional[tuple] = None, expert_heat: Union[str, bool, None] = None,
-                 expert_placement: str = "contiguous"):
+                 expert_placement: str = "contiguous", spec_fixed: bool = False):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -107,7 +107,7 @@ class LLM:
             self.engine.start_watchdog()
         self.sched = Scheduler(self.engine, SchedConfig(chunk=chunk, max_seqs=max_seqs, prefix_cache=enable_prefix_caching,
                                                         cache_slots=cache_slots, spec_method=spec_method, max_draft=max_draft,
-                                                        draft_tree_width=draft_tree_width, max_verify=max_verify,
+                                                        draft_tree_width=draft_tree_width, max_verify=max_verify, spec_fixed=spec_fixed,
                                                         draft_tree_depth=draft_tree_depth,
                                                         eos_ids=eos, max_model_len=max_model_len,
                                                         max_step_tokens=max_step_tokens, kv_host_pages=kv_host_tokens // 16, schedule=schedule),

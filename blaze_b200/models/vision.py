@@ -374,9 +374,17 @@ class Vision:
         pad = raw.get("image_token_id", raw.get("vision_config", {}).get("image_token_id", -1))
         return cls(tower, int(pad))
 
-    def encode(self, image) -> Tuple[torch.Tensor, Tuple[int, int]]:
-        """One decoded RGB image (``[H, W, 3]`` uint8) -> (embeddings ``[tokens, out_hidden]``, merged (h, w) grid)."""
-        patches, grid = preprocess(torch.as_tensor(image), self.cfg)
+    def encode(self, image, min_pixels: Optional[int] = None, max_pixels: Optional[int] = None) -> Tuple[torch.Tensor, Tuple[int, int]]:
+        """One decoded RGB image (``[H, W, 3]`` uint8) -> (embeddings ``[tokens, out_hidden]``, merged (h, w) grid).
+        ``min_pixels`` / ``max_pixels`` replace the processor's resize limits for this image."""
+        cfg = self.cfg
+        if min_pixels is not None or max_pixels is not None:
+            import dataclasses
+            cfg = dataclasses.replace(cfg, min_pixels=min_pixels or cfg.min_pixels, max_pixels=max_pixels or cfg.max_pixels)
+        if not isinstance(image, torch.Tensor):
+            import numpy as np
+            image = torch.from_numpy(np.array(image))      # a decoded PIL image or an array (copied: writable)
+        patches, grid = preprocess(image, cfg)
         emb = self.tower.encode(patches, [grid])
         m = self.cfg.spatial_merge_size
         return emb, (grid[1] // m, grid[2] // m)
@@ -393,7 +401,8 @@ def check_reference(model_dir: Optional[str], image_path: Optional[str]) -> int:
         from ..server.media import decode_image
         with open(image_path, "rb") as f:
             img = decode_image(f.read())
-        img = torch.as_tensor(img)
+        import numpy as np
+        img = torch.from_numpy(np.array(img))
     else:
         img = (torch.rand(224, 224, 3, generator=torch.Generator().manual_seed(0)) * 255).to(torch.uint8)
     patches, grid = preprocess(img, vt.cfg)

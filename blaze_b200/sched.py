@@ -379,6 +379,7 @@ class SchedConfig:
     spec_method: str = "none"          # none | ngram | suffix | mtp | eagle
     max_draft: int = 4
     max_verify: int = 8
+    spec_fixed: bool = False           # verify every draft at full length instead of asking the cost model
     draft_tree_width: int = 1          # > 1: n-gram drafts branch into up to this many continuations, verified as a tree
     uniform_verify: bool = True        # pad chain drafts to one length when the verify step can then replay a captured graph
     draft_tree_depth: int = 4          # deepest level of a draft tree (n-gram continuations are cut, drafter trees grown, to it)
@@ -1098,7 +1099,8 @@ class Scheduler:
             room = a.req.params.max_tokens - len(a.generated) - 1
             ok = a.req.constraint is None and not a.forced
             maxd.append(max(0, min(cfg.max_draft, room)) if ok else 0)
-        want = self.cost.choose([a.acc for a in decoders], maxd)
+        # spec_fixed: always verify the whole draft; else drafts are cut or skipped by the measured verify cost
+        want = list(maxd) if cfg.spec_fixed else self.cost.choose([a.acc for a in decoders], maxd)
         out: Dict[int, List[int]] = {}
         if cfg.spec_method == "ngram":
             eng = self.engine

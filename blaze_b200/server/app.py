@@ -70,6 +70,14 @@ class ServerState:
         self.shutting_down = False
 
     def attach(self, llm, tokenizer, vision=None) -> None:
+        from .media import MediaPolicy
+        svc = self.svc
+        self.media_policy = MediaPolicy(limit_images=svc.limit_mm_per_prompt, low_detail_pixels=svc.mm_low_detail_pixels,
+                                        fetch_timeout_s=svc.image_fetch_timeout, fetch_max_bytes=svc.image_fetch_max_mib << 20,
+                                        allowed_domains=tuple(svc.allowed_media_domains), processor=dict(svc.mm_processor_kwargs),
+                                        enabled=svc.vision != "off")
+        if svc.vision == "off":
+            vision = None
         self.tokenizer = tokenizer
         cfg = llm.model.cfg
         self.formatter = ChatFormatter.for_checkpoint(
@@ -422,7 +430,7 @@ def create_app(st: ServerState) -> FastAPI:
         params.max_tokens = max(1, min(params.max_tokens, st.max_len - n_prompt - 1))
 
     def _think(b, enable_thinking) -> Optional[ThinkBudget]:
-        budget = thinking_budget_of(b)
+        budget = thinking_budget_of(b, st.svc.thinking_budget)
         if budget is None:
             return None
         o, c = st.tokenizer.token_id("<think>"), st.tokenizer.token_id("</think>")
@@ -528,7 +536,7 @@ def create_app(st: ServerState) -> FastAPI:
         mm = None
         if st.vision is not None:
             from .media import collect_images
-            mm = await collect_images(msgs, st.vision)
+            mm = await collect_images(msgs, st.vision, st.svc.allow_remote_images, st.media_policy, b.get("mm_processor_kwargs"))
         params = sampling_of(b, st.svc, st.vocab)
         _check_len(len(ids), params)
         spec = grammar_of(b, st.svc.grammar_whitespace)

@@ -12,6 +12,31 @@ from .app import ServerState, create_app
 
 
 def service_args_of(ns) -> ServiceArgs:
+    from .media import parse_limit
+    try:
+        limit = parse_limit(getattr(ns, "limit_mm_per_prompt", ""))
+    except ValueError as e:
+        raise SystemExit(str(e))
+    svc = _service_args(ns)
+    svc.limit_mm_per_prompt = limit
+    svc.thinking_budget = getattr(ns, "thinking_budget", None)
+    svc.vision, svc.vision_threads = getattr(ns, "vision", "auto"), getattr(ns, "vision_threads", None)
+    svc.mm_processor_kwargs = _json_object(getattr(ns, "mm_processor_kwargs", None), "--mm-processor-kwargs")
+    svc.mm_low_detail_pixels = int(getattr(ns, "mm_low_detail_pixels", 512 * 512))
+    svc.image_fetch_timeout = float(getattr(ns, "image_fetch_timeout", 5.0))
+    svc.image_fetch_max_mib = int(getattr(ns, "image_fetch_max_mib", 64))
+    svc.allowed_media_domains = tuple(d.strip().lower() for d in (getattr(ns, "allowed_media_domains", "") or "").split(",") if d.strip())
+    if getattr(ns, "max_tokens", None):
+        svc.default_max_tokens = int(ns.max_tokens)
+    for flag, key in (("temperature", "temperature"), ("top_p", "top_p"), ("top_k", "top_k"), ("min_p", "min_p"),
+                      ("presence_penalty", "presence_penalty")):
+        v = getattr(ns, flag, None)
+        if v is not None:
+            svc.defaults[key] = v          # a flag wins over --generation-config
+    return svc
+
+
+def _service_args(ns) -> ServiceArgs:
     return ServiceArgs(host=ns.host, port=ns.port, api_keys=tuple(ns.api_key or ()), served_model_name=ns.served_model_name,
                        max_queue=ns.max_queue, max_concurrency=ns.max_concurrency, request_timeout_s=ns.request_timeout,
                        default_max_tokens=ns.default_max_tokens, log_level=ns.log_level, log_format=ns.log_format,
@@ -54,10 +79,13 @@ def serve(ns) -> int:
                 with open(ns.chat_template, encoding="utf-8") as f:
                     tok.chat_template = f.read()
             vision = None
-            if llm.model.cfg.vision_config and ns.model and os.path.isdir(ns.model):
+            if llm.model.cfg.vision_config and ns.model and os.path.isdir(ns.model) and svc.vision != "off":
                 from ..models.vision import Vision
                 with log.Stage("vision"):
-                    vision = Vision.load(ns.model, llm.device)
+                    if svc.vision == "cpu" and svc.vision_threads:
+                        import torch
+                        torch.set_num_threads(int(svc.vision_threads))
+                    vision = Vision.load(ns.model, "cpu" if svc.vision == "cpu" else llm.device)
             st.attach(llm, tok, vision)
             log.info("server.ready", model=st.model_name, port=svc.port)
         except Exception as e:

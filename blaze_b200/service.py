@@ -51,6 +51,16 @@ class ServiceArgs:
     chat_family: Optional[str] = None            # built-in renderer + message normalisation: chatml, deepseek, glm, kimi
     chat_template_kwargs: Dict[str, Any] = field(default_factory=dict)    # template arguments a request may override
     grammar_whitespace: int = 64                 # longest white-space run between JSON tokens of structured outputs (0: unbounded)
+    thinking_budget: Optional[int] = None        # default thinking budget in tokens (requests override it with thinking_token_budget)
+    vision: str = "auto"                         # where the vision tower runs: auto | gpu | cpu | off
+    vision_threads: Optional[int] = None
+    mm_processor_kwargs: Dict[str, Any] = field(default_factory=dict)
+    limit_mm_per_prompt: int = 999
+    mm_low_detail_pixels: int = 512 * 512
+    image_fetch_timeout: float = 5.0
+    image_fetch_max_mib: int = 64
+    allowed_media_domains: Tuple[str, ...] = ()
+    allow_remote_images: bool = True
     cors_origins: Tuple[str, ...] = ("*",)
     defaults: Dict[str, Any] = field(default_factory=dict)
 
@@ -185,8 +195,8 @@ def stop_strings_of(body: Dict[str, Any]) -> List[str]:
     return [s for s in stop if s]
 
 
-def thinking_budget_of(body: Dict[str, Any]) -> Optional[int]:
-    v = body.get("thinking_token_budget", body.get("thinking_budget"))
+def thinking_budget_of(body: Dict[str, Any], default: Optional[int] = None) -> Optional[int]:
+    v = body.get("thinking_token_budget", body.get("thinking_budget", default))
     if v is None:
         return None
     if isinstance(v, bool) or not isinstance(v, int) or v < 0:
