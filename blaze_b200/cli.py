@@ -95,9 +95,31 @@ def service_parser(p: argparse.ArgumentParser) -> None:
     g.add_argument("--port", type=int, default=8000)
     g.add_argument("--api-key", action="append", default=None)
     g.add_argument("--served-model-name", default=None)
-    g.add_argument("--max-queue", type=int, default=1024)
-    g.add_argument("--max-concurrency", type=int, default=512)
+    g.add_argument("--print-config", action="store_true", help="print the effective configuration (API keys redacted) and exit "
+                                                               "without loading a model")
+    g.add_argument("--api-key-file", default=None, help="file with one API key per line (blank lines ignored)")
+    g.add_argument("--max-queue", "--max-queued-requests", dest="max_queue", type=int, default=1024,
+                   help="most accepted generations, queued ones included; beyond it requests get 429")
+    g.add_argument("--max-concurrency", "--max-concurrent-requests", dest="max_concurrency", type=int, default=512,
+                   help="most HTTP requests in flight, their streaming bodies included")
     g.add_argument("--request-timeout", type=float, default=600.0)
+    g.add_argument("--shutdown-timeout", type=float, default=10.0, help="longest graceful drain after SIGINT / SIGTERM, seconds")
+    g.add_argument("--max-request-body-mib", type=int, default=64)
+    g.add_argument("--allowed-origins", default="*", help="allowed CORS origins, comma separated; '*' allows all, 'none' disables CORS")
+    g.add_argument("--log-color", default="auto", choices=["auto", "always", "never"])
+    g.add_argument("--disable-log-requests", action="store_true", help="no per-request lifecycle log lines (metrics continue)")
+    g.add_argument("--log-inputs", action="store_true", help="log bounded previews of request payloads")
+    g.add_argument("--log-outputs", action="store_true", help="log bounded previews of response payloads")
+    g.add_argument("--max-log-len", type=int, default=400, help="most characters of a payload preview")
+    g.add_argument("--log-stats-interval", type=float, default=5.0, help="seconds between scheduler summaries; 0 disables them")
+    g.add_argument("--override-generation-config", default=None, metavar="JSON",
+                   help="sampling defaults over --generation-config (explicit flags and request parameters win)")
+    g.add_argument("--instruct-sampling", default=None, metavar="JSON",
+                   help="sampling defaults of chat requests with thinking off, over the defaults above, e.g. "
+                        "'{\"temperature\":0.7,\"top_p\":0.8,\"presence_penalty\":1.5}'")
+    g.add_argument("--frequency-penalty", type=float, default=None)
+    g.add_argument("--repetition-penalty", type=float, default=None)
+    g.add_argument("--min-tokens", type=int, default=None)
     g.add_argument("--default-max-tokens", type=int, default=512)
     g.add_argument("--log-level", default="info")
     g.add_argument("--log-format", default="text", choices=["text", "json"])

@@ -196,6 +196,12 @@ def _lp_entry(tok, lp: dict) -> Dict[str, Any]:
     return e
 
 
+def _preview(text: str, limit: int) -> str:
+    """A bounded, single-line preview of a payload for the log (control characters escaped)."""
+    text = text if len(text) <= limit else text[:limit] + f"... ({len(text)} characters)"
+    return text.encode("unicode_escape").decode("ascii") if any(ord(c) < 32 for c in text) else text
+
+
 def create_app(st: ServerState) -> FastAPI:
     app = FastAPI(title="blaze_b200", version=__version__)
 
@@ -206,8 +212,12 @@ def create_app(st: ServerState) -> FastAPI:
         if not rid or len(rid) > 128 or not all(c.isalnum() or c in "-_.:" for c in rid):
             rid = uuid.uuid4().hex          # absent or not a plain token: the server names the request
         path = request.url.path
-        cors = {"access-control-allow-origin": ",".join(st.svc.cors_origins), "access-control-allow-headers": "*",
-                "access-control-allow-methods": "GET,POST,DELETE,OPTIONS", "x-request-id": rid}
+        cors = {"x-request-id": rid}
+        if st.svc.cors_origins:
+            origin = request.headers.get("origin")
+            allowed = "*" if "*" in st.svc.cors_origins else (origin if origin in st.svc.cors_origins else st.svc.cors_origins[0])
+            cors.update({"access-control-allow-origin": allowed, "access-control-allow-headers": "*",
+                         "access-control-allow-methods": "GET,POST,DELETE,OPTIONS"})
         if request.method == "OPTIONS":
             return PlainTextResponse("", headers=cors)
         open_paths = ("/health", "/ping", "/version", "/metrics")
@@ -269,8 +279,17 @@ def create_app(st: ServerState) -> FastAPI:
         return resp
 
     async def _body(request: Request) -> Dict[str, Any]:
+        limit = st.svc.max_request_body_mib << 20
+        declared = request.headers.get("content-length")
+        if declared and declared.isdigit() and int(declared) > limit:
+            raise RequestError(f"request body is larger than {st.svc.max_request_body_mib} MiB", None, "request_too_large", 413)
+        raw = await request.body()
+        if len(raw) > limit:
+            raise RequestError(f"request body is larger than {st.svc.max_request_body_mib} MiB", None, "request_too_large", 413)
+        if st.svc.log_inputs:
+            log.info("request.input", path=request.url.path, body=_preview(raw.decode("utf-8", "replace"), st.svc.max_log_len))
         try:
-            b = await request.json()
+            b = json.loads(raw)
         except Exception:
             raise RequestError("request body must be JSON")
         if not isinstance(b, dict):
@@ -537,7 +556,9 @@ def create_app(st: ServerState) -> FastAPI:
         if st.vision is not None:
             from .media import collect_images
             mm = await collect_images(msgs, st.vision, st.svc.allow_remote_images, st.media_policy, b.get("mm_processor_kwargs"))
-        params = sampling_of(b, st.svc, st.vocab)
+        # a reasoning model's prompt with thinking switched off takes the instruct sampling defaults
+        instruct = st.svc.reasoning_parser is not None and (enable_thinking is False or text.rstrip("\n").endswith("</think>"))
+        params = sampling_of(b, st.svc, st.vocab, instruct=instruct)
         _check_len(len(ids), params)
         spec = grammar_of(b, st.svc.grammar_whitespace)
         in_think = text.rstrip("\n").endswith(("<think>", "<|open|>think<|sep|>")) and not prefix

@@ -28,11 +28,37 @@ def service_args_of(ns) -> ServiceArgs:
     svc.allowed_media_domains = tuple(d.strip().lower() for d in (getattr(ns, "allowed_media_domains", "") or "").split(",") if d.strip())
     if getattr(ns, "max_tokens", None):
         svc.default_max_tokens = int(ns.max_tokens)
-    for flag, key in (("temperature", "temperature"), ("top_p", "top_p"), ("top_k", "top_k"), ("min_p", "min_p"),
-                      ("presence_penalty", "presence_penalty")):
+    from ..service import merge_sampling
+    try:
+        # order of precedence, lowest first: generation_config.json, --override-generation-config, explicit flags
+        gc = getattr(ns, "generation_config", None)
+        if gc in (None, "auto") and getattr(ns, "model", None) and os.path.isdir(ns.model):
+            auto = os.path.join(ns.model, "generation_config.json")
+            if os.path.isfile(auto):
+                svc.read_generation_config(auto)
+        merge_sampling(svc.defaults, _json_object(getattr(ns, "override_generation_config", None), "--override-generation-config"),
+                       "--override-generation-config")
+        merge_sampling(svc.instruct_sampling, _json_object(getattr(ns, "instruct_sampling", None), "--instruct-sampling"),
+                       "--instruct-sampling")
+    except ValueError as e:
+        raise SystemExit(str(e))
+    for flag in ("temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty", "repetition_penalty", "min_tokens"):
         v = getattr(ns, flag, None)
         if v is not None:
-            svc.defaults[key] = v          # a flag wins over --generation-config
+            svc.defaults[flag] = v
+    keys = list(svc.api_keys)
+    if getattr(ns, "api_key_file", None):
+        with open(ns.api_key_file) as f:
+            keys += [ln.strip() for ln in f if ln.strip()]
+    svc.api_keys = tuple(keys)
+    origins = (getattr(ns, "allowed_origins", "*") or "*").strip()
+    svc.cors_origins = () if origins == "none" else tuple(o.strip() for o in origins.split(",") if o.strip())
+    svc.shutdown_timeout = float(getattr(ns, "shutdown_timeout", 10.0))
+    svc.max_request_body_mib = int(getattr(ns, "max_request_body_mib", 64))
+    svc.log_requests = not getattr(ns, "disable_log_requests", False)
+    svc.log_inputs, svc.log_outputs = bool(getattr(ns, "log_inputs", False)), bool(getattr(ns, "log_outputs", False))
+    svc.max_log_len = int(getattr(ns, "max_log_len", 400))
+    svc.log_stats_interval = float(getattr(ns, "log_stats_interval", 5.0))
     return svc
 
 
@@ -65,6 +91,11 @@ def serve(ns) -> int:
     from ..cli import build_llm
     from ..text import load_tokenizer
     svc = service_args_of(ns)
+    if getattr(ns, "print_config", False):
+        import json
+        engine = {k: v for k, v in sorted(vars(ns).items()) if not k.startswith("_") and k not in ("api_key", "command")}
+        print(json.dumps({"service": svc.public_config(), "flags": engine}, indent=1, default=str))
+        return 0
     name = os.path.basename(os.path.normpath(ns.model)) if ns.model else "blaze"
     st = ServerState(svc, name)
     app = create_app(st)
@@ -98,7 +129,7 @@ def serve(ns) -> int:
         from ..parallel.worker import follow
         return follow(llm)
     threading.Thread(target=load, name="blaze-load", daemon=True).start()
-    config = uvicorn.Config(app, host=svc.host, port=svc.port, log_level="warning", timeout_graceful_shutdown=10)
+    config = uvicorn.Config(app, host=svc.host, port=svc.port, log_level="warning", timeout_graceful_shutdown=max(int(svc.shutdown_timeout), 1))
     server = uvicorn.Server(config)
 
     @app.on_event("shutdown")

@@ -61,6 +61,13 @@ class ServiceArgs:
     image_fetch_max_mib: int = 64
     allowed_media_domains: Tuple[str, ...] = ()
     allow_remote_images: bool = True
+    shutdown_timeout: float = 10.0               # longest graceful drain after SIGINT / SIGTERM, seconds
+    max_request_body_mib: int = 64               # larger request bodies are refused with 413
+    log_inputs: bool = False                     # bounded previews of request payloads in the request log
+    log_outputs: bool = False                    # bounded previews of response payloads
+    max_log_len: int = 400                       # characters of a payload preview
+    log_stats_interval: float = 5.0              # seconds between scheduler summaries (0: none)
+    instruct_sampling: Dict[str, Any] = field(default_factory=dict)   # defaults of chat requests with thinking off, over `defaults`
     cors_origins: Tuple[str, ...] = ("*",)
     defaults: Dict[str, Any] = field(default_factory=dict)
 
@@ -79,18 +86,40 @@ class ServiceArgs:
         env = os.environ.get("BLAZE_API_KEY")
         if env and not self.api_keys:
             self.api_keys = tuple(k for k in env.split(",") if k)
-        if self.generation_config:
-            with open(self.generation_config) as f:
-                g = json.load(f)
-            for k in ("temperature", "top_p", "top_k", "min_p", "repetition_penalty", "presence_penalty", "frequency_penalty"):
-                if k in g and g[k] is not None:
-                    self.defaults.setdefault(k, g[k])
+        if self.generation_config and self.generation_config not in ("auto", "none"):
+            self.read_generation_config(self.generation_config)
         if self.samplers:
             self.defaults.setdefault("samplers", self.samplers)
         if self.top_nsigma is not None:
             self.defaults.setdefault("top_nsigma", self.top_nsigma)
         if self.top_h is not None:
             self.defaults.setdefault("top_h", self.top_h)
+
+
+SAMPLING_KEYS = ("temperature", "top_p", "top_k", "min_p", "repetition_penalty", "presence_penalty", "frequency_penalty",
+                 "top_nsigma", "top_h", "seed", "min_tokens", "samplers")
+
+
+def merge_sampling(into: Dict[str, Any], src: Dict[str, Any], what: str, override: bool = True) -> None:
+    """Merge a JSON object of sampling defaults; unknown keys are an error (a misspelt key must not be ignored)."""
+    if not isinstance(src, dict):
+        raise ValueError(f"{what} must be a JSON object")
+    for k, v in src.items():
+        if k not in SAMPLING_KEYS:
+            raise ValueError(f"{what}: unknown sampling parameter {k!r}")
+        if v is not None and (override or k not in into):
+            into[k] = v
+
+
+def _read_generation_config(self, path: str) -> None:
+    with open(path) as f:
+        g = json.load(f)
+    for k in ("temperature", "top_p", "top_k", "min_p", "repetition_penalty", "presence_penalty", "frequency_penalty"):
+        if k in g and g[k] is not None:
+            self.defaults.setdefault(k, g[k])
+
+
+ServiceArgs.read_generation_config = _read_generation_config
 
 
 def _num(body, key, default, lo=None, hi=None, lo_open=False, integer=False):
@@ -116,9 +145,13 @@ def validate_pipeline_fields(body: Dict[str, Any], pipeline: Sequence[Stage]) ->
             raise RequestError(f"{key} is set but the sampler chain has no {key} stage; add it to `samplers`", key)
 
 
-def sampling_of(body: Dict[str, Any], svc: ServiceArgs, vocab_size: int, max_tokens_key: str = "max_tokens") -> SamplingParams:
-    """Build and range-check sampling parameters from a request body (``server.rs:430-504``, :512)."""
+def sampling_of(body: Dict[str, Any], svc: ServiceArgs, vocab_size: int, max_tokens_key: str = "max_tokens",
+                instruct: bool = False) -> SamplingParams:
+    """Build and range-check sampling parameters from a request body (``server.rs:430-504``, :512).  ``instruct``: a chat
+    request whose prompt switches thinking off takes the ``instruct_sampling`` defaults over the general ones."""
     b = dict(svc.defaults)
+    if instruct:
+        b.update(svc.instruct_sampling)
     b.update({k: v for k, v in body.items() if v is not None})
     try:
         pipeline = parse_pipeline(b.get("samplers"))

@@ -330,3 +330,54 @@ def test_structured_output_fields_and_bounded_white_space():
                 {"response_format": {"type": "yaml"}}, {"guided_choice": []}, {"guided_regex": 5}):
         with pytest.raises(ConstraintError):
             grammar_of(bad)
+
+
+def test_service_flags_layers_and_limits(tmp_path, capsys):
+    from blaze_b200.cli import build_parser, main
+    from blaze_b200.server.run import service_args_of
+    model = tmp_path / "ckpt"
+    model.mkdir()
+    (model / "generation_config.json").write_text(json.dumps({"temperature": 0.6, "top_k": 20, "top_p": 0.95}))
+    keys = tmp_path / "keys.txt"
+    keys.write_text("k1\n\nk2\n")
+    ns = build_parser().parse_args(["serve", "--model", str(model), "--override-generation-config", '{"top_k": 40, "min_p": 0.1}',
+                                    "--instruct-sampling", '{"temperature": 0.7, "presence_penalty": 1.5}', "--top-p", "0.8",
+                                    "--api-key", "k0", "--api-key-file", str(keys), "--allowed-origins", "https://a.example, https://b.example",
+                                    "--max-queued-requests", "7", "--max-concurrent-requests", "3", "--shutdown-timeout", "2",
+                                    "--max-request-body-mib", "1", "--disable-log-requests", "--log-inputs", "--repetition-penalty", "1.1"])
+    svc = service_args_of(ns)
+    # generation_config.json < --override-generation-config < explicit flags
+    assert svc.defaults["temperature"] == 0.6 and svc.defaults["top_k"] == 40 and svc.defaults["min_p"] == 0.1 and svc.defaults["top_p"] == 0.8
+    assert svc.defaults["repetition_penalty"] == 1.1 and svc.instruct_sampling == {"temperature": 0.7, "presence_penalty": 1.5}
+    assert svc.api_keys == ("k0", "k1", "k2") and svc.cors_origins == ("https://a.example", "https://b.example")
+    assert (svc.max_queue, svc.max_concurrency, svc.shutdown_timeout, svc.max_request_body_mib) == (7, 3, 2.0, 1)
+    assert svc.log_requests is False and svc.log_inputs is True
+    assert service_args_of(build_parser().parse_args(["serve", "--model", "tiny", "--allowed-origins", "none"])).cors_origins == ()
+    with pytest.raises(SystemExit, match="unknown sampling parameter"):
+        service_args_of(build_parser().parse_args(["serve", "--model", "tiny", "--instruct-sampling", '{"temperatur": 0.7}']))
+    # --print-config shows the effective settings without the keys and loads nothing
+    assert main(["serve", "--model", "tiny", "--api-key", "topsecret", "--print-config", "--top-k", "5"]) == 0
+    out = capsys.readouterr().out
+    assert "topsecret" not in out and '"top_k": 5' in out and "[REDACTED]" in out
+
+
+def test_instruct_defaults_body_limit_and_cors():
+    from blaze_b200.service import sampling_of
+    svc = ServiceArgs(defaults={"temperature": 0.6, "top_p": 0.95}, instruct_sampling={"temperature": 0.7, "presence_penalty": 1.5},
+                      max_request_body_mib=1, cors_origins=("https://a.example",), reasoning_parser="qwen3")
+    think, plain = sampling_of({}, svc, 1024), sampling_of({}, svc, 1024, instruct=True)
+    assert (think.temperature, think.presence_penalty) == (0.6, 0.0) and (plain.temperature, plain.presence_penalty, plain.top_p) == (0.7, 1.5, 0.95)
+    assert sampling_of({"temperature": 0.1}, svc, 1024, instruct=True).temperature == 0.1          # the request wins
+    st = ServerState(svc, "tiny")
+    c = TestClient(create_app(st))
+    llm = LLM(named_config("tiny"), device="cpu", dtype=torch.float32, max_seqs=4, max_model_len=256, use_graphs=False)
+    st.attach(llm, ByteTokenizer(1024))
+    try:
+        r = c.post("/v1/completions", content=b'{"prompt": "' + b"x" * (1 << 20) + b'"}', headers={"content-type": "application/json"})
+        assert r.status_code == 413 and r.json()["error"]["code"] == "request_too_large"
+        r = c.get("/v1/models", headers={"origin": "https://a.example"})
+        assert r.headers["access-control-allow-origin"] == "https://a.example"
+        st.svc.cors_origins = ()
+        assert "access-control-allow-origin" not in c.get("/v1/models").headers
+    finally:
+        llm.sched.stop()
