@@ -346,7 +346,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ns = resolve(argv)
     from . import log
     if hasattr(ns, "log_level"):
-        log.configure(level=ns.log_level, fmt=ns.log_format)
+        color = {"always": True, "never": False}.get(getattr(ns, "log_color", "auto"))      # auto: a terminal decides
+        log.configure(level=ns.log_level, fmt=ns.log_format, color=color)
     if ns.command == "inspect":
         if getattr(ns, "expert_heat", None):
             from .inspect import inspect_expert_heat

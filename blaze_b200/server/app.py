@@ -618,6 +618,9 @@ def create_app(st: ServerState) -> FastAPI:
                     ch["logprobs"] = {"content": [_lp_entry(st.tokenizer, l) for l in lps]}
                 choices.append(ch)
             usage = _usage(len(ids), sum(g.n_out for g, _ in gens), gens[0][0].cached)
+            if st.svc.log_outputs:
+                log.info("request.output", id=cid, text=_preview(choices[0]["message"].get("content") or "", st.svc.max_log_len),
+                         finish=choices[0]["finish_reason"])
             return {"id": cid, "object": "chat.completion", "created": created, "model": st.model_name, "choices": choices,
                     "usage": usage}
 
@@ -746,6 +749,8 @@ def create_app(st: ServerState) -> FastAPI:
                 if params.logprobs is not None:
                     ch["logprobs"] = lp_obj(lps)
                 choices.append(ch)
+            if st.svc.log_outputs:
+                log.info("request.output", id=cid, text=_preview(choices[0]["text"], st.svc.max_log_len), finish=choices[0]["finish_reason"])
             return {"id": cid, "object": "text_completion", "created": created, "model": st.model_name, "choices": choices,
                     "usage": _usage(sum(len(p) for _, _, p in gens), sum(g.n_out for g, _, _ in gens), 0)}
 
