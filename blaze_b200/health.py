@@ -47,7 +47,7 @@ class Health:
     def tick(self, **extra) -> bool:
         now = time.monotonic()
         dt = now - self.last_tick
-        if dt < self.TICK_S:
+        if self.TICK_S <= 0 or dt < self.TICK_S:          # an interval of 0 switches the periodic summary off
             return False
         log.info("engine.stats", steps_per_s=round(self.steps_since_tick / dt, 2),
                  rows_per_s=round(self.tokens_since_tick / dt, 1), mean_step_ms=round(self.mean_s * 1e3, 3), **extra)

@@ -78,6 +78,7 @@ class ServerState:
                                         enabled=svc.vision != "off")
         if svc.vision == "off":
             vision = None
+        llm.sched.health.TICK_S = float(svc.log_stats_interval)          # --log-stats-interval
         self.tokenizer = tokenizer
         cfg = llm.model.cfg
         self.formatter = ChatFormatter.for_checkpoint(
