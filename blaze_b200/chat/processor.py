@@ -33,6 +33,11 @@ class ChatResponseProcessor:
         self.tool_calls: List[ToolCall] = []
         self.stopped = False
 
+    @property
+    def stop_matched(self) -> Optional[str]:
+        """The stop string that ended the answer (None: it ended otherwise)."""
+        return self.cut.matched if self.cut is not None else None
+
     def _route(self, text: str, d: Delta, final: bool = False) -> None:
         r, c = (self.think.push(text) if self.think else ("", text))
         if final and self.think:

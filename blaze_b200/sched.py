@@ -49,6 +49,7 @@ class GenEvent:
     prompt_tokens: int = 0
     cached_tokens: int = 0
     hidden: Optional[torch.Tensor] = None     # embeddings requests
+    stopped_on: Optional[int] = None          # the last of ``tokens`` is the end-of-sequence / stop token that ended the generation
 
 
 @dataclass
@@ -1206,7 +1207,7 @@ class Scheduler:
             self.tpot.observe((now - a.t_last) / len(out))
         a.t_last = now
         self._emit(a, GenEvent(a.req.request_id, tokens=out, logprobs=lps or None, prompt_tokens=a.n_prompt,
-                               cached_tokens=a.cached))
+                               cached_tokens=a.cached, stopped_on=out[-1] if (finish == Finish.STOP and out) else None))
         if finish is not None:
             self._retire(a, finish)
 

@@ -27,6 +27,8 @@ from .. import __version__, log
 from ..chat import ChatFormatter, ChatResponseProcessor, get_think_parser, get_tool_parser
 from ..sampler import SamplingParams
 from ..sched import Finish, GenEvent, GenRequest, ThinkBudget
+from . import messages as anth
+from . import responses as rsp
 from ..service import (MAX_COMPLETIONS_PER_REQUEST, RequestError, ServiceArgs, sampling_of, stop_strings_of,
                        thinking_budget_of)
 from ..structured import forced_call_grammar, ConstraintError, Grammars, grammar_of
@@ -41,6 +43,10 @@ _current_request: "contextvars.ContextVar[Optional[Request]]" = contextvars.Cont
 
 
 def _err(status: int, message: str, typ: str = "invalid_request_error", param=None, code=None) -> JSONResponse:
+    """An error in the OpenAI shape; on the Messages routes in Anthropic's (``server/messages.rs:13``)."""
+    req = _current_request.get()
+    if req is not None and req.url.path.startswith("/v1/messages"):
+        return JSONResponse(anth.error_body(status, message), status_code=status)
     return JSONResponse({"error": {"message": message, "type": typ, "param": param, "code": code}}, status_code=status)
 
 
@@ -68,6 +74,7 @@ class ServerState:
         self.sem = asyncio.Semaphore(svc.max_concurrency)
         self.waiting = 0
         self.shutting_down = False
+        self.developer_as_system = False
 
     def attach(self, llm, tokenizer, vision=None) -> None:
         from .media import MediaPolicy
@@ -81,6 +88,9 @@ class ServerState:
         llm.sched.health.TICK_S = float(svc.log_stats_interval)          # --log-stats-interval
         self.tokenizer = tokenizer
         cfg = llm.model.cfg
+        tpl = getattr(tokenizer, "chat_template", None) or ""
+        # family encoders place developer turns themselves; a Jinja template that never names the role would reject them
+        self.developer_as_system = bool(tpl) and "developer" not in tpl
         self.formatter = ChatFormatter.for_checkpoint(
             self.model_name, {"model_type": cfg.model_type, "architectures": [cfg.architecture]},
             getattr(tokenizer, "chat_template", None), self.svc.chat_family or None)
@@ -173,6 +183,14 @@ class Gen:
         self.st.llm.sched.abort(self.rid)
 
 
+def shown(ev: GenEvent, include_stop: bool = False):
+    """(tokens, logprobs) of an event as the answer shows them: the end-of-sequence or stop token that ended the generation
+    is not part of the text unless the request asked for it (``include_stop_str_in_output``)."""
+    if ev.stopped_on is None or include_stop or not ev.tokens:
+        return ev.tokens, ev.logprobs
+    return ev.tokens[:-1], (ev.logprobs[:-1] if ev.logprobs else ev.logprobs)
+
+
 def finish_reason(f: Optional[Finish], tool_calls: bool = False, stopped_by_string: bool = False) -> str:
     if tool_calls:
         return "tool_calls"
@@ -213,6 +231,7 @@ def create_app(st: ServerState) -> FastAPI:
         if not rid or len(rid) > 128 or not all(c.isalnum() or c in "-_.:" for c in rid):
             rid = uuid.uuid4().hex          # absent or not a plain token: the server names the request
         path = request.url.path
+        _current_request.set(request)
         cors = {"x-request-id": rid}
         if st.svc.cors_origins:
             origin = request.headers.get("origin")
@@ -308,9 +327,9 @@ def create_app(st: ServerState) -> FastAPI:
     @app.exception_handler(_HTTPException)
     async def on_http_error(request: Request, e: _HTTPException):
         # unknown routes and wrong methods answer with the OpenAI error object too
-        msg = {404: f"no route {request.method} {request.url.path}", 405: f"method {request.method} is not allowed on {request.url.path}"}.get(
+        what = {404: f"no route {request.method} {request.url.path}", 405: f"method {request.method} is not allowed on {request.url.path}"}.get(
             e.status_code, str(e.detail))
-        return _err(e.status_code, msg, "invalid_request_error", code={404: "not_found", 405: "method_not_allowed"}.get(e.status_code))
+        return _err(e.status_code, what, "invalid_request_error", code={404: "not_found", 405: "method_not_allowed"}.get(e.status_code))
 
     @app.exception_handler(ConstraintError)
     async def on_constraint_error(request: Request, e: ConstraintError):
@@ -416,12 +435,16 @@ def create_app(st: ServerState) -> FastAPI:
         b = await _body(request)
         if "messages" in b:
             # what a chat request with the same body would use as its prompt (tools, tool_choice, template arguments)
-            text = _render_chat(b)[0]
+            _check_continuation(b, b["messages"] if isinstance(b["messages"], list) else [])
+            text, prefix, _ = _render_chat(b)
+            ids = st.tokenizer.encode(text, add_special_tokens=bool(b.get("add_special_tokens", False)))
+            if prefix:                        # a continued turn is tokenised on its own, after the prompt
+                ids = ids + st.tokenizer.encode(prefix, add_special_tokens=False)
         else:
             text = b.get("prompt", b.get("text"))
-        if not isinstance(text, str):
-            raise RequestError("prompt must be a string", "prompt")
-        ids = st.tokenizer.encode(text, add_special_tokens=bool(b.get("add_special_tokens", False)))
+            if not isinstance(text, str):
+                raise RequestError("prompt must be a string", "prompt")
+            ids = st.tokenizer.encode(text, add_special_tokens=bool(b.get("add_special_tokens", False)))
         out = {"tokens": ids, "count": len(ids), "max_model_len": st.max_len}
         if b.get("return_token_strs"):
             out["token_strs"] = [st.tokenizer.decode([t], skip_special_tokens=False) for t in ids]
@@ -524,6 +547,10 @@ def create_app(st: ServerState) -> FastAPI:
             # agent frameworks replay an assistant turn's reasoning under either name
             b = {**b, "messages": [({**m, "reasoning_content": m["reasoning"]} if isinstance(m, dict) and isinstance(m.get("reasoning"), str)
                                     and "reasoning_content" not in m else m) for m in msgs]}
+        if isinstance(msgs, list) and st.developer_as_system and any(isinstance(m, dict) and str(m.get("role", "")).lower() == "developer" for m in msgs):
+            # new OpenAI SDKs send system prompts as developer messages; a template that does not know the role gets them as system
+            b = {**b, "messages": [({**m, "role": "system"} if isinstance(m, dict) and str(m.get("role", "")).lower() == "developer" else m)
+                                   for m in b["messages"]]}
         try:
             return st.formatter.render_request(b, st.svc.chat_template_kwargs)
         except (ValueError, TypeError, IndexError, KeyError) as e:
@@ -599,9 +626,10 @@ def create_app(st: ServerState) -> FastAPI:
             for i, (g, proc) in enumerate(gens):
                 lps = []
                 async for ev in g.events():
-                    d = proc.push(ev.tokens)
-                    if ev.logprobs:
-                        lps.extend(ev.logprobs)
+                    toks, elp = shown(ev, include_stop)
+                    d = proc.push(toks)
+                    if elp:
+                        lps.extend(elp)
                     if d.stopped:
                         g.abort(cancelled=False)
                         break
@@ -610,11 +638,13 @@ def create_app(st: ServerState) -> FastAPI:
                 if g.finish == Finish.ERROR:
                     return _err(500, g.error or "generation failed", "server_error")
                 msg: Dict[str, Any] = {"role": "assistant", "content": proc.text or (None if proc.tool_calls else "")}
-                if proc.reasoning_text:
+                if proc.reasoning_text and b.get("include_reasoning") is not False:
                     msg["reasoning_content"] = proc.reasoning_text
                 if proc.tool_calls:
-                    msg["tool_calls"] = [{k: v for k, v in c.to_openai(j).items() if k != "index"} for j, c in enumerate(proc.tool_calls)]
-                ch = {"index": i, "message": msg, "finish_reason": finish_reason(g.finish, bool(proc.tool_calls), proc.stopped)}
+                    calls = proc.tool_calls[:1] if b.get("parallel_tool_calls") is False else proc.tool_calls
+                    msg["tool_calls"] = [{k: v for k, v in c.to_openai(j).items() if k != "index"} for j, c in enumerate(calls)]
+                ch = {"index": i, "message": msg, "finish_reason": finish_reason(g.finish, bool(proc.tool_calls), proc.stopped),
+                      "stop_reason": proc.stop_matched}
                 if want_lp:
                     ch["logprobs"] = {"content": [_lp_entry(st.tokenizer, l) for l in lps]}
                 choices.append(ch)
@@ -652,8 +682,9 @@ def create_app(st: ServerState) -> FastAPI:
                             out.append(_sse({**base, "choices": [ch]}))
                         return out
                     async for ev in g.events():
-                        d = proc.push(ev.tokens)
-                        for c in chunks_of(d, ev.logprobs if want_lp else None):
+                        toks, elp = shown(ev, include_stop)
+                        d = proc.push(toks)
+                        for c in chunks_of(d, elp if want_lp else None):
                             yield c
                         if d.stopped:
                             g.abort(cancelled=False)
@@ -663,7 +694,7 @@ def create_app(st: ServerState) -> FastAPI:
                     _account(g)
                     if g.finish == Finish.ERROR:
                         yield _sse({"error": {"message": g.error or "generation failed", "type": "server_error"}})
-                    yield _sse({**base, "choices": [{"index": i, "delta": {}, "finish_reason":
+                    yield _sse({**base, "choices": [{"index": i, "delta": {}, "stop_reason": proc.stop_matched, "finish_reason":
                                                      finish_reason(g.finish, bool(proc.tool_calls), proc.stopped)}]})
                 if include_usage:
                     yield _sse({**base, "choices": [], "usage": _usage(len(ids), sum(g.n_out for g, _ in gens), gens[0][0].cached)})
@@ -735,9 +766,10 @@ def create_app(st: ServerState) -> FastAPI:
             for i, (g, proc, p) in enumerate(gens):
                 lps = []
                 async for ev in g.events():
-                    d = proc.push(ev.tokens)
-                    if ev.logprobs:
-                        lps.extend(ev.logprobs)
+                    toks, elp = shown(ev, include_stop)
+                    d = proc.push(toks)
+                    if elp:
+                        lps.extend(elp)
                     if d.stopped:
                         g.abort(cancelled=False)
                         break
@@ -746,7 +778,8 @@ def create_app(st: ServerState) -> FastAPI:
                 if g.finish == Finish.ERROR:
                     return _err(500, g.error or "generation failed", "server_error")
                 text = (st.tokenizer.decode(p) if echo else "") + proc.text
-                ch = {"index": i, "text": text, "finish_reason": finish_reason(g.finish, False, proc.stopped), "logprobs": None}
+                ch = {"index": i, "text": text, "finish_reason": finish_reason(g.finish, False, proc.stopped), "logprobs": None,
+                      "stop_reason": proc.stop_matched}
                 if params.logprobs is not None:
                     ch["logprobs"] = lp_obj(lps)
                 choices.append(ch)
@@ -766,9 +799,10 @@ def create_app(st: ServerState) -> FastAPI:
                     sent = 0                     # characters of this choice's text already sent (text_offset of the next token)
                     pend_lp = []
                     async for ev in g.events():
-                        d = proc.push(ev.tokens)
-                        if ev.logprobs and params.logprobs is not None:
-                            pend_lp.extend(ev.logprobs)
+                        toks, elp = shown(ev, include_stop)
+                        d = proc.push(toks)
+                        if elp and params.logprobs is not None:
+                            pend_lp.extend(elp)
                         if d.content or pend_lp:
                             ch = {"index": i, "text": d.content or "", "finish_reason": None}
                             if params.logprobs is not None:
@@ -838,120 +872,94 @@ def create_app(st: ServerState) -> FastAPI:
         return {"object": "list", "data": data, "model": st.model_name, "usage": {"prompt_tokens": total, "total_tokens": total}}
 
     # ------------------------------------------------------------------ /v1/responses (OpenAI Responses API adapter)
-    def _responses_to_messages(b) -> List[Dict[str, Any]]:
-        msgs: List[Dict[str, Any]] = []
-        prev = b.get("previous_response_id")
-        if prev:
-            old = st.responses.get(prev)
-            if old is None:
-                raise RequestError(f"previous response {prev!r} not found", "previous_response_id", "not_found", 404)
-            msgs.extend(old["_messages"])
-        if b.get("instructions"):
-            msgs.insert(0, {"role": "system", "content": b["instructions"]})
-        inp = b.get("input")
-        if isinstance(inp, str):
-            msgs.append({"role": "user", "content": inp})
-        elif isinstance(inp, list):
-            for it in inp:
-                t = it.get("type", "message")
-                if t == "message":
-                    msgs.append({"role": it.get("role", "user"), "content": it.get("content")})
-                elif t == "function_call":
-                    msgs.append({"role": "assistant", "content": None, "tool_calls": [
-                        {"id": it.get("call_id"), "type": "function", "function": {"name": it.get("name"), "arguments": it.get("arguments", "{}")}}]})
-                elif t == "function_call_output":
-                    msgs.append({"role": "tool", "tool_call_id": it.get("call_id"), "content": it.get("output", "")})
-        else:
-            raise RequestError("input must be a string or a list of items", "input")
-        return msgs
-
     @app.post("/v1/responses")
     async def responses(request: Request):
         b = await _body(request)
         _check_model(b)
-        msgs = _responses_to_messages(b)
-        tools = [{"type": "function", "function": {k: v for k, v in t.items() if k != "type"}} for t in (b.get("tools") or [])
-                 if t.get("type") == "function"] or None
-        cb = {**b, "messages": msgs, "tools": tools, "max_tokens": b.get("max_output_tokens")}
-        effort = (b.get("reasoning") or {}).get("effort") if isinstance(b.get("reasoning"), dict) else None
-        if effort is not None:
-            # "minimal": as little as possible, i.e. no thinking section for a model that has one
-            cb.pop("reasoning", None)
-            cb["reasoning_effort"] = "none" if effort == "minimal" else effort
-        tf = (b.get("text") or {}).get("format")
-        if isinstance(tf, dict) and tf.get("type") in ("json_schema", "json_object"):
-            cb["response_format"] = {"type": tf["type"], "json_schema": {"schema": tf.get("schema", {})}}
+        kept = None
+        prev = b.get("previous_response_id")
+        if prev:
+            old = st.responses.get(prev)
+            if old is None:
+                raise RequestError(f"no response with id {prev!r} is kept", "previous_response_id", "not_found", 404)
+            kept = old["_messages"]
+        cb, msgs, custom = rsp.chat_request(b, kept)
         ids, params, tools_p, enable_thinking, spec, mm, in_think = await _prepare_chat(cb)
-        rid, created = "resp_" + uuid.uuid4().hex[:24], int(time.time())
+        rid = rsp.new_id("resp")
         cons = st.grammars.constraint(spec) if spec else None
         g = Gen(st, ids, params, cache_point=_cache_point(ids), constraint=cons, mm=mm)
-        proc = ChatResponseProcessor(st.tokenizer, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
+        proc = ChatResponseProcessor(st.tokenizer, stop_strings_of(cb),
+                                     reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
                                      tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None,
                                      think_parser=_think_parser(st, in_think))
-        stream = bool(b.get("stream", False))
+        single = cb.get("parallel_tool_calls") is False
 
-        def build(status: str) -> Dict[str, Any]:
-            output = []
-            if proc.reasoning_text:
-                output.append({"type": "reasoning", "id": "rs_" + rid[5:], "summary": [{"type": "summary_text", "text": proc.reasoning_text}]})
-            if proc.text or not proc.tool_calls:
-                output.append({"type": "message", "id": "msg_" + rid[5:], "role": "assistant", "status": "completed",
-                               "content": [{"type": "output_text", "text": proc.text, "annotations": []}]})
-            for c in proc.tool_calls:
-                output.append({"type": "function_call", "id": "fc_" + c.id[5:], "call_id": c.id, "name": c.name,
-                               "arguments": c.arguments, "status": "completed"})
-            return {"id": rid, "object": "response", "created_at": created, "status": status, "model": st.model_name,
-                    "output": output, "output_text": proc.text,
-                    "incomplete_details": {"reason": "max_output_tokens"} if g.finish == Finish.LENGTH else None,
-                    "usage": {"input_tokens": len(ids), "output_tokens": g.n_out, "total_tokens": len(ids) + g.n_out,
-                              "input_tokens_details": {"cached_tokens": g.cached}},
-                    "previous_response_id": b.get("previous_response_id")}
+        def calls():
+            return proc.tool_calls[:1] if single else proc.tool_calls
 
-        def remember(obj):
+        def use():
+            return rsp.usage(len(ids), g.n_out, g.cached)
+
+        def remember(obj, reasoning, text):
             if b.get("store", True):
-                kept = dict(obj)
-                am: Dict[str, Any] = {"role": "assistant", "content": proc.text}
-                if proc.tool_calls:
-                    am["tool_calls"] = [{k: v for k, v in c.to_openai().items() if k != "index"} for c in proc.tool_calls]
-                kept["_messages"] = [m for m in msgs if m.get("role") != "system"] + [am]
-                st.responses[rid] = kept
+                st.responses[rid] = {**obj, "_messages": rsp.kept_messages(msgs, reasoning, text, calls())}
                 while len(st.responses) > RESPONSES_KEPT:
                     st.responses.popitem(last=False)
 
-        if not stream:
+        if not cb.get("stream"):
             async for ev in g.events():
-                proc.push(ev.tokens)
+                if proc.push(shown(ev)[0]).stopped:
+                    g.abort(cancelled=False)
+                    break
             proc.finish()
             _account(g)
             if g.finish == Finish.ERROR:
                 return _err(500, g.error or "generation failed", "server_error")
-            obj = build("incomplete" if g.finish == Finish.LENGTH else "completed")
-            remember(obj)
+            length = g.finish == Finish.LENGTH and not proc.stopped
+            reasoning, text = rsp.settle(proc.reasoning_text, proc.text, len(calls()), not length)
+            obj = rsp.shell(b, rid, st.model_name, "incomplete" if length else "completed")
+            obj["output"] = rsp.output_items(reasoning, text, calls(), custom)
+            obj["output_text"] = text
+            obj["usage"] = use()
+            if length:
+                obj["incomplete_details"] = {"reason": "max_output_tokens"}
+            remember(obj, reasoning, text)
             return obj
 
         async def gen_stream():
-            seq = 0
+            es = rsp.EventStream(b, rid, st.model_name, custom)
+            sent = 0
 
-            def evt(typ, **kw):
-                nonlocal seq
-                seq += 1
-                return (f"event: {typ}\n" + "data: " + json.dumps({"type": typ, "sequence_number": seq, **kw}, ensure_ascii=False) + "\n\n").encode()
-            yield evt("response.created", response={"id": rid, "object": "response", "status": "in_progress", "model": st.model_name})
+            def wire(pairs):
+                return b"".join((f"event: {k}\n" + "data: " + json.dumps(v, ensure_ascii=False) + "\n\n").encode() for k, v in pairs)
+
+            def route(d):
+                nonlocal sent
+                pairs = es.on_reasoning(d.reasoning) + es.on_text(d.content)
+                for c in d.tool_calls:
+                    if not (single and sent):
+                        pairs += es.on_call(c)
+                    sent += 1
+                return pairs
+            yield wire(es.start())
             try:
                 async for ev in g.events():
-                    d = proc.push(ev.tokens)
-                    if d.reasoning:
-                        yield evt("response.reasoning_summary_text.delta", delta=d.reasoning, item_id="rs_" + rid[5:])
-                    if d.content:
-                        yield evt("response.output_text.delta", delta=d.content, item_id="msg_" + rid[5:], output_index=0, content_index=0)
-                d = proc.finish()
-                if d.content:
-                    yield evt("response.output_text.delta", delta=d.content, item_id="msg_" + rid[5:], output_index=0, content_index=0)
+                    d = proc.push(shown(ev)[0])
+                    pairs = route(d)
+                    if pairs:
+                        yield wire(pairs)
+                    if d.stopped:
+                        g.abort(cancelled=False)
+                        break
+                pairs = route(proc.finish())
                 _account(g)
-                obj = build("incomplete" if g.finish == Finish.LENGTH else "completed")
-                remember(obj)
-                yield evt("response.output_text.done", text=proc.text, item_id="msg_" + rid[5:])
-                yield evt("response.completed", response=obj)
+                if g.finish == Finish.ERROR:
+                    yield wire(pairs + es.failed(g.error or "generation failed"))
+                    return
+                length = g.finish == Finish.LENGTH and not proc.stopped
+                pairs += es.finish(length, not length, len(calls()), use())
+                remember(es.resp, es.reasoning, es.text)
+                yield wire(pairs)
             finally:
                 if g.finish is None:
                     g.abort()
@@ -971,163 +979,75 @@ def create_app(st: ServerState) -> FastAPI:
         return {"id": rid, "object": "response.deleted", "deleted": True}
 
     # ------------------------------------------------------------------ /v1/messages (Anthropic Messages adapter)
-    def _anthropic_to_chat(b) -> Dict[str, Any]:
-        msgs: List[Dict[str, Any]] = []
-        sysm = b.get("system")
-        if isinstance(sysm, list):
-            sysm = "".join(p.get("text", "") for p in sysm if p.get("type") == "text")
-        if sysm:
-            msgs.append({"role": "system", "content": sysm})
-        for m in b.get("messages") or []:
-            role, content = m.get("role"), m.get("content")
-            if isinstance(content, str):
-                msgs.append({"role": role, "content": content})
-                continue
-            text, calls = [], []
-            for p in content or []:
-                t = p.get("type")
-                if t == "text":
-                    text.append(p.get("text", ""))
-                elif t == "tool_use":
-                    calls.append({"id": p.get("id"), "type": "function", "function": {"name": p.get("name"), "arguments": json.dumps(p.get("input", {}))}})
-                elif t == "tool_result":
-                    c = p.get("content")
-                    if isinstance(c, list):
-                        c = "".join(x.get("text", "") for x in c if x.get("type") == "text")
-                    msgs.append({"role": "tool", "tool_call_id": p.get("tool_use_id"), "content": c or ""})
-                elif t == "image":
-                    src = p.get("source", {})
-                    if src.get("type") == "base64":
-                        text.append("")
-                        msgs.append({"role": role, "content": [{"type": "image_url", "image_url": {"url": f"data:{src.get('media_type')};base64,{src.get('data')}"}}]})
-            if text or calls:
-                mm: Dict[str, Any] = {"role": role, "content": "".join(text)}
-                if calls:
-                    mm["tool_calls"] = calls
-                msgs.append(mm)
-        tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
-                                                   "parameters": t.get("input_schema", {})}} for t in (b.get("tools") or [])] or None
-        out = {**{k: v for k, v in b.items() if k in ("temperature", "top_p", "top_k", "stop_sequences", "stream", "model")},
-               "messages": msgs, "tools": tools, "max_tokens": b.get("max_tokens")}
-        if b.get("stop_sequences"):
-            out["stop"] = b["stop_sequences"]
-        th = b.get("thinking") or {}
-        if th.get("type") == "enabled":
-            out["enable_thinking"] = True
-            if th.get("budget_tokens"):
-                out["thinking_token_budget"] = th["budget_tokens"]
-        elif th.get("type") == "disabled":
-            out["enable_thinking"] = False
-        if "enable_thinking" in out:       # the families' templates read one of the two names
-            out["chat_template_kwargs"] = {"enable_thinking": out["enable_thinking"], "thinking": out["enable_thinking"]}
-        return out
-
     @app.post("/v1/messages/count_tokens")
     async def count_tokens(request: Request):
         b = await _body(request)
-        cb = _anthropic_to_chat(b)
-        text, prefix, _ = _render_chat(cb)
+        text, prefix, _ = _render_chat(anth.chat_request(b))
         return {"input_tokens": len(st.tokenizer.encode(text)) + (len(st.tokenizer.encode(prefix, add_special_tokens=False)) if prefix else 0)}
 
     @app.post("/v1/messages")
     async def messages(request: Request):
         b = await _body(request)
-        if not isinstance(b.get("max_tokens"), int):
+        if not isinstance(b.get("max_tokens"), int) or isinstance(b.get("max_tokens"), bool):
             raise RequestError("max_tokens is required", "max_tokens")
-        cb = _anthropic_to_chat(b)
+        _check_model(b)
+        cb = anth.chat_request(b)
         ids, params, tools_p, enable_thinking, spec, mm, in_think = await _prepare_chat(cb)
-        stops = stop_strings_of(cb)
-        mid = "msg_" + uuid.uuid4().hex[:24]
-        g = Gen(st, ids, params, cache_point=_cache_point(ids), mm=mm)
-        proc = ChatResponseProcessor(st.tokenizer, stops, reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
+        mid = anth.new_id("msg")
+        cons = st.grammars.constraint(spec) if spec else None
+        g = Gen(st, ids, params, cache_point=_cache_point(ids), constraint=cons, mm=mm)
+        proc = ChatResponseProcessor(st.tokenizer, stop_strings_of(cb),
+                                     reasoning=st.svc.reasoning_parser is not None and enable_thinking is not False,
                                      tool_parser=get_tool_parser(st.svc.tool_call_parser, tools_p) if tools_p else None,
                                      think_parser=_think_parser(st, in_think))
+        single = cb.get("parallel_tool_calls") is False
 
-        def stop_reason():
-            if proc.tool_calls:
-                return "tool_use"
-            if proc.stopped:
-                return "stop_sequence"
-            return "max_tokens" if g.finish == Finish.LENGTH else "end_turn"
-
-        def blocks():
-            out = []
-            if proc.reasoning_text:
-                out.append({"type": "thinking", "thinking": proc.reasoning_text, "signature": ""})
-            if proc.text or not proc.tool_calls:
-                out.append({"type": "text", "text": proc.text})
-            for c in proc.tool_calls:
-                try:
-                    inp = json.loads(c.arguments)
-                except ValueError:
-                    inp = {"_raw": c.arguments}
-                out.append({"type": "tool_use", "id": c.id.replace("call_", "toolu_"), "name": c.name, "input": inp})
-            return out
-
-        if not b.get("stream"):
+        if not cb.get("stream"):
             async for ev in g.events():
-                d = proc.push(ev.tokens)
-                if d.stopped:
+                if proc.push(shown(ev)[0]).stopped:
                     g.abort(cancelled=False)
                     break
             proc.finish()
             _account(g)
             if g.finish == Finish.ERROR:
                 return JSONResponse({"type": "error", "error": {"type": "api_error", "message": g.error or "generation failed"}}, status_code=500)
-            return {"id": mid, "type": "message", "role": "assistant", "model": st.model_name, "content": blocks(),
-                    "stop_reason": stop_reason(), "stop_sequence": None,
-                    "usage": {"input_tokens": len(ids), "output_tokens": g.n_out, "cache_read_input_tokens": g.cached}}
+            calls = proc.tool_calls[:1] if single else proc.tool_calls
+            length = g.finish == Finish.LENGTH and not proc.stopped
+            reasoning, text = rsp.settle(proc.reasoning_text, proc.text, len(calls), not length)
+            reason, sequence = anth.stop_reason(length, bool(calls), proc.stop_matched)
+            return {"id": mid, "type": "message", "role": "assistant", "model": b.get("model") or st.model_name,
+                    "content": anth.blocks(reasoning, text, calls), "stop_reason": reason, "stop_sequence": sequence,
+                    "usage": anth.usage(len(ids), g.n_out, g.cached)}
 
         async def gen_stream():
-            def evt(typ, **kw):
-                return (f"event: {typ}\n" + "data: " + json.dumps({"type": typ, **kw}, ensure_ascii=False) + "\n\n").encode()
-            yield evt("message_start", message={"id": mid, "type": "message", "role": "assistant", "model": st.model_name, "content": [],
-                                                "stop_reason": None, "usage": {"input_tokens": len(ids), "output_tokens": 0}})
-            idx, open_kind = -1, None
+            bs = anth.BlockStream(mid, b.get("model") or st.model_name, len(ids))
 
-            def open_block(kind):
-                nonlocal idx, open_kind
-                out = []
-                if open_kind is not None and open_kind != kind:
-                    out.append(evt("content_block_stop", index=idx))
-                    open_kind = None
-                if open_kind is None:
-                    idx += 1
-                    open_kind = kind
-                    cb_ = {"type": "thinking", "thinking": ""} if kind == "thinking" else {"type": "text", "text": ""}
-                    out.append(evt("content_block_start", index=idx, content_block=cb_))
+            def wire(events):
+                return b"".join((f"event: {e['type']}\n" + "data: " + json.dumps(e, ensure_ascii=False) + "\n\n").encode() for e in events)
+
+            def route(d):
+                out = bs.on_reasoning(d.reasoning) + bs.on_text(d.content)
+                for c in d.tool_calls:
+                    if not (single and bs.calls):
+                        out += bs.on_call(c)
                 return out
+            yield wire(bs.start())
             try:
-                async def emit(d):
-                    out = []
-                    if d.reasoning:
-                        out += open_block("thinking")
-                        out.append(evt("content_block_delta", index=idx, delta={"type": "thinking_delta", "thinking": d.reasoning}))
-                    if d.content:
-                        out += open_block("text")
-                        out.append(evt("content_block_delta", index=idx, delta={"type": "text_delta", "text": d.content}))
-                    return out
                 async for ev in g.events():
-                    d = proc.push(ev.tokens)
-                    for c in await emit(d):
-                        yield c
+                    d = proc.push(shown(ev)[0])
+                    out = route(d)
+                    if out:
+                        yield wire(out)
                     if d.stopped:
                         g.abort(cancelled=False)
                         break
-                for c in await emit(proc.finish()):
-                    yield c
-                nonlocal_idx = idx
-                if open_kind is not None:
-                    yield evt("content_block_stop", index=nonlocal_idx)
-                for c in proc.tool_calls:
-                    nonlocal_idx += 1
-                    yield evt("content_block_start", index=nonlocal_idx, content_block={"type": "tool_use", "id": c.id.replace("call_", "toolu_"),
-                                                                                      "name": c.name, "input": {}})
-                    yield evt("content_block_delta", index=nonlocal_idx, delta={"type": "input_json_delta", "partial_json": c.arguments})
-                    yield evt("content_block_stop", index=nonlocal_idx)
+                out = route(proc.finish())
                 _account(g)
-                yield evt("message_delta", delta={"stop_reason": stop_reason(), "stop_sequence": None}, usage={"output_tokens": g.n_out})
-                yield evt("message_stop")
+                if g.finish == Finish.ERROR:
+                    yield wire(out + bs.error(g.error or "generation failed"))
+                    return
+                length = g.finish == Finish.LENGTH and not proc.stopped
+                yield wire(out + bs.finish(length, proc.stop_matched, g.n_out, g.cached))
             finally:
                 if g.finish is None:
                     g.abort()

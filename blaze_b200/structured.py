@@ -69,9 +69,14 @@ class ChoiceConstraint(Constraint):
 
 
 class LLGuidanceConstraint(Constraint):
-    def __init__(self, ll_tokenizer, grammar: str, vocab_size: int):
+    """``eos_ids``: every token that ends a generation.  The matcher knows one end-of-sequence token (the first); where it
+    allows that one, all are allowed (a chat model ends its turn with ``<|im_end|>``, not ``<|endoftext|>``), and any of
+    them is consumed as that one."""
+
+    def __init__(self, ll_tokenizer, grammar: str, vocab_size: int, eos_ids: Sequence[int] = ()):
         import llguidance
         self.V = vocab_size
+        self.eos = [int(e) for e in eos_ids if int(e) < vocab_size]
         self.m = llguidance.LLMatcher(ll_tokenizer, grammar)
         err = self.m.get_error()
         if err:
@@ -83,15 +88,21 @@ class LLGuidanceConstraint(Constraint):
         if pending:
             m = m.deep_copy()
             for t in pending:
-                m.consume_token(int(t))
+                m.consume_token(self._as_matcher_token(t))
         bits = llt.allocate_token_bitmask(1, self.V)
         llt.fill_next_token_bitmask(m, bits, 0)
         words = bits[0].to(torch.int64) & 0xFFFFFFFF
         idx = torch.arange(self.V)
-        return ((words[idx // 32] >> (idx % 32)) & 1).bool()
+        out = ((words[idx // 32] >> (idx % 32)) & 1).bool()
+        if self.eos and bool(out[self.eos[0]]):
+            out[self.eos] = True
+        return out
+
+    def _as_matcher_token(self, token: int) -> int:
+        return self.eos[0] if self.eos and int(token) in self.eos else int(token)
 
     def advance(self, token: int) -> None:
-        self.m.consume_token(int(token))
+        self.m.consume_token(self._as_matcher_token(token))
 
     def finished(self) -> bool:
         return self.m.is_stopped()
@@ -165,7 +176,7 @@ class Grammars:
             g = llguidance.LLMatcher.grammar_from_lark(spec["grammar"])
         else:
             raise ConstraintError(f"unknown structured-output kind {kind!r}")
-        return LLGuidanceConstraint(self.ll_tok, g, self.V)
+        return LLGuidanceConstraint(self.ll_tok, g, self.V, self.eos)
 
 
 def grammar_of(body: Dict[str, Any], max_ws: int = 64) -> Optional[Dict[str, Any]]:

@@ -167,6 +167,7 @@ class StopCutter:
         self.include = include
         self.buf = ""
         self.done = False
+        self.matched: Optional[str] = None       # the stop string that ended the text
 
     def push(self, text: str):
         """Returns (text safe to emit, stopped?)."""
@@ -180,7 +181,7 @@ class StopCutter:
                 first = (i, s)
         if first is not None:
             end = first[0] + (len(first[1]) if self.include else 0)
-            out, self.buf, self.done = self.buf[:end], "", True
+            out, self.buf, self.done, self.matched = self.buf[:end], "", True, first[1]
             return out, True
         hold = 0
         for s in self.stops:
