@@ -72,6 +72,20 @@ class ModelConfig:
     norm_topk_prob: bool = True
     # MTP
     mtp_num_hidden_layers: int = 0
+    # Qwen4-Exp extras (``crates/blaze/src/config.rs:56-80``, :181-212): hyper-connections, per-layer n-gram embedding,
+    # sparse-attention indexer
+    hc_count: int = 0                       # residual streams (0 or 1: plain pre-norm residual)
+    hc_lowrank: int = 16
+    ple_layers: List[int] = field(default_factory=list)      # decoder layers that add an n-gram embedding (0-based)
+    ngram_size: int = 3
+    heads_per_ngram: int = 0
+    ple_embed_dim: int = 0
+    ple_conv_kernel: int = 4
+    gdn_output_gate: str = "silu"           # activation of the Gated DeltaNet output gate: "silu" | "sigmoid"
+    indexer_heads: int = 0                  # > 0: the checkpoint carries a sparse-attention indexer (not used: dense attention)
+    indexer_head_dim: int = 0
+    indexer_budget: int = 0
+    indexer_compress_ratio: int = 0
     # tokens
     eos_token_ids: List[int] = field(default_factory=list)
     bos_token_id: Optional[int] = None
@@ -89,6 +103,10 @@ class ModelConfig:
     @property
     def has_gdn(self) -> bool:
         return any(t == "linear_attention" for t in self.layer_types)
+
+    @property
+    def has_hc(self) -> bool:
+        return self.hc_count > 1
 
     @property
     def rotary_dim(self) -> int:
@@ -179,6 +197,21 @@ class ModelConfig:
             vision_config=raw.get("vision_config"),
         )
         cfg._add_eos(g("eos_token_id"))
+        hc = int(g("hc_count", 0) or 0)
+        if hc > 1:
+            cfg.hc_count, cfg.hc_lowrank = hc, int(g("hc_lowrank", 16) or 16)
+        ple_ids = g("ple_layer_ids")
+        if ple_ids:
+            # the checkpoint counts layers from 1 (SGLang: layer_id + 1 in ple_layer_ids)
+            cfg.ple_layers = [int(i) - 1 for i in ple_ids if int(i) >= 1]
+            cfg.ngram_size = int(g("ngram_size"))
+            cfg.heads_per_ngram = int(g("heads_per_ngram"))
+            cfg.ple_embed_dim = int(g("ple_embed_dim"))
+            cfg.ple_conv_kernel = int(g("ple_conv_kernel_size", 4) or 4)
+        cfg.gdn_output_gate = str(g("output_gate_type", "silu") or "silu")
+        if g("indexer_n_heads"):
+            cfg.indexer_heads, cfg.indexer_head_dim = int(g("indexer_n_heads")), int(g("indexer_head_dim", 0) or 0)
+            cfg.indexer_budget, cfg.indexer_compress_ratio = int(g("indexer_budget", 0) or 0), int(g("indexer_compress_ratio", 0) or 0)
         # layer pattern
         lt = g("layer_types")
         if lt:
@@ -195,10 +228,10 @@ class ModelConfig:
             else:
                 cfg.layer_types = ["full_attention"] * n_layers
         # architecture family switches
-        hybrid = cfg.has_gdn or model_type in ("qwen3_next", "qwen3_5", "qwen3_5_moe", "qwen3_6", "qwen3_8")
+        hybrid = cfg.has_gdn or model_type in ("qwen3_next", "qwen3_5", "qwen3_5_moe", "qwen3_6", "qwen3_8", "qwen4_exp")
         cfg.attn_output_gate = bool(g("attn_output_gate", hybrid))
         cfg.zero_centered_norm = bool(g("zero_centered_norm", hybrid))
-        cfg.qk_norm = bool(g("qk_norm", model_type.startswith("qwen3")))
+        cfg.qk_norm = bool(g("qk_norm", model_type.startswith(("qwen3", "qwen4"))))
         # rope
         rp = g("rope_parameters") or g("rope_scaling") or {}
         rope = RopeConfig(
@@ -265,6 +298,13 @@ def named_config(name: str) -> ModelConfig:
                         linear_conv_kernel_dim=4, attn_output_gate=True, zero_centered_norm=True,
                         rope=RopeConfig(theta=1e6, partial_rotary_factor=0.25))
         c.layer_types = ["linear_attention", "full_attention", "linear_attention", "full_attention"]
+    elif n in ("tiny-qwen4",):
+        # the hybrid in miniature with two residual streams and an n-gram embedding on two of its layers
+        c = named_config("tiny-hybrid")
+        c.architecture, c.model_type = "Qwen4ExpForCausalLM", "qwen4_exp"
+        c.hc_count, c.hc_lowrank = 2, 8
+        c.ple_layers, c.ngram_size, c.heads_per_ngram, c.ple_embed_dim, c.ple_conv_kernel = [0, 2], 3, 2, 16, 4
+        c.eos_token_ids = [1]
     elif n in ("qwen3-8b",):
         c = ModelConfig(vocab_size=151936, hidden_size=4096, num_layers=36, num_heads=32, num_kv_heads=8,
                         head_dim=128, intermediate_size=12288, rope=RopeConfig(theta=1e6))

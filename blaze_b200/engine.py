@@ -124,6 +124,9 @@ class Engine:
         cfg = model.cfg
         self.device = model.device
         tpw = model.tp.world
+        if cfg.has_hc and ecfg.use_graphs:
+            # the stream mixing and the n-gram embedding index their state rows from the host: nothing of it is captured
+            ecfg.use_graphs = False
         per_tok = max(kv_bytes_per_token(cfg, ecfg.kv_dtype, tpw), 1)
         kv_tokens = ecfg.kv_tokens
         if kv_tokens <= 0:

@@ -83,6 +83,15 @@ class KVCache:
                 self.rec_state[i] = torch.zeros(self.state_rows, hv, cfg.linear_key_head_dim,
                                                 cfg.linear_value_head_dim, dtype=torch.float32, device=device)
 
+        # n-gram embedding layers of this stage keep a token window and a convolution history per row
+        self.ple = None
+        ple_layers = [i for i in range(lo, hi) if i in set(getattr(cfg, "ple_layers", ()) or ())]
+        if ple_layers:
+            if not self.gdn_layers:
+                raise ValueError("per-layer n-gram embeddings are kept with the recurrent state rows: the model needs linear-attention layers")
+            from .models.qwen4 import PleState
+            self.ple = PleState(cfg, ple_layers, self.state_rows, torch.float32 if kv_dtype == "fp32" else torch.bfloat16, device)
+
     # ------------------------------------------------------------------ block table
     def set_pages(self, row: int, pages: List[int], start: int = 0) -> None:
         """Record pages ``start..`` of sequence row ``row`` (host mirror + device)."""
@@ -123,7 +132,7 @@ class KVCache:
         n = 0
         for d in (self.k, self.v, self.kv, self.conv_state, self.rec_state):
             n += sum(t.numel() * t.element_size() for t in d.values())
-        return n
+        return n + (self.ple.nbytes() if self.ple is not None else 0)
 
     # ------------------------------------------------------------------ recurrent state rows
     def copy_state(self, src: int, dst: int) -> None:
@@ -131,11 +140,15 @@ class KVCache:
         for i in self.gdn_layers:
             self.conv_state[i][dst].copy_(self.conv_state[i][src])
             self.rec_state[i][dst].copy_(self.rec_state[i][src])
+        if self.ple is not None:
+            self.ple.copy(src, dst)
 
     def zero_state(self, row: int) -> None:
         for i in self.gdn_layers:
             self.conv_state[i][row].zero_()
             self.rec_state[i][row].zero_()
+        if self.ple is not None:
+            self.ple.zero(row)
 
     # ------------------------------------------------------------------ row moves (tree speculation)
     def move_rows(self, moves: Sequence[Sequence[tuple]], ops=None) -> None:

@@ -85,6 +85,9 @@ class Layer:
         self.attn: Optional[Attn] = None
         self.gdn: Optional[Gdn] = None
         self.mlp = None
+        # Qwen4-Exp: hyper-connections around the two blocks (in place of the norms above) and an n-gram embedding
+        self.hc_attn = self.hc_mlp = None
+        self.ple = None
 
 
 _PROFILE_PHASES = os.environ.get("BLAZE_PROFILE_PHASES", "0") == "1"
@@ -171,6 +174,13 @@ class Model:
         self.capture_layers: List[int] = []                   # hidden states kept for drafters
         self.captured: Dict[int, torch.Tensor] = {}
         self.gdn_records: Dict[int, tuple] = {}               # per GDN layer: inputs of the last step that deferred state
+        self.ple_records: Dict = {}                           # per n-gram embedding layer: the same for its convolution
+        self.hc_final = None                                  # hyper-connection that reads the streams out (last stage)
+        if cfg.has_hc and (self.tp.world > 1 or first_layer != 0 or self.last_layer != cfg.num_layers):
+            # as in the reference (crates/blaze/src/model.rs:1077): the streams are not cut over ranks or stages
+            raise ValueError("hyper-connection models run on one rank (no tensor or pipeline parallelism)")
+        if cfg.ple_layers and not cfg.has_hc:
+            raise ValueError("per-layer n-gram embeddings are defined on hyper-connection streams (hc_count > 1)")
         self.weight_format = Format.DENSE
 
     @property
@@ -234,6 +244,13 @@ class Model:
             L.kind = cfg.layer_type(i)
             base = 100 + i * 50
             L.input_norm, L.post_norm = ones(H), ones(H)
+            if cfg.has_hc:
+                from . import qwen4
+                L.hc_attn = qwen4.random_hc(rnd, H, cfg.hc_count, cfg.hc_lowrank, 7000 + i * 20, dtype)
+                L.hc_mlp = qwen4.random_hc(rnd, H, cfg.hc_count, cfg.hc_lowrank, 7000 + i * 20 + 5, dtype)
+                if i in cfg.ple_layers:
+                    L.ple = qwen4.random_ple(rnd, cfg, 7000 + i * 20 + 10, dtype, device,
+                                             lambda w: _tag(Linear.from_dense(w, Format.DENSE, dtype=dtype), Cut.ALL))
             if L.kind == "full_attention":
                 A = Attn()
                 A.heads, A.kv_heads = cfg.num_heads // tpw, max(cfg.num_kv_heads // tpw, 1)
@@ -326,6 +343,9 @@ class Model:
             m.layers.append(L)
         if m.is_last_stage:
             m.final_norm = ones(H)
+            if cfg.has_hc:
+                from . import qwen4
+                m.hc_final = qwen4.random_hc(rnd, H, cfg.hc_count, cfg.hc_lowrank, 6990, dtype, inject=False)
             if cfg.tie_word_embeddings:
                 wl = m.embed.float()
             else:
@@ -367,8 +387,15 @@ class Model:
             L = Layer()
             L.kind = cfg.layer_type(i)
             lp = f"{p}layers.{i}."
-            L.input_norm = vec(lp + "input_layernorm.weight")
-            L.post_norm = vec(lp + "post_attention_layernorm.weight")
+            if cfg.has_hc:
+                from . import qwen4
+                L.hc_attn = qwen4.load_hc(ck, lp + "attn_hyper_connection.", dtype, device)
+                L.hc_mlp = qwen4.load_hc(ck, lp + "mlp_hyper_connection.", dtype, device)
+                if i in cfg.ple_layers:
+                    L.ple = qwen4.load_ple(ck, lp + "ple.", cfg, dtype, device, lambda mods: load_lin(mods, Cut.ALL))
+            else:
+                L.input_norm = vec(lp + "input_layernorm.weight")
+                L.post_norm = vec(lp + "post_attention_layernorm.weight")
             if L.kind == "full_attention":
                 A = Attn()
                 A.heads, A.kv_heads = cfg.num_heads // tpw, max(cfg.num_kv_heads // tpw, 1)
@@ -448,7 +475,11 @@ class Model:
                 L.mlp = P
             m.layers.append(L)
         if m.is_last_stage:
-            m.final_norm = vec(f"{p}norm.weight")
+            if cfg.has_hc:
+                from . import qwen4
+                m.hc_final = qwen4.load_hc(ck, f"{p}hyper_connection_mixer.", dtype, device, inject=False)
+            else:
+                m.final_norm = vec(f"{p}norm.weight")
             if cfg.tie_word_embeddings or "lm_head.weight" not in ck:
                 wl = m.embed.float()
                 if tpw > 1:
@@ -479,6 +510,8 @@ class Model:
                 # image tokens: the vision tower's rows take the place of the pad tokens' embeddings
                 for r0, t in batch.embed_over:
                     x[r0:r0 + t.shape[0]] = t.to(device=x.device, dtype=x.dtype)
+        if cfg.has_hc:
+            return self._forward_streams(x, batch, kv)
         fused = self._fused()
         rope = ops.rope_tables(self, batch)
         residual = None          # full rows, or this rank's row shard on the reduce+norm path
@@ -508,6 +541,41 @@ class Model:
         if _DUMP_DIR:
             _dump_step[0] += 1
         return self._materialise(x, residual, kind, fused)
+
+    def _forward_streams(self, x, batch: StepBatch, kv: KVCache) -> torch.Tensor:
+        """The layer loop of a hyper-connection model (``scripts/ref_qwen4.py`` :318-340): the embedding is copied into
+        ``hc_count`` streams; every block reads a gated mix of the normed streams and writes its output back into each stream
+        through a gate; layers with an n-gram embedding add it to the streams first.  Returns the streams ``[T, hc * hidden]``
+        (:meth:`final_hidden` reads them out)."""
+        from . import qwen4
+        ops, cfg = self.ops, self.cfg
+        hc, eps = cfg.hc_count, cfg.rms_norm_eps
+        rope = ops.rope_tables(self, batch)
+        streams = x.repeat(1, hc)
+        state = kv.ple
+        w1 = w0 = None
+        if state is not None:
+            w1, w0 = qwen4.window_tokens(batch, state)
+            if batch.h_gdn_defer is not None:
+                self.ple_records = {}
+        for li, L in enumerate(self.layers):
+            gi = self.first_layer + li
+            if L.ple is not None:
+                streams = qwen4.ple_apply(self, L.ple, gi, streams, batch, state, w1, w0)
+            h, n = qwen4.hc_mix(streams, L.hc_attn, hc, eps)
+            if L.kind == "full_attention":
+                y, _ = self._attention(L.attn, h, batch, kv, gi, rope, None)
+            else:
+                y, _ = self._gdn(L.gdn, h, batch, kv, gi, None)
+            streams = qwen4.hc_combine(streams, n, L.hc_attn, y, hc)
+            h, n = qwen4.hc_mix(streams, L.hc_mlp, hc, eps)
+            y, _ = self._mlp(L.mlp, h, None, gi)
+            streams = qwen4.hc_combine(streams, n, L.hc_mlp, y, hc)
+            if _DUMP_DIR and not (streams.is_cuda and torch.cuda.is_current_stream_capturing()):
+                _dump(f"layer{gi:03d}_streams", streams)
+        if state is not None:
+            qwen4.advance_history(batch, batch.tokens, state, skip=batch.h_gdn_defer)
+        return streams
 
     def _fused(self):
         g = self.tp.group
@@ -612,6 +680,9 @@ class Model:
             mixed, b, a = rec
             ba = torch.stack([b[idx], a[idx]]).contiguous()      # one buffer: the kernels take a common row stride
             self.ops.gdn(mixed[idx].contiguous(), None, ba[0], ba[1], L.gdn, self, batch, kv, gi, state_only=True)
+        if kv.ple is not None:
+            from . import qwen4
+            qwen4.ple_replay(self, batch, rows, kv.ple)
 
     heat = None          # expert_heat.ExpertHeat when routing statistics are collected
     _order_dev = None    # tp.expert_order on the device (slot -> checkpoint expert), for the statistics
@@ -664,6 +735,10 @@ class Model:
     def final_hidden(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         if rows is not None:
             x = x[rows.long()]
+        if self.hc_final is not None:
+            # the read-out mix of the streams stands where the final norm does (``scripts/ref_qwen4.py`` :341)
+            from . import qwen4
+            return qwen4.hc_mix(x, self.hc_final, self.cfg.hc_count, self.cfg.rms_norm_eps)[0]
         h, _ = self.ops.norm(x, None, self.final_norm, self.cfg.rms_norm_eps, self.cfg.zero_centered_norm)
         return h
 

@@ -803,6 +803,8 @@ class CudaOps:
     def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx, state_only: bool = False):
         """Causal conv + SiLU → gated delta rule (gates computed in the kernel) → gated RMSNorm.  Sequences flagged in
         ``batch.gdn_defer`` leave their state untouched; ``state_only`` advances the states and returns nothing."""
+        if model.cfg.gdn_output_gate != "silu":
+            raise NotImplementedError("the gated-norm kernel multiplies by silu(z); output_gate_type %r is not built" % model.cfg.gdn_output_gate)
         cfg = model.cfg
         dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         hk, hv = gdn.k_heads, gdn.v_heads

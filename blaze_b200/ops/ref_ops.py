@@ -122,7 +122,7 @@ class RefOps:
             if state_only:
                 continue
             zz = z[r0:r1].view(-1, hv, dv)
-            on = ref.gated_rmsnorm(o, zz, gdn.norm_w, cfg.rms_norm_eps, zero_centered=False)
+            on = ref.gated_rmsnorm(o, zz, gdn.norm_w, cfg.rms_norm_eps, zero_centered=False, gate=cfg.gdn_output_gate)
             out[r0:r1] = on.reshape(r1 - r0, hv * dv)
         return None if state_only else out
 
