@@ -803,8 +803,6 @@ class CudaOps:
     def gdn(self, mixed_qkv, z, b, a, gdn, model, batch, kv, layer_idx, state_only: bool = False):
         """Causal conv + SiLU → gated delta rule (gates computed in the kernel) → gated RMSNorm.  Sequences flagged in
         ``batch.gdn_defer`` leave their state untouched; ``state_only`` advances the states and returns nothing."""
-        if model.cfg.gdn_output_gate != "silu":
-            raise NotImplementedError("the gated-norm kernel multiplies by silu(z); output_gate_type %r is not built" % model.cfg.gdn_output_gate)
         cfg = model.cfg
         dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         hk, hv = gdn.k_heads, gdn.v_heads
@@ -844,5 +842,6 @@ class CudaOps:
             return None
         y = torch.empty(T, hv * dv, dtype=torch.bfloat16, device=self.device)
         self._check(self.lib.blz_gated_rmsnorm(_ptr(o), _ptr(z), z.stride(0), _ptr(gdn.norm_w), _ptr(y), T, hv, dv,
-                                               cfg.rms_norm_eps, 0, self._stream()), "gated_rmsnorm")
+                                               cfg.rms_norm_eps, 2 if cfg.gdn_output_gate == "sigmoid" else 0, self._stream()),
+                    "gated_rmsnorm")
         return y

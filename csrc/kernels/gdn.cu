@@ -152,10 +152,12 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(
   for (int i = 0; i < PER; ++i) st[(size_t)(qt * PER + i) * DV + col] = S[i];
 }
 
-// one warp per (token, head): y = rmsnorm(o) * w * silu(z)
+// one warp per (token, head): y = rmsnorm(o) * w * gate(z), gate = silu, or sigmoid with flag bit 1 (a checkpoint's
+// output_gate_type); flag bit 0: w is stored as w - 1
 __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, long long ldz,
                                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int rows, int Hv, int DV,
-                                     float eps, int zero_centered) {
+                                     float eps, int flags) {
+  const bool zero_centered = flags & 1, sigmoid_gate = flags & 2;
   const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (wid >= rows * Hv) return;
   const int t = wid / Hv, h = wid % Hv;
@@ -168,7 +170,8 @@ __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ o, const 
   for (int i = lane; i < DV; i += 32) {
     const float g = bf2f(zz[i]);
     const float wf = bf2f(w[i]) + (zero_centered ? 1.f : 0.f);
-    y[((size_t)t * Hv + h) * DV + i] = __float2bfloat16(bf2f(src[i]) * rstd * wf * (g / (1.f + __expf(-g))));
+    const float sg = 1.f / (1.f + __expf(-g));
+    y[((size_t)t * Hv + h) * DV + i] = __float2bfloat16(bf2f(src[i]) * rstd * wf * (sigmoid_gate ? sg : g * sg));
   }
 }
 
@@ -248,11 +251,12 @@ static int gdn_recurrent_impl(const void* conv, const void* a_in, const void* b_
   return (int)cudaGetLastError();
 }
 
+// flags: bit 0 = weights stored as w - 1, bit 1 = multiply by sigmoid(z) instead of silu(z)
 BLZ_API int blz_gated_rmsnorm(const void* o, const void* z, long long ldz, const void* w, void* y, int rows, int Hv, int DV,
-                              float eps, int zero_centered, cudaStream_t s) {
+                              float eps, int flags, cudaStream_t s) {
   if (rows == 0) return 0;
   const int warps = rows * Hv;
   gated_rmsnorm_kernel<<<(warps + 7) / 8, 256, 0, s>>>((const bf16*)o, (const bf16*)z, ldz, (const bf16*)w, (bf16*)y, rows, Hv, DV,
-                                                       eps, zero_centered);
+                                                       eps, flags);
   return (int)cudaGetLastError();
 }

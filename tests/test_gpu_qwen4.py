@@ -22,11 +22,13 @@ def _cfg():
     return cfg
 
 
-def test_streams_and_ngram_embedding_match_the_oracle_ops():
+@pytest.mark.parametrize("gate", ["silu", "sigmoid"])
+def test_streams_and_ngram_embedding_match_the_oracle_ops(gate):
     from blaze_b200.engine import Engine, EngineConfig
     from blaze_b200.models.qwen3 import Model
     from blaze_b200.ops.ref_ops import RefOps
     cfg = _cfg()
+    cfg.gdn_output_gate = gate          # the Gated DeltaNet output gate a checkpoint names (output_gate_type)
     mk = Model.random_init(cfg, seed=5, device="cuda")
     mr = Model.random_init(cfg, seed=5, device="cuda", ops=RefOps())
     assert mk.ops.is_cuda and not mr.ops.is_cuda and mk.layers[0].ple is not None and mk.hc_final is not None
