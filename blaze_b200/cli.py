@@ -70,8 +70,8 @@ def engine_parser(p: argparse.ArgumentParser) -> None:
     c.add_argument("--l2-prefetch-mib", type=float, default=None, help="0: there is no L2 weight prefetch between kernels")
     c.add_argument("--draft-head-vram", default="auto", help="auto | on: a drafter's LM head is always in device memory")
     c.add_argument("--pp-remote", default=None, help="not offered: pipeline stages are ranks of one torch.distributed job")
-    c.add_argument("--ple-threads", type=int, default=None, help="not offered: per-layer n-gram embeddings are not built")
-    c.add_argument("--ple-cache-gib", type=float, default=None, help="not offered: per-layer n-gram embeddings are not built")
+    c.add_argument("--ple-threads", type=int, default=None, help="accepted and unused: the n-gram embedding tables (PLE) live in device memory, no host threads read them")
+    c.add_argument("--ple-cache-gib", type=float, default=None, help="accepted and unused: the PLE tables live in device memory, there is no host row cache")
     g.add_argument("--spec-method", default=None, choices=["none", "ngram", "suffix", "mtp", "eagle", "dflash"])
     g.add_argument("--max-verify", type=int, default=None)
     g.add_argument("--suffix-assist", action="store_true")
@@ -247,8 +247,6 @@ _COMPAT = {
     "draft_head_vram": (("auto", "on"), "a drafter's LM head always lives in device memory"),
     "pp_remote": ((None,), "pipeline stages are ranks of one torch.distributed job: launch every stage with torch.distributed.run "
                            "(--nnodes / --node-rank for several machines) and --pp"),
-    "ple_threads": ((None,), "per-layer n-gram embeddings (PLE) are not built"),
-    "ple_cache_gib": ((None,), "per-layer n-gram embeddings (PLE) are not built"),
 }
 
 

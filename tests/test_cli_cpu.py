@@ -52,11 +52,12 @@ def test_reference_engine_flags_carry_over_or_are_refused_with_a_reason(capsys):
     a value it cannot honour ends the command with the reason instead of being ignored."""
     base = ["generate", "--model", "tiny", "--device", "cpu", "--prompt-ids", IDS, "--max-tokens", "3"]
     rc, out = _run(capsys, base + ["--gemm", "auto", "--attn-f16-acc", "off", "--prefill-attention", "auto", "--verify-attention", "auto",
-                                   "--prefill-a16", "none", "--l2-prefetch-mib", "0", "--draft-head-vram", "auto"])
+                                   "--prefill-a16", "none", "--l2-prefetch-mib", "0", "--draft-head-vram", "auto",
+                                   "--ple-threads", "8", "--ple-cache-gib", "2"])
     assert rc == 0 and len(json.loads(out[-1])["token_ids"]) == 3
     for extra, word in ((["--gemm", "bf16"], "weight format"), (["--attn-f16-acc", "on"], "fp32"),
                         (["--l2-prefetch-mib", "4"], "prefetch"), (["--pp-remote", "1=host:9000"], "torch.distributed"),
-                        (["--prefill-a16", "kv"], "16-bit"), (["--ple-cache-gib", "2"], "PLE"),
+                        (["--prefill-a16", "kv"], "16-bit"),
                         (["--mtp-model", "/nowhere", "--spec-method", "eagle"], "--spec-method mtp")):
         with pytest.raises(SystemExit) as e:
             cli.main(base + extra)
