@@ -83,6 +83,12 @@ class KVCache:
                 self.rec_state[i] = torch.zeros(self.state_rows, hv, cfg.linear_key_head_dim,
                                                 cfg.linear_value_head_dim, dtype=torch.float32, device=device)
 
+        # sparse-attention indexer: the raw index key of every token, paged like K and V (shared prefixes share them)
+        self.idx_k: Dict[int, torch.Tensor] = {}
+        if getattr(cfg, "indexer_heads", 0) > 0:
+            act = torch.float32 if kv_dtype == "fp32" else torch.bfloat16
+            for i in self.attn_layers:
+                self.idx_k[i] = torch.zeros(num_pages, PAGE, cfg.indexer_head_dim, dtype=act, device=device)
         # n-gram embedding layers of this stage keep a token window and a convolution history per row
         self.ple = None
         ple_layers = [i for i in range(lo, hi) if i in set(getattr(cfg, "ple_layers", ()) or ())]
@@ -130,7 +136,7 @@ class KVCache:
 
     def nbytes(self) -> int:
         n = 0
-        for d in (self.k, self.v, self.kv, self.conv_state, self.rec_state):
+        for d in (self.k, self.v, self.kv, self.conv_state, self.rec_state, self.idx_k):
             n += sum(t.numel() * t.element_size() for t in d.values())
         return n + (self.ple.nbytes() if self.ple is not None else 0)
 

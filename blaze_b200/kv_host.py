@@ -60,8 +60,10 @@ class HostKVTier:
     def spill(self, dev_pages: List[int]) -> Optional[Tuple[int, int]]:
         """Copy the given device pages to the host; returns the host run, or None when there is no room."""
         n = len(dev_pages)
-        if n == 0 or self.kv.gdn_layers:
-            return None          # recurrent state rows are not paged: models with GDN layers keep their snapshots on the device
+        if n == 0 or self.kv.gdn_layers or getattr(self.kv, "idx_k", None):
+            # recurrent state rows are not paged, and an indexer's key pages are not copied here: such models keep their
+            # snapshots on the device
+            return None
         s0 = self._alloc(n)
         if s0 is None:
             return None

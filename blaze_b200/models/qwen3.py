@@ -23,6 +23,8 @@ from ..quant import Format
 
 
 class Attn:
+    index = None         # qwen4.Indexer of a sparse-attention model (class default: none)
+
     def __init__(self):
         self.qkv: Linear = None
         self.o: Linear = None
@@ -179,6 +181,8 @@ class Model:
         if cfg.has_hc and (self.tp.world > 1 or first_layer != 0 or self.last_layer != cfg.num_layers):
             # as in the reference (crates/blaze/src/model.rs:1077): the streams are not cut over ranks or stages
             raise ValueError("hyper-connection models run on one rank (no tensor or pipeline parallelism)")
+        if cfg.indexer_heads and (self.tp.world > 1 or first_layer != 0 or self.last_layer != cfg.num_layers):
+            raise ValueError("sparse-attention (indexer) models run on one rank (no tensor or pipeline parallelism)")
         if cfg.ple_layers and not cfg.has_hc:
             raise ValueError("per-layer n-gram embeddings are defined on hyper-connection streams (hc_count > 1)")
         self.weight_format = Format.DENSE
@@ -271,6 +275,13 @@ class Model:
                 A.o = lin(rnd(H, cfg.num_heads * D, base + 4), Cut.COLS)
                 if cfg.qk_norm:
                     A.q_norm, A.k_norm = ones(D), ones(D)
+                if cfg.indexer_heads:
+                    from . import qwen4
+                    A.index = qwen4.Indexer()
+                    A.index.proj = _tag(Linear.from_dense(rnd((cfg.indexer_heads + 1) * cfg.indexer_head_dim, H, base + 6, 0.1),
+                                                          Format.DENSE, dtype=dtype), Cut.ALL)
+                    A.index.q_norm = torch.zeros(cfg.indexer_head_dim, dtype=dtype, device=device)
+                    A.index.k_norm = torch.zeros(cfg.indexer_head_dim, dtype=dtype, device=device)
                 L.attn = A
             else:
                 G = Gdn()
@@ -406,6 +417,12 @@ class Model:
                 A.o = load_lin([sp + "o_proj"], Cut.COLS)
                 if cfg.qk_norm and (sp + "q_norm.weight") in ck:
                     A.q_norm, A.k_norm = vec(sp + "q_norm.weight"), vec(sp + "k_norm.weight")
+                if cfg.indexer_heads:
+                    # tensor names of crates/blaze/src/model.rs:1127-1134
+                    from . import qwen4
+                    A.index = qwen4.Indexer()
+                    A.index.proj = load_lin([sp + "indexer.index_qk_proj"], Cut.ALL)
+                    A.index.q_norm, A.index.k_norm = vec(sp + "indexer.q_layernorm.weight"), vec(sp + "indexer.k_layernorm.weight")
                 L.attn = A
             else:
                 G = Gdn()
@@ -645,7 +662,13 @@ class Model:
         ops = self.ops
         qkv = ops.linear(A.qkv, h)
         q, gate = ops.attn_prep_store(qkv, A, self, batch, kv, gi, rope)
-        o = ops.attention(q, self, batch, kv, gi, self.attn_scale)
+        if A.index is not None:
+            from . import qwen4
+            sel = qwen4.qsa_step(self, A.index, h, batch, kv, gi)
+            o = ops.attention(q, self, batch, kv, gi, self.attn_scale, allowed=sel) if sel is not None else \
+                ops.attention(q, self, batch, kv, gi, self.attn_scale)
+        else:
+            o = ops.attention(q, self, batch, kv, gi, self.attn_scale)
         if gate is not None:
             o = ops.mul_sigmoid(o, gate.reshape(o.shape))
         return self._row_cut(A.o, o, o.shape[0], fused)

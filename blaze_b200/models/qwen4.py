@@ -12,8 +12,15 @@ points where the reference rounds to bf16.
 Per-sequence state (kept with the recurrent state rows of :class:`blaze_b200.kv.KVCache`): the two tokens before the
 next one (the n-gram window) and the last ``3 * ngram_size`` rows that entered each PLE layer's dilated convolution.
 
-The sparse-attention indexer of the same family (QSA) is not built: its softmax layers run dense attention, which is what
-the indexer selects while a context is shorter than its budget (``ref_qwen4.py`` :4)."""
+The sparse-attention indexer of the same family (QSA; reference: ``kernels/src/cuda/qsa_index.cu``, driven by
+``crates/blaze/src/model.rs:2809`` ``qsa_index``, stated by ``kernels/tests/test_qsa_index.cu``): every softmax layer projects
+index queries (a few heads) and one index key per token; the keys of each complete block of ``compress_ratio`` tokens are
+averaged, normed and rotated to the block's first position; a row scores a block by the sum over heads of
+``relu(q . k)`` over ``sqrt(dim)`` and attends to the tokens of its ``budget / compress_ratio`` best blocks (ties: the
+earlier block) plus those of the incomplete block it stands in.  While a context has no more blocks than that, every key
+is selected and attention is dense.  Here the raw index keys are paged like K and V (``KVCache.idx_k``), compressed keys
+are formed when a row scores them, and the selection is a mask for the oracle attention; the attention kernels read whole
+sequences, so on them a context beyond the budget is refused rather than answered densely."""
 from __future__ import annotations
 
 import math
@@ -276,3 +283,93 @@ def ple_replay(model, batch, rows: torch.Tensor, state: PleState) -> None:
             if r1 > r0:
                 hist[slot] = torch.cat([hist[slot], g[r0:r1]])[-depth:]
     advance_history(batch, model.ple_records["tokens"][idx], state)
+
+
+# ----------------------------------------------------------------------------------- sparse-attention indexer (QSA)
+class Indexer:
+    """Weights of a softmax layer's indexer: ``proj`` (hidden -> heads * dim index queries, then one index key of dim),
+    ``q_norm`` / ``k_norm`` [dim] (stored as w - 1)."""
+
+    def __init__(self):
+        self.proj = None
+        self.q_norm = self.k_norm = None
+
+
+def _norm_rope(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, rot: int, eps: float, scale: float, dt):
+    """RMSNorm times ``1 + w`` over the last axis (rounded to ``dt``), then the rotation of the first ``rot`` dims (pairs
+    ``i, i + rot / 2``) by ``pos`` (broadcast over the axes between), rounded again; fp32 out."""
+    xf = x.float()
+    xf = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + w.float())).to(dt).float()
+    half = rot // 2
+    ang = pos.float()[..., None] * inv_freq.float()[:half]
+    c, s = torch.cos(ang) * scale, torch.sin(ang) * scale
+    while c.dim() < xf.dim():
+        c, s = c.unsqueeze(-2), s.unsqueeze(-2)
+    a, b = xf[..., :half], xf[..., half:rot]
+    return torch.cat([a * c - b * s, b * c + a * s, xf[..., rot:]], -1).to(dt).float()
+
+
+def compressed_keys(kraw: torch.Tensor, I: Indexer, ratio: int, inv_freq, rot: int, eps: float, scale: float) -> torch.Tensor:
+    """Keys of the complete blocks of one sequence: ``kraw [n, dim]`` raw index keys in position order -> ``[n // ratio, dim]``."""
+    nb = kraw.shape[0] // ratio
+    dt = kraw.dtype
+    mean = (kraw[:nb * ratio].float().view(nb, ratio, -1).sum(1) / ratio).to(dt)
+    pos = torch.arange(nb, device=kraw.device) * ratio
+    return _norm_rope(mean, I.k_norm, pos, inv_freq, rot, eps, scale, dt)
+
+
+def block_scores(iq: torch.Tensor, comp: torch.Tensor) -> torch.Tensor:
+    """``iq [rows, heads, dim]`` (normed, rotated) against ``comp [blocks, dim]``: ``sum_h relu(q_h . k) / sqrt(dim)``."""
+    return torch.relu(torch.einsum("rhd,bd->rhb", iq.float(), comp.float())).sum(1) / math.sqrt(iq.shape[-1])
+
+
+def select_keys(scores: torch.Tensor, pos: torch.Tensor, ratio: int, top_blocks: int, n: int) -> torch.Tensor:
+    """bool ``[rows, n]``: for the row at position ``pos[r]`` the tokens of its best ``top_blocks`` blocks among the
+    ``(pos + 1) // ratio`` complete ones it can see (equal scores: the earlier block), and the tokens after them up to
+    ``pos`` (the incomplete block)."""
+    rows, nb = scores.shape
+    nvis = (pos.long() + 1) // ratio
+    blk = torch.arange(nb, device=scores.device)
+    sc = scores.float().masked_fill(blk[None, :] >= nvis[:, None], float("-inf"))
+    order = torch.sort(sc, dim=1, descending=True, stable=True).indices             # stable: ties keep block order
+    rank = torch.empty_like(order)
+    rank.scatter_(1, order, blk[None, :].expand(rows, nb).contiguous())
+    chosen = (rank < top_blocks) & (blk[None, :] < nvis[:, None])                  # [rows, nb]
+    tok = torch.arange(n, device=scores.device)
+    out = torch.zeros(rows, n, dtype=torch.bool, device=scores.device)
+    full = min(nb * ratio, n)
+    out[:, :full] = chosen.repeat_interleave(ratio, dim=1)[:, :full]
+    tail = (tok[None, :] >= (nvis * ratio)[:, None]) & (tok[None, :] <= pos.long()[:, None])
+    return out | tail
+
+
+def qsa_step(model, I: Indexer, h: torch.Tensor, batch, kv, layer: int):
+    """The indexer's part of a softmax layer's step: index keys of the new tokens go to their slots; sequences whose
+    context exceeds the budget get the selection of every row.  Returns the per-sequence masks for the attention (None
+    when every sequence is within the budget)."""
+    cfg, ops = model.cfg, model.ops
+    Hi, Di, ratio = cfg.indexer_heads, cfg.indexer_head_dim, cfg.indexer_compress_ratio
+    proj = ops.linear(I.proj, h)
+    pool = kv.idx_k[layer]
+    valid = batch.slot_mapping >= 0
+    pool.view(-1, Di)[batch.slot_mapping[valid].long()] = proj[valid, Hi * Di:].to(pool.dtype)
+    top_blocks = cfg.indexer_budget // ratio
+    if max(batch.h_ctx_len, default=0) // ratio <= top_blocks:
+        return None
+    rot, eps, dt = cfg.rotary_dim, cfg.rms_norm_eps, pool.dtype
+    pos_all = batch.positions if batch.positions.dim() == 1 else batch.positions[0]
+    iq = _norm_rope(proj[:, :Hi * Di].reshape(-1, Hi, Di), I.q_norm, pos_all, model.inv_freq, rot, eps, model.rope_scale, dt)
+    table = kv.block_table
+    out = []
+    for b, slot in enumerate(batch.h_slots):
+        r0, r1 = batch.h_q_start[b], batch.h_q_start[b + 1]
+        n = batch.h_ctx_len[b]
+        if r1 == r0 or n // ratio <= top_blocks:
+            out.append(None)
+            continue
+        npg = (n + pool.shape[1] - 1) // pool.shape[1]
+        kraw = pool[table[slot, :npg].long()].reshape(-1, Di)[:n]
+        comp = compressed_keys(kraw, I, ratio, model.inv_freq, rot, eps, model.rope_scale)
+        pos = torch.arange(n - (r1 - r0), n, device=h.device)
+        out.append(select_keys(block_scores(iq[r0:r1], comp), pos, ratio, top_blocks, n))
+    return out

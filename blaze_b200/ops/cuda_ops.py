@@ -584,8 +584,11 @@ class CudaOps:
         self._check(self.lib.blz_kv_move_rows(_ptr(pool), _ptr(src), _ptr(dst), _ptr(seg), seg.numel() - 1, pool.shape[1], D,
                                               pool.stride(0), pool.stride(1), self._stream()), "kv_move_rows")
 
-    def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0):
+    def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0, allowed=None):
         """Sequences with few query rows (decode, verify) go to the decode kernel, the rest to the row-block kernel."""
+        if allowed is not None:
+            raise NotImplementedError("the attention kernels read every key of a sequence: a sparse selection (a context beyond "
+                                      "the indexer's budget) runs on the oracle op set only")
         T, Hq, D = q.shape
         Hkv = kv.kv_heads
         group = Hq // Hkv

@@ -134,12 +134,13 @@ def kv_write(k_pool: torch.Tensor, v_pool: torch.Tensor, k: torch.Tensor, v: tor
 
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                     slots: Sequence[int], q_start: Sequence[int], ctx_len: Sequence[int], scale: float,
-                    tree_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    tree_mask: Optional[torch.Tensor] = None, allowed: Optional[Sequence] = None) -> torch.Tensor:
     """Causal GQA attention of q ``[T, H, D]`` over the paged pools.
 
     Sequence ``b`` owns rows ``q_start[b]:q_start[b+1]``; its KV length *including* those rows is
     ``ctx_len[b]``; row i attends to positions ``<= ctx_len - q_len + i``.  With ``tree_mask`` (``[T]`` int32) row i
     sees, among its sequence's own new tokens, only those whose bit is set in its word (a draft tree's ancestors).
+    ``allowed[b]`` (bool ``[q_len, ctx_len]`` or None) further restricts what sequence b's rows see (a sparse selection).
     """
     T, H, D = q.shape
     KH = k_pool.shape[1]
@@ -164,6 +165,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             own = ((words >> torch.arange(min(ql, 32), device=q.device).view(1, -1)) & 1).bool()      # [ql, min(ql, 32)]
             mask = mask.clone()
             mask[:, n - ql:n - ql + own.shape[1]] &= own
+        if allowed is not None and allowed[b] is not None:
+            mask = mask & allowed[b]
         s = s.masked_fill(~mask, float("-inf"))
         p = torch.softmax(s, dim=-1)
         o = torch.einsum("hgqn,hnd->hgqd", p, V)                               # [KH, g, ql, D]

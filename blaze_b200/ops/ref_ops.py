@@ -72,10 +72,11 @@ class RefOps:
             ref.kv_write(kv.k[layer_idx], kv.v[layer_idx], k[valid], v[valid], batch.slot_mapping[valid])
         return q, gate
 
-    def attention(self, q, model, batch, kv, layer_idx, scale):
+    def attention(self, q, model, batch, kv, layer_idx, scale, allowed=None):
+        """``allowed``: per sequence a bool ``[q_len, ctx_len]`` of the keys its rows may see (None: all), a sparse selection."""
         kl, vl = kv.logical_kv(layer_idx)
         o = ref.paged_attention(q, kl, vl, kv.block_table, batch.h_slots, batch.h_q_start, batch.h_ctx_len, scale,
-                                tree_mask=getattr(batch, "tree_mask", None))
+                                tree_mask=getattr(batch, "tree_mask", None), allowed=allowed)
         return o.reshape(q.shape[0], -1)
 
     # -------------------------------------------------------------- MoE

@@ -54,6 +54,10 @@ def write(model, out_dir: str, prefix: str = "model.language_model.", ple_shards
             if A.q_norm is not None:
                 put(sp + "q_norm.weight", A.q_norm)
                 put(sp + "k_norm.weight", A.k_norm)
+            if A.index is not None:
+                put(sp + "indexer.index_qk_proj.weight", A.index.proj.dequant())
+                put(sp + "indexer.q_layernorm.weight", A.index.q_norm)
+                put(sp + "indexer.k_layernorm.weight", A.index.k_norm)
         else:
             G, gp = L.gdn, lp + "linear_attn."
             hk, hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
@@ -102,6 +106,9 @@ def write(model, out_dir: str, prefix: str = "model.language_model.", ple_shards
             "shared_expert_intermediate_size": cfg.shared_expert_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob,
             "rope_parameters": {"rope_theta": cfg.rope.theta, "partial_rotary_factor": cfg.rope.partial_rotary_factor},
             "eos_token_id": cfg.eos_token_ids[0] if cfg.eos_token_ids else None, "output_gate_type": cfg.gdn_output_gate}
+    if cfg.indexer_heads:
+        text.update({"indexer_n_heads": cfg.indexer_heads, "indexer_head_dim": cfg.indexer_head_dim,
+                     "indexer_budget": cfg.indexer_budget, "indexer_compress_ratio": cfg.indexer_compress_ratio})
     if cfg.has_hc:
         text.update({"hc_count": cfg.hc_count, "hc_lowrank": cfg.hc_lowrank})
     if cfg.ple_layers:

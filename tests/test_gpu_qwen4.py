@@ -22,13 +22,16 @@ def _cfg():
     return cfg
 
 
-@pytest.mark.parametrize("gate", ["silu", "sigmoid"])
-def test_streams_and_ngram_embedding_match_the_oracle_ops(gate):
+@pytest.mark.parametrize("gate,indexer", [("silu", False), ("sigmoid", False), ("silu", True)])
+def test_streams_and_ngram_embedding_match_the_oracle_ops(gate, indexer):
     from blaze_b200.engine import Engine, EngineConfig
     from blaze_b200.models.qwen3 import Model
     from blaze_b200.ops.ref_ops import RefOps
     cfg = _cfg()
     cfg.gdn_output_gate = gate          # the Gated DeltaNet output gate a checkpoint names (output_gate_type)
+    if indexer:
+        # a sparse-attention indexer whose budget the contexts stay within: its keys are written, attention is dense
+        cfg.indexer_heads, cfg.indexer_head_dim, cfg.indexer_budget, cfg.indexer_compress_ratio = 2, 64, 2048, 4
     mk = Model.random_init(cfg, seed=5, device="cuda")
     mr = Model.random_init(cfg, seed=5, device="cuda", ops=RefOps())
     assert mk.ops.is_cuda and not mr.ops.is_cuda and mk.layers[0].ple is not None and mk.hc_final is not None
@@ -55,5 +58,15 @@ def test_streams_and_ngram_embedding_match_the_oracle_ops(gate):
     # the token window and the convolution history moved alike on both sides
     for a, b in ((ek.kv.ple.hist, er.kv.ple.hist),):
         assert torch.equal(a[[s.row for s in sk]], b[[s.row for s in sr]])
+    if indexer:
+        # both sides wrote the same index keys (the same torch ops on the same projection kernel's output)
+        pk, pr = ek.kv.idx_k[1], er.kv.idx_k[1]
+        rows_k = pk[ek.kv.block_table[sk[0].row, :4].long()].float()
+        rows_r = pr[er.kv.block_table[sr[0].row, :4].long()].float()
+        assert rows_k.abs().sum() > 0 and torch.nn.functional.cosine_similarity(rows_k.flatten(), rows_r.flatten(), dim=0) > 0.999
+        # beyond the budget the kernels refuse instead of answering densely
+        cfg.indexer_budget = 16
+        with pytest.raises(NotImplementedError):
+            ek.forward(ek.plan([(s, [t], 1) for s, t in zip(sk, toks)]), "logits")
     torch.cuda.synchronize()
     assert mk.ops.take_status() == 0

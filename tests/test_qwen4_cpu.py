@@ -205,3 +205,86 @@ def test_a_checkpoint_with_the_reference_names_loads(tmp_path):
     assert isinstance(m, Model) and m.cfg.hc_count == 2 and m.cfg.ple_layers == [0, 2] and m.layers[2].ple.table.shape == src.model.layers[2].ple.table.shape
     ps = _prompts()[:2]
     assert [o.token_ids for o in loaded.generate(ps, GREEDY)] == [o.token_ids for o in src.generate(ps, GREEDY)]
+
+
+# ----------------------------------------------------------------------------------- sparse-attention indexer
+def test_indexer_scores_and_selection_against_loops():
+    """Compressed keys, block scores and the selected tokens as ``kernels/tests/test_qsa_index.cu`` states them."""
+    g = torch.Generator().manual_seed(9)
+    D, HEADS, RATIO, ROT, eps = 32, 3, 4, 16, 1e-6
+    n, top = 45, 5
+    inv = torch.tensor([1.0 / (1e7 ** (2.0 * i / ROT)) for i in range(ROT // 2)])
+    I = qwen4.Indexer()
+    I.q_norm, I.k_norm = torch.randn(D, generator=g) * 0.1, torch.randn(D, generator=g) * 0.1
+    kraw = torch.randn(n, D, generator=g)
+    qraw = torch.randn(n, HEADS, D, generator=g)
+
+    def norm_rope(v, w, pos):
+        v = v.double()
+        v = v / math.sqrt(float((v * v).sum() / D) + eps) * (1.0 + w.double())
+        o = v.clone()
+        for i in range(ROT // 2):
+            c, s = math.cos(pos * float(inv[i])), math.sin(pos * float(inv[i]))
+            o[i] = v[i] * c - v[i + ROT // 2] * s
+            o[i + ROT // 2] = v[i + ROT // 2] * c + v[i] * s
+        return o
+    comp = qwen4.compressed_keys(kraw, I, RATIO, inv, ROT, eps, 1.0)
+    assert comp.shape == (n // RATIO, D)
+    for b in range(n // RATIO):
+        want = norm_rope(kraw[b * RATIO:(b + 1) * RATIO].double().sum(0) / RATIO, I.k_norm, b * RATIO)
+        assert torch.allclose(comp[b].double(), want, atol=1e-4)
+    pos = torch.arange(n)
+    iq = qwen4._norm_rope(qraw, I.q_norm, pos, inv, ROT, eps, 1.0, torch.float32)
+    for r in (0, 17, 44):
+        for h in range(HEADS):
+            assert torch.allclose(iq[r, h].double(), norm_rope(qraw[r, h], I.q_norm, r), atol=1e-4)
+    sc = qwen4.block_scores(iq, comp)
+    sc[:, 3] = sc[:, 7]                     # equal scores: the earlier block wins
+    sel = qwen4.select_keys(sc, pos, RATIO, top, n)
+    for r in range(n):
+        nvis = (r + 1) // RATIO
+        for b in range(n // RATIO):
+            d = sum(max(float((iq[r, h].double() * comp[b].double()).sum()), 0.0) for h in range(HEADS)) / math.sqrt(D)
+            if b not in (3, 7):
+                assert abs(d - float(sc[r, b])) < 1e-4
+        order = sorted(range(nvis), key=lambda b: (-float(sc[r, b]), b))[:top]
+        want = set()
+        for b in order:
+            want.update(range(b * RATIO, (b + 1) * RATIO))
+        want.update(range(nvis * RATIO, r + 1))
+        assert set(torch.nonzero(sel[r]).flatten().tolist()) == want, r
+
+
+def _sparse_llm(budget, **kw):
+    cfg = named_config("tiny-qwen4")
+    cfg.indexer_heads, cfg.indexer_head_dim, cfg.indexer_budget, cfg.indexer_compress_ratio = 2, 32, budget, 4
+    base = dict(device="cpu", dtype=torch.float32, max_seqs=8, max_model_len=256, use_graphs=False, seed=0)
+    base.update(kw)
+    return LLM(cfg, **base)
+
+
+def test_sparse_attention_through_the_engine():
+    g = torch.Generator().manual_seed(21)
+    ps = [torch.randint(2, 1024, (n,), generator=g).tolist() for n in (90, 20, 61)]
+    # within the budget every key is selected: the tokens of the model whose budget is never reached
+    dense = [o.token_ids for o in _sparse_llm(4096).generate(ps, GREEDY)]
+    assert [o.token_ids for o in _sparse_llm(128).generate(ps, GREEDY)] == dense
+    # beyond it rows see their best blocks only: another answer, and the same one however the prompt is cut into steps
+    sparse = [o.token_ids for o in _sparse_llm(32, chunk=256).generate(ps, GREEDY)]
+    assert sparse != dense and sparse[1] == dense[1], "the 20-token prompt stays within a budget of 32"
+    assert [o.token_ids for o in _sparse_llm(32, chunk=16).generate(ps, GREEDY)] == sparse
+    one = _sparse_llm(32)
+    assert [one.generate([p], GREEDY)[0].token_ids for p in ps] == sparse
+    # a shared prefix brings its index keys with its pages
+    again = one.generate([ps[0] + [5, 6, 7]], GREEDY)[0]
+    assert again.token_ids == _sparse_llm(32).generate([ps[0] + [5, 6, 7]], GREEDY)[0].token_ids
+
+
+def test_a_checkpoint_with_an_indexer_loads(tmp_path):
+    import synthetic_checkpoint
+    src = _sparse_llm(32, dtype=torch.bfloat16, kv_cache_dtype="bf16")
+    synthetic_checkpoint.write(src.model, str(tmp_path))
+    loaded = LLM(str(tmp_path), device="cpu", dtype=torch.bfloat16, kv_cache_dtype="bf16", max_seqs=8, max_model_len=256, use_graphs=False)
+    assert loaded.model.cfg.indexer_budget == 32 and loaded.model.layers[1].attn.index is not None
+    p = torch.randint(2, 1024, (70,), generator=torch.Generator().manual_seed(2)).tolist()
+    assert loaded.generate([p], GREEDY)[0].token_ids == src.generate([p], GREEDY)[0].token_ids
