@@ -298,8 +298,9 @@ def build_llm(ns: argparse.Namespace):
         group = TPGroup.from_env(device, pp=pp)
     tp = TPInfo(group.rank, group.world, group if group.world > 1 else None, ep=ns.ep) if group else TPInfo()
     kv = ns.kv_cache_dtype or "auto"
-    if kv.startswith("nvfp4"):
-        raise SystemExit(f"--kv-cache-dtype {kv}: 4-bit KV pages are not built; use fp8 (the compact format here), bf16 or fp32")
+    if kv.startswith("nvfp4") and device.startswith("cuda"):
+        raise SystemExit(f"--kv-cache-dtype {kv}: the attention kernels read FP8 pages; NVFP4 pages (plain or 4-over-6 scales) are "
+                         "written and read by the oracle op set only (--device cpu).  Use fp8 (the compact format here), bf16 or fp32")
     if getattr(ns, "kv_host", False):
         raise SystemExit("--kv-host (live sequences in pinned host memory) is not built; --kv-host-tokens N gives the prefix "
                          "cache a pinned-host tier of N tokens")

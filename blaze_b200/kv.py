@@ -27,10 +27,28 @@ PAGE = 16
 
 
 def kv_bytes_per_token(cfg: ModelConfig, kv_dtype: str, tp_world: int = 1) -> int:
-    esz = {"fp32": 4, "bf16": 2, "fp8": 1}[kv_dtype]
     n_attn = sum(1 for i in range(cfg.num_layers) if cfg.layer_type(i) == "full_attention")
     kvh = max(cfg.num_kv_heads // tp_world, 1)
+    if kv_dtype in FP4_KV:
+        return n_attn * 2 * kvh * (cfg.head_dim // 2 + cfg.head_dim // 16)      # 4-bit codes and one scale byte per 16
+    esz = {"fp32": 4, "bf16": 2, "fp8": 1}[kv_dtype]
     return n_attn * 2 * kvh * cfg.head_dim * esz
+
+
+FP4_KV = ("nvfp4", "nvfp4_4over6")       # NVFP4 rows with the plain block scale, or with the searched one
+
+
+class Fp4Pool:
+    """A K or V pool of NVFP4 rows seen as ``[pages, kv_heads, 16, D]``: indexing by pages dequantises those pages."""
+
+    def __init__(self, rows: torch.Tensor, D: int):
+        self.rows, self.D = rows, D
+        self.shape = (*rows.shape[:-1], D)
+        self.device = rows.device
+
+    def __getitem__(self, pages):
+        from .quant import nvfp4_kv_dequantize
+        return nvfp4_kv_dequantize(self.rows[pages], self.D)
 
 
 HEAD_MAJOR = os.environ.get("BLAZE_KV_HEAD_MAJOR", "0") == "1"
@@ -45,7 +63,9 @@ class KVCache:
         self.kv_dtype, self.layout, self.device = kv_dtype, layout, torch.device(device)
         self.kv_heads = max(cfg.num_kv_heads // tp_world, 1)
         D = cfg.head_dim
-        tdt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[kv_dtype]
+        tdt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn, "nvfp4": torch.uint8,
+               "nvfp4_4over6": torch.uint8}[kv_dtype]
+        row = D // 2 + D // 16 if kv_dtype in FP4_KV else D       # NVFP4: a row's codes, then its block scales
         lo, hi = layers if layers is not None else (0, cfg.num_layers)      # a pipeline stage holds the caches of its layers only
         self.attn_layers = [i for i in range(lo, hi) if cfg.layer_type(i) == "full_attention"]
         self.gdn_layers = [i for i in range(lo, hi) if cfg.layer_type(i) == "linear_attention"]
@@ -63,8 +83,8 @@ class KVCache:
                 else:
                     self.kv[i] = torch.zeros(num_pages, self.kv_heads, 2, PAGE * D, dtype=torch.uint8, device=device)
             else:
-                self.k[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
-                self.v[i] = torch.zeros(num_pages, self.kv_heads, PAGE, D, dtype=tdt, device=device)
+                self.k[i] = torch.zeros(num_pages, self.kv_heads, PAGE, row, dtype=tdt, device=device)
+                self.v[i] = torch.zeros(num_pages, self.kv_heads, PAGE, row, dtype=tdt, device=device)
         self._block_table = torch.zeros(max_seqs, max_pages_per_seq, dtype=torch.int32, device=device)
         self.block_table_host = np.zeros((max_seqs, max_pages_per_seq), dtype=np.int32)
         self._dirty: List[tuple] = []          # (row, first page slot, count) not yet uploaded
@@ -156,6 +176,15 @@ class KVCache:
         if self.ple is not None:
             self.ple.zero(row)
 
+    def write_fp4(self, layer: int, k: torch.Tensor, v: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+        """Quantise the new tokens' K and V rows ``[T, kv_heads, D]`` to NVFP4 into their slots (``nvfp4_4over6``: with the
+        block-scale search)."""
+        from .quant import nvfp4_kv_quantize
+        search = self.kv_dtype == "nvfp4_4over6"
+        page, off = slot_mapping.long() // PAGE, slot_mapping.long() % PAGE
+        self.k[layer][page, :, off] = nvfp4_kv_quantize(k, search=search)
+        self.v[layer][page, :, off] = nvfp4_kv_quantize(v, search=search)
+
     # ------------------------------------------------------------------ row moves (tree speculation)
     def move_rows(self, moves: Sequence[Sequence[tuple]], ops=None) -> None:
         """``moves[i]`` = ordered (src slot, dst slot) pairs of sequence i (flat slots: page * 16 + offset): copy the K/V
@@ -207,6 +236,8 @@ class KVCache:
 
     def logical_kv(self, layer: int):
         """Return (k, v) ``[pages, kv_heads, 16, D]`` e4m3 whatever the layout (copy for ``umma``)."""
+        if self.kv_dtype in FP4_KV:
+            return Fp4Pool(self.k[layer], self.cfg.head_dim), Fp4Pool(self.v[layer], self.cfg.head_dim)
         if self.layout != "umma":
             return self.k[layer], self.v[layer]
         D = self.cfg.head_dim

@@ -92,6 +92,8 @@ class LLM:
         if kv_cache_dtype == "auto":
             kv_cache_dtype = "fp8" if (self.device.type == "cuda" and self.model.ops.is_cuda) else \
                 ("fp32" if dtype == torch.float32 else "bf16")
+        if kv_cache_dtype.startswith("nvfp4") and self.model.ops.is_cuda:
+            raise ValueError(f"kv_cache_dtype {kv_cache_dtype!r}: the attention kernels read FP8 pages; NVFP4 pages run on the oracle op set")
         with log.Stage("kv"):
             self.engine = Engine(self.model, EngineConfig(kv_tokens=kv_tokens, max_seqs=max_seqs, max_model_len=max_model_len,
                                                           kv_dtype=kv_cache_dtype, chunk=chunk, use_graphs=use_graphs,

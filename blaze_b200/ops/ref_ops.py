@@ -58,7 +58,9 @@ class RefOps:
                                       cfg.rms_norm_eps, cos, sin, gated=cfg.attn_output_gate,
                                       zero_centered=cfg.zero_centered_norm, rotate=getattr(model, "kv_rotate", False))
         valid = batch.slot_mapping >= 0
-        if kv.layout == "umma":
+        if kv.kv_dtype in ("nvfp4", "nvfp4_4over6"):
+            kv.write_fp4(layer_idx, k[valid], v[valid], batch.slot_mapping[valid])
+        elif kv.layout == "umma":
             kl, vl = kv.logical_kv(layer_idx)
             ref.kv_write(kl, vl, k[valid], v[valid], batch.slot_mapping[valid])
             # write back in kernel layout

@@ -212,6 +212,54 @@ def nvfp4_dequantize(packed: torch.Tensor, block_scale: torch.Tensor, global_sca
     return (vals * block_scale.float().unsqueeze(-1) * g).view(rows, -1)
 
 
+def nvfp4_kv_quantize(x: torch.Tensor, g: float = 1.0, search: bool = False) -> torch.Tensor:
+    """Rows of a KV cache in NVFP4: ``x [..., D]`` (D % 16 == 0) -> uint8 ``[..., D/2 + D/16]``, the packed E2M1 codes of a row
+    followed by its E4M3 block scales (one per 16 elements); value = e2m1 * scale * g.
+
+    The block scale is the E4M3 rounding of ``amax / (6 g)``.  With ``search`` ("four over six") the candidates are that
+    scale, the rounding of ``amax / (4 g)``, and the E4M3 codes -1 .. +5 steps from the first; the one with the lowest
+    squared error of the block is kept, earlier candidates winning ties (reference: ``kv_store_kernel``,
+    kernels/src/cuda/nvfp4_kv.cu:62-113, ``kScaleSearchFirst`` / ``Last`` in kernels/include/blaze/nvfp4.h:28)."""
+    D = x.shape[-1]
+    assert D % NVFP4_BLOCK == 0
+    xb = x.float().reshape(-1, D // NVFP4_BLOCK, NVFP4_BLOCK)
+    amax = xb.abs().amax(dim=2)
+
+    def code_of(v):
+        return v.clamp(max=FP8_MAX).to(torch.float8_e4m3fn).view(torch.uint8).to(torch.int32)
+
+    def attempt(code):
+        t = code.clamp(0, 0x7E).to(torch.uint8).view(torch.float8_e4m3fn).float() * g          # [rows, blocks]
+        inv = torch.where(t > 0, 1.0 / t.clamp_min(1e-30), torch.zeros_like(t))
+        codes = _e2m1_codes(xb * inv[..., None])
+        err = ((_e2m1_decode(codes) * t[..., None] - xb) ** 2).sum(dim=2)
+        return codes, err
+
+    lo = code_of(amax / (6.0 * g))
+    best_code = lo.clone()
+    best, best_err = attempt(lo)
+    if search:
+        cands = [code_of(amax / (4.0 * g))] + [lo + s for s in range(-1, 6) if s != 0]
+        for c in cands:
+            valid = (c >= 0) & (c <= 0x7E)
+            codes, err = attempt(c)
+            take = valid & (err < best_err)
+            best = torch.where(take[..., None], codes, best)
+            best_err = torch.where(take, err, best_err)
+            best_code = torch.where(take, c, best_code)
+    packed = pack_fp4(best.reshape(-1, D))
+    out = torch.cat([packed, best_code.to(torch.uint8)], dim=1)
+    return out.reshape(*x.shape[:-1], D // 2 + D // NVFP4_BLOCK)
+
+
+def nvfp4_kv_dequantize(rows: torch.Tensor, D: int, g: float = 1.0) -> torch.Tensor:
+    """Inverse of :func:`nvfp4_kv_quantize`: uint8 ``[..., D/2 + D/16]`` -> fp32 ``[..., D]``."""
+    flat = rows.reshape(-1, rows.shape[-1])
+    vals = _e2m1_decode(unpack_fp4(flat[:, :D // 2])).view(flat.shape[0], D // NVFP4_BLOCK, NVFP4_BLOCK)
+    sc = flat[:, D // 2:].contiguous().view(torch.float8_e4m3fn).float() * g
+    return (vals * sc[..., None]).reshape(*rows.shape[:-1], D)
+
+
 # ------------------------------------------------------------------------------- MXFP8
 def mxfp8_quantize(x: torch.Tensor):
     """``x [rows, K]`` → (e4m3 [rows, K], e8m0 exponent bytes uint8 [rows, K/32])."""

@@ -133,3 +133,35 @@ def test_draft_tree_rows_match_their_chains_and_commit_compacts_the_path():
     assert torch.allclose(nxt, want, atol=2e-4)
     with pytest.raises(ValueError):
         eng.plan_tree([(seq, [1, 2], [0, 0])])
+
+
+def test_nvfp4_kv_rows_and_the_scale_search():
+    """KV rows in NVFP4 (``--kv-cache-dtype nvfp4`` / ``nvfp4_4over6``): 4-bit codes plus one E4M3 scale per 16 elements.  The
+    searched scale never does worse than the plain one on any block, a block whose values sit on the grid comes back exactly,
+    and decoding over such a cache stays close to the fp32 cache."""
+    from blaze_b200.quant import nvfp4_kv_dequantize, nvfp4_kv_quantize
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 2, 64, generator=g) * torch.rand(64, 2, 1, generator=g) * 3
+    plain, best = nvfp4_kv_quantize(x), nvfp4_kv_quantize(x, search=True)
+    assert plain.shape == (64, 2, 64 // 2 + 64 // 16) and plain.dtype == torch.uint8
+    e_plain = ((nvfp4_kv_dequantize(plain, 64) - x) ** 2).view(64, 2, 4, 16).sum(-1)
+    e_best = ((nvfp4_kv_dequantize(best, 64) - x) ** 2).view(64, 2, 4, 16).sum(-1)
+    assert (e_best <= e_plain + 1e-6).all() and e_best.sum() < 0.95 * e_plain.sum()
+    rel = (nvfp4_kv_dequantize(best, 64) - x).norm() / x.norm()
+    assert rel < 0.12
+    grid = torch.tensor([0.0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.5, -1, -1.5, -2, -3, -4, -6, 6]).repeat(4) * 0.25
+    assert torch.equal(nvfp4_kv_dequantize(nvfp4_kv_quantize(grid[None]), 64)[0], grid)
+    # through the engine: prefill, then a decode step over the cache, fp32 pages against the 4-bit ones
+    ps = torch.randint(0, 1024, (3, 40), generator=g).tolist()
+    cfg = named_config("tiny")
+    m = Model.random_init(cfg, seed=0, device="cpu", dtype=torch.float32)
+    out = {}
+    for kvd in ("fp32", "nvfp4", "nvfp4_4over6"):
+        eng = Engine(m, EngineConfig(max_seqs=4, max_model_len=128, kv_dtype=kvd, use_graphs=False))
+        seqs = [eng.open_from() for _ in ps]
+        eng.forward(eng.plan([(s, p, 1) for s, p in zip(seqs, ps)]), "logits")
+        out[kvd] = eng.forward(eng.plan([(s, [7], 1) for s in seqs]), "logits")
+        if kvd != "fp32":
+            assert eng.kv.k[0].dtype == torch.uint8 and eng.kv.k[0].shape[-1] == 64 // 2 + 64 // 16
+    cos = {k: torch.nn.functional.cosine_similarity(out[k], out["fp32"], dim=1).min().item() for k in ("nvfp4", "nvfp4_4over6")}
+    assert cos["nvfp4"] > 0.97 and cos["nvfp4_4over6"] > 0.97, cos
