@@ -19,8 +19,8 @@ averaged, normed and rotated to the block's first position; a row scores a block
 ``relu(q . k)`` over ``sqrt(dim)`` and attends to the tokens of its ``budget / compress_ratio`` best blocks (ties: the
 earlier block) plus those of the incomplete block it stands in.  While a context has no more blocks than that, every key
 is selected and attention is dense.  Here the raw index keys are paged like K and V (``KVCache.idx_k``), compressed keys
-are formed when a row scores them, and the selection is a mask for the oracle attention; the attention kernels read whole
-sequences, so on them a context beyond the budget is refused rather than answered densely."""
+are formed when a row scores them, and the selection is a mask for the torch attention; the attention kernels read whole
+sequences, so steps with a context beyond the budget take the masked torch attention on either op set."""
 from __future__ import annotations
 
 import math

@@ -587,8 +587,13 @@ class CudaOps:
     def attention(self, q, model, batch, kv, layer_idx, scale, splits: int = 0, max_ctas: int = 0, allowed=None):
         """Sequences with few query rows (decode, verify) go to the decode kernel, the rest to the row-block kernel."""
         if allowed is not None:
-            raise NotImplementedError("the attention kernels read every key of a sequence: a sparse selection (a context beyond "
-                                      "the indexer's budget) runs on the oracle op set only")
+            # a sparse selection (a context beyond an indexer's budget): the kernels read every key of a sequence, so these
+            # steps take the masked torch attention over the pages on this device (correct, not fast)
+            from . import ref
+            kl, vl = kv.logical_kv(layer_idx)
+            o = ref.paged_attention(q, kl, vl, kv.block_table, batch.h_slots, batch.h_q_start, batch.h_ctx_len, scale,
+                                    tree_mask=getattr(batch, "tree_mask", None), allowed=allowed)
+            return o.reshape(q.shape[0], -1).contiguous()
         T, Hq, D = q.shape
         Hkv = kv.kv_heads
         group = Hq // Hkv

@@ -64,9 +64,5 @@ def test_streams_and_ngram_embedding_match_the_oracle_ops(gate, indexer):
         rows_k = pk[ek.kv.block_table[sk[0].row, :4].long()].float()
         rows_r = pr[er.kv.block_table[sr[0].row, :4].long()].float()
         assert rows_k.abs().sum() > 0 and torch.nn.functional.cosine_similarity(rows_k.flatten(), rows_r.flatten(), dim=0) > 0.999
-        # beyond the budget the kernels refuse instead of answering densely
-        cfg.indexer_budget = 16
-        with pytest.raises(NotImplementedError):
-            ek.forward(ek.plan([(s, [t], 1) for s, t in zip(sk, toks)]), "logits")
     torch.cuda.synchronize()
     assert mk.ops.take_status() == 0
