@@ -1,9 +1,11 @@
 #!/bin/bash
 # Builds the UNMODIFIED reference CUDA kernel library (its own CMake project, `kernels/`) for sm_100a into baseline/_ref/
 # and links the static library into one shared object that blaze_b200.benchmarks.reference_kernels loads through ctypes.
-# Needs only cmake, ninja, nvcc and cuBLAS; no Rust.  Usage: baseline/build_reference_kernels.sh [path to the reference checkout]
+# Needs only cmake, ninja, nvcc and cuBLAS; no Rust.  Usage: baseline/build_reference_kernels.sh <path to the reference checkout>
+# (or BLAZE_REFERENCE_DIR in the environment)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${BLAZE_REFERENCE_DIR:-}}"
+[ -n "$REF" ] && [ -d "$REF/kernels" ] || { echo "usage: $0 <path to the reference checkout>" >&2; exit 2; }
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 mkdir -p "$OUT/build"
