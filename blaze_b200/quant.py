@@ -112,7 +112,9 @@ def resolve_format(names: Dict[str, Tuple[str, Tuple[int, ...]]], module: str) -
                     sdt, sshape = names[f"{module}.{sname}"]
                     if sdt in ("U8", "uint8", "F8_E8M0", "float8_e8m0fnu"):
                         return Format.MXFP8
-                    if len(sshape) == 2 and sshape[0] > 1 and sshape[1] > 1:
+                    # a block-scale grid is [ceil(N / bn), ceil(K / bk)]: more than one column, or fewer rows than the weight
+                    # has (a per-channel scale is [N] or [N, 1]); a module of one block row still has its columns
+                    if len(sshape) == 2 and (sshape[1] > 1 or 1 < sshape[0] < shape[0]):
                         return Format.FP8_BLOCK
                     if len(sshape) >= 1 and max(sshape) > 1:
                         return Format.FP8_CHANNEL

@@ -11,12 +11,44 @@ from blaze_b200.models.qwen3 import DenseMlp
 from blaze_b200.weights import save_safetensors
 
 
-def write(model, out_dir: str, prefix: str = "model.language_model.", ple_shards: int = 2) -> None:
+QUANTISED = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+def quantised(name: str, w: torch.Tensor, fmt: str):
+    """Tensors of one linear module ``name`` (without ``.weight``) in a checkpoint format: ``nvfp4`` (compressed-tensors names),
+    ``nvfp4_modelopt``, ``mxfp8``, ``fp8_block`` (128 x 128), ``fp8_channel``, ``fp8_tensor``."""
+    from blaze_b200 import quant
+    w = w.float()
+    if fmt in ("nvfp4", "nvfp4_modelopt"):
+        packed, sf, g = quant.nvfp4_quantize(w)
+        if fmt == "nvfp4":
+            return {name + ".weight_packed": packed, name + ".weight_scale": sf, name + ".weight_global_scale": (1.0 / g).reshape(1).float()}
+        return {name + ".weight": packed, name + ".weight_scale": sf, name + ".weight_scale_2": g.reshape(1).float()}
+    if fmt == "mxfp8":
+        q, e8 = quant.mxfp8_quantize(w)
+        return {name + ".weight": q, name + ".weight_scale": e8.view(torch.uint8)}
+    if fmt == "fp8_block":
+        q, sc = quant.fp8_block_quantize(w)
+        return {name + ".weight": q, name + ".weight_scale_inv": sc.float()}
+    if fmt == "fp8_channel":
+        q, sc = quant.fp8_channel_quantize(w)
+        return {name + ".weight": q, name + ".weight_scale": sc.float().reshape(-1, 1)}
+    if fmt == "fp8_tensor":
+        sc = (w.abs().amax() / 448.0).clamp_min(1e-12)
+        return {name + ".weight": quant.to_e4m3(w / sc), name + ".weight_scale": sc.reshape(1).float()}
+    raise ValueError(fmt)
+
+
+def write(model, out_dir: str, prefix: str = "model.language_model.", ple_shards: int = 2, fmt: str = "dense") -> None:
+    """``fmt``: the format of the attention and MLP projections (routers, gates, norms and embeddings stay bf16)."""
     cfg = model.cfg
     D, H = cfg.head_dim, cfg.hidden_size
     t = {}
 
     def put(name, w):
+        if fmt != "dense" and name.endswith(".weight") and name[:-7].rsplit(".", 1)[-1] in QUANTISED and "shared_expert_gate" not in name:
+            t.update(quantised(name[:-7], w.detach(), fmt))
+            return
         t[name] = w.detach().float().to(torch.bfloat16 if w.is_floating_point() else w.dtype).contiguous()
     put(prefix + "embed_tokens.weight", model.embed)
     put("lm_head.weight", model.lm_head.dequant())

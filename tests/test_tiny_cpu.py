@@ -165,3 +165,68 @@ def test_nvfp4_kv_rows_and_the_scale_search():
             assert eng.kv.k[0].dtype == torch.uint8 and eng.kv.k[0].shape[-1] == 64 // 2 + 64 // 16
     cos = {k: torch.nn.functional.cosine_similarity(out[k], out["fp32"], dim=1).min().item() for k in ("nvfp4", "nvfp4_4over6")}
     assert cos["nvfp4"] > 0.97 and cos["nvfp4_4over6"] > 0.97, cos
+
+
+@pytest.mark.parametrize("fmt,want,lo", [("nvfp4", "NVFP4", 0.90), ("nvfp4_modelopt", "NVFP4", 0.90), ("mxfp8", "MXFP8", 0.99),
+                                         ("fp8_block", "FP8_BLOCK", 0.99), ("fp8_channel", "FP8_CHANNEL", 0.99),
+                                         ("fp8_tensor", "FP8_CHANNEL", 0.98)])
+def test_checkpoints_in_every_weight_format_load(tmp_path, fmt, want, lo):
+    """A local checkpoint whose projections are stored in each supported format (tensor names as the quantisation tools
+    write them) loads into that format: the stored codes and scales arrive unchanged (the loaded weight dequantises to what
+    was written), and the model's logits follow the bf16 model's within the format's error."""
+    import synthetic_checkpoint
+    from blaze_b200.quant import Format
+    cfg = named_config("tiny")
+    dense = Model.random_init(cfg, seed=3, device="cpu", dtype=torch.float32)
+    synthetic_checkpoint.write(dense, str(tmp_path), prefix="model.", fmt=fmt)
+    m = Model.load(str(tmp_path), device="cpu", dtype=torch.float32)
+    L0 = m.layers[0]
+    assert L0.attn.qkv.fmt == getattr(Format, want) and L0.mlp.down.fmt == getattr(Format, want) and m.lm_head.fmt == Format.DENSE
+    # exactness of the round trip: dequantising the loaded module gives the dequantisation of what the writer stored
+    w = dense.layers[0].mlp.down.dequant()
+    stored = synthetic_checkpoint.quantised("x", w, fmt)
+    from blaze_b200 import quant
+    if fmt.startswith("nvfp4"):
+        g = stored.get("x.weight_scale_2")
+        g = g if g is not None else 1.0 / stored["x.weight_global_scale"]
+        ref_w = quant.nvfp4_dequantize(stored.get("x.weight_packed", stored.get("x.weight")), stored["x.weight_scale"], g[0])
+    elif fmt == "mxfp8":
+        ref_w = quant.mxfp8_dequantize(stored["x.weight"], stored["x.weight_scale"])
+    elif fmt == "fp8_block":
+        ref_w = quant.fp8_block_dequantize(stored["x.weight"], stored["x.weight_scale_inv"])
+    else:
+        ref_w = stored["x.weight"].float() * stored["x.weight_scale"].float().reshape(-1, 1)
+    assert torch.allclose(L0.mlp.down.dequant().float(), ref_w.float(), atol=1e-6)
+    assert (ref_w - w).norm() / w.norm() < (0.15 if fmt.startswith("nvfp4") else 0.05)
+    toks = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(1))
+    out = {}
+    for name, model in (("dense", dense), ("loaded", m)):
+        eng = Engine(model, EngineConfig(max_seqs=2, max_model_len=64, kv_dtype="fp32", use_graphs=False))
+        s = eng.open_from()
+        out[name] = eng.forward(eng.plan([(s, toks.tolist(), len(toks))]), "logits")
+    cos = torch.nn.functional.cosine_similarity(out["loaded"], out["dense"], dim=1)
+    assert cos.min().item() > lo, (fmt, cos.min().item())
+
+
+def test_a_hybrid_moe_checkpoint_with_mxfp8_projections_loads(tmp_path):
+    """The hybrid family (Gated DeltaNet + gated attention + MoE with a shared expert) from a checkpoint whose attention,
+    expert and shared-expert projections are MXFP8 while the GDN projections, router and gates are bf16."""
+    import synthetic_checkpoint
+    from blaze_b200.quant import Format
+    cfg = named_config("tiny-hybrid")
+    dense = Model.random_init(cfg, seed=3, device="cpu", dtype=torch.float32)
+    synthetic_checkpoint.write(dense, str(tmp_path), fmt="mxfp8")
+    m = Model.load(str(tmp_path), device="cpu", dtype=torch.float32)
+    assert m.cfg.layer_types == cfg.layer_types and m.cfg.num_experts == 8
+    assert m.layers[1].attn.qkv.fmt == Format.MXFP8 and m.layers[0].mlp.experts.gate_up[3].fmt == Format.MXFP8
+    assert m.layers[0].mlp.shared.down.fmt == Format.MXFP8 and m.layers[0].gdn.in_proj.fmt == Format.DENSE
+    assert m.layers[0].mlp.router.fmt == Format.DENSE
+    toks = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(1)).tolist()
+    out = {}
+    for name, model in (("dense", dense), ("loaded", m)):
+        eng = Engine(model, EngineConfig(max_seqs=2, max_model_len=64, kv_dtype="fp32", use_graphs=False))
+        s = eng.open_from()
+        out[name] = eng.forward(eng.plan([(s, toks, len(toks))]), "logits")
+    cos = torch.nn.functional.cosine_similarity(out["loaded"], out["dense"], dim=1)
+    # a row whose routing flips an expert under the 8-bit weights moves further than the others
+    assert cos.mean().item() > 0.985 and cos.min().item() > 0.9, (cos.mean().item(), cos.min().item())
