@@ -99,6 +99,9 @@ class LLM:
                                                           kv_dtype=kv_cache_dtype, chunk=chunk, use_graphs=use_graphs,
                                                           kv_rotate=kv_rotate))
         eos = tuple(eos_ids) or tuple(cfg.eos_token_ids)
+        if self.model.cfg.has_hc and (drafter is not None or spec_method in ("mtp", "eagle", "dflash")):
+            # a drafter reads the target's hidden rows; a hyper-connection model hands out its streams instead
+            raise ValueError("model drafters are not built for hyper-connection models: use --spec-method ngram or suffix")
         if drafter is None and spec_method in ("mtp", "eagle", "dflash"):
             from .models.drafter import build_drafter
             with log.Stage("drafter"):

@@ -288,3 +288,8 @@ def test_a_checkpoint_with_an_indexer_loads(tmp_path):
     assert loaded.model.cfg.indexer_budget == 32 and loaded.model.layers[1].attn.index is not None
     p = torch.randint(2, 1024, (70,), generator=torch.Generator().manual_seed(2)).tolist()
     assert loaded.generate([p], GREEDY)[0].token_ids == src.generate([p], GREEDY)[0].token_ids
+
+
+def test_model_drafters_are_refused_for_stream_models():
+    with pytest.raises(ValueError, match="hyper-connection"):
+        _llm(spec_method="mtp")
