@@ -147,6 +147,10 @@ def service_parser(p: argparse.ArgumentParser) -> None:
                    help="default thinking budget in tokens of chat requests (requests override it with thinking_token_budget)")
     g.add_argument("--vision", default="auto", choices=["auto", "gpu", "cpu", "off"], help="where the vision tower runs; off: no image input")
     g.add_argument("--vision-threads", type=int, default=None, help="CPU threads of a vision tower that runs on the CPU")
+    g.add_argument("--mm-encoder-batch", type=int, default=None,
+                   help="most images in one pass of the vision tower: 0 (the reference's auto) or 1; images are encoded one at a time here")
+    g.add_argument("--mm-encoder-patches", type=int, default=None,
+                   help="patch budget of one pass of the vision tower: accepted and unused, a pass encodes one image whatever its size")
     g.add_argument("--mm-processor-kwargs", default=None, metavar="JSON",
                    help="image processor settings over the checkpoint's (min_pixels, max_pixels, size.shortest_edge / longest_edge); "
                         "requests override them with mm_processor_kwargs")
@@ -245,6 +249,7 @@ _COMPAT = {
     "prefill_a16": (("none",), "prefill quantises activations like decode does; 16-bit prefill inputs are not built"),
     "l2_prefetch_mib": ((None, 0, 0.0), "there is no L2 weight prefetch between kernels"),
     "draft_head_vram": (("auto", "on"), "a drafter's LM head always lives in device memory"),
+    "mm_encoder_batch": ((None, 0, 1), "the vision tower encodes one image per pass; passes over several images are not built"),
     "pp_remote": ((None,), "pipeline stages are ranks of one torch.distributed job: launch every stage with torch.distributed.run "
                            "(--nnodes / --node-rank for several machines) and --pp"),
 }
